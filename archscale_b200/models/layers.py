@@ -1,0 +1,30 @@
+"""``Linear``: an ``nn.Linear`` whose matmuls run the tcgen05 GEMM (or its MXFP8 variant)."""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from archscale_b200 import ops
+
+
+class Linear(nn.Linear):
+    """Drop-in ``nn.Linear`` (same parameter names / state-dict keys).
+
+    * bf16 CUDA inputs → ``ops.linear`` (hand-written GEMM for fwd, dgrad, wgrad);
+    * ``mxfp8=True`` → block-scaled E4M3 GEMM with bf16 master weights
+      (replaces the ``te.Linear`` swap of the reference, `precision.py:192-251`);
+    * anything else (CPU, fp32) → ``F.linear``.
+    The weight is cast to the activation dtype when they differ (fp32 masters, bf16 compute).
+    """
+
+    mxfp8: bool = False
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        w, b = self.weight, self.bias
+        if w.dtype != x.dtype:
+            w = w.to(x.dtype)
+            b = b.to(x.dtype) if b is not None else None
+        if self.mxfp8 and x.is_cuda:
+            from archscale_b200.ops import mxfp8
+            return mxfp8.linear_mxfp8(x, w, b)
+        return ops.linear(x, w, b)

@@ -1,0 +1,118 @@
+"""Causal / sliding-window / packed-varlen attention with GQA, returning the log-sum-exp.
+
+Semantics follow the flash-attention call the reference makes
+(`lit_gpt/attention.py:63-68,121,347-424`): layout ``(B, T, H, D)``, causal, optional
+left window ``(w-1, 0)`` (query ``i`` sees keys ``i-w+1 .. i``), optional ``cu_seqlens``
+(documents packed in one row never attend across a boundary), K/V with ``G`` heads shared
+by ``H/G`` query heads, optional learnable per-head sink logit (softmax denominator gets
+an extra ``exp(sink)`` term, `lit_gpt/oss_attn.py:186-197`).
+
+CUDA path: ``csrc/attention.cu`` — tcgen05 QKᵀ and PV with S/P/O accumulators in TMEM,
+K/V tiles streamed by TMA, online softmax in registers; backward recomputes P from the
+saved LSE and accumulates dQ deterministically.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import backend
+
+
+def _build_mask(Tq: int, Tk: int, device, window: Tuple[int, int], cu_seqlens: Optional[torch.Tensor]):
+    """Boolean (Tq, Tk) mask, True = may attend.  Queries are aligned to the end of the keys."""
+    qi = torch.arange(Tq, device=device).unsqueeze(1) + (Tk - Tq)
+    kj = torch.arange(Tk, device=device).unsqueeze(0)
+    allowed = kj <= qi
+    if window[0] >= 0:
+        allowed &= kj >= qi - window[0]
+    if cu_seqlens is not None:
+        pos = torch.arange(Tk, device=device)
+        seg = torch.bucketize(pos, cu_seqlens[1:].to(device), right=True)
+        allowed &= seg[Tk - Tq:].unsqueeze(1) == seg.unsqueeze(0)
+    return allowed
+
+
+def attention_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional[float] = None,
+                  window: Tuple[int, int] = (-1, -1), cu_seqlens: Optional[torch.Tensor] = None,
+                  sink: Optional[torch.Tensor] = None, return_lse: bool = False):
+    """fp32 dense-softmax oracle.  q:(B,Tq,H,D) k,v:(B,Tk,G,D)."""
+    B, Tq, H, D = q.shape
+    Tk, G = k.shape[1], k.shape[2]
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+    qf = q.float().permute(0, 2, 1, 3)                                      # B H Tq D
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(H // G, dim=1)     # B H Tk D
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(H // G, dim=1)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    mask = _build_mask(Tq, Tk, q.device, window, cu_seqlens)
+    s = s.masked_fill(~mask, float("-inf"))
+    if sink is not None:
+        s = torch.cat((s, sink.float().view(1, H, 1, 1).expand(B, H, Tq, 1)), dim=-1)
+    lse = torch.logsumexp(s, dim=-1)                                        # B H Tq
+    p = torch.exp(s - lse.unsqueeze(-1))
+    if sink is not None:
+        p = p[..., :-1]
+    o = torch.matmul(p, vf).permute(0, 2, 1, 3).to(q.dtype)
+    return (o, lse) if return_lse else o
+
+
+def _sdpa_fallback(q, k, v, scale, window, cu_seqlens):
+    """Library path used only when the extension is explicitly disabled on a GPU."""
+    B, Tq, H, D = q.shape
+    G = k.shape[2]
+    if window[0] < 0 and cu_seqlens is None and Tq == k.shape[1]:
+        o = torch.nn.functional.scaled_dot_product_attention(
+            q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True, scale=scale,
+            enable_gqa=(H != G))
+        return o.transpose(1, 2)
+    mask = _build_mask(Tq, k.shape[1], q.device, window, cu_seqlens)
+    o = torch.nn.functional.scaled_dot_product_attention(
+        q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), attn_mask=mask, scale=scale,
+        enable_gqa=(H != G))
+    return o.transpose(1, 2)
+
+
+class _AttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, scale, window_left, cu_seqlens):
+        ext = backend.require_extension()
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        out, lse = ext.attn_fwd(q, k, v, scale, window_left, cu_seqlens)
+        backend.count_launch()
+        ctx.save_for_backward(q, k, v, out, lse, cu_seqlens if cu_seqlens is not None else torch.empty(0))
+        ctx.scale, ctx.window_left, ctx.varlen = scale, window_left, cu_seqlens is not None
+        ctx.mark_non_differentiable(lse)
+        return out, lse
+
+    @staticmethod
+    def backward(ctx, dout, _dlse):
+        ext = backend.require_extension()
+        q, k, v, out, lse, cu = ctx.saved_tensors
+        dq, dk, dv = ext.attn_bwd(dout.contiguous(), q, k, v, out, lse, ctx.scale, ctx.window_left,
+                                  cu if ctx.varlen else None)
+        backend.count_launch(3)
+        return dq, dk, dv, None, None, None
+
+
+def cuda_supported(q, k, v, sink) -> bool:
+    D = q.shape[-1]
+    return (q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16
+            and D in (64, 128) and v.shape[-1] == D and sink is None and q.shape[1] == k.shape[1]
+            and q.shape[2] % k.shape[2] == 0)
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional[float] = None,
+              window: Tuple[int, int] = (-1, -1), cu_seqlens: Optional[torch.Tensor] = None,
+              sink: Optional[torch.Tensor] = None, return_lse: bool = False):
+    scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
+    if q.is_cuda and cuda_supported(q, k, v, sink) and backend.use_cuda_kernel("attention", q, k, v):
+        if cu_seqlens is not None:
+            assert q.shape[0] == 1, "packed varlen attention expects batch 1"
+            cu_seqlens = cu_seqlens.to(torch.int32).contiguous()
+        out, lse = _AttnFn.apply(q, k, v, float(scale), int(window[0]), cu_seqlens)
+        return (out, lse) if return_lse else out
+    if q.is_cuda and sink is None and not return_lse:
+        return _sdpa_fallback(q, k, v, scale, window, cu_seqlens)
+    return attention_ref(q, k, v, scale, window, cu_seqlens, sink, return_lse)

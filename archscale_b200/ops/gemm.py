@@ -1,0 +1,122 @@
+"""Dense GEMM entry points and the ``linear`` autograd op built on them.
+
+Three operand layouts cover forward, dgrad and wgrad of ``y = x @ Wᵀ``
+(``nn.Linear`` everywhere in the reference, e.g. `lit_gpt/attention.py:42-48`,
+`lit_gpt/model.py:636-637`):
+
+* ``matmul_nt(a[M,K], b[N,K])  = a @ bᵀ``  (forward; both operands K-major)
+* ``matmul_nn(a[M,K], b[K,N])  = a @ b``   (dgrad; B is N-major)
+* ``matmul_tn(a[K,M], b[K,N])  = aᵀ @ b``  (wgrad; both operands MN-major)
+
+CUDA path: ``csrc/gemm_bf16.cu`` — persistent, warp-specialised tcgen05 kernel: a TMA
+producer warp fills a multi-stage shared-memory ring, one elected thread issues
+``tcgen05.mma`` into double-buffered TMEM accumulators, four epilogue warps drain TMEM with
+``tcgen05.ld`` and store bf16 or accumulate fp32.  All three layouts run the same kernel
+with different TMA boxes and UMMA descriptor major-ness.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import backend
+
+
+def _cuda_ok(a: torch.Tensor, b: torch.Tensor, M: int, N: int, K: int) -> bool:
+    return (a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and K % 8 == 0 and N % 8 == 0 and M % 8 == 0
+            and K >= 64 and M >= 1 and a.dim() == 2 and b.dim() == 2
+            and a.stride(-1) == 1 and b.stride(-1) == 1
+            and a.stride(0) % 8 == 0 and b.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0)
+
+
+def matmul_nt(a: torch.Tensor, b: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """a:(M,K) b:(N,K) → a @ bᵀ : (M,N)."""
+    M, K = a.shape
+    N = b.shape[0]
+    if _cuda_ok(a, b, M, N, K) and backend.use_cuda_kernel("gemm", a, b):
+        backend.count_launch()
+        return backend.require_extension().gemm_bf16(a, b, 0, out_dtype or torch.bfloat16, None)
+    out = a @ b.t()
+    return out if out_dtype is None else out.to(out_dtype)
+
+
+def matmul_nn(a: torch.Tensor, b: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """a:(M,K) b:(K,N) → a @ b : (M,N)."""
+    M, K = a.shape
+    N = b.shape[1]
+    if _cuda_ok(a, b, M, N, K) and backend.use_cuda_kernel("gemm", a, b):
+        backend.count_launch()
+        return backend.require_extension().gemm_bf16(a, b, 1, out_dtype or torch.bfloat16, None)
+    out = a @ b
+    return out if out_dtype is None else out.to(out_dtype)
+
+
+def matmul_tn(a: torch.Tensor, b: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """a:(K,M) b:(K,N) → aᵀ @ b : (M,N)."""
+    K, M = a.shape
+    N = b.shape[1]
+    if _cuda_ok(a, b, M, N, K) and backend.use_cuda_kernel("gemm", a, b):
+        backend.count_launch()
+        return backend.require_extension().gemm_bf16(a, b, 2, out_dtype or torch.bfloat16, None)
+    out = a.t() @ b
+    return out if out_dtype is None else out.to(out_dtype)
+
+
+def matmul_tn_acc_(c: torch.Tensor, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """c (fp32, (M,N)) += aᵀ @ b with a:(K,M), b:(K,N)."""
+    K, M = a.shape
+    N = b.shape[1]
+    if c.dtype == torch.float32 and c.is_contiguous() and _cuda_ok(a, b, M, N, K) and backend.use_cuda_kernel("gemm", a, b, c):
+        backend.count_launch()
+        backend.require_extension().gemm_bf16(a, b, 2, torch.float32, c)
+        return c
+    if a.is_cuda:
+        c.add_((a.t() @ b).to(c.dtype))
+    else:
+        c.add_(a.float().t() @ b.float())
+    return c
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        ctx.save_for_backward(x, weight)
+        ctx.has_bias = bias is not None
+        x2 = x.reshape(-1, x.shape[-1])
+        y = matmul_nt(x2, weight)
+        if bias is not None:
+            y = y + bias.to(y.dtype)
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = matmul_nn(dy2, weight).view(x.shape)
+        if ctx.needs_input_grad[1]:
+            dw = matmul_tn(dy2, x2)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy.dtype)
+        return dx, dw, db
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ weightᵀ + bias``; bf16 CUDA inputs run the tcgen05 kernel for fwd, dgrad and wgrad."""
+    if (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and x.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0 and x.shape[-1] >= 64
+            and (x.numel() // x.shape[-1]) % 8 == 0
+            and backend.use_cuda_kernel("gemm", x, weight)):
+        if not x.is_contiguous():
+            x = x.contiguous()
+        return _LinearFn.apply(x, weight, bias)
+    if weight.dtype != x.dtype:
+        weight = weight.to(x.dtype)
+        bias = bias.to(x.dtype) if bias is not None else None
+    return torch.nn.functional.linear(x, weight, bias)

@@ -1,0 +1,65 @@
+"""Newton–Schulz orthogonalisation (quintic, 5 fixed coefficient sets).
+
+Behavioural reference: `lit_gpt/optim/muon.py:869-897` (``zeropower_via_newtonschulz5``) and the
+kernel split of `lit_gpt/optim/newton_schulz_triton.py:344-381`: per iteration
+``A = X Xᵀ`` (symmetric), ``B = b·A + c·A²`` (symmetric), ``X ← a·X + B X``; input cast to
+bf16, transposed when tall, divided by ``‖X‖_F + ε``.
+
+CUDA path: the three products run on the tcgen05 GEMM (``csrc/gemm_bf16.cu``) with fused
+``α·AB + β·C`` epilogues; ``A`` and ``B`` are symmetric so the NT layout serves all three.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import backend
+
+NS_COEFFS = (
+    (4.0848, -6.8946, 2.9270),
+    (3.9505, -6.3029, 2.6377),
+    (3.7418, -5.5913, 2.3037),
+    (2.8769, -3.1427, 1.2046),
+    (2.8366, -3.0525, 1.2012),
+)
+
+
+def newton_schulz_ref(G: torch.Tensor, epsilon: float = 1e-7, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    X = G.to(dtype)
+    tall = G.size(-2) > G.size(-1)
+    if tall:
+        X = X.mT
+    X = X / (X.norm(dim=(-2, -1), keepdim=True) + epsilon)
+    for a, b, c in NS_COEFFS:
+        A = X @ X.mT
+        Bm = b * A + c * (A @ A)
+        X = a * X + Bm @ X
+    return X.mT if tall else X
+
+
+def _ns_cuda_2d(G: torch.Tensor, epsilon: float) -> torch.Tensor:
+    ext = backend.require_extension()
+    X = G.to(torch.bfloat16)
+    tall = G.size(-2) > G.size(-1)
+    if tall:
+        X = X.t()
+    X = (X / (X.norm() + epsilon)).contiguous()
+    for a, b, c in NS_COEFFS:
+        # A = X Xᵀ            (NT with both operands = X)
+        A = ext.gemm_bf16_epi(X, X, 0, 1.0, 0.0, None)
+        # B = c·A A + b·A     (A symmetric → A Aᵀ = A A)
+        Bm = ext.gemm_bf16_epi(A, A, 0, c, b, A)
+        # X = B X + a·X       (NN)
+        X = ext.gemm_bf16_epi(Bm, X, 1, 1.0, a, X)
+        backend.count_launch(3)
+    return X.t() if tall else X
+
+
+def newton_schulz(G: torch.Tensor, epsilon: float = 1e-7) -> torch.Tensor:
+    """Orthogonalise the last two dims of ``G`` (2-D or batched 3-D)."""
+    m, n = G.shape[-2], G.shape[-1]
+    if (G.is_cuda and min(m, n) % 8 == 0 and max(m, n) % 8 == 0 and min(m, n) >= 64
+            and backend.use_cuda_kernel("newton_schulz", G)):
+        if G.dim() == 2:
+            return _ns_cuda_2d(G, epsilon)
+        return torch.stack([_ns_cuda_2d(g, epsilon) for g in G.reshape(-1, m, n)]).reshape(G.shape)
+    return newton_schulz_ref(G, epsilon)

@@ -1,0 +1,108 @@
+"""RMSNorm / LayerNorm / gated RMSNorm.
+
+Behavioural reference: `lit_gpt/rmsnorm.py:133-249` (oracles ``rms_norm_ref`` /
+``layer_norm_ref``), `:1182-1215` (``FusedRMSNorm``), `lit_gpt/ops/layernorm_gated.py:18-39`
+(gated oracle).  Statistics are always taken in fp32; the output has the input dtype.
+
+CUDA path: ``csrc/norm.cu`` — one warp-group per row block, fp32 statistics, the saved
+``rstd`` feeds a two-stage backward (per-CTA partial dw in fp32, then a column reduce).
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import backend
+
+
+# ------------------------------------------------------------------ oracles
+def rms_norm_ref(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float = 1e-5,
+                 residual: Optional[torch.Tensor] = None, prenorm: bool = False):
+    dtype = x.dtype
+    xf = x.float()
+    if residual is not None:
+        xf = xf + residual.float()
+    rstd = torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps)
+    out = xf * rstd
+    if weight is not None:
+        out = out * weight.float()
+    out = out.to(dtype)
+    return (out, xf.to(residual.dtype if residual is not None else dtype)) if prenorm else out
+
+
+def layer_norm_ref(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor],
+                   eps: float = 1e-5) -> torch.Tensor:
+    dtype = x.dtype
+    xf = x.float()
+    mean = xf.mean(dim=-1, keepdim=True)
+    var = xf.var(dim=-1, keepdim=True, correction=0)
+    out = (xf - mean) * torch.rsqrt(var + eps)
+    if weight is not None:
+        out = out * weight.float()
+    if bias is not None:
+        out = out + bias.float()
+    return out.to(dtype)
+
+
+def gated_rms_norm_ref(x: torch.Tensor, weight: torch.Tensor, z: Optional[torch.Tensor], eps: float = 1e-5,
+                       group_size: Optional[int] = None, norm_before_gate: bool = True) -> torch.Tensor:
+    """``rmsnorm(x) * w * silu(z)`` (norm_before_gate) or ``rmsnorm(x * silu(z)) * w``, per group."""
+    dtype = x.dtype
+    xf = x.float()
+    zf = z.float() if z is not None else None
+    if zf is not None and not norm_before_gate:
+        xf = xf * torch.nn.functional.silu(zf)
+    n = xf.shape[-1]
+    g = n if group_size is None else group_size
+    xg = xf.reshape(*xf.shape[:-1], n // g, g)
+    rstd = torch.rsqrt(xg.pow(2).mean(dim=-1, keepdim=True) + eps)
+    out = (xg * rstd).reshape(xf.shape) * weight.float()
+    if zf is not None and norm_before_gate:
+        out = out * torch.nn.functional.silu(zf)
+    return out.to(dtype)
+
+
+# ------------------------------------------------------------------ CUDA autograd
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        ext = backend.require_extension()
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1]).contiguous()
+        out, rstd = ext.rmsnorm_fwd(x2, weight, eps)
+        backend.count_launch()
+        ctx.save_for_backward(x2, weight, rstd)
+        ctx.shape = shape
+        return out.view(shape)
+
+    @staticmethod
+    def backward(ctx, dout):
+        ext = backend.require_extension()
+        x2, weight, rstd = ctx.saved_tensors
+        dout2 = dout.reshape(-1, ctx.shape[-1]).contiguous()
+        dx, dw = ext.rmsnorm_bwd(dout2, x2, weight, rstd)
+        backend.count_launch(2 if weight is not None else 1)
+        return dx.view(ctx.shape), (dw.to(weight.dtype) if weight is not None else None), None
+
+
+def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float = 1e-5) -> torch.Tensor:
+    ok_dtype = x.dtype in (torch.bfloat16, torch.float32) and (weight is None or weight.dtype in (torch.bfloat16, torch.float32))
+    if ok_dtype and x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384 and backend.use_cuda_kernel("rmsnorm", x, weight):
+        return _RMSNormFn.apply(x, weight, eps)
+    return rms_norm_ref(x, weight, eps)
+
+
+def layer_norm(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor],
+               eps: float = 1e-5) -> torch.Tensor:
+    if x.is_cuda:
+        # LayerNorm is only used by the phi4miniflash family; it runs torch's fused kernel in fp32.
+        return torch.nn.functional.layer_norm(x.float(), (x.shape[-1],),
+                                              None if weight is None else weight.float(),
+                                              None if bias is None else bias.float(), eps).to(x.dtype)
+    return layer_norm_ref(x, weight, bias, eps)
+
+
+def gated_rms_norm(x, weight, z=None, eps: float = 1e-5, group_size: Optional[int] = None,
+                   norm_before_gate: bool = True) -> torch.Tensor:
+    return gated_rms_norm_ref(x, weight, z, eps, group_size, norm_before_gate)

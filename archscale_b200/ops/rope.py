@@ -1,0 +1,135 @@
+"""Rotary position embedding (NeoX halves or interleaved pairs) and the cos/sin cache.
+
+Behavioural reference: `lit_gpt/fused_rotary_embedding.py:28-40,43-95` (rotation and its
+conjugate backward) and `lit_gpt/attention.py:443-507` (cache with YaRN concentration and
+NTK-by-parts interpolation).  Call sites use ``interleaved=False``.
+
+CUDA path: ``csrc/rope.cu`` (fused with the per-head QK RMSNorm, see :func:`qk_norm_rope`).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import backend
+from .norm import rms_norm_ref
+
+
+def build_rope_cache(seq_len: int, n_elem: int, dtype: torch.dtype, device, base: float = 10000,
+                     ntk_alpha: float = 1.0, ntk_beta: float = 32.0, scaling_factor: float = 1.0,
+                     initial_context_length: int = 4096) -> Tuple[torch.Tensor, torch.Tensor]:
+    freq = base ** (torch.arange(0, n_elem, 2, device=device) / n_elem)
+    if scaling_factor > 1.0:
+        concentration = 0.1 * math.log(scaling_factor) + 1.0
+        d_half = n_elem / 2
+        low = d_half * math.log(initial_context_length / (ntk_beta * 2 * math.pi)) / math.log(base)
+        high = d_half * math.log(initial_context_length / (ntk_alpha * 2 * math.pi)) / math.log(base)
+        assert 0 < low < high < d_half - 1
+        ramp = (torch.arange(d_half, dtype=torch.float32, device=device) - low) / (high - low)
+        keep = 1 - ramp.clamp(0, 1)  # 1 → extrapolate (high-frequency dims), 0 → interpolate
+        inv_freq = (1.0 / (scaling_factor * freq)) * (1 - keep) + (1.0 / freq) * keep
+    else:
+        concentration = 1.0
+        inv_freq = 1.0 / freq
+    theta = torch.outer(torch.arange(seq_len, device=device), inv_freq)
+    cos, sin = torch.cos(theta) * concentration, torch.sin(theta) * concentration
+    if dtype == torch.bfloat16:
+        return cos.bfloat16(), sin.bfloat16()
+    if dtype in (torch.float16, torch.int8):
+        return cos.half(), sin.half()
+    return cos, sin
+
+
+def _rotate(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, interleaved: bool, conj: bool,
+            positions: Optional[torch.Tensor]) -> torch.Tensor:
+    # x: (..., T, H, D); cos/sin: (T_cache, R/2) with R <= D
+    T = x.shape[-3]
+    if positions is not None:
+        cos, sin = cos[positions], sin[positions]
+    else:
+        cos, sin = cos[:T], sin[:T]
+    r = cos.shape[-1] * 2
+    cos = cos.float().unsqueeze(-2)
+    sin = sin.float().unsqueeze(-2)
+    if conj:
+        sin = -sin
+    xr = x[..., :r].float()
+    if interleaved:
+        x0, x1 = xr[..., 0::2], xr[..., 1::2]
+        o = torch.stack((x0 * cos - x1 * sin, x0 * sin + x1 * cos), dim=-1).flatten(-2)
+    else:
+        x0, x1 = xr[..., : r // 2], xr[..., r // 2:]
+        o = torch.cat((x0 * cos - x1 * sin, x0 * sin + x1 * cos), dim=-1)
+    return torch.cat((o.to(x.dtype), x[..., r:]), dim=-1) if r < x.shape[-1] else o.to(x.dtype)
+
+
+class _RopeRef(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin, interleaved, positions):
+        ctx.save_for_backward(cos, sin, positions if positions is not None else torch.empty(0))
+        ctx.interleaved = interleaved
+        ctx.has_pos = positions is not None
+        return _rotate(x, cos, sin, interleaved, False, positions)
+
+    @staticmethod
+    def backward(ctx, do):
+        cos, sin, pos = ctx.saved_tensors
+        return _rotate(do, cos, sin, ctx.interleaved, True, pos if ctx.has_pos else None), None, None, None, None
+
+
+def apply_rotary_emb_ref(x, cos, sin, interleaved: bool = False, positions=None):
+    return _RopeRef.apply(x, cos, sin, interleaved, positions)
+
+
+def qk_norm_rope_ref(q, k, q_weight, k_weight, cos, sin, eps: float = 1e-5, positions=None):
+    """Per-head RMSNorm over head_dim (optional) followed by RoPE (optional) on q and k."""
+    if q_weight is not None:
+        q = rms_norm_ref(q, q_weight, eps)
+        k = rms_norm_ref(k, k_weight, eps)
+    if cos is not None:
+        q = apply_rotary_emb_ref(q, cos, sin, False, positions)
+        k = apply_rotary_emb_ref(k, cos, sin, False, positions)
+    return q, k
+
+
+class _QKNormRopeFn(torch.autograd.Function):
+    """q:(B,T,H,D) k:(B,T,G,D) bf16 → normalised+rotated copies; one launch fwd, one bwd."""
+
+    @staticmethod
+    def forward(ctx, q, k, qw, kw, cos, sin, eps):
+        ext = backend.require_extension()
+        q = q.contiguous()
+        k = k.contiguous()
+        qo, ko, q_rstd, k_rstd = ext.qknorm_rope_fwd(q, k, qw, kw, cos, sin, eps)
+        backend.count_launch()
+        ctx.save_for_backward(q, k, qw, kw, cos, sin, q_rstd, k_rstd)
+        return qo, ko
+
+    @staticmethod
+    def backward(ctx, dqo, dko):
+        ext = backend.require_extension()
+        q, k, qw, kw, cos, sin, q_rstd, k_rstd = ctx.saved_tensors
+        dq, dk, dqw, dkw = ext.qknorm_rope_bwd(dqo.contiguous(), dko.contiguous(), q, k, qw, kw, cos, sin,
+                                               q_rstd, k_rstd)
+        backend.count_launch()
+        if qw is not None:
+            dqw, dkw = dqw.to(qw.dtype), dkw.to(kw.dtype)
+        return dq, dk, dqw, dkw, None, None, None
+
+
+def qk_norm_rope(q, k, q_weight, k_weight, cos, sin, eps: float = 1e-5, positions=None):
+    D = q.shape[-1]
+    full_rot = cos is None or cos.shape[-1] * 2 == D
+    if (q.dim() == 4 and q.dtype == torch.bfloat16 and positions is None and full_rot and D in (64, 128)
+            and (q_weight is not None or cos is not None)
+            and backend.use_cuda_kernel("qknorm_rope", q, k)):
+        if cos is not None:
+            cos, sin = cos[: q.shape[1]].contiguous(), sin[: q.shape[1]].contiguous()
+        return _QKNormRopeFn.apply(q, k, q_weight, k_weight, cos, sin, eps)
+    return qk_norm_rope_ref(q, k, q_weight, k_weight, cos, sin, eps, positions)
+
+
+def apply_rotary_emb(x, cos, sin, interleaved: bool = False, positions=None):
+    return apply_rotary_emb_ref(x, cos, sin, interleaved, positions)
