@@ -1,0 +1,326 @@
+"""Hybrid Muon / MuonH / AdamW / Adam-H optimizer working directly on the FSDP flat shards.
+
+Role of `lit_gpt/optim/muon.py:27-650` + `scalar_opts.py:380-443` + `pretrain.py:565-592,
+642-697` in the reference, re-designed around the flat shards of
+:class:`archscale_b200.parallel.fsdp.FSDPEngine`:
+
+* parameter classes follow the reference name rule: names without ``"weight"`` or containing
+  any of ``conv1d wte lm_head norm ln layernorm`` are *vectors* (AdamW; 2-D ones get the
+  Adam-hyperball step under MuonH except ``wte``), the rest are *matrices* (Muon);
+* the whole model is processed as one batch per step (no per-parameter generator tasks):
+  momentum update on the local shard slices → every matrix is assembled on one owner rank →
+  Newton–Schulz on the owner (same-shape matrices batched) → orthogonalised updates return to
+  the shards → MuonH norms are partial sums over local slices + **two** tiny all-reduces for the
+  whole model (the reference issues three per parameter batch);
+* expert tensors ``(E, out, in)`` are E independent matrices; each keeps its own norm under
+  MuonH (the reference normalises the local slab as a whole — see DESIGN notes);
+* state (``momentum``, ``variance``) lives in fp32 buffers aligned with the master shards, so
+  checkpoints consolidate it with the same gather as the weights.
+
+Transport of matrices between shards and owners is pluggable: ``torch.distributed``
+(all-gather + reduce-scatter; works on gloo) or the peer-memory kernels of
+:mod:`archscale_b200.parallel.symm`.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from archscale_b200 import ops
+from archscale_b200.optim import scalar_opts
+from archscale_b200.parallel import dist_utils as du
+from archscale_b200.parallel.fsdp import FlatGroup, FSDPEngine, ParamSpec
+
+VECTOR_NAMES = ("conv1d", "wte", "lm_head", "norm", "ln", "layernorm")
+
+
+def is_vector_param(name: str) -> bool:
+    n = name.lower()
+    return ("weight" not in n) or any(v in n for v in VECTOR_NAMES)
+
+
+@dataclass
+class _Mat:
+    """One 2-D matrix handled by Muon (a whole 2-D parameter or one expert of a 3-D tensor)."""
+    group: FlatGroup
+    spec: ParamSpec
+    sub: int            # expert index inside a 3-D parameter (0 for 2-D)
+    rows: int
+    cols: int
+    offset: int         # element offset inside the group's flat buffer
+    owner: int          # rank (inside the shard group) that orthogonalises it
+    norm_idx: int       # slot in the global norm vectors
+
+
+class ShardedOptimizer:
+    def __init__(self, engine: FSDPEngine, lr: float = 1e-3, betas: Tuple[float, float] = (0.9, 0.95),
+                 eps: float = 1e-8, weight_decay: float = 0.0, vector_weight_decay: float = 0.0,
+                 weight_lr_mult: float = 1.0, algorithm: str = "adamw", mu: float = 0.95, nesterov: bool = True,
+                 adjust_lr: Optional[str] = "spectral_norm", ns_epsilon: float = 1e-8,
+                 hyperball_exclude: Sequence[str] = ("transformer.wte.weight",), split_groups: bool = True) -> None:
+        """algorithm: "adamw" | "muon" | "muonh" | "lion".  ``split_groups=False`` applies AdamW with
+        ``weight_decay`` to every parameter (the non-μP branch of the reference)."""
+        assert algorithm in ("adamw", "muon", "muonh", "lion")
+        self.engine, self.lr, self.betas, self.eps = engine, lr, betas, eps
+        self.weight_decay, self.vector_weight_decay = weight_decay, vector_weight_decay
+        self.weight_lr_mult, self.algorithm = weight_lr_mult, algorithm
+        self.mu, self.nesterov, self.adjust_lr, self.ns_epsilon = mu, nesterov, adjust_lr, ns_epsilon
+        self.hyperball_exclude = set(hyperball_exclude)
+        self.split_groups = split_groups
+        self.step_count = 0
+        self.use_muon = algorithm in ("muon", "muonh")
+        self.use_muonh = algorithm == "muonh"
+        # per-group state buffers aligned with the master shard
+        self.m: Dict[int, torch.Tensor] = {}
+        self.v: Dict[int, torch.Tensor] = {}
+        self.mats: List[_Mat] = []
+        self.hyper_vecs: List[Tuple[FlatGroup, ParamSpec, int]] = []   # Adam-H parameters (group, spec, norm_idx)
+        self._classify()
+        self.last_lrs: Dict[str, float] = {}
+
+    # ------------------------------------------------------------------ setup
+    def _classify(self) -> None:
+        n_norm = 0
+        mats: List[_Mat] = []
+        self.kind: Dict[int, str] = {}    # id(spec) -> "vector" (element-wise rule) | "matrix" (Muon)
+        self.cls: Dict[int, str] = {}     # id(spec) -> "vector" | "matrix" by the name rule (lr mult / wd class)
+        for g in self.engine.groups():
+            gid = id(g)
+            self.m[gid] = torch.zeros_like(g.master)
+            need_v = False
+            for s in g.specs:
+                is_vec = is_vector_param(s.name) if self.split_groups else True
+                self.cls[id(s)] = "vector" if is_vec else "matrix"
+                elementwise = is_vec or len(s.shape) < 2 or not self.use_muon
+                self.kind[id(s)] = "vector" if elementwise else "matrix"
+                if elementwise:
+                    need_v = True
+                    if (self.use_muonh and len(s.shape) == 2 and is_vec and self.split_groups
+                            and s.name not in self.hyperball_exclude):
+                        self.hyper_vecs.append((g, s, n_norm))
+                        n_norm += 1
+                else:
+                    rows, cols = s.shape[-2], s.shape[-1]
+                    n_sub = s.numel // (rows * cols)
+                    for e in range(n_sub):
+                        mats.append(_Mat(g, s, e, rows, cols, s.offset + e * rows * cols, 0, n_norm))
+                        n_norm += 1
+            if need_v and self.algorithm != "lion":
+                self.v[gid] = torch.zeros_like(g.master)
+        # owners: biggest matrices first, round-robin → balanced Newton–Schulz work
+        order = sorted(range(len(mats)), key=lambda i: -(mats[i].rows * mats[i].cols))
+        load: Dict[Tuple[int, int], List[int]] = {}
+        for i in order:
+            mt = mats[i]
+            w = mt.group.world
+            key = (id(mt.group.group), w)
+            if key not in load:
+                load[key] = [0] * w
+            r = min(range(w), key=lambda k: load[key][k])
+            mt.owner = r
+            load[key][r] += mt.rows * mt.cols * min(mt.rows, mt.cols)
+        self.mats = mats
+        self.n_norm = n_norm
+
+    # ------------------------------------------------------------------ helpers
+    def _lr_for(self, kind: str) -> float:
+        return self.lr * (self.weight_lr_mult if kind == "matrix" else 1.0)
+
+    def _adjusted_lr(self, lr: float, rows: int, cols: int) -> float:
+        if self.adjust_lr is None:
+            return lr
+        if self.adjust_lr == "spectral_norm":
+            return lr * math.sqrt(rows / cols)
+        if self.adjust_lr == "clip_norm":
+            return lr * max(1.0, rows / cols) ** 0.5
+        if self.adjust_lr == "rms_norm":
+            return lr * 0.2 * math.sqrt(max(rows, cols))
+        raise ValueError(self.adjust_lr)
+
+    # ------------------------------------------------------------------ step
+    @torch.no_grad()
+    def step(self, lr: Optional[float] = None, weight_decay: Optional[float] = None) -> None:
+        if lr is not None:
+            self.lr = lr
+        if weight_decay is not None:
+            self.weight_decay = weight_decay
+        self.step_count += 1
+        eng = self.engine
+        dev = eng.device
+        x_sq = torch.zeros(max(self.n_norm, 1), dtype=torch.float32, device=dev)
+        u_sq = torch.zeros_like(x_sq)
+        pending_hyper: List[Tuple[torch.Tensor, torch.Tensor, int, float]] = []   # (x_slice, u_slice, norm_idx, lr)
+
+        # ---- vectors: AdamW / Lion / Adam-H on the local slices
+        hyper_idx = {id(s): k for (_, s, k) in self.hyper_vecs}
+        buckets: Dict[Tuple[float, float], List[Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]]] = {}
+        for g in eng.groups():
+            if g.grad is None:
+                continue
+            gid = id(g)
+            for s, lo, hi, slo in g.local_slices():
+                if self.kind[id(s)] != "vector":
+                    continue
+                n = hi - lo
+                x, gr, m = g.master[slo:slo + n], g.grad[slo:slo + n], self.m[gid][slo:slo + n]
+                v = self.v[gid][slo:slo + n] if gid in self.v else None
+                is_vec_cls = self.cls[id(s)] == "vector" and self.split_groups
+                lr_p = self.lr if is_vec_cls or not self.split_groups else self.lr * self.weight_lr_mult
+                wd = self.vector_weight_decay if is_vec_cls else self.weight_decay
+                if id(s) in hyper_idx:
+                    u = scalar_opts.adamw_direction_([m], [v], [gr], self.betas[0], self.betas[1], self.eps,
+                                                     self.step_count)[0]
+                    if wd:
+                        x.mul_(1 - lr_p * wd)
+                    k = hyper_idx[id(s)]
+                    x_sq[k] += x.float().pow(2).sum()
+                    u_sq[k] += u.float().pow(2).sum()
+                    pending_hyper.append((x, u, k, lr_p))
+                else:
+                    buckets.setdefault((lr_p, wd), []).append((x, gr, m, v))
+        for (lr_p, wd), items in buckets.items():
+            xs, gs, ms, vs = (list(t) for t in zip(*items))
+            if self.algorithm == "lion":
+                scalar_opts.lion_update_foreach(xs, gs, ms, lr_p, self.betas[0], self.betas[1], wd)
+            else:
+                scalar_opts.adamw_update_foreach(xs, gs, ms, vs, lr_p, self.betas[0], self.betas[1], wd,
+                                                 self.step_count, self.eps)
+
+        # ---- matrices: momentum on local slices, orthogonalise on owners, scatter back
+        if self.mats:
+            o_shards = self._orthogonalised_updates(u_sq)
+            lr_m = self._lr_for("matrix")
+            wd = self.weight_decay
+            for mt in self.mats:
+                g = mt.group
+                if g.grad is None:
+                    continue
+                a, b = g.shard_range()
+                lo, hi = max(mt.offset, a), min(mt.offset + mt.rows * mt.cols, b)
+                if lo >= hi:
+                    continue
+                x = g.master[lo - a:hi - a]
+                o = o_shards[id(g)][lo - a:hi - a]
+                if wd:
+                    x.mul_(1 - lr_m * wd)
+                if self.use_muonh:
+                    x_sq[mt.norm_idx] += x.float().pow(2).sum()
+                    pending_hyper.append((x, o, mt.norm_idx, lr_m))
+                else:
+                    x.add_(o.to(x.dtype), alpha=-self._adjusted_lr(lr_m, mt.rows, mt.cols))
+
+        # ---- hyperball: global norms (2 all-reduces for the whole model), update, renormalise
+        if pending_hyper:
+            if eng.mesh.fsdp > 1:
+                packed = torch.stack((x_sq, u_sq))
+                du.all_reduce_sum(packed, group=eng.mesh.fsdp_group)
+                x_sq, u_sq = packed[0], packed[1]
+            x_norm, u_norm = x_sq.sqrt(), u_sq.sqrt().clamp_min(self.ns_epsilon)
+            new_sq = torch.zeros_like(x_sq)
+            for x, u, k, lr_p in pending_hyper:
+                x.add_(u.to(x.dtype) * (x_norm[k] / u_norm[k] * lr_p).to(x.dtype), alpha=-1.0)
+                new_sq[k] += x.float().pow(2).sum()
+            if eng.mesh.fsdp > 1:
+                du.all_reduce_sum(new_sq, group=eng.mesh.fsdp_group)
+            scale = x_norm / new_sq.sqrt().clamp_min(self.ns_epsilon)
+            for x, u, k, lr_p in pending_hyper:
+                x.mul_(scale[k])
+        eng.mark_params_updated()
+
+    # ------------------------------------------------------------------ Muon transport + NS
+    @torch.no_grad()
+    def _orthogonalised_updates(self, u_sq: torch.Tensor) -> Dict[int, torch.Tensor]:
+        """Returns {id(group): bf16/fp32 shard-shaped tensor with the orthogonalised update O};
+        fills ``u_sq[norm_idx] = ‖O‖²`` (complete on every rank after the hyperball all-reduce)."""
+        eng = self.engine
+        groups = {id(mt.group): mt.group for mt in self.mats}
+        cdt = torch.bfloat16 if eng.is_cuda else torch.float32
+        out: Dict[int, torch.Tensor] = {}
+        for gid, g in groups.items():
+            if g.grad is None:
+                continue
+            # 1. momentum (fp32) and the pre-orthogonalisation update U on the local shard
+            m = self.m[gid]
+            mask_mats = [mt for mt in self.mats if mt.group is g]
+            a, b = g.shard_range()
+            u_shard = torch.zeros(g.shard_numel, dtype=cdt, device=eng.device)
+            for mt in mask_mats:
+                lo, hi = max(mt.offset, a), min(mt.offset + mt.rows * mt.cols, b)
+                if lo >= hi:
+                    continue
+                ms, gs = m[lo - a:hi - a], g.grad[lo - a:hi - a]
+                ms.mul_(self.mu).add_(gs)
+                u = gs.add(ms, alpha=self.mu) if self.nesterov else ms
+                u_shard[lo - a:hi - a].copy_(u)
+            # 2. assemble whole matrices (every rank gets the full flat U; owners use their matrices)
+            if g.world > 1:
+                if eng.symm is not None:
+                    u_full = eng.symm.gather_flat(g, u_shard)
+                else:
+                    u_full = torch.empty(g.padded, dtype=cdt, device=eng.device)
+                    du.all_gather_into(u_full, u_shard, group=g.group)
+            else:
+                u_full = u_shard
+            # 3. Newton–Schulz on owned matrices, same shapes batched
+            o_full = torch.zeros(g.padded, dtype=cdt, device=eng.device) if g.world > 1 else u_full
+            mine = [mt for mt in mask_mats if mt.owner == g.rank]
+            by_shape: Dict[Tuple[int, int], List[_Mat]] = {}
+            for mt in mine:
+                by_shape.setdefault((mt.rows, mt.cols), []).append(mt)
+            for (r, c), lst in by_shape.items():
+                stack = torch.stack([u_full[mt.offset:mt.offset + r * c].view(r, c) for mt in lst])
+                O = ops.newton_schulz(stack, epsilon=self.ns_epsilon)
+                sq = O.float().pow(2).sum(dim=(-2, -1))
+                for i, mt in enumerate(lst):
+                    o_full[mt.offset:mt.offset + r * c].copy_(O[i].reshape(-1))
+                    u_sq[mt.norm_idx] += sq[i]
+            # 4. return the updates to the shards
+            if g.world > 1:
+                if eng.symm is not None:
+                    o_shard = eng.symm.scatter_flat(g, o_full)
+                else:
+                    o_shard = torch.empty(g.shard_numel, dtype=cdt, device=eng.device)
+                    du.reduce_scatter_sum(o_shard, o_full, group=g.group)
+            else:
+                o_shard = o_full
+            out[gid] = o_shard
+        return out
+
+    # ------------------------------------------------------------------ checkpoint
+    def zero_grad(self) -> None:
+        self.engine.zero_grad()
+
+    @torch.no_grad()
+    def state_dict(self, rank0_only: bool = True) -> Dict:
+        """Consolidated, world-size independent: per-parameter ``momentum`` / ``variance`` tensors."""
+        eng = self.engine
+        keep = (not rank0_only) or eng.mesh.rank == 0
+        state: Dict[str, Dict[str, torch.Tensor]] = {}
+        for g in eng.groups():
+            gid = id(g)
+            for key, store in (("momentum", self.m), ("variance", self.v)):
+                if gid not in store:
+                    continue
+                full = eng._gather_master(store[gid], g)
+                if keep:
+                    for s in g.specs:
+                        state.setdefault(s.name, {})[key] = full[s.offset:s.offset + s.numel].view(s.shape).cpu().clone()
+                del full
+        return {"state": state, "step": self.step_count, "algorithm": self.algorithm} if keep else {}
+
+    @torch.no_grad()
+    def load_state_dict(self, sd: Dict) -> None:
+        self.step_count = int(sd.get("step", 0))
+        state = sd.get("state", {})
+        for g in self.engine.groups():
+            gid = id(g)
+            for s, lo, hi, slo in g.local_slices():
+                st = state.get(s.name)
+                if not st:
+                    continue
+                for key, store in (("momentum", self.m), ("variance", self.v)):
+                    if key in st and gid in store:
+                        store[gid][slo:slo + hi - lo].copy_(st[key].reshape(-1)[lo:hi].to(torch.float32))

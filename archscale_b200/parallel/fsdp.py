@@ -1,0 +1,576 @@
+"""Fully-sharded data parallel engine (the FSDP2 role of the reference, re-designed).
+
+What the reference gets from ``torch.distributed.fsdp.fully_shard`` per ``Block`` plus the root
+module with ``MixedPrecisionPolicy(param_dtype=bf16, reduce_dtype=fp32)``
+(`pretrain.py:536-563,806-807,924-928`) is provided here by one explicit engine:
+
+* every *unit* (each ``Block``; the root unit holds embeddings, final norm and head) owns flat
+  **fp32 master shards** (1/world of the unit, flat 1-D sharding so that the all-gather output
+  *is* the parameter storage — no copy-out), a cached low-precision copy of its shard, and an
+  fp32 gradient shard;
+* forward / backward: all-gather (low precision) into a pooled buffer on a communication
+  stream, prefetching the next unit while the current one computes; after the unit's backward
+  the unit's gradients are packed in fp32, reduce-scattered (sum in fp32), scaled by 1/world and
+  accumulated into the gradient shard on a second stream;
+* numerically sensitive parameters (``A_log``, ``D``, ``dt_bias`` …) travel in fp32;
+* expert-parallel parameters (``_ep_local``) are never gathered: each rank owns its experts;
+* hybrid sharding: with ``dp > 1`` the gradient shard is all-reduced over the replica group.
+
+Collectives are either ``torch.distributed`` (NCCL on GPUs, gloo on CPU test ranks) or the
+peer-memory kernels of :mod:`archscale_b200.parallel.symm` when ``fused_comm`` is on.
+Optimizers consume the flat shards through :meth:`FSDPEngine.shard_views`.
+"""
+from __future__ import annotations
+
+import contextlib
+from dataclasses import dataclass, field
+from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn as nn
+
+from . import dist_utils as du
+from .mesh import Mesh
+
+_FP32_NAME_HINTS = ("A_log", ".D", "dt_bias", "dt_proj.bias", "lambda_q", "lambda_k", "softmax_offset")
+
+
+def _keep_fp32(name: str) -> bool:
+    return any(name.endswith(h) or (h in name and h.startswith("lambda")) for h in _FP32_NAME_HINTS)
+
+
+@dataclass
+class ParamSpec:
+    name: str            # fully-qualified name in the model
+    param: nn.Parameter
+    shape: torch.Size
+    numel: int
+    offset: int          # element offset inside the group's flat (unsharded) buffer
+
+
+class BufferPool:
+    """Re-uses gathered-parameter / gradient buffers; cross-stream safety through events."""
+
+    def __init__(self) -> None:
+        self._free: Dict[Tuple[int, torch.dtype, str], List[Tuple[torch.Tensor, Optional[object]]]] = {}
+
+    def get(self, numel: int, dtype: torch.dtype, device, stream=None) -> torch.Tensor:
+        key = (numel, dtype, str(device))
+        lst = self._free.get(key)
+        if lst:
+            buf, ev = lst.pop()
+            if ev is not None:
+                (stream or torch.cuda.current_stream()).wait_event(ev)
+            return buf
+        return torch.empty(numel, dtype=dtype, device=device)
+
+    def put(self, buf: torch.Tensor) -> None:
+        ev = None
+        if buf.is_cuda:
+            ev = torch.cuda.Event()
+            ev.record()
+        self._free.setdefault((buf.numel(), buf.dtype, str(buf.device)), []).append((buf, ev))
+
+
+class FlatGroup:
+    """Parameters of one unit that share a gather dtype, stored as one flat sharded vector."""
+
+    def __init__(self, specs: List[ParamSpec], dtype: torch.dtype, world: int, rank: int, group, device,
+                 sharded: bool = True, align: int = 64) -> None:
+        self.specs, self.dtype, self.device = specs, dtype, device
+        self.sharded = sharded and world > 1
+        self.world = world if self.sharded else 1
+        self.rank = rank if self.sharded else 0
+        self.group = group if self.sharded else None
+        total = sum(s.numel for s in specs)
+        self.numel = total
+        mult = self.world * align
+        self.padded = ((total + mult - 1) // mult) * mult
+        self.shard_numel = self.padded // self.world
+        self.master: Optional[torch.Tensor] = None     # fp32 (shard_numel,)
+        self.shard_lp: Optional[torch.Tensor] = None   # gather dtype copy of master (None if dtype is fp32)
+        self.grad: Optional[torch.Tensor] = None       # fp32 (shard_numel,), accumulated over micro-steps
+        self.full: Optional[torch.Tensor] = None       # gathered (padded,) in gather dtype
+        self.full_grad: Optional[torch.Tensor] = None
+        self.gather_event = None
+        self.lp_stale = True
+
+    # -- construction --------------------------------------------------------------
+    @torch.no_grad()
+    def shard_from_params(self) -> None:
+        flat = torch.zeros(self.padded, dtype=torch.float32, device=self.device)
+        for s in self.specs:
+            flat[s.offset:s.offset + s.numel].copy_(s.param.detach().reshape(-1).to(torch.float32))
+        lo = self.rank * self.shard_numel
+        self.master = flat[lo:lo + self.shard_numel].clone()
+        del flat
+        self.lp_stale = True
+
+    def shard_range(self) -> Tuple[int, int]:
+        lo = self.rank * self.shard_numel
+        return lo, lo + self.shard_numel
+
+    def local_slices(self):
+        """Yield (spec, lo, hi, shard_lo) for the part of each parameter stored on this rank:
+        parameter elements [lo, hi) live at ``master[shard_lo : shard_lo + hi - lo]``."""
+        a, b = self.shard_range()
+        for s in self.specs:
+            lo, hi = max(s.offset, a), min(s.offset + s.numel, b)
+            if lo < hi:
+                yield s, lo - s.offset, hi - s.offset, lo - a
+
+    def refresh_lp(self) -> torch.Tensor:
+        if self.dtype == torch.float32:
+            return self.master
+        if self.shard_lp is None:
+            self.shard_lp = torch.empty_like(self.master, dtype=self.dtype)
+        if self.lp_stale:
+            self.shard_lp.copy_(self.master)
+            self.lp_stale = False
+        return self.shard_lp
+
+    def set_param_views(self, full: Optional[torch.Tensor]) -> None:
+        for s in self.specs:
+            if full is None:
+                s.param.data = torch.empty(0, dtype=self.dtype, device=self.device)
+            else:
+                s.param.data = full[s.offset:s.offset + s.numel].view(s.shape)
+
+
+class Unit:
+    def __init__(self, name: str, module: nn.Module, groups: List[FlatGroup], is_root: bool) -> None:
+        self.name, self.module, self.groups, self.is_root = name, module, groups, is_root
+        self.unsharded = False
+        self.bwd_pending = False      # a backward for this unit is expected in the current step
+        self.post_bwd_done = False
+
+
+class _PostBackward(torch.autograd.Function):
+    """Identity on the unit's inputs; its backward marks the end of the unit's backward pass."""
+
+    @staticmethod
+    def forward(ctx, engine, unit, *tensors):
+        ctx.engine, ctx.unit = engine, unit
+        return tensors if len(tensors) != 1 else tensors[0]
+
+    @staticmethod
+    def backward(ctx, *grads):
+        ctx.engine._post_backward(ctx.unit)
+        return (None, None) + grads
+
+
+class FSDPEngine:
+    def __init__(self, model: nn.Module, mesh: Optional[Mesh] = None, unit_classes: Sequence[type] = (),
+                 param_dtype: torch.dtype = torch.bfloat16, reshard_after_forward: bool = True,
+                 device: Optional[torch.device] = None, fused_comm: bool = False) -> None:
+        self.model = model
+        self.mesh = mesh or Mesh(world=1, rank=0, dp=1, fsdp=1, tp=1)
+        self.world, self.rank, self.group = self.mesh.fsdp, self.mesh.fsdp_rank, self.mesh.fsdp_group
+        self.param_dtype = param_dtype
+        self.reshard_after_forward = reshard_after_forward and self.world > 1
+        p0 = next(model.parameters())
+        self.device = device or p0.device
+        self.is_cuda = self.device.type == "cuda"
+        self.pool = BufferPool()
+        self.comm_stream = torch.cuda.Stream(self.device) if self.is_cuda else None
+        self.rs_stream = torch.cuda.Stream(self.device) if self.is_cuda else None
+        self.fused_comm = fused_comm and self.world > 1 and self.is_cuda
+        self.symm = None
+        self.in_backward = False
+        self.requires_gradient_sync = True
+        self.grad_scale = 1.0 / max(self.mesh.data_world, 1)
+        self._rs_events: List[object] = []
+        self._fwd_order: List[Unit] = []
+        self._order_frozen = False
+        self.units: List[Unit] = []
+        self._build_units(unit_classes)
+        self._register_hooks()
+        if self.fused_comm:
+            from . import symm
+            self.symm = symm.SymmetricContext(self)
+
+    # ------------------------------------------------------------------ construction
+    def _build_units(self, unit_classes: Sequence[type]) -> None:
+        model = self.model
+        claimed: Dict[int, str] = {}
+        unit_modules: List[Tuple[str, nn.Module]] = []
+        for name, mod in model.named_modules():
+            if unit_classes and isinstance(mod, tuple(unit_classes)):
+                unit_modules.append((name, mod))
+        named = dict(model.named_parameters(remove_duplicate=True))
+        owner: Dict[int, Tuple[str, nn.Parameter]] = {}
+
+        def make_unit(uname: str, mod: nn.Module, pnames: List[Tuple[str, nn.Parameter]], is_root: bool) -> Unit:
+            buckets: Dict[Tuple[torch.dtype, bool], List[Tuple[str, nn.Parameter]]] = {}
+            for n, p in pnames:
+                local = bool(getattr(p, "_ep_local", False) or getattr(p, "_no_shard", False))
+                dt = torch.float32 if (_keep_fp32(n) or self.param_dtype == torch.float32) else self.param_dtype
+                buckets.setdefault((dt, local), []).append((n, p))
+            groups = []
+            for (dt, local), items in buckets.items():
+                specs, off = [], 0
+                for n, p in items:
+                    specs.append(ParamSpec(n, p, p.shape, p.numel(), off))
+                    off += p.numel()
+                g = FlatGroup(specs, dt, self.world, self.rank, self.group, self.device, sharded=not local)
+                g.ep_local = local
+                g.shard_from_params()
+                groups.append(g)
+            return Unit(uname, mod, groups, is_root)
+
+        for uname, mod in unit_modules:
+            pn = []
+            for n, p in mod.named_parameters(remove_duplicate=True):
+                full = f"{uname}.{n}" if uname else n
+                if id(p) in claimed:
+                    continue
+                claimed[id(p)] = full
+                pn.append((full, p))
+            if pn:
+                self.units.append(make_unit(uname, mod, pn, False))
+        rest = [(n, p) for n, p in named.items() if id(p) not in claimed]
+        self.root = make_unit("", model, rest, True)
+        self.units.append(self.root)
+        # parameters now live in the shards; drop the full fp32 copies
+        for u in self.units:
+            for g in u.groups:
+                g.set_param_views(None)
+
+    def _register_hooks(self) -> None:
+        for u in self.units:
+            if u.is_root:
+                u.module.register_forward_pre_hook(self._root_pre_forward, with_kwargs=True)
+                u.module.register_forward_hook(self._root_post_forward)
+            else:
+                u.module.register_forward_pre_hook(lambda m, a, k, u=u: self._pre_forward(u, a, k), with_kwargs=True)
+                u.module.register_forward_hook(lambda m, a, o, u=u: self._post_forward(u, o))
+
+    # ------------------------------------------------------------------ gather / reshard
+    def _unshard(self, unit: Unit, wait: bool = True) -> None:
+        if not unit.unsharded:
+            for g in unit.groups:
+                lp = g.refresh_lp()
+                if g.world == 1:
+                    g.full = lp
+                    g.gather_event = None
+                else:
+                    if self.is_cuda:
+                        self.comm_stream.wait_stream(torch.cuda.current_stream())
+                        with torch.cuda.stream(self.comm_stream):
+                            g.full = self.pool.get(g.padded, g.dtype, self.device, self.comm_stream)
+                            self._all_gather(g, lp)
+                            g.gather_event = torch.cuda.Event()
+                            g.gather_event.record(self.comm_stream)
+                    else:
+                        g.full = self.pool.get(g.padded, g.dtype, self.device)
+                        self._all_gather(g, lp)
+                g.set_param_views(g.full)
+            unit.unsharded = True
+        if wait and self.is_cuda:
+            for g in unit.groups:
+                if g.gather_event is not None:
+                    torch.cuda.current_stream().wait_event(g.gather_event)
+                    g.gather_event = None
+
+    def _all_gather(self, g: FlatGroup, lp: torch.Tensor) -> None:
+        if self.symm is not None:
+            self.symm.all_gather(g, lp)
+        else:
+            du.all_gather_into(g.full, lp, group=g.group)
+
+    def _reshard(self, unit: Unit) -> None:
+        if not unit.unsharded:
+            return
+        for g in unit.groups:
+            g.set_param_views(None)
+            if g.world > 1 and g.full is not None:
+                self.pool.put(g.full)
+            g.full = None
+        unit.unsharded = False
+
+    # ------------------------------------------------------------------ hooks
+    def _root_pre_forward(self, module, args, kwargs):
+        if not self._order_frozen:
+            self._fwd_order = []
+        self._unshard(self.root)
+        # first block gathers while embeddings run
+        return None
+
+    def _root_post_forward(self, module, args, output):
+        self._order_frozen = True
+        if not torch.is_grad_enabled():
+            self._reshard_all()
+        return None
+
+    def _pre_forward(self, unit: Unit, args, kwargs):
+        if not self._order_frozen and not self.in_backward:
+            self._fwd_order.append(unit)
+        self._unshard(unit)
+        if not self.in_backward:
+            nxt = self._neighbor(unit, +1)
+            if nxt is not None:
+                self._unshard(nxt, wait=False)
+        if torch.is_grad_enabled() and not self.in_backward:
+            unit.bwd_pending, unit.post_bwd_done = True, False
+            tensors = [(i, a) for i, a in enumerate(args) if isinstance(a, torch.Tensor) and a.requires_grad]
+            if tensors:
+                outs = _PostBackward.apply(self, unit, *[a for _, a in tensors])
+                outs = (outs,) if isinstance(outs, torch.Tensor) else outs
+                args = list(args)
+                for (i, _), o in zip(tensors, outs):
+                    args[i] = o
+                return tuple(args), kwargs
+        return None
+
+    def _post_forward(self, unit: Unit, output):
+        if self.in_backward:
+            return None  # recomputation inside backward: parameters are needed right away
+        if torch.is_grad_enabled():
+            def hook(grad, unit=unit):
+                self._pre_backward(unit)
+                return grad
+            for t in _flatten_tensors(output):
+                if t.requires_grad:
+                    t.register_hook(hook)
+        if self.reshard_after_forward:
+            self._reshard(unit)
+        return None
+
+    def _neighbor(self, unit: Unit, step: int) -> Optional[Unit]:
+        order = self._fwd_order
+        if not self._order_frozen:
+            return None
+        try:
+            i = order.index(unit)
+        except ValueError:
+            return None
+        j = i + step
+        return order[j] if 0 <= j < len(order) else None
+
+    def _pre_backward(self, unit: Unit) -> None:
+        if unit.post_bwd_done:
+            return
+        self._unshard(unit)
+        prv = self._neighbor(unit, -1)
+        if prv is not None and prv.bwd_pending and not prv.post_bwd_done:
+            self._unshard(prv, wait=False)
+
+    def _post_backward(self, unit: Unit) -> None:
+        if unit.post_bwd_done:
+            return
+        unit.post_bwd_done, unit.bwd_pending = True, False
+        self._reduce_unit_grads(unit)
+        if self.world > 1:
+            self._reshard(unit)
+
+    # ------------------------------------------------------------------ gradient reduction
+    @torch.no_grad()
+    def _reduce_unit_grads(self, unit: Unit) -> None:
+        for g in unit.groups:
+            have = [s for s in g.specs if s.param.grad is not None]
+            if not have and g.full_grad is None:
+                continue
+            if g.full_grad is None:
+                g.full_grad = self.pool.get(g.padded, torch.float32, self.device)
+                g.full_grad.zero_()
+            if have:
+                dst = [g.full_grad[s.offset:s.offset + s.numel].view(s.shape) for s in have]
+                src = [s.param.grad for s in have]
+                if all(t.dtype == torch.float32 for t in src):
+                    torch._foreach_add_(dst, src)
+                else:
+                    torch._foreach_add_(dst, [t.to(torch.float32) for t in src])
+                for s in have:
+                    s.param.grad = None
+            if not self.requires_gradient_sync:
+                continue
+            scale = self.grad_scale
+            if g.world == 1:
+                # not sharded: a single-process run, expert-parallel experts (each rank owns its
+                # experts, gradients are already complete) or replicated parameters (all-reduce)
+                fg, g.full_grad = g.full_grad, None
+                if scale != 1.0:
+                    fg.mul_(scale)
+                if self.mesh.fsdp > 1 and not getattr(g, "ep_local", False):
+                    du.all_reduce_sum(fg, group=self.mesh.fsdp_group)
+                if self.mesh.dp > 1:
+                    du.all_reduce_sum(fg, group=self.mesh.dp_group)
+                if g.grad is None:
+                    g.grad = fg
+                else:
+                    g.grad.add_(fg)
+                    self.pool.put(fg)
+                continue
+            full_grad = g.full_grad
+            g.full_grad = None
+            if self.is_cuda:
+                self.rs_stream.wait_stream(torch.cuda.current_stream())
+                ctx = torch.cuda.stream(self.rs_stream)
+            else:
+                ctx = contextlib.nullcontext()
+            with ctx:
+                out = torch.empty(g.shard_numel, dtype=torch.float32, device=self.device)
+                if self.symm is not None:
+                    self.symm.reduce_scatter(g, out, full_grad, scale)
+                else:
+                    du.reduce_scatter_sum(out, full_grad, group=g.group)
+                    out.mul_(scale)
+                if self.mesh.dp > 1:
+                    du.all_reduce_sum(out, group=self.mesh.dp_group)
+                if g.grad is None:
+                    g.grad = out
+                else:
+                    g.grad.add_(out)
+                if self.is_cuda:
+                    full_grad.record_stream(self.rs_stream)
+                    ev = torch.cuda.Event()
+                    ev.record(self.rs_stream)
+                    self._rs_events.append(ev)
+            self.pool.put(full_grad)
+
+    # ------------------------------------------------------------------ public API
+    def backward(self, loss: torch.Tensor) -> None:
+        """``loss.backward()`` with unit-wise gather / reduce-scatter; returns after every
+        gradient shard of this micro-step has been accumulated (on the compute stream)."""
+        self.in_backward = True
+        try:
+            loss.backward()
+        finally:
+            self.in_backward = False
+        for u in self.units:
+            if u.is_root or (u.bwd_pending and not u.post_bwd_done):
+                u.post_bwd_done, u.bwd_pending = True, False
+                self._reduce_unit_grads(u)
+        if self.world > 1:
+            self._reshard_all()
+        if self.is_cuda:
+            for ev in self._rs_events:
+                torch.cuda.current_stream().wait_event(ev)
+            self._rs_events.clear()
+
+    def _reshard_all(self) -> None:
+        if self.world == 1:
+            return
+        for u in self.units:
+            self._reshard(u)
+
+    def unshard_all(self) -> None:
+        for u in self.units:
+            self._unshard(u)
+
+    def set_requires_gradient_sync(self, flag: bool) -> None:
+        self.requires_gradient_sync = flag
+
+    def zero_grad(self) -> None:
+        for u in self.units:
+            for g in u.groups:
+                g.grad = None
+
+    def groups(self) -> Iterable[FlatGroup]:
+        for u in self.units:
+            yield from u.groups
+
+    def mark_params_updated(self) -> None:
+        """Call after the optimizer changed the master shards."""
+        for g in self.groups():
+            g.lp_stale = True
+        for u in self.units:
+            if u.unsharded and self.world == 1:
+                for g in u.groups:
+                    g.refresh_lp()
+
+    @torch.no_grad()
+    def clip_grad_norm_(self, max_norm: float, eps: float = 1e-6) -> torch.Tensor:
+        """Global L2 norm over all gradient shards (+ scale when above ``max_norm``);
+        the role of ``fabric.clip_gradients`` (`pretrain.py:965-971`)."""
+        sq_sharded = torch.zeros((), dtype=torch.float32, device=self.device)
+        sq_local = torch.zeros((), dtype=torch.float32, device=self.device)
+        grads = []
+        for g in self.groups():
+            if g.grad is None:
+                continue
+            grads.append(g.grad)
+            s = g.grad.float().pow(2).sum()
+            if g.world > 1 or getattr(g, "ep_local", False):
+                sq_sharded += s
+            else:
+                sq_local += s
+        if self.mesh.fsdp > 1:
+            du.all_reduce_sum(sq_sharded, group=self.mesh.fsdp_group)
+        total = torch.sqrt(sq_sharded + sq_local)
+        if self.mesh.tp > 1:
+            # tensor-parallel ranks hold different slices of the sharded matrices
+            t2 = total.pow(2)
+            du.all_reduce_sum(t2, group=self.mesh.tp_group)
+            total = torch.sqrt(t2)
+        if max_norm is not None and max_norm > 0:
+            coef = torch.clamp(max_norm / (total + eps), max=1.0)
+            if grads:
+                torch._foreach_mul_(grads, coef)
+        return total
+
+    # -- checkpoint support ----------------------------------------------------------
+    @torch.no_grad()
+    def full_state_dict(self, rank0_only: bool = True, dtype: Optional[torch.dtype] = None) -> Dict[str, torch.Tensor]:
+        """Consolidated fp32 (or ``dtype``) state dict with the model's own key names, on CPU."""
+        out: Dict[str, torch.Tensor] = {}
+        keep = (not rank0_only) or self.mesh.rank == 0
+        for g in self.groups():
+            full = self._gather_master(g.master, g)
+            if keep:
+                for s in g.specs:
+                    t = full[s.offset:s.offset + s.numel].view(s.shape)
+                    out[s.name] = (t.to(dtype) if dtype else t).cpu().clone()
+            del full
+        # tied / duplicate names (e.g. lm_head.weight tied to wte.weight) and buffers
+        if keep:
+            seen = {id(p): n for n, p in self.model.named_parameters(remove_duplicate=True)}
+            for n, p in self.model.named_parameters(remove_duplicate=False):
+                if n not in out and id(p) in seen and seen[id(p)] in out:
+                    out[n] = out[seen[id(p)]]
+            for n, b in self.model.named_buffers():
+                out[n] = b.detach().cpu().clone()
+        return out
+
+    def _gather_master(self, shard: torch.Tensor, g: FlatGroup) -> torch.Tensor:
+        if g.world == 1:
+            return shard
+        full = torch.empty(g.padded, dtype=shard.dtype, device=self.device)
+        du.all_gather_into(full, shard.contiguous(), group=g.group)
+        return full
+
+    @torch.no_grad()
+    def load_full_state_dict(self, sd: Dict[str, torch.Tensor], strict: bool = True) -> None:
+        missing = []
+        for g in self.groups():
+            a, b = g.shard_range()
+            for s, lo, hi, slo in g.local_slices():
+                if s.name not in sd:
+                    missing.append(s.name)
+                    continue
+                src = sd[s.name].reshape(-1)[lo:hi]
+                g.master[slo:slo + hi - lo].copy_(src.to(torch.float32))
+            g.lp_stale = True
+        if strict and missing:
+            raise KeyError(f"missing keys in checkpoint: {missing[:8]}{'…' if len(missing) > 8 else ''}")
+        self._reshard_all()
+        for u in self.units:
+            if u.unsharded:
+                for g in u.groups:
+                    g.refresh_lp()
+
+
+def _flatten_tensors(obj) -> List[torch.Tensor]:
+    if isinstance(obj, torch.Tensor):
+        return [obj]
+    if isinstance(obj, (list, tuple)):
+        out: List[torch.Tensor] = []
+        for o in obj:
+            out.extend(_flatten_tensors(o))
+        return out
+    if isinstance(obj, dict):
+        out = []
+        for o in obj.values():
+            out.extend(_flatten_tensors(o))
+        return out
+    return []
