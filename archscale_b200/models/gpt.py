@@ -71,6 +71,14 @@ def compute_outlier_percentage(x: torch.Tensor, sigma: float = 5.0) -> torch.Ten
     return ((x - mean).abs() > sigma * std).float().mean() * 100.0
 
 
+def _norm_to(norm: nn.Module, x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """Apply ``norm`` and deliver ``dtype``; RMSNorm modules convert inside their kernel."""
+    from archscale_b200.models.norms import FusedRMSNorm
+    if isinstance(norm, FusedRMSNorm):
+        return norm(x, out_dtype=dtype)
+    return norm(x).to(dtype)
+
+
 class LLaMAMLP(nn.Module):
     def __init__(self, config: Config) -> None:
         super().__init__()
@@ -246,7 +254,7 @@ class Block(nn.Module):
                 ox = self.skip_proj(ox)
         else:
             ox = ox_src.to(torch.float32)
-            n_1 = self.norm_1(x).to(compute_dtype)
+            n_1 = _norm_to(self.norm_1, x, compute_dtype)
         new_kv_cache = kv_cache
         if self.use_rnn:
             if self.rnn_type in ("mamba", "mamba2"):
@@ -276,7 +284,7 @@ class Block(nn.Module):
                 ox, n_2 = self._norm_in(self.norm_2, ox_src, compute_dtype)
             else:
                 ox = ox_src.to(torch.float32)
-                n_2 = self.norm_2(x).to(compute_dtype)
+                n_2 = _norm_to(self.norm_2, x, compute_dtype)
             if cfg.moe:
                 h = self.mlp(n_2)
             else:
@@ -456,7 +464,7 @@ class GPT(nn.Module):
                 run(block)
         if cfg.sum_skip:
             x = input_embed
-        x = self.transformer.ln_f(x).to(self.compute_dtype)
+        x = _norm_to(self.transformer.ln_f, x, self.compute_dtype)
         if self.logit_scale != 1.0:
             x = x * self.logit_scale
         if use_flce_loss:

@@ -20,8 +20,8 @@ class FusedRMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(size))
         self.eps = eps
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return ops.rms_norm(x, self.weight, self.eps)
+    def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        return ops.rms_norm(x, self.weight, self.eps, out_dtype)
 
     def reset_parameters(self) -> None:
         nn.init.ones_(self.weight)

@@ -98,8 +98,8 @@ class _AttnFn(torch.autograd.Function):
 
 def cuda_supported(q, k, v, sink) -> bool:
     D = q.shape[-1]
-    return (q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16
-            and D in (64, 128) and v.shape[-1] == D and sink is None and q.shape[1] == k.shape[1]
+    return (backend.has("attn_fwd") and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
+            and v.dtype == torch.bfloat16 and D in (64, 128) and v.shape[-1] == D and sink is None and q.shape[1] == k.shape[1]
             and q.shape[2] % k.shape[2] == 0)
 
 

@@ -85,6 +85,12 @@ def use_cuda_kernel(op: str, *tensors: torch.Tensor) -> bool:
     return True
 
 
+def has(symbol: str) -> bool:
+    """True when the loaded extension exports ``symbol`` (kernels land one by one)."""
+    ext = load_extension()
+    return ext is not None and hasattr(ext, symbol)
+
+
 def count_launch(n: int = 1) -> None:
     global _launch_count
     _launch_count += n

@@ -67,7 +67,7 @@ def causal_conv1d(x, weight, bias=None, seq_idx=None, activation: Optional[str] 
         xl = x
     else:
         xl = x.transpose(1, 2)
-    if (xl.dtype in (torch.bfloat16, torch.float32) and weight.shape[1] <= 4 and xl.shape[-1] % 8 == 0
+    if (backend.has("causal_conv1d_fwd") and xl.dtype in (torch.bfloat16, torch.float32) and weight.shape[1] <= 4 and xl.shape[-1] % 8 == 0
             and backend.use_cuda_kernel("conv1d", xl, weight)):
         y = _ConvFn.apply(xl.contiguous(), weight.contiguous(), bias,
                           None if seq_idx is None else seq_idx.to(torch.int32).contiguous(),

@@ -1,0 +1,48 @@
+// C entry points of the sm_100a kernels (called from bindings.cpp; no torch types here so the
+// kernels compile in seconds).  dtype codes: 0 = fp32, 1 = bf16.  All launches are asynchronous
+// on `stream`; a non-zero return value is a host-side launch / argument error.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// D = alpha·op(A)·op(B) (+beta·C).  mode 0: A[M,K]·B[N,K]ᵀ, 1: A[M,K]·B[K,N], 2: A[K,M]ᵀ·B[K,N].
+int b200_gemm_bf16(int mode, const void* A, const void* B, void* out, const void* cin, int M, int N, int K, int lda,
+                   int ldb, int ldc, float alpha, float beta, int out_f32, int accumulate, int num_sms, int* status,
+                   cudaStream_t stream);
+
+// RMSNorm over the last dim.  x:[rows,cols] (fp32|bf16), w:[cols] or null, out dtype chosen by out_dtype.
+int b200_rmsnorm_fwd(const void* x, int x_dtype, const void* w, int w_dtype, void* out, int out_dtype, float* rstd,
+                     int rows, int cols, float eps, cudaStream_t stream);
+// dx (dtype of x) and per-CTA partial dw [n_partials, cols] fp32 (n_partials = return of b200_rmsnorm_bwd_partials).
+int b200_rmsnorm_bwd_partials(int rows, int cols);
+int b200_rmsnorm_bwd(const void* dy, int dy_dtype, const void* x, int x_dtype, const void* w, int w_dtype,
+                     const float* rstd, void* dx, float* dw_partial, float* dw, int rows, int cols, cudaStream_t stream);
+
+// SwiGLU: y = silu(g)·u.  Packed variant reads g = x[:, :I], u = x[:, I:] from a [rows, 2I] bf16 tensor.
+int b200_swiglu_fwd(const void* g, const void* u, void* y, int64_t n, cudaStream_t stream);
+int b200_swiglu_bwd(const void* g, const void* u, const void* dy, void* dg, void* du, int64_t n, cudaStream_t stream);
+int b200_swiglu_packed_fwd(const void* x, void* y, int64_t rows, int I, cudaStream_t stream);
+int b200_swiglu_packed_bwd(const void* x, const void* dy, void* dx, int64_t rows, int I, cudaStream_t stream);
+
+// Cross-entropy over a logits chunk, in place: logits ← d(Σ loss)/d logits, loss[row] fp32.
+int b200_cross_entropy_fwd_bwd(void* logits, int dtype, const int64_t* target, float* loss, int rows, int vocab,
+                               int64_t row_stride, int ignore_index, float label_smoothing, float lse_square_scale,
+                               cudaStream_t stream);
+
+// Per-head RMSNorm (optional) + NeoX RoPE (optional) on q:[N,H,D] and k:[N,G,D] bf16; T = positions per batch row.
+int b200_qknorm_rope_fwd(const void* q, const void* k, const void* qw, const void* kw, int w_dtype, const void* cos,
+                         const void* sin, void* qo, void* ko, float* q_rstd, float* k_rstd, int64_t n_tokens, int T,
+                         int H, int G, int D, float eps, cudaStream_t stream);
+int b200_qknorm_rope_bwd(const void* dqo, const void* dko, const void* q, const void* k, const void* qw, const void* kw,
+                         int w_dtype, const void* cos, const void* sin, const float* q_rstd, const float* k_rstd,
+                         void* dq, void* dk, float* dqw, float* dkw, float* dw_partial /* [grid, 2, D] */,
+                         int64_t n_tokens, int T, int H, int G, int D, cudaStream_t stream);
+int b200_qknorm_rope_grid();
+
+#ifdef __cplusplus
+}
+#endif

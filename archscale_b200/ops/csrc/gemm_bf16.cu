@@ -1,0 +1,286 @@
+// bf16 GEMM on the 5th-generation tensor cores:  D = alpha · op(A) · op(B) (+ beta · C)
+//
+// Persistent, warp-specialised kernel, one CTA per SM, 192 threads:
+//   warp 0      TMA producer  — fills a 4-stage shared-memory ring (A 128×64, B 256×64 per stage)
+//   warp 1      MMA issuer    — one thread issues tcgen05.mma (M128 × N256 × K16) into one of two
+//                               256-column fp32 accumulators in tensor memory
+//   warps 2..5  epilogue      — tcgen05.ld the finished accumulator (32 lanes × 32 columns per
+//                               instruction), scale / add C, store bf16 or accumulate into fp32
+// The two TMEM accumulators let the epilogue of tile i overlap the main loop of tile i+1.
+//
+// Operand layouts (all via TMA tensor maps with 128-byte swizzle, no multicast):
+//   A: K-major   (row-major [M,K])  or MN-major (row-major [K,M], i.e. Aᵀ is stored)
+//   B: K-major   (row-major [N,K])  or MN-major (row-major [K,N])
+// which covers forward (NT), dgrad (NN) and wgrad (TN) of a linear layer without any transpose copy.
+//
+// All waits are bounded (sm100.cuh); on expiry the kernel records a status code and exits cleanly.
+#include "sm100.cuh"
+#include "api.h"
+
+namespace b200 {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KB
+constexpr int B_STAGE_BYTES = BN * BK * 2;   // 32 KB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int GEMM_SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int GROUP_M = 16;
+constexpr int NUM_THREADS = 192;
+
+struct GemmParams {
+  void* out;
+  const void* cin;
+  int M, N, K;
+  int ldc;          // row stride of out / cin in elements
+  float alpha, beta;
+  int accumulate;   // fp32 output: out += result
+  int* status;
+};
+
+template <int A_MN, int B_MN, int OUT_F32>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full_bar = bars;                    // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;          // [STAGES]
+  uint64_t* tmem_full = bars + 2 * STAGES;      // [2]
+  uint64_t* tmem_empty = bars + 2 * STAGES + 2; // [2]
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 4); }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) { tmem_alloc(tmem_ptr, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  auto tile_coords = [&](int t, int& m_idx, int& n_idx) {
+    const int per_group = GROUP_M * num_n;
+    const int g = t / per_group;
+    const int first_m = g * GROUP_M;
+    const int gsz = min(num_m - first_m, GROUP_M);
+    const int r = t - g * per_group;
+    m_idx = first_m + (r % gsz);
+    n_idx = r / gsz;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        int mi, ni; tile_coords(t, mi, ni);
+        const int m0 = mi * BM, n0 = ni * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) goto done;
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_STAGE_BYTES;
+          mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
+          if (A_MN) {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (64 * BK * 2), &tmap_a, &full_bar[stage], m0 + c * 64, kb * BK);
+          } else {
+            tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * (64 * BK * 2), &tmap_b, &full_bar[stage], n0 + c * 64, kb * BK);
+          } else {
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BK, n0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      // per-K16 advance of the descriptor start address (in 16-byte units)
+      constexpr uint32_t a_kstep = A_MN ? (16 * 128) >> 4 : 32 >> 4;
+      constexpr uint32_t b_kstep = B_MN ? (16 * 128) >> 4 : 32 >> 4;
+      int stage = 0; uint32_t phase = 0;
+      int it = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+        const int acc = it & 1; const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) goto done;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_FULL)) goto done;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_STAGE_BYTES;
+          const uint64_t da = A_MN ? make_smem_desc(sa, 64 * BK * 2, 1024) : make_smem_desc(sa, 16, 1024);
+          const uint64_t db = B_MN ? make_smem_desc(sb, 64 * BK * 2, 1024) : make_smem_desc(sb, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            umma_bf16(d_tmem, da + static_cast<uint64_t>(k * a_kstep), db + static_cast<uint64_t>(k * b_kstep), idesc,
+                      (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        umma_commit(&tmem_full[acc]);
+      }
+    }
+  } else {
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    int it = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+      int mi, ni; tile_coords(t, mi, ni);
+      const int acc = it & 1; const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
+      tc_fence_after();
+      const int row = mi * BM + q * 32 + lane;
+      const int col0 = ni * BN;
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int col = col0 + c * 32;
+        if (row < p.M && col < p.N) {
+          if (OUT_F32) {
+            float* o = reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ldc + col;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (col + j < p.N) {
+                float4 v = make_float4(__uint_as_float(r[j]) * p.alpha, __uint_as_float(r[j + 1]) * p.alpha,
+                                       __uint_as_float(r[j + 2]) * p.alpha, __uint_as_float(r[j + 3]) * p.alpha);
+                if (p.accumulate) {
+                  const float4 old = *reinterpret_cast<const float4*>(o + j);
+                  v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                }
+                *reinterpret_cast<float4*>(o + j) = v;
+              }
+            }
+          } else {
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ldc + col;
+            const __nv_bfloat16* ci = p.cin ? reinterpret_cast<const __nv_bfloat16*>(p.cin) + static_cast<size_t>(row) * p.ldc + col : nullptr;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col + j < p.N) {
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[j + e]) * p.alpha;
+                if (ci) {
+                  const uint4 cv = *reinterpret_cast<const uint4*>(ci + j);
+                  const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 c2 = unpack_bf16x2(cw[e]);
+                    f[2 * e] += p.beta * c2.x; f[2 * e + 1] += p.beta * c2.y;
+                  }
+                }
+                uint4 ov;
+                ov.x = pack_bf16x2(f[0], f[1]); ov.y = pack_bf16x2(f[2], f[3]);
+                ov.z = pack_bf16x2(f[4], f[5]); ov.w = pack_bf16x2(f[6], f[7]);
+                *reinterpret_cast<uint4*>(o + j) = ov;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+    }
+  }
+
+done:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess) {
+      return nullptr;
+    }
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map: inner dimension `inner` (contiguous), `outer` rows of `row_stride_elems`.
+int make_tmap_2d_bf16(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_elems,
+                      uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t gdim[2] = {inner, outer};
+  cuuint64_t gstride[1] = {row_stride_elems * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+template <int A_MN, int B_MN, int OUT_F32>
+static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int sms, cudaStream_t st) {
+  auto kern = gemm_bf16_kernel<A_MN, B_MN, OUT_F32>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess) return -2;
+    configured = true;
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < sms ? tiles : sms;
+  kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+}  // namespace b200
+
+extern "C" int b200_gemm_bf16(int mode, const void* A, const void* B, void* out, const void* cin, int M, int N, int K,
+                              int lda, int ldb, int ldc, float alpha, float beta, int out_f32, int accumulate,
+                              int num_sms, int* status, cudaStream_t stream) {
+  using namespace b200;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  CUtensorMap ta, tb;
+  int rc;
+  // A
+  if (mode == 2) rc = make_tmap_2d_bf16(&ta, A, M, K, lda, 64, BK);      // stored [K, M]
+  else           rc = make_tmap_2d_bf16(&ta, A, K, M, lda, BK, BM);      // stored [M, K]
+  if (rc) return rc;
+  // B
+  if (mode == 0) rc = make_tmap_2d_bf16(&tb, B, K, N, ldb, BK, BN);      // stored [N, K]
+  else           rc = make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, BK);      // stored [K, N]
+  if (rc) return rc;
+  GemmParams p{out, cin, M, N, K, ldc, alpha, beta, accumulate, status};
+  if (mode == 0) return out_f32 ? launch_variant<0, 0, 1>(ta, tb, p, num_sms, stream) : launch_variant<0, 0, 0>(ta, tb, p, num_sms, stream);
+  if (mode == 1) return out_f32 ? launch_variant<0, 1, 1>(ta, tb, p, num_sms, stream) : launch_variant<0, 1, 0>(ta, tb, p, num_sms, stream);
+  if (mode == 2) return out_f32 ? launch_variant<1, 1, 1>(ta, tb, p, num_sms, stream) : launch_variant<1, 1, 0>(ta, tb, p, num_sms, stream);
+  return -4;
+}

@@ -1,0 +1,183 @@
+// RMSNorm forward / backward.  One warp per row, 16-byte vector loads, fp32 statistics.
+// Forward reads the row twice (the second pass hits L1) so any row length works without keeping the
+// row in registers.  Backward is persistent: each CTA walks a strided set of rows, writes dx and
+// accumulates dw in shared memory; per-CTA partials are reduced by a second tiny kernel.
+#include "sm100.cuh"
+#include "api.h"
+
+namespace b200 {
+
+template <typename T> struct Vec8;
+template <> struct Vec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+};
+template <> struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = unpack_bf16x2(w[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 u;
+    u.x = pack_bf16x2(v[0], v[1]); u.y = pack_bf16x2(v[2], v[3]); u.z = pack_bf16x2(v[4], v[5]); u.w = pack_bf16x2(v[6], v[7]);
+    *reinterpret_cast<uint4*>(p) = u;
+  }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <typename TX, typename TW, typename TO>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const TX* __restrict__ x, const TW* __restrict__ w,
+                                                          TO* __restrict__ out, float* __restrict__ rstd_out, int rows,
+                                                          int cols, float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + warp;
+  if (row >= rows) return;
+  const TX* xr = x + static_cast<size_t>(row) * cols;
+  float ss = 0.f;
+  for (int c = lane * 8; c < cols; c += 256) {
+    float v[8]; Vec8<TX>::load(xr + c, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+  }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / cols + eps);
+  if (lane == 0 && rstd_out) rstd_out[row] = rstd;
+  TO* orow = out + static_cast<size_t>(row) * cols;
+  for (int c = lane * 8; c < cols; c += 256) {
+    float v[8]; Vec8<TX>::load(xr + c, v);
+    if (w) {
+      float g[8]; Vec8<TW>::load(w + c, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = v[i] * rstd * g[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = v[i] * rstd;
+    }
+    Vec8<TO>::store(orow + c, v);
+  }
+}
+
+template <typename TDY, typename TX, typename TW>
+__global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x,
+                                                          const TW* __restrict__ w, const float* __restrict__ rstd,
+                                                          TX* __restrict__ dx, float* __restrict__ dw_partial, int rows,
+                                                          int cols) {
+  extern __shared__ float dw_s[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (w) { for (int c = threadIdx.x; c < cols; c += blockDim.x) dw_s[c] = 0.f; __syncthreads(); }
+  for (int row = blockIdx.x * 8 + warp; row < rows; row += gridDim.x * 8) {
+    const TX* xr = x + static_cast<size_t>(row) * cols;
+    const TDY* dyr = dy + static_cast<size_t>(row) * cols;
+    const float rs = rstd[row];
+    float dot = 0.f;
+    for (int c = lane * 8; c < cols; c += 256) {
+      float xv[8], dv[8]; Vec8<TX>::load(xr + c, xv); Vec8<TDY>::load(dyr + c, dv);
+      if (w) {
+        float g[8]; Vec8<TW>::load(w + c, g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dot += dv[i] * g[i] * xv[i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dot += dv[i] * xv[i];
+      }
+    }
+    dot = warp_sum(dot);
+    const float c1 = dot * rs * rs * rs / cols;   // mean(dy·w·x̂)·rstd, with x̂ = x·rstd
+    TX* dxr = dx + static_cast<size_t>(row) * cols;
+    for (int c = lane * 8; c < cols; c += 256) {
+      float xv[8], dv[8], o[8]; Vec8<TX>::load(xr + c, xv); Vec8<TDY>::load(dyr + c, dv);
+      if (w) {
+        float g[8]; Vec8<TW>::load(w + c, g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          o[i] = dv[i] * g[i] * rs - xv[i] * c1;
+          atomicAdd(&dw_s[c + i], dv[i] * xv[i] * rs);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = dv[i] * rs - xv[i] * c1;
+      }
+      Vec8<TX>::store(dxr + c, o);
+    }
+  }
+  if (w) {
+    __syncthreads();
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) dw_partial[static_cast<size_t>(blockIdx.x) * cols + c] = dw_s[c];
+  }
+}
+
+__global__ void reduce_partials_kernel(const float* __restrict__ part, float* __restrict__ out, int n, int cols) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float s = 0.f;
+  for (int i = 0; i < n; ++i) s += part[static_cast<size_t>(i) * cols + c];
+  out[c] = s;
+}
+
+constexpr int kBwdCtas = 148 * 2;
+
+}  // namespace b200
+
+using namespace b200;
+
+#define DISPATCH_3(xd, wd, od, CALL)                                                           \
+  if (xd == 0 && wd == 0 && od == 0) { CALL(float, float, float) }                              \
+  else if (xd == 0 && wd == 0 && od == 1) { CALL(float, float, __nv_bfloat16) }                 \
+  else if (xd == 0 && wd == 1 && od == 1) { CALL(float, __nv_bfloat16, __nv_bfloat16) }         \
+  else if (xd == 0 && wd == 1 && od == 0) { CALL(float, __nv_bfloat16, float) }                 \
+  else if (xd == 1 && wd == 1 && od == 1) { CALL(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16) } \
+  else if (xd == 1 && wd == 0 && od == 1) { CALL(__nv_bfloat16, float, __nv_bfloat16) }         \
+  else if (xd == 1 && wd == 0 && od == 0) { CALL(__nv_bfloat16, float, float) }                 \
+  else if (xd == 1 && wd == 1 && od == 0) { CALL(__nv_bfloat16, __nv_bfloat16, float) }         \
+  else return -1;
+
+extern "C" int b200_rmsnorm_fwd(const void* x, int x_dtype, const void* w, int w_dtype, void* out, int out_dtype,
+                                float* rstd, int rows, int cols, float eps, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (cols % 8) return -1;
+  const int grid = (rows + 7) / 8;
+#define CALL(TX, TW, TO)                                                                                          \
+  rmsnorm_fwd_kernel<TX, TW, TO><<<grid, 256, 0, stream>>>(static_cast<const TX*>(x), static_cast<const TW*>(w), \
+                                                           static_cast<TO*>(out), rstd, rows, cols, eps);
+  DISPATCH_3(x_dtype, w_dtype, out_dtype, CALL)
+#undef CALL
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int b200_rmsnorm_bwd_partials(int rows, int cols) {
+  const int need = (rows + 7) / 8;
+  return need < kBwdCtas ? need : kBwdCtas;
+}
+
+extern "C" int b200_rmsnorm_bwd(const void* dy, int dy_dtype, const void* x, int x_dtype, const void* w, int w_dtype,
+                                const float* rstd, void* dx, float* dw_partial, float* dw, int rows, int cols,
+                                cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (cols % 8) return -1;
+  const int grid = b200_rmsnorm_bwd_partials(rows, cols);
+  const size_t smem = w ? sizeof(float) * cols : 0;
+#define CALL(TDY, TW, TX)                                                                                     \
+  {                                                                                                           \
+    auto kern = rmsnorm_bwd_kernel<TDY, TX, TW>;                                                              \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    kern<<<grid, 256, smem, stream>>>(static_cast<const TDY*>(dy), static_cast<const TX*>(x),                \
+                                      static_cast<const TW*>(w), rstd, static_cast<TX*>(dx), dw_partial, rows, cols); \
+  }
+  DISPATCH_3(dy_dtype, w_dtype, x_dtype, CALL)
+#undef CALL
+  if (w) reduce_partials_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(dw_partial, dw, grid, cols);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

@@ -66,11 +66,11 @@ def gated_rms_norm_ref(x: torch.Tensor, weight: torch.Tensor, z: Optional[torch.
 # ------------------------------------------------------------------ CUDA autograd
 class _RMSNormFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, eps):
+    def forward(ctx, x, weight, eps, out_dtype):
         ext = backend.require_extension()
         shape = x.shape
         x2 = x.reshape(-1, shape[-1]).contiguous()
-        out, rstd = ext.rmsnorm_fwd(x2, weight, eps)
+        out, rstd = ext.rmsnorm_fwd(x2, weight, eps, out_dtype)
         backend.count_launch()
         ctx.save_for_backward(x2, weight, rstd)
         ctx.shape = shape
@@ -83,14 +83,18 @@ class _RMSNormFn(torch.autograd.Function):
         dout2 = dout.reshape(-1, ctx.shape[-1]).contiguous()
         dx, dw = ext.rmsnorm_bwd(dout2, x2, weight, rstd)
         backend.count_launch(2 if weight is not None else 1)
-        return dx.view(ctx.shape), (dw.to(weight.dtype) if weight is not None else None), None
+        return dx.view(ctx.shape), (dw.to(weight.dtype) if weight is not None else None), None, None
 
 
-def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float = 1e-5) -> torch.Tensor:
+def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float = 1e-5,
+             out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """RMSNorm over the last dim; ``out_dtype`` (default: dtype of ``x``) lets the kernel read an fp32
+    residual stream and write the bf16 mixer input in one pass."""
     ok_dtype = x.dtype in (torch.bfloat16, torch.float32) and (weight is None or weight.dtype in (torch.bfloat16, torch.float32))
     if ok_dtype and x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384 and backend.use_cuda_kernel("rmsnorm", x, weight):
-        return _RMSNormFn.apply(x, weight, eps)
-    return rms_norm_ref(x, weight, eps)
+        return _RMSNormFn.apply(x, weight, eps, out_dtype)
+    out = rms_norm_ref(x, weight, eps)
+    return out if out_dtype is None else out.to(out_dtype)
 
 
 def layer_norm(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor],

@@ -82,7 +82,7 @@ class _ScanFn(torch.autograd.Function):
 
 def selective_scan(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta_softplus: bool = False,
                    cu_seqlens: Optional[torch.Tensor] = None):
-    if (u.dtype in (torch.bfloat16, torch.float32) and A.shape[1] == 16 and D is not None and B.dim() == 3
+    if (backend.has("selective_scan_fwd") and u.dtype in (torch.bfloat16, torch.float32) and A.shape[1] == 16 and D is not None and B.dim() == 3
             and backend.use_cuda_kernel("selective_scan", u, delta, A, B, C)):
         cu = None if cu_seqlens is None else cu_seqlens.to(torch.int32).contiguous()
         return _ScanFn.apply(u, delta.to(u.dtype), A.float().contiguous(), B.to(u.dtype), C.to(u.dtype),

@@ -610,7 +610,7 @@ def setup(train_data_dir: str = "data/redpajama_sample", val_data_dir: Optional[
           # --- additions ---
           tp: int = 1, ep: int = 1, dp_replicate: int = 1, precision: str = "bf16", fused_comm: bool = False,
           max_steps: Optional[int] = None, config_overrides: Optional[Dict[str, Any]] = None,
-          return_trainer: bool = False):
+          return_trainer: bool = False, quiet: bool = False):
     """Same keyword surface as the reference ``setup()`` plus the parallelism additions.
 
     ``fsdp2`` is accepted for compatibility: this engine is always the sharded one.
@@ -641,7 +641,7 @@ def setup(train_data_dir: str = "data/redpajama_sample", val_data_dir: Optional[
         ckpt.make_dirs(plan.out_dir)
     trainer = Trainer(plan, mesh, device, train_data_dir, val_data_dir, resume, load_dir, base_hps,
                       use_mlflow=use_mlflow, wandb_project=wandb_project, precision=precision,
-                      fused_comm=fused_comm, max_steps=max_steps)
+                      fused_comm=fused_comm, max_steps=max_steps, quiet=quiet)
     if return_trainer:
         return trainer
     trainer.logger.log_hyperparams({**dataclasses.asdict(base_hps),

@@ -1,0 +1,240 @@
+"""Headline benchmark: training throughput (tokens/s, whole job) of the depth-16 dense GQA
+transformer with the MuonH optimizer (or the depth-8 64-expert MoE with ``--config moe``) on N GPUs
+of one node, synthetic uniform-random tokens, random-init weights, bf16 compute.
+
+    python bench.py --gpus 1 --steps 10 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 10 --warmup 3
+
+One step = forward + backward + gradient clip + optimizer step on one micro-batch per GPU
+(8×4096 tokens for the dense config, 16×4096 for the MoE config).  Rank 0 prints one JSON line.
+``value`` is device-timed (CUDA events, max over ranks) with inputs already on the device;
+``e2e`` repeats the measurement through the public trainer API with a pinned-host → device copy
+of every step's tokens and a device → host read of every step's loss inside the timed region.
+``--impl reference`` would run the unmodified reference; it cannot be installed offline (no
+build metadata, and its imports lightning / transformer_engine / sonicmoe / mamba_ssm are absent),
+so that arm reports ``unavailable``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CONFIGS = {
+    "dense": dict(
+        name="dense GQA d16 (d_model 2048, 16q/4kv heads, head_dim 128, QK-RMSNorm, SwiGLU 5632, vocab 32000), muP++ MuonH",
+        train_model="transformer_gqa4", depth=16, train_name="scaling_mup_muonh_qknorm", micro_bsz=8, ctx_len=4096,
+        overrides={"intermediate_size": 5632}, sparsity=1, top_k=2),
+    "moe": dict(
+        name="MoE d8 (d_model 1024, 8q/2kv heads, 64 routed experts hidden 256 + shared 2048, top-8, SqrtGate, "
+             "global aux 0.01), muP++ MuonH",
+        train_model="transformer_gqa4_h2_moe", depth=8, train_name="scaling_mup_muonh_qknorm", micro_bsz=16, ctx_len=4096,
+        overrides={"n_head": 8, "n_query_groups": 2, "n_routed_experts": 64, "router_top_k": 8,
+                   "moe_intermediate_size": 256, "shared_intermediate_size": 2048},
+        sparsity=8, top_k=8, share_expert=True, sqrt_gate=True, global_aux=True, aux_gamma=0.01),
+}
+
+CLOCK_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+
+class ClockSampler:
+    """``nvidia-smi`` sampling in a child process while the timed region runs (read-only)."""
+
+    def __init__(self, gpu_index: int) -> None:
+        self.path = tempfile.mktemp(suffix=".csv")
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self) -> None:
+        try:
+            self.fh = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={CLOCK_QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu_index)], stdout=self.fh,
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.fh.close()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), samples=len(sm))
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from archscale_b200.ops import backend
+    from archscale_b200.parallel import dist_utils as du
+    from archscale_b200.train.pretrain import setup
+    from archscale_b200.utils.speed_monitor import estimate_flops
+    from archscale_b200.config import get_parameters_count
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run"
+    c = CONFIGS[args.config]
+    os.environ.setdefault("LIGHTNING_ARTIFACTS_DIR", os.path.join(tempfile.gettempdir(), "archscale_b200_bench"))
+    ep = world if (args.config == "moe" and world > 1 and not args.no_ep) else 1
+    kwargs = dict(train_data_dir="synthetic", train_model=c["train_model"], depth=c["depth"], train_name=c["train_name"],
+                  micro_bsz=c["micro_bsz"], ctx_len=c["ctx_len"], total_bsz=world * c["micro_bsz"] * c["ctx_len"],
+                  max_tokens=1e12, use_flce=True, sparsity=c["sparsity"], top_k=c["top_k"],
+                  config_overrides=dict(c["overrides"]), ep=ep, fused_comm=args.fused_comm, return_trainer=True, quiet=True)
+    for k in ("share_expert", "sqrt_gate", "global_aux", "aux_gamma"):
+        if k in c:
+            kwargs[k] = c[k]
+    trainer = setup(**kwargs)
+    trainer.quiet = True
+    dev = trainer.device
+    cfg = trainer.config
+    mb, T = c["micro_bsz"], c["ctx_len"]
+    tokens_per_step = world * mb * T
+    lr = trainer.plan.learning_rate
+
+    g = torch.Generator().manual_seed(0 * 1000003 + trainer.mesh.data_rank)
+    n_batches = args.steps + args.warmup
+    host_batches = [torch.randint(0, cfg.vocab_size, (mb, T + 1), generator=g).pin_memory() for _ in range(min(n_batches, 8))]
+    dev_batches = [b.to(dev) for b in host_batches]
+
+    def step_dev(i):
+        loss, _ = trainer.forward_backward(dev_batches[i % len(dev_batches)])
+        trainer.optimizer_step(lr)
+        return loss
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        sync_all()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms) / steps
+
+    for i in range(args.warmup):
+        step_dev(i)
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    if trainer.mesh.rank == 0:
+        sampler.start()
+    backend.reset_launches()
+    ms_per_step = timed(step_dev, args.steps)
+    launches = backend.launches()
+    clocks = sampler.stop() if trainer.mesh.rank == 0 else {}
+
+    # end to end: pinned host tokens → device every step, loss read back every step
+    h2d = mb * (T + 1) * 8
+    losses = []
+
+    def step_e2e(i):
+        batch = host_batches[i % len(host_batches)].to(dev, non_blocking=True)
+        loss, _ = trainer.forward_backward(batch)
+        trainer.optimizer_step(lr)
+        losses.append(float(loss))        # device → host read of the step's result
+
+    e2e_ms = timed(step_e2e, args.steps)
+    status = backend.load_extension().device_status() if backend.load_extension() is not None else 0
+
+    n_law = get_parameters_count(trainer.plan.model_name, trainer.plan.depth, cfg, trainer.plan.train_config)
+    flops_step = estimate_flops(cfg, n_law) * mb
+    if trainer.mesh.rank == 0:
+        value = tokens_per_step / (ms_per_step / 1e3)
+        out = {
+            "metric": "train tokens/sec (whole job; per GPU = value / n_gpus), device-timed, max over ranks",
+            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic uniform-random token ids (seed 0), random-init weights",
+            "tokens_per_sec_per_gpu": value / world,
+            "mfu": flops_step / (ms_per_step / 1e3) / 2.25e15,
+            "config": {"model": c["name"], "global_batch": world * mb, "seq_len": T,
+                       "parallelism": (f"fsdp{world}" if world > 1 else "single") + (f"+ep{ep}" if ep > 1 else ""),
+                       "optimizer": "MuonH (Newton-Schulz 5) + AdamW/Adam-H, grad clip 1.0",
+                       "l2": "per-step working set (weights + activations, > 10 GB) far exceeds the 126 MB L2; "
+                             "no explicit flush",
+                       "params": trainer.n_params_actual, "final_loss": losses[-1] if losses else None,
+                       "device_status": int(status), "fused_comm": bool(args.fused_comm)},
+            "clocks": clocks,
+            "e2e": {"value": tokens_per_step / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms},
+            "gpu_launches": launches,
+        }
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_reference(args) -> None:
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    why = ("reference is not installable offline: /root/reference has neither setup.py nor pyproject.toml "
+           "(pip: 'Directory is not installable'), and its imports lightning, transformer_engine, sonicmoe, "
+           "mamba_ssm, causal_conv1d, jsonargparse, blobfile, flash_attn.cute are not in the image")
+    if os.path.isdir(ref) and os.listdir(ref):
+        why = "baseline/_ref exists but the reference's dependencies (lightning, transformer_engine, sonicmoe) are not importable"
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="dense", choices=sorted(CONFIGS))
+    ap.add_argument("--fused-comm", dest="fused_comm", action="store_true")
+    ap.add_argument("--no-ep", dest="no_ep", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

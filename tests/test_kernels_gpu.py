@@ -1,0 +1,183 @@
+"""sm_100a kernels vs plain PyTorch fp32 oracles (run on a B200)."""
+import math
+
+import pytest
+import torch
+
+from archscale_b200 import ops
+from archscale_b200.ops import backend
+
+pytestmark = pytest.mark.gpu
+
+
+def _ext():
+    return backend.require_extension()
+
+
+def _rel(a, b):
+    return (a.float() - b.float()).norm() / (b.float().norm() + 1e-12)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 512), (200, 264, 136), (1024, 2048, 2048), (8, 8, 64),
+                                   (4096, 1024, 264)])
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_gemm_bf16_layouts(M, N, K, mode):
+    torch.manual_seed(0)
+    dev = "cuda"
+    A = torch.randn(M, K, device=dev) * 0.5
+    B = torch.randn(N, K, device=dev) * 0.5
+    ref = A @ B.t()
+    a = A.bfloat16() if mode != 2 else A.t().contiguous().bfloat16()          # mode 2 stores Aᵀ: [K, M]
+    b = B.bfloat16() if mode == 0 else B.t().contiguous().bfloat16()          # modes 1, 2 store [K, N]
+    ref = (a.float() if mode != 2 else a.float().t()) @ (b.float().t() if mode == 0 else b.float())
+    out = _ext().gemm_bf16(a, b, mode, torch.bfloat16, None)
+    torch.cuda.synchronize()
+    assert _ext().device_status() == 0
+    assert out.shape == (M, N)
+    assert _rel(out, ref) < 1e-2, float(_rel(out, ref))
+
+
+def test_gemm_fp32_accumulate_and_epilogue():
+    torch.manual_seed(1)
+    M, N, K = 384, 520, 320
+    a = (torch.randn(K, M, device="cuda") * 0.3).bfloat16()
+    b = (torch.randn(K, N, device="cuda") * 0.3).bfloat16()
+    acc = torch.randn(M, N, device="cuda")
+    ref = acc + a.float().t() @ b.float()
+    _ext().gemm_bf16(a, b, 2, torch.float32, acc)
+    assert _rel(acc, ref) < 1e-3
+    x = (torch.randn(M, K, device="cuda") * 0.3).bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.3).bfloat16()
+    c = torch.randn(M, N, device="cuda").bfloat16()
+    out = _ext().gemm_bf16_epi(x, w, 0, 0.5, -2.0, c)
+    ref = 0.5 * (x.float() @ w.float().t()) - 2.0 * c.float()
+    assert _rel(out, ref) < 1e-2
+    assert _ext().device_status() == 0
+
+
+def test_linear_autograd_matches_reference():
+    torch.manual_seed(2)
+    x = (torch.randn(4, 96, 256, device="cuda")).bfloat16().requires_grad_()
+    w = (torch.randn(512, 256, device="cuda") * 0.05).bfloat16().requires_grad_()
+    bias = torch.randn(512, device="cuda").bfloat16().requires_grad_()
+    y = ops.linear(x, w, bias)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, bias))
+    yr = torch.nn.functional.linear(xr, wr, br)
+    yr.backward(g.float())
+    assert _rel(y, yr) < 1e-2 and _rel(x.grad, xr.grad) < 1e-2 and _rel(w.grad, wr.grad) < 1e-2 and _rel(bias.grad, br.grad) < 1e-2
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 256), (1000, 2048), (37, 1024)])
+@pytest.mark.parametrize("xdt,odt", [(torch.float32, torch.bfloat16), (torch.bfloat16, torch.bfloat16), (torch.float32, torch.float32)])
+def test_rmsnorm(rows, cols, xdt, odt):
+    torch.manual_seed(3)
+    x = torch.randn(rows, cols, device="cuda").to(xdt).requires_grad_()
+    w = (1 + 0.1 * torch.randn(cols, device="cuda")).requires_grad_()
+    y = ops.rms_norm(x, w, 1e-5, out_dtype=odt)
+    assert y.dtype == odt
+    g = torch.randn(rows, cols, device="cuda").to(odt)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = ops.rms_norm_ref(xr, wr, 1e-5)
+    yr.backward(g.float())
+    tol = 2e-2 if (xdt == torch.bfloat16 or odt == torch.bfloat16) else 1e-5
+    assert _rel(y, yr) < tol and _rel(x.grad, xr.grad) < tol and _rel(w.grad, wr.grad) < tol
+
+
+def test_rmsnorm_no_weight():
+    x = torch.randn(100, 512, device="cuda").requires_grad_()
+    y = ops.rms_norm(x, None, 1e-5)
+    y.sum().backward()
+    xr = x.detach().clone().requires_grad_()
+    ops.rms_norm_ref(xr, None, 1e-5).sum().backward()
+    assert _rel(x.grad, xr.grad) < 1e-4
+
+
+def test_swiglu_both_forms():
+    torch.manual_seed(4)
+    x = torch.randn(300, 2 * 704, device="cuda").bfloat16().requires_grad_()
+    y = ops.swiglu_packed(x)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    a, b = xr.chunk(2, dim=-1)
+    yr = torch.nn.functional.silu(a) * b
+    yr.backward(g.float())
+    assert _rel(y, yr) < 1e-2 and _rel(x.grad, xr.grad) < 1e-2
+    p = torch.randn(64, 256, device="cuda").bfloat16().requires_grad_()
+    q = torch.randn(64, 256, device="cuda").bfloat16().requires_grad_()
+    z = ops.swiglu(p, q)
+    z.backward(torch.ones_like(z))
+    pr, qr = p.detach().float().requires_grad_(), q.detach().float().requires_grad_()
+    (torch.nn.functional.silu(pr) * qr).sum().backward()
+    assert _rel(p.grad, pr.grad) < 1e-2 and _rel(q.grad, qr.grad) < 1e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("ls,zs", [(0.0, 0.0), (0.1, 1e-4)])
+def test_cross_entropy_kernel(dtype, ls, zs):
+    torch.manual_seed(5)
+    rows, V = 77, 32000
+    logits = (torch.randn(rows, V, device="cuda") * 2).to(dtype)
+    tgt = torch.randint(0, V, (rows,), device="cuda")
+    tgt[5] = -100
+    lr = logits.detach().float().requires_grad_()
+    loss_ref = ops.cross_entropy_ref(lr, tgt, -100, ls, zs, reduction="sum")
+    loss_ref.backward()
+    work = logits.clone()
+    loss = _ext().cross_entropy_fwd_bwd_(work, tgt, -100, ls, zs)
+    assert abs(float(loss.sum()) - float(loss_ref)) / abs(float(loss_ref)) < 1e-3
+    assert _rel(work, lr.grad) < (2e-2 if dtype == torch.bfloat16 else 1e-4)
+
+
+def test_fused_linear_cross_entropy_matches_reference():
+    torch.manual_seed(6)
+    N, H, V = 1024, 256, 4096
+    x = (torch.randn(N, H, device="cuda") * 0.5).bfloat16().requires_grad_()
+    w = (torch.randn(V, H, device="cuda") * 0.05).bfloat16().requires_grad_()
+    t = torch.randint(0, V, (N,), device="cuda")
+    loss = ops.fused_linear_cross_entropy(x, w, t, chunk_rows=256)
+    loss.backward()
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    lr = ops.fused_linear_cross_entropy_ref(xr, wr, t)
+    lr.backward()
+    assert abs(float(loss) - float(lr)) < 2e-2
+    assert _rel(x.grad, xr.grad) < 3e-2 and _rel(w.grad, wr.grad) < 3e-2
+
+
+@pytest.mark.parametrize("D,H,G", [(128, 4, 2), (64, 6, 3)])
+@pytest.mark.parametrize("use_norm,use_rope", [(True, True), (False, True), (True, False)])
+def test_qknorm_rope(D, H, G, use_norm, use_rope):
+    torch.manual_seed(7)
+    B, T = 2, 50
+    q = torch.randn(B, T, H, D, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(B, T, G, D, device="cuda").bfloat16().requires_grad_()
+    qw = (1 + 0.1 * torch.randn(D, device="cuda")).requires_grad_() if use_norm else None
+    kw = (1 + 0.1 * torch.randn(D, device="cuda")).requires_grad_() if use_norm else None
+    cos, sin = ops.build_rope_cache(T, D, torch.bfloat16, "cuda") if use_rope else (None, None)
+    qo, ko = ops.qk_norm_rope(q, k, qw, kw, cos, sin, 1e-5)
+    gq, gk = torch.randn_like(qo), torch.randn_like(ko)
+    (qo.float() * gq.float()).sum().backward(retain_graph=True)
+    (ko.float() * gk.float()).sum().backward()
+    from archscale_b200.ops.rope import qk_norm_rope_ref
+    qr, kr = q.detach().float().requires_grad_(), k.detach().float().requires_grad_()
+    qwr = qw.detach().clone().requires_grad_() if use_norm else None
+    kwr = kw.detach().clone().requires_grad_() if use_norm else None
+    qro, kro = qk_norm_rope_ref(qr, kr, qwr, kwr, cos, sin, 1e-5)
+    ((qro * gq.float()).sum() + (kro * gk.float()).sum()).backward()
+    assert _rel(qo, qro) < 2e-2 and _rel(ko, kro) < 2e-2
+    assert _rel(q.grad, qr.grad) < 2e-2 and _rel(k.grad, kr.grad) < 2e-2
+    if use_norm:
+        assert _rel(qw.grad, qwr.grad) < 2e-2 and _rel(kw.grad, kwr.grad) < 2e-2
+
+
+def test_newton_schulz_cuda_close_to_reference():
+    torch.manual_seed(8)
+    G = torch.randn(512, 1024, device="cuda")
+    O = ops.newton_schulz(G)
+    R = ops.newton_schulz_ref(G)
+    assert _rel(O, R) < 0.1
+    s = torch.linalg.svdvals(O.float())
+    assert s.max() < 1.6 and s.min() > 0.3
