@@ -1,0 +1,197 @@
+"""Per-kernel microbenchmarks against the measured roofline (``MEASURED_PEAKS.json``) and the
+library kernel doing the same op.  CUDA-event timing, warm-up, L2 flushed between iterations.
+
+    python -m archscale_b200.ops.bench_kernels gemm rmsnorm swiglu ce rope attn     # any subset
+    python -m archscale_b200.ops.bench_kernels gemm --json out.json
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+from archscale_b200 import ops
+from archscale_b200.ops import backend
+
+_flush = None
+
+
+def flush_l2() -> None:
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    _flush.zero_()
+
+
+def time_ms(fn, iters: int = 10, warmup: int = 3) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def peaks() -> dict:
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "kind": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "kind": "fallback"}
+
+
+def bench_gemm(res: list) -> None:
+    ext = backend.require_extension()
+    pk = peaks()
+    shapes = [  # (mode, M, N, K, what)
+        (0, 32768, 3072, 2048, "fwd qkv d16"), (0, 32768, 2048, 2048, "fwd proj d16"),
+        (0, 32768, 11264, 2048, "fwd w1 d16"), (0, 32768, 2048, 5632, "fwd w3 d16"),
+        (1, 32768, 2048, 11264, "dgrad w1 d16"), (1, 32768, 5632, 2048, "dgrad w3 d16"),
+        (2, 11264, 2048, 32768, "wgrad w1 d16"), (2, 2048, 5632, 32768, "wgrad w3 d16"),
+        (0, 4096, 32000, 2048, "flce logits chunk"), (0, 2048, 2048, 2048, "NS XXt 2048"),
+        (0, 8192, 8192, 8192, "square 8192"),
+    ]
+    for mode, M, N, K, what in shapes:
+        if mode == 0:
+            a, b = torch.randn(M, K, device="cuda").bfloat16(), torch.randn(N, K, device="cuda").bfloat16()
+            lib = lambda: a @ b.t()
+        elif mode == 1:
+            a, b = torch.randn(M, K, device="cuda").bfloat16(), torch.randn(K, N, device="cuda").bfloat16()
+            lib = lambda: a @ b
+        else:
+            a, b = torch.randn(K, M, device="cuda").bfloat16(), torch.randn(K, N, device="cuda").bfloat16()
+            lib = lambda: a.t() @ b
+        ours = lambda: ext.gemm_bf16(a, b, mode, torch.bfloat16, None)
+        t_o, t_l = time_ms(ours), time_ms(lib)
+        fl = 2.0 * M * N * K
+        res.append({"kernel": "gemm_bf16", "case": what, "mode": mode, "M": M, "N": N, "K": K, "ms": t_o,
+                    "tflops": fl / t_o / 1e9, "frac_of_" + pk["kind"] + "_peak": fl / t_o / 1e9 / pk["bf16_tflops"],
+                    "cublas_ms": t_l, "cublas_tflops": fl / t_l / 1e9, "vs_cublas": t_l / t_o})
+        print(res[-1], flush=True)
+
+
+def bench_rmsnorm(res: list) -> None:
+    pk = peaks()
+    for rows, cols, xdt in [(32768, 2048, torch.float32), (32768, 2048, torch.bfloat16), (65536, 1024, torch.float32)]:
+        x = torch.randn(rows, cols, device="cuda", dtype=xdt).requires_grad_()
+        w = torch.ones(cols, device="cuda", requires_grad=True)
+        t_f = time_ms(lambda: ops.rms_norm(x, w, 1e-5, out_dtype=torch.bfloat16))
+        y = ops.rms_norm(x, w, 1e-5, out_dtype=torch.bfloat16)
+        g = torch.randn_like(y)
+        t_b = time_ms(lambda: torch.autograd.grad(y, (x, w), g, retain_graph=True))
+        by_f = rows * cols * (x.element_size() + 2)
+        by_b = rows * cols * (2 + 2 * x.element_size())
+        t_lib = time_ms(lambda: torch.nn.functional.rms_norm(x, (cols,), w, 1e-5).bfloat16())
+        res.append({"kernel": "rmsnorm", "rows": rows, "cols": cols, "x": str(xdt), "fwd_ms": t_f,
+                    "fwd_gbs": by_f / t_f / 1e6, "fwd_frac_hbm": by_f / t_f / 1e6 / pk["hbm_gbs"], "bwd_ms": t_b,
+                    "bwd_gbs": by_b / t_b / 1e6, "bwd_frac_hbm": by_b / t_b / 1e6 / pk["hbm_gbs"], "torch_fwd_ms": t_lib})
+        print(res[-1], flush=True)
+
+
+def bench_swiglu(res: list) -> None:
+    pk = peaks()
+    rows, I = 32768, 5632
+    x = torch.randn(rows, 2 * I, device="cuda").bfloat16().requires_grad_()
+    t_f = time_ms(lambda: ops.swiglu_packed(x))
+    y = ops.swiglu_packed(x)
+    g = torch.randn_like(y)
+    t_b = time_ms(lambda: torch.autograd.grad(y, x, g, retain_graph=True))
+    by_f, by_b = rows * I * 2 * 3, rows * I * 2 * 5
+    a, b = x.detach().chunk(2, dim=-1)
+    t_lib = time_ms(lambda: torch.nn.functional.silu(a) * b)
+    res.append({"kernel": "swiglu_packed", "rows": rows, "I": I, "fwd_ms": t_f, "fwd_frac_hbm": by_f / t_f / 1e6 / pk["hbm_gbs"],
+                "bwd_ms": t_b, "bwd_frac_hbm": by_b / t_b / 1e6 / pk["hbm_gbs"], "torch_fwd_ms": t_lib})
+    print(res[-1], flush=True)
+
+
+def bench_ce(res: list) -> None:
+    pk = peaks()
+    ext = backend.require_extension()
+    rows, V = 4096, 32000
+    logits = torch.randn(rows, V, device="cuda").bfloat16()
+    tgt = torch.randint(0, V, (rows,), device="cuda")
+    t = time_ms(lambda: ext.cross_entropy_fwd_bwd_(logits, tgt, -100, 0.0, 0.0))
+    by = rows * V * 2 * 2
+    res.append({"kernel": "cross_entropy_fwd_bwd", "rows": rows, "V": V, "ms": t, "frac_hbm_min_traffic": by / t / 1e6 / pk["hbm_gbs"]})
+    print(res[-1], flush=True)
+    N, H = 32768, 2048
+    x = (torch.randn(N, H, device="cuda") * 0.5).bfloat16().requires_grad_()
+    w = (torch.randn(V, H, device="cuda") * 0.02).bfloat16().requires_grad_()
+    tg = torch.randint(0, V, (N,), device="cuda")
+
+    def flce():
+        loss = ops.fused_linear_cross_entropy(x, w, tg)
+        loss.backward()
+        x.grad = w.grad = None
+    t = time_ms(flce, iters=5)
+    fl = 3 * 2.0 * N * H * V
+    res.append({"kernel": "flce_fwd_bwd", "N": N, "H": H, "V": V, "ms": t, "tflops": fl / t / 1e9,
+                "frac_of_" + pk["kind"] + "_peak": fl / t / 1e9 / pk["bf16_tflops"]})
+    print(res[-1], flush=True)
+
+
+def bench_rope(res: list) -> None:
+    pk = peaks()
+    B, T, H, G, D = 8, 4096, 16, 4, 128
+    q = torch.randn(B, T, H, D, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(B, T, G, D, device="cuda").bfloat16().requires_grad_()
+    qw = torch.ones(D, device="cuda", requires_grad=True)
+    kw = torch.ones(D, device="cuda", requires_grad=True)
+    cos, sin = ops.build_rope_cache(T, D, torch.bfloat16, "cuda")
+    t_f = time_ms(lambda: ops.qk_norm_rope(q, k, qw, kw, cos, sin, 1e-5))
+    by = B * T * (H + G) * D * 2 * 2
+    res.append({"kernel": "qknorm_rope_fwd", "shape": [B, T, H, G, D], "ms": t_f, "frac_hbm": by / t_f / 1e6 / pk["hbm_gbs"]})
+    print(res[-1], flush=True)
+
+
+def bench_attn(res: list) -> None:
+    pk = peaks()
+    for (B, T, H, G, D, win) in [(8, 4096, 16, 4, 128, -1), (1, 8192, 20, 10, 64, 511)]:
+        q = torch.randn(B, T, H, D, device="cuda").bfloat16().requires_grad_()
+        k = torch.randn(B, T, G, D, device="cuda").bfloat16().requires_grad_()
+        v = torch.randn(B, T, G, D, device="cuda").bfloat16().requires_grad_()
+        f = lambda: ops.attention(q, k, v, window=(win, 0) if win >= 0 else (-1, -1))
+        t_f = time_ms(f)
+        o = f()
+        g = torch.randn_like(o)
+        t_b = time_ms(lambda: torch.autograd.grad(o, (q, k, v), g, retain_graph=True), iters=5)
+        span = T if win < 0 else min(T, win + 1)
+        fl = 4.0 * B * H * T * span * D * (0.5 if win < 0 else 1.0)
+        res.append({"kernel": "attention", "shape": [B, T, H, G, D], "window": win, "native": backend.has("attn_fwd"),
+                    "fwd_ms": t_f, "fwd_tflops": fl / t_f / 1e9, "bwd_ms": t_b, "bwd_tflops": 2.5 * fl / t_b / 1e9,
+                    "fwd_frac_of_" + pk["kind"] + "_peak": fl / t_f / 1e9 / pk["bf16_tflops"]})
+        print(res[-1], flush=True)
+
+
+ALL = {"gemm": bench_gemm, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "ce": bench_ce, "rope": bench_rope,
+       "attn": bench_attn}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("which", nargs="*", default=list(ALL))
+    ap.add_argument("--json", default=None)
+    a = ap.parse_args()
+    res: list = []
+    for w in a.which:
+        ALL[w](res)
+    status = backend.require_extension().device_status()
+    print("device status word:", status)
+    if a.json:
+        json.dump({"peaks": peaks(), "results": res, "device_status": status}, open(a.json, "w"), indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -268,6 +268,14 @@ extern "C" int b200_gemm_bf16(int mode, const void* A, const void* B, void* out,
                               int num_sms, int* status, cudaStream_t stream) {
   using namespace b200;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  // The tensor-map encoder is a driver call and needs the primary context current in this thread
+  // (autograd worker threads may not have touched the runtime yet).
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return -5;
+    ctx_bound = true;
+  }
   CUtensorMap ta, tb;
   int rc;
   // A
