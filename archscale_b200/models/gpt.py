@@ -235,10 +235,61 @@ class Block(nn.Module):
             x = ox + h
         return x, h, input_embed
 
+    def _deferred_ok(self, x, lc, residual_dropout) -> bool:
+        """The fused pre-norm path (residual add deferred into the next norm kernel) applies to the
+        standard block: pre-norm RMSNorm with weight, plain skip connection, MLP present, no token skipping."""
+        from archscale_b200.models.norms import FusedRMSNorm
+        cfg = self.config
+        return (x.is_cuda and not cfg.post_norm and not cfg.no_skip and not cfg.sum_skip and cfg.mlp and lc is None
+                and not hasattr(self, "layer_configurator") and type(self.norm_1) in (FusedRMSNorm,)
+                and type(self.norm_2) in (FusedRMSNorm,) and not (self.training and residual_dropout > 0))
+
+    def forward_deferred(self, x, h_pending, input_embed, rope, max_seq_length, seq_meta, kv_cache, gmu_mems,
+                         compute_dtype):
+        """Same math as :meth:`forward`; takes the residual stream ``x`` plus the not-yet-added branch
+        output ``h_pending`` of the previous block and returns its own MLP output un-added."""
+        cfg = self.config
+        scale = 1.0 / math.sqrt(2 * cfg.n_layer) if cfg.depth_scale else 1.0
+        cu_seqlens = seq_meta.get("cu_seqlens") if seq_meta else None
+        seq_idx = seq_meta.get("seq_idx") if seq_meta else None
+        pad_mask = seq_meta.get("pad_mask") if seq_meta else None
+        x, n_1 = ops.add_rms_norm(x, h_pending, self.norm_1.weight, self.norm_1.eps, scale, compute_dtype)
+        new_kv_cache = kv_cache
+        if self.use_rnn:
+            if self.rnn_type in ("mamba", "mamba2"):
+                h, gmu_mems = self.attn(n_1, seq_idx=seq_idx, mask=cu_seqlens if cfg.use_cu_seqlen else pad_mask,
+                                        gmu_mems=gmu_mems)
+            else:
+                h, gmu_mems = self.attn(n_1, attention_mask=None if cfg.use_cu_seqlen else pad_mask,
+                                        cu_seqlens=cu_seqlens, gmu_mems=gmu_mems)
+        elif self.use_gmu:
+            h, gmu_mems = self.attn(n_1, gmu_mems)
+        else:
+            h, new_kv_cache, gmu_mems = self.attn(n_1, rope, max_seq_length, cu_seqlens, None, kv_cache, gmu_mems)
+        if self.collect_stats:
+            with torch.no_grad():
+                self.attn_output_rmsnorm = compute_rmsnorm(h) * scale
+                self.attn_outlier_pct = compute_outlier_percentage(h)
+                self.attn_z_mean = getattr(self.attn, "z_mean", None)
+        x, n_2 = ops.add_rms_norm(x, h.to(compute_dtype), self.norm_2.weight, self.norm_2.eps, scale, compute_dtype)
+        if cfg.moe:
+            h = self.mlp(n_2)
+        else:
+            h, gmu_mems = self.mlp(n_2, self.layer_idx, gmu_mems)
+        if self.collect_stats:
+            with torch.no_grad():
+                self.mlp_output_rmsnorm = compute_rmsnorm(h) * scale
+                self.mlp_outlier_pct = compute_outlier_percentage(h)
+                self.router_z_mean = getattr(self.mlp, "router_z_mean", None)
+        return x, new_kv_cache, gmu_mems, input_embed, h.to(compute_dtype)
+
     def forward(self, x, input_embed, rope, max_seq_length: int, seq_meta=None, input_pos=None, kv_cache=None,
                 lc=None, gmu_mems=None, residual_dropout: float = 0.0, lc_gate_hist=None,
-                compute_dtype: torch.dtype = torch.bfloat16):
+                compute_dtype: torch.dtype = torch.bfloat16, h_pending=None, deferred: bool = False):
         cfg = self.config
+        if deferred:
+            return self.forward_deferred(x, h_pending, input_embed, rope, max_seq_length, seq_meta, kv_cache, gmu_mems,
+                                         compute_dtype)
         cu_seqlens = seq_meta.get("cu_seqlens") if seq_meta else None
         seq_idx = seq_meta.get("seq_idx") if seq_meta else None
         pad_mask = seq_meta.get("pad_mask") if seq_meta else None
@@ -434,12 +485,24 @@ class GPT(nn.Module):
         self.attn_outlier_pcts, self.mlp_outlier_pcts = [], []
         self.attn_z_means, self.router_z_means = [], []
 
+        h_pending = None
+        blocks = list(self.transformer.h)
+        from archscale_b200.models.norms import FusedRMSNorm
+        use_deferred = (self.compute_dtype == torch.bfloat16 and self.layer_configurator is None
+                        and type(self.transformer.ln_f) is FusedRMSNorm and cfg.n_embd in ops.norm._FUSED_COLS
+                        and all(b._deferred_ok(x, None, residual_dropout) for b in blocks))
+
         def run(block):
-            nonlocal x, kv_cache, gmu_mems, input_embed
-            x, kv_cache, gmu_mems, input_embed = block(
-                x, input_embed, rope, max_seq_length, seq_meta, lc=self.layer_configurator, kv_cache=kv_cache,
-                gmu_mems=gmu_mems, residual_dropout=residual_dropout, lc_gate_hist=self.lc_gate_hist,
-                compute_dtype=self.compute_dtype)
+            nonlocal x, kv_cache, gmu_mems, input_embed, h_pending
+            if use_deferred:
+                x, kv_cache, gmu_mems, input_embed, h_pending = block(
+                    x, input_embed, rope, max_seq_length, seq_meta, kv_cache=kv_cache, gmu_mems=gmu_mems,
+                    compute_dtype=self.compute_dtype, h_pending=h_pending, deferred=True)
+            else:
+                x, kv_cache, gmu_mems, input_embed = block(
+                    x, input_embed, rope, max_seq_length, seq_meta, lc=self.layer_configurator, kv_cache=kv_cache,
+                    gmu_mems=gmu_mems, residual_dropout=residual_dropout, lc_gate_hist=self.lc_gate_hist,
+                    compute_dtype=self.compute_dtype)
             if self.collect_stats:
                 self.attn_output_rmsnorms.append(block.attn_output_rmsnorm)
                 self.mlp_output_rmsnorms.append(block.mlp_output_rmsnorm)
@@ -464,7 +527,12 @@ class GPT(nn.Module):
                 run(block)
         if cfg.sum_skip:
             x = input_embed
-        x = _norm_to(self.transformer.ln_f, x, self.compute_dtype)
+        if use_deferred:
+            scale = 1.0 / math.sqrt(2 * cfg.n_layer) if cfg.depth_scale else 1.0
+            _, x = ops.add_rms_norm(x, h_pending, self.transformer.ln_f.weight, self.transformer.ln_f.eps, scale,
+                                    self.compute_dtype)
+        else:
+            x = _norm_to(self.transformer.ln_f, x, self.compute_dtype)
         if self.logit_scale != 1.0:
             x = x * self.logit_scale
         if use_flce_loss:

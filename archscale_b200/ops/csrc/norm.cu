@@ -127,6 +127,109 @@ __global__ void reduce_partials_kernel(const float* __restrict__ part, float* __
   out[c] = s;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Fused residual-add + RMSNorm (pre-norm transformer block):
+//   x = res + h_scale·h  (fp32, written back as the new residual stream)   n = rmsnorm(x)·w  (bf16)
+// Backward in one pass: d_res = g_res + rmsnorm_bwd(g_n),  d_h = bf16(h_scale·d_res); the weight
+// gradient is accumulated in registers (a lane owns columns lane·8 + 256·i), then per CTA in shared
+// memory, then written as per-CTA partials.
+template <typename TRES, typename TW, bool HAS_H>
+__global__ void __launch_bounds__(256) add_rmsnorm_fwd_kernel(const TRES* __restrict__ res, const __nv_bfloat16* __restrict__ h,
+                                                              float h_scale, const TW* __restrict__ w, float* __restrict__ res_out,
+                                                              __nv_bfloat16* __restrict__ n_out, float* __restrict__ rstd_out,
+                                                              int rows, int cols, float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + warp;
+  if (row >= rows) return;
+  const size_t base = static_cast<size_t>(row) * cols;
+  float ss = 0.f;
+  for (int c = lane * 8; c < cols; c += 256) {
+    float v[8]; Vec8<TRES>::load(res + base + c, v);
+    if (HAS_H) {
+      float hv[8]; Vec8<__nv_bfloat16>::load(h + base + c, hv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] += h_scale * hv[i];
+      Vec8<float>::store(res_out + base + c, v);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+  }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / cols + eps);
+  if (lane == 0) rstd_out[row] = rstd;
+  for (int c = lane * 8; c < cols; c += 256) {
+    float v[8];
+    if (HAS_H) Vec8<float>::load(res_out + base + c, v);   // just written by this lane (L1 hit)
+    else Vec8<TRES>::load(res + base + c, v);
+    float g[8]; Vec8<TW>::load(w + c, g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = v[i] * rstd * g[i];
+    Vec8<__nv_bfloat16>::store(n_out + base + c, v);
+  }
+}
+
+template <typename TX, typename TW, int NCH>
+__global__ void __launch_bounds__(256) add_rmsnorm_bwd_kernel(const float* __restrict__ g_res, const __nv_bfloat16* __restrict__ g_n,
+                                                              const TX* __restrict__ x, const TW* __restrict__ w,
+                                                              const float* __restrict__ rstd, float* __restrict__ d_res,
+                                                              __nv_bfloat16* __restrict__ d_h, float h_scale,
+                                                              float* __restrict__ dw_partial, int rows, int cols) {
+  extern __shared__ float dw_s[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) dw_s[c] = 0.f;
+  __syncthreads();
+  float dwacc[NCH][8];
+#pragma unroll
+  for (int i = 0; i < NCH; ++i)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dwacc[i][e] = 0.f;
+  float wreg[NCH][8];
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) Vec8<TW>::load(w + lane * 8 + i * 256, wreg[i]);
+  for (int row = blockIdx.x * 8 + warp; row < rows; row += gridDim.x * 8) {
+    const size_t base = static_cast<size_t>(row) * cols;
+    const float rs = rstd[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      const int c = lane * 8 + i * 256;
+      float xv[8], dv[8]; Vec8<TX>::load(x + base + c, xv); Vec8<__nv_bfloat16>::load(g_n + base + c, dv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dot += dv[e] * wreg[i][e] * xv[e];
+    }
+    dot = warp_sum(dot);
+    const float c1 = dot * rs * rs * rs / cols;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      const int c = lane * 8 + i * 256;
+      float xv[8], dv[8], o[8]; Vec8<TX>::load(x + base + c, xv); Vec8<__nv_bfloat16>::load(g_n + base + c, dv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        o[e] = dv[e] * wreg[i][e] * rs - xv[e] * c1;
+        dwacc[i][e] += dv[e] * xv[e] * rs;
+      }
+      if (g_res) {
+        float gr[8]; Vec8<float>::load(g_res + base + c, gr);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] += gr[e];
+      }
+      Vec8<float>::store(d_res + base + c, o);
+      if (d_h) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] *= h_scale;
+        Vec8<__nv_bfloat16>::store(d_h + base + c, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NCH; ++i)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) atomicAdd(&dw_s[lane * 8 + i * 256 + e], dwacc[i][e]);
+  __syncthreads();
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) dw_partial[static_cast<size_t>(blockIdx.x) * cols + c] = dw_s[c];
+}
+
 constexpr int kBwdCtas = 148 * 2;
 
 }  // namespace b200
@@ -179,5 +282,62 @@ extern "C" int b200_rmsnorm_bwd(const void* dy, int dy_dtype, const void* x, int
   DISPATCH_3(dy_dtype, w_dtype, x_dtype, CALL)
 #undef CALL
   if (w) reduce_partials_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(dw_partial, dw, grid, cols);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int b200_add_rmsnorm_fwd(const void* res, int res_dtype, const void* h, float h_scale, const void* w, int w_dtype,
+                                    float* res_out, void* n_out, float* rstd, int rows, int cols, float eps,
+                                    cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (cols % 8) return -1;
+  const int grid = (rows + 7) / 8;
+  typedef __nv_bfloat16 bf;
+#define L(TRES, TW, HH)                                                                                              \
+  add_rmsnorm_fwd_kernel<TRES, TW, HH><<<grid, 256, 0, stream>>>(static_cast<const TRES*>(res), static_cast<const bf*>(h), \
+                                                                 h_scale, static_cast<const TW*>(w), res_out,         \
+                                                                 static_cast<bf*>(n_out), rstd, rows, cols, eps)
+  if (h) {
+    if (res_dtype == 0 && w_dtype == 0) L(float, float, true);
+    else if (res_dtype == 0 && w_dtype == 1) L(float, bf, true);
+    else if (res_dtype == 1 && w_dtype == 0) L(bf, float, true);
+    else L(bf, bf, true);
+  } else {
+    if (res_dtype == 0 && w_dtype == 0) L(float, float, false);
+    else if (res_dtype == 0 && w_dtype == 1) L(float, bf, false);
+    else if (res_dtype == 1 && w_dtype == 0) L(bf, float, false);
+    else L(bf, bf, false);
+  }
+#undef L
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// cols must be one of 1024, 2048, 2560, 3072, 4096 (register-resident dw accumulators); returns -2 otherwise.
+extern "C" int b200_add_rmsnorm_bwd(const float* g_res, const void* g_n, const void* x, int x_dtype, const void* w, int w_dtype,
+                                    const float* rstd, float* d_res, void* d_h, float h_scale, float* dw_partial, float* dw,
+                                    int rows, int cols, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  const int grid = b200_rmsnorm_bwd_partials(rows, cols);
+  const size_t smem = sizeof(float) * cols;
+  typedef __nv_bfloat16 bf;
+#define L(TX, TW, NCH)                                                                                                 \
+  add_rmsnorm_bwd_kernel<TX, TW, NCH><<<grid, 256, smem, stream>>>(g_res, static_cast<const bf*>(g_n), static_cast<const TX*>(x), \
+                                                                   static_cast<const TW*>(w), rstd, d_res, static_cast<bf*>(d_h), \
+                                                                   h_scale, dw_partial, rows, cols)
+#define LN(NCH)                                                  \
+  if (x_dtype == 0 && w_dtype == 0) L(float, float, NCH);        \
+  else if (x_dtype == 0 && w_dtype == 1) L(float, bf, NCH);      \
+  else if (x_dtype == 1 && w_dtype == 0) L(bf, float, NCH);      \
+  else L(bf, bf, NCH);
+  switch (cols) {
+    case 1024: LN(4) break;
+    case 2048: LN(8) break;
+    case 2560: LN(10) break;
+    case 3072: LN(12) break;
+    case 4096: LN(16) break;
+    default: return -2;
+  }
+#undef LN
+#undef L
+  reduce_partials_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(dw_partial, dw, grid, cols);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

@@ -84,6 +84,7 @@ class _LinearFn(torch.autograd.Function):
     def forward(ctx, x, weight, bias):
         ctx.save_for_backward(x, weight)
         ctx.has_bias = bias is not None
+        ctx.weight_ref = weight            # to find ``main_grad`` (fp32 flat-buffer view) in backward
         x2 = x.reshape(-1, x.shape[-1])
         y = matmul_nt(x2, weight)
         if bias is not None:
@@ -101,7 +102,11 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = matmul_nn(dy2, weight).view(x.shape)
         if ctx.needs_input_grad[1]:
-            dw = matmul_tn(dy2, x2)
+            main_grad = getattr(ctx.weight_ref, "main_grad", None)
+            if main_grad is not None:
+                matmul_tn_acc_(main_grad, dy2, x2)      # wgrad accumulates straight into fp32
+            else:
+                dw = matmul_tn(dy2, x2)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.float().sum(0).to(dy.dtype)
         return dx, dw, db

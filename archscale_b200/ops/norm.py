@@ -110,3 +110,64 @@ def layer_norm(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[t
 def gated_rms_norm(x, weight, z=None, eps: float = 1e-5, group_size: Optional[int] = None,
                    norm_before_gate: bool = True) -> torch.Tensor:
     return gated_rms_norm_ref(x, weight, z, eps, group_size, norm_before_gate)
+
+
+# ------------------------------------------------------------------ fused residual add + RMSNorm
+def add_rms_norm_ref(res: torch.Tensor, h: Optional[torch.Tensor], weight: torch.Tensor, eps: float = 1e-5,
+                     h_scale: float = 1.0, out_dtype: torch.dtype = torch.bfloat16):
+    """x = res + h_scale·h in fp32; returns (x fp32, rmsnorm(x)·w in ``out_dtype``)."""
+    x = res.float()
+    if h is not None:
+        x = x + h_scale * h.float()
+    return x, rms_norm_ref(x, weight, eps).to(out_dtype)
+
+
+class _AddRMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, res, h, weight, eps, h_scale):
+        ext = backend.require_extension()
+        shape = res.shape
+        res2 = res.reshape(-1, shape[-1])
+        h2 = h.reshape(-1, shape[-1]) if h is not None else None
+        x, n, rstd = ext.add_rmsnorm_fwd(res2, h2, h_scale, weight, eps)
+        backend.count_launch()
+        ctx.save_for_backward(x, weight, rstd)
+        ctx.shape, ctx.h_scale, ctx.has_h, ctx.res_dtype = shape, h_scale, h is not None, res.dtype
+        return x.view(shape), n.view(shape)
+
+    @staticmethod
+    def backward(ctx, g_x, g_n):
+        ext = backend.require_extension()
+        x, weight, rstd = ctx.saved_tensors
+        C = ctx.shape[-1]
+        if g_n is None:
+            g_n = torch.zeros(x.shape, dtype=torch.bfloat16, device=x.device)
+        g_n2 = g_n.reshape(-1, C)
+        if not g_n2.is_contiguous():
+            g_n2 = g_n2.contiguous()
+        g_x2 = None
+        if g_x is not None:
+            g_x2 = g_x.reshape(-1, C)
+            if g_x2.dtype != torch.float32 or not g_x2.is_contiguous():
+                g_x2 = g_x2.float().contiguous()
+        d_res, d_h, dw = ext.add_rmsnorm_bwd(g_x2, g_n2, x, weight, rstd, ctx.has_h, ctx.h_scale)
+        backend.count_launch(2)
+        if ctx.res_dtype != torch.float32:
+            d_res = d_res.to(ctx.res_dtype)
+        return d_res.view(ctx.shape), (d_h.view(ctx.shape) if ctx.has_h else None), dw.to(weight.dtype), None, None
+
+
+_FUSED_COLS = (1024, 2048, 2560, 3072, 4096)
+
+
+def add_rms_norm(res: torch.Tensor, h: Optional[torch.Tensor], weight: torch.Tensor, eps: float = 1e-5,
+                 h_scale: float = 1.0, out_dtype: torch.dtype = torch.bfloat16):
+    """Pre-norm block entry: ``x = res + h_scale·h`` (new fp32 residual stream) and ``rmsnorm(x)·w``.
+
+    One kernel forward; backward fuses the residual-gradient add, the RMSNorm backward and the bf16
+    cast of the branch gradient."""
+    if (res.shape[-1] in _FUSED_COLS and out_dtype == torch.bfloat16 and res.dtype in (torch.float32, torch.bfloat16)
+            and (h is None or h.dtype == torch.bfloat16) and backend.has("add_rmsnorm_fwd")
+            and backend.use_cuda_kernel("add_rmsnorm", res, h, weight)):
+        return _AddRMSNormFn.apply(res.contiguous(), None if h is None else h.contiguous(), weight, eps, h_scale)
+    return add_rms_norm_ref(res, h, weight, eps, h_scale, out_dtype)

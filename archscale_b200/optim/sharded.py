@@ -34,12 +34,7 @@ from archscale_b200.optim import scalar_opts
 from archscale_b200.parallel import dist_utils as du
 from archscale_b200.parallel.fsdp import FlatGroup, FSDPEngine, ParamSpec
 
-VECTOR_NAMES = ("conv1d", "wte", "lm_head", "norm", "ln", "layernorm")
-
-
-def is_vector_param(name: str) -> bool:
-    n = name.lower()
-    return ("weight" not in n) or any(v in n for v in VECTOR_NAMES)
+from archscale_b200.utils.param_groups import VECTOR_NAMES, is_vector_param  # noqa: E402,F401
 
 
 @dataclass
@@ -190,10 +185,15 @@ class ShardedOptimizer:
                                                  self.step_count, self.eps)
 
         # ---- matrices: momentum on local slices, orthogonalise on owners, scatter back
+        hb_x: List[torch.Tensor] = [t[0] for t in pending_hyper]
+        hb_u: List[torch.Tensor] = [t[1] for t in pending_hyper]
+        hb_k: List[int] = [t[2] for t in pending_hyper]
+        hb_lr: List[float] = [t[3] for t in pending_hyper]
         if self.mats:
             o_shards = self._orthogonalised_updates(u_sq)
             lr_m = self._lr_for("matrix")
             wd = self.weight_decay
+            xs, os_, ks, adj = [], [], [], []
             for mt in self.mats:
                 g = mt.group
                 if g.grad is None:
@@ -202,32 +202,42 @@ class ShardedOptimizer:
                 lo, hi = max(mt.offset, a), min(mt.offset + mt.rows * mt.cols, b)
                 if lo >= hi:
                     continue
-                x = g.master[lo - a:hi - a]
-                o = o_shards[id(g)][lo - a:hi - a]
+                xs.append(g.master[lo - a:hi - a])
+                os_.append(o_shards[id(g)][lo - a:hi - a])
+                ks.append(mt.norm_idx)
+                adj.append(-self._adjusted_lr(lr_m, mt.rows, mt.cols))
+            if xs:
                 if wd:
-                    x.mul_(1 - lr_m * wd)
+                    torch._foreach_mul_(xs, 1 - lr_m * wd)
                 if self.use_muonh:
-                    x_sq[mt.norm_idx] += x.float().pow(2).sum()
-                    pending_hyper.append((x, o, mt.norm_idx, lr_m))
+                    sq = torch.stack(torch._foreach_norm(xs)).square()
+                    x_sq.index_add_(0, torch.tensor(ks, device=dev), sq)
+                    hb_x += xs
+                    hb_u += os_
+                    hb_k += ks
+                    hb_lr += [lr_m] * len(xs)
                 else:
-                    x.add_(o.to(x.dtype), alpha=-self._adjusted_lr(lr_m, mt.rows, mt.cols))
+                    upd = torch._foreach_mul([o.to(x.dtype) for o, x in zip(os_, xs)], adj)
+                    torch._foreach_add_(xs, upd)
 
         # ---- hyperball: global norms (2 all-reduces for the whole model), update, renormalise
-        if pending_hyper:
+        if hb_x:
             if eng.mesh.fsdp > 1:
                 packed = torch.stack((x_sq, u_sq))
                 du.all_reduce_sum(packed, group=eng.mesh.fsdp_group)
                 x_sq, u_sq = packed[0], packed[1]
             x_norm, u_norm = x_sq.sqrt(), u_sq.sqrt().clamp_min(self.ns_epsilon)
+            kidx = torch.tensor(hb_k, device=dev)
+            coef = (x_norm / u_norm)[kidx] * torch.tensor(hb_lr, device=dev, dtype=torch.float32)
+            upd = [u.to(x.dtype) if u.dtype != x.dtype else u for u, x in zip(hb_u, hb_x)]
+            upd = torch._foreach_mul(upd, list(coef.unbind(0)))
+            torch._foreach_sub_(hb_x, upd)
             new_sq = torch.zeros_like(x_sq)
-            for x, u, k, lr_p in pending_hyper:
-                x.add_(u.to(x.dtype) * (x_norm[k] / u_norm[k] * lr_p).to(x.dtype), alpha=-1.0)
-                new_sq[k] += x.float().pow(2).sum()
+            new_sq.index_add_(0, kidx, torch.stack(torch._foreach_norm(hb_x)).square())
             if eng.mesh.fsdp > 1:
                 du.all_reduce_sum(new_sq, group=eng.mesh.fsdp_group)
-            scale = x_norm / new_sq.sqrt().clamp_min(self.ns_epsilon)
-            for x, u, k, lr_p in pending_hyper:
-                x.mul_(scale[k])
+            scale = (x_norm / new_sq.sqrt().clamp_min(self.ns_epsilon))[kidx]
+            torch._foreach_mul_(hb_x, list(scale.unbind(0)))
         eng.mark_params_updated()
 
     # ------------------------------------------------------------------ Muon transport + NS
@@ -242,19 +252,20 @@ class ShardedOptimizer:
         for gid, g in groups.items():
             if g.grad is None:
                 continue
-            # 1. momentum (fp32) and the pre-orthogonalisation update U on the local shard
+            # 1. momentum (fp32) and the pre-orthogonalisation update U on the local shard.  Matrices
+            #    are the contiguous prefix [0, matrix_numel) of the flat group, so this is one slice.
             m = self.m[gid]
             mask_mats = [mt for mt in self.mats if mt.group is g]
             a, b = g.shard_range()
             u_shard = torch.zeros(g.shard_numel, dtype=cdt, device=eng.device)
-            for mt in mask_mats:
-                lo, hi = max(mt.offset, a), min(mt.offset + mt.rows * mt.cols, b)
-                if lo >= hi:
-                    continue
-                ms, gs = m[lo - a:hi - a], g.grad[lo - a:hi - a]
+            n_loc = min(b, g.matrix_numel) - a
+            if n_loc > 0:
+                ms, gs = m[:n_loc], g.grad[:n_loc]
                 ms.mul_(self.mu).add_(gs)
-                u = gs.add(ms, alpha=self.mu) if self.nesterov else ms
-                u_shard[lo - a:hi - a].copy_(u)
+                if self.nesterov:
+                    u_shard[:n_loc].copy_(torch.add(gs, ms, alpha=self.mu))
+                else:
+                    u_shard[:n_loc].copy_(ms)
             # 2. assemble whole matrices (every rank gets the full flat U; owners use their matrices)
             if g.world > 1:
                 if eng.symm is not None:

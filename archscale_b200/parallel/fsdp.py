@@ -29,6 +29,8 @@ from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
 import torch
 import torch.nn as nn
 
+from archscale_b200.utils.param_groups import is_matrix_param
+
 from . import dist_utils as du
 from .mesh import Mesh
 
@@ -136,6 +138,23 @@ class FlatGroup:
             else:
                 s.param.data = full[s.offset:s.offset + s.numel].view(s.shape)
 
+    # The gathered buffer is ONE persistent tensor per group whose storage is shrunk to zero bytes
+    # when the unit is resharded and grown again before the next gather.  Parameter views and the
+    # tensors autograd saved for backward keep pointing at this storage object, so they see the
+    # re-gathered values in backward (a pooled buffer would be recycled for another unit in between).
+    def alloc_full(self) -> torch.Tensor:
+        if self.full is None:
+            self.full = torch.empty(self.padded, dtype=self.dtype, device=self.device)
+            self._full_nbytes = self.full.untyped_storage().nbytes()
+            self.set_param_views(self.full)
+        elif self.full.untyped_storage().nbytes() == 0:
+            self.full.untyped_storage().resize_(self._full_nbytes)
+        return self.full
+
+    def free_full(self) -> None:
+        if self.full is not None and self.world > 1:
+            self.full.untyped_storage().resize_(0)
+
 
 class Unit:
     def __init__(self, name: str, module: nn.Module, groups: List[FlatGroup], is_root: bool) -> None:
@@ -177,6 +196,7 @@ class FSDPEngine:
         self.fused_comm = fused_comm and self.world > 1 and self.is_cuda
         self.symm = None
         self.in_backward = False
+        self.use_main_grad = self.is_cuda and param_dtype == torch.bfloat16
         self.requires_gradient_sync = True
         self.grad_scale = 1.0 / max(self.mesh.data_world, 1)
         self._rs_events: List[object] = []
@@ -209,11 +229,14 @@ class FSDPEngine:
             groups = []
             for (dt, local), items in buckets.items():
                 specs, off = [], 0
+                # matrices first: the Muon-managed part of every flat group is one contiguous prefix
+                items = sorted(items, key=lambda it: 0 if is_matrix_param(it[0], it[1].dim()) else 1)
                 for n, p in items:
                     specs.append(ParamSpec(n, p, p.shape, p.numel(), off))
                     off += p.numel()
                 g = FlatGroup(specs, dt, self.world, self.rank, self.group, self.device, sharded=not local)
                 g.ep_local = local
+                g.matrix_numel = sum(s.numel for s in specs if is_matrix_param(s.name, len(s.shape)))
                 g.shard_from_params()
                 groups.append(g)
             return Unit(uname, mod, groups, is_root)
@@ -235,6 +258,9 @@ class FSDPEngine:
         for u in self.units:
             for g in u.groups:
                 g.set_param_views(None)
+                if g.world > 1:
+                    g.alloc_full()
+                    g.free_full()
 
     def _register_hooks(self) -> None:
         for u in self.units:
@@ -251,20 +277,20 @@ class FSDPEngine:
             for g in unit.groups:
                 lp = g.refresh_lp()
                 if g.world == 1:
-                    g.full = lp
+                    if g.full is not lp:
+                        g.full = lp
+                        g.set_param_views(lp)
                     g.gather_event = None
-                else:
-                    if self.is_cuda:
-                        self.comm_stream.wait_stream(torch.cuda.current_stream())
-                        with torch.cuda.stream(self.comm_stream):
-                            g.full = self.pool.get(g.padded, g.dtype, self.device, self.comm_stream)
-                            self._all_gather(g, lp)
-                            g.gather_event = torch.cuda.Event()
-                            g.gather_event.record(self.comm_stream)
-                    else:
-                        g.full = self.pool.get(g.padded, g.dtype, self.device)
+                elif self.is_cuda:
+                    self.comm_stream.wait_stream(torch.cuda.current_stream())
+                    with torch.cuda.stream(self.comm_stream):
+                        g.alloc_full()
                         self._all_gather(g, lp)
-                g.set_param_views(g.full)
+                        g.gather_event = torch.cuda.Event()
+                        g.gather_event.record(self.comm_stream)
+                else:
+                    g.alloc_full()
+                    self._all_gather(g, lp)
             unit.unsharded = True
         if wait and self.is_cuda:
             for g in unit.groups:
@@ -282,10 +308,14 @@ class FSDPEngine:
         if not unit.unsharded:
             return
         for g in unit.groups:
-            g.set_param_views(None)
             if g.world > 1 and g.full is not None:
-                self.pool.put(g.full)
-            g.full = None
+                if self.is_cuda:
+                    # free on the communication stream, after the compute stream is done with the values
+                    self.comm_stream.wait_stream(torch.cuda.current_stream())
+                    with torch.cuda.stream(self.comm_stream):
+                        g.free_full()
+                else:
+                    g.free_full()
         unit.unsharded = False
 
     # ------------------------------------------------------------------ hooks
@@ -347,10 +377,25 @@ class FSDPEngine:
         j = i + step
         return order[j] if 0 <= j < len(order) else None
 
+    def _attach_main_grads(self, unit: Unit) -> None:
+        """fp32 flat gradient buffers for the unit; ``Linear`` weight gradients are accumulated into
+        them by the wgrad GEMM itself (``param.main_grad``), so no bf16 dW is ever materialised."""
+        if not self.use_main_grad:
+            return
+        for g in unit.groups:
+            if g.full_grad is None:
+                g.full_grad = self.pool.get(g.padded, torch.float32, self.device)
+                g.full_grad.zero_()
+            for s in g.specs:
+                s.param.main_grad = g.full_grad[s.offset:s.offset + s.numel].view(s.shape)
+
     def _pre_backward(self, unit: Unit) -> None:
         if unit.post_bwd_done:
             return
         self._unshard(unit)
+        if not getattr(unit, "_mg_attached", False):
+            self._attach_main_grads(unit)
+            unit._mg_attached = True
         prv = self._neighbor(unit, -1)
         if prv is not None and prv.bwd_pending and not prv.post_bwd_done:
             self._unshard(prv, wait=False)
@@ -359,6 +404,11 @@ class FSDPEngine:
         if unit.post_bwd_done:
             return
         unit.post_bwd_done, unit.bwd_pending = True, False
+        unit._mg_attached = False
+        for g in unit.groups:
+            for s in g.specs:
+                if hasattr(s.param, "main_grad"):
+                    del s.param.main_grad
         self._reduce_unit_grads(unit)
         if self.world > 1:
             self._reshard(unit)

@@ -181,3 +181,54 @@ def test_newton_schulz_cuda_close_to_reference():
     assert _rel(O, R) < 0.1
     s = torch.linalg.svdvals(O.float())
     assert s.max() < 1.6 and s.min() > 0.3
+
+
+@pytest.mark.parametrize("cols", [1024, 2048, 2560])
+@pytest.mark.parametrize("res_dtype", [torch.float32, torch.bfloat16])
+def test_add_rms_norm_fused(cols, res_dtype):
+    torch.manual_seed(9)
+    rows = 517
+    res = torch.randn(rows, cols, device="cuda").to(res_dtype).requires_grad_()
+    h = torch.randn(rows, cols, device="cuda").bfloat16().requires_grad_()
+    w = (1 + 0.1 * torch.randn(cols, device="cuda")).requires_grad_()
+    x, n = ops.add_rms_norm(res, h, w, 1e-5, 0.25)
+    gx, gn = torch.randn_like(x), torch.randn_like(n)
+    torch.autograd.backward((x, n), (gx, gn))
+    rr, hr, wr = (t.detach().float().requires_grad_() for t in (res, h, w))
+    xr, nr = ops.add_rms_norm_ref(rr, hr, wr, 1e-5, 0.25, torch.float32)
+    torch.autograd.backward((xr, nr), (gx.float(), gn.float()))
+    assert _rel(x, xr) < 1e-5 and _rel(n, nr) < 1e-2
+    assert _rel(res.grad, rr.grad) < 1e-2 and _rel(h.grad, hr.grad) < 1e-2 and _rel(w.grad, wr.grad) < 1e-2
+    # without a pending branch (first block): residual passes through unchanged
+    x2, n2 = ops.add_rms_norm(res.detach(), None, w.detach(), 1e-5, 1.0)
+    assert _rel(n2, ops.rms_norm_ref(res.detach().float(), w.detach(), 1e-5)) < 1e-2
+
+
+def test_model_deferred_residual_matches_generic_path():
+    """The fused (deferred residual) block path and the generic module path give the same loss/grads."""
+    from archscale_b200 import Config
+    from archscale_b200.models.gpt import GPT
+    torch.manual_seed(10)
+    cfg = Config.from_name("transformer_gqa4_d8", n_layer=2, ar=None, n_embd=1024, n_head=8, n_query_groups=4,
+                           head_dim=128, intermediate_size=2048, vocab_size=1024, padding_multiple=64, block_size=256,
+                           qk_norm=True, depth_scale=True)
+    with torch.device("cuda"):
+        m = GPT(cfg)
+    m.reset_parameters()
+    m = m.bfloat16()
+    idx = torch.randint(0, 1024, (2, 256), device="cuda")
+    out = m(idx).logits
+    out.float().pow(2).mean().backward()
+    g1 = {n: p.grad.clone() for n, p in m.named_parameters()}
+    m.zero_grad()
+    import archscale_b200.ops.norm as nm
+    saved = nm._FUSED_COLS
+    nm._FUSED_COLS = ()
+    try:
+        out2 = m(idx).logits
+        out2.float().pow(2).mean().backward()
+    finally:
+        nm._FUSED_COLS = saved
+    assert _rel(out, out2) < 2e-2
+    for n, p in m.named_parameters():
+        assert _rel(g1[n], p.grad) < 5e-2, n
