@@ -51,6 +51,21 @@ int b200_qknorm_rope_bwd(const void* dqo, const void* dko, const void* q, const 
                          int64_t n_tokens, int T, int H, int G, int D, cudaStream_t stream);
 int b200_qknorm_rope_grid();
 
+// ---- peer-memory collectives (comm.cu).  `bases[p]` = local mapping of rank p's symmetric heap.
+void b200_set_peer_wait_limit_cycles(long long cycles);
+int b200_symm_barrier(const void* const* bases, size_t signal_off, int channel, int rank, int world, uint32_t epoch,
+                      int* status, cudaStream_t stream);
+int b200_symm_post(const void* const* bases, size_t signal_off, int channel, int rank, int world, uint32_t epoch,
+                   cudaStream_t stream);
+int b200_symm_wait(const void* const* bases, size_t signal_off, int channel, int rank, int world, uint32_t epoch,
+                   int* status, cudaStream_t stream);
+int b200_allgather_pull(const void* const* bases, size_t src_off, void* dst, size_t shard_bytes, int rank, int world,
+                        int max_ctas, cudaStream_t stream);
+int b200_reduce_scatter_pull(const void* const* bases, size_t full_off, float* out, size_t shard_elems, int rank,
+                             int world, float scale, int accumulate, int max_ctas, cudaStream_t stream);
+int b200_reduce_scatter_pull_bf16(const void* const* bases, size_t full_off, void* out, size_t shard_elems, int rank,
+                                  int world, int max_ctas, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -257,7 +257,11 @@ class ShardedOptimizer:
             m = self.m[gid]
             mask_mats = [mt for mt in self.mats if mt.group is g]
             a, b = g.shard_range()
-            u_shard = torch.zeros(g.shard_numel, dtype=cdt, device=eng.device)
+            if eng.symm is not None and g.world > 1:
+                u_shard = eng.symm.u_buffer(g)
+                u_shard.zero_()
+            else:
+                u_shard = torch.zeros(g.shard_numel, dtype=cdt, device=eng.device)
             n_loc = min(b, g.matrix_numel) - a
             if n_loc > 0:
                 ms, gs = m[:n_loc], g.grad[:n_loc]
@@ -276,7 +280,11 @@ class ShardedOptimizer:
             else:
                 u_full = u_shard
             # 3. Newton–Schulz on owned matrices, same shapes batched
-            o_full = torch.zeros(g.padded, dtype=cdt, device=eng.device) if g.world > 1 else u_full
+            if g.world > 1 and eng.symm is not None:
+                o_full = eng.symm.o_buffer(g)
+                o_full.zero_()
+            else:
+                o_full = torch.zeros(g.padded, dtype=cdt, device=eng.device) if g.world > 1 else u_full
             mine = [mt for mt in mask_mats if mt.owner == g.rank]
             by_shape: Dict[Tuple[int, int], List[_Mat]] = {}
             for mt in mine:

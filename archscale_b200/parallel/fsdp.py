@@ -275,7 +275,7 @@ class FSDPEngine:
     def _unshard(self, unit: Unit, wait: bool = True) -> None:
         if not unit.unsharded:
             for g in unit.groups:
-                lp = g.refresh_lp()
+                lp = self.symm.lp_shard(g) if (self.symm is not None and g.world > 1) else g.refresh_lp()
                 if g.world == 1:
                     if g.full is not lp:
                         g.full = lp
@@ -383,11 +383,23 @@ class FSDPEngine:
         if not self.use_main_grad:
             return
         for g in unit.groups:
-            if g.full_grad is None:
-                g.full_grad = self.pool.get(g.padded, torch.float32, self.device)
-                g.full_grad.zero_()
+            self._ensure_full_grad(g)
             for s in g.specs:
                 s.param.main_grad = g.full_grad[s.offset:s.offset + s.numel].view(s.shape)
+
+    def _ensure_full_grad(self, g: FlatGroup) -> None:
+        """Flat fp32 gradient buffer of the group for this micro-step (zeroed when it starts a new
+        accumulation); with peer-memory collectives it is the group's buffer in the symmetric heap."""
+        if g.full_grad is not None:
+            return
+        if self.symm is not None and g.world > 1:
+            g.full_grad = g.symm_full_grad
+            if not g.symm_fg_dirty:
+                g.full_grad.zero_()
+                g.symm_fg_dirty = True
+        else:
+            g.full_grad = self.pool.get(g.padded, torch.float32, self.device)
+            g.full_grad.zero_()
 
     def _pre_backward(self, unit: Unit) -> None:
         if unit.post_bwd_done:
@@ -420,9 +432,7 @@ class FSDPEngine:
             have = [s for s in g.specs if s.param.grad is not None]
             if not have and g.full_grad is None:
                 continue
-            if g.full_grad is None:
-                g.full_grad = self.pool.get(g.padded, torch.float32, self.device)
-                g.full_grad.zero_()
+            self._ensure_full_grad(g)
             if have:
                 dst = [g.full_grad[s.offset:s.offset + s.numel].view(s.shape) for s in have]
                 src = [s.param.grad for s in have]
@@ -476,7 +486,10 @@ class FSDPEngine:
                     ev = torch.cuda.Event()
                     ev.record(self.rs_stream)
                     self._rs_events.append(ev)
-            self.pool.put(full_grad)
+            if self.symm is not None:
+                g.symm_fg_dirty = False      # consumed; the next micro-step starts from zero
+            else:
+                self.pool.put(full_grad)
 
     # ------------------------------------------------------------------ public API
     def backward(self, loss: torch.Tensor) -> None:
@@ -528,6 +541,13 @@ class FSDPEngine:
             if u.unsharded and self.world == 1:
                 for g in u.groups:
                     g.refresh_lp()
+        if self.symm is not None:
+            # publish the new shards in the symmetric heap, then meet the peers: after this barrier every
+            # rank may pull any shard, and nobody still reads last step's gradient / Muon buffers
+            for g in self.groups():
+                if g.world > 1:
+                    self.symm.lp_shard(g)
+            self.symm.step_barrier()
 
     @torch.no_grad()
     def clip_grad_norm_(self, max_norm: float, eps: float = 1e-6) -> torch.Tensor:
