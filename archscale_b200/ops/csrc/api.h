@@ -52,6 +52,10 @@ int b200_qknorm_rope_bwd(const void* dqo, const void* dko, const void* q, const 
 int b200_qknorm_rope_grid();
 
 // ---- peer-memory collectives (comm.cu).  `bases[p]` = local mapping of rank p's symmetric heap.
+// Forward GEMM with the FSDP all-gather of the whole flat parameter group fused in (gemm_bf16.cu).
+int b200_ag_gemm_bf16(const void* A, void* out, int M, int N, int K, int lda, int ldc, const void* const* bases,
+                      size_t src_off, void* dst, size_t shard_bytes, size_t b_off, uint32_t* flags, uint32_t epoch,
+                      int rank, int world, int n_copy, int num_sms, int* status, cudaStream_t stream);
 void b200_set_peer_wait_limit_cycles(long long cycles);
 int b200_symm_barrier(const void* const* bases, size_t signal_off, int channel, int rank, int world, uint32_t epoch,
                       int* status, cudaStream_t stream);

@@ -72,58 +72,101 @@ __global__ void symm_wait_kernel(Peers peers, size_t signal_off, int channel, in
 // dst (local, contiguous [world · shard_bytes]) ← every peer's shard at heap offset src_off.
 __global__ void __launch_bounds__(512) allgather_pull_kernel(Peers peers, size_t src_off, uint4* __restrict__ dst,
                                                             size_t shard_vec /* uint4 per shard */, int rank, int world) {
-  const size_t total = shard_vec * world;
-  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    // start with the next rank so that the ranks do not all hammer the same peer at once
-    const int step = static_cast<int>(i / shard_vec);
+  // 8 independent 16-byte loads in flight per thread: NVLink latency is ~µs, so bandwidth = bytes in flight
+  constexpr int U = 8;
+  const size_t chunk = static_cast<size_t>(blockDim.x) * U;
+  const size_t chunks_per_shard = (shard_vec + chunk - 1) / chunk;
+  const size_t total_chunks = chunks_per_shard * world;
+  for (size_t c = blockIdx.x; c < total_chunks; c += gridDim.x) {
+    // start with the next rank so that the ranks do not all read the same peer at once
+    const int step = static_cast<int>(c / chunks_per_shard);
     const int p = (rank + step) % world;
-    const size_t j = i - static_cast<size_t>(step) * shard_vec;
+    const size_t j0 = (c - static_cast<size_t>(step) * chunks_per_shard) * chunk + threadIdx.x;
     const uint4* src = reinterpret_cast<const uint4*>(static_cast<const char*>(peers.base[p]) + src_off);
-    dst[static_cast<size_t>(p) * shard_vec + j] = src[j];
+    uint4* d = dst + static_cast<size_t>(p) * shard_vec;
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) { const size_t j = j0 + static_cast<size_t>(u) * blockDim.x; if (j < shard_vec) v[u] = src[j]; }
+#pragma unroll
+    for (int u = 0; u < U; ++u) { const size_t j = j0 + static_cast<size_t>(u) * blockDim.x; if (j < shard_vec) d[j] = v[u]; }
   }
 }
 
 // out[i] = (accumulate ? out[i] : 0) + scale · Σ_p full_p[rank·S + i]; full_p at heap offset full_off, fp32.
-__global__ void __launch_bounds__(512) reduce_scatter_pull_kernel(Peers peers, size_t full_off, float4* __restrict__ out,
+__global__ void __launch_bounds__(256) reduce_scatter_pull_kernel(Peers peers, size_t full_off, float4* __restrict__ out,
                                                                  size_t shard_vec /* float4 per shard */, int rank,
                                                                  int world, float scale, int accumulate) {
-  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < shard_vec;
-       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 1
-    for (int p = 0; p < world; ++p) {   // fixed order → bitwise reproducible
-      const float4* src = reinterpret_cast<const float4*>(static_cast<const char*>(peers.base[p]) + full_off) +
-                          static_cast<size_t>(rank) * shard_vec;
-      const float4 v = src[i];
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  // The loads from all (≤ 8) peers for U vectors are issued before any of them is consumed: with a
+  // round trip of several µs over NVLink, throughput is the number of bytes in flight.
+  constexpr int U = 2;
+  const float4* src[8];
+#pragma unroll
+  for (int p = 0; p < 8; ++p)
+    src[p] = reinterpret_cast<const float4*>(static_cast<const char*>(peers.base[p < world ? p : 0]) + full_off) +
+             static_cast<size_t>(rank) * shard_vec;
+  const size_t chunk = static_cast<size_t>(blockDim.x) * U;
+  for (size_t c0 = blockIdx.x * chunk; c0 < shard_vec; c0 += static_cast<size_t>(gridDim.x) * chunk) {
+    float4 v[8][U];
+#pragma unroll
+    for (int p = 0; p < 8; ++p)
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const size_t i = c0 + threadIdx.x + static_cast<size_t>(u) * blockDim.x;
+        v[p][u] = (p < world && i < shard_vec) ? src[p][i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t i = c0 + threadIdx.x + static_cast<size_t>(u) * blockDim.x;
+      if (i >= shard_vec) continue;
+      float4 a = v[0][u];
+#pragma unroll
+      for (int p = 1; p < 8; ++p) {   // fixed rank order → bitwise reproducible
+        a.x += v[p][u].x; a.y += v[p][u].y; a.z += v[p][u].z; a.w += v[p][u].w;
+      }
+      a.x *= scale; a.y *= scale; a.z *= scale; a.w *= scale;
+      if (accumulate) { const float4 o = out[i]; a.x += o.x; a.y += o.y; a.z += o.z; a.w += o.w; }
+      out[i] = a;
     }
-    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
-    if (accumulate) { const float4 o = out[i]; acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w; }
-    out[i] = acc;
   }
 }
 
 // Same as reduce_scatter_pull for a 16-bit payload summed in fp32 (Muon: O returns to the shards; every
 // element is non-zero on exactly one rank, so the sum is exact).
-__global__ void __launch_bounds__(512) reduce_scatter_pull_bf16_kernel(Peers peers, size_t full_off, uint4* __restrict__ out,
+__global__ void __launch_bounds__(256) reduce_scatter_pull_bf16_kernel(Peers peers, size_t full_off, uint4* __restrict__ out,
                                                                       size_t shard_vec /* uint4 (8 bf16) per shard */,
                                                                       int rank, int world) {
-  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < shard_vec;
-       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll 1
-    for (int p = 0; p < world; ++p) {
-      const uint4 v = (reinterpret_cast<const uint4*>(static_cast<const char*>(peers.base[p]) + full_off) +
-                       static_cast<size_t>(rank) * shard_vec)[i];
-      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  constexpr int U = 2;
+  const uint4* src[8];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) { const float2 f = unpack_bf16x2(w[e]); acc[2 * e] += f.x; acc[2 * e + 1] += f.y; }
+  for (int p = 0; p < 8; ++p)
+    src[p] = reinterpret_cast<const uint4*>(static_cast<const char*>(peers.base[p < world ? p : 0]) + full_off) +
+             static_cast<size_t>(rank) * shard_vec;
+  const size_t chunk = static_cast<size_t>(blockDim.x) * U;
+  for (size_t c0 = blockIdx.x * chunk; c0 < shard_vec; c0 += static_cast<size_t>(gridDim.x) * chunk) {
+    uint4 v[8][U];
+#pragma unroll
+    for (int p = 0; p < 8; ++p)
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const size_t i = c0 + threadIdx.x + static_cast<size_t>(u) * blockDim.x;
+        v[p][u] = (p < world && i < shard_vec) ? src[p][i] : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t i = c0 + threadIdx.x + static_cast<size_t>(u) * blockDim.x;
+      if (i >= shard_vec) continue;
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+      for (int p = 0; p < 8; ++p) {
+        const uint32_t w[4] = {v[p][u].x, v[p][u].y, v[p][u].z, v[p][u].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 f = unpack_bf16x2(w[e]); acc[2 * e] += f.x; acc[2 * e + 1] += f.y; }
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+      out[i] = o;
     }
-    uint4 o;
-    o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
-    o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
-    out[i] = o;
   }
 }
 
@@ -178,7 +221,7 @@ extern "C" int b200_reduce_scatter_pull(const void* const* bases, size_t full_of
                                         int world, float scale, int accumulate, int max_ctas, cudaStream_t st) {
   if (world > 8 || shard_elems % 4 || full_off % 16) return -1;
   const size_t sv = shard_elems / 4;
-  reduce_scatter_pull_kernel<<<comm_grid(sv, max_ctas), 512, 0, st>>>(make_peers(bases, world), full_off,
+  reduce_scatter_pull_kernel<<<comm_grid(sv, max_ctas), 256, 0, st>>>(make_peers(bases, world), full_off,
                                                                       reinterpret_cast<float4*>(out), sv, rank, world,
                                                                       scale, accumulate);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
@@ -187,7 +230,7 @@ extern "C" int b200_reduce_scatter_pull_bf16(const void* const* bases, size_t fu
                                              int rank, int world, int max_ctas, cudaStream_t st) {
   if (world > 8 || shard_elems % 8 || full_off % 16) return -1;
   const size_t sv = shard_elems / 8;
-  reduce_scatter_pull_bf16_kernel<<<comm_grid(sv, max_ctas), 512, 0, st>>>(make_peers(bases, world), full_off,
+  reduce_scatter_pull_bf16_kernel<<<comm_grid(sv, max_ctas), 256, 0, st>>>(make_peers(bases, world), full_off,
                                                                            static_cast<uint4*>(out), sv, rank, world);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

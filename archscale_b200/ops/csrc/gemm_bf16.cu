@@ -27,6 +27,23 @@ constexpr int GEMM_SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ 
 constexpr int GROUP_M = 16;
 constexpr int NUM_THREADS = 192;
 
+// All-gather fused into the GEMM (FSDP forward): the first `n_copy` CTAs do not compute; they pull every
+// rank's low-precision shard (symmetric heap, NVLink loads) into the local gathered buffer `dst`, chunk by
+// chunk in address order, and publish a flag per chunk.  The producer warp of a computing CTA waits
+// (bounded) for the chunks that hold the rows of B it is about to load, so math on the first rows of
+// the weight overlaps the transfer of the rest of the unit's parameters.
+struct AgParams {
+  const void* peer[8];     // heap bases as mapped in this process
+  size_t src_off;          // offset of the low-precision shard in every heap
+  char* dst;               // local gathered buffer (world · shard_bytes)
+  size_t shard_bytes;
+  size_t b_off;            // byte offset of B inside dst
+  uint32_t* flags;         // one per chunk of dst, value = epoch when the chunk is complete
+  uint32_t epoch;
+  int rank, world, n_copy;
+};
+constexpr size_t AG_CHUNK = 256 * 1024;
+
 struct GemmParams {
   void* out;
   const void* cin;
@@ -37,10 +54,74 @@ struct GemmParams {
   int* status;
 };
 
-template <int A_MN, int B_MN, int OUT_F32>
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ void ag_copier(const AgParams& ag) {
+  const size_t total = ag.shard_bytes * ag.world;
+  const size_t n_chunks = (total + AG_CHUNK - 1) / AG_CHUNK;
+  constexpr int U = 8;
+  for (size_t c = blockIdx.x; c < n_chunks; c += ag.n_copy) {
+    const size_t beg = c * AG_CHUNK, end = beg + AG_CHUNK < total ? beg + AG_CHUNK : total;
+    // a chunk may straddle two shards; walk it in 16-byte vectors and resolve the owner per vector
+    const size_t v0 = beg / 16, v1 = end / 16;
+    for (size_t v = v0 + threadIdx.x; v < v1; v += static_cast<size_t>(blockDim.x) * U) {
+      uint4 r[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const size_t vv = v + static_cast<size_t>(u) * blockDim.x;
+        if (vv < v1) {
+          const size_t byte = vv * 16;
+          const int owner = static_cast<int>(byte / ag.shard_bytes);
+          const size_t within = byte - static_cast<size_t>(owner) * ag.shard_bytes;
+          r[u] = *reinterpret_cast<const uint4*>(static_cast<const char*>(ag.peer[owner]) + ag.src_off + within);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const size_t vv = v + static_cast<size_t>(u) * blockDim.x;
+        if (vv < v1) *reinterpret_cast<uint4*>(ag.dst + vv * 16) = r[u];
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) { __threadfence(); st_release_gpu(ag.flags + c, ag.epoch); }
+  }
+}
+
+// Wait until dst bytes [lo, hi) are complete.  Returns false on timeout.
+__device__ __forceinline__ bool ag_wait(const AgParams& ag, size_t lo, size_t hi, volatile int* abort_flag, int* status) {
+  for (size_t c = lo / AG_CHUNK; c * AG_CHUNK < hi; ++c) {
+    long long t0 = clock64();
+    while (ld_acquire_gpu(ag.flags + c) != ag.epoch) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitLimitCycles * 8) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, STATUS_TIMEOUT_PEER);
+        return false;
+      }
+      __nanosleep(100);
+    }
+  }
+  asm volatile("fence.proxy.async;" ::: "memory");   // chunk was written through the generic proxy, TMA reads it
+  return true;
+}
+
+template <int A_MN, int B_MN, int OUT_F32, int FUSED_AG = 0>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const GemmParams p) {
+                 const GemmParams p, const AgParams ag) {
+  if (FUSED_AG && static_cast<int>(blockIdx.x) < ag.n_copy) {   // copier CTAs: lowest indices, scheduled first
+    ag_copier(ag);
+    return;
+  }
+  const int cta = FUSED_AG ? static_cast<int>(blockIdx.x) - ag.n_copy : static_cast<int>(blockIdx.x);
+  const int n_cta = FUSED_AG ? static_cast<int>(gridDim.x) - ag.n_copy : static_cast<int>(gridDim.x);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -83,9 +164,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if (warp == 0) {
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
-      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      for (int t = cta; t < num_tiles; t += n_cta) {
         int mi, ni; tile_coords(t, mi, ni);
         const int m0 = mi * BM, n0 = ni * BN;
+        if (FUSED_AG) {
+          const size_t row_bytes = static_cast<size_t>(p.K) * 2;
+          const int n_hi = n0 + BN < p.N ? n0 + BN : p.N;
+          if (!ag_wait(ag, ag.b_off + n0 * row_bytes, ag.b_off + n_hi * row_bytes, abort_flag, p.status)) goto done;
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) goto done;
           uint8_t* sa = smem + stage * STAGE_BYTES;
@@ -115,7 +201,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       constexpr uint32_t b_kstep = B_MN ? (16 * 128) >> 4 : 32 >> 4;
       int stage = 0; uint32_t phase = 0;
       int it = 0;
-      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+      for (int t = cta; t < num_tiles; t += n_cta, ++it) {
         const int acc = it & 1; const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) goto done;
         tc_fence_after();
@@ -141,7 +227,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else {
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     int it = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+    for (int t = cta; t < num_tiles; t += n_cta, ++it) {
       int mi, ni; tile_coords(t, mi, ni);
       const int acc = it & 1; const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
@@ -257,7 +343,8 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const Ge
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
-  kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb, p);
+  AgParams none{};
+  kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb, p, none);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -291,4 +378,43 @@ extern "C" int b200_gemm_bf16(int mode, const void* A, const void* B, void* out,
   if (mode == 1) return out_f32 ? launch_variant<0, 1, 1>(ta, tb, p, num_sms, stream) : launch_variant<0, 1, 0>(ta, tb, p, num_sms, stream);
   if (mode == 2) return out_f32 ? launch_variant<1, 1, 1>(ta, tb, p, num_sms, stream) : launch_variant<1, 1, 0>(ta, tb, p, num_sms, stream);
   return -4;
+}
+
+// out[M,N] (bf16) = A[M,K] · Bᵀ where B[N,K] sits at byte offset b_off of the gathered buffer `dst` that this
+// same launch fills from all ranks' shards (see AgParams).  `flags` needs one uint32 per 256 KiB of dst
+// and must never hold `epoch` from an earlier launch (use a fresh epoch per call).
+extern "C" int b200_ag_gemm_bf16(const void* A, void* out, int M, int N, int K, int lda, int ldc,
+                                 const void* const* bases, size_t src_off, void* dst, size_t shard_bytes, size_t b_off,
+                                 uint32_t* flags, uint32_t epoch, int rank, int world, int n_copy, int num_sms,
+                                 int* status, cudaStream_t stream) {
+  using namespace b200;
+  if (M <= 0 || N <= 0 || K <= 0 || world > 8 || (shard_bytes % 16) || (b_off % 16)) return -1;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return -5;
+    ctx_bound = true;
+  }
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d_bf16(&ta, A, K, M, lda, BK, BM);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tb, static_cast<const char*>(dst) + b_off, K, N, K, BK, BN);
+  if (rc) return rc;
+  GemmParams p{out, nullptr, M, N, K, ldc, 1.f, 0.f, 0, status};
+  AgParams ag{};
+  for (int i = 0; i < 8; ++i) ag.peer[i] = i < world ? bases[i] : nullptr;
+  ag.src_off = src_off; ag.dst = static_cast<char*>(dst); ag.shard_bytes = shard_bytes; ag.b_off = b_off;
+  ag.flags = flags; ag.epoch = epoch; ag.rank = rank; ag.world = world; ag.n_copy = n_copy;
+  auto kern = gemm_bf16_kernel<0, 0, 0, 1>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess) return -2;
+    configured = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int compute = num_sms - n_copy;
+  if (compute > tiles) compute = tiles;
+  if (compute < 1) return -6;
+  kern<<<compute + n_copy, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, ag);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

@@ -86,7 +86,18 @@ class _LinearFn(torch.autograd.Function):
         ctx.has_bias = bias is not None
         ctx.weight_ref = weight            # to find ``main_grad`` (fp32 flat-buffer view) in backward
         x2 = x.reshape(-1, x.shape[-1])
-        y = matmul_nt(x2, weight)
+        g = getattr(weight, "_fsdp_group", None)
+        if g is not None and getattr(g, "ag_pending", False):
+            eng = weight._fsdp_engine
+            if weight._fsdp_first and _cuda_ok(x2, weight, x2.shape[0], weight.shape[0], x2.shape[1]):
+                # FSDP forward: this GEMM also gathers the unit's matrix parameters from all ranks
+                g.ag_pending = False
+                y = eng.symm.ag_gemm(x2, g, weight.shape[0])
+            else:
+                eng.finish_pending_gather(g)
+                y = matmul_nt(x2, weight)
+        else:
+            y = matmul_nt(x2, weight)
         if bias is not None:
             y = y + bias.to(y.dtype)
         return y.view(*x.shape[:-1], weight.shape[0])
@@ -121,6 +132,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         if not x.is_contiguous():
             x = x.contiguous()
         return _LinearFn.apply(x, weight, bias)
+    g = getattr(weight, "_fsdp_group", None)
+    if g is not None and getattr(g, "ag_pending", False):
+        weight._fsdp_engine.finish_pending_gather(g)
     if weight.dtype != x.dtype:
         weight = weight.to(x.dtype)
         bias = bias.to(x.dtype) if bias is not None else None

@@ -194,6 +194,7 @@ class FSDPEngine:
         self.comm_stream = torch.cuda.Stream(self.device) if self.is_cuda else None
         self.rs_stream = torch.cuda.Stream(self.device) if self.is_cuda else None
         self.fused_comm = fused_comm and self.world > 1 and self.is_cuda
+        self.fused_ag = self.fused_comm
         self.symm = None
         self.in_backward = False
         self.use_main_grad = self.is_cuda and param_dtype == torch.bfloat16
@@ -208,6 +209,16 @@ class FSDPEngine:
         if self.fused_comm:
             from . import symm
             self.symm = symm.SymmetricContext(self)
+            for u in self.units:
+                for g in u.groups:
+                    first = g.specs[0] if g.specs else None
+                    g.ag_pending = False
+                    g.first_linear_ok = bool(first is not None and first.offset == 0 and len(first.shape) == 2
+                                             and g.world > 1 and not u.is_root)
+                    for sp in g.specs:
+                        sp.param._fsdp_group = g
+                        sp.param._fsdp_engine = self
+                        sp.param._fsdp_first = sp is first
 
     # ------------------------------------------------------------------ construction
     def _build_units(self, unit_classes: Sequence[type]) -> None:
@@ -225,9 +236,11 @@ class FSDPEngine:
             for n, p in pnames:
                 local = bool(getattr(p, "_ep_local", False) or getattr(p, "_no_shard", False))
                 dt = torch.float32 if (_keep_fp32(n) or self.param_dtype == torch.float32) else self.param_dtype
-                buckets.setdefault((dt, local), []).append((n, p))
+                # matrices (GEMM weights, Muon-managed) and vectors travel in separate flat groups: the matrix
+                # group can then be gathered by the unit's first GEMM itself, after the norm weights are in place
+                buckets.setdefault((dt, local, is_matrix_param(n, p.dim())), []).append((n, p))
             groups = []
-            for (dt, local), items in buckets.items():
+            for (dt, local, _is_mat), items in sorted(buckets.items(), key=lambda kv: (not kv[0][2], str(kv[0][0]), kv[0][1])):
                 specs, off = [], 0
                 # matrices first: the Muon-managed part of every flat group is one contiguous prefix
                 items = sorted(items, key=lambda it: 0 if is_matrix_param(it[0], it[1].dim()) else 1)
@@ -281,6 +294,16 @@ class FSDPEngine:
                         g.full = lp
                         g.set_param_views(lp)
                     g.gather_event = None
+                elif self.is_cuda and self._defer_to_first_gemm(unit, g, wait):
+                    # fused path: the unit's first GEMM pulls the shards itself (ops.linear → symm.ag_gemm)
+                    self.comm_stream.wait_stream(torch.cuda.current_stream())
+                    with torch.cuda.stream(self.comm_stream):
+                        g.alloc_full()
+                        ev = torch.cuda.Event()
+                        ev.record(self.comm_stream)
+                    torch.cuda.current_stream().wait_event(ev)
+                    g.ag_pending = True
+                    g.gather_event = None
                 elif self.is_cuda:
                     self.comm_stream.wait_stream(torch.cuda.current_stream())
                     with torch.cuda.stream(self.comm_stream):
@@ -298,6 +321,19 @@ class FSDPEngine:
                     torch.cuda.current_stream().wait_event(g.gather_event)
                     g.gather_event = None
 
+    def _defer_to_first_gemm(self, unit: Unit, g: FlatGroup, wait: bool) -> bool:
+        """Forward of a non-root unit with peer-memory collectives: leave the matrix group to the fused
+        all-gather→GEMM of the unit's first ``Linear``."""
+        return (self.symm is not None and self.fused_ag and wait and not self.in_backward and not unit.is_root
+                and g.dtype == torch.bfloat16 and getattr(g, "matrix_numel", 0) == g.numel and g.numel > 0
+                and getattr(g, "first_linear_ok", False))
+
+    def finish_pending_gather(self, g: FlatGroup) -> None:
+        """Plain pull of a group whose gather was left to a GEMM that did not come first."""
+        if getattr(g, "ag_pending", False):
+            self._all_gather(g, g.shard_lp)
+            g.ag_pending = False
+
     def _all_gather(self, g: FlatGroup, lp: torch.Tensor) -> None:
         if self.symm is not None:
             self.symm.all_gather(g, lp)
@@ -308,6 +344,7 @@ class FSDPEngine:
         if not unit.unsharded:
             return
         for g in unit.groups:
+            g.ag_pending = False
             if g.world > 1 and g.full is not None:
                 if self.is_cuda:
                     # free on the communication stream, after the compute stream is done with the values
@@ -336,7 +373,8 @@ class FSDPEngine:
         if not self._order_frozen and not self.in_backward:
             self._fwd_order.append(unit)
         self._unshard(unit)
-        if not self.in_backward:
+        if not self.in_backward and not (self.symm is not None and self.fused_ag):
+            # (with the fused all-gather→GEMM the next unit's first GEMM fetches its own parameters)
             nxt = self._neighbor(unit, +1)
             if nxt is not None:
                 self._unshard(nxt, wait=False)

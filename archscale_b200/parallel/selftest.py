@@ -66,7 +66,7 @@ def main() -> None:
     ref_rs /= world
     err = float((out - ref_rs).abs().max())
     assert err < 1e-5, f"pull reduce-scatter error {err}"
-    for ctas in (16, 32, 64):
+    for ctas in (16, 32, 48, 64, 128):
         t_ag = _time(lambda: ext.allgather_pull(heap.bases, off_lp, full, S * 2, rank, ctas))
         t_rs = _time(lambda: ext.reduce_scatter_pull(heap.bases, off_fg, out, rank, 1.0 / world, False, ctas))
         if rank == 0:
@@ -77,6 +77,48 @@ def main() -> None:
     if rank == 0:
         print(f"NCCL: all-gather {S * 2 * (world - 1) / t_ag / 1e6:.0f} GB/s ({t_ag:.3f} ms); reduce-scatter "
               f"{S * 4 * (world - 1) / t_rs / 1e6:.0f} GB/s ({t_rs:.3f} ms)", flush=True)
+
+    # ---- all-gather fused into the consuming GEMM
+    N, K, M = 2048, 2048, 32768
+    shard_elems = 6 * 1024 * 1024                       # per-rank shard of a "unit" (bf16)
+    off_w = heap.alloc(shard_elems * 2)
+    wshard = heap.tensor(off_w, (shard_elems,), torch.bfloat16)
+    wshard.copy_(torch.randn(shard_elems, device=dev) * 0.02)
+    torch.cuda.synchronize()
+    heap.barrier(0)
+    gathered = torch.zeros(shard_elems * world, dtype=torch.bfloat16, device=dev)
+    flags = torch.zeros((shard_elems * world * 2 + 262143) // 262144, dtype=torch.int32, device=dev)
+    x = (torch.randn(M, K, device=dev) * 0.1).bfloat16()
+    y = ext.ag_gemm(x, heap.bases, off_w, gathered, shard_elems * 2, 0, N, flags, 1, rank, 16)
+    ref_full = torch.empty_like(gathered)
+    dist.all_gather_into_tensor(ref_full, wshard)
+    assert torch.equal(gathered, ref_full), "fused gather produced a different buffer"
+    y_ref = x.float() @ ref_full[: N * K].view(N, K).float().t()
+    rel = float((y.float() - y_ref).norm() / y_ref.norm())
+    assert rel < 1e-2, f"ag_gemm result off by {rel}"
+    ep = [1]
+
+    def fused():
+        ep[0] += 1
+        ext.ag_gemm(x, heap.bases, off_w, gathered, shard_elems * 2, 0, N, flags, ep[0], rank, 16)
+
+    def separate():
+        ext.allgather_pull(heap.bases, off_w, gathered, shard_elems * 2, rank, 48)
+        ext.gemm_bf16(x, gathered[: N * K].view(N, K), 0, torch.bfloat16, None)
+
+    def nccl_sep():
+        dist.all_gather_into_tensor(ref_full, wshard)
+        x @ ref_full[: N * K].view(N, K).t()
+
+    t_f, t_s, t_n = _time(fused), _time(separate), _time(nccl_sep)
+    t_g = _time(lambda: ext.gemm_bf16(x, gathered[: N * K].view(N, K), 0, torch.bfloat16, None))
+    if rank == 0:
+        fl = 2.0 * M * N * K
+        nv = shard_elems * 2 * (world - 1)
+        print(f"ag_gemm fused {t_f:.3f} ms | pull-gather then gemm {t_s:.3f} ms | NCCL gather then cuBLAS {t_n:.3f} ms | "
+              f"gemm alone {t_g:.3f} ms; roofline max(flops/peak, bytes/link) = "
+              f"{max(fl / 1.7138e15, nv / 770e9) * 1e3:.3f} ms → fraction {max(fl / 1.7138e15, nv / 770e9) * 1e3 / t_f:.2f}",
+              flush=True)
 
     # ---- training steps: fused vs NCCL
     from archscale_b200 import Config

@@ -76,7 +76,7 @@ class SymmetricHeap:
 class SymmetricContext:
     """Places the engine's shards / gradient buffers in a symmetric heap and serves its collectives."""
 
-    def __init__(self, engine, comm_ctas: int = 32) -> None:
+    def __init__(self, engine, comm_ctas: int = 48) -> None:
         self.engine = engine
         self.comm_ctas = comm_ctas
         groups = [g for g in engine.groups() if g.world > 1]
@@ -127,6 +127,20 @@ class SymmetricContext:
         self.ext.allgather_pull(self.heap.bases, m["lp_off"], g.full, g.shard_numel * g.full.element_size(),
                                 self.heap.rank, self.comm_ctas)
         backend.count_launch()
+
+    def ag_gemm(self, x2: torch.Tensor, g, n_out: int, n_copy: int = 16) -> torch.Tensor:
+        """``x2 @ Wᵀ`` for the first weight ``W (n_out × K)`` of group ``g`` with the all-gather of the whole
+        group fused into the same kernel launch."""
+        m = self.meta[id(g)]
+        if "ag_flags" not in m:
+            n_chunks = (g.padded * g.full.element_size() + 256 * 1024 - 1) // (256 * 1024)
+            m["ag_flags"] = torch.zeros(n_chunks, dtype=torch.int32, device=self.engine.device)
+            m["ag_epoch"] = 0
+        m["ag_epoch"] += 1
+        out = self.ext.ag_gemm(x2, self.heap.bases, m["lp_off"], g.full, g.shard_numel * g.full.element_size(), 0,
+                               n_out, m["ag_flags"], m["ag_epoch"], self.heap.rank, n_copy)
+        backend.count_launch()
+        return out
 
     def reduce_scatter(self, g, out: torch.Tensor, full_grad: torch.Tensor, scale: float) -> None:
         m = self.meta[id(g)]
