@@ -63,35 +63,76 @@ __device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-__device__ void ag_copier(const AgParams& ag) {
+// Copier CTA: one thread drives bulk-asynchronous copies (peer global → shared → local global) through a
+// 3-deep ring of 64 KiB buffers, so ~192 KiB are in flight per CTA; NVLink round trips are several µs and
+// bandwidth is what is in flight.  A chunk's flag is published once the stores of its pieces completed.
+constexpr int AG_PIECE = 64 * 1024, AG_BUFS = 3, AG_PIECES_PER_CHUNK = AG_CHUNK / AG_PIECE;
+
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(reinterpret_cast<uint64_t>(gdst)), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+}
+
+__device__ void ag_copier(const AgParams& ag, uint8_t* smem, int* status) {
+  if (threadIdx.x != 0) return;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AG_BUFS * AG_PIECE);
+  volatile int abort_local = 0;
+  for (int b = 0; b < AG_BUFS; ++b) mbar_init(&bars[b], 1);
+  mbar_fence_init();
   const size_t total = ag.shard_bytes * ag.world;
   const size_t n_chunks = (total + AG_CHUNK - 1) / AG_CHUNK;
-  constexpr int U = 8;
-  for (size_t c = blockIdx.x; c < n_chunks; c += ag.n_copy) {
-    const size_t beg = c * AG_CHUNK, end = beg + AG_CHUNK < total ? beg + AG_CHUNK : total;
-    // a chunk may straddle two shards; walk it in 16-byte vectors and resolve the owner per vector
-    const size_t v0 = beg / 16, v1 = end / 16;
-    for (size_t v = v0 + threadIdx.x; v < v1; v += static_cast<size_t>(blockDim.x) * U) {
-      uint4 r[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const size_t vv = v + static_cast<size_t>(u) * blockDim.x;
-        if (vv < v1) {
-          const size_t byte = vv * 16;
-          const int owner = static_cast<int>(byte / ag.shard_bytes);
-          const size_t within = byte - static_cast<size_t>(owner) * ag.shard_bytes;
-          r[u] = *reinterpret_cast<const uint4*>(static_cast<const char*>(ag.peer[owner]) + ag.src_off + within);
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const size_t vv = v + static_cast<size_t>(u) * blockDim.x;
-        if (vv < v1) *reinterpret_cast<uint4*>(ag.dst + vv * 16) = r[u];
-      }
+  const size_t my_chunks = n_chunks > blockIdx.x ? (n_chunks - blockIdx.x + ag.n_copy - 1) / ag.n_copy : 0;
+  const size_t n_pieces = my_chunks * AG_PIECES_PER_CHUNK;
+  auto piece_range = [&](size_t i, size_t& beg, size_t& end, size_t& chunk) {
+    chunk = blockIdx.x + (i / AG_PIECES_PER_CHUNK) * ag.n_copy;
+    beg = chunk * AG_CHUNK + (i % AG_PIECES_PER_CHUNK) * AG_PIECE;
+    end = beg + AG_PIECE;
+    if (beg > total) beg = total;
+    if (end > total) end = total;
+  };
+  auto issue_load = [&](size_t i) {
+    size_t beg, end, chunk; piece_range(i, beg, end, chunk);
+    const int buf = static_cast<int>(i % AG_BUFS);
+    if (end <= beg) { mbar_arrive(&bars[buf]); return; }
+    mbar_arrive_expect_tx(&bars[buf], static_cast<uint32_t>(end - beg));
+    size_t pos = beg;
+    while (pos < end) {   // a piece may straddle a shard boundary: one bulk copy per owner
+      const int owner = static_cast<int>(pos / ag.shard_bytes);
+      const size_t within = pos - static_cast<size_t>(owner) * ag.shard_bytes;
+      size_t n = ag.shard_bytes - within;
+      if (n > end - pos) n = end - pos;
+      bulk_g2s(smem + buf * AG_PIECE + (pos - beg), static_cast<const char*>(ag.peer[owner]) + ag.src_off + within,
+               static_cast<uint32_t>(n), &bars[buf]);
+      pos += n;
     }
-    __syncthreads();
-    if (threadIdx.x == 0) { __threadfence(); st_release_gpu(ag.flags + c, ag.epoch); }
+  };
+  auto publish = [&](size_t chunk) {
+    asm volatile("fence.proxy.async;" ::: "memory");
+    __threadfence();
+    st_release_gpu(ag.flags + chunk, ag.epoch);
+  };
+  for (size_t i = 0; i < n_pieces && i < AG_BUFS; ++i) issue_load(i);
+  for (size_t i = 0; i < n_pieces; ++i) {
+    const int buf = static_cast<int>(i % AG_BUFS);
+    if (!mbar_wait(&bars[buf], static_cast<uint32_t>((i / AG_BUFS) & 1), &abort_local, status, STATUS_TIMEOUT_PEER)) break;
+    size_t beg, end, chunk; piece_range(i, beg, end, chunk);
+    if (end > beg) bulk_s2g(ag.dst + beg, smem + buf * AG_PIECE, static_cast<uint32_t>(end - beg));
+    tma_store_commit();
+    if (i + AG_BUFS < n_pieces) {
+      // buffer `buf` is refilled by piece i+3: its store must have finished reading shared memory
+      tma_store_wait_read<0>();
+      issue_load(i + AG_BUFS);
+    }
+    if (i % AG_PIECES_PER_CHUNK == AG_PIECES_PER_CHUNK - 1) {
+      tma_store_wait<0>();       // all stores of this chunk have completed
+      publish(chunk);
+    }
   }
+  tma_store_wait<0>();
 }
 
 // Wait until dst bytes [lo, hi) are complete.  Returns false on timeout.
@@ -117,7 +158,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmParams p, const AgParams ag) {
   if (FUSED_AG && static_cast<int>(blockIdx.x) < ag.n_copy) {   // copier CTAs: lowest indices, scheduled first
-    ag_copier(ag);
+    extern __shared__ uint8_t smem_copier[];
+    ag_copier(ag, reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_copier) + 1023) & ~uintptr_t(1023)), p.status);
     return;
   }
   const int cta = FUSED_AG ? static_cast<int>(blockIdx.x) - ag.n_copy : static_cast<int>(blockIdx.x);

@@ -45,7 +45,7 @@ def main() -> None:
 
     # ---- raw collectives
     S = 32 * 1024 * 1024                        # elements per shard
-    heap = SymmetricHeap(dist.group.WORLD, S * 2 + S * world * 4 + 4096, dev)
+    heap = SymmetricHeap(dist.group.WORLD, S * 2 + S * world * 4 + (64 << 20), dev)
     off_lp = heap.alloc(S * 2)
     lp = heap.tensor(off_lp, (S,), torch.bfloat16)
     lp.copy_(torch.randn(S, device=dev))
@@ -66,7 +66,7 @@ def main() -> None:
     ref_rs /= world
     err = float((out - ref_rs).abs().max())
     assert err < 1e-5, f"pull reduce-scatter error {err}"
-    for ctas in (16, 32, 48, 64, 128):
+    for ctas in (32, 64, 128, 296):
         t_ag = _time(lambda: ext.allgather_pull(heap.bases, off_lp, full, S * 2, rank, ctas))
         t_rs = _time(lambda: ext.reduce_scatter_pull(heap.bases, off_fg, out, rank, 1.0 / world, False, ctas))
         if rank == 0:

@@ -76,9 +76,10 @@ class SymmetricHeap:
 class SymmetricContext:
     """Places the engine's shards / gradient buffers in a symmetric heap and serves its collectives."""
 
-    def __init__(self, engine, comm_ctas: int = 48) -> None:
+    def __init__(self, engine, comm_ctas: int = 64, reduce_ctas: int = 296) -> None:
         self.engine = engine
         self.comm_ctas = comm_ctas
+        self.reduce_ctas = reduce_ctas      # latency-bound pulls: co-resident with the GEMM CTAs, light on ALUs
         groups = [g for g in engine.groups() if g.world > 1]
         esize = lambda dt: torch.empty((), dtype=dt).element_size()
         need = 0
@@ -147,7 +148,7 @@ class SymmetricContext:
         assert full_grad.data_ptr() == g.symm_full_grad.data_ptr(), "gradient buffer must live in the symmetric heap"
         e = self.heap.post(m["chan"])
         self.heap.wait(m["chan"], e)
-        self.ext.reduce_scatter_pull(self.heap.bases, m["fg_off"], out, self.heap.rank, scale, False, self.comm_ctas)
+        self.ext.reduce_scatter_pull(self.heap.bases, m["fg_off"], out, self.heap.rank, scale, False, self.reduce_ctas)
         backend.count_launch(3)
 
     # ------------------------------------------------------------------ Muon transport
@@ -173,6 +174,6 @@ class SymmetricContext:
         e = self.heap.post(m["chan"] + 2)
         self.heap.wait(m["chan"] + 2, e)
         out = torch.empty(g.shard_numel, dtype=torch.bfloat16, device=self.engine.device)
-        self.ext.reduce_scatter_pull(self.heap.bases, m["o_off"], out, self.heap.rank, 1.0, False, self.comm_ctas)
+        self.ext.reduce_scatter_pull(self.heap.bases, m["o_off"], out, self.heap.rank, 1.0, False, self.reduce_ctas)
         backend.count_launch(3)
         return out
