@@ -58,6 +58,13 @@ def attention_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Opti
     return (o, lse) if return_lse else o
 
 
+def row_start_from_cu_seqlens(cu_seqlens: torch.Tensor, total: int) -> torch.Tensor:
+    """int32 (total,) first token of the document each position belongs to (device op, no host sync)."""
+    pos = torch.arange(total, device=cu_seqlens.device)
+    seg = torch.bucketize(pos, cu_seqlens[1:].to(pos.dtype), right=True)
+    return cu_seqlens.to(torch.int32)[seg.clamp_max(cu_seqlens.numel() - 2)].contiguous()
+
+
 def _sdpa_fallback(q, k, v, scale, window, cu_seqlens):
     """Library path used only when the extension is explicitly disabled on a GPU."""
     B, Tq, H, D = q.shape
@@ -74,14 +81,27 @@ def _sdpa_fallback(q, k, v, scale, window, cu_seqlens):
     return o.transpose(1, 2)
 
 
+def doc_end_from_cu_seqlens(cu_seqlens: torch.Tensor, total: int) -> torch.Tensor:
+    """int32 (total,) exclusive end of the document each position belongs to."""
+    pos = torch.arange(total, device=cu_seqlens.device)
+    seg = torch.bucketize(pos, cu_seqlens[1:].to(pos.dtype), right=True)
+    return cu_seqlens.to(torch.int32)[(seg + 1).clamp_max(cu_seqlens.numel() - 1)].contiguous()
+
+
 class _AttnFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, scale, window_left, cu_seqlens):
         ext = backend.require_extension()
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-        out, lse = ext.attn_fwd(q, k, v, scale, window_left, cu_seqlens)
+        row_start = doc_end = None
+        if cu_seqlens is not None:
+            T = q.shape[1]
+            row_start, doc_end = row_start_from_cu_seqlens(cu_seqlens, T), doc_end_from_cu_seqlens(cu_seqlens, T)
+        out, lse = ext.attn_fwd(q, k, v, scale, window_left, row_start)
         backend.count_launch()
-        ctx.save_for_backward(q, k, v, out, lse, cu_seqlens if cu_seqlens is not None else torch.empty(0))
+        none = torch.empty(0)
+        ctx.save_for_backward(q, k, v, out, lse, row_start if row_start is not None else none,
+                              doc_end if doc_end is not None else none)
         ctx.scale, ctx.window_left, ctx.varlen = scale, window_left, cu_seqlens is not None
         ctx.mark_non_differentiable(lse)
         return out, lse
@@ -89,16 +109,16 @@ class _AttnFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout, _dlse):
         ext = backend.require_extension()
-        q, k, v, out, lse, cu = ctx.saved_tensors
+        q, k, v, out, lse, row_start, doc_end = ctx.saved_tensors
         dq, dk, dv = ext.attn_bwd(dout.contiguous(), q, k, v, out, lse, ctx.scale, ctx.window_left,
-                                  cu if ctx.varlen else None)
+                                  row_start if ctx.varlen else None, doc_end if ctx.varlen else None)
         backend.count_launch(3)
         return dq, dk, dv, None, None, None
 
 
 def cuda_supported(q, k, v, sink) -> bool:
     D = q.shape[-1]
-    return (backend.has("attn_fwd") and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
+    return (backend.has("attn_fwd") and backend.has("attn_bwd") and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
             and v.dtype == torch.bfloat16 and D in (64, 128) and v.shape[-1] == D and sink is None and q.shape[1] == k.shape[1]
             and q.shape[2] % k.shape[2] == 0)
 

@@ -51,6 +51,17 @@ int b200_qknorm_rope_bwd(const void* dqo, const void* dko, const void* q, const 
                          int64_t n_tokens, int T, int H, int G, int D, cudaStream_t stream);
 int b200_qknorm_rope_grid();
 
+// Attention forward (attention_fwd.cu).  q:[B,T,H,D] k,v:[B,T,G,D] bf16 → out bf16, lse fp32 [B,H,T].
+// row_start: optional int32 [B*T], first key each query row may see (packed documents).
+int b200_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* row_start, int B, int T,
+                  int H, int G, int D, int window_left, float scale, int* status, cudaStream_t stream);
+
+// Attention backward (attention_bwd.cu): δ preprocess + dK/dV kernel + dQ kernel, deterministic.
+// delta: fp32 scratch [B,H,T]; doc_end: optional int32 [B*T] (exclusive end of each position's document).
+int b200_attn_bwd(const void* d_out, const void* q, const void* k, const void* v, const void* out, const float* lse,
+                  float* delta, const int* row_start, const int* doc_end, void* dq, void* dk, void* dv, int B, int T,
+                  int H, int G, int D, int window_left, float scale, int* status, cudaStream_t stream);
+
 // ---- peer-memory collectives (comm.cu).  `bases[p]` = local mapping of rank p's symmetric heap.
 // Forward GEMM with the FSDP all-gather of the whole flat parameter group fused in (gemm_bf16.cu).
 int b200_ag_gemm_bf16(const void* A, void* out, int M, int N, int K, int lda, int ldc, const void* const* bases,

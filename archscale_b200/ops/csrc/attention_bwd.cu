@@ -1,0 +1,517 @@
+// Attention backward on tcgen05, deterministic (no atomics).  Three kernels:
+//
+//   attn_bwd_delta   δ[b,h,r] = Σ_d dO·O                               (one warp per row/head)
+//   attn_bwd_dq      CTA per (query tile, head, batch), loop over key tiles:
+//                      S = Q·Kᵀ, dP = dO·Vᵀ  →  dS = P∘(dP − δ)·scale (bf16, in TMEM)  →  dQ += dS·K
+//   attn_bwd_dkdv    CTA per (key tile, kv head, batch), loop over the query heads of the group and
+//                    their query tiles, in the transposed domain so that the lane index is the key row:
+//                      Sᵀ = K·Qᵀ, dPᵀ = V·dOᵀ  →  Pᵀ, dSᵀ (bf16, in TMEM)  →  dV += Pᵀ·dO, dK += dSᵀ·Q
+//                    GQA reduction over the group's query heads happens in the TMEM accumulators.
+//
+// P is recomputed from the saved log-sum-exp.  The bf16 P / dS tiles overwrite the fp32 S / dP tiles
+// in place, 32 columns at a time (16 packed columns land inside the 32 columns just read), which
+// keeps TMEM at 512 columns: S|P 128, dP|dS 128, two 128-column accumulators.
+// Masking rule as in the forward: row r sees keys lo(r) ≤ k ≤ r.
+#include "sm100.cuh"
+#include "api.h"
+
+namespace b200 {
+
+constexpr int BT = 128;                 // tile edge (queries and keys)
+constexpr int BWD_THREADS = 192;
+constexpr float kLog2e_b = 1.4426950408889634f;
+
+int make_tmap_2d_bf16(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_elems,
+                      uint32_t box_inner, uint32_t box_outer);
+
+struct AttnBwdParams {
+  const float* lse;        // [B,H,T] natural log
+  const float* delta;      // [B,H,T]
+  const int* row_start;    // [B*T] or null
+  const int* doc_end;      // [B*T] exclusive end of the document of each position, or null
+  __nv_bfloat16* dq;       // [B,T,H,D]
+  __nv_bfloat16* dk;       // [B,T,G,D]
+  __nv_bfloat16* dv;
+  int B, T, H, G;
+  int window_left;
+  float scale, scale_log2;
+  int* status;
+};
+
+__device__ __forceinline__ int lo_of_row(const AttnBwdParams& p, int b, int r) {
+  int lo = p.row_start ? p.row_start[static_cast<size_t>(b) * p.T + r] : 0;
+  if (p.window_left >= 0) lo = max(lo, r - p.window_left);
+  return lo;
+}
+
+// ------------------------------------------------------------------------------------------- δ
+template <int D>
+__global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                                             float* __restrict__ delta, int B, int T, int H) {
+  const int lane = threadIdx.x & 31;
+  const size_t row = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;   // over B*T*H
+  if (row >= static_cast<size_t>(B) * T * H) return;
+  constexpr int EPL = D / 32;
+  const __nv_bfloat16* a = o + row * D + lane * EPL;
+  const __nv_bfloat16* c = d_o + row * D + lane * EPL;
+  float s = 0.f;
+#pragma unroll
+  for (int e = 0; e < EPL; e += 2) {
+    const float2 x = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(a + e));
+    const float2 y = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(c + e));
+    s += x.x * y.x + x.y * y.y;
+  }
+#pragma unroll
+  for (int ofs = 16; ofs > 0; ofs >>= 1) s += __shfl_xor_sync(0xffffffffu, s, ofs);
+  if (lane == 0) {
+    const size_t bt = row / H; const int h = static_cast<int>(row % H);
+    const size_t b = bt / T; const int t = static_cast<int>(bt % T);
+    delta[(b * H + h) * T + t] = s;
+  }
+}
+
+template <int D>
+struct BwdSmem {
+  static constexpr int TILE = BT * D * 2;                       // one [128 × D] bf16 tile
+  static constexpr int FIXED = 2 * TILE;                        // the two tiles loaded once
+  static constexpr int RING = 2 * 2 * TILE;                     // 2 stages × 2 tiles
+  static constexpr int AUX = 2 * 3 * BT * 4;                    // per stage: lse·log2e, δ, lo (dkdv only)
+  static constexpr int TOTAL = FIXED + RING + AUX + 1024 + 256;
+};
+
+__device__ __forceinline__ void named_bar_sync_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// ------------------------------------------------------------------------------------------- dQ
+template <int D>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+                   const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                   const AttnBwdParams p) {
+  using SM = BwdSmem<D>;
+  constexpr int DC = D / 64;
+  constexpr int CHUNK_BYTES = 128 * 64 * 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sq = smem;
+  uint8_t* sdo = smem + SM::TILE;
+  uint8_t* ring = smem + SM::FIXED;                 // stage s: K then V
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + SM::RING + SM::AUX);
+  uint64_t* fixed_full = bars;      // 1
+  uint64_t* kv_full = bars + 1;     // [2]
+  uint64_t* kv_empty = bars + 3;    // [2]
+  uint64_t* sdp_full = bars + 5;    // 1   S and dP of the current tile are in TMEM
+  uint64_t* ds_full = bars + 6;     // 1   (count 4) dS written
+  uint64_t* acc_done = bars + 7;    // 1   all dQ MMAs finished
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qt = (p.T + BT - 1) / BT;
+  const int qt = n_qt - 1 - static_cast<int>(blockIdx.x);
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int g = h / (p.H / p.G);
+  const int q0 = qt * BT;
+  const int r_last = min(q0 + BT, p.T) - 1;
+  const int j_begin = lo_of_row(p, b, q0) / BT;
+  const int n_tiles = r_last / BT + 1 - j_begin;
+
+  if (threadIdx.x == 0) {
+    mbar_init(fixed_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(sdp_full, 1); mbar_init(ds_full, 4); mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_ptr, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr;
+  const uint32_t T_S = tmem_base, T_DP = tmem_base + 128, T_DQ = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(fixed_full, 2 * SM::TILE);
+#pragma unroll
+      for (int c = 0; c < DC; ++c) {
+        tma_load_2d(sq + c * CHUNK_BYTES, &tmap_q, fixed_full, h * D + c * 64, b * p.T + q0);
+        tma_load_2d(sdo + c * CHUNK_BYTES, &tmap_do, fixed_full, h * D + c * 64, b * p.T + q0);
+      }
+      for (int t = 0; t < n_tiles; ++t) {
+        const int st = t & 1; const uint32_t ph = (t >> 1) & 1;
+        if (!mbar_wait(&kv_empty[st], ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) goto done;
+        uint8_t* sk = ring + st * 2 * SM::TILE;
+        uint8_t* sv = sk + SM::TILE;
+        const int k0 = (j_begin + t) * BT;
+        mbar_arrive_expect_tx(&kv_full[st], 2 * SM::TILE);
+#pragma unroll
+        for (int c = 0; c < DC; ++c) {
+          tma_load_2d(sk + c * CHUNK_BYTES, &tmap_k, &kv_full[st], g * D + c * 64, b * p.T + k0);
+          tma_load_2d(sv + c * CHUNK_BYTES, &tmap_v, &kv_full[st], g * D + c * 64, b * p.T + k0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(BT, BT, 0, 0);
+      constexpr uint32_t idesc_dq = make_idesc_bf16(BT, D, 0, 1);        // dQ += dS·K, K is N-major
+      if (!mbar_wait(fixed_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL)) goto done;
+      for (int t = 0; t < n_tiles; ++t) {
+        const int st = t & 1; const uint32_t ph = (t >> 1) & 1;
+        if (!mbar_wait(&kv_full[st], ph, abort_flag, p.status, STATUS_TIMEOUT_FULL)) goto done;
+        tc_fence_after();
+        const uint32_t sk = smem_u32(ring + st * 2 * SM::TILE), sv = sk + SM::TILE;
+        const uint32_t sqa = smem_u32(sq), sdoa = smem_u32(sdo);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k / 4) * CHUNK_BYTES + (k % 4) * 32;
+          umma_bf16(T_S, make_smem_desc(sqa + off, 16, 1024), make_smem_desc(sk + off, 16, 1024), idesc_s, k != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k / 4) * CHUNK_BYTES + (k % 4) * 32;
+          umma_bf16(T_DP, make_smem_desc(sdoa + off, 16, 1024), make_smem_desc(sv + off, 16, 1024), idesc_s, k != 0);
+        }
+        umma_commit(sdp_full);
+        if (!mbar_wait(ds_full, t & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < BT / 16; ++k)
+          umma_bf16_ts(T_DQ, T_DP + k * 8, make_smem_desc(sk + k * 2048, CHUNK_BYTES, 1024), idesc_dq, (t | k) != 0);
+        umma_commit(&kv_empty[st]);
+      }
+      umma_commit(acc_done);
+    }
+  } else {
+    const int qtr = warp & 3;
+    const int r = q0 + qtr * 32 + lane;
+    const bool row_valid = r < p.T;
+    const int lo_r = row_valid ? lo_of_row(p, b, r) : 0;
+    const int lo_last = lo_of_row(p, b, r_last);
+    const size_t stat_idx = (static_cast<size_t>(b) * p.H + h) * p.T + (row_valid ? r : 0);
+    const float lse2 = row_valid ? p.lse[stat_idx] * kLog2e_b : 0.f;
+    const float dlt = row_valid ? p.delta[stat_idx] : 0.f;
+    const uint32_t lane_off = static_cast<uint32_t>(qtr * 32) << 16;
+    for (int t = 0; t < n_tiles; ++t) {
+      const int k0 = (j_begin + t) * BT;
+      if (!mbar_wait(sdp_full, t & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
+      tc_fence_after();
+      const bool full_tile = (k0 + BT - 1 <= q0) && (k0 >= lo_last);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sr[32], dr[32];
+        tmem_ld_32x32(T_S + c * 32 + lane_off, sr);
+        tmem_ld_32x32(T_DP + c * 32 + lane_off, dr);
+        tmem_ld_wait();
+        uint32_t w[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          float ds2[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int kk = k0 + c * 32 + 2 * e + u;
+            float pr = exp2f(__uint_as_float(sr[2 * e + u]) * p.scale_log2 - lse2);
+            if (!full_tile && (kk > r || kk < lo_r)) pr = 0.f;
+            if (!row_valid) pr = 0.f;
+            ds2[u] = pr * (__uint_as_float(dr[2 * e + u]) - dlt) * p.scale;
+          }
+          w[e] = pack_bf16x2(ds2[0], ds2[1]);
+        }
+        tmem_st_32x16(T_DP + c * 16 + lane_off, w);      // in place: lands inside the columns just read
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_full);
+    }
+    if (!mbar_wait(acc_done, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
+    tc_fence_after();
+    __nv_bfloat16* orow = p.dq + ((static_cast<size_t>(b) * p.T + r) * p.H + h) * D;
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t rr[32];
+      if (n_tiles > 0) { tmem_ld_32x32(T_DQ + c * 32 + lane_off, rr); tmem_ld_wait(); }
+      else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) rr[e] = 0u;
+      }
+      if (row_valid) {
+#pragma unroll
+        for (int e = 0; e < 32; e += 8) {
+          uint4 o;
+          o.x = pack_bf16x2(__uint_as_float(rr[e]), __uint_as_float(rr[e + 1]));
+          o.y = pack_bf16x2(__uint_as_float(rr[e + 2]), __uint_as_float(rr[e + 3]));
+          o.z = pack_bf16x2(__uint_as_float(rr[e + 4]), __uint_as_float(rr[e + 5]));
+          o.w = pack_bf16x2(__uint_as_float(rr[e + 6]), __uint_as_float(rr[e + 7]));
+          *reinterpret_cast<uint4*>(orow + c * 32 + e) = o;
+        }
+      }
+    }
+  }
+
+done:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------- dK, dV
+template <int D>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+                     const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                     const AttnBwdParams p) {
+  using SM = BwdSmem<D>;
+  constexpr int DC = D / 64;
+  constexpr int CHUNK_BYTES = 128 * 64 * 2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sk = smem;
+  uint8_t* sv = smem + SM::TILE;
+  uint8_t* ring = smem + SM::FIXED;                 // stage s: Q then dO
+  float* aux = reinterpret_cast<float*>(ring + SM::RING);   // stage s: [lse2 | delta | lo] × 128
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + SM::RING + SM::AUX);
+  uint64_t* fixed_full = bars;      // 1
+  uint64_t* qd_full = bars + 1;     // [2]
+  uint64_t* qd_empty = bars + 3;    // [2]
+  uint64_t* sdp_full = bars + 5;    // 1
+  uint64_t* ds_full = bars + 6;     // 1 (count 4)
+  uint64_t* acc_done = bars + 7;    // 1
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int jt = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  const int k0 = jt * BT;
+  const int k_last = min(k0 + BT, p.T) - 1;
+  const int group = p.H / p.G;
+  // query rows that can see a key of this tile: k0 ≤ r ≤ r_hi
+  int r_hi = p.T - 1;
+  if (p.window_left >= 0) r_hi = min(r_hi, k_last + p.window_left);
+  if (p.doc_end) r_hi = min(r_hi, p.doc_end[static_cast<size_t>(b) * p.T + k_last] - 1);
+  const int i_begin = k0 / BT, i_end = r_hi / BT + 1;
+  const int tiles_per_head = i_end - i_begin;
+  const int n_iter = tiles_per_head * group;
+
+  if (threadIdx.x == 0) {
+    mbar_init(fixed_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&qd_full[s], 1); mbar_init(&qd_empty[s], 1); }
+    mbar_init(sdp_full, 1); mbar_init(ds_full, 4); mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_ptr, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr;
+  const uint32_t T_ST = tmem_base, T_DPT = tmem_base + 128, T_DV = tmem_base + 256, T_DK = tmem_base + 384;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(fixed_full, 2 * SM::TILE);
+#pragma unroll
+      for (int c = 0; c < DC; ++c) {
+        tma_load_2d(sk + c * CHUNK_BYTES, &tmap_k, fixed_full, g * D + c * 64, b * p.T + k0);
+        tma_load_2d(sv + c * CHUNK_BYTES, &tmap_v, fixed_full, g * D + c * 64, b * p.T + k0);
+      }
+      for (int it = 0; it < n_iter; ++it) {
+        const int st = it & 1; const uint32_t ph = (it >> 1) & 1;
+        const int hq = g * group + it / tiles_per_head;
+        const int q0 = (i_begin + it % tiles_per_head) * BT;
+        if (!mbar_wait(&qd_empty[st], ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) goto done;
+        uint8_t* sqs = ring + st * 2 * SM::TILE;
+        uint8_t* sdos = sqs + SM::TILE;
+        mbar_arrive_expect_tx(&qd_full[st], 2 * SM::TILE);
+#pragma unroll
+        for (int c = 0; c < DC; ++c) {
+          tma_load_2d(sqs + c * CHUNK_BYTES, &tmap_q, &qd_full[st], hq * D + c * 64, b * p.T + q0);
+          tma_load_2d(sdos + c * CHUNK_BYTES, &tmap_do, &qd_full[st], hq * D + c * 64, b * p.T + q0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(BT, BT, 0, 0);       // Sᵀ = K·Qᵀ, dPᵀ = V·dOᵀ
+      constexpr uint32_t idesc_acc = make_idesc_bf16(BT, D, 0, 1);      // dV += Pᵀ·dO, dK += dSᵀ·Q (N-major B)
+      if (!mbar_wait(fixed_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL)) goto done;
+      const uint32_t ska = smem_u32(sk), sva = smem_u32(sv);
+      for (int it = 0; it < n_iter; ++it) {
+        const int st = it & 1; const uint32_t ph = (it >> 1) & 1;
+        if (!mbar_wait(&qd_full[st], ph, abort_flag, p.status, STATUS_TIMEOUT_FULL)) goto done;
+        tc_fence_after();
+        const uint32_t sqa = smem_u32(ring + st * 2 * SM::TILE), sdoa = sqa + SM::TILE;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k / 4) * CHUNK_BYTES + (k % 4) * 32;
+          umma_bf16(T_ST, make_smem_desc(ska + off, 16, 1024), make_smem_desc(sqa + off, 16, 1024), idesc_s, k != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k / 4) * CHUNK_BYTES + (k % 4) * 32;
+          umma_bf16(T_DPT, make_smem_desc(sva + off, 16, 1024), make_smem_desc(sdoa + off, 16, 1024), idesc_s, k != 0);
+        }
+        umma_commit(sdp_full);
+        if (!mbar_wait(ds_full, it & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < BT / 16; ++k) {
+          umma_bf16_ts(T_DV, T_ST + k * 8, make_smem_desc(sdoa + k * 2048, CHUNK_BYTES, 1024), idesc_acc, (it | k) != 0);
+          umma_bf16_ts(T_DK, T_DPT + k * 8, make_smem_desc(sqa + k * 2048, CHUNK_BYTES, 1024), idesc_acc, (it | k) != 0);
+        }
+        umma_commit(&qd_empty[st]);
+      }
+      umma_commit(acc_done);
+    }
+  } else {
+    const int qtr = warp & 3;
+    const int tid128 = qtr * 32 + lane;               // 0..127 among the softmax threads
+    const int kk = k0 + tid128;                       // this thread's key row
+    const bool key_valid = kk < p.T;
+    const uint32_t lane_off = static_cast<uint32_t>(qtr * 32) << 16;
+    bool ok = true;     // after a timed-out wait the thread keeps meeting its peers at the named barrier, idle
+    for (int it = 0; it < n_iter; ++it) {
+      const int st = it & 1;
+      if (!ok) { named_bar_sync_128(); continue; }
+      const int hq = g * group + it / tiles_per_head;
+      const int q0 = (i_begin + it % tiles_per_head) * BT;
+      // per-query statistics of this tile → shared memory (each softmax thread fills one entry)
+      float* a_lse = aux + st * 3 * BT;
+      float* a_dlt = a_lse + BT;
+      int* a_lo = reinterpret_cast<int*>(a_dlt + BT);
+      {
+        const int rq = q0 + tid128;
+        const bool v = rq < p.T;
+        const size_t si = (static_cast<size_t>(b) * p.H + hq) * p.T + (v ? rq : 0);
+        a_lse[tid128] = v ? p.lse[si] * kLog2e_b : 0.f;
+        a_dlt[tid128] = v ? p.delta[si] : 0.f;
+        a_lo[tid128] = v ? lo_of_row(p, b, rq) : 0x7fffffff;    // invalid query rows see nothing
+      }
+      named_bar_sync_128();
+      if (!mbar_wait(sdp_full, it & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; continue; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sr[32], dr[32];
+        tmem_ld_32x32(T_ST + c * 32 + lane_off, sr);
+        tmem_ld_32x32(T_DPT + c * 32 + lane_off, dr);
+        tmem_ld_wait();
+        uint32_t wp[16], wd[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          float pv[2], dv2[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int col = c * 32 + 2 * e + u;
+            const int rq = q0 + col;
+            float pr = exp2f(__uint_as_float(sr[2 * e + u]) * p.scale_log2 - a_lse[col]);
+            if (!key_valid || kk > rq || kk < a_lo[col]) pr = 0.f;
+            pv[u] = pr;
+            dv2[u] = pr * (__uint_as_float(dr[2 * e + u]) - a_dlt[col]) * p.scale;
+          }
+          wp[e] = pack_bf16x2(pv[0], pv[1]);
+          wd[e] = pack_bf16x2(dv2[0], dv2[1]);
+        }
+        tmem_st_32x16(T_ST + c * 16 + lane_off, wp);
+        tmem_st_32x16(T_DPT + c * 16 + lane_off, wd);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_full);
+    }
+    if (!ok) goto done;
+    if (!mbar_wait(acc_done, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
+    tc_fence_after();
+    const size_t obase = ((static_cast<size_t>(b) * p.T + kk) * p.G + g) * D;
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      __nv_bfloat16* orow = (which ? p.dk : p.dv) + obase;
+      const uint32_t tsrc = which ? T_DK : T_DV;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t rr[32];
+        if (n_iter > 0) { tmem_ld_32x32(tsrc + c * 32 + lane_off, rr); tmem_ld_wait(); }
+        else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) rr[e] = 0u;
+        }
+        if (key_valid) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(rr[e]), __uint_as_float(rr[e + 1]));
+            o.y = pack_bf16x2(__uint_as_float(rr[e + 2]), __uint_as_float(rr[e + 3]));
+            o.z = pack_bf16x2(__uint_as_float(rr[e + 4]), __uint_as_float(rr[e + 5]));
+            o.w = pack_bf16x2(__uint_as_float(rr[e + 6]), __uint_as_float(rr[e + 7]));
+            *reinterpret_cast<uint4*>(orow + c * 32 + e) = o;
+          }
+        }
+      }
+    }
+  }
+
+done:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int D>
+static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const CUtensorMap& tk, const CUtensorMap& tv,
+                      const AttnBwdParams& p, cudaStream_t st) {
+  auto kq = attn_bwd_dq_kernel<D>;
+  auto kkv = attn_bwd_dkdv_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<D>::TOTAL) != cudaSuccess) return -2;
+    if (cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<D>::TOTAL) != cudaSuccess) return -2;
+    configured = true;
+  }
+  const int nt = (p.T + BT - 1) / BT;
+  kkv<<<dim3(nt, p.G, p.B), BWD_THREADS, BwdSmem<D>::TOTAL, st>>>(tq, tdo, tk, tv, p);
+  kq<<<dim3(nt, p.H, p.B), BWD_THREADS, BwdSmem<D>::TOTAL, st>>>(tq, tdo, tk, tv, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+}  // namespace b200
+
+extern "C" int b200_attn_bwd(const void* d_out, const void* q, const void* k, const void* v, const void* out,
+                             const float* lse, float* delta, const int* row_start, const int* doc_end, void* dq, void* dk,
+                             void* dv, int B, int T, int H, int G, int D, int window_left, float scale, int* status,
+                             cudaStream_t stream) {
+  using namespace b200;
+  if (B <= 0 || T <= 0) return 0;
+  if ((D != 64 && D != 128) || H % G) return -1;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return -5;
+    ctx_bound = true;
+  }
+  const size_t rows = static_cast<size_t>(B) * T * H;
+  const int grid = static_cast<int>((rows * 32 + 255) / 256);
+  if (D == 128) attn_bwd_delta_kernel<128><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out, delta, B, T, H);
+  else attn_bwd_delta_kernel<64><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out, delta, B, T, H);
+  CUtensorMap tq, tdo, tk, tv;
+  const uint64_t hd = static_cast<uint64_t>(H) * D, gd = static_cast<uint64_t>(G) * D, bt = static_cast<uint64_t>(B) * T;
+  int rc = make_tmap_2d_bf16(&tq, q, hd, bt, hd, 64, 128);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tdo, d_out, hd, bt, hd, 64, 128);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tk, k, gd, bt, gd, 64, 128);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tv, v, gd, bt, gd, 64, 128);
+  if (rc) return rc;
+  AttnBwdParams p{lse, delta, row_start, doc_end, (__nv_bfloat16*)dq, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv,
+                  B, T, H, G, window_left, scale, scale * kLog2e_b, status};
+  return D == 128 ? launch_bwd<128>(tq, tdo, tk, tv, p, stream) : launch_bwd<64>(tq, tdo, tk, tv, p, stream);
+}

@@ -1,0 +1,84 @@
+"""tcgen05 attention kernels vs the dense fp32 softmax oracle."""
+import math
+
+import pytest
+import torch
+
+from archscale_b200.ops import backend
+from archscale_b200.ops.attention import attention_ref, row_start_from_cu_seqlens
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
+
+
+CASES = [
+    # B, T, H, G, D, window_left, cu_seqlens
+    (2, 256, 4, 2, 128, -1, None),
+    (1, 300, 2, 1, 128, -1, None),          # ragged tail tile
+    (2, 512, 4, 4, 64, -1, None),
+    (1, 640, 4, 2, 128, 99, None),          # sliding window 100
+    (1, 1024, 2, 2, 64, 511, None),         # window 512, head_dim 64 (phi4-mini-flash shape)
+    (1, 700, 4, 2, 128, -1, [0, 130, 131, 400, 700]),   # packed documents
+    (1, 900, 2, 1, 64, 63, [0, 500, 900]),  # packed + window
+]
+
+
+@pytest.mark.parametrize("B,T,H,G,D,win,cu", CASES)
+def test_attention_forward(B, T, H, G, D, win, cu):
+    ext = backend.require_extension()
+    torch.manual_seed(0)
+    q = torch.randn(B, T, H, D, device="cuda").bfloat16()
+    k = torch.randn(B, T, G, D, device="cuda").bfloat16()
+    v = torch.randn(B, T, G, D, device="cuda").bfloat16()
+    scale = 1.0 / math.sqrt(D)
+    cu_t = torch.tensor(cu, device="cuda", dtype=torch.int32) if cu else None
+    rs = row_start_from_cu_seqlens(cu_t, T) if cu else None
+    out, lse = ext.attn_fwd_only(q, k, v, scale, win, rs)
+    torch.cuda.synchronize()
+    assert ext.device_status() == 0
+    ref, lse_ref = attention_ref(q, k, v, scale, (win, 0) if win >= 0 else (-1, -1), cu_t, None, True)
+    assert _rel(out, ref) < 2e-2, _rel(out, ref)
+    assert float((lse - lse_ref).abs().max()) < 2e-2
+
+
+@pytest.mark.parametrize("B,T,H,G,D,win,cu", CASES)
+def test_attention_backward(B, T, H, G, D, win, cu):
+    from archscale_b200 import ops
+    ext = backend.require_extension()
+    torch.manual_seed(1)
+    q = torch.randn(B, T, H, D, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(B, T, G, D, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(B, T, G, D, device="cuda").bfloat16().requires_grad_()
+    scale = 1.0 / math.sqrt(D)
+    cu_t = torch.tensor(cu, device="cuda", dtype=torch.int32) if cu else None
+    window = (win, 0) if win >= 0 else (-1, -1)
+    out = ops.attention(q, k, v, scale=scale, window=window, cu_seqlens=cu_t)
+    g = torch.randn_like(out)
+    out.backward(g)
+    torch.cuda.synchronize()
+    assert ext.device_status() == 0
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = attention_ref(qr, kr, vr, scale, window, cu_t)
+    ref.backward(g.float())
+    assert _rel(out, ref) < 2e-2
+    assert _rel(q.grad, qr.grad) < 3e-2, _rel(q.grad, qr.grad)
+    assert _rel(k.grad, kr.grad) < 3e-2, _rel(k.grad, kr.grad)
+    assert _rel(v.grad, vr.grad) < 3e-2, _rel(v.grad, vr.grad)
+
+
+def test_attention_backward_is_deterministic():
+    from archscale_b200 import ops
+    torch.manual_seed(2)
+    q = torch.randn(2, 512, 8, 128, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(2, 512, 2, 128, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(2, 512, 2, 128, device="cuda").bfloat16().requires_grad_()
+    g = torch.randn(2, 512, 8, 128, device="cuda").bfloat16()
+    grads = []
+    for _ in range(2):
+        out = ops.attention(q, k, v)
+        grads.append(torch.autograd.grad(out, (q, k, v), g))
+    for a, b in zip(*grads):
+        assert torch.equal(a, b)
