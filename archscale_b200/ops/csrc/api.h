@@ -51,6 +51,19 @@ int b200_qknorm_rope_bwd(const void* dqo, const void* dko, const void* q, const 
                          int64_t n_tokens, int T, int H, int G, int D, cudaStream_t stream);
 int b200_qknorm_rope_grid();
 
+// ---- mixture of experts (moe_routing.cu, gemm_bf16.cu)
+int b200_topk_indices(const float* logits, int* idx, int N, int E, int K, cudaStream_t stream);
+int b200_routing_chunks(int n_pairs);
+int b200_routing_capacity(int n_pairs, int E);
+int b200_routing_layout(const int* expert_of_pair, int n_pairs, int E, int* counts, int* offsets, int* slot_pair,
+                        int* pair_slot, int capacity, int* scratch, cudaStream_t stream);
+int b200_gather_rows(const void* x, const int* slot_pair, const float* pair_scale, void* xs, int capacity, int C, int K,
+                     const int* offsets, int E, cudaStream_t stream);
+int b200_combine_rows(const void* y, const int* pair_slot, const float* w, void* out, int N, int C, int K, cudaStream_t stream);
+int b200_pair_dots(const void* y, const void* g, const int* pair_slot, float* dots, int n_pairs, int C, int K, cudaStream_t stream);
+int b200_grouped_gemm_bf16(int kind, const void* A, const void* B, void* out, const int* offsets, int E, int capacity, int M,
+                           int N, int K, int out_f32, int accumulate, int num_sms, int* status, cudaStream_t stream);
+
 // Attention forward (attention_fwd.cu).  q:[B,T,H,D] k,v:[B,T,G,D] bf16 → out bf16, lse fp32 [B,H,T].
 // row_start: optional int32 [B*T], first key each query row may see (packed documents).
 int b200_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* row_start, int B, int T,

@@ -44,6 +44,17 @@ struct AgParams {
 };
 constexpr size_t AG_CHUNK = 256 * 1024;
 
+// Grouped (mixture-of-experts) GEMMs.  Activations are stored expert-sorted with every expert's segment
+// starting at a multiple of 128 rows (offsets[E+1], device memory, written by the routing kernels):
+//   GROUPED = 1  rows grouped:  out[r, :] = A[r, :] · op(B[e(r)])   — B holds E matrices back to back
+//                (forward up/down projection with B [E·N, K] K-major; dgrad with B [E·K, N] N-major)
+//   GROUPED = 2  wgrad: out[e] (M×N) (+)= A[rows of e, :M]ᵀ · B[rows of e, :N]   (TN, K-loop over the segment)
+struct GroupParams {
+  const int* offsets;   // [E+1], multiples of 128
+  int E;
+  int b_rows;           // rows of one expert's matrix inside B (N for K-major B, K for N-major B)
+};
+
 struct GemmParams {
   void* out;
   const void* cin;
@@ -153,10 +164,18 @@ __device__ __forceinline__ bool ag_wait(const AgParams& ag, size_t lo, size_t hi
   return true;
 }
 
-template <int A_MN, int B_MN, int OUT_F32, int FUSED_AG = 0>
+struct Tile {
+  int m0;        // first row of the A / output tile (for GROUPED=2: first output row inside the expert's matrix)
+  int n0;        // first output column
+  int b_row;     // row offset added to B's row coordinate (expert base)
+  int kb0, kb1;  // K-block range
+  size_t out_off;  // element offset added to the output pointer (expert base for GROUPED=2)
+};
+
+template <int A_MN, int B_MN, int OUT_F32, int FUSED_AG = 0, int GROUPED = 0>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const GemmParams p, const AgParams ag) {
+                 const GemmParams p, const AgParams ag, const GroupParams gp) {
   if (FUSED_AG && static_cast<int>(blockIdx.x) < ag.n_copy) {   // copier CTAs: lowest indices, scheduled first
     extern __shared__ uint8_t smem_copier[];
     ag_copier(ag, reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_copier) + 1023) & ~uintptr_t(1023)), p.status);
@@ -175,8 +194,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN;
-  const int num_tiles = num_m * num_n;
+  __shared__ int s_off[258];
+  if (GROUPED) {
+    for (int i = threadIdx.x; i <= gp.E; i += blockDim.x) s_off[i] = gp.offsets[i];
+    __syncthreads();
+  }
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_m = GROUPED == 1 ? s_off[GROUPED ? gp.E : 0] / BM : (p.M + BM - 1) / BM;
+  const int num_tiles = (GROUPED == 2 ? gp.E : 1) * num_m * num_n;
   const int num_kb = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -202,19 +227,36 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     m_idx = first_m + (r % gsz);
     n_idx = r / gsz;
   };
+  auto get_tile = [&](int t, Tile& tl) {
+    if (GROUPED == 2) {
+      const int per_e = num_m * num_n;
+      const int e = t / per_e, r = t - e * per_e;
+      tl.m0 = (r % num_m) * BM; tl.n0 = (r / num_m) * BN; tl.b_row = 0;
+      tl.kb0 = s_off[e] / BK; tl.kb1 = s_off[e + 1] / BK;
+      tl.out_off = static_cast<size_t>(e) * p.M * p.ldc;
+    } else {
+      int mi, ni; tile_coords(t, mi, ni);
+      tl.m0 = mi * BM; tl.n0 = ni * BN; tl.kb0 = 0; tl.kb1 = num_kb; tl.out_off = 0; tl.b_row = 0;
+      if (GROUPED == 1) {
+        int lo = 0, hi = gp.E;          // expert whose segment holds row m0
+        while (lo + 1 < hi) { const int mid = (lo + hi) >> 1; if (s_off[mid] <= tl.m0) lo = mid; else hi = mid; }
+        tl.b_row = lo * gp.b_rows;
+      }
+    }
+  };
 
   if (warp == 0) {
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       for (int t = cta; t < num_tiles; t += n_cta) {
-        int mi, ni; tile_coords(t, mi, ni);
-        const int m0 = mi * BM, n0 = ni * BN;
+        Tile tl; get_tile(t, tl);
+        const int m0 = tl.m0, n0 = tl.n0;
         if (FUSED_AG) {
           const size_t row_bytes = static_cast<size_t>(p.K) * 2;
           const int n_hi = n0 + BN < p.N ? n0 + BN : p.N;
           if (!ag_wait(ag, ag.b_off + n0 * row_bytes, ag.b_off + n_hi * row_bytes, abort_flag, p.status)) goto done;
         }
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = tl.kb0; kb < tl.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) goto done;
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_STAGE_BYTES;
@@ -227,9 +269,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           if (B_MN) {
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sb + c * (64 * BK * 2), &tmap_b, &full_bar[stage], n0 + c * 64, kb * BK);
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sb + c * (64 * BK * 2), &tmap_b, &full_bar[stage], n0 + c * 64, (GROUPED == 1 ? tl.b_row : 0) + kb * BK);
           } else {
-            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BK, n0);
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BK, (GROUPED == 1 ? tl.b_row : 0) + n0);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -248,7 +291,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) goto done;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        Tile tl; get_tile(t, tl);
+        for (int kb = tl.kb0; kb < tl.kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_FULL)) goto done;
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
@@ -258,34 +302,41 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             umma_bf16(d_tmem, da + static_cast<uint64_t>(k * a_kstep), db + static_cast<uint64_t>(k * b_kstep), idesc,
-                      (kb | k) != 0 ? 1u : 0u);
+                      (kb != tl.kb0 || k != 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        umma_commit(&tmem_full[acc]);
+        if (tl.kb0 == tl.kb1) mbar_arrive(&tmem_full[acc]);   // empty expert segment: nothing was issued
+        else umma_commit(&tmem_full[acc]);
       }
     }
   } else {
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     int it = 0;
     for (int t = cta; t < num_tiles; t += n_cta, ++it) {
-      int mi, ni; tile_coords(t, mi, ni);
+      Tile tl; get_tile(t, tl);
+      const bool empty_tile = tl.kb0 == tl.kb1;
       const int acc = it & 1; const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
       tc_fence_after();
-      const int row = mi * BM + q * 32 + lane;
-      const int col0 = ni * BN;
+      const int row = tl.m0 + q * 32 + lane;
+      const int col0 = tl.n0;
+      const int row_limit = GROUPED == 1 ? s_off[gp.E] : p.M;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
+        if (empty_tile) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r[e] = 0u;
+        }
         const int col = col0 + c * 32;
-        if (row < p.M && col < p.N) {
+        if (row < row_limit && col < p.N) {
           if (OUT_F32) {
-            float* o = reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ldc + col;
+            float* o = reinterpret_cast<float*>(p.out) + tl.out_off + static_cast<size_t>(row) * p.ldc + col;
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
               if (col + j < p.N) {
@@ -299,8 +350,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               }
             }
           } else {
-            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ldc + col;
-            const __nv_bfloat16* ci = p.cin ? reinterpret_cast<const __nv_bfloat16*>(p.cin) + static_cast<size_t>(row) * p.ldc + col : nullptr;
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + tl.out_off + static_cast<size_t>(row) * p.ldc + col;
+            const __nv_bfloat16* ci = p.cin ? reinterpret_cast<const __nv_bfloat16*>(p.cin) + tl.out_off + static_cast<size_t>(row) * p.ldc + col : nullptr;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               if (col + j < p.N) {
@@ -386,7 +437,8 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const Ge
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
   AgParams none{};
-  kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb, p, none);
+  GroupParams nog{};
+  kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb, p, none, nog);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -457,6 +509,74 @@ extern "C" int b200_ag_gemm_bf16(const void* A, void* out, int M, int N, int K, 
   int compute = num_sms - n_copy;
   if (compute > tiles) compute = tiles;
   if (compute < 1) return -6;
-  kern<<<compute + n_copy, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, ag);
+  GroupParams nog{};
+  kern<<<compute + n_copy, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, ag, nog);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// Grouped GEMMs over an expert-sorted, 128-row-aligned activation layout (see GroupParams).
+//   kind 0: out[rows, N] = A[rows, K] · B[e]ᵀ   with B stored [E·N, K]           (forward projections)
+//   kind 1: out[rows, N] = A[rows, K] · B[e]    with B stored [E·K, N]           (dgrad)
+//   kind 2: out[e][M, N] (+)= A[rows_e, M]ᵀ · B[rows_e, N], fp32 or bf16 output  (wgrad)
+// `capacity` = number of rows allocated in the sorted layout (upper bound of offsets[E]).
+extern "C" int b200_grouped_gemm_bf16(int kind, const void* A, const void* B, void* out, const int* offsets, int E,
+                                      int capacity, int M, int N, int K, int out_f32, int accumulate, int num_sms,
+                                      int* status, cudaStream_t stream) {
+  using namespace b200;
+  if (E <= 0 || E > 256 || capacity <= 0) return -1;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return -5;
+    ctx_bound = true;
+  }
+  CUtensorMap ta, tb;
+  int rc;
+  AgParams none{};
+  GroupParams gp{offsets, E, 0};
+  if (kind == 0 || kind == 1) {
+    // A: [capacity, K] K-major
+    rc = make_tmap_2d_bf16(&ta, A, K, capacity, K, BK, BM);
+    if (rc) return rc;
+    if (kind == 0) { rc = make_tmap_2d_bf16(&tb, B, K, static_cast<uint64_t>(E) * N, K, BK, BN); gp.b_rows = N; }
+    else           { rc = make_tmap_2d_bf16(&tb, B, N, static_cast<uint64_t>(E) * K, N, 64, BK); gp.b_rows = K; }
+    if (rc) return rc;
+    GemmParams p{out, nullptr, capacity, N, K, N, 1.f, 0.f, 0, status};
+    const int max_tiles = (capacity / BM) * ((N + BN - 1) / BN);
+    const int grid = max_tiles < num_sms ? (max_tiles > 0 ? max_tiles : 1) : num_sms;
+    if (kind == 0) {
+      auto kern = gemm_bf16_kernel<0, 0, 0, 0, 1>;
+      static bool cfg = false;
+      if (!cfg) { if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess) return -2; cfg = true; }
+      kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, none, gp);
+    } else {
+      auto kern = gemm_bf16_kernel<0, 1, 0, 0, 1>;
+      static bool cfg = false;
+      if (!cfg) { if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess) return -2; cfg = true; }
+      kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, none, gp);
+    }
+  } else if (kind == 2) {
+    // A: [capacity, M] (MN-major), B: [capacity, N] (MN-major); K = rows of the expert's segment
+    rc = make_tmap_2d_bf16(&ta, A, M, capacity, M, 64, BK);
+    if (rc) return rc;
+    rc = make_tmap_2d_bf16(&tb, B, N, capacity, N, 64, BK);
+    if (rc) return rc;
+    GemmParams p{out, nullptr, M, N, capacity, N, 1.f, 0.f, accumulate, status};
+    const int tiles = E * ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int grid = tiles < num_sms ? tiles : num_sms;
+    if (out_f32) {
+      auto kern = gemm_bf16_kernel<1, 1, 1, 0, 2>;
+      static bool cfg = false;
+      if (!cfg) { if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess) return -2; cfg = true; }
+      kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, none, gp);
+    } else {
+      auto kern = gemm_bf16_kernel<1, 1, 0, 0, 2>;
+      static bool cfg = false;
+      if (!cfg) { if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess) return -2; cfg = true; }
+      kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, none, gp);
+    }
+  } else {
+    return -4;
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

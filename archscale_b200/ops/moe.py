@@ -42,7 +42,19 @@ def router_topk_softmax_ref(logits: torch.Tensor, k: int, sqrt_gate: bool = Fals
 
 
 def router_topk_softmax(logits: torch.Tensor, k: int, sqrt_gate: bool = False):
-    """(N,E) logits → (scores (N,k) fp32 with grad, indices (N,k) int32)."""
+    """(N,E) logits → (scores (N,k) fp32 with grad, indices (N,k) int32).
+
+    The selection (the expensive part) is one kernel; the softmax over the k selected logits is a
+    gather + softmax on an (N,k) tensor, differentiable through plain autograd."""
+    if (logits.is_cuda and logits.dtype == torch.float32 and logits.shape[1] <= 256 and backend.has("topk_indices")
+            and backend.use_cuda_kernel("router", logits)):
+        idx = backend.require_extension().topk_indices(logits.detach().contiguous(), k)
+        backend.count_launch()
+        vals = torch.gather(logits, 1, idx.long())
+        scores = torch.softmax(vals, dim=-1)
+        if sqrt_gate:
+            scores = torch.sqrt(scores + 1e-30)
+        return scores, idx
     return router_topk_softmax_ref(logits, k, sqrt_gate)
 
 

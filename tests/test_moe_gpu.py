@@ -1,0 +1,70 @@
+"""MoE routing kernels and the grouped tcgen05 GEMM path vs the dense per-expert oracle."""
+import pytest
+import torch
+
+from archscale_b200 import ops
+from archscale_b200.ops import backend
+from archscale_b200.ops.moe import moe_ffn_ref, router_topk_softmax_ref, routing_metadata_ref
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
+
+
+def test_topk_indices_matches_stable_topk():
+    torch.manual_seed(0)
+    logits = torch.randn(4099, 64, device="cuda")
+    logits[:, 5] = logits[:, 9]                 # ties: the lower index must win
+    s, i = ops.router_topk_softmax(logits, 8, sqrt_gate=True)
+    sr, ir = router_topk_softmax_ref(logits, 8, sqrt_gate=True)
+    assert torch.equal(i, ir)
+    assert torch.allclose(s, sr, atol=1e-6)
+
+
+@pytest.mark.parametrize("N,E,K", [(1000, 64, 8), (37, 63, 7), (5000, 8, 2)])
+def test_routing_layout_is_a_stable_aligned_sort(N, E, K):
+    ext = backend.require_extension()
+    torch.manual_seed(1)
+    idx = torch.stack([torch.randperm(E, device="cuda")[:K] for _ in range(N)]).to(torch.int32)
+    if E == 63:
+        idx[idx == 17] = 18                     # an expert that receives nothing
+    counts, offsets, slot_pair, pair_slot = ext.routing_layout(idx.reshape(-1).contiguous(), E)
+    c_ref, _, order = routing_metadata_ref(idx, E)
+    assert torch.equal(counts, c_ref)
+    off = offsets.tolist()
+    assert all(o % 128 == 0 for o in off) and off[0] == 0
+    pos = 0
+    sp = slot_pair.tolist()
+    order = order.tolist()
+    for e in range(E):
+        n = int(counts[e])
+        assert sp[off[e]:off[e] + n] == order[pos:pos + n]          # stable order inside the expert
+        assert all(v == -1 for v in sp[off[e] + n:off[e + 1]])      # padding
+        pos += n
+    assert torch.equal(slot_pair[pair_slot.long()].cpu(), torch.arange(N * K, dtype=torch.int32))
+
+
+@pytest.mark.parametrize("N,C,E,I,K", [(512, 256, 8, 128, 2), (1000, 1024, 64, 256, 8), (300, 512, 63, 64, 7)])
+def test_moe_ffn_forward_backward(N, C, E, I, K):
+    torch.manual_seed(2)
+    x = (torch.randn(N, C, device="cuda") * 0.5).bfloat16().requires_grad_()
+    w_in = (torch.randn(E, 2 * I, C, device="cuda") * 0.05).bfloat16().requires_grad_()
+    w_out = (torch.randn(E, C, I, device="cuda") * 0.05).bfloat16().requires_grad_()
+    logits = torch.randn(N, E, device="cuda", requires_grad=True)
+    scores, idx = ops.router_topk_softmax(logits, K, sqrt_gate=True)
+    out = ops.moe_ffn(x, w_in, w_out, scores, idx)
+    g = torch.randn_like(out)
+    out.backward(g)
+    torch.cuda.synchronize()
+    assert backend.require_extension().device_status() == 0
+    xr, wir, wor, lr = (t.detach().float().requires_grad_() for t in (x, w_in, w_out, logits))
+    sr, ir = router_topk_softmax_ref(lr, K, sqrt_gate=True)
+    ref = moe_ffn_ref(xr, wir, wor, sr, ir)
+    ref.backward(g.float())
+    assert _rel(out, ref) < 2e-2
+    assert _rel(x.grad, xr.grad) < 3e-2
+    assert _rel(w_in.grad, wir.grad) < 3e-2
+    assert _rel(w_out.grad, wor.grad) < 3e-2
+    assert _rel(logits.grad, lr.grad) < 3e-2
