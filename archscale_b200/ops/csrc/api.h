@@ -14,6 +14,9 @@ int b200_gemm_bf16(int mode, const void* A, const void* B, void* out, const void
                    int ldb, int ldc, float alpha, float beta, int out_f32, int accumulate, int num_sms, int* status,
                    cudaStream_t stream);
 
+int b200_gemm_bf16_batched(int mode, const void* A, const void* B, void* out, const void* cin, int batch, int M, int N,
+                           int K, float alpha, float beta, int num_sms, int* status, cudaStream_t stream);
+
 // RMSNorm over the last dim.  x:[rows,cols] (fp32|bf16), w:[cols] or null, out dtype chosen by out_dtype.
 int b200_rmsnorm_fwd(const void* x, int x_dtype, const void* w, int w_dtype, void* out, int out_dtype, float* rstd,
                      int rows, int cols, float eps, cudaStream_t stream);
@@ -93,6 +96,13 @@ int b200_reduce_scatter_pull(const void* const* bases, size_t full_off, float* o
                              int world, float scale, int accumulate, int max_ctas, cudaStream_t stream);
 int b200_reduce_scatter_pull_bf16(const void* const* bases, size_t full_off, void* out, size_t shard_elems, int rank,
                                   int world, int max_ctas, cudaStream_t stream);
+
+// Expert-parallel dispatch (owners pull their experts' rows from every rank's send buffer) and return.
+int b200_ep_dispatch(const void* const* bases, size_t off_counts, size_t off_offsets, size_t off_table, size_t off_send,
+                     size_t off_recv, int rank, int world, int e_local, int C, int recv_cap, int* recv_offsets, int* status,
+                     cudaStream_t stream);
+int b200_ep_return(const void* const* bases, size_t off_counts, size_t off_offsets, size_t off_table, size_t off_result,
+                   void* dst, int rank, int world, int e_local, int C, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -234,3 +234,134 @@ extern "C" int b200_reduce_scatter_pull_bf16(const void* const* bases, size_t fu
                                                                            static_cast<uint4*>(out), sv, rank, world);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Expert-parallel dispatch / combine by peer pulls.  Every rank publishes in its heap:
+//   send rows   [rows_cap, C] bf16, expert-sorted (segment of expert e starts at offsets[e], counts[e] rows)
+//   counts[E], offsets[E+1]
+// The owner of local expert e_l (global e = rank·E_l + e_l) lays its receive buffer out expert-major,
+// sources in rank order inside an expert, expert segments starting at multiples of 128 rows, and records
+// in `table[src][e_l]` where each source's rows start (sources read it to pull their results back).
+namespace b200 {
+
+struct EpArgs {
+  const void* peer[8];
+  size_t off_counts, off_offsets, off_table, off_send, off_recv;   // heap offsets (same on every rank)
+  int rank, world, e_local, C, recv_cap;
+};
+
+// one CTA: build recv_offsets[e_local+1] (local device array) and table (in my heap); flag overflow
+__global__ void ep_plan_kernel(EpArgs a, int* __restrict__ recv_offsets, int* status) {
+  __shared__ int s_total[256];
+  const int el = threadIdx.x;
+  if (el < a.e_local) {
+    int tot = 0;
+    for (int s = 0; s < a.world; ++s)
+      tot += reinterpret_cast<const int*>(static_cast<const char*>(a.peer[s]) + a.off_counts)[a.rank * a.e_local + el];
+    s_total[el] = tot;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < a.e_local; ++e) { recv_offsets[e] = acc; acc += (s_total[e] + 127) / 128 * 128; }
+    recv_offsets[a.e_local] = acc;
+    if (acc > a.recv_cap && status) atomicCAS(status, 0, STATUS_BAD_ARG);
+  }
+  __syncthreads();
+  if (el < a.e_local) {
+    int* table = reinterpret_cast<int*>(static_cast<char*>(const_cast<void*>(a.peer[a.rank])) + a.off_table);
+    int run = recv_offsets[el];
+    for (int s = 0; s < a.world; ++s) {
+      table[s * a.e_local + el] = run;
+      run += reinterpret_cast<const int*>(static_cast<const char*>(a.peer[s]) + a.off_counts)[a.rank * a.e_local + el];
+    }
+  }
+}
+
+// grid (e_local, world, chunks): copy the rows of (source s, local expert el) into my recv buffer;
+// the last source also zero-fills the padding rows of the expert segment.
+__global__ void __launch_bounds__(256) ep_pull_kernel(EpArgs a, const int* __restrict__ recv_offsets) {
+  const int el = blockIdx.x, s = blockIdx.y;
+  const int e = a.rank * a.e_local + el;
+  const char* src_base = static_cast<const char*>(a.peer[s]);
+  const int cnt = reinterpret_cast<const int*>(src_base + a.off_counts)[e];
+  const int src_row = reinterpret_cast<const int*>(src_base + a.off_offsets)[e];
+  const int* table = reinterpret_cast<const int*>(static_cast<const char*>(a.peer[a.rank]) + a.off_table);
+  const int dst_row = table[s * a.e_local + el];
+  const int vec_per_row = a.C / 8;
+  const uint4* src = reinterpret_cast<const uint4*>(src_base + a.off_send) + static_cast<size_t>(src_row) * vec_per_row;
+  uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(const_cast<void*>(a.peer[a.rank])) + a.off_recv) +
+               static_cast<size_t>(dst_row) * vec_per_row;
+  const size_t total = static_cast<size_t>(cnt) * vec_per_row;
+  constexpr int U = 8;
+  for (size_t i0 = (blockIdx.z * static_cast<size_t>(blockDim.x)) * U + threadIdx.x; i0 < total;
+       i0 += static_cast<size_t>(gridDim.z) * blockDim.x * U) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) { const size_t i = i0 + static_cast<size_t>(u) * blockDim.x; if (i < total) v[u] = src[i]; }
+#pragma unroll
+    for (int u = 0; u < U; ++u) { const size_t i = i0 + static_cast<size_t>(u) * blockDim.x; if (i < total) dst[i] = v[u]; }
+  }
+  if (s == a.world - 1) {
+    const size_t pad_begin = static_cast<size_t>(dst_row + cnt) * vec_per_row;
+    const size_t pad_end = static_cast<size_t>(recv_offsets[el + 1]) * vec_per_row;
+    uint4* base = reinterpret_cast<uint4*>(static_cast<char*>(const_cast<void*>(a.peer[a.rank])) + a.off_recv);
+    for (size_t i = pad_begin + blockIdx.z * static_cast<size_t>(blockDim.x) + threadIdx.x; i < pad_end;
+         i += static_cast<size_t>(gridDim.z) * blockDim.x)
+      base[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+// grid (E, chunks): pull my rows of global expert e back from its owner's result buffer into `dst`
+// (local, same expert-sorted layout as my send buffer).
+__global__ void __launch_bounds__(256) ep_return_kernel(EpArgs a, size_t off_result, uint4* __restrict__ dst) {
+  const int e = blockIdx.x;
+  const int owner = e / a.e_local, el = e - owner * a.e_local;
+  const char* me = static_cast<const char*>(a.peer[a.rank]);
+  const int cnt = reinterpret_cast<const int*>(me + a.off_counts)[e];
+  const int my_row = reinterpret_cast<const int*>(me + a.off_offsets)[e];
+  const char* ob = static_cast<const char*>(a.peer[owner]);
+  const int their_row = reinterpret_cast<const int*>(ob + a.off_table)[a.rank * a.e_local + el];
+  const int vec_per_row = a.C / 8;
+  const uint4* src = reinterpret_cast<const uint4*>(ob + off_result) + static_cast<size_t>(their_row) * vec_per_row;
+  uint4* d = dst + static_cast<size_t>(my_row) * vec_per_row;
+  const size_t total = static_cast<size_t>(cnt) * vec_per_row;
+  constexpr int U = 8;
+  for (size_t i0 = (blockIdx.y * static_cast<size_t>(blockDim.x)) * U + threadIdx.x; i0 < total;
+       i0 += static_cast<size_t>(gridDim.y) * blockDim.x * U) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) { const size_t i = i0 + static_cast<size_t>(u) * blockDim.x; if (i < total) v[u] = src[i]; }
+#pragma unroll
+    for (int u = 0; u < U; ++u) { const size_t i = i0 + static_cast<size_t>(u) * blockDim.x; if (i < total) d[i] = v[u]; }
+  }
+}
+
+}  // namespace b200
+
+static b200::EpArgs make_ep(const void* const* bases, size_t off_counts, size_t off_offsets, size_t off_table, size_t off_send,
+                            size_t off_recv, int rank, int world, int e_local, int C, int recv_cap) {
+  b200::EpArgs a;
+  for (int i = 0; i < 8; ++i) a.peer[i] = i < world ? bases[i] : nullptr;
+  a.off_counts = off_counts; a.off_offsets = off_offsets; a.off_table = off_table; a.off_send = off_send; a.off_recv = off_recv;
+  a.rank = rank; a.world = world; a.e_local = e_local; a.C = C; a.recv_cap = recv_cap;
+  return a;
+}
+
+extern "C" int b200_ep_dispatch(const void* const* bases, size_t off_counts, size_t off_offsets, size_t off_table,
+                                size_t off_send, size_t off_recv, int rank, int world, int e_local, int C, int recv_cap,
+                                int* recv_offsets, int* status, cudaStream_t st) {
+  if (world > 8 || e_local > 256 || C % 8) return -1;
+  b200::EpArgs a = make_ep(bases, off_counts, off_offsets, off_table, off_send, off_recv, rank, world, e_local, C, recv_cap);
+  b200::ep_plan_kernel<<<1, 256, 0, st>>>(a, recv_offsets, status);
+  b200::ep_pull_kernel<<<dim3(e_local, world, 8), 256, 0, st>>>(a, recv_offsets);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int b200_ep_return(const void* const* bases, size_t off_counts, size_t off_offsets, size_t off_table,
+                              size_t off_result, void* dst, int rank, int world, int e_local, int C, cudaStream_t st) {
+  if (world > 8 || C % 8) return -1;
+  b200::EpArgs a = make_ep(bases, off_counts, off_offsets, off_table, 0, 0, rank, world, e_local, C, 0);
+  b200::ep_return_kernel<<<dim3(e_local * world, 4), 256, 0, st>>>(a, off_result, static_cast<uint4*>(dst));
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

@@ -195,13 +195,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   __shared__ int s_off[258];
-  if (GROUPED) {
+  if (GROUPED == 1 || GROUPED == 2) {
     for (int i = threadIdx.x; i <= gp.E; i += blockDim.x) s_off[i] = gp.offsets[i];
     __syncthreads();
   }
   const int num_n = (p.N + BN - 1) / BN;
   const int num_m = GROUPED == 1 ? s_off[GROUPED ? gp.E : 0] / BM : (p.M + BM - 1) / BM;
-  const int num_tiles = (GROUPED == 2 ? gp.E : 1) * num_m * num_n;
+  const int num_tiles = ((GROUPED == 2 || GROUPED == 3) ? gp.E : 1) * num_m * num_n;
   const int num_kb = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -228,7 +228,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     n_idx = r / gsz;
   };
   auto get_tile = [&](int t, Tile& tl) {
-    if (GROUPED == 2) {
+    if (GROUPED == 3) {          // batched: gp.E matrices of identical shape, 3-D tensor maps
+      const int per_b = num_m * num_n;
+      const int bi = t / per_b, r = t - bi * per_b;
+      tl.m0 = (r % num_m) * BM; tl.n0 = (r / num_m) * BN; tl.b_row = bi;
+      tl.kb0 = 0; tl.kb1 = num_kb;
+      tl.out_off = static_cast<size_t>(bi) * p.M * p.ldc;
+    } else if (GROUPED == 2) {
       const int per_e = num_m * num_n;
       const int e = t / per_e, r = t - e * per_e;
       tl.m0 = (r % num_m) * BM; tl.n0 = (r / num_m) * BN; tl.b_row = 0;
@@ -261,6 +267,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_STAGE_BYTES;
           mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
+          if (GROUPED == 3) {
+            if (A_MN) {
+#pragma unroll
+              for (int c = 0; c < BM / 64; ++c) tma_load_3d(sa + c * (64 * BK * 2), &tmap_a, &full_bar[stage], m0 + c * 64, kb * BK, tl.b_row);
+            } else {
+              tma_load_3d(sa, &tmap_a, &full_bar[stage], kb * BK, m0, tl.b_row);
+            }
+            if (B_MN) {
+#pragma unroll
+              for (int c = 0; c < BN / 64; ++c) tma_load_3d(sb + c * (64 * BK * 2), &tmap_b, &full_bar[stage], n0 + c * 64, kb * BK, tl.b_row);
+            } else {
+              tma_load_3d(sb, &tmap_b, &full_bar[stage], kb * BK, n0, tl.b_row);
+            }
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            continue;
+          }
           if (A_MN) {
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (64 * BK * 2), &tmap_a, &full_bar[stage], m0 + c * 64, kb * BK);
@@ -426,6 +448,21 @@ int make_tmap_2d_bf16(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+// 3-D bf16 tensor map: [inner (contiguous), rows, batch]; box covers one batch entry.
+int make_tmap_3d_bf16(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t rows, uint64_t batch,
+                      uint64_t row_stride_elems, uint64_t batch_stride_elems, uint32_t box_inner, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t gdim[3] = {inner, rows, batch};
+  cuuint64_t gstride[2] = {row_stride_elems * 2, batch_stride_elems * 2};
+  cuuint32_t box[3] = {box_inner, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
 template <int A_MN, int B_MN, int OUT_F32>
 static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int sms, cudaStream_t st) {
   auto kern = gemm_bf16_kernel<A_MN, B_MN, OUT_F32>;
@@ -577,6 +614,44 @@ extern "C" int b200_grouped_gemm_bf16(int kind, const void* A, const void* B, vo
     }
   } else {
     return -4;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// Batched GEMM over `batch` contiguous matrices of identical shape (Newton–Schulz on stacked experts):
+//   out[b] = alpha · op(A[b]) · op(B[b]) + beta · C[b], bf16 in / bf16 out, mode as in b200_gemm_bf16 (0: NT, 1: NN).
+extern "C" int b200_gemm_bf16_batched(int mode, const void* A, const void* B, void* out, const void* cin, int batch, int M,
+                                      int N, int K, float alpha, float beta, int num_sms, int* status, cudaStream_t stream) {
+  using namespace b200;
+  if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return 0;
+  if (mode != 0 && mode != 1) return -4;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return -5;
+    ctx_bound = true;
+  }
+  CUtensorMap ta, tb;
+  int rc = make_tmap_3d_bf16(&ta, A, K, M, batch, K, static_cast<uint64_t>(M) * K, BK, BM);
+  if (rc) return rc;
+  if (mode == 0) rc = make_tmap_3d_bf16(&tb, B, K, N, batch, K, static_cast<uint64_t>(N) * K, BK, BN);
+  else           rc = make_tmap_3d_bf16(&tb, B, N, K, batch, N, static_cast<uint64_t>(K) * N, 64, BK);
+  if (rc) return rc;
+  GemmParams p{out, cin, M, N, K, N, alpha, beta, 0, status};
+  AgParams none{};
+  GroupParams gp{nullptr, batch, 0};
+  const int tiles = batch * ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  if (mode == 0) {
+    auto kern = gemm_bf16_kernel<0, 0, 0, 0, 3>;
+    static bool cfg = false;
+    if (!cfg) { if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess) return -2; cfg = true; }
+    kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, none, gp);
+  } else {
+    auto kern = gemm_bf16_kernel<0, 1, 0, 0, 3>;
+    static bool cfg = false;
+    if (!cfg) { if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess) return -2; cfg = true; }
+    kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, none, gp);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

@@ -119,6 +119,10 @@ class ShardedOptimizer:
             load[key][r] += mt.rows * mt.cols * min(mt.rows, mt.cols)
         self.mats = mats
         self.n_norm = n_norm
+        # norm slots of parameters that are complete on this rank (expert-parallel experts, replicated
+        # tensors): they must not be summed over the shard group
+        local = [mt.norm_idx for mt in mats if mt.group.world == 1] + [k for (g, _, k) in self.hyper_vecs if g.world == 1]
+        self.local_norm_idx = torch.tensor(sorted(set(local)), dtype=torch.long, device=self.engine.device) if local else None
 
     # ------------------------------------------------------------------ helpers
     def _lr_for(self, kind: str) -> float:
@@ -224,7 +228,10 @@ class ShardedOptimizer:
         if hb_x:
             if eng.mesh.fsdp > 1:
                 packed = torch.stack((x_sq, u_sq))
+                keep = packed[:, self.local_norm_idx].clone() if self.local_norm_idx is not None else None
                 du.all_reduce_sum(packed, group=eng.mesh.fsdp_group)
+                if keep is not None:
+                    packed[:, self.local_norm_idx] = keep
                 x_sq, u_sq = packed[0], packed[1]
             x_norm, u_norm = x_sq.sqrt(), u_sq.sqrt().clamp_min(self.ns_epsilon)
             kidx = torch.tensor(hb_k, device=dev)
@@ -235,7 +242,10 @@ class ShardedOptimizer:
             new_sq = torch.zeros_like(x_sq)
             new_sq.index_add_(0, kidx, torch.stack(torch._foreach_norm(hb_x)).square())
             if eng.mesh.fsdp > 1:
+                keep = new_sq[self.local_norm_idx].clone() if self.local_norm_idx is not None else None
                 du.all_reduce_sum(new_sq, group=eng.mesh.fsdp_group)
+                if keep is not None:
+                    new_sq[self.local_norm_idx] = keep
             scale = (x_norm / new_sq.sqrt().clamp_min(self.ns_epsilon))[kidx]
             torch._foreach_mul_(hb_x, list(scale.unbind(0)))
         eng.mark_params_updated()

@@ -625,9 +625,15 @@ class FSDPEngine:
         keep = (not rank0_only) or self.mesh.rank == 0
         for g in self.groups():
             full = self._gather_master(g.master, g)
-            if keep:
-                for s in g.specs:
-                    t = full[s.offset:s.offset + s.numel].view(s.shape)
+            ep = getattr(g, "ep_local", False) and self.mesh.ep > 1
+            for s in g.specs:
+                t = full[s.offset:s.offset + s.numel].view(s.shape)
+                if ep:
+                    # every rank owns different experts: concatenate the slabs along the expert dim
+                    parts = [torch.empty_like(t) for _ in range(self.mesh.ep)]
+                    torch.distributed.all_gather(parts, t.contiguous(), group=self.mesh.ep_group)
+                    t = torch.cat(parts, dim=0)
+                if keep:
                     out[s.name] = (t.to(dtype) if dtype else t).cpu().clone()
             del full
         # tied / duplicate names (e.g. lm_head.weight tied to wte.weight) and buffers
@@ -656,7 +662,11 @@ class FSDPEngine:
                 if s.name not in sd:
                     missing.append(s.name)
                     continue
-                src = sd[s.name].reshape(-1)[lo:hi]
+                t = sd[s.name]
+                if getattr(g, "ep_local", False) and self.mesh.ep > 1:
+                    n_local = s.shape[0]
+                    t = t[self.mesh.ep_rank * n_local:(self.mesh.ep_rank + 1) * n_local]
+                src = t.reshape(-1)[lo:hi]
                 g.master[slo:slo + hi - lo].copy_(src.to(torch.float32))
             g.lp_stale = True
         if strict and missing:

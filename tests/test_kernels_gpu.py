@@ -232,3 +232,26 @@ def test_model_deferred_residual_matches_generic_path():
     assert _rel(out, out2) < 2e-2
     for n, p in m.named_parameters():
         assert _rel(g1[n], p.grad) < 5e-2, n
+
+
+@pytest.mark.parametrize("Bn,M,N,K,mode", [(5, 256, 256, 1024, 0), (3, 200, 136, 264, 0), (7, 256, 1024, 256, 1), (2, 384, 520, 136, 1)])
+def test_gemm_batched(Bn, M, N, K, mode):
+    torch.manual_seed(11)
+    a = (torch.randn(Bn, M, K, device="cuda") * 0.3).bfloat16()
+    b = (torch.randn(Bn, N, K, device="cuda") * 0.3).bfloat16() if mode == 0 else (torch.randn(Bn, K, N, device="cuda") * 0.3).bfloat16()
+    c = torch.randn(Bn, M, N, device="cuda").bfloat16()
+    out = _ext().gemm_bf16_batched(a, b, mode, 0.5, 2.0, c)
+    ref = 0.5 * torch.bmm(a.float(), b.float().transpose(1, 2) if mode == 0 else b.float()) + 2.0 * c.float()
+    torch.cuda.synchronize()
+    assert _ext().device_status() == 0
+    assert _rel(out, ref) < 1e-2
+
+
+def test_newton_schulz_batched_matches_per_matrix():
+    torch.manual_seed(12)
+    G = torch.randn(6, 256, 1024, device="cuda")
+    O = ops.newton_schulz(G)
+    R = torch.stack([ops.newton_schulz(g) for g in G])
+    assert _rel(O, R) < 2e-2
+    Gt = torch.randn(4, 1024, 256, device="cuda")          # tall: transposed internally
+    assert _rel(ops.newton_schulz(Gt), ops.newton_schulz_ref(Gt)) < 0.1
