@@ -98,9 +98,11 @@ int b200_reduce_scatter_pull_bf16(const void* const* bases, size_t full_off, voi
                                   int world, int max_ctas, cudaStream_t stream);
 
 // Expert-parallel dispatch (owners pull their experts' rows from every rank's send buffer) and return.
-int b200_ep_dispatch(const void* const* bases, size_t off_counts, size_t off_offsets, size_t off_table, size_t off_send,
-                     size_t off_recv, int rank, int world, int e_local, int C, int recv_cap, int* recv_offsets, int* status,
-                     cudaStream_t stream);
+int b200_ep_plan(const void* const* bases, size_t off_counts, size_t off_table, int rank, int world, int e_local,
+                 int recv_cap, int* recv_offsets, int* status, cudaStream_t stream);
+int b200_ep_pull(const void* const* bases, size_t off_counts, size_t off_offsets, size_t off_table, size_t off_send,
+                 void* recv_local, int rank, int world, int e_local, int C, int recv_cap, const int* recv_offsets,
+                 cudaStream_t stream);
 int b200_ep_return(const void* const* bases, size_t off_counts, size_t off_offsets, size_t off_table, size_t off_result,
                    void* dst, int rank, int world, int e_local, int C, cudaStream_t stream);
 

@@ -246,7 +246,8 @@ namespace b200 {
 
 struct EpArgs {
   const void* peer[8];
-  size_t off_counts, off_offsets, off_table, off_send, off_recv;   // heap offsets (same on every rank)
+  size_t off_counts, off_offsets, off_table, off_send;   // heap offsets (same on every rank)
+  char* recv_local;        // destination of the pulled rows (local memory, recv_cap rows)
   int rank, world, e_local, C, recv_cap;
 };
 
@@ -290,8 +291,9 @@ __global__ void __launch_bounds__(256) ep_pull_kernel(EpArgs a, const int* __res
   const int dst_row = table[s * a.e_local + el];
   const int vec_per_row = a.C / 8;
   const uint4* src = reinterpret_cast<const uint4*>(src_base + a.off_send) + static_cast<size_t>(src_row) * vec_per_row;
-  uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(const_cast<void*>(a.peer[a.rank])) + a.off_recv) +
-               static_cast<size_t>(dst_row) * vec_per_row;
+  // second guard (the host refuses to launch this kernel when the plan exceeds the capacity)
+  if (recv_offsets[a.e_local] > a.recv_cap || dst_row + cnt > a.recv_cap) return;
+  uint4* dst = reinterpret_cast<uint4*>(a.recv_local) + static_cast<size_t>(dst_row) * vec_per_row;
   const size_t total = static_cast<size_t>(cnt) * vec_per_row;
   constexpr int U = 8;
   for (size_t i0 = (blockIdx.z * static_cast<size_t>(blockDim.x)) * U + threadIdx.x; i0 < total;
@@ -305,7 +307,7 @@ __global__ void __launch_bounds__(256) ep_pull_kernel(EpArgs a, const int* __res
   if (s == a.world - 1) {
     const size_t pad_begin = static_cast<size_t>(dst_row + cnt) * vec_per_row;
     const size_t pad_end = static_cast<size_t>(recv_offsets[el + 1]) * vec_per_row;
-    uint4* base = reinterpret_cast<uint4*>(static_cast<char*>(const_cast<void*>(a.peer[a.rank])) + a.off_recv);
+    uint4* base = reinterpret_cast<uint4*>(a.recv_local);
     for (size_t i = pad_begin + blockIdx.z * static_cast<size_t>(blockDim.x) + threadIdx.x; i < pad_end;
          i += static_cast<size_t>(gridDim.z) * blockDim.x)
       base[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -340,20 +342,31 @@ __global__ void __launch_bounds__(256) ep_return_kernel(EpArgs a, size_t off_res
 }  // namespace b200
 
 static b200::EpArgs make_ep(const void* const* bases, size_t off_counts, size_t off_offsets, size_t off_table, size_t off_send,
-                            size_t off_recv, int rank, int world, int e_local, int C, int recv_cap) {
+                            void* recv_local, int rank, int world, int e_local, int C, int recv_cap) {
   b200::EpArgs a;
   for (int i = 0; i < 8; ++i) a.peer[i] = i < world ? bases[i] : nullptr;
-  a.off_counts = off_counts; a.off_offsets = off_offsets; a.off_table = off_table; a.off_send = off_send; a.off_recv = off_recv;
+  a.off_counts = off_counts; a.off_offsets = off_offsets; a.off_table = off_table; a.off_send = off_send;
+  a.recv_local = static_cast<char*>(recv_local);
   a.rank = rank; a.world = world; a.e_local = e_local; a.C = C; a.recv_cap = recv_cap;
   return a;
 }
 
-extern "C" int b200_ep_dispatch(const void* const* bases, size_t off_counts, size_t off_offsets, size_t off_table,
-                                size_t off_send, size_t off_recv, int rank, int world, int e_local, int C, int recv_cap,
-                                int* recv_offsets, int* status, cudaStream_t st) {
-  if (world > 8 || e_local > 256 || C % 8) return -1;
-  b200::EpArgs a = make_ep(bases, off_counts, off_offsets, off_table, off_send, off_recv, rank, world, e_local, C, recv_cap);
+// Step 1: layout of the rows this rank will receive (recv_offsets[e_local+1], 128-aligned) and the table
+// its peers read to find their results.  The caller reads recv_offsets[e_local] to size its buffers.
+extern "C" int b200_ep_plan(const void* const* bases, size_t off_counts, size_t off_table, int rank, int world, int e_local,
+                            int recv_cap, int* recv_offsets, int* status, cudaStream_t st) {
+  if (world > 8 || e_local > 256) return -1;
+  b200::EpArgs a = make_ep(bases, off_counts, 0, off_table, 0, nullptr, rank, world, e_local, 8, recv_cap);
   b200::ep_plan_kernel<<<1, 256, 0, st>>>(a, recv_offsets, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// Step 2: pull the rows into `recv_local` (recv_cap rows of C bf16).
+extern "C" int b200_ep_pull(const void* const* bases, size_t off_counts, size_t off_offsets, size_t off_table, size_t off_send,
+                            void* recv_local, int rank, int world, int e_local, int C, int recv_cap,
+                            const int* recv_offsets, cudaStream_t st) {
+  if (world > 8 || e_local > 256 || C % 8) return -1;
+  b200::EpArgs a = make_ep(bases, off_counts, off_offsets, off_table, off_send, recv_local, rank, world, e_local, C, recv_cap);
   b200::ep_pull_kernel<<<dim3(e_local, world, 8), 256, 0, st>>>(a, recv_offsets);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
@@ -361,7 +374,7 @@ extern "C" int b200_ep_dispatch(const void* const* bases, size_t off_counts, siz
 extern "C" int b200_ep_return(const void* const* bases, size_t off_counts, size_t off_offsets, size_t off_table,
                               size_t off_result, void* dst, int rank, int world, int e_local, int C, cudaStream_t st) {
   if (world > 8 || C % 8) return -1;
-  b200::EpArgs a = make_ep(bases, off_counts, off_offsets, off_table, 0, 0, rank, world, e_local, C, 0);
+  b200::EpArgs a = make_ep(bases, off_counts, off_offsets, off_table, 0, nullptr, rank, world, e_local, C, 0);
   b200::ep_return_kernel<<<dim3(e_local * world, 4), 256, 0, st>>>(a, off_result, static_cast<uint4*>(dst));
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

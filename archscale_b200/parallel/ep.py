@@ -115,19 +115,25 @@ class PeerDispatcher:
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.rows_cap, self.C, self.E = rows_cap, C, n_experts
         self.e_local = n_experts // self.world
-        self.recv_cap = rows_cap * 2                          # capacity factor 2 over the balanced load
+        # Rows one rank may have to process.  Routing is not balanced (least of all at initialisation), so
+        # the default covers the worst case (every token of every rank lands here); lower it with
+        # ARCHSCALE_B200_EP_CAPACITY=<factor over the balanced load> to save memory — an overflow is
+        # detected before anything is copied and raises.
+        import os
+        factor = float(os.environ.get("ARCHSCALE_B200_EP_CAPACITY", self.world))
+        self.recv_cap = ((int(rows_cap * min(factor, self.world)) + 127) // 128) * 128
         row_bytes = C * 2
-        need = 2 * rows_cap * row_bytes + 2 * self.recv_cap * row_bytes + 16 * (n_experts + 1) * 4 + (1 << 20)
+        need = 2 * rows_cap * row_bytes + self.recv_cap * row_bytes + 16 * (n_experts + 1) * 4 + (1 << 20)
         self.heap = SymmetricHeap(group, need, device)
         self.ext = self.heap.ext
         a = self.heap.alloc
         self.off_send = [a(rows_cap * row_bytes) for _ in range(2)]        # [0] activations out, [1] results back
-        self.off_recv = [a(self.recv_cap * row_bytes) for _ in range(2)]    # [0] rows received, [1] expert outputs
+        self.off_result = a(self.recv_cap * row_bytes)                      # expert outputs, pulled back by the sources
         self.off_counts = a(n_experts * 4)
         self.off_offsets = a((n_experts + 1) * 4)
         self.off_table = a(self.world * self.e_local * 4)                    # where (src, local expert) starts in my recv
         self.send = [self.heap.tensor(o, (rows_cap, C), torch.bfloat16) for o in self.off_send]
-        self.recv = [self.heap.tensor(o, (self.recv_cap, C), torch.bfloat16) for o in self.off_recv]
+        self.result = self.heap.tensor(self.off_result, (self.recv_cap, C), torch.bfloat16)
         self.counts = self.heap.tensor(self.off_counts, (n_experts,), torch.int32)
         self.offsets = self.heap.tensor(self.off_offsets, (n_experts + 1,), torch.int32)
         self.table = self.heap.tensor(self.off_table, (self.world, self.e_local), torch.int32)
@@ -135,6 +141,19 @@ class PeerDispatcher:
 
     def exchange(self) -> None:
         self.heap.barrier(self.chan)
+
+    def receive(self, e_local: int) -> tuple:
+        """Plan + pull: returns (rows received [used, C] in local memory, recv_offsets).  One 4-byte
+        device→host read sizes the buffers exactly (the reference reads all counts per layer)."""
+        recv_off = self.ext.ep_plan(self.heap.bases, self.off_counts, self.off_table, self.rank, e_local, self.recv_cap)
+        used = int(recv_off[-1].item())
+        if used > self.recv_cap:
+            raise RuntimeError(f"expert-parallel receive overflow: {used} rows > capacity {self.recv_cap}; "
+                               "raise ARCHSCALE_B200_EP_CAPACITY")
+        rows = torch.empty(max(used, 128), self.C, dtype=torch.bfloat16, device=self.device)
+        self.ext.ep_pull(self.heap.bases, self.off_counts, self.off_offsets, self.off_table, self.off_send[0], rows,
+                         self.rank, e_local, recv_off)
+        return rows, recv_off
 
 
 class _EPPeerFn(torch.autograd.Function):
@@ -155,18 +174,16 @@ class _EPPeerFn(torch.autograd.Function):
         d.offsets.copy_(offsets)
         ext.gather_rows(h, slot_pair, None, K, offsets, d.send[0])
         d.exchange()                                                       # every rank's rows and counts are published
-        recv_off = ext.ep_dispatch(d.heap.bases, d.off_counts, d.off_offsets, d.off_table, d.off_send[0], d.off_recv[0],
-                                   d.rank, E_l, C, d.recv_cap)
-        xr = d.recv[0]
+        xr, recv_off = d.receive(E_l)
         h1 = ext.grouped_gemm_bf16(0, xr, w_in.reshape(E_l * I2, C), recv_off, 0, I2, C)
         a = ext.swiglu_packed_fwd(h1)
-        ext.grouped_gemm_bf16(0, a, w_out.reshape(E_l * C, I), recv_off, 0, C, I, None, d.recv[1])
+        ext.grouped_gemm_bf16(0, a, w_out.reshape(E_l * C, I), recv_off, 0, C, I, None, d.result)
         d.exchange()                                                       # expert outputs are ready everywhere
         yb = torch.empty(slot_pair.numel(), C, dtype=h.dtype, device=h.device)
-        ext.ep_return(d.heap.bases, d.off_counts, d.off_offsets, d.off_table, d.off_recv[1], yb, d.rank, E_l, C)
+        ext.ep_return(d.heap.bases, d.off_counts, d.off_offsets, d.off_table, d.off_result, yb, d.rank, E_l, C)
         out = ext.combine_rows(yb, pair_slot, sc, N, K)
         backend.count_launch(14)
-        ctx.save_for_backward(xr.clone(), h1, yb, w_in, w_out, sc, counts, offsets, slot_pair, pair_slot)
+        ctx.save_for_backward(xr, h1, yb, w_in, w_out, sc, counts, offsets, slot_pair, pair_slot)
         ctx.meta = (N, C, K, E_l, I2, I, n_experts, group, scores.dtype)
         ctx.w_refs = (w_in, w_out)
         return out
@@ -183,27 +200,25 @@ class _EPPeerFn(torch.autograd.Function):
         d.offsets.copy_(offsets)
         ext.gather_rows(dout, slot_pair, sc.reshape(-1), K, offsets, d.send[0])      # dy[slot] = score · dout[token]
         d.exchange()
-        recv_off = ext.ep_dispatch(d.heap.bases, d.off_counts, d.off_offsets, d.off_table, d.off_send[0], d.off_recv[0],
-                                   d.rank, E_l, C, d.recv_cap)
-        dyr = d.recv[0]
+        dyr, recv_off = d.receive(E_l)
         a = ext.swiglu_packed_fwd(h1)
         da = ext.grouped_gemm_bf16(1, dyr, w_out.reshape(E_l * C, I), recv_off, 0, I, C)
         mg_out = getattr(ctx.w_refs[1], "main_grad", None)
         dw_out = ext.grouped_gemm_bf16(2, dyr, a, recv_off, C, I, 0, mg_out)
         dh = ext.swiglu_packed_bwd(h1, da)
-        ext.grouped_gemm_bf16(1, dh, w_in.reshape(E_l * I2, C), recv_off, 0, C, I2, None, d.recv[1])
+        ext.grouped_gemm_bf16(1, dh, w_in.reshape(E_l * I2, C), recv_off, 0, C, I2, None, d.result)
         mg_in = getattr(ctx.w_refs[0], "main_grad", None)
         dw_in = ext.grouped_gemm_bf16(2, dh, xr, recv_off, I2, C, 0, mg_in)
         d.exchange()
         dxs = torch.empty(slot_pair.numel(), C, dtype=dout.dtype, device=dout.device)
-        ext.ep_return(d.heap.bases, d.off_counts, d.off_offsets, d.off_table, d.off_recv[1], dxs, d.rank, E_l, C)
+        ext.ep_return(d.heap.bases, d.off_counts, d.off_offsets, d.off_table, d.off_result, dxs, d.rank, E_l, C)
         dx = ext.combine_rows(dxs, pair_slot, None, N, K)
         backend.count_launch(14)
         return dx, (None if mg_in is not None else dw_in), (None if mg_out is not None else dw_out), dscores, None, None, None
 
 
 def peer_path_supported(h, w_in, w_out) -> bool:
-    return (h.is_cuda and h.dtype == torch.bfloat16 and w_in.dtype == torch.bfloat16 and backend.has("ep_dispatch")
+    return (h.is_cuda and h.dtype == torch.bfloat16 and w_in.dtype == torch.bfloat16 and backend.has("ep_pull")
             and h.shape[1] % 64 == 0 and w_in.shape[1] % 64 == 0 and w_out.shape[2] % 64 == 0)
 
 
