@@ -456,7 +456,7 @@ class GPT(nn.Module):
 
     def build_rope_cache(self, idx: torch.Tensor, seq_len: int):
         cfg = self.config
-        return ops.build_rope_cache(seq_len, int(cfg.rotary_percentage * cfg.head_size), torch.bfloat16, idx.device,
+        return ops.build_rope_cache(seq_len, int(cfg.rotary_percentage * cfg.head_size), self.compute_dtype, idx.device,
                                     base=cfg.rope_base, scaling_factor=cfg.scaling_factor)
 
     # -- forward -------------------------------------------------------------------------

@@ -22,8 +22,8 @@ class Linear(nn.Linear):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         w, b = self.weight, self.bias
         g = getattr(w, "_fsdp_group", None)
-        if g is not None and getattr(g, "ag_pending", False) and not (
-                w._fsdp_first and x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
+        if g is not None and getattr(g, "ag_pending", False) and (self.mxfp8 or not (
+                w._fsdp_first and x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16)):
             w._fsdp_engine.finish_pending_gather(g)
         if w.dtype != x.dtype:
             w = w.to(x.dtype)

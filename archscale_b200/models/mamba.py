@@ -95,10 +95,8 @@ class Mamba(nn.Module):
             dt, Bm, Cm = self.dt_layernorm(dt), self.b_layernorm(Bm), self.c_layernorm(Cm)
         dt = F.linear(dt, self.dt_proj.weight.to(dt.dtype))    # bias is added inside the scan (fp32)
         A = -torch.exp(self.A_log.float())
-        y = ops.selective_scan(
-            x.transpose(1, 2), dt.transpose(1, 2), A, Bm.transpose(1, 2), Cm.transpose(1, 2), self.D.float(),
-            z=None if self.gmu_save else z.transpose(1, 2), delta_bias=self.dt_proj.bias.float(),
-            delta_softplus=True, cu_seqlens=cu).transpose(1, 2)
+        y = ops.selective_scan(x, dt, A, Bm, Cm, self.D.float(), z=None if self.gmu_save else z,
+                               delta_bias=self.dt_proj.bias.float(), delta_softplus=True, cu_seqlens=cu, channel_last=True)
         if self.gmu_save:
             gmu_mems = y
             y = ops.swiglu(z.contiguous(), y.contiguous())

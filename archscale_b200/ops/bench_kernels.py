@@ -1,7 +1,7 @@
 """Per-kernel microbenchmarks against the measured roofline (``MEASURED_PEAKS.json``) and the
 library kernel doing the same op.  CUDA-event timing, warm-up, L2 flushed between iterations.
 
-    python -m archscale_b200.ops.bench_kernels gemm rmsnorm swiglu ce rope attn     # any subset
+    python -m archscale_b200.ops.bench_kernels gemm rmsnorm swiglu ce rope attn mamba    # any subset
     python -m archscale_b200.ops.bench_kernels gemm --json out.json
 """
 from __future__ import annotations
@@ -175,8 +175,47 @@ def bench_attn(res: list) -> None:
         print(res[-1], flush=True)
 
 
+def bench_mamba(res: list) -> None:
+    """Causal conv1d and selective scan at the Mamba-1 shapes of the SambaY / Phi-4-mini-flash family."""
+    pk = peaks()
+    for (B, L, Di, what) in [(1, 8192, 5120, "phi4-mini-flash d_inner"), (8, 4096, 4096, "d16-class d_inner")]:
+        N = 16
+        xz = torch.randn(B, L, 2 * Di, device="cuda").bfloat16()
+        x, z = xz[..., :Di], xz[..., Di:]
+        w, b = torch.randn(Di, 4, device="cuda"), torch.randn(Di, device="cuda")
+        f = lambda: ops.causal_conv1d(x, w, b, activation="silu", channel_last=True)
+        t = time_ms(f)
+        by = 2 * x.numel() * 2
+        res.append({"kernel": "causal_conv1d_fwd", "what": what, "shape": [B, L, Di], "ms": t, "gbs": by / t / 1e6,
+                    "frac_of_" + pk["kind"] + "_hbm": by / t / 1e6 / pk["hbm_gbs"]})
+        print(res[-1], flush=True)
+        xr = x.detach().contiguous().requires_grad_()
+        wr = w.clone().requires_grad_()
+        y = ops.causal_conv1d(xr, wr, b, activation="silu", channel_last=True)
+        g = torch.randn_like(y)
+        t = time_ms(lambda: torch.autograd.grad(y, (xr, wr), g, retain_graph=True))
+        res.append({"kernel": "causal_conv1d_bwd", "what": what, "shape": [B, L, Di], "ms": t, "gbs": 3 * x.numel() * 2 / t / 1e6})
+        print(res[-1], flush=True)
+        u = torch.randn(B, L, Di, device="cuda").bfloat16().requires_grad_()
+        delta = (torch.randn(B, L, Di, device="cuda") * 0.5).bfloat16().requires_grad_()
+        Bm = torch.randn(B, L, N, device="cuda").bfloat16().requires_grad_()
+        Cm = torch.randn(B, L, N, device="cuda").bfloat16().requires_grad_()
+        A = (-torch.exp(torch.rand(Di, N, device="cuda"))).requires_grad_()
+        D, bias = torch.randn(Di, device="cuda").requires_grad_(), torch.randn(Di, device="cuda").requires_grad_()
+        zz = z.detach().contiguous().requires_grad_()
+        f = lambda: ops.selective_scan(u, delta, A, Bm, Cm, D, z=zz, delta_bias=bias, delta_softplus=True, channel_last=True)
+        t_f = time_ms(f)
+        y = f()
+        g = torch.randn_like(y)
+        t_b = time_ms(lambda: torch.autograd.grad(y, (u, delta, A, Bm, Cm, D, zz, bias), g, retain_graph=True), iters=5)
+        by_f, by_b = 4 * u.numel() * 2, 8 * u.numel() * 2
+        res.append({"kernel": "selective_scan", "what": what, "shape": [B, L, Di, N], "fwd_ms": t_f, "fwd_gbs": by_f / t_f / 1e6,
+                    "bwd_ms": t_b, "bwd_gbs": by_b / t_b / 1e6, "steps_per_s": B * L * Di * N / t_f / 1e-3})
+        print(res[-1], flush=True)
+
+
 ALL = {"gemm": bench_gemm, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "ce": bench_ce, "rope": bench_rope,
-       "attn": bench_attn}
+       "attn": bench_attn, "mamba": bench_mamba}
 
 
 def main() -> None:

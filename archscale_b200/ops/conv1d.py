@@ -40,37 +40,44 @@ def causal_conv1d_ref(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torc
     return y.to(x.dtype)
 
 
+def _rows(t: torch.Tensor) -> torch.Tensor:
+    if t.stride(2) == 1 and t.stride(1) % 8 == 0 and (t.size(0) == 1 or t.stride(0) == t.size(1) * t.stride(1)) \
+            and t.data_ptr() % 16 == 0:
+        return t
+    return t.contiguous()
+
+
 class _ConvFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, seq_idx, silu):
         ext = backend.require_extension()
-        y = ext.causal_conv1d_fwd(x, weight, bias, seq_idx, silu)
+        x = _rows(x)
+        wf = weight.float().contiguous()
+        bf = None if bias is None else bias.float().contiguous()
+        y = ext.causal_conv1d_fwd(x, wf, bf, seq_idx, silu)
         backend.count_launch()
-        ctx.save_for_backward(x, weight, bias if bias is not None else torch.empty(0),
+        ctx.save_for_backward(x, wf, bf if bf is not None else torch.empty(0),
                               seq_idx if seq_idx is not None else torch.empty(0))
         ctx.silu, ctx.has_bias, ctx.has_seq = silu, bias is not None, seq_idx is not None
+        ctx.wdtype, ctx.bdtype = weight.dtype, (None if bias is None else bias.dtype)
         return y
 
     @staticmethod
     def backward(ctx, dy):
         ext = backend.require_extension()
-        x, weight, bias, seq_idx = ctx.saved_tensors
-        dx, dw, db = ext.causal_conv1d_bwd(dy, x, weight, bias if ctx.has_bias else None,
+        x, wf, bf, seq_idx = ctx.saved_tensors
+        dx, dw, db = ext.causal_conv1d_bwd(_rows(dy), x, wf, bf if ctx.has_bias else None,
                                            seq_idx if ctx.has_seq else None, ctx.silu)
         backend.count_launch()
-        return dx, dw.to(weight.dtype), (db.to(bias.dtype) if ctx.has_bias else None), None, None
+        return dx, dw.to(ctx.wdtype), (db.to(ctx.bdtype) if ctx.has_bias else None), None, None
 
 
 def causal_conv1d(x, weight, bias=None, seq_idx=None, activation: Optional[str] = None, channel_last: bool = False):
     """x:(B,C,L), or (B,L,C) when ``channel_last`` (the kernel's native layout); returns the same layout."""
-    if channel_last:
-        xl = x
-    else:
-        xl = x.transpose(1, 2)
-    if (backend.has("causal_conv1d_fwd") and xl.dtype in (torch.bfloat16, torch.float32) and weight.shape[1] <= 4 and xl.shape[-1] % 8 == 0
-            and backend.use_cuda_kernel("conv1d", xl, weight)):
-        y = _ConvFn.apply(xl.contiguous(), weight.contiguous(), bias,
-                          None if seq_idx is None else seq_idx.to(torch.int32).contiguous(),
+    xl = x if channel_last else x.transpose(1, 2)
+    if (backend.has("causal_conv1d_fwd") and xl.dtype in (torch.bfloat16, torch.float32) and 2 <= weight.shape[1] <= 4
+            and xl.shape[-1] % 8 == 0 and backend.use_cuda_kernel("conv1d", xl, weight)):
+        y = _ConvFn.apply(xl, weight, bias, None if seq_idx is None else seq_idx.to(torch.int32).contiguous(),
                           activation in ("silu", "swish"))
         return y if channel_last else y.transpose(1, 2)
     y = causal_conv1d_ref(xl.transpose(1, 2), weight, bias, seq_idx, activation)

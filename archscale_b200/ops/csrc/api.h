@@ -106,6 +106,28 @@ int b200_ep_pull(const void* const* bases, size_t off_counts, size_t off_offsets
 int b200_ep_return(const void* const* bases, size_t off_counts, size_t off_offsets, size_t off_table, size_t off_result,
                    void* dst, int rank, int world, int e_local, int C, cudaStream_t stream);
 
+// Depthwise causal conv1d (+SiLU) on token-major rows (conv1d.cu); dw [C,W], db [C] fp32 must be zero on entry.
+int b200_conv1d_fwd(const void* x, int dtype, const float* w, const float* bias, const int* seq_idx, void* y, int B, int L, int C,
+                    int W, int silu, int xs, cudaStream_t st);
+int b200_conv1d_bwd(const void* dy, const void* x, int dtype, const float* w, const float* bias, const int* seq_idx, void* dx,
+                    float* dw, float* db, int B, int L, int C, int W, int silu, int xs, int dys, cudaStream_t st);
+// Mamba-1 selective scan (selective_scan.cu), 16 states per channel, token-major.
+int b200_selective_scan_ckpt_segments(int L);
+int b200_selective_scan_fwd(const void* u, int su, const void* delta, int sd, const float* A, const void* Bm, int sB,
+                            const void* Cm, int sC, const float* D, const void* z, int sz, const float* dbias, const int* reset,
+                            void* y, float* ckpt, int dtype, int B, int L, int Di, int softplus, cudaStream_t st);
+int b200_selective_scan_bwd(const void* dy, int sdy, const void* u, int su, const void* delta, int sd, const float* A,
+                            const void* Bm, int sB, const void* Cm, int sC, const float* D, const void* z, int sz,
+                            const float* dbias, const int* reset, const float* ckpt, void* du, void* ddelta, void* dz, float* dA,
+                            float* dBf, float* dCf, float* dD, float* ddbias, int dtype, int B, int L, int Di, int softplus,
+                            cudaStream_t st);
+
+// Block-scaled MXFP8 (gemm_mxfp8.cu): quantisers and the tcgen05 block-scaled GEMM.
+size_t b200_mxfp8_sf_bytes(int rows, int K);
+int b200_mxfp8_quantize(const void* x, int ld, void* q, void* sf, int R, int C, int colwise, cudaStream_t st);
+int b200_gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, void* out, int M, int N, int K, int lda,
+                    int ldb, int ldc, float alpha, int out_f32, int accumulate, int num_sms, int* status, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,405 @@
+// Block-scaled MXFP8 (OCP microscaling: e4m3 elements, one E8M0 scale per 32 elements along K) on the
+// 5th-generation tensor cores:  out[M,N] = alpha · (A ⊙ sfA) · (B ⊙ sfB)ᵀ, both operands K-major.
+//
+//   quantisers   bf16 → e4m3 + E8M0, row-wise (blocks along the contiguous dimension) or column-wise (the
+//                transposed operand is written, blocks along the original rows), so that forward, dgrad and
+//                wgrad of a linear layer are all "NT" GEMMs over K-major fp8 operands.
+//   GEMM         persistent warp-specialised kernel (TMA producer / MMA issuer / 4 epilogue warps) issuing
+//                tcgen05.mma.kind::mxf8f6f4.block_scale, tile 128 × 192 × 128, 5-stage ring, two TMEM
+//                accumulators (2 × 192 columns) so the epilogue of a tile overlaps the next main loop.
+//
+// Scale factors are stored in global memory in the order the tensor core wants them in TMEM, in 512-byte
+// chunks that cover 128 rows × 4 K-blocks:  byte (m % 32)·16 + ((m / 32) % 4)·4 + (kb % 4) of chunk
+// (m / 128, kb / 4).  A chunk is fetched with one bulk copy and moved to tensor memory with one
+// tcgen05.cp.32x128b.warpx4: lane m % 32 of every lane quarter, column (m / 32) % 4, byte kb % 4.
+// A 192-wide B tile starts at a multiple of 64 rows; when that is the middle of a chunk the MMA is given
+// the scale address two columns further (rows 64.. of the first chunk), and two chunks are always loaded.
+#include <cuda_fp8.h>
+
+#include "api.h"
+#include "sm100.cuh"
+
+namespace b200 {
+
+constexpr int QBM = 128, QBN = 192, QBK = 128, QSTAGES = 5;
+constexpr int QA_BYTES = QBM * QBK, QB_BYTES = QBN * QBK;
+constexpr int QSFA_OFF = QA_BYTES + QB_BYTES, QSFB_OFF = QSFA_OFF + 512;
+constexpr int QSTAGE_BYTES = 43008;                               // 42 KiB: keeps every stage 1024-byte aligned
+constexpr int QSMEM_BYTES = QSTAGES * QSTAGE_BYTES + 1024 + 256;
+constexpr int Q_TMEM_SFA = 384, Q_TMEM_SFB = 392;                 // columns after the two accumulators
+constexpr int Q_GROUP_M = 16;
+
+struct QGemmParams {
+  void* out;
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  int M, N, K, ldc;
+  float alpha;
+  int accumulate;
+  int* status;
+};
+
+__device__ __forceinline__ void q_bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+// Unswizzled K-major descriptor of a 32-row × 16-byte scale chunk: 8-row groups are 128 bytes apart.
+__device__ __forceinline__ uint64_t make_sf_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(128 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  return d;
+}
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void umma_mxf8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t tsfa,
+                                          uint32_t tsfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n" ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb)
+      : "memory");
+}
+// e4m3 × e4m3, E8M0 scales, fp32 accumulate, both operands K-major
+__host__ __device__ constexpr uint32_t make_idesc_mxf8(int M, int N) {
+  return (static_cast<uint32_t>(N >> 3) << 17) | (1u << 23) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+template <int OUT_F32>
+__global__ void __launch_bounds__(192, 1)
+gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const QGemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + QSTAGES * QSTAGE_BYTES);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + QSTAGES;
+  uint64_t* tmem_full = bars + 2 * QSTAGES;
+  uint64_t* tmem_empty = bars + 2 * QSTAGES + 2;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 2 * QSTAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cta = blockIdx.x, n_cta = gridDim.x;
+  const int num_m = (p.M + QBM - 1) / QBM, num_n = (p.N + QBN - 1) / QBN;
+  const int num_tiles = num_m * num_n;
+  const int KC = p.K / QBK;                      // K chunks of 128 elements = 4 scale blocks
+  const int n_chunks_n = (p.N + 127) / 128;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < QSTAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 4); }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) { tmem_alloc(tmem_ptr, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  auto tile_coords = [&](int t, int& m0, int& n0) {
+    const int per_group = Q_GROUP_M * num_n;
+    const int g = t / per_group, first_m = g * Q_GROUP_M;
+    const int gsz = min(num_m - first_m, Q_GROUP_M);
+    const int r = t - g * per_group;
+    m0 = (first_m + (r % gsz)) * QBM;
+    n0 = (r / gsz) * QBN;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      for (int t = cta; t < num_tiles; t += n_cta) {
+        int m0, n0; tile_coords(t, m0, n0);
+        const int c0 = n0 >> 7;                                  // first 128-row scale chunk of the B tile
+        const int nb = (c0 + 1 < n_chunks_n) ? 2 : 1;
+        for (int kb = 0; kb < KC; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) goto done;
+          uint8_t* sa = smem + stage * QSTAGE_BYTES;
+          mbar_arrive_expect_tx(&full_bar[stage], QA_BYTES + QB_BYTES + 512 + 512 * nb);
+          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * QBK, m0);
+          tma_load_2d(sa + QA_BYTES, &tmap_b, &full_bar[stage], kb * QBK, n0);
+          q_bulk_g2s(sa + QSFA_OFF, p.sfa + (static_cast<size_t>(m0 >> 7) * KC + kb) * 512, 512, &full_bar[stage]);
+          q_bulk_g2s(sa + QSFB_OFF, p.sfb + (static_cast<size_t>(c0) * KC + kb) * 512, 512, &full_bar[stage]);
+          if (nb == 2)
+            q_bulk_g2s(sa + QSFB_OFF + 512, p.sfb + (static_cast<size_t>(c0 + 1) * KC + kb) * 512, 512, &full_bar[stage]);
+          if (++stage == QSTAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc0 = make_idesc_mxf8(QBM, QBN);
+      int stage = 0; uint32_t phase = 0;
+      int it = 0;
+      for (int t = cta; t < num_tiles; t += n_cta, ++it) {
+        const int acc = it & 1; const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) goto done;
+        tc_fence_after();
+        int m0, n0; tile_coords(t, m0, n0);
+        const uint32_t d_tmem = tmem_base + acc * QBN;
+        const uint32_t tsfa = tmem_base + Q_TMEM_SFA;
+        const uint32_t tsfb = tmem_base + Q_TMEM_SFB + ((n0 >> 5) & 3);   // 0 or 2: rows 64.. of the first chunk
+        for (int kb = 0; kb < KC; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_FULL)) goto done;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * QSTAGE_BYTES);
+          tmem_cp_sf(tmem_base + Q_TMEM_SFA, make_sf_desc(sa + QSFA_OFF));
+          tmem_cp_sf(tmem_base + Q_TMEM_SFB, make_sf_desc(sa + QSFB_OFF));
+          tmem_cp_sf(tmem_base + Q_TMEM_SFB + 4, make_sf_desc(sa + QSFB_OFF + 512));
+          const uint64_t da = make_smem_desc(sa, 16, 1024);
+          const uint64_t db = make_smem_desc(sa + QA_BYTES, 16, 1024);
+#pragma unroll
+          for (uint32_t k = 0; k < QBK / 32; ++k) {
+            // K-block k of the stage: operands advance 32 bytes, the scale of byte k of each column is used
+            const uint32_t idesc = idesc0 | (k << 4) | (k << 29);
+            umma_mxf8(d_tmem, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2), idesc,
+                      tsfa | (k << 30), tsfb | (k << 30), (kb != 0 || k != 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == QSTAGES) { stage = 0; phase ^= 1; }
+        }
+        if (KC == 0) mbar_arrive(&tmem_full[acc]);
+        else umma_commit(&tmem_full[acc]);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    int it = 0;
+    for (int t = cta; t < num_tiles; t += n_cta, ++it) {
+      int m0, n0; tile_coords(t, m0, n0);
+      const int acc = it & 1; const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t taddr = tmem_base + acc * QBN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < QBN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (KC == 0) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r[e] = 0u;
+        }
+        const int col = n0 + c * 32;
+        if (row < p.M && col < p.N) {
+          if (OUT_F32) {
+            float* o = reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ldc + col;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (col + j < p.N) {
+                float4 v = make_float4(__uint_as_float(r[j]) * p.alpha, __uint_as_float(r[j + 1]) * p.alpha,
+                                       __uint_as_float(r[j + 2]) * p.alpha, __uint_as_float(r[j + 3]) * p.alpha);
+                if (p.accumulate) {
+                  const float4 old = *reinterpret_cast<const float4*>(o + j);
+                  v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                }
+                *reinterpret_cast<float4*>(o + j) = v;
+              }
+            }
+          } else {
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ldc + col;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col + j < p.N) {
+                uint4 ov;
+                ov.x = pack_bf16x2(__uint_as_float(r[j]) * p.alpha, __uint_as_float(r[j + 1]) * p.alpha);
+                ov.y = pack_bf16x2(__uint_as_float(r[j + 2]) * p.alpha, __uint_as_float(r[j + 3]) * p.alpha);
+                ov.z = pack_bf16x2(__uint_as_float(r[j + 4]) * p.alpha, __uint_as_float(r[j + 5]) * p.alpha);
+                ov.w = pack_bf16x2(__uint_as_float(r[j + 6]) * p.alpha, __uint_as_float(r[j + 7]) * p.alpha);
+                *reinterpret_cast<uint4*>(o + j) = ov;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+    }
+  }
+
+done:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------ quantisers
+// Smallest power of two ≥ amax / 448 as a biased E8M0 exponent (clamped to [1, 253]).
+__device__ __forceinline__ uint32_t e8m0_for_amax(float amax) {
+  const uint32_t b = __float_as_uint(__fdiv_rn(amax, 448.f));   // exact: powers of two must not round up
+  uint32_t ex = (b >> 23) & 0xffu;
+  if (b & 0x7fffffu) ex += 1;
+  return min(max(ex, 1u), 253u);
+}
+__device__ __forceinline__ size_t sf_offset(int row, int kb, int KC) {
+  return (static_cast<size_t>(row >> 7) * KC + (kb >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (kb & 3);
+}
+__device__ __forceinline__ uint32_t cvt4_e4m3(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
+// One thread per 32-element block of a row.  x: [R, C] bf16 (row stride ld), q: [R, C] e4m3, C % 128 == 0.
+__global__ void __launch_bounds__(256) mxfp8_quant_rowwise_kernel(const __nv_bfloat16* __restrict__ x, int ld,
+                                                                 uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int R, int C) {
+  const int nblk = C >> 5;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long long>(R) * nblk) return;
+  const int r = static_cast<int>(idx / nblk), kb = static_cast<int>(idx % nblk);
+  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * ld + kb * 32);
+  float v[32];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint4 u = src[i];
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = unpack_bf16x2(w[e]);
+      v[i * 8 + 2 * e] = f.x; v[i * 8 + 2 * e + 1] = f.y;
+      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+  }
+  const uint32_t ex = e8m0_for_amax(amax);
+  const float inv = __uint_as_float((254u - ex) << 23);
+  uint4* dst = reinterpret_cast<uint4*>(q + static_cast<size_t>(r) * C + kb * 32);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    uint4 o;
+    o.x = cvt4_e4m3(v[i * 16 + 0] * inv, v[i * 16 + 1] * inv, v[i * 16 + 2] * inv, v[i * 16 + 3] * inv);
+    o.y = cvt4_e4m3(v[i * 16 + 4] * inv, v[i * 16 + 5] * inv, v[i * 16 + 6] * inv, v[i * 16 + 7] * inv);
+    o.z = cvt4_e4m3(v[i * 16 + 8] * inv, v[i * 16 + 9] * inv, v[i * 16 + 10] * inv, v[i * 16 + 11] * inv);
+    o.w = cvt4_e4m3(v[i * 16 + 12] * inv, v[i * 16 + 13] * inv, v[i * 16 + 14] * inv, v[i * 16 + 15] * inv);
+    dst[i] = o;
+  }
+  sf[sf_offset(r, kb, nblk >> 2)] = static_cast<uint8_t>(ex);
+}
+
+// Column-wise: writes the transposed operand qT [C, R] with scale blocks along R.  R % 128 == 0, C % 64 == 0.
+__global__ void __launch_bounds__(256) mxfp8_quant_colwise_kernel(const __nv_bfloat16* __restrict__ x, int ld,
+                                                                 uint8_t* __restrict__ qT, uint8_t* __restrict__ sfT, int R, int C) {
+  __shared__ __nv_bfloat16 s[128][72];
+  const int r0 = blockIdx.y * 128, c0 = blockIdx.x * 64, tid = threadIdx.x;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int idx = tid + 256 * i, row = idx >> 3, cv = idx & 7;
+    const uint4 u = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(r0 + row) * ld + c0 + cv * 8);
+    *reinterpret_cast<uint4*>(&s[row][cv * 8]) = u;
+  }
+  __syncthreads();
+  const int c = tid & 63, rb = tid >> 6;
+  float v[32];
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) { v[j] = __bfloat162float(s[rb * 32 + j][c]); amax = fmaxf(amax, fabsf(v[j])); }
+  const uint32_t ex = e8m0_for_amax(amax);
+  const float inv = __uint_as_float((254u - ex) << 23);
+  uint4* dst = reinterpret_cast<uint4*>(qT + static_cast<size_t>(c0 + c) * R + r0 + rb * 32);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    uint4 o;
+    o.x = cvt4_e4m3(v[i * 16 + 0] * inv, v[i * 16 + 1] * inv, v[i * 16 + 2] * inv, v[i * 16 + 3] * inv);
+    o.y = cvt4_e4m3(v[i * 16 + 4] * inv, v[i * 16 + 5] * inv, v[i * 16 + 6] * inv, v[i * 16 + 7] * inv);
+    o.z = cvt4_e4m3(v[i * 16 + 8] * inv, v[i * 16 + 9] * inv, v[i * 16 + 10] * inv, v[i * 16 + 11] * inv);
+    o.w = cvt4_e4m3(v[i * 16 + 12] * inv, v[i * 16 + 13] * inv, v[i * 16 + 14] * inv, v[i * 16 + 15] * inv);
+    dst[i] = o;
+  }
+  sfT[sf_offset(c0 + c, (r0 >> 5) + rb, R >> 7)] = static_cast<uint8_t>(ex);
+}
+
+typedef CUresult (*EncodeTiledFnQ)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static int make_tmap_2d_u8(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                           uint32_t box_inner, uint32_t box_outer) {
+  static EncodeTiledFnQ fn = nullptr;
+  if (!fn) {
+    void* ptr_fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr_fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return -1;
+    fn = reinterpret_cast<EncodeTiledFnQ>(ptr_fn);
+  }
+  cuuint64_t gdim[2] = {inner, outer};
+  cuuint64_t gstride[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// Bytes of the scale buffer of an operand with `rows` rows and K elements per row (zero-fill it once: rows
+// beyond the operand inside the last 128-row chunk are never written by the quantisers).
+extern "C" size_t b200_mxfp8_sf_bytes(int rows, int K) { return static_cast<size_t>((rows + 127) / 128) * (K / 128) * 512; }
+
+extern "C" int b200_mxfp8_quantize(const void* x, int ld, void* q, void* sf, int R, int C, int colwise, cudaStream_t st) {
+  if (R <= 0 || C <= 0) return 0;
+  if (ld % 8) return -1;
+  if (!colwise) {
+    if (C % 128) return -1;
+    const long long total = static_cast<long long>(R) * (C / 32);
+    mxfp8_quant_rowwise_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(
+        (const __nv_bfloat16*)x, ld, (uint8_t*)q, (uint8_t*)sf, R, C);
+  } else {
+    if (R % 128 || C % 64) return -1;
+    mxfp8_quant_colwise_kernel<<<dim3(C / 64, R / 128), 256, 0, st>>>((const __nv_bfloat16*)x, ld, (uint8_t*)q, (uint8_t*)sf, R, C);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// out[M,N] = alpha · A[M,K] · B[N,K]ᵀ with e4m3 operands (row strides lda, ldb bytes) and chunked E8M0 scales.
+extern "C" int b200_gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, void* out, int M, int N, int K,
+                               int lda, int ldb, int ldc, float alpha, int out_f32, int accumulate, int num_sms, int* status,
+                               cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % QBK || lda % 16 || ldb % 16 || N % 8) return -1;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return -5;
+    ctx_bound = true;
+  }
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d_u8(&ta, A, K, M, lda, QBK, QBM);
+  if (rc) return rc;
+  rc = make_tmap_2d_u8(&tb, B, K, N, ldb, QBK, QBN);
+  if (rc) return rc;
+  QGemmParams p{out, (const uint8_t*)sfa, (const uint8_t*)sfb, M, N, K, ldc, alpha, accumulate, status};
+  const int tiles = ((M + QBM - 1) / QBM) * ((N + QBN - 1) / QBN);
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  static bool configured[2] = {false, false};
+  if (out_f32) {
+    if (!configured[1]) {
+      if (cudaFuncSetAttribute(gemm_mxfp8_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, QSMEM_BYTES) != cudaSuccess) return -2;
+      configured[1] = true;
+    }
+    gemm_mxfp8_kernel<1><<<grid, 192, QSMEM_BYTES, stream>>>(ta, tb, p);
+  } else {
+    if (!configured[0]) {
+      if (cudaFuncSetAttribute(gemm_mxfp8_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, QSMEM_BYTES) != cudaSuccess) return -2;
+      configured[0] = true;
+    }
+    gemm_mxfp8_kernel<0><<<grid, 192, QSMEM_BYTES, stream>>>(ta, tb, p);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

@@ -5,9 +5,9 @@ Behavioural reference: `lit_gpt/selective_scan_interface.py:102-168` (``selectiv
 ``Δ = softplus(Δ + bias)``; packed sequences reset ``h`` at every ``cu_seqlens`` boundary
 (the varlen fork used at `lit_gpt/mamba_simple.py:84-88`).
 
-CUDA path: ``csrc/selective_scan.cu`` — one CTA per (batch, channel block), chunked
-associative scan over L with the 16 states in registers, backward recomputes the chunk
-states from checkpoints saved by the forward.
+CUDA path: ``csrc/selective_scan.cu`` — one thread per (batch, channel, state), 64-step tiles staged
+through shared memory, state sums by warp shuffles; the backward recomputes each tile's states from
+the per-tile checkpoints saved by the forward and runs the adjoint recurrence in reverse.
 """
 from __future__ import annotations
 
@@ -52,43 +52,68 @@ def selective_scan_ref(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta
     return (y, h) if return_last_state else y
 
 
+def _rows(t: torch.Tensor) -> torch.Tensor:
+    """[B, L, C] with a dense last dimension and a uniform row stride (slices of a wider matrix qualify)."""
+    if t.stride(2) == 1 and (t.size(0) == 1 or t.stride(0) == t.size(1) * t.stride(1)):
+        return t
+    return t.contiguous()
+
+
 class _ScanFn(torch.autograd.Function):
+    """Token-major kernel path: u, delta, z (B,L,Di); B, C (B,L,16); reset int32 (B·L,) or None."""
+
     @staticmethod
-    def forward(ctx, u, delta, A, B, C, D, z, delta_bias, delta_softplus, cu_seqlens):
+    def forward(ctx, u, delta, A, B, C, D, z, delta_bias, delta_softplus, reset):
         ext = backend.require_extension()
-        u, delta, B, C = u.contiguous(), delta.contiguous(), B.contiguous(), C.contiguous()
-        z = z.contiguous() if z is not None else None
-        y, ckpt = ext.selective_scan_fwd(u, delta, A, B, C, D, z, delta_bias, delta_softplus, cu_seqlens)
+        u, delta, B, C = _rows(u), _rows(delta), _rows(B), _rows(C)
+        z = _rows(z) if z is not None else None
+        need_grad = any(t is not None and t.requires_grad for t in (u, delta, A, B, C, D, z, delta_bias))
+        y, ckpt = ext.selective_scan_fwd(u, delta, A, B, C, D, z, delta_bias, delta_softplus, reset, need_grad)
         backend.count_launch()
         none = torch.empty(0)
         ctx.save_for_backward(u, delta, A, B, C, D, z if z is not None else none,
                               delta_bias if delta_bias is not None else none,
-                              cu_seqlens if cu_seqlens is not None else none, ckpt)
-        ctx.flags = (delta_softplus, z is not None, delta_bias is not None, cu_seqlens is not None)
+                              reset if reset is not None else none, ckpt if ckpt is not None else none)
+        ctx.flags = (delta_softplus, z is not None, delta_bias is not None, reset is not None)
         return y
 
     @staticmethod
     def backward(ctx, dy):
         ext = backend.require_extension()
-        u, delta, A, B, C, D, z, dbias, cu, ckpt = ctx.saved_tensors
-        sp, has_z, has_b, has_cu = ctx.flags
-        du, ddelta, dA, dB, dC, dD, dz, ddb = ext.selective_scan_bwd(
-            dy.contiguous(), u, delta, A, B, C, D, z if has_z else None, dbias if has_b else None, sp,
-            cu if has_cu else None, ckpt)
-        backend.count_launch(2)
-        return (du, ddelta, dA.to(A.dtype), dB, dC, dD.to(D.dtype), dz if has_z else None,
-                ddb.to(dbias.dtype) if has_b else None, None, None)
+        u, delta, A, B, C, D, z, dbias, reset, ckpt = ctx.saved_tensors
+        sp, has_z, has_b, has_r = ctx.flags
+        du, ddelta, dz, dA, dB, dC, dD, ddb = ext.selective_scan_bwd(
+            _rows(dy), u, delta, A, B, C, D, z if has_z else None, dbias if has_b else None, sp,
+            reset if has_r else None, ckpt)
+        backend.count_launch()
+        return (du, ddelta, dA, dB.to(B.dtype), dC.to(C.dtype), dD, dz if has_z else None,
+                ddb if has_b else None, None, None)
+
+
+def _reset_flags(cu_seqlens: torch.Tensor, n_tokens: int) -> torch.Tensor:
+    r = torch.zeros(n_tokens + 1, dtype=torch.int32, device=cu_seqlens.device)
+    r[cu_seqlens.long()] = 1
+    return r[:n_tokens].contiguous()
 
 
 def selective_scan(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta_softplus: bool = False,
-                   cu_seqlens: Optional[torch.Tensor] = None):
-    if (backend.has("selective_scan_fwd") and u.dtype in (torch.bfloat16, torch.float32) and A.shape[1] == 16 and D is not None and B.dim() == 3
+                   cu_seqlens: Optional[torch.Tensor] = None, channel_last: bool = False):
+    """``channel_last=False``: u,delta,z (B,Di,L), B,C (B,N,L) as in the reference interface;
+    ``channel_last=True``: u,delta,z (B,L,Di), B,C (B,L,N) — the kernel's native layout.  Returns y in the layout of u."""
+    if (backend.has("selective_scan_fwd") and u.dtype in (torch.bfloat16, torch.float32) and A.shape[1] == 16 and D is not None
+            and B.dim() == 3 and u.shape[1 if not channel_last else 2] % 16 == 0
             and backend.use_cuda_kernel("selective_scan", u, delta, A, B, C)):
-        cu = None if cu_seqlens is None else cu_seqlens.to(torch.int32).contiguous()
-        return _ScanFn.apply(u, delta.to(u.dtype), A.float().contiguous(), B.to(u.dtype), C.to(u.dtype),
-                             D.float().contiguous(), None if z is None else z.to(u.dtype),
-                             None if delta_bias is None else delta_bias.float().contiguous(),
-                             delta_softplus, cu)
+        tm = (lambda t: t) if channel_last else (lambda t: t.transpose(1, 2))
+        ut = tm(u)
+        reset = None if cu_seqlens is None else _reset_flags(cu_seqlens, ut.shape[0] * ut.shape[1])
+        y = _ScanFn.apply(ut, tm(delta).to(u.dtype), A.float().contiguous(), tm(B).to(u.dtype), tm(C).to(u.dtype),
+                          D.float().contiguous(), None if z is None else tm(z).to(u.dtype),
+                          None if delta_bias is None else delta_bias.float().contiguous(), delta_softplus, reset)
+        return tm(y)
+    if channel_last:
+        t = lambda v: None if v is None else v.transpose(1, 2)
+        return _scan_chunked_torch(t(u), t(delta), A, t(B), t(C), D, t(z), delta_bias, delta_softplus,
+                                   cu_seqlens).transpose(1, 2)
     return _scan_chunked_torch(u, delta, A, B, C, D, z, delta_bias, delta_softplus, cu_seqlens)
 
 

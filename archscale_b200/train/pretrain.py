@@ -194,7 +194,12 @@ def make_plan(*, train_model: Optional[str], train_name: str, depth: int, max_to
     p.base_model_name = f"{model_name}_d{hps.d0}"
     p.model_name = model_name = f"{model_name}_d{depth}"
     model_config = Config.from_name(model_name)
-    base_config = Config.from_name(p.base_model_name)
+    # fixed-size registry entries (e.g. phi4miniflash_d32) have no base-depth sibling; the base is only
+    # needed for the token-budget law, i.e. when --max_tokens is not given
+    try:
+        base_config = Config.from_name(p.base_model_name)
+    except KeyError:
+        base_config = None
     p.use_flce_loss = use_flce if use_flce is not None else (model_config.vocab_size > 100_000 or "validation" in tc or fp8)
     name = f"{tc}_{model_name}"
     if ar is not None:
@@ -211,6 +216,8 @@ def make_plan(*, train_model: Optional[str], train_name: str, depth: int, max_to
     if max_tokens is not None:
         p.train_tokens = int(max_tokens)
     else:
+        if base_config is None:
+            raise ValueError(f"{p.base_model_name} is not a registered config: pass --max_tokens for {model_name}")
         if ar is not None:
             model_config.ar = base_config.ar = ar
         n_base = get_parameters_count(p.base_model_name, hps.d0, base_config, tc)

@@ -42,6 +42,15 @@ CONFIGS = {
         overrides={"n_head": 8, "n_query_groups": 2, "n_routed_experts": 64, "router_top_k": 8,
                    "moe_intermediate_size": 256, "shared_intermediate_size": 2048},
         sparsity=8, top_k=8, share_expert=True, sqrt_gate=True, global_aux=True, aux_gamma=0.01),
+    "phi4": dict(
+        name="SambaY 3.8B phi4miniflash_d32 (d_model 2560, 40q/20kv heads, head_dim 64, Mamba-1 + SWA 512 + YOCO + GMU, "
+             "differential attention, LayerNorm, vocab 200064, tied embeddings), packed 8192-token rows",
+        train_model="phi4miniflash", depth=32, train_name="scaling_mup_muonh_tie", micro_bsz=1, ctx_len=8192,
+        overrides={}, sparsity=1, top_k=2),
+    "sambay": dict(
+        name="SambaY d16 (Mamba-1 + SWA + YOCO + GMU), muP++ MuonH",
+        train_model="sambay", depth=16, train_name="scaling_mup_muonh", micro_bsz=8, ctx_len=4096,
+        overrides={}, sparsity=1, top_k=2),
 }
 
 CLOCK_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
