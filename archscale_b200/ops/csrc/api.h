@@ -119,8 +119,9 @@ int b200_selective_scan_fwd(const void* u, int su, const void* delta, int sd, co
 int b200_selective_scan_bwd(const void* dy, int sdy, const void* u, int su, const void* delta, int sd, const float* A,
                             const void* Bm, int sB, const void* Cm, int sC, const float* D, const void* z, int sz,
                             const float* dbias, const int* reset, const float* ckpt, void* du, void* ddelta, void* dz, float* dA,
-                            float* dBf, float* dCf, float* dD, float* ddbias, int dtype, int B, int L, int Di, int softplus,
-                            cudaStream_t st);
+                            float* partB, float* partC, void* dB, void* dC, float* dD, float* ddbias, int dtype, int B, int L,
+                            int Di, int softplus, cudaStream_t st);
+int b200_selective_scan_channel_blocks(int Di);
 
 // Block-scaled MXFP8 (gemm_mxfp8.cu): quantisers and the tcgen05 block-scaled GEMM.
 size_t b200_mxfp8_sf_bytes(int rows, int K);

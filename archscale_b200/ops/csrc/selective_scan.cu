@@ -6,10 +6,11 @@
 // Time runs sequentially inside the thread in tiles of 64 steps that the CTA stages through shared memory with
 // 32-byte row segments; sums over the 16 states use a 15-shuffle "reduce-scatter" per 16 steps (lane n ends up with
 // the total of step n), so the recurrence itself is one FMA per step and everything else has ILP across steps.
-// The forward stores the state entering every 64-step tile (fp32, L/64 × Di × 16); the backward walks the tiles in
-// reverse, recomputes the 64 states of a tile into registers and runs the adjoint recurrence
+// The forward stores the state entering every 32-step half tile (fp32, L/32 × Di × 16); the backward walks the halves
+// in reverse, recomputes the 32 states of a half into registers and runs the adjoint recurrence
 //   G_t = C_t·dy'_t + a_{t+1}·G_{t+1}
-// dB/dC (sums over channels) are reduced in shared memory per tile and added to fp32 global accumulators.
+// dB/dC (sums over channels) are reduced over the CTA's 16 channels in shared memory, written as per-CTA partial
+// sums and summed over channel blocks by a second kernel (deterministic, no atomics).
 #include "sm100.cuh"
 #include "api.h"
 
@@ -82,9 +83,9 @@ sscan_fwd_kernel(const T* __restrict__ u, int su, const T* __restrict__ delta, i
     }
     if (tid < SS_T) s_reset[tid] = (reset && t0 + tid < L) ? reset[row0 + t0 + tid] : 0;
     __syncthreads();
-    if (ckpt) ckpt[((static_cast<size_t>(b) * nseg + seg) * Di + d) * SS_N + n] = h;
 #pragma unroll
     for (int sb = 0; sb < SS_T / 16; ++sb) {
+      if ((sb & 1) == 0 && ckpt) ckpt[((static_cast<size_t>(b) * nseg * 2 + seg * 2 + (sb >> 1)) * Di + d) * SS_N + n] = h;
       float p[16];
 #pragma unroll
       for (int s = 0; s < 16; ++s) {
@@ -119,9 +120,14 @@ sscan_bwd_kernel(const T* __restrict__ dy, int sdy, const T* __restrict__ u, int
                  const int* __restrict__ reset, const float* __restrict__ ckpt, T* __restrict__ du, T* __restrict__ ddelta,
                  T* __restrict__ dz, float* __restrict__ dA, float* __restrict__ dBf, float* __restrict__ dCf,
                  float* __restrict__ dD, float* __restrict__ ddbias, int L, int Di, int softplus) {
-  __shared__ float s_dt[SS_T][SS_C], s_u[SS_T][SS_C], s_dyp[SS_T][SS_C], s_B[SS_T][SS_N], s_C[SS_T][SS_N];
-  __shared__ float s_ypre[SS_T][SS_C], s_ddt[SS_T][SS_C], s_du[SS_T][SS_C], s_dB[SS_T][SS_N], s_dC[SS_T][SS_N];
-  __shared__ int s_reset[SS_T];
+  extern __shared__ float ss_dyn[];
+  typedef float (*Tile)[SS_C];
+  Tile s_dt = reinterpret_cast<Tile>(ss_dyn), s_u = s_dt + SS_T, s_dyp = s_u + SS_T, s_B = s_dyp + SS_T, s_C = s_B + SS_T;
+  Tile s_ypre = s_C + SS_T, s_ddt = s_ypre + SS_T, s_du = s_ddt + SS_T;
+  // per-warp slabs for the channel sums of dB / dC: plain stores, summed over the 8 warps in the tile epilogue
+  float (*s_dBw)[SS_T][SS_N] = reinterpret_cast<float (*)[SS_T][SS_N]>(s_du + SS_T);
+  float (*s_dCw)[SS_T][SS_N] = s_dBw + 8;
+  int* s_reset = reinterpret_cast<int*>(s_dCw + 8);
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int cl = 2 * w + (lane >> 4), n = lane & 15;
   const int d0 = blockIdx.x * SS_C, b = blockIdx.y, d = d0 + cl;
@@ -152,53 +158,57 @@ sscan_bwd_kernel(const T* __restrict__ dy, int sdy, const T* __restrict__ u, int
       ur[k] = uu; sg[k] = sig; dyr[k] = dyv; zr[k] = zz;
       s_dt[i][cj] = dt; s_u[i][cj] = uu; s_B[i][cj] = bv; s_C[i][cj] = cv;
       s_dyp[i][cj] = z ? dyv * zz * ss_sigmoid(zz) : dyv;
-      s_dB[i][cj] = 0.f; s_dC[i][cj] = 0.f;
     }
     if (tid < SS_T) s_reset[tid] = (reset && t0 + tid < L) ? reset[row0 + t0 + tid] : 0;
     __syncthreads();
-    float h = ckpt[((static_cast<size_t>(b) * nseg + seg) * Di + d) * SS_N + n];
-    float hs[SS_T];              // state before each step of the tile (0 where the step resets)
+#pragma unroll 1
+    for (int half = 1; half >= 0; --half) {      // 32-step halves: the recomputed states of a half fit in registers
+      float h = ckpt[((static_cast<size_t>(b) * nseg * 2 + seg * 2 + half) * Di + d) * SS_N + n];
+      float hs[32];              // state before each step of the half (0 where the step resets)
 #pragma unroll
-    for (int sb = 0; sb < SS_T / 16; ++sb) {
-      float p[16];
+      for (int sbl = 0; sbl < 2; ++sbl) {
+        const int sb = half * 2 + sbl;
+        float p[16];
 #pragma unroll
-      for (int s = 0; s < 16; ++s) {
-        const int i = sb * 16 + s;
-        const float dt = s_dt[i][cl];
-        float a = exp2f(dt * A2);
-        if (s_reset[i]) { a = 0.f; h = 0.f; }
-        hs[i] = h;
-        h = a * h + dt * s_u[i][cl] * s_B[i][n];
-        p[s] = h * s_C[i][n];
+        for (int s = 0; s < 16; ++s) {
+          const int i = sb * 16 + s;
+          const float dt = s_dt[i][cl];
+          float a = exp2f(dt * A2);
+          if (s_reset[i]) { a = 0.f; h = 0.f; }
+          hs[sbl * 16 + s] = h;
+          h = a * h + dt * s_u[i][cl] * s_B[i][n];
+          p[s] = h * s_C[i][n];
+        }
+        const float tot = treduce16(p, n);
+        s_ypre[sb * 16 + n][cl] = tot;
       }
-      const float tot = treduce16(p, n);
-      s_ypre[sb * 16 + n][cl] = tot;
-    }
 #pragma unroll
-    for (int sb = SS_T / 16 - 1; sb >= 0; --sb) {
-      float vdt[16], vdu[16];
+      for (int sbl = 1; sbl >= 0; --sbl) {
+        const int sb = half * 2 + sbl;
+        float vdt[16], vdu[16];
 #pragma unroll
-      for (int s = 15; s >= 0; --s) {
-        const int i = sb * 16 + s;
-        const float dt = s_dt[i][cl], uu = s_u[i][cl], Bv = s_B[i][n], Cv = s_C[i][n], dyp = s_dyp[i][cl];
-        float a = exp2f(dt * A2);
-        if (s_reset[i]) a = 0.f;
-        const float hprev = hs[i];
-        const float ht = a * hprev + dt * uu * Bv;
-        const float g = G + Cv * dyp;
-        float vC = dyp * ht, vB = g * dt * uu;
-        const float daa = g * hprev * a;
-        dA_acc += daa * dt;
-        vdt[s] = daa * Araw + g * Bv * uu;
-        vdu[s] = g * dt * Bv;
-        G = g * a;
-        vB += __shfl_xor_sync(0xffffffffu, vB, 16);
-        vC += __shfl_xor_sync(0xffffffffu, vC, 16);
-        if (lane < 16) { atomicAdd(&s_dB[i][n], vB); atomicAdd(&s_dC[i][n], vC); }
+        for (int s = 15; s >= 0; --s) {
+          const int i = sb * 16 + s;
+          const float dt = s_dt[i][cl], uu = s_u[i][cl], Bv = s_B[i][n], Cv = s_C[i][n], dyp = s_dyp[i][cl];
+          float a = exp2f(dt * A2);
+          if (s_reset[i]) a = 0.f;
+          const float hprev = hs[sbl * 16 + s];
+          const float ht = a * hprev + dt * uu * Bv;
+          const float g = G + Cv * dyp;
+          float vC = dyp * ht, vB = g * dt * uu;
+          const float daa = g * hprev * a;
+          dA_acc += daa * dt;
+          vdt[s] = daa * Araw + g * Bv * uu;
+          vdu[s] = g * dt * Bv;
+          G = g * a;
+          vB += __shfl_xor_sync(0xffffffffu, vB, 16);
+          vC += __shfl_xor_sync(0xffffffffu, vC, 16);
+          if (lane < 16) { s_dBw[w][i][n] = vB; s_dCw[w][i][n] = vC; }
+        }
+        const float tdt = treduce16(vdt, n), tdu = treduce16(vdu, n);
+        s_ddt[sb * 16 + n][cl] = tdt;
+        s_du[sb * 16 + n][cl] = tdu;
       }
-      const float tdt = treduce16(vdt, n), tdu = treduce16(vdu, n);
-      s_ddt[sb * 16 + n][cl] = tdt;
-      s_du[sb * 16 + n][cl] = tdu;
     }
     __syncthreads();
 #pragma unroll
@@ -217,8 +227,13 @@ sscan_bwd_kernel(const T* __restrict__ dy, int sdy, const T* __restrict__ u, int
           const float sgz = ss_sigmoid(zr[k]);
           st1(dz + r * Di + d0 + cj, dyr[k] * ypre * sgz * (1.f + zr[k] * (1.f - sgz)));
         }
-        atomicAdd(&dBf[r * SS_N + cj], s_dB[i][cj]);
-        atomicAdd(&dCf[r * SS_N + cj], s_dC[i][cj]);
+        float sb = 0.f, sc = 0.f;
+#pragma unroll
+        for (int ww = 0; ww < 8; ++ww) { sb += s_dBw[ww][i][cj]; sc += s_dCw[ww][i][cj]; }
+        // partial sums of this 16-channel block; summed over blocks by sscan_reduce_bc_kernel
+        const size_t po = (static_cast<size_t>(blockIdx.x) * gridDim.y * L + r) * SS_N + cj;
+        dBf[po] = sb;
+        dCf[po] = sc;
       }
     }
     __syncthreads();
@@ -228,14 +243,31 @@ sscan_bwd_kernel(const T* __restrict__ dy, int sdy, const T* __restrict__ u, int
   if (ddbias) atomicAdd(&ddbias[d0 + cj], dbias_acc);
 }
 
+// dB / dC [rows, 16] = Σ over channel blocks of the partial sums [nblk, rows, 16] written by the backward.
+template <typename T>
+__global__ void __launch_bounds__(256) sscan_reduce_bc_kernel(const float* __restrict__ pB, const float* __restrict__ pC,
+                                                             T* __restrict__ dB, T* __restrict__ dC, size_t n, int nblk) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float sb = 0.f, sc = 0.f;
+#pragma unroll 4
+  for (int k = 0; k < nblk; ++k) { sb += pB[k * n + i]; sc += pC[k * n + i]; }
+  st1(dB + i, sb);
+  st1(dC + i, sc);
+}
+
+constexpr int SS_BWD_SMEM = (8 * SS_T * SS_C + 16 * SS_T * SS_N) * 4 + SS_T * 4;
+
 }  // namespace b200
 
 using namespace b200;
 
-extern "C" int b200_selective_scan_ckpt_segments(int L) { return (L + SS_T - 1) / SS_T; }
+extern "C" int b200_selective_scan_channel_blocks(int Di) { return Di / SS_C; }
+
+extern "C" int b200_selective_scan_ckpt_segments(int L) { return 2 * ((L + SS_T - 1) / SS_T); }
 
 // u, delta, z: rows of `su`, `sd`, `sz` elements; Bm, Cm: [B·L, 16] with row strides sB, sC; y: dense [B, L, Di].
-// reset: int32 per token (1 = h is cleared before this step) or null.  ckpt: fp32 [B, ceil(L/64), Di, 16] or null.
+// reset: int32 per token (1 = h is cleared before this step) or null.  ckpt: fp32 [B, 2·ceil(L/64), Di, 16] or null.
 extern "C" int b200_selective_scan_fwd(const void* u, int su, const void* delta, int sd, const float* A, const void* Bm, int sB,
                                        const void* Cm, int sC, const float* D, const void* z, int sz, const float* dbias,
                                        const int* reset, void* y, float* ckpt, int dtype, int B, int L, int Di, int softplus,
@@ -253,23 +285,36 @@ extern "C" int b200_selective_scan_fwd(const void* u, int su, const void* delta,
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-// dA [Di,16], dBf / dCf [B·L,16], dD [Di], ddbias [Di] are fp32 accumulators that must be zero on entry.
+// dA [Di,16], dD [Di], ddbias [Di] are fp32 accumulators that must be zero on entry.  partB / partC: fp32 scratch
+// [Di/16, B·L, 16] (fully overwritten); dB / dC: [B·L, 16] in the activation dtype.
 extern "C" int b200_selective_scan_bwd(const void* dy, int sdy, const void* u, int su, const void* delta, int sd, const float* A,
                                        const void* Bm, int sB, const void* Cm, int sC, const float* D, const void* z, int sz,
                                        const float* dbias, const int* reset, const float* ckpt, void* du, void* ddelta, void* dz,
-                                       float* dA, float* dBf, float* dCf, float* dD, float* ddbias, int dtype, int B, int L,
-                                       int Di, int softplus, cudaStream_t st) {
+                                       float* dA, float* partB, float* partC, void* dB, void* dC, float* dD, float* ddbias,
+                                       int dtype, int B, int L, int Di, int softplus, cudaStream_t st) {
   if (Di % SS_C) return -1;
   if (B * L == 0) return 0;
   dim3 grid(Di / SS_C, B);
-  if (dtype == 1)
-    sscan_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)dy, sdy, (const __nv_bfloat16*)u, su,
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(sscan_bwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SS_BWD_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(sscan_bwd_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, SS_BWD_SMEM) != cudaSuccess)
+      return -2;
+    configured = true;
+  }
+  const size_t n = static_cast<size_t>(B) * L * SS_N;
+  const unsigned rgrid = static_cast<unsigned>((n + 255) / 256);
+  if (dtype == 1) {
+    sscan_bwd_kernel<__nv_bfloat16><<<grid, 256, SS_BWD_SMEM, st>>>((const __nv_bfloat16*)dy, sdy, (const __nv_bfloat16*)u, su,
         (const __nv_bfloat16*)delta, sd, A, (const __nv_bfloat16*)Bm, sB, (const __nv_bfloat16*)Cm, sC, D,
         (const __nv_bfloat16*)z, sz, dbias, reset, ckpt, (__nv_bfloat16*)du, (__nv_bfloat16*)ddelta, (__nv_bfloat16*)dz, dA,
-        dBf, dCf, dD, ddbias, L, Di, softplus);
-  else
-    sscan_bwd_kernel<float><<<grid, 256, 0, st>>>((const float*)dy, sdy, (const float*)u, su, (const float*)delta, sd, A,
+        partB, partC, dD, ddbias, L, Di, softplus);
+    sscan_reduce_bc_kernel<__nv_bfloat16><<<rgrid, 256, 0, st>>>(partB, partC, (__nv_bfloat16*)dB, (__nv_bfloat16*)dC, n, Di / SS_C);
+  } else {
+    sscan_bwd_kernel<float><<<grid, 256, SS_BWD_SMEM, st>>>((const float*)dy, sdy, (const float*)u, su, (const float*)delta, sd, A,
         (const float*)Bm, sB, (const float*)Cm, sC, D, (const float*)z, sz, dbias, reset, ckpt, (float*)du, (float*)ddelta,
-        (float*)dz, dA, dBf, dCf, dD, ddbias, L, Di, softplus);
+        (float*)dz, dA, partB, partC, dD, ddbias, L, Di, softplus);
+    sscan_reduce_bc_kernel<float><<<rgrid, 256, 0, st>>>(partB, partC, (float*)dB, (float*)dC, n, Di / SS_C);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
