@@ -32,3 +32,16 @@ class Linear(nn.Linear):
             from archscale_b200.ops import mxfp8
             return mxfp8.linear_mxfp8(x, w, b)
         return ops.linear(x, w, b)
+
+
+def apply_mxfp8(model: nn.Module, skip=("lm_head", "lc_proj")) -> int:
+    """Switch every :class:`Linear` of ``model`` to the MXFP8 path, except modules whose name contains one of
+    ``skip`` and layers whose dimensions are not multiples of 128 (the rule of `precision.py:192-251`, with
+    the block-scaled kernel's granularity instead of 16).  Returns the number of layers switched."""
+    n = 0
+    for name, mod in model.named_modules():
+        if isinstance(mod, Linear) and not any(s in name for s in skip) \
+                and mod.in_features % 128 == 0 and mod.out_features % 128 == 0:
+            mod.mxfp8 = True
+            n += 1
+    return n

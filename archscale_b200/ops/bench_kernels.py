@@ -214,8 +214,31 @@ def bench_mamba(res: list) -> None:
         print(res[-1], flush=True)
 
 
+def bench_mxfp8(res: list) -> None:
+    """Block-scaled MXFP8 GEMM and its quantisers against the bf16 tcgen05 kernel on the same shapes."""
+    from archscale_b200.ops import mxfp8
+    ext = backend.require_extension()
+    pk = peaks()
+    for (M, N, K, what) in [(32768, 3072, 2048, "fwd qkv d16"), (32768, 11264, 2048, "fwd w1 d16"),
+                            (32768, 2048, 5632, "fwd w3 d16"), (8192, 8192, 8192, "square 8192")]:
+        a, b = torch.randn(M, K, device="cuda").bfloat16(), torch.randn(N, K, device="cuda").bfloat16()
+        aq, asf = mxfp8.quantize(a)
+        bq, bsf = mxfp8.quantize(b)
+        t_q = time_ms(lambda: mxfp8.gemm(aq, asf, bq, bsf))
+        t_b = time_ms(lambda: ext.gemm_bf16(a, b, 0, torch.bfloat16, None))
+        t_row = time_ms(lambda: mxfp8.quantize(a))
+        t_col = time_ms(lambda: mxfp8.quantize(a, colwise=True))
+        fl = 2.0 * M * N * K
+        res.append({"kernel": "gemm_mxfp8", "case": what, "M": M, "N": N, "K": K, "ms": t_q, "tflops": fl / t_q / 1e9,
+                    "bf16_kernel_ms": t_b, "speedup_vs_bf16_kernel": t_b / t_q,
+                    "frac_of_" + pk["kind"] + "_bf16_peak": fl / t_q / 1e9 / pk["bf16_tflops"],
+                    "quant_rowwise_ms": t_row, "quant_rowwise_gbs": 3.0 * M * K / t_row / 1e6,
+                    "quant_colwise_ms": t_col, "quant_colwise_gbs": 3.0 * M * K / t_col / 1e6})
+        print(res[-1], flush=True)
+
+
 ALL = {"gemm": bench_gemm, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "ce": bench_ce, "rope": bench_rope,
-       "attn": bench_attn, "mamba": bench_mamba}
+       "attn": bench_attn, "mamba": bench_mamba, "mxfp8": bench_mxfp8}
 
 
 def main() -> None:

@@ -129,6 +129,13 @@ int b200_mxfp8_quantize(const void* x, int ld, void* q, void* sf, int R, int C, 
 int b200_gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, void* out, int M, int N, int K, int lda,
                     int ldb, int ldc, float alpha, int out_f32, int accumulate, int num_sms, int* status, cudaStream_t stream);
 
+// LayerNorm (layernorm.cu)
+int b200_layernorm_bwd_partials(int rows);
+int b200_layernorm_fwd(const void* x, int dtype, const float* w, const float* bias, void* y, float* mean, float* rstd, int rows,
+                       int cols, float eps, cudaStream_t st);
+int b200_layernorm_bwd(const void* dy, const void* x, int dtype, const float* w, const float* mean, const float* rstd, void* dx,
+                       float* part, float* dw, float* db, int rows, int cols, cudaStream_t st);
+
 #ifdef __cplusplus
 }
 #endif

@@ -8,9 +8,9 @@
 //                      Sᵀ = K·Qᵀ, dPᵀ = V·dOᵀ  →  Pᵀ, dSᵀ (bf16, in TMEM)  →  dV += Pᵀ·dO, dK += dSᵀ·Q
 //                    GQA reduction over the group's query heads happens in the TMEM accumulators.
 //
-// P is recomputed from the saved log-sum-exp.  The bf16 P / dS tiles overwrite the fp32 S / dP tiles
-// in place, 32 columns at a time (16 packed columns land inside the 32 columns just read), which
-// keeps TMEM at 512 columns: S|P 128, dP|dS 128, two 128-column accumulators.
+// P is recomputed from the saved log-sum-exp.  The bf16 P / dS values overwrite the fp32 S / dP columns
+// in place (16 packed columns land inside the 32 columns a warp just read).  Inner tiles are processed as two
+// halves of 64 columns with two (S, dP) buffers: 2 × 128 columns + the 128-column accumulators ≤ 512.
 // Masking rule as in the forward: row r sees keys lo(r) ≤ k ≤ r.
 #include "sm100.cuh"
 #include "api.h"
@@ -18,7 +18,7 @@
 namespace b200 {
 
 constexpr int BT = 128;                 // tile edge (queries and keys)
-constexpr int BWD_THREADS = 192;
+constexpr int BWD_THREADS = 320;            // warp 0 TMA, warp 1 MMA, warps 2..9 softmax (two per TMEM lane quarter)
 constexpr float kLog2e_b = 1.4426950408889634f;
 
 int make_tmap_2d_bf16(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_elems,
@@ -79,7 +79,15 @@ struct BwdSmem {
   static constexpr int TOTAL = FIXED + RING + AUX + 1024 + 256;
 };
 
-__device__ __forceinline__ void named_bar_sync_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void named_bar_sync_256() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+// Both kernels below walk their inner tiles in halves of 64 columns so that two (S, dP) buffers, 64 fp32 columns
+// each, fit in tensor memory beside the accumulators.  The MMA thread runs one half ahead: while the 8 softmax
+// warps turn half h into P / dS, the tensor pipe computes S, dP of half h+1 and the accumulation of half h−1.
+// A softmax warp (lane quarter q, column half ch) owns 32 fp32 columns of a half and packs its bf16 result into
+// the first 16 of them, so the TS-MMA reads k-step k (16 rows of the contraction) at column (k/2)·32 + (k%2)·8.
+constexpr int HB = 64;
+__device__ __forceinline__ uint32_t packed_col(int k) { return static_cast<uint32_t>((k >> 1) * 32 + (k & 1) * 8); }
 
 // ------------------------------------------------------------------------------------------- dQ
 template <int D>
@@ -99,10 +107,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   uint64_t* fixed_full = bars;      // 1
   uint64_t* kv_full = bars + 1;     // [2]
   uint64_t* kv_empty = bars + 3;    // [2]
-  uint64_t* sdp_full = bars + 5;    // 1   S and dP of the current tile are in TMEM
-  uint64_t* ds_full = bars + 6;     // 1   (count 4) dS written
-  uint64_t* acc_done = bars + 7;    // 1   all dQ MMAs finished
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* sdp_full = bars + 5;    // [2]  S and dP of a half are in TMEM buffer b
+  uint64_t* ds_full = bars + 7;     // [2]  (count 8) dS of buffer b written
+  uint64_t* acc_done = bars + 9;    // 1    all dQ MMAs finished
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -114,11 +122,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   const int r_last = min(q0 + BT, p.T) - 1;
   const int j_begin = lo_of_row(p, b, q0) / BT;
   const int n_tiles = r_last / BT + 1 - j_begin;
+  const int n_half = 2 * n_tiles;
 
   if (threadIdx.x == 0) {
     mbar_init(fixed_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    mbar_init(sdp_full, 1); mbar_init(ds_full, 4); mbar_init(acc_done, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1);
+      mbar_init(&sdp_full[s], 1); mbar_init(&ds_full[s], 8);
+    }
+    mbar_init(acc_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -127,7 +139,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr;
-  const uint32_t T_S = tmem_base, T_DP = tmem_base + 128, T_DQ = tmem_base + 256;
+  const uint32_t T_DQ = tmem_base + 256;            // buffers: S[b] = base + 128 b, dP[b] = base + 128 b + 64
 
   if (warp == 0) {
     if (lane == 0) {
@@ -153,37 +165,48 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(BT, BT, 0, 0);
+      constexpr uint32_t idesc_s = make_idesc_bf16(BT, HB, 0, 0);
       constexpr uint32_t idesc_dq = make_idesc_bf16(BT, D, 0, 1);        // dQ += dS·K, K is N-major
       if (!mbar_wait(fixed_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL)) goto done;
-      for (int t = 0; t < n_tiles; ++t) {
-        const int st = t & 1; const uint32_t ph = (t >> 1) & 1;
-        if (!mbar_wait(&kv_full[st], ph, abort_flag, p.status, STATUS_TIMEOUT_FULL)) goto done;
+      const uint32_t sqa = smem_u32(sq), sdoa = smem_u32(sdo);
+      // S, dP of half `hx` into buffer hx & 1 (keys hf·64.. of the tile: rows 8192 bytes into each 64-column chunk)
+      auto issue_sdp = [&](int hx) -> bool {
+        const int t = hx >> 1, hf = hx & 1, st = t & 1, buf = hx & 1;
+        if (hf == 0 && !mbar_wait(&kv_full[st], (t >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
         tc_fence_after();
-        const uint32_t sk = smem_u32(ring + st * 2 * SM::TILE), sv = sk + SM::TILE;
-        const uint32_t sqa = smem_u32(sq), sdoa = smem_u32(sdo);
+        const uint32_t sk = smem_u32(ring + st * 2 * SM::TILE) + hf * 8192, sv = sk + SM::TILE;
+        const uint32_t ts = tmem_base + buf * 128, tdp = ts + 64;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k / 4) * CHUNK_BYTES + (k % 4) * 32;
-          umma_bf16(T_S, make_smem_desc(sqa + off, 16, 1024), make_smem_desc(sk + off, 16, 1024), idesc_s, k != 0);
+          umma_bf16(ts, make_smem_desc(sqa + off, 16, 1024), make_smem_desc(sk + off, 16, 1024), idesc_s, k != 0);
         }
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k / 4) * CHUNK_BYTES + (k % 4) * 32;
-          umma_bf16(T_DP, make_smem_desc(sdoa + off, 16, 1024), make_smem_desc(sv + off, 16, 1024), idesc_s, k != 0);
+          umma_bf16(tdp, make_smem_desc(sdoa + off, 16, 1024), make_smem_desc(sv + off, 16, 1024), idesc_s, k != 0);
         }
-        umma_commit(sdp_full);
-        if (!mbar_wait(ds_full, t & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
+        umma_commit(&sdp_full[buf]);
+        return true;
+      };
+      if (n_half > 0 && !issue_sdp(0)) goto done;
+      for (int hx = 0; hx < n_half; ++hx) {
+        if (hx + 1 < n_half && !issue_sdp(hx + 1)) goto done;
+        const int t = hx >> 1, hf = hx & 1, st = t & 1, buf = hx & 1;
+        if (!mbar_wait(&ds_full[buf], (hx >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
         tc_fence_after();
+        const uint32_t sk = smem_u32(ring + st * 2 * SM::TILE);
+        const uint32_t tdp = tmem_base + buf * 128 + 64;
 #pragma unroll
-        for (int k = 0; k < BT / 16; ++k)
-          umma_bf16_ts(T_DQ, T_DP + k * 8, make_smem_desc(sk + k * 2048, CHUNK_BYTES, 1024), idesc_dq, (t | k) != 0);
-        umma_commit(&kv_empty[st]);
+        for (int k = 0; k < HB / 16; ++k)
+          umma_bf16_ts(T_DQ, tdp + packed_col(k), make_smem_desc(sk + (hf * 4 + k) * 2048, CHUNK_BYTES, 1024), idesc_dq,
+                       (hx | k) != 0);
+        if (hf == 1) umma_commit(&kv_empty[st]);
       }
       umma_commit(acc_done);
     }
   } else {
-    const int qtr = warp & 3;
+    const int qtr = warp & 3, ch = (warp - 2) >> 2;
     const int r = q0 + qtr * 32 + lane;
     const bool row_valid = r < p.T;
     const int lo_r = row_valid ? lo_of_row(p, b, r) : 0;
@@ -192,45 +215,46 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const float lse2 = row_valid ? p.lse[stat_idx] * kLog2e_b : 0.f;
     const float dlt = row_valid ? p.delta[stat_idx] : 0.f;
     const uint32_t lane_off = static_cast<uint32_t>(qtr * 32) << 16;
-    for (int t = 0; t < n_tiles; ++t) {
-      const int k0 = (j_begin + t) * BT;
-      if (!mbar_wait(sdp_full, t & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
+    for (int hx = 0; hx < n_half; ++hx) {
+      const int t = hx >> 1, hf = hx & 1, buf = hx & 1;
+      const int kt0 = (j_begin + t) * BT;
+      const int k0 = kt0 + hf * HB + ch * 32;
+      if (!mbar_wait(&sdp_full[buf], (hx >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
       tc_fence_after();
-      const bool full_tile = (k0 + BT - 1 <= q0) && (k0 >= lo_last);
+      const bool full_tile = (kt0 + BT - 1 <= q0) && (kt0 >= lo_last);
+      const uint32_t ts = tmem_base + buf * 128 + ch * 32 + lane_off, tdp = ts + 64;
+      uint32_t sr[32], dr[32];
+      tmem_ld_32x32(ts, sr);
+      tmem_ld_32x32(tdp, dr);
+      tmem_ld_wait();
+      uint32_t w[16];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sr[32], dr[32];
-        tmem_ld_32x32(T_S + c * 32 + lane_off, sr);
-        tmem_ld_32x32(T_DP + c * 32 + lane_off, dr);
-        tmem_ld_wait();
-        uint32_t w[16];
+      for (int e = 0; e < 16; ++e) {
+        float ds2[2];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          float ds2[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int kk = k0 + c * 32 + 2 * e + u;
-            float pr = exp2f(__uint_as_float(sr[2 * e + u]) * p.scale_log2 - lse2);
-            if (!full_tile && (kk > r || kk < lo_r)) pr = 0.f;
-            if (!row_valid) pr = 0.f;
-            ds2[u] = pr * (__uint_as_float(dr[2 * e + u]) - dlt) * p.scale;
-          }
-          w[e] = pack_bf16x2(ds2[0], ds2[1]);
+        for (int u = 0; u < 2; ++u) {
+          const int kk = k0 + 2 * e + u;
+          float pr = exp2f(__uint_as_float(sr[2 * e + u]) * p.scale_log2 - lse2);
+          if (!full_tile && (kk > r || kk < lo_r)) pr = 0.f;
+          if (!row_valid) pr = 0.f;
+          ds2[u] = pr * (__uint_as_float(dr[2 * e + u]) - dlt) * p.scale;
         }
-        tmem_st_32x16(T_DP + c * 16 + lane_off, w);      // in place: lands inside the columns just read
+        w[e] = pack_bf16x2(ds2[0], ds2[1]);
       }
+      tmem_st_32x16(tdp, w);                          // in place: the first 16 of the 32 columns just read
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(ds_full);
+      if (lane == 0) mbar_arrive(&ds_full[buf]);
     }
     if (!mbar_wait(acc_done, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
     tc_fence_after();
     __nv_bfloat16* orow = p.dq + ((static_cast<size_t>(b) * p.T + r) * p.H + h) * D;
 #pragma unroll
-    for (int c = 0; c < D / 32; ++c) {
+    for (int c = 0; c < D / 64; ++c) {
+      const int col = ch * (D / 2) + c * 32;
       uint32_t rr[32];
-      if (n_tiles > 0) { tmem_ld_32x32(T_DQ + c * 32 + lane_off, rr); tmem_ld_wait(); }
+      if (n_tiles > 0) { tmem_ld_32x32(T_DQ + col + lane_off, rr); tmem_ld_wait(); }
       else {
 #pragma unroll
         for (int e = 0; e < 32; ++e) rr[e] = 0u;
@@ -243,7 +267,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           o.y = pack_bf16x2(__uint_as_float(rr[e + 2]), __uint_as_float(rr[e + 3]));
           o.z = pack_bf16x2(__uint_as_float(rr[e + 4]), __uint_as_float(rr[e + 5]));
           o.w = pack_bf16x2(__uint_as_float(rr[e + 6]), __uint_as_float(rr[e + 7]));
-          *reinterpret_cast<uint4*>(orow + c * 32 + e) = o;
+          *reinterpret_cast<uint4*>(orow + col + e) = o;
         }
       }
     }
@@ -278,10 +302,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   uint64_t* fixed_full = bars;      // 1
   uint64_t* qd_full = bars + 1;     // [2]
   uint64_t* qd_empty = bars + 3;    // [2]
-  uint64_t* sdp_full = bars + 5;    // 1
-  uint64_t* ds_full = bars + 6;     // 1 (count 4)
-  uint64_t* acc_done = bars + 7;    // 1
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* sdp_full = bars + 5;    // [2]
+  uint64_t* ds_full = bars + 7;     // [2] (count 8)
+  uint64_t* acc_done = bars + 9;    // 1
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -296,11 +320,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const int i_begin = k0 / BT, i_end = r_hi / BT + 1;
   const int tiles_per_head = i_end - i_begin;
   const int n_iter = tiles_per_head * group;
+  const int n_half = 2 * n_iter;
 
   if (threadIdx.x == 0) {
     mbar_init(fixed_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&qd_full[s], 1); mbar_init(&qd_empty[s], 1); }
-    mbar_init(sdp_full, 1); mbar_init(ds_full, 4); mbar_init(acc_done, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&qd_full[s], 1); mbar_init(&qd_empty[s], 1);
+      mbar_init(&sdp_full[s], 1); mbar_init(&ds_full[s], 8);
+    }
+    mbar_init(acc_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -309,7 +337,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr;
-  const uint32_t T_ST = tmem_base, T_DPT = tmem_base + 128, T_DV = tmem_base + 256, T_DK = tmem_base + 384;
+  const uint32_t T_DV = tmem_base + 256, T_DK = tmem_base + 384;   // Sᵀ[b] = base + 128 b, dPᵀ[b] = base + 128 b + 64
 
   if (warp == 0) {
     if (lane == 0) {
@@ -336,93 +364,105 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(BT, BT, 0, 0);       // Sᵀ = K·Qᵀ, dPᵀ = V·dOᵀ
+      constexpr uint32_t idesc_s = make_idesc_bf16(BT, HB, 0, 0);       // Sᵀ = K·Qᵀ, dPᵀ = V·dOᵀ (64 queries)
       constexpr uint32_t idesc_acc = make_idesc_bf16(BT, D, 0, 1);      // dV += Pᵀ·dO, dK += dSᵀ·Q (N-major B)
       if (!mbar_wait(fixed_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL)) goto done;
       const uint32_t ska = smem_u32(sk), sva = smem_u32(sv);
-      for (int it = 0; it < n_iter; ++it) {
-        const int st = it & 1; const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait(&qd_full[st], ph, abort_flag, p.status, STATUS_TIMEOUT_FULL)) goto done;
+      auto issue_sdp = [&](int hx) -> bool {
+        const int it = hx >> 1, hf = hx & 1, st = it & 1, buf = hx & 1;
+        if (hf == 0 && !mbar_wait(&qd_full[st], (it >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
+        tc_fence_after();
+        const uint32_t sqa = smem_u32(ring + st * 2 * SM::TILE) + hf * 8192, sdoa = sqa + SM::TILE;
+        const uint32_t ts = tmem_base + buf * 128, tdp = ts + 64;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k / 4) * CHUNK_BYTES + (k % 4) * 32;
+          umma_bf16(ts, make_smem_desc(ska + off, 16, 1024), make_smem_desc(sqa + off, 16, 1024), idesc_s, k != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k / 4) * CHUNK_BYTES + (k % 4) * 32;
+          umma_bf16(tdp, make_smem_desc(sva + off, 16, 1024), make_smem_desc(sdoa + off, 16, 1024), idesc_s, k != 0);
+        }
+        umma_commit(&sdp_full[buf]);
+        return true;
+      };
+      if (n_half > 0 && !issue_sdp(0)) goto done;
+      for (int hx = 0; hx < n_half; ++hx) {
+        if (hx + 1 < n_half && !issue_sdp(hx + 1)) goto done;
+        const int it = hx >> 1, hf = hx & 1, st = it & 1, buf = hx & 1;
+        if (!mbar_wait(&ds_full[buf], (hx >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
         tc_fence_after();
         const uint32_t sqa = smem_u32(ring + st * 2 * SM::TILE), sdoa = sqa + SM::TILE;
+        const uint32_t ts = tmem_base + buf * 128, tdp = ts + 64;
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k / 4) * CHUNK_BYTES + (k % 4) * 32;
-          umma_bf16(T_ST, make_smem_desc(ska + off, 16, 1024), make_smem_desc(sqa + off, 16, 1024), idesc_s, k != 0);
+        for (int k = 0; k < HB / 16; ++k) {
+          umma_bf16_ts(T_DV, ts + packed_col(k), make_smem_desc(sdoa + (hf * 4 + k) * 2048, CHUNK_BYTES, 1024), idesc_acc,
+                       (hx | k) != 0);
+          umma_bf16_ts(T_DK, tdp + packed_col(k), make_smem_desc(sqa + (hf * 4 + k) * 2048, CHUNK_BYTES, 1024), idesc_acc,
+                       (hx | k) != 0);
         }
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k / 4) * CHUNK_BYTES + (k % 4) * 32;
-          umma_bf16(T_DPT, make_smem_desc(sva + off, 16, 1024), make_smem_desc(sdoa + off, 16, 1024), idesc_s, k != 0);
-        }
-        umma_commit(sdp_full);
-        if (!mbar_wait(ds_full, it & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < BT / 16; ++k) {
-          umma_bf16_ts(T_DV, T_ST + k * 8, make_smem_desc(sdoa + k * 2048, CHUNK_BYTES, 1024), idesc_acc, (it | k) != 0);
-          umma_bf16_ts(T_DK, T_DPT + k * 8, make_smem_desc(sqa + k * 2048, CHUNK_BYTES, 1024), idesc_acc, (it | k) != 0);
-        }
-        umma_commit(&qd_empty[st]);
+        if (hf == 1) umma_commit(&qd_empty[st]);
       }
       umma_commit(acc_done);
     }
   } else {
-    const int qtr = warp & 3;
-    const int tid128 = qtr * 32 + lane;               // 0..127 among the softmax threads
-    const int kk = k0 + tid128;                       // this thread's key row
+    const int qtr = warp & 3, ch = (warp - 2) >> 2;
+    const int tid256 = (warp - 2) * 32 + lane;        // 0..255 among the softmax threads
+    const int kk = k0 + qtr * 32 + lane;              // this thread's key row
     const bool key_valid = kk < p.T;
     const uint32_t lane_off = static_cast<uint32_t>(qtr * 32) << 16;
     bool ok = true;     // after a timed-out wait the thread keeps meeting its peers at the named barrier, idle
-    for (int it = 0; it < n_iter; ++it) {
-      const int st = it & 1;
-      if (!ok) { named_bar_sync_128(); continue; }
+    for (int hx = 0; hx < n_half; ++hx) {
+      const int it = hx >> 1, hf = hx & 1, st = it & 1, buf = hx & 1;
       const int hq = g * group + it / tiles_per_head;
       const int q0 = (i_begin + it % tiles_per_head) * BT;
-      // per-query statistics of this tile → shared memory (each softmax thread fills one entry)
       float* a_lse = aux + st * 3 * BT;
       float* a_dlt = a_lse + BT;
       int* a_lo = reinterpret_cast<int*>(a_dlt + BT);
-      {
-        const int rq = q0 + tid128;
-        const bool v = rq < p.T;
-        const size_t si = (static_cast<size_t>(b) * p.H + hq) * p.T + (v ? rq : 0);
-        a_lse[tid128] = v ? p.lse[si] * kLog2e_b : 0.f;
-        a_dlt[tid128] = v ? p.delta[si] : 0.f;
-        a_lo[tid128] = v ? lo_of_row(p, b, rq) : 0x7fffffff;    // invalid query rows see nothing
-      }
-      named_bar_sync_128();
-      if (!mbar_wait(sdp_full, it & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; continue; }
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sr[32], dr[32];
-        tmem_ld_32x32(T_ST + c * 32 + lane_off, sr);
-        tmem_ld_32x32(T_DPT + c * 32 + lane_off, dr);
-        tmem_ld_wait();
-        uint32_t wp[16], wd[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          float pv[2], dv2[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = c * 32 + 2 * e + u;
-            const int rq = q0 + col;
-            float pr = exp2f(__uint_as_float(sr[2 * e + u]) * p.scale_log2 - a_lse[col]);
-            if (!key_valid || kk > rq || kk < a_lo[col]) pr = 0.f;
-            pv[u] = pr;
-            dv2[u] = pr * (__uint_as_float(dr[2 * e + u]) - a_dlt[col]) * p.scale;
-          }
-          wp[e] = pack_bf16x2(pv[0], pv[1]);
-          wd[e] = pack_bf16x2(dv2[0], dv2[1]);
+      if (hf == 0) {
+        // per-query statistics of this tile → shared memory (the first 128 softmax threads fill one entry each)
+        if (ok && tid256 < BT) {
+          const int rq = q0 + tid256;
+          const bool v = rq < p.T;
+          const size_t si = (static_cast<size_t>(b) * p.H + hq) * p.T + (v ? rq : 0);
+          a_lse[tid256] = v ? p.lse[si] * kLog2e_b : 0.f;
+          a_dlt[tid256] = v ? p.delta[si] : 0.f;
+          a_lo[tid256] = v ? lo_of_row(p, b, rq) : 0x7fffffff;    // invalid query rows see nothing
         }
-        tmem_st_32x16(T_ST + c * 16 + lane_off, wp);
-        tmem_st_32x16(T_DPT + c * 16 + lane_off, wd);
+        named_bar_sync_256();
       }
+      if (!ok) continue;
+      if (!mbar_wait(&sdp_full[buf], (hx >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; continue; }
+      tc_fence_after();
+      const uint32_t ts = tmem_base + buf * 128 + ch * 32 + lane_off, tdp = ts + 64;
+      const int cbase = hf * HB + ch * 32;            // first query column (within the 128-query tile) of this warp
+      uint32_t sr[32], dr[32];
+      tmem_ld_32x32(ts, sr);
+      tmem_ld_32x32(tdp, dr);
+      tmem_ld_wait();
+      uint32_t wp[16], wd[16];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        float pv[2], dv2[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int col = cbase + 2 * e + u;
+          const int rq = q0 + col;
+          float pr = exp2f(__uint_as_float(sr[2 * e + u]) * p.scale_log2 - a_lse[col]);
+          if (!key_valid || kk > rq || kk < a_lo[col]) pr = 0.f;
+          pv[u] = pr;
+          dv2[u] = pr * (__uint_as_float(dr[2 * e + u]) - a_dlt[col]) * p.scale;
+        }
+        wp[e] = pack_bf16x2(pv[0], pv[1]);
+        wd[e] = pack_bf16x2(dv2[0], dv2[1]);
+      }
+      tmem_st_32x16(ts, wp);
+      tmem_st_32x16(tdp, wd);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(ds_full);
+      if (lane == 0) mbar_arrive(&ds_full[buf]);
     }
     if (!ok) goto done;
     if (!mbar_wait(acc_done, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
@@ -433,9 +473,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       __nv_bfloat16* orow = (which ? p.dk : p.dv) + obase;
       const uint32_t tsrc = which ? T_DK : T_DV;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
+        const int col = ch * (D / 2) + c * 32;
         uint32_t rr[32];
-        if (n_iter > 0) { tmem_ld_32x32(tsrc + c * 32 + lane_off, rr); tmem_ld_wait(); }
+        if (n_iter > 0) { tmem_ld_32x32(tsrc + col + lane_off, rr); tmem_ld_wait(); }
         else {
 #pragma unroll
           for (int e = 0; e < 32; ++e) rr[e] = 0u;
@@ -448,7 +489,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             o.y = pack_bf16x2(__uint_as_float(rr[e + 2]), __uint_as_float(rr[e + 3]));
             o.z = pack_bf16x2(__uint_as_float(rr[e + 4]), __uint_as_float(rr[e + 5]));
             o.w = pack_bf16x2(__uint_as_float(rr[e + 6]), __uint_as_float(rr[e + 7]));
-            *reinterpret_cast<uint4*>(orow + c * 32 + e) = o;
+            *reinterpret_cast<uint4*>(orow + col + e) = o;
           }
         }
       }

@@ -97,13 +97,41 @@ def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float = 1e-5,
     return out if out_dtype is None else out.to(out_dtype)
 
 
+class _LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps):
+        ext = backend.require_extension()
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        wf = None if weight is None else weight.float().contiguous()
+        bf = None if bias is None else bias.float().contiguous()
+        y, mean, rstd = ext.layernorm_fwd(x2, wf, bf, eps)
+        backend.count_launch()
+        ctx.save_for_backward(x2, wf if wf is not None else torch.empty(0), mean, rstd)
+        ctx.has_w, ctx.has_b = weight is not None, bias is not None
+        ctx.wdtype = None if weight is None else weight.dtype
+        ctx.bdtype = None if bias is None else bias.dtype
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        ext = backend.require_extension()
+        x2, wf, mean, rstd = ctx.saved_tensors
+        dy2 = dy.reshape(x2.shape)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx, dw, db = ext.layernorm_bwd(dy2, x2, wf if ctx.has_w else None, mean, rstd)
+        backend.count_launch(2)
+        return (dx.view(dy.shape), dw.to(ctx.wdtype) if ctx.has_w else None, db.to(ctx.bdtype) if ctx.has_b else None, None)
+
+
 def layer_norm(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor],
                eps: float = 1e-5) -> torch.Tensor:
-    if x.is_cuda:
-        # LayerNorm is only used by the phi4miniflash family; it runs torch's fused kernel in fp32.
-        return torch.nn.functional.layer_norm(x.float(), (x.shape[-1],),
-                                              None if weight is None else weight.float(),
-                                              None if bias is None else bias.float(), eps).to(x.dtype)
+    """LayerNorm over the last dimension (`lit_gpt/rmsnorm.py:935-1096` with ``is_rms_norm=False``)."""
+    if (x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 2560
+            and backend.has("layernorm_fwd") and backend.use_cuda_kernel("layernorm", x)):
+        return _LayerNormFn.apply(x, weight, bias, eps)
     return layer_norm_ref(x, weight, bias, eps)
 
 

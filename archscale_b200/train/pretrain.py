@@ -318,6 +318,10 @@ class Trainer:
         self.model.reset_parameters()
         self.model.compute_dtype = compute_dtype
         self.n_params_actual = num_parameters(self.model)
+        if self.config.mxfp8:
+            from archscale_b200.models.layers import apply_mxfp8
+            n_fp8 = apply_mxfp8(self.model)
+            self.print(f"MXFP8: {n_fp8} linear layers run the block-scaled e4m3 GEMM")
         if self.config.tp_size > 1:
             from archscale_b200.parallel import tp as tp_mod
             tp_mod.apply_tensor_parallel(self.model, mesh)

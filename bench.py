@@ -126,7 +126,8 @@ def run_ours(args) -> None:
     kwargs = dict(train_data_dir="synthetic", train_model=c["train_model"], depth=c["depth"], train_name=c["train_name"],
                   micro_bsz=c["micro_bsz"], ctx_len=c["ctx_len"], total_bsz=world * c["micro_bsz"] * c["ctx_len"],
                   max_tokens=1e12, use_flce=True, sparsity=c["sparsity"], top_k=c["top_k"],
-                  config_overrides=dict(c["overrides"]), ep=ep, fused_comm=args.fused_comm, return_trainer=True, quiet=True)
+                  config_overrides=dict(c["overrides"]), ep=ep, fused_comm=args.fused_comm, fp8=args.fp8,
+                  return_trainer=True, quiet=True)
     for k in ("share_expert", "sqrt_gate", "global_aux", "aux_gamma"):
         if k in c:
             kwargs[k] = c[k]
@@ -197,7 +198,7 @@ def run_ours(args) -> None:
             "metric": "train tokens/sec (whole job; per GPU = value / n_gpus), device-timed, max over ranks",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic uniform-random token ids (seed 0), random-init weights",
+            "dtype": "mxfp8 linears (bf16 elsewhere)" if args.fp8 else "bf16", "data": "synthetic uniform-random token ids (seed 0), random-init weights",
             "tokens_per_sec_per_gpu": value / world,
             "mfu": flops_step / (ms_per_step / 1e3) / 2.25e15,
             "config": {"model": c["name"], "global_batch": world * mb, "seq_len": T,
@@ -236,6 +237,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="dense", choices=sorted(CONFIGS))
+    ap.add_argument("--fp8", action="store_true", help="MXFP8 block-scaled linear layers (dtype is then reported as mxfp8)")
     ap.add_argument("--fused-comm", dest="fused_comm", action="store_true")
     ap.add_argument("--no-ep", dest="no_ep", action="store_true")
     args = ap.parse_args()
