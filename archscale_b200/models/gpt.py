@@ -477,6 +477,10 @@ class GPT(nn.Module):
         x = self.transformer.wte(idx)
         if self.scale_embed:
             x = x * math.sqrt(cfg.n_embd)
+        if getattr(self, "tp_size", 1) > 1:
+            # tensor + sequence parallelism: between blocks each rank carries its slice of the sequence
+            from archscale_b200.parallel.tp import sequence_slice
+            x = sequence_slice(x, self.tp_size, self.tp_rank).contiguous()
         input_embed = x
         kv_cache = gmu_mems = None
         self.lc_gate_hist, self.tokens_per_expert, self.token_indices = [], [], []

@@ -2,7 +2,7 @@
 //
 //   attn_bwd_delta   δ[b,h,r] = Σ_d dO·O                               (one warp per row/head)
 //   attn_bwd_dq      CTA per (query tile, head, batch), loop over key tiles:
-//                      S = Q·Kᵀ, dP = dO·Vᵀ  →  dS = P∘(dP − δ)·scale (bf16, in TMEM)  →  dQ += dS·K
+//                      S = Q·Kᵀ, dP = dO·Vᵀ  →  dS = P∘(dP − δ) (bf16, in TMEM)  →  dQ += dS·K, ·scale at the end
 //   attn_bwd_dkdv    CTA per (key tile, kv head, batch), loop over the query heads of the group and
 //                    their query tiles, in the transposed domain so that the lane index is the key row:
 //                      Sᵀ = K·Qᵀ, dPᵀ = V·dOᵀ  →  Pᵀ, dSᵀ (bf16, in TMEM)  →  dV += Pᵀ·dO, dK += dSᵀ·Q
@@ -228,18 +228,27 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       tmem_ld_32x32(tdp, dr);
       tmem_ld_wait();
       uint32_t w[16];
+      const float sl2 = p.scale_log2;
+      if (full_tile && row_valid) {                   // no key of this tile is masked for any row: 4 ops per element
 #pragma unroll
-      for (int e = 0; e < 16; ++e) {
-        float ds2[2];
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int kk = k0 + 2 * e + u;
-          float pr = exp2f(__uint_as_float(sr[2 * e + u]) * p.scale_log2 - lse2);
-          if (!full_tile && (kk > r || kk < lo_r)) pr = 0.f;
-          if (!row_valid) pr = 0.f;
-          ds2[u] = pr * (__uint_as_float(dr[2 * e + u]) - dlt) * p.scale;
+        for (int e = 0; e < 16; ++e) {
+          const float p0 = exp2f(fmaf(__uint_as_float(sr[2 * e]), sl2, -lse2));
+          const float p1 = exp2f(fmaf(__uint_as_float(sr[2 * e + 1]), sl2, -lse2));
+          w[e] = pack_bf16x2(p0 * (__uint_as_float(dr[2 * e]) - dlt), p1 * (__uint_as_float(dr[2 * e + 1]) - dlt));
         }
-        w[e] = pack_bf16x2(ds2[0], ds2[1]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          float ds2[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int kk = k0 + 2 * e + u;
+            float pr = exp2f(fmaf(__uint_as_float(sr[2 * e + u]), sl2, -lse2));
+            if (kk > r || kk < lo_r || !row_valid) pr = 0.f;
+            ds2[u] = pr * (__uint_as_float(dr[2 * e + u]) - dlt);
+          }
+          w[e] = pack_bf16x2(ds2[0], ds2[1]);
+        }
       }
       tmem_st_32x16(tdp, w);                          // in place: the first 16 of the 32 columns just read
       tmem_st_wait();
@@ -262,11 +271,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       if (row_valid) {
 #pragma unroll
         for (int e = 0; e < 32; e += 8) {
-          uint4 o;
-          o.x = pack_bf16x2(__uint_as_float(rr[e]), __uint_as_float(rr[e + 1]));
-          o.y = pack_bf16x2(__uint_as_float(rr[e + 2]), __uint_as_float(rr[e + 3]));
-          o.z = pack_bf16x2(__uint_as_float(rr[e + 4]), __uint_as_float(rr[e + 5]));
-          o.w = pack_bf16x2(__uint_as_float(rr[e + 6]), __uint_as_float(rr[e + 7]));
+          uint4 o;      // dS was formed without the softmax scale: apply it once here
+          o.x = pack_bf16x2(__uint_as_float(rr[e]) * p.scale, __uint_as_float(rr[e + 1]) * p.scale);
+          o.y = pack_bf16x2(__uint_as_float(rr[e + 2]) * p.scale, __uint_as_float(rr[e + 3]) * p.scale);
+          o.z = pack_bf16x2(__uint_as_float(rr[e + 4]) * p.scale, __uint_as_float(rr[e + 5]) * p.scale);
+          o.w = pack_bf16x2(__uint_as_float(rr[e + 6]) * p.scale, __uint_as_float(rr[e + 7]) * p.scale);
           *reinterpret_cast<uint4*>(orow + col + e) = o;
         }
       }
@@ -413,6 +422,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     const bool key_valid = kk < p.T;
     const uint32_t lane_off = static_cast<uint32_t>(qtr * 32) << 16;
     bool ok = true;     // after a timed-out wait the thread keeps meeting its peers at the named barrier, idle
+    const bool plain_causal = p.row_start == nullptr && p.window_left < 0 && k0 + BT <= p.T;
     for (int hx = 0; hx < n_half; ++hx) {
       const int it = hx >> 1, hf = hx & 1, st = it & 1, buf = hx & 1;
       const int hq = g * group + it / tiles_per_head;
@@ -442,20 +452,41 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       tmem_ld_32x32(tdp, dr);
       tmem_ld_wait();
       uint32_t wp[16], wd[16];
+      const float sl2 = p.scale_log2;
+      // every (key, query) pair of the tile is visible: queries at or after the last key, no window / document bound
+      const bool full_tile = plain_causal && q0 >= k0 + BT - 1 && q0 + BT <= p.T;
+      if (full_tile) {
+        const float4* l4 = reinterpret_cast<const float4*>(a_lse + cbase);
+        const float4* d4 = reinterpret_cast<const float4*>(a_dlt + cbase);
 #pragma unroll
-      for (int e = 0; e < 16; ++e) {
-        float pv[2], dv2[2];
+        for (int v4 = 0; v4 < 8; ++v4) {
+          const float4 ls = l4[v4], dl = d4[v4];
+          const float lsa[4] = {ls.x, ls.y, ls.z, ls.w}, dla[4] = {dl.x, dl.y, dl.z, dl.w};
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int col = cbase + 2 * e + u;
-          const int rq = q0 + col;
-          float pr = exp2f(__uint_as_float(sr[2 * e + u]) * p.scale_log2 - a_lse[col]);
-          if (!key_valid || kk > rq || kk < a_lo[col]) pr = 0.f;
-          pv[u] = pr;
-          dv2[u] = pr * (__uint_as_float(dr[2 * e + u]) - a_dlt[col]) * p.scale;
+          for (int h2 = 0; h2 < 2; ++h2) {
+            const int c = 4 * v4 + 2 * h2;
+            const float p0 = exp2f(fmaf(__uint_as_float(sr[c]), sl2, -lsa[2 * h2]));
+            const float p1 = exp2f(fmaf(__uint_as_float(sr[c + 1]), sl2, -lsa[2 * h2 + 1]));
+            wp[c >> 1] = pack_bf16x2(p0, p1);
+            wd[c >> 1] = pack_bf16x2(p0 * (__uint_as_float(dr[c]) - dla[2 * h2]), p1 * (__uint_as_float(dr[c + 1]) - dla[2 * h2 + 1]));
+          }
         }
-        wp[e] = pack_bf16x2(pv[0], pv[1]);
-        wd[e] = pack_bf16x2(dv2[0], dv2[1]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          float pv[2], dv2[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int col = cbase + 2 * e + u;
+            const int rq = q0 + col;
+            float pr = exp2f(fmaf(__uint_as_float(sr[2 * e + u]), sl2, -a_lse[col]));
+            if (!key_valid || kk > rq || kk < a_lo[col]) pr = 0.f;
+            pv[u] = pr;
+            dv2[u] = pr * (__uint_as_float(dr[2 * e + u]) - a_dlt[col]);
+          }
+          wp[e] = pack_bf16x2(pv[0], pv[1]);
+          wd[e] = pack_bf16x2(dv2[0], dv2[1]);
+        }
       }
       tmem_st_32x16(ts, wp);
       tmem_st_32x16(tdp, wd);
@@ -472,6 +503,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     for (int which = 0; which < 2; ++which) {
       __nv_bfloat16* orow = (which ? p.dk : p.dv) + obase;
       const uint32_t tsrc = which ? T_DK : T_DV;
+      const float osc = which ? p.scale : 1.f;     // dSᵀ was formed without the softmax scale
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) {
         const int col = ch * (D / 2) + c * 32;
@@ -485,10 +517,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #pragma unroll
           for (int e = 0; e < 32; e += 8) {
             uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(rr[e]), __uint_as_float(rr[e + 1]));
-            o.y = pack_bf16x2(__uint_as_float(rr[e + 2]), __uint_as_float(rr[e + 3]));
-            o.z = pack_bf16x2(__uint_as_float(rr[e + 4]), __uint_as_float(rr[e + 5]));
-            o.w = pack_bf16x2(__uint_as_float(rr[e + 6]), __uint_as_float(rr[e + 7]));
+            o.x = pack_bf16x2(__uint_as_float(rr[e]) * osc, __uint_as_float(rr[e + 1]) * osc);
+            o.y = pack_bf16x2(__uint_as_float(rr[e + 2]) * osc, __uint_as_float(rr[e + 3]) * osc);
+            o.z = pack_bf16x2(__uint_as_float(rr[e + 4]) * osc, __uint_as_float(rr[e + 5]) * osc);
+            o.w = pack_bf16x2(__uint_as_float(rr[e + 6]) * osc, __uint_as_float(rr[e + 7]) * osc);
             *reinterpret_cast<uint4*>(orow + col + e) = o;
           }
         }

@@ -591,26 +591,36 @@ class FSDPEngine:
     def clip_grad_norm_(self, max_norm: float, eps: float = 1e-6) -> torch.Tensor:
         """Global L2 norm over all gradient shards (+ scale when above ``max_norm``);
         the role of ``fabric.clip_gradients`` (`pretrain.py:965-971`)."""
-        sq_sharded = torch.zeros((), dtype=torch.float32, device=self.device)
-        sq_local = torch.zeros((), dtype=torch.float32, device=self.device)
+        # accumulators indexed [needs a sum over the fsdp group][parameter is split over the tp group]
+        sq = [[torch.zeros((), dtype=torch.float32, device=self.device) for _ in range(2)] for _ in range(2)]
         grads = []
+        tp_on = self.mesh.tp > 1
+        if tp_on:
+            from .tp import _replicated_mask
         for g in self.groups():
             if g.grad is None:
                 continue
             grads.append(g.grad)
-            s = g.grad.float().pow(2).sum()
-            if g.world > 1 or getattr(g, "ep_local", False):
-                sq_sharded += s
+            fs = 1 if (g.world > 1 or getattr(g, "ep_local", False)) else 0
+            g2 = g.grad.float().pow(2)
+            mask = _replicated_mask(g) if tp_on else True
+            if mask is True:
+                sq[fs][0] += g2.sum()
+            elif mask is None:
+                sq[fs][1] += g2.sum()
             else:
-                sq_local += s
+                sq[fs][0] += (g2 * mask).sum()
+                sq[fs][1] += (g2 * (1 - mask)).sum()
         if self.mesh.fsdp > 1:
-            du.all_reduce_sum(sq_sharded, group=self.mesh.fsdp_group)
-        total = torch.sqrt(sq_sharded + sq_local)
-        if self.mesh.tp > 1:
-            # tensor-parallel ranks hold different slices of the sharded matrices
-            t2 = total.pow(2)
-            du.all_reduce_sum(t2, group=self.mesh.tp_group)
-            total = torch.sqrt(t2)
+            both = torch.stack(sq[1])
+            du.all_reduce_sum(both, group=self.mesh.fsdp_group)
+            sq[1] = [both[0], both[1]]
+        rep, split = sq[0][0] + sq[1][0], sq[0][1] + sq[1][1]
+        if tp_on:
+            # tensor-parallel ranks hold different slices of the split matrices; unsplit parameters count once
+            split = split.clone()
+            du.all_reduce_sum(split, group=self.mesh.tp_group)
+        total = torch.sqrt(rep + split)
         if max_norm is not None and max_norm > 0:
             coef = torch.clamp(max_norm / (total + eps), max=1.0)
             if grads:

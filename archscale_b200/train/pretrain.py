@@ -450,20 +450,32 @@ class Trainer:
             batch_dev = batch_dev.reshape(1, -1)
         input_ids = batch_dev[:, :T].contiguous()
         targets = batch_dev[:, 1:T + 1].contiguous()
+        tp = self.mesh.tp
+        if tp > 1:
+            # the model returns this rank's slice of the sequence; the global loss is the mean of the tp ranks' means
+            from archscale_b200.parallel.tp import sequence_slice
+            targets = sequence_slice(targets, tp, self.mesh.tp_rank).contiguous()
         if p.use_flce_loss:
             out = self.model(input_ids, use_flce_loss=True)
             loss = self.loss_func(out.logits, out.weight, targets)
         else:
             loss = self.loss_func(self.model(input_ids).logits, targets)
-        back = loss
+        back = loss / tp if tp > 1 else loss
         bal = None
         if self.config.moe:
             bal = self.model.aux_loss
             back = back + bal
         self.engine.backward(back / accum if accum != 1 else back)
-        return loss.detach(), (bal.detach() if isinstance(bal, torch.Tensor) else None)
+        loss = loss.detach()
+        if tp > 1:
+            loss = loss / tp
+            du.all_reduce_sum(loss, group=self.mesh.tp_group)
+        return loss, (bal.detach() if isinstance(bal, torch.Tensor) else None)
 
     def optimizer_step(self, lr: float):
+        if self.mesh.tp > 1:
+            from archscale_b200.parallel.tp import sync_replicated_grads
+            sync_replicated_grads(self.engine, self.mesh)
         gn = self.engine.clip_grad_norm_(self.plan.grad_clip)
         self.optimizer.step(lr=lr)
         self.optimizer.zero_grad()

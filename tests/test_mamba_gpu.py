@@ -104,3 +104,25 @@ def test_mamba_block_runs_on_kernels():
     assert backend.launches() - before >= 4
     assert torch.isfinite(out.float()).all() and torch.isfinite(x.grad.float()).all()
     assert m.A_log.grad is not None and torch.isfinite(m.A_log.grad).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,cols", [(257, 2560), (64, 512), (1000, 1032)])
+def test_layernorm_kernel(dtype, rows, cols):
+    from archscale_b200.ops.norm import layer_norm, layer_norm_ref
+    dev = _dev()
+    torch.manual_seed(4)
+    x = (torch.randn(rows, cols, device=dev) * 2 + 0.5).to(dtype).requires_grad_(True)
+    w = torch.randn(cols, device=dev).requires_grad_(True)
+    b = torch.randn(cols, device=dev).requires_grad_(True)
+    y = layer_norm(x, w, b, 1e-5)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr, br = x.detach().float().requires_grad_(True), w.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    yr = layer_norm_ref(xr, wr, br, 1e-5)
+    yr.backward(g.float())
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    assert torch.allclose(y.float(), yr, atol=tol, rtol=tol)
+    assert torch.allclose(x.grad.float(), xr.grad, atol=tol * 4, rtol=tol * 4)
+    for a, r in ((w.grad, wr.grad), (b.grad, br.grad)):
+        assert (a - r).abs().max().item() <= (2e-4 if dtype == torch.float32 else 2e-2) * max(1.0, r.abs().max().item())
