@@ -478,9 +478,10 @@ class GPT(nn.Module):
         if self.scale_embed:
             x = x * math.sqrt(cfg.n_embd)
         if getattr(self, "tp_size", 1) > 1:
-            # tensor + sequence parallelism: between blocks each rank carries its slice of the sequence
-            from archscale_b200.parallel.tp import sequence_slice
-            x = sequence_slice(x, self.tp_size, self.tp_rank).contiguous()
+            # tensor + sequence parallelism: between blocks each rank carries a 1/tp chunk of the flattened tokens
+            from archscale_b200.parallel.tp import token_slice
+            self._tp_batch_shape = (B, T)
+            x = token_slice(x, self.tp_size, self.tp_rank).contiguous()
         input_embed = x
         kv_cache = gmu_mems = None
         self.lc_gate_hist, self.tokens_per_expert, self.token_indices = [], [], []

@@ -136,6 +136,14 @@ int b200_layernorm_fwd(const void* x, int dtype, const float* w, const float* bi
 int b200_layernorm_bwd(const void* dy, const void* x, int dtype, const float* w, const float* mean, const float* rstd, void* dx,
                        float* part, float* dw, float* db, int rows, int cols, cudaStream_t st);
 
+// Tensor-parallel fused layers (gemm_bf16.cu): activation all-gather → GEMM, and GEMM → reduce-scatter over peer memory.
+int b200_ag_a_gemm_bf16(const void* const* bases, size_t src_off, void* dst, size_t shard_bytes, const void* B, void* out, int M,
+                        int N, int K, int ldb, int ldc, uint32_t* flags, uint32_t epoch, int rank, int world, int n_copy,
+                        int num_sms, int* status, cudaStream_t stream);
+int b200_gemm_rs_bf16(const void* A, const void* B, int M, int N, int K, int lda, int ldb, const void* const* bases,
+                      size_t part_off, size_t cnt_off, uint32_t expect, void* out_local, int rank, int world, int num_sms,
+                      int* status, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -41,8 +41,26 @@ struct AgParams {
   uint32_t* flags;         // one per chunk of dst, value = epoch when the chunk is complete
   uint32_t epoch;
   int rank, world, n_copy;
+  int gather_a;            // 1: the gathered buffer is the A operand ([M, K] rows in rank order) instead of B
+  size_t a_off;            // byte offset of A inside dst (gather_a)
 };
 constexpr size_t AG_CHUNK = 256 * 1024;
+
+// GEMM with the reduce-scatter of its output fused in (tensor-parallel row-parallel layer, FUSED_AG = 2):
+// every rank computes the full [M, N] partial product into `part` (its symmetric heap), finishing the row blocks of
+// the other ranks' slices first and its own last; each epilogue warp bumps a per-row-block counter (release, system
+// scope) after its stores.  By the time a rank reaches the tiles of its own slice its peers have (at equal speed)
+// finished theirs for those rows: the epilogue of an own tile waits (bounded) for the peers' counters, adds their
+// partial rows with loads from peer memory to the accumulator it just read from TMEM and writes `out_local`
+// [M / world, N] — the transfer of a tile overlaps the main loop of the next one.
+struct RsParams {
+  const void* peer[8];     // heap bases as mapped in this process
+  size_t part_off;         // offset of the [M, N] bf16 partial-product buffer in every heap
+  size_t cnt_off;          // offset of the per-row-block counters (uint32, one per 128 rows) in every heap
+  uint32_t expect;         // counter value that marks a complete row block for this call (4 warps · N tiles · calls)
+  int rank, world;
+  __nv_bfloat16* out_local;
+};
 
 // Grouped (mixture-of-experts) GEMMs.  Activations are stored expert-sorted with every expert's segment
 // starting at a multiple of 128 rows (offsets[E+1], device memory, written by the routing kernels):
@@ -175,14 +193,14 @@ struct Tile {
 template <int A_MN, int B_MN, int OUT_F32, int FUSED_AG = 0, int GROUPED = 0>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const GemmParams p, const AgParams ag, const GroupParams gp) {
-  if (FUSED_AG && static_cast<int>(blockIdx.x) < ag.n_copy) {   // copier CTAs: lowest indices, scheduled first
+                 const GemmParams p, const AgParams ag, const GroupParams gp, const RsParams rs) {
+  if (FUSED_AG == 1 && static_cast<int>(blockIdx.x) < ag.n_copy) {   // copier CTAs: lowest indices, scheduled first
     extern __shared__ uint8_t smem_copier[];
     ag_copier(ag, reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_copier) + 1023) & ~uintptr_t(1023)), p.status);
     return;
   }
-  const int cta = FUSED_AG ? static_cast<int>(blockIdx.x) - ag.n_copy : static_cast<int>(blockIdx.x);
-  const int n_cta = FUSED_AG ? static_cast<int>(gridDim.x) - ag.n_copy : static_cast<int>(gridDim.x);
+  const int cta = FUSED_AG == 1 ? static_cast<int>(blockIdx.x) - ag.n_copy : static_cast<int>(blockIdx.x);
+  const int n_cta = FUSED_AG == 1 ? static_cast<int>(gridDim.x) - ag.n_copy : static_cast<int>(gridDim.x);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -226,6 +244,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int r = t - g * per_group;
     m_idx = first_m + (r % gsz);
     n_idx = r / gsz;
+    if (FUSED_AG == 2) {       // row blocks of the next rank's slice first, this rank's own slice last
+      const int per = num_m / rs.world;
+      m_idx = (m_idx + ((rs.rank + 1) % rs.world) * per) % num_m;
+    }
   };
   auto get_tile = [&](int t, Tile& tl) {
     if (GROUPED == 3) {          // batched: gp.E matrices of identical shape, 3-D tensor maps
@@ -257,10 +279,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int t = cta; t < num_tiles; t += n_cta) {
         Tile tl; get_tile(t, tl);
         const int m0 = tl.m0, n0 = tl.n0;
-        if (FUSED_AG) {
+        if (FUSED_AG == 1) {
           const size_t row_bytes = static_cast<size_t>(p.K) * 2;
-          const int n_hi = n0 + BN < p.N ? n0 + BN : p.N;
-          if (!ag_wait(ag, ag.b_off + n0 * row_bytes, ag.b_off + n_hi * row_bytes, abort_flag, p.status)) goto done;
+          if (ag.gather_a) {
+            const int m_hi = m0 + BM < p.M ? m0 + BM : p.M;
+            if (!ag_wait(ag, ag.a_off + m0 * row_bytes, ag.a_off + m_hi * row_bytes, abort_flag, p.status)) goto done;
+          } else {
+            const int n_hi = n0 + BN < p.N ? n0 + BN : p.N;
+            if (!ag_wait(ag, ag.b_off + n0 * row_bytes, ag.b_off + n_hi * row_bytes, abort_flag, p.status)) goto done;
+          }
         }
         for (int kb = tl.kb0; kb < tl.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) goto done;
@@ -346,6 +373,38 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int col0 = tl.n0;
       const int row_limit = GROUPED == 1 ? s_off[gp.E] : p.M;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      // FUSED_AG == 2: a tile of this rank's own slice is finished here — the peers computed their partial products of
+      // these rows first, so the epilogue adds them (loads from peer memory) and writes the reduced rows directly.
+      bool own_tile = false;
+      if (FUSED_AG == 2) {
+        const int per = num_m / rs.world;
+        const int blk = tl.m0 / BM;
+        own_tile = blk / per == rs.rank;
+        if (own_tile) {
+          bool ok = true;
+          if (lane == 0) {
+            for (int pq = 0; pq < rs.world && ok; ++pq) {
+              if (pq == rs.rank) continue;
+              const uint32_t* cq = reinterpret_cast<const uint32_t*>(static_cast<const char*>(rs.peer[pq]) + rs.cnt_off) + blk;
+              const long long t0 = clock64();
+              while (true) {
+                uint32_t v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(cq) : "memory");
+                if (static_cast<int32_t>(v - rs.expect) >= 0) break;
+                if (*abort_flag || clock64() - t0 > kWaitLimitCycles * 8) {
+                  *abort_flag = 1;
+                  if (p.status) atomicCAS(p.status, 0, STATUS_TIMEOUT_PEER);
+                  ok = false;
+                  break;
+                }
+                __nanosleep(200);
+              }
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          if (!ok) goto done;
+        }
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -373,6 +432,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           } else {
             __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + tl.out_off + static_cast<size_t>(row) * p.ldc + col;
+            if (FUSED_AG == 2 && own_tile)
+              o = rs.out_local + static_cast<size_t>(row - rs.rank * (num_m / rs.world) * BM) * p.N + col;
             const __nv_bfloat16* ci = p.cin ? reinterpret_cast<const __nv_bfloat16*>(p.cin) + tl.out_off + static_cast<size_t>(row) * p.ldc + col : nullptr;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
@@ -380,6 +441,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 float f[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[j + e]) * p.alpha;
+                if (FUSED_AG == 2 && own_tile) {
+#pragma unroll
+                  for (int pq = 0; pq < 8; ++pq) {
+                    if (pq < rs.world && pq != rs.rank) {
+                      const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(static_cast<const char*>(rs.peer[pq]) + rs.part_off) +
+                                                 static_cast<size_t>(row) * p.ldc + col + j;
+                      const uint4 pv = *reinterpret_cast<const uint4*>(src);
+                      const uint32_t pw[4] = {pv.x, pv.y, pv.z, pv.w};
+#pragma unroll
+                      for (int e = 0; e < 4; ++e) {
+                        const float2 c2 = unpack_bf16x2(pw[e]);
+                        f[2 * e] += c2.x; f[2 * e + 1] += c2.y;
+                      }
+                    }
+                  }
+                }
                 if (ci) {
                   const uint4 cv = *reinterpret_cast<const uint4*>(ci + j);
                   const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
@@ -401,6 +478,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (FUSED_AG == 2 && !own_tile) {
+        // this warp's 32 rows × 256 columns of the tile are stored: publish them to the peers
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          uint32_t* cnt = reinterpret_cast<uint32_t*>(const_cast<char*>(static_cast<const char*>(rs.peer[rs.rank])) + rs.cnt_off);
+          asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt + tl.m0 / BM) : "memory");
+        }
+      }
     }
   }
 
@@ -475,7 +561,7 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const Ge
   const int grid = tiles < sms ? tiles : sms;
   AgParams none{};
   GroupParams nog{};
-  kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb, p, none, nog);
+  kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb, p, none, nog, RsParams{});
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -547,7 +633,87 @@ extern "C" int b200_ag_gemm_bf16(const void* A, void* out, int M, int N, int K, 
   if (compute > tiles) compute = tiles;
   if (compute < 1) return -6;
   GroupParams nog{};
-  kern<<<compute + n_copy, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, ag, nog);
+  kern<<<compute + n_copy, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, ag, nog, RsParams{});
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// Tensor-parallel column-parallel layer: out[M,N] (bf16) = A[M,K] · B[N,K]ᵀ where A is the concatenation, in rank order,
+// of every rank's [M/world, K] activation chunk (at `src_off` of each symmetric heap).  The same launch pulls the chunks
+// into the local buffer `dst` ([M, K], ordinary device memory) and multiplies row blocks as they arrive.
+extern "C" int b200_ag_a_gemm_bf16(const void* const* bases, size_t src_off, void* dst, size_t shard_bytes, const void* B,
+                                   void* out, int M, int N, int K, int ldb, int ldc, uint32_t* flags, uint32_t epoch, int rank,
+                                   int world, int n_copy, int num_sms, int* status, cudaStream_t stream) {
+  using namespace b200;
+  if (M <= 0 || N <= 0 || K <= 0 || world > 8 || (shard_bytes % 16)) return -1;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return -5;
+    ctx_bound = true;
+  }
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d_bf16(&ta, dst, K, M, K, BK, BM);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tb, B, K, N, ldb, BK, BN);
+  if (rc) return rc;
+  GemmParams p{out, nullptr, M, N, K, ldc, 1.f, 0.f, 0, status};
+  AgParams ag{};
+  for (int i = 0; i < 8; ++i) ag.peer[i] = i < world ? bases[i] : nullptr;
+  ag.src_off = src_off; ag.dst = static_cast<char*>(dst); ag.shard_bytes = shard_bytes; ag.b_off = 0;
+  ag.flags = flags; ag.epoch = epoch; ag.rank = rank; ag.world = world; ag.n_copy = n_copy;
+  ag.gather_a = 1; ag.a_off = 0;
+  auto kern = gemm_bf16_kernel<0, 0, 0, 1>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess) return -2;
+    configured = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int compute = num_sms - n_copy;
+  if (compute > tiles) compute = tiles;
+  if (compute < 1) return -6;
+  GroupParams nog{};
+  kern<<<compute + n_copy, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, ag, nog, RsParams{});
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// Tensor-parallel row-parallel layer: out_local[M/world, N] (bf16) = this rank's rows of Σ_ranks A_r[M,K_r] · B_r[N,K_r]ᵀ.
+// `part_off` / `cnt_off`: the [M, N] bf16 partial-product buffer and the per-128-row counters inside every symmetric heap;
+// `expect` = counter value of a finished row block after this call (counters only grow: add 4 · ceil(N/256) per call).
+// Every rank must launch the same call; the grid is at most one CTA per SM so all CTAs are resident while they wait.
+extern "C" int b200_gemm_rs_bf16(const void* A, const void* B, int M, int N, int K, int lda, int ldb, const void* const* bases,
+                                 size_t part_off, size_t cnt_off, uint32_t expect, void* out_local, int rank, int world,
+                                 int num_sms, int* status, cudaStream_t stream) {
+  using namespace b200;
+  if (M <= 0 || N <= 0 || K <= 0 || world < 1 || world > 8 || M % (BM * world) || N % 8 || (part_off % 16) || (cnt_off % 4)) return -1;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return -5;
+    ctx_bound = true;
+  }
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d_bf16(&ta, A, K, M, lda, BK, BM);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tb, B, K, N, ldb, BK, BN);
+  if (rc) return rc;
+  void* part = const_cast<char*>(static_cast<const char*>(bases[rank])) + part_off;
+  GemmParams p{part, nullptr, M, N, K, N, 1.f, 0.f, 0, status};
+  RsParams rs{};
+  for (int i = 0; i < 8; ++i) rs.peer[i] = i < world ? bases[i] : nullptr;
+  rs.part_off = part_off; rs.cnt_off = cnt_off; rs.expect = expect; rs.rank = rank; rs.world = world;
+  rs.out_local = static_cast<__nv_bfloat16*>(out_local);
+  auto kern = gemm_bf16_kernel<0, 0, 0, 2>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess) return -2;
+    configured = true;
+  }
+  const int tiles = (M / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  AgParams none{};
+  GroupParams nog{};
+  kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, none, nog, rs);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -585,12 +751,12 @@ extern "C" int b200_grouped_gemm_bf16(int kind, const void* A, const void* B, vo
       auto kern = gemm_bf16_kernel<0, 0, 0, 0, 1>;
       static bool cfg = false;
       if (!cfg) { if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess) return -2; cfg = true; }
-      kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, none, gp);
+      kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, none, gp, RsParams{});
     } else {
       auto kern = gemm_bf16_kernel<0, 1, 0, 0, 1>;
       static bool cfg = false;
       if (!cfg) { if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess) return -2; cfg = true; }
-      kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, none, gp);
+      kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, none, gp, RsParams{});
     }
   } else if (kind == 2) {
     // A: [capacity, M] (MN-major), B: [capacity, N] (MN-major); K = rows of the expert's segment
@@ -605,12 +771,12 @@ extern "C" int b200_grouped_gemm_bf16(int kind, const void* A, const void* B, vo
       auto kern = gemm_bf16_kernel<1, 1, 1, 0, 2>;
       static bool cfg = false;
       if (!cfg) { if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess) return -2; cfg = true; }
-      kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, none, gp);
+      kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, none, gp, RsParams{});
     } else {
       auto kern = gemm_bf16_kernel<1, 1, 0, 0, 2>;
       static bool cfg = false;
       if (!cfg) { if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess) return -2; cfg = true; }
-      kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, none, gp);
+      kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, none, gp, RsParams{});
     }
   } else {
     return -4;
@@ -646,12 +812,12 @@ extern "C" int b200_gemm_bf16_batched(int mode, const void* A, const void* B, vo
     auto kern = gemm_bf16_kernel<0, 0, 0, 0, 3>;
     static bool cfg = false;
     if (!cfg) { if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess) return -2; cfg = true; }
-    kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, none, gp);
+    kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, none, gp, RsParams{});
   } else {
     auto kern = gemm_bf16_kernel<0, 1, 0, 0, 3>;
     static bool cfg = false;
     if (!cfg) { if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) != cudaSuccess) return -2; cfg = true; }
-    kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, none, gp);
+    kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p, none, gp, RsParams{});
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

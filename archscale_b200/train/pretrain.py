@@ -325,6 +325,9 @@ class Trainer:
         if self.config.tp_size > 1:
             from archscale_b200.parallel import tp as tp_mod
             tp_mod.apply_tensor_parallel(self.model, mesh)
+            if fused_comm:
+                # all-gather→GEMM and GEMM→reduce-scatter over peer memory for the column- / row-parallel layers
+                tp_mod.enable_fused_layers(self.model, mesh, device, p.micro_batch_size * self.config.block_size)
         if self.config.ep_size > 1:
             from archscale_b200.parallel import ep as ep_mod
             ep_mod.attach(self.model, mesh)
@@ -452,9 +455,9 @@ class Trainer:
         targets = batch_dev[:, 1:T + 1].contiguous()
         tp = self.mesh.tp
         if tp > 1:
-            # the model returns this rank's slice of the sequence; the global loss is the mean of the tp ranks' means
-            from archscale_b200.parallel.tp import sequence_slice
-            targets = sequence_slice(targets, tp, self.mesh.tp_rank).contiguous()
+            # the model returns this rank's chunk of the tokens; the global loss is the mean of the tp ranks' means
+            from archscale_b200.parallel.tp import token_slice
+            targets = token_slice(targets, tp, self.mesh.tp_rank).contiguous()
         if p.use_flce_loss:
             out = self.model(input_ids, use_flce_loss=True)
             loss = self.loss_func(out.logits, out.weight, targets)

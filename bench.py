@@ -124,9 +124,9 @@ def run_ours(args) -> None:
     os.environ.setdefault("LIGHTNING_ARTIFACTS_DIR", os.path.join(tempfile.gettempdir(), "archscale_b200_bench"))
     ep = world if (args.config == "moe" and world > 1 and not args.no_ep) else 1
     kwargs = dict(train_data_dir="synthetic", train_model=c["train_model"], depth=c["depth"], train_name=c["train_name"],
-                  micro_bsz=c["micro_bsz"], ctx_len=c["ctx_len"], total_bsz=world * c["micro_bsz"] * c["ctx_len"],
+                  micro_bsz=c["micro_bsz"], ctx_len=c["ctx_len"], total_bsz=(world // max(args.tp, 1)) * c["micro_bsz"] * c["ctx_len"],
                   max_tokens=1e12, use_flce=True, sparsity=c["sparsity"], top_k=c["top_k"],
-                  config_overrides=dict(c["overrides"]), ep=ep, fused_comm=args.fused_comm, fp8=args.fp8,
+                  config_overrides=dict(c["overrides"]), ep=ep, tp=args.tp, fused_comm=args.fused_comm, fp8=args.fp8,
                   return_trainer=True, quiet=True)
     for k in ("share_expert", "sqrt_gate", "global_aux", "aux_gamma"):
         if k in c:
@@ -136,7 +136,7 @@ def run_ours(args) -> None:
     dev = trainer.device
     cfg = trainer.config
     mb, T = c["micro_bsz"], c["ctx_len"]
-    tokens_per_step = world * mb * T
+    tokens_per_step = (world // max(args.tp, 1)) * mb * T      # tensor-parallel peers share a micro-batch
     lr = trainer.plan.learning_rate
 
     g = torch.Generator().manual_seed(0 * 1000003 + trainer.mesh.data_rank)
@@ -202,7 +202,8 @@ def run_ours(args) -> None:
             "tokens_per_sec_per_gpu": value / world,
             "mfu": flops_step / (ms_per_step / 1e3) / 2.25e15,
             "config": {"model": c["name"], "global_batch": world * mb, "seq_len": T,
-                       "parallelism": (f"fsdp{world}" if world > 1 else "single") + (f"+ep{ep}" if ep > 1 else ""),
+                       "parallelism": (f"fsdp{world // max(args.tp, 1)}" if world > 1 else "single") + (f"+ep{ep}" if ep > 1 else "")
+                                      + (f"+tp{args.tp}" if args.tp > 1 else ""),
                        "optimizer": "MuonH (Newton-Schulz 5) + AdamW/Adam-H, grad clip 1.0",
                        "l2": "per-step working set (weights + activations, > 10 GB) far exceeds the 126 MB L2; "
                              "no explicit flush",
@@ -237,6 +238,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="dense", choices=sorted(CONFIGS))
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (ranks of a tp group share a micro-batch)")
     ap.add_argument("--fp8", action="store_true", help="MXFP8 block-scaled linear layers (dtype is then reported as mxfp8)")
     ap.add_argument("--fused-comm", dest="fused_comm", action="store_true")
     ap.add_argument("--no-ep", dest="no_ep", action="store_true")

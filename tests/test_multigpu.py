@@ -26,3 +26,12 @@ def test_expert_parallel_peer_transport_matches_all_to_all():
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "SELFTEST EP PASS" in r.stdout
+
+
+def test_tensor_parallel_fused_layers_match_nccl():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", "29673", "-m", "archscale_b200.parallel.selftest_tp"]
+    r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "selftest_tp PASS" in r.stdout
