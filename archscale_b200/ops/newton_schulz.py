@@ -23,7 +23,23 @@ NS_COEFFS = (
 )
 
 
-def newton_schulz_ref(G: torch.Tensor, epsilon: float = 1e-7, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+# Polar-Express coefficient schedule of the matrix-sign iteration used by MuonBall
+# (`emerging_optimizers/orthogonalized_optimizers/spectral_ball_utils.py:55-64`); steps beyond the 8th repeat the last set.
+POLAR_EXPRESS_COEFFS = (
+    (8.2051, -22.9019, 16.4607),
+    (4.0664, -2.8612, 0.5184),
+    (3.9096, -2.8234, 0.5250),
+    (3.2856, -2.4153, 0.4853),
+    (2.2779, -1.6198, 0.3985),
+    (1.8726, -1.2307, 0.3585),
+    (1.8564, -1.2132, 0.3568),
+    (1.8750, -1.2500, 0.3750),
+)
+
+
+def newton_schulz_ref(G: torch.Tensor, epsilon: float = 1e-7, dtype: torch.dtype = torch.bfloat16,
+                      coeffs=None) -> torch.Tensor:
+    NS_COEFFS = coeffs if coeffs is not None else globals()["NS_COEFFS"]
     X = G.to(dtype)
     tall = G.size(-2) > G.size(-1)
     if tall:
@@ -36,7 +52,8 @@ def newton_schulz_ref(G: torch.Tensor, epsilon: float = 1e-7, dtype: torch.dtype
     return X.mT if tall else X
 
 
-def _ns_cuda_2d(G: torch.Tensor, epsilon: float) -> torch.Tensor:
+def _ns_cuda_2d(G: torch.Tensor, epsilon: float, coeffs=None) -> torch.Tensor:
+    NS_COEFFS = coeffs if coeffs is not None else globals()["NS_COEFFS"]
     ext = backend.require_extension()
     X = G.to(torch.bfloat16)
     tall = G.size(-2) > G.size(-1)
@@ -54,8 +71,9 @@ def _ns_cuda_2d(G: torch.Tensor, epsilon: float) -> torch.Tensor:
     return X.t() if tall else X
 
 
-def _ns_cuda_batched(G: torch.Tensor, epsilon: float) -> torch.Tensor:
+def _ns_cuda_batched(G: torch.Tensor, epsilon: float, coeffs=None) -> torch.Tensor:
     """G:(B,m,n) — all B matrices advance together: 3 batched tcgen05 GEMM launches per iteration."""
+    NS_COEFFS = coeffs if coeffs is not None else globals()["NS_COEFFS"]
     ext = backend.require_extension()
     X = G.to(torch.bfloat16)
     tall = G.size(-2) > G.size(-1)
@@ -70,14 +88,14 @@ def _ns_cuda_batched(G: torch.Tensor, epsilon: float) -> torch.Tensor:
     return X.mT if tall else X
 
 
-def newton_schulz(G: torch.Tensor, epsilon: float = 1e-7) -> torch.Tensor:
-    """Orthogonalise the last two dims of ``G`` (2-D or batched 3-D)."""
+def newton_schulz(G: torch.Tensor, epsilon: float = 1e-7, coeffs=None) -> torch.Tensor:
+    """Orthogonalise the last two dims of ``G`` (2-D or batched 3-D); ``coeffs`` overrides the (a, b, c) schedule."""
     m, n = G.shape[-2], G.shape[-1]
     if (G.is_cuda and min(m, n) % 8 == 0 and max(m, n) % 8 == 0 and min(m, n) >= 64
             and backend.use_cuda_kernel("newton_schulz", G)):
         if G.dim() == 2:
-            return _ns_cuda_2d(G, epsilon)
+            return _ns_cuda_2d(G, epsilon, coeffs)
         if backend.has("gemm_bf16_batched"):
-            return _ns_cuda_batched(G.reshape(-1, m, n), epsilon).reshape(G.shape)
-        return torch.stack([_ns_cuda_2d(g, epsilon) for g in G.reshape(-1, m, n)]).reshape(G.shape)
-    return newton_schulz_ref(G, epsilon)
+            return _ns_cuda_batched(G.reshape(-1, m, n), epsilon, coeffs).reshape(G.shape)
+        return torch.stack([_ns_cuda_2d(g, epsilon, coeffs) for g in G.reshape(-1, m, n)]).reshape(G.shape)
+    return newton_schulz_ref(G, epsilon, coeffs=coeffs)

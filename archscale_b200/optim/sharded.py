@@ -251,6 +251,10 @@ class ShardedOptimizer:
         eng.mark_params_updated()
 
     # ------------------------------------------------------------------ Muon transport + NS
+    def _orthogonalise(self, stack: torch.Tensor) -> torch.Tensor:
+        """(B, rows, cols) pre-orthogonalisation updates → orthogonalised updates (overridden by MuonBall)."""
+        return ops.newton_schulz(stack, epsilon=self.ns_epsilon)
+
     @torch.no_grad()
     def _orthogonalised_updates(self, u_sq: torch.Tensor) -> Dict[int, torch.Tensor]:
         """Returns {id(group): bf16/fp32 shard-shaped tensor with the orthogonalised update O};
@@ -301,7 +305,7 @@ class ShardedOptimizer:
                 by_shape.setdefault((mt.rows, mt.cols), []).append(mt)
             for (r, c), lst in by_shape.items():
                 stack = torch.stack([u_full[mt.offset:mt.offset + r * c].view(r, c) for mt in lst])
-                O = ops.newton_schulz(stack, epsilon=self.ns_epsilon)
+                O = self._orthogonalise(stack)
                 sq = O.float().pow(2).sum(dim=(-2, -1))
                 for i, mt in enumerate(lst):
                     o_full[mt.offset:mt.offset + r * c].copy_(O[i].reshape(-1))

@@ -358,6 +358,22 @@ class Trainer:
             self.resumed = True
 
     # ------------------------------------------------------------------ utils
+    def _health(self):
+        """Heartbeat / abort store shared by the ranks (multi-rank runs only; ARCHSCALE_B200_HEALTH=0 disables)."""
+        if self.mesh.world <= 1 or os.environ.get("ARCHSCALE_B200_HEALTH", "1") == "0":
+            return None
+        try:
+            import torch.distributed as dist
+            from archscale_b200.utils.health import Heartbeat
+            port = int(os.environ.get("MASTER_PORT", "29500")) + 7
+            store = dist.TCPStore(os.environ.get("MASTER_ADDR", "127.0.0.1"), port, self.mesh.world, self.mesh.rank == 0,
+                                  wait_for_workers=False)
+            return Heartbeat(store, self.mesh.rank, self.mesh.world,
+                             stale_after_s=float(os.environ.get("ARCHSCALE_B200_HEARTBEAT_STALE_S", "600")))
+        except Exception as e:  # noqa: BLE001 - failure detection must never stop a healthy run
+            self.print(f"health store unavailable ({e!r}); continuing without heartbeats")
+            return None
+
     def print(self, *a) -> None:
         if self.rank0 and not self.quiet:
             print(*a, flush=True)
@@ -516,10 +532,15 @@ class Trainer:
         log_iter_interval = p.log_step_interval * accum
         self.model.train()
         batch_info = None
+        health = self._health()
         for train_data, is_code in loader:
             lu.drain_logging_queue(self.logger.log_dict, self.print)
             if state["iter_num"] >= max_iters:
                 break
+            if health is not None:
+                # learn about a failed peer on the host, before launching collectives that would wait for it
+                health.check()
+                health.beat(state["iter_num"])
             is_accumulating = (state["iter_num"] + 1) % accum != 0
             if ramp and not is_accumulating:
                 mult = batch_size_rampup_func(state["iter_num"], max_iters, p.bsz_rampup_ratio)
