@@ -18,7 +18,7 @@ module with ``MixedPrecisionPolicy(param_dtype=bf16, reduce_dtype=fp32)``
 
 Collectives are either ``torch.distributed`` (NCCL on GPUs, gloo on CPU test ranks) or the
 peer-memory kernels of :mod:`archscale_b200.parallel.symm` when ``fused_comm`` is on.
-Optimizers consume the flat shards through :meth:`FSDPEngine.shard_views`.
+Optimizers consume the flat shards through :meth:`FSDPEngine.groups` and :meth:`FlatGroup.local_slices`.
 """
 from __future__ import annotations
 
