@@ -144,6 +144,11 @@ int b200_gemm_rs_bf16(const void* A, const void* B, int M, int N, int K, int lda
                       size_t part_off, size_t cnt_off, uint32_t expect, void* out_local, int rank, int world, int num_sms,
                       int* status, cudaStream_t stream);
 
+// Optimizer kernels on flat fp32 shards (optim.cu)
+int b200_muon_momentum(const float* g, float* m, void* u, long long n, float mu, int nesterov, const float* gscale, cudaStream_t st);
+int b200_seg_update(int mode, float* x, const void* u, long long n, const long long* bounds, const int* kidx, int nseg,
+                    const float* coef, float* acc, cudaStream_t st);
+
 #ifdef __cplusplus
 }
 #endif

@@ -193,14 +193,22 @@ class ShardedOptimizer:
         hb_u: List[torch.Tensor] = [t[1] for t in pending_hyper]
         hb_k: List[int] = [t[2] for t in pending_hyper]
         hb_lr: List[float] = [t[3] for t in pending_hyper]
+        seg_groups: List[Tuple[torch.Tensor, torch.Tensor, dict]] = []   # (master prefix, O prefix, tables): fused path
+        lr_m = self._lr_for("matrix")
         if self.mats:
             o_shards = self._orthogonalised_updates(u_sq)
-            lr_m = self._lr_for("matrix")
             wd = self.weight_decay
             xs, os_, ks, adj = [], [], [], []
+            fused_gids = set()
+            for gid, g in {id(mt.group): mt.group for mt in self.mats}.items():
+                tb = self._seg_tables(g) if g.grad is not None else None
+                if tb is not None and o_shards[gid].dtype == torch.bfloat16:
+                    n = tb["n"]
+                    seg_groups.append((g.master[:n], o_shards[gid][:n], tb))
+                    fused_gids.add(gid)
             for mt in self.mats:
                 g = mt.group
-                if g.grad is None:
+                if g.grad is None or id(g) in fused_gids:
                     continue
                 a, b = g.shard_range()
                 lo, hi = max(mt.offset, a), min(mt.offset + mt.rows * mt.cols, b)
@@ -210,6 +218,9 @@ class ShardedOptimizer:
                 os_.append(o_shards[id(g)][lo - a:hi - a])
                 ks.append(mt.norm_idx)
                 adj.append(-self._adjusted_lr(lr_m, mt.rows, mt.cols))
+            if wd:
+                for x, _, _ in seg_groups:
+                    x.mul_(1 - lr_m * wd)
             if xs:
                 if wd:
                     torch._foreach_mul_(xs, 1 - lr_m * wd)
@@ -223,9 +234,19 @@ class ShardedOptimizer:
                 else:
                     upd = torch._foreach_mul([o.to(x.dtype) for o, x in zip(os_, xs)], adj)
                     torch._foreach_add_(xs, upd)
+            if seg_groups:
+                ext = ops.backend.require_extension()
+                if self.use_muonh:
+                    for x, _, tb in seg_groups:
+                        ext.seg_update_(0, x, None, tb["bounds"], tb["kidx"], None, x_sq)
+                else:
+                    for x, o, tb in seg_groups:          # plain Muon: x ← x − lr·sqrt(rows/cols)·O
+                        ext.seg_update_(1, x, o, tb["bounds"], tb["kidx"], self._adjusted_lr_vector(lr_m), self._scratch_acc())
+                    seg_groups = []
+                ops.backend.count_launch(len(seg_groups))
 
         # ---- hyperball: global norms (2 all-reduces for the whole model), update, renormalise
-        if hb_x:
+        if hb_x or seg_groups:
             if eng.mesh.fsdp > 1:
                 packed = torch.stack((x_sq, u_sq))
                 keep = packed[:, self.local_norm_idx].clone() if self.local_norm_idx is not None else None
@@ -234,21 +255,73 @@ class ShardedOptimizer:
                     packed[:, self.local_norm_idx] = keep
                 x_sq, u_sq = packed[0], packed[1]
             x_norm, u_norm = x_sq.sqrt(), u_sq.sqrt().clamp_min(self.ns_epsilon)
-            kidx = torch.tensor(hb_k, device=dev)
-            coef = (x_norm / u_norm)[kidx] * torch.tensor(hb_lr, device=dev, dtype=torch.float32)
-            upd = [u.to(x.dtype) if u.dtype != x.dtype else u for u, x in zip(hb_u, hb_x)]
-            upd = torch._foreach_mul(upd, list(coef.unbind(0)))
-            torch._foreach_sub_(hb_x, upd)
+            ratio = x_norm / u_norm
             new_sq = torch.zeros_like(x_sq)
-            new_sq.index_add_(0, kidx, torch.stack(torch._foreach_norm(hb_x)).square())
+            if hb_x:
+                kidx = torch.tensor(hb_k, device=dev)
+                coef = ratio[kidx] * torch.tensor(hb_lr, device=dev, dtype=torch.float32)
+                upd = [u.to(x.dtype) if u.dtype != x.dtype else u for u, x in zip(hb_u, hb_x)]
+                upd = torch._foreach_mul(upd, list(coef.unbind(0)))
+                torch._foreach_sub_(hb_x, upd)
+                new_sq.index_add_(0, kidx, torch.stack(torch._foreach_norm(hb_x)).square())
+            if seg_groups:
+                ext = ops.backend.require_extension()
+                coef_m = (ratio * lr_m).contiguous()
+                for x, o, tb in seg_groups:
+                    ext.seg_update_(1, x, o, tb["bounds"], tb["kidx"], coef_m, new_sq)
+                ops.backend.count_launch(len(seg_groups))
             if eng.mesh.fsdp > 1:
                 keep = new_sq[self.local_norm_idx].clone() if self.local_norm_idx is not None else None
                 du.all_reduce_sum(new_sq, group=eng.mesh.fsdp_group)
                 if keep is not None:
                     new_sq[self.local_norm_idx] = keep
-            scale = (x_norm / new_sq.sqrt().clamp_min(self.ns_epsilon))[kidx]
-            torch._foreach_mul_(hb_x, list(scale.unbind(0)))
+            scale_v = (x_norm / new_sq.sqrt().clamp_min(self.ns_epsilon)).contiguous()
+            if hb_x:
+                torch._foreach_mul_(hb_x, list(scale_v[kidx].unbind(0)))
+            if seg_groups:
+                for x, _, tb in seg_groups:
+                    ext.seg_update_(2, x, None, tb["bounds"], tb["kidx"], scale_v, None)
+                ops.backend.count_launch(len(seg_groups))
         eng.mark_params_updated()
+
+    # ------------------------------------------------------------------ fused segment kernels (CUDA)
+    def _seg_tables(self, g):
+        """Segment tables of group ``g`` for ``csrc/optim.cu``: the Muon matrices must tile the local prefix of the
+        flat fp32 shard without gaps (they are the contiguous prefix of a block's flat group).  None → foreach path."""
+        cache = self.__dict__.setdefault("_seg_cache", {})
+        if id(g) in cache:
+            return cache[id(g)]
+        tb = None
+        eng = self.engine
+        if eng.is_cuda and g.master.dtype == torch.float32 and ops.backend.has("seg_update_"):
+            a, b = g.shard_range()
+            segs = []
+            for mt in self.mats:
+                if mt.group is not g:
+                    continue
+                lo, hi = max(mt.offset, a), min(mt.offset + mt.rows * mt.cols, b)
+                if lo < hi:
+                    segs.append((lo - a, hi - a, mt.norm_idx))
+            segs.sort()
+            ok = bool(segs) and segs[0][0] == 0 and all(segs[i][1] == segs[i + 1][0] for i in range(len(segs) - 1)) \
+                and all(s[0] % 4 == 0 for s in segs) and segs[-1][1] % 4 == 0
+            if ok:
+                dev = eng.device
+                tb = {"n": segs[-1][1],
+                      "bounds": torch.tensor([s[0] for s in segs] + [segs[-1][1]], dtype=torch.int64, device=dev),
+                      "kidx": torch.tensor([s[2] for s in segs], dtype=torch.int32, device=dev)}
+        cache[id(g)] = tb
+        return tb
+
+    def _adjusted_lr_vector(self, lr_m: float) -> torch.Tensor:
+        """Per-matrix step sizes (slot = norm index) for the plain-Muon fused update."""
+        v = torch.zeros(max(self.n_norm, 1), dtype=torch.float32)
+        for mt in self.mats:
+            v[mt.norm_idx] = self._adjusted_lr(lr_m, mt.rows, mt.cols)
+        return v.to(self.engine.device)
+
+    def _scratch_acc(self) -> torch.Tensor:
+        return torch.zeros(max(self.n_norm, 1), dtype=torch.float32, device=self.engine.device)
 
     # ------------------------------------------------------------------ Muon transport + NS
     def _orthogonalise(self, stack: torch.Tensor) -> torch.Tensor:
@@ -279,11 +352,17 @@ class ShardedOptimizer:
             n_loc = min(b, g.matrix_numel) - a
             if n_loc > 0:
                 ms, gs = m[:n_loc], g.grad[:n_loc]
-                ms.mul_(self.mu).add_(gs)
-                if self.nesterov:
-                    u_shard[:n_loc].copy_(torch.add(gs, ms, alpha=self.mu))
+                if (eng.is_cuda and u_shard.dtype == torch.bfloat16 and ms.dtype == torch.float32 and gs.dtype == torch.float32
+                        and n_loc % 4 == 0 and ops.backend.has("muon_momentum_")):
+                    # one pass: momentum update, Nesterov combination and the bf16 cast of U
+                    ops.backend.require_extension().muon_momentum_(gs, ms, u_shard[:n_loc], self.mu, self.nesterov, None)
+                    ops.backend.count_launch()
                 else:
-                    u_shard[:n_loc].copy_(ms)
+                    ms.mul_(self.mu).add_(gs)
+                    if self.nesterov:
+                        u_shard[:n_loc].copy_(torch.add(gs, ms, alpha=self.mu))
+                    else:
+                        u_shard[:n_loc].copy_(ms)
             # 2. assemble whole matrices (every rank gets the full flat U; owners use their matrices)
             if g.world > 1:
                 if eng.symm is not None:
@@ -306,7 +385,7 @@ class ShardedOptimizer:
             for (r, c), lst in by_shape.items():
                 stack = torch.stack([u_full[mt.offset:mt.offset + r * c].view(r, c) for mt in lst])
                 O = self._orthogonalise(stack)
-                sq = O.float().pow(2).sum(dim=(-2, -1))
+                sq = torch.linalg.vector_norm(O, dim=(-2, -1), dtype=torch.float32).square()
                 for i, mt in enumerate(lst):
                     o_full[mt.offset:mt.offset + r * c].copy_(O[i].reshape(-1))
                     u_sq[mt.norm_idx] += sq[i]

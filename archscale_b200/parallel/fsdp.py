@@ -602,13 +602,13 @@ class FSDPEngine:
                 continue
             grads.append(g.grad)
             fs = 1 if (g.world > 1 or getattr(g, "ep_local", False)) else 0
-            g2 = g.grad.float().pow(2)
             mask = _replicated_mask(g) if tp_on else True
             if mask is True:
-                sq[fs][0] += g2.sum()
+                sq[fs][0] += torch.linalg.vector_norm(g.grad, dtype=torch.float32).square()
             elif mask is None:
-                sq[fs][1] += g2.sum()
+                sq[fs][1] += torch.linalg.vector_norm(g.grad, dtype=torch.float32).square()
             else:
+                g2 = g.grad.float().pow(2)
                 sq[fs][0] += (g2 * mask).sum()
                 sq[fs][1] += (g2 * (1 - mask)).sum()
         if self.mesh.fsdp > 1:

@@ -188,6 +188,23 @@ def run_ours(args) -> None:
         losses.append(float(loss))        # device → host read of the step's result
 
     e2e_ms = timed(step_e2e, args.steps)
+
+    phases = None
+    if args.phases:
+        # forward+backward vs optimizer step, device-timed separately (after the headline measurement)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        fb = op = 0.0
+        for i in range(args.steps):
+            sync_all()
+            ev[0].record()
+            trainer.forward_backward(dev_batches[i % len(dev_batches)])
+            ev[1].record()
+            trainer.optimizer_step(lr)
+            ev[2].record()
+            torch.cuda.synchronize()
+            fb += ev[0].elapsed_time(ev[1])
+            op += ev[1].elapsed_time(ev[2])
+        phases = {"forward_backward_ms": fb / args.steps, "optimizer_step_ms": op / args.steps}
     status = backend.load_extension().device_status() if backend.load_extension() is not None else 0
 
     n_law = get_parameters_count(trainer.plan.model_name, trainer.plan.depth, cfg, trainer.plan.train_config)
@@ -210,6 +227,7 @@ def run_ours(args) -> None:
                        "params": trainer.n_params_actual, "final_loss": losses[-1] if losses else None,
                        "device_status": int(status), "fused_comm": bool(args.fused_comm)},
             "clocks": clocks,
+            **({"phases": phases} if phases else {}),
             "e2e": {"value": tokens_per_step / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms},
             "gpu_launches": launches,
@@ -238,6 +256,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="dense", choices=sorted(CONFIGS))
+    ap.add_argument("--phases", action="store_true", help="also report forward+backward and optimizer-step times")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (ranks of a tp group share a micro-batch)")
     ap.add_argument("--fp8", action="store_true", help="MXFP8 block-scaled linear layers (dtype is then reported as mxfp8)")
     ap.add_argument("--fused-comm", dest="fused_comm", action="store_true")

@@ -126,3 +126,44 @@ def test_layernorm_kernel(dtype, rows, cols):
     assert torch.allclose(x.grad.float(), xr.grad, atol=tol * 4, rtol=tol * 4)
     for a, r in ((w.grad, wr.grad), (b.grad, br.grad)):
         assert (a - r).abs().max().item() <= (2e-4 if dtype == torch.float32 else 2e-2) * max(1.0, r.abs().max().item())
+
+
+def test_optimizer_kernels_match_torch():
+    """Fused Muon momentum and the segmented hyperball kernels of csrc/optim.cu against the foreach formulation."""
+    from archscale_b200.ops import backend
+    dev = _dev()
+    ext = backend.require_extension()
+    torch.manual_seed(5)
+    n = 3 * 4096 + 1000 * 4
+    g, m = torch.randn(n, device=dev), torch.randn(n, device=dev)
+    u = torch.empty(n, device=dev, dtype=torch.bfloat16)
+    m_ref = 0.95 * m + g * 0.5
+    u_ref = (g * 0.5 + 0.95 * m_ref).bfloat16()
+    ext.muon_momentum_(g, m, u, 0.95, True, torch.tensor(0.5, device=dev))
+    assert torch.allclose(m, m_ref, atol=1e-6) and torch.equal(u, u_ref)
+    # segments with boundaries inside a block and inside a warp's 128-element span
+    cuts = [0, 1000, 1000 + 4100, 1000 + 4100 + 36, 9000, n]
+    kidx = [4, 0, 2, 1, 3]
+    bounds = torch.tensor(cuts, dtype=torch.int64, device=dev)
+    kt = torch.tensor(kidx, dtype=torch.int32, device=dev)
+    x = torch.randn(n, device=dev)
+    acc = torch.zeros(6, device=dev)
+    ext.seg_update_(0, x, None, bounds, kt, None, acc)
+    want = torch.zeros(6, device=dev)
+    for (a, b), k in zip(zip(cuts[:-1], cuts[1:]), kidx):
+        want[k] = x[a:b].double().pow(2).sum().float()
+    assert torch.allclose(acc, want, rtol=1e-4)
+    coef = torch.rand(6, device=dev)
+    x_ref = x.clone()
+    for (a, b), k in zip(zip(cuts[:-1], cuts[1:]), kidx):
+        x_ref[a:b] -= coef[k] * u[a:b].float()
+    acc.zero_()
+    ext.seg_update_(1, x, u, bounds, kt, coef, acc)
+    assert torch.allclose(x, x_ref, atol=1e-6)
+    for (a, b), k in zip(zip(cuts[:-1], cuts[1:]), kidx):
+        want[k] = x_ref[a:b].double().pow(2).sum().float()
+    assert torch.allclose(acc, want, rtol=1e-4)
+    ext.seg_update_(2, x, None, bounds, kt, coef, None)
+    for (a, b), k in zip(zip(cuts[:-1], cuts[1:]), kidx):
+        x_ref[a:b] *= coef[k]
+    assert torch.allclose(x, x_ref, atol=1e-6)
