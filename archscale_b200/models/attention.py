@@ -203,7 +203,7 @@ class CausalSelfAttention(nn.Module):
             return self.proj(y.reshape(B, T, -1)), kv_cache, gmu_mems
 
         if cfg.separate_qkv:
-            q, k, v = self.q_proj(x), self.k_proj(x), self.v_proj(x)
+            q, k, v = ops.gemm.linear_multi(x, (self.q_proj, self.k_proj, self.v_proj))
             if cfg.gated_attn:
                 g = self.g_proj(x).reshape(B, T, H, 1)
         else:

@@ -47,11 +47,12 @@ int b200_cross_entropy_fwd_bwd(void* logits, int dtype, const int64_t* target, f
 // Per-head RMSNorm (optional) + NeoX RoPE (optional) on q:[N,H,D] and k:[N,G,D] bf16; T = positions per batch row.
 int b200_qknorm_rope_fwd(const void* q, const void* k, const void* qw, const void* kw, int w_dtype, const void* cos,
                          const void* sin, void* qo, void* ko, float* q_rstd, float* k_rstd, int64_t n_tokens, int T,
-                         int H, int G, int D, float eps, cudaStream_t stream);
+                         int H, int G, int D, float eps, int64_t q_token_stride, int64_t k_token_stride, cudaStream_t stream);
 int b200_qknorm_rope_bwd(const void* dqo, const void* dko, const void* q, const void* k, const void* qw, const void* kw,
                          int w_dtype, const void* cos, const void* sin, const float* q_rstd, const float* k_rstd,
                          void* dq, void* dk, float* dqw, float* dkw, float* dw_partial /* [grid, 2, D] */,
-                         int64_t n_tokens, int T, int H, int G, int D, cudaStream_t stream);
+                         int64_t n_tokens, int T, int H, int G, int D, int64_t q_token_stride, int64_t k_token_stride,
+                         cudaStream_t stream);
 int b200_qknorm_rope_grid();
 
 // ---- mixture of experts (moe_routing.cu, gemm_bf16.cu)

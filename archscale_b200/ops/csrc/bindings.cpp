@@ -153,7 +153,14 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> qknorm_rope_fwd(
     const c10::optional<at::Tensor>& cos, const c10::optional<at::Tensor>& sin, double eps) {
   c10::cuda::CUDAGuard guard(q.device());
   const int64_t B = q.size(0), T = q.size(1), H = q.size(2), D = q.size(3), G = k.size(2);
-  at::Tensor qo = at::empty_like(q), ko = at::empty_like(k), qr, kr;
+  // q / k may be column slices of a wider matrix: rows of heads must be dense, tokens a uniform stride apart
+  auto tok_stride = [](const at::Tensor& t) {
+    TORCH_CHECK(t.stride(3) == 1 && t.stride(2) == t.size(3) && (t.size(0) == 1 || t.stride(0) == t.size(1) * t.stride(1)),
+                "qknorm_rope: unsupported strides");
+    return t.stride(1);
+  };
+  const int64_t q_ts = tok_stride(q), k_ts = tok_stride(k);
+  at::Tensor qo = at::empty({B, T, H, D}, q.options()), ko = at::empty({B, T, G, D}, k.options()), qr, kr;
   if (qw.has_value()) {
     qr = at::empty({B * T * H}, q.options().dtype(at::kFloat));
     kr = at::empty({B * T * G}, q.options().dtype(at::kFloat));
@@ -161,7 +168,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> qknorm_rope_fwd(
   check(b200_qknorm_rope_fwd(q.data_ptr(), k.data_ptr(), ptr_opt(qw), ptr_opt(kw), dcode_opt(qw, 0), ptr_opt(cos),
                              ptr_opt(sin), qo.data_ptr(), ko.data_ptr(), qw.has_value() ? qr.data_ptr<float>() : nullptr,
                              qw.has_value() ? kr.data_ptr<float>() : nullptr, B * T, (int)T, (int)H, (int)G, (int)D,
-                             (float)eps, cur_stream()), "qknorm_rope_fwd");
+                             (float)eps, q_ts, k_ts, cur_stream()), "qknorm_rope_fwd");
   return {qo, ko, qr, kr};
 }
 
@@ -171,7 +178,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> qknorm_rope_bwd(
     const c10::optional<at::Tensor>& sin, const c10::optional<at::Tensor>& q_rstd, const c10::optional<at::Tensor>& k_rstd) {
   c10::cuda::CUDAGuard guard(q.device());
   const int64_t B = q.size(0), T = q.size(1), H = q.size(2), D = q.size(3), G = k.size(2);
-  at::Tensor dq = at::empty_like(q), dk = at::empty_like(k), dqw, dkw, part;
+  TORCH_CHECK(dqo.is_contiguous() && dko.is_contiguous());
+  at::Tensor dq = at::empty({B, T, H, D}, q.options()), dk = at::empty({B, T, G, D}, k.options()), dqw, dkw, part;
   if (qw.has_value()) {
     dqw = at::empty({D}, q.options().dtype(at::kFloat));
     dkw = at::empty({D}, q.options().dtype(at::kFloat));
@@ -183,7 +191,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> qknorm_rope_bwd(
                              k_rstd.has_value() ? k_rstd->data_ptr<float>() : nullptr, dq.data_ptr(), dk.data_ptr(),
                              qw.has_value() ? dqw.data_ptr<float>() : nullptr, qw.has_value() ? dkw.data_ptr<float>() : nullptr,
                              qw.has_value() ? part.data_ptr<float>() : nullptr, B * T, (int)T, (int)H, (int)G, (int)D,
-                             cur_stream()), "qknorm_rope_bwd");
+                             q.stride(1), k.stride(1), cur_stream()), "qknorm_rope_bwd");
   return {dq, dk, dqw, dkw};
 }
 

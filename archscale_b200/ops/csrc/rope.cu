@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const TW* __restrict__ qw,
     const TW* __restrict__ kw, const __nv_bfloat16* __restrict__ cosb, const __nv_bfloat16* __restrict__ sinb,
     __nv_bfloat16* __restrict__ qo, __nv_bfloat16* __restrict__ ko, float* __restrict__ q_rstd,
-    float* __restrict__ k_rstd, int64_t n_tokens, int T, int H, int G, float eps) {
+    float* __restrict__ k_rstd, int64_t n_tokens, int T, int H, int G, float eps, int64_t q_ts, int64_t k_ts) {
   constexpr int D = EPL * 32;
   const int lane = threadIdx.x & 31;
   const int64_t warp_global = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
@@ -53,7 +53,8 @@ __global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(
     const int64_t rr = is_q ? r : r - q_rows;
     const int heads = is_q ? H : G;
     const int64_t tok = rr / heads;
-    const __nv_bfloat16* src = (is_q ? q : k) + rr * D + lane * EPL;
+    // inputs may be column slices of a wider (fused projection) matrix: token stride q_ts / k_ts elements
+    const __nv_bfloat16* src = (is_q ? q + tok * q_ts : k + tok * k_ts) + (rr - tok * heads) * D + lane * EPL;
     __nv_bfloat16* dst = (is_q ? qo : ko) + rr * D + lane * EPL;
     const TW* w = is_q ? qw : kw;
     float x[EPL];
@@ -92,7 +93,7 @@ __global__ void __launch_bounds__(256) qknorm_rope_bwd_kernel(
     const __nv_bfloat16* __restrict__ k, const TW* __restrict__ qw, const TW* __restrict__ kw,
     const __nv_bfloat16* __restrict__ cosb, const __nv_bfloat16* __restrict__ sinb, const float* __restrict__ q_rstd,
     const float* __restrict__ k_rstd, __nv_bfloat16* __restrict__ dq, __nv_bfloat16* __restrict__ dk,
-    float* __restrict__ dw_partial /* [grid, 2, D] */, int64_t n_tokens, int T, int H, int G) {
+    float* __restrict__ dw_partial /* [grid, 2, D] */, int64_t n_tokens, int T, int H, int G, int64_t q_ts, int64_t k_ts) {
   constexpr int D = EPL * 32;
   __shared__ float dw_s[2][D];
   const int lane = threadIdx.x & 31;
@@ -129,7 +130,7 @@ __global__ void __launch_bounds__(256) qknorm_rope_bwd_kernel(
     const TW* w = is_q ? qw : kw;
     if (w) {
       float x[EPL];
-      ld_row<EPL>((is_q ? q : k) + off, x);
+      ld_row<EPL>((is_q ? q + tok * q_ts : k + tok * k_ts) + (rr - tok * heads) * D + lane * EPL, x);
       const float rs = (is_q ? q_rstd : k_rstd)[rr];
       float dot = 0.f;
       float gw[EPL];
@@ -177,12 +178,12 @@ extern "C" int b200_qknorm_rope_grid() { return kRopeGrid; }
 
 extern "C" int b200_qknorm_rope_fwd(const void* q, const void* k, const void* qw, const void* kw, int w_dtype,
                                     const void* cos, const void* sin, void* qo, void* ko, float* q_rstd, float* k_rstd,
-                                    int64_t n_tokens, int T, int H, int G, int D, float eps, cudaStream_t st) {
+                                    int64_t n_tokens, int T, int H, int G, int D, float eps, int64_t q_ts, int64_t k_ts, cudaStream_t st) {
   if (n_tokens == 0) return 0;
 #define LAUNCH(EPL, TW)                                                                                               \
   qknorm_rope_fwd_kernel<EPL, TW><<<kRopeGrid, 256, 0, st>>>((const bf16*)q, (const bf16*)k, (const TW*)qw, (const TW*)kw, \
                                                              (const bf16*)cos, (const bf16*)sin, (bf16*)qo, (bf16*)ko,  \
-                                                             q_rstd, k_rstd, n_tokens, T, H, G, eps)
+                                                             q_rstd, k_rstd, n_tokens, T, H, G, eps, q_ts, k_ts)
   if (D == 128) { if (w_dtype == 1) LAUNCH(4, bf16); else LAUNCH(4, float); }
   else if (D == 64) { if (w_dtype == 1) LAUNCH(2, bf16); else LAUNCH(2, float); }
   else return -1;
@@ -193,12 +194,12 @@ extern "C" int b200_qknorm_rope_fwd(const void* q, const void* k, const void* qw
 extern "C" int b200_qknorm_rope_bwd(const void* dqo, const void* dko, const void* q, const void* k, const void* qw,
                                      const void* kw, int w_dtype, const void* cos, const void* sin, const float* q_rstd,
                                      const float* k_rstd, void* dq, void* dk, float* dqw, float* dkw, float* dw_partial,
-                                     int64_t n_tokens, int T, int H, int G, int D, cudaStream_t st) {
+                                     int64_t n_tokens, int T, int H, int G, int D, int64_t q_ts, int64_t k_ts, cudaStream_t st) {
   if (n_tokens == 0) return 0;
 #define LAUNCH(EPL, TW)                                                                                                \
   qknorm_rope_bwd_kernel<EPL, TW><<<kRopeGrid, 256, 0, st>>>((const bf16*)dqo, (const bf16*)dko, (const bf16*)q, (const bf16*)k, \
                                                              (const TW*)qw, (const TW*)kw, (const bf16*)cos, (const bf16*)sin,  \
-                                                             q_rstd, k_rstd, (bf16*)dq, (bf16*)dk, dw_partial, n_tokens, T, H, G)
+                                                             q_rstd, k_rstd, (bf16*)dq, (bf16*)dk, dw_partial, n_tokens, T, H, G, q_ts, k_ts)
   if (D == 128) { if (w_dtype == 1) LAUNCH(4, bf16); else LAUNCH(4, float); }
   else if (D == 64) { if (w_dtype == 1) LAUNCH(2, bf16); else LAUNCH(2, float); }
   else return -1;

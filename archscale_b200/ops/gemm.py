@@ -139,3 +139,81 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         weight = weight.to(x.dtype)
         bias = bias.to(x.dtype) if bias is not None else None
     return torch.nn.functional.linear(x, weight, bias)
+
+
+# ------------------------------------------------------------------------------------------ fused sibling projections
+def _adjacent(ts) -> bool:
+    """True when the tensors are dense 2-D row blocks stored back to back (views of one flat parameter buffer)."""
+    for a, b in zip(ts[:-1], ts[1:]):
+        if not (a.is_contiguous() and b.is_contiguous() and a.dtype == b.dtype and a.shape[1] == b.shape[1]
+                and a.data_ptr() + a.numel() * a.element_size() == b.data_ptr()):
+            return False
+    return True
+
+
+def _cat_view(ts) -> torch.Tensor:
+    rows = sum(t.shape[0] for t in ts)
+    return ts[0].as_strided((rows, ts[0].shape[1]), (ts[0].shape[1], 1))
+
+
+class _MultiLinearFn(torch.autograd.Function):
+    """y = x @ [W₀; W₁; …]ᵀ for weights stored back to back: one forward GEMM, one dgrad GEMM (no partial-sum adds) and
+    one wgrad GEMM that accumulates into the equally adjacent fp32 ``main_grad`` views."""
+
+    @staticmethod
+    def forward(ctx, x, *weights):
+        w_cat = _cat_view([w.detach() for w in weights])
+        x2 = x.reshape(-1, x.shape[-1])
+        g = getattr(weights[0], "_fsdp_group", None)
+        if g is not None and getattr(g, "ag_pending", False):
+            eng = weights[0]._fsdp_engine
+            if weights[0]._fsdp_first and _cuda_ok(x2, w_cat, x2.shape[0], w_cat.shape[0], x2.shape[1]):
+                g.ag_pending = False
+                y = eng.symm.ag_gemm(x2, g, w_cat.shape[0])
+            else:
+                eng.finish_pending_gather(g)
+                y = matmul_nt(x2, w_cat)
+        else:
+            y = matmul_nt(x2, w_cat)
+        ctx.save_for_backward(x2, w_cat)
+        ctx.weights = weights
+        return y.view(*x.shape[:-1], w_cat.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w_cat = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = matmul_nn(dy2, w_cat).view(*dy.shape[:-1], x2.shape[1]) if ctx.needs_input_grad[0] else None
+        mgs = [getattr(w, "main_grad", None) for w in ctx.weights]
+        if all(m is not None for m in mgs) and _adjacent(mgs):
+            matmul_tn_acc_(_cat_view(mgs), dy2, x2)
+            return (dx,) + (None,) * len(ctx.weights)
+        dw = matmul_tn(dy2, x2)
+        outs, r = [], 0
+        for w, m in zip(ctx.weights, mgs):
+            piece = dw[r:r + w.shape[0]]
+            r += w.shape[0]
+            if m is not None:
+                m.add_(piece.float())
+                outs.append(None)
+            else:
+                outs.append(piece)
+        return (dx,) + tuple(outs)
+
+
+def linear_multi(x: torch.Tensor, layers) -> list:
+    """Outputs of several bias-free ``Linear`` layers that share the input ``x``.  When their weights sit back to back in
+    memory (consecutive views of the flat parameter buffer) the layers run as one GEMM and the outputs are column
+    slices of its result; otherwise each layer is called on its own."""
+    ws = [l.weight for l in layers]
+    fusable = (x.is_cuda and x.dtype == torch.bfloat16 and all(type(l).__name__ == "Linear" and l.bias is None and not l.mxfp8
+                                                              for l in layers)
+               and all(w.dtype == torch.bfloat16 for w in ws) and _adjacent(ws)
+               and (x.numel() // x.shape[-1]) % 8 == 0 and x.shape[-1] % 8 == 0 and x.shape[-1] >= 64
+               and backend.use_cuda_kernel("gemm", x, ws[0]))
+    if not fusable:
+        return [l(x) for l in layers]
+    y = _MultiLinearFn.apply(x if x.is_contiguous() else x.contiguous(), *ws)
+    return list(y.split([w.shape[0] for w in ws], dim=-1))

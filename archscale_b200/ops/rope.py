@@ -94,14 +94,20 @@ def qk_norm_rope_ref(q, k, q_weight, k_weight, cos, sin, eps: float = 1e-5, posi
     return q, k
 
 
+def _rows_ok(t: torch.Tensor) -> torch.Tensor:
+    """(B,T,H,D) with dense head rows and a uniform token stride (a column slice of a fused projection qualifies)."""
+    if t.stride(3) == 1 and t.stride(2) == t.size(3) and (t.size(0) == 1 or t.stride(0) == t.size(1) * t.stride(1)):
+        return t
+    return t.contiguous()
+
+
 class _QKNormRopeFn(torch.autograd.Function):
     """q:(B,T,H,D) k:(B,T,G,D) bf16 → normalised+rotated copies; one launch fwd, one bwd."""
 
     @staticmethod
     def forward(ctx, q, k, qw, kw, cos, sin, eps):
         ext = backend.require_extension()
-        q = q.contiguous()
-        k = k.contiguous()
+        q, k = _rows_ok(q), _rows_ok(k)
         qo, ko, q_rstd, k_rstd = ext.qknorm_rope_fwd(q, k, qw, kw, cos, sin, eps)
         backend.count_launch()
         ctx.save_for_backward(q, k, qw, kw, cos, sin, q_rstd, k_rstd)
