@@ -60,8 +60,7 @@ class DiffAttention(nn.Module):
         lam1 = torch.exp(torch.sum(self.lambda_q1 * self.lambda_k1, dim=-1).float()).type_as(q)
         lam2 = torch.exp(torch.sum(self.lambda_q2 * self.lambda_k2, dim=-1).float()).type_as(q)
         lam = lam1 - lam2 + self.lambda_init
-        a = a1 - lam * a2
-        a = ops.rms_norm(a, self.subln.weight, 1e-5) * (1 - self.lambda_init)
+        a = ops.diff_combine(a1, a2, lam, self.subln.weight, 1 - self.lambda_init, 1e-5)
         # (B,T,H/2,2D) → (B,T,H,D)
         return a.reshape(B, T, H // 2, 2, D).reshape(B, T, H, D)
 

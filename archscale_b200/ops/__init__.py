@@ -14,3 +14,4 @@ from .norm import add_rms_norm, add_rms_norm_ref, gated_rms_norm, layer_norm, rm
 from .rope import apply_rotary_emb, build_rope_cache, qk_norm_rope  # noqa: F401
 from .selective_scan import selective_scan, selective_scan_ref  # noqa: F401
 from .ssd import ssd_scan, ssd_scan_ref  # noqa: F401
+from .diff_attn import diff_combine, diff_combine_ref  # noqa: F401,E402

@@ -150,6 +150,18 @@ int b200_muon_momentum(const float* g, float* m, void* u, long long n, float mu,
 int b200_seg_update(int mode, float* x, const void* u, long long n, const long long* bounds, const int* kidx, int nseg,
                     const float* coef, float* acc, cudaStream_t st);
 
+// Gated RMSNorm with groups (gated_norm.cu)
+int b200_gated_rmsnorm_fwd(const void* x, const void* z, const float* w, void* y, float* rstd, int dtype, long long rows, int cols,
+                           int gsize, float eps, int norm_before_gate, cudaStream_t st);
+int b200_gated_rmsnorm_bwd(const void* dy, const void* x, const void* z, const float* w, const float* rstd, void* dx, void* dz, float* dw,
+                           int dtype, long long rows, int cols, int gsize, int norm_before_gate, cudaStream_t st);
+
+// Differential-attention combine (diff_attn.cu)
+int b200_diff_combine_fwd(const void* a1, const void* a2, const float* lam, const float* w, float c, void* y, float* rstd, long long rows,
+                          int width, float eps, cudaStream_t st);
+int b200_diff_combine_bwd(const void* dy, const void* a1, const void* a2, const float* lam, const float* w, float c, const float* rstd,
+                          void* da1, void* da2, float* dlam, float* dw, long long rows, int width, cudaStream_t st);
+
 #ifdef __cplusplus
 }
 #endif

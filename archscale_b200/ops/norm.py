@@ -135,8 +135,37 @@ def layer_norm(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[t
     return layer_norm_ref(x, weight, bias, eps)
 
 
+class _GatedRMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, z, eps, gsize, nbg):
+        ext = backend.require_extension()
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        z2 = None if z is None else z.reshape(-1, z.shape[-1]).contiguous()
+        wf = weight.float().contiguous()
+        y, rstd = ext.gated_rmsnorm_fwd(x2, z2, wf, eps, gsize, nbg)
+        backend.count_launch()
+        ctx.save_for_backward(x2, z2 if z2 is not None else torch.empty(0), wf, rstd)
+        ctx.meta = (gsize, nbg, z is not None, weight.dtype, x.shape)
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        ext = backend.require_extension()
+        x2, z2, wf, rstd = ctx.saved_tensors
+        gsize, nbg, has_z, wdtype, shape = ctx.meta
+        dx, dz, dw = ext.gated_rmsnorm_bwd(dy.reshape(x2.shape).contiguous(), x2, z2 if has_z else None, wf, rstd, gsize, nbg)
+        backend.count_launch()
+        return dx.view(shape), dw.to(wdtype), (dz.view(shape) if has_z else None), None, None, None
+
+
 def gated_rms_norm(x, weight, z=None, eps: float = 1e-5, group_size: Optional[int] = None,
                    norm_before_gate: bool = True) -> torch.Tensor:
+    """Gated RMSNorm with groups (`lit_gpt/ops/layernorm_gated.py:42-105,151-270`)."""
+    n = x.shape[-1]
+    g = n if group_size is None else group_size
+    if (x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and (z is None or z.dtype == x.dtype) and g % 8 == 0 and n % g == 0
+            and g <= 12288 and backend.has("gated_rmsnorm_fwd") and backend.use_cuda_kernel("gated_rmsnorm", x)):
+        return _GatedRMSNormFn.apply(x, weight, z, eps, g, norm_before_gate)
     return gated_rms_norm_ref(x, weight, z, eps, group_size, norm_before_gate)
 
 

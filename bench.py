@@ -259,7 +259,9 @@ def main() -> None:
     ap.add_argument("--phases", action="store_true", help="also report forward+backward and optimizer-step times")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (ranks of a tp group share a micro-batch)")
     ap.add_argument("--fp8", action="store_true", help="MXFP8 block-scaled linear layers (dtype is then reported as mxfp8)")
-    ap.add_argument("--fused-comm", dest="fused_comm", action="store_true")
+    ap.add_argument("--fused-comm", dest="fused_comm", action="store_true", default=True,
+                    help="peer-memory collectives fused with compute (default on more than one GPU)")
+    ap.add_argument("--no-fused-comm", dest="fused_comm", action="store_false", help="NCCL collectives (the baseline path)")
     ap.add_argument("--no-ep", dest="no_ep", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -167,3 +167,52 @@ def test_optimizer_kernels_match_torch():
     for (a, b), k in zip(zip(cuts[:-1], cuts[1:]), kidx):
         x_ref[a:b] *= coef[k]
     assert torch.allclose(x, x_ref, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("cols,gsize,nbg,with_z", [(512, None, True, True), (512, 128, False, True), (1024, 256, True, False),
+                                                    (2048, None, False, True)])
+def test_gated_rmsnorm_kernel(dtype, cols, gsize, nbg, with_z):
+    from archscale_b200.ops.norm import gated_rms_norm, gated_rms_norm_ref
+    dev = _dev()
+    torch.manual_seed(6)
+    rows = 300
+    x = torch.randn(rows, cols, device=dev).to(dtype).requires_grad_(True)
+    z = torch.randn(rows, cols, device=dev).to(dtype).requires_grad_(True) if with_z else None
+    w = (torch.rand(cols, device=dev) + 0.5).requires_grad_(True)
+    y = gated_rms_norm(x, w, z, 1e-5, gsize, nbg)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_(True)
+    zr = z.detach().float().requires_grad_(True) if with_z else None
+    wr = w.detach().clone().requires_grad_(True)
+    yr = gated_rms_norm_ref(xr, wr, zr, 1e-5, gsize, nbg)
+    yr.backward(g.float())
+    tol = 3e-5 if dtype == torch.float32 else 4e-2
+    assert torch.allclose(y.float(), yr, atol=tol, rtol=tol)
+    assert torch.allclose(x.grad.float(), xr.grad, atol=tol * 4, rtol=tol * 4)
+    if with_z:
+        assert torch.allclose(z.grad.float(), zr.grad, atol=tol * 4, rtol=tol * 4)
+    assert (w.grad - wr.grad).abs().max().item() <= (3e-4 if dtype == torch.float32 else 3e-2) * max(1.0, wr.grad.abs().max().item())
+
+
+@pytest.mark.parametrize("W", [128, 256])
+def test_diff_combine_kernel(W):
+    from archscale_b200.ops.diff_attn import diff_combine, diff_combine_ref
+    dev = _dev()
+    torch.manual_seed(7)
+    a1 = torch.randn(2, 70, 5, W, device=dev).bfloat16().requires_grad_(True)
+    a2 = torch.randn(2, 70, 5, W, device=dev).bfloat16().requires_grad_(True)
+    lam = torch.tensor(0.37, device=dev).bfloat16().requires_grad_(True)
+    w = (torch.rand(W, device=dev) + 0.5).requires_grad_(True)
+    y = diff_combine(a1, a2, lam, w, 0.8)
+    g = torch.randn_like(y)
+    y.backward(g)
+    r = [t.detach().float().requires_grad_(True) for t in (a1, a2, lam, w)]
+    yr = diff_combine_ref(r[0], r[1], r[2], r[3], 0.8)
+    yr.backward(g.float())
+    assert torch.allclose(y.float(), yr, atol=3e-2, rtol=3e-2)
+    for got, ref in ((a1.grad, r[0].grad), (a2.grad, r[1].grad)):
+        assert torch.allclose(got.float(), ref, atol=5e-2, rtol=5e-2)
+    assert abs(float(lam.grad) - float(r[2].grad)) <= 3e-2 * max(1.0, abs(float(r[2].grad)))
+    assert (w.grad - r[3].grad).abs().max().item() <= 3e-2 * max(1.0, r[3].grad.abs().max().item())
