@@ -101,3 +101,40 @@ class Mamba(nn.Module):
             gmu_mems = y
             y = ops.swiglu(z.contiguous(), y.contiguous())
         return self.out_proj(y), gmu_mems
+
+    # -- single-token decode (`lit_gpt/mamba_simple.py:363-408`) -----------------------------------------------------
+    def allocate_inference_cache(self, batch_size: int, device=None, dtype=None):
+        """(conv_state (B, d_inner, d_conv), ssm_state (B, d_inner, d_state)) filled with zeros."""
+        device = device or self.out_proj.weight.device
+        dtype = dtype or self.conv1d.weight.dtype
+        return (torch.zeros(batch_size, self.d_inner, self.d_conv, device=device, dtype=dtype),
+                torch.zeros(batch_size, self.d_inner, self.d_state, device=device, dtype=torch.float32))
+
+    @torch.no_grad()
+    def step(self, hidden_states: torch.Tensor, conv_state: torch.Tensor, ssm_state: torch.Tensor):
+        """One token: hidden_states (B, 1, C); the states are updated in place and returned with the output."""
+        assert hidden_states.shape[1] == 1, "step() decodes one token at a time"
+        dtype = hidden_states.dtype
+        xz = self.in_proj(hidden_states.squeeze(1))
+        x, z = xz.chunk(2, dim=-1)
+        conv_state.copy_(torch.roll(conv_state, shifts=-1, dims=-1))
+        conv_state[:, :, -1] = x
+        x = torch.sum(conv_state.float() * self.conv1d.weight.squeeze(1).float(), dim=-1)
+        if self.conv1d.bias is not None:
+            x = x + self.conv1d.bias.float()
+        x = F.silu(x).to(dtype)
+        dt, Bm, Cm = torch.split(self.x_proj(x), [self.dt_rank, self.d_state, self.d_state], dim=-1)
+        if self.jamba_norm:
+            dt, Bm, Cm = self.dt_layernorm(dt), self.b_layernorm(Bm), self.c_layernorm(Cm)
+        dt = F.softplus(F.linear(dt, self.dt_proj.weight.to(dt.dtype)).float() + self.dt_proj.bias.float())
+        A = -torch.exp(self.A_log.float())
+        dA = torch.exp(torch.einsum("bd,dn->bdn", dt, A))
+        dB = torch.einsum("bd,bn->bdn", dt, Bm.float())
+        ssm_state.copy_(ssm_state * dA + x.float().unsqueeze(-1) * dB)
+        y = torch.einsum("bdn,bn->bd", ssm_state, Cm.float()) + self.D.float() * x.float()
+        if self.gmu_save:
+            mem = y.to(dtype)
+            y = y * F.silu(z.float())
+            return self.out_proj(y.to(dtype)).unsqueeze(1), conv_state, ssm_state, mem.unsqueeze(1)
+        y = y * F.silu(z.float())
+        return self.out_proj(y.to(dtype)).unsqueeze(1), conv_state, ssm_state

@@ -42,6 +42,11 @@ CONFIGS = {
         overrides={"n_head": 8, "n_query_groups": 2, "n_routed_experts": 64, "router_top_k": 8,
                    "moe_intermediate_size": 256, "shared_intermediate_size": 2048},
         sparsity=8, top_k=8, share_expert=True, sqrt_gate=True, global_aux=True, aux_gamma=0.01),
+    "d24": dict(
+        name="dense GQA d24 (d_model 3072, 24q/8kv heads, head_dim 128, SwiGLU 8192, vocab 32000), muP++ MuonH; run it with "
+             "--fp8 --tp 2 --act-ckpt for the MXFP8 tensor-parallel configuration",
+        train_model="transformer_gqa4", depth=24, train_name="scaling_mup_muonh_qknorm", micro_bsz=4, ctx_len=8192,
+        overrides={"n_embd": 3072, "n_head": 24, "n_query_groups": 8, "intermediate_size": 8192}, sparsity=1, top_k=2),
     "phi4": dict(
         name="SambaY 3.8B phi4miniflash_d32 (d_model 2560, 40q/20kv heads, head_dim 64, Mamba-1 + SWA 512 + YOCO + GMU, "
              "differential attention, LayerNorm, vocab 200064, tied embeddings), packed 8192-token rows",
@@ -127,7 +132,7 @@ def run_ours(args) -> None:
                   micro_bsz=c["micro_bsz"], ctx_len=c["ctx_len"], total_bsz=(world // max(args.tp, 1)) * c["micro_bsz"] * c["ctx_len"],
                   max_tokens=1e12, use_flce=True, sparsity=c["sparsity"], top_k=c["top_k"],
                   config_overrides=dict(c["overrides"]), ep=ep, tp=args.tp, fused_comm=args.fused_comm, fp8=args.fp8,
-                  return_trainer=True, quiet=True)
+                  act_ckpt=args.act_ckpt, return_trainer=True, quiet=True)
     for k in ("share_expert", "sqrt_gate", "global_aux", "aux_gamma"):
         if k in c:
             kwargs[k] = c[k]
@@ -217,7 +222,7 @@ def run_ours(args) -> None:
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "mxfp8 linears (bf16 elsewhere)" if args.fp8 else "bf16", "data": "synthetic uniform-random token ids (seed 0), random-init weights",
             "tokens_per_sec_per_gpu": value / world,
-            "mfu": flops_step / (ms_per_step / 1e3) / 2.25e15,
+            "mfu": flops_step / max(args.tp, 1) / (ms_per_step / 1e3) / 2.25e15,   # per GPU: tp peers share a micro-batch
             "config": {"model": c["name"], "global_batch": world * mb, "seq_len": T,
                        "parallelism": (f"fsdp{world // max(args.tp, 1)}" if world > 1 else "single") + (f"+ep{ep}" if ep > 1 else "")
                                       + (f"+tp{args.tp}" if args.tp > 1 else ""),
@@ -256,6 +261,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="dense", choices=sorted(CONFIGS))
+    ap.add_argument("--act-ckpt", dest="act_ckpt", action="store_true", help="activation checkpointing per block")
     ap.add_argument("--phases", action="store_true", help="also report forward+backward and optimizer-step times")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (ranks of a tp group share a micro-batch)")
     ap.add_argument("--fp8", action="store_true", help="MXFP8 block-scaled linear layers (dtype is then reported as mxfp8)")
