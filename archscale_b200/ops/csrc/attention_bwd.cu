@@ -18,7 +18,8 @@
 namespace b200 {
 
 constexpr int BT = 128;                 // tile edge (queries and keys)
-constexpr int BWD_THREADS = 320;            // warp 0 TMA, warp 1 MMA, warps 2..9 softmax (two per TMEM lane quarter)
+constexpr int BWD_THREADS = 352;            // warp 0 TMA, warp 1 MMA (S, dP), warps 2..9 softmax, warp 10 MMA (accumulations)
+constexpr int ACC_WARP = 10;
 constexpr float kLog2e_b = 1.4426950408889634f;
 
 int make_tmap_2d_bf16(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_elems,
@@ -84,8 +85,9 @@ __device__ __forceinline__ void named_bar_sync_256() { asm volatile("bar.sync 1,
 // Both kernels below walk their inner tiles in halves of 64 columns so that two (S, dP) buffers, 64 fp32 columns
 // each, fit in tensor memory beside the accumulators.  The MMA thread runs one half ahead: while the 8 softmax
 // warps turn half h into P / dS, the tensor pipe computes S, dP of half h+1 and the accumulation of half h−1.
-// A softmax warp (lane quarter q, column half ch) owns 32 fp32 columns of a half and packs its bf16 result into
-// the first 16 of them, so the TS-MMA reads k-step k (16 rows of the contraction) at column (k/2)·32 + (k%2)·8.
+// The 8 softmax warps form two groups of four (one warp per TMEM lane quarter); group c converts the halves that live in
+// buffer c, 32 fp32 columns at a time, packing the bf16 result into the first 16 of the 32 columns just read, so the
+// TS-MMA reads k-step k (16 rows of the contraction) at column (k/2)·32 + (k%2)·8.
 constexpr int HB = 64;
 __device__ __forceinline__ uint32_t packed_col(int k) { return static_cast<uint32_t>((k >> 1) * 32 + (k & 1) * 8); }
 
@@ -108,9 +110,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   uint64_t* kv_full = bars + 1;     // [2]
   uint64_t* kv_empty = bars + 3;    // [2]
   uint64_t* sdp_full = bars + 5;    // [2]  S and dP of a half are in TMEM buffer b
-  uint64_t* ds_full = bars + 7;     // [2]  (count 8) dS of buffer b written
+  uint64_t* ds_full = bars + 7;     // [2]  (count 4) dS of buffer b written by its warp group
   uint64_t* acc_done = bars + 9;    // 1    all dQ MMAs finished
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* buf_free = bars + 10;   // [2]  accumulation MMAs that read buffer b have completed
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -128,7 +131,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     mbar_init(fixed_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1);
-      mbar_init(&sdp_full[s], 1); mbar_init(&ds_full[s], 8);
+      mbar_init(&sdp_full[s], 1); mbar_init(&ds_full[s], 4); mbar_init(&buf_free[s], 1);
     }
     mbar_init(acc_done, 1);
     *abort_flag = 0;
@@ -166,7 +169,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(BT, HB, 0, 0);
-      constexpr uint32_t idesc_dq = make_idesc_bf16(BT, D, 0, 1);        // dQ += dS·K, K is N-major
       if (!mbar_wait(fixed_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL)) goto done;
       const uint32_t sqa = smem_u32(sq), sdoa = smem_u32(sdo);
       // S, dP of half `hx` into buffer hx & 1 (keys hf·64.. of the tile: rows 8192 bytes into each 64-column chunk)
@@ -189,9 +191,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         umma_commit(&sdp_full[buf]);
         return true;
       };
-      if (n_half > 0 && !issue_sdp(0)) goto done;
+      // One thread can only issue a tcgen05.mma every ~85 cycles, whatever its N: S/dP and the accumulations are issued by
+      // two different threads so that the tensor pipe sees both streams.  buf_free[b] orders the reuse of buffer b:
+      // S, dP of half hx+2 may overwrite it once the accumulation MMAs of half hx (which read dS from it) have completed.
       for (int hx = 0; hx < n_half; ++hx) {
-        if (hx + 1 < n_half && !issue_sdp(hx + 1)) goto done;
+        if (hx >= 2 && !mbar_wait(&buf_free[hx & 1], ((hx - 2) >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) goto done;
+        if (!issue_sdp(hx)) goto done;
+      }
+    }
+  } else if (warp == ACC_WARP) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_dq = make_idesc_bf16(BT, D, 0, 1);        // dQ += dS·K, K is N-major
+      for (int hx = 0; hx < n_half; ++hx) {
         const int t = hx >> 1, hf = hx & 1, st = t & 1, buf = hx & 1;
         if (!mbar_wait(&ds_full[buf], (hx >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
         tc_fence_after();
@@ -201,6 +212,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         for (int k = 0; k < HB / 16; ++k)
           umma_bf16_ts(T_DQ, tdp + packed_col(k), make_smem_desc(sk + (hf * 4 + k) * 2048, CHUNK_BYTES, 1024), idesc_dq,
                        (hx | k) != 0);
+        umma_commit(&buf_free[buf]);
         if (hf == 1) umma_commit(&kv_empty[st]);
       }
       umma_commit(acc_done);
@@ -215,42 +227,47 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const float lse2 = row_valid ? p.lse[stat_idx] * kLog2e_b : 0.f;
     const float dlt = row_valid ? p.delta[stat_idx] : 0.f;
     const uint32_t lane_off = static_cast<uint32_t>(qtr * 32) << 16;
-    for (int hx = 0; hx < n_half; ++hx) {
+    // Ping-pong: warp group `ch` owns the halves with hx & 1 == ch (buffer ch) and converts all 64 columns of such a half,
+    // so the load → exp2 → store chains of two consecutive halves overlap instead of running back to back.
+    for (int hx = ch; hx < n_half; hx += 2) {
       const int t = hx >> 1, hf = hx & 1, buf = hx & 1;
       const int kt0 = (j_begin + t) * BT;
-      const int k0 = kt0 + hf * HB + ch * 32;
       if (!mbar_wait(&sdp_full[buf], (hx >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
       tc_fence_after();
       const bool full_tile = (kt0 + BT - 1 <= q0) && (kt0 >= lo_last);
-      const uint32_t ts = tmem_base + buf * 128 + ch * 32 + lane_off, tdp = ts + 64;
-      uint32_t sr[32], dr[32];
-      tmem_ld_32x32(ts, sr);
-      tmem_ld_32x32(tdp, dr);
-      tmem_ld_wait();
-      uint32_t w[16];
       const float sl2 = p.scale_log2;
-      if (full_tile && row_valid) {                   // no key of this tile is masked for any row: 4 ops per element
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const float p0 = exp2f(fmaf(__uint_as_float(sr[2 * e]), sl2, -lse2));
-          const float p1 = exp2f(fmaf(__uint_as_float(sr[2 * e + 1]), sl2, -lse2));
-          w[e] = pack_bf16x2(p0 * (__uint_as_float(dr[2 * e]) - dlt), p1 * (__uint_as_float(dr[2 * e + 1]) - dlt));
-        }
-      } else {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int k0 = kt0 + hf * HB + cc * 32;
+        const uint32_t ts = tmem_base + buf * 128 + cc * 32 + lane_off, tdp = ts + 64;
+        uint32_t sr[32], dr[32];
+        tmem_ld_32x32(ts, sr);
+        tmem_ld_32x32(tdp, dr);
+        tmem_ld_wait();
+        uint32_t w[16];
+        if (full_tile && row_valid) {                 // no key of this tile is masked for any row: 4 ops per element
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          float ds2[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int kk = k0 + 2 * e + u;
-            float pr = exp2f(fmaf(__uint_as_float(sr[2 * e + u]), sl2, -lse2));
-            if (kk > r || kk < lo_r || !row_valid) pr = 0.f;
-            ds2[u] = pr * (__uint_as_float(dr[2 * e + u]) - dlt);
+          for (int e = 0; e < 16; ++e) {
+            const float p0 = exp2f(fmaf(__uint_as_float(sr[2 * e]), sl2, -lse2));
+            const float p1 = exp2f(fmaf(__uint_as_float(sr[2 * e + 1]), sl2, -lse2));
+            w[e] = pack_bf16x2(p0 * (__uint_as_float(dr[2 * e]) - dlt), p1 * (__uint_as_float(dr[2 * e + 1]) - dlt));
           }
-          w[e] = pack_bf16x2(ds2[0], ds2[1]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            float ds2[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int kk = k0 + 2 * e + u;
+              float pr = exp2f(fmaf(__uint_as_float(sr[2 * e + u]), sl2, -lse2));
+              if (kk > r || kk < lo_r || !row_valid) pr = 0.f;
+              ds2[u] = pr * (__uint_as_float(dr[2 * e + u]) - dlt);
+            }
+            w[e] = pack_bf16x2(ds2[0], ds2[1]);
+          }
         }
+        tmem_st_32x16(tdp, w);                        // in place: the first 16 of the 32 columns just read
       }
-      tmem_st_32x16(tdp, w);                          // in place: the first 16 of the 32 columns just read
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -312,9 +329,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   uint64_t* qd_full = bars + 1;     // [2]
   uint64_t* qd_empty = bars + 3;    // [2]
   uint64_t* sdp_full = bars + 5;    // [2]
-  uint64_t* ds_full = bars + 7;     // [2] (count 8)
+  uint64_t* ds_full = bars + 7;     // [2] (count 4)
   uint64_t* acc_done = bars + 9;    // 1
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* buf_free = bars + 10;   // [2]
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -335,7 +353,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     mbar_init(fixed_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&qd_full[s], 1); mbar_init(&qd_empty[s], 1);
-      mbar_init(&sdp_full[s], 1); mbar_init(&ds_full[s], 8);
+      mbar_init(&sdp_full[s], 1); mbar_init(&ds_full[s], 4); mbar_init(&buf_free[s], 1);
     }
     mbar_init(acc_done, 1);
     *abort_flag = 0;
@@ -374,7 +392,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(BT, HB, 0, 0);       // Sᵀ = K·Qᵀ, dPᵀ = V·dOᵀ (64 queries)
-      constexpr uint32_t idesc_acc = make_idesc_bf16(BT, D, 0, 1);      // dV += Pᵀ·dO, dK += dSᵀ·Q (N-major B)
       if (!mbar_wait(fixed_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL)) goto done;
       const uint32_t ska = smem_u32(sk), sva = smem_u32(sv);
       auto issue_sdp = [&](int hx) -> bool {
@@ -396,9 +413,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         umma_commit(&sdp_full[buf]);
         return true;
       };
-      if (n_half > 0 && !issue_sdp(0)) goto done;
+      for (int hx = 0; hx < n_half; ++hx) {       // see the dQ kernel: two issuing threads, buf_free orders buffer reuse
+        if (hx >= 2 && !mbar_wait(&buf_free[hx & 1], ((hx - 2) >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) goto done;
+        if (!issue_sdp(hx)) goto done;
+      }
+    }
+  } else if (warp == ACC_WARP) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_acc = make_idesc_bf16(BT, D, 0, 1);      // dV += Pᵀ·dO, dK += dSᵀ·Q (N-major B)
       for (int hx = 0; hx < n_half; ++hx) {
-        if (hx + 1 < n_half && !issue_sdp(hx + 1)) goto done;
         const int it = hx >> 1, hf = hx & 1, st = it & 1, buf = hx & 1;
         if (!mbar_wait(&ds_full[buf], (hx >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
         tc_fence_after();
@@ -411,85 +434,90 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           umma_bf16_ts(T_DK, tdp + packed_col(k), make_smem_desc(sqa + (hf * 4 + k) * 2048, CHUNK_BYTES, 1024), idesc_acc,
                        (hx | k) != 0);
         }
+        umma_commit(&buf_free[buf]);
         if (hf == 1) umma_commit(&qd_empty[st]);
       }
       umma_commit(acc_done);
     }
   } else {
     const int qtr = warp & 3, ch = (warp - 2) >> 2;
-    const int tid256 = (warp - 2) * 32 + lane;        // 0..255 among the softmax threads
     const int kk = k0 + qtr * 32 + lane;              // this thread's key row
     const bool key_valid = kk < p.T;
     const uint32_t lane_off = static_cast<uint32_t>(qtr * 32) << 16;
     bool ok = true;     // after a timed-out wait the thread keeps meeting its peers at the named barrier, idle
     const bool plain_causal = p.row_start == nullptr && p.window_left < 0 && k0 + BT <= p.T;
-    for (int hx = 0; hx < n_half; ++hx) {
+    // Ping-pong: warp group `ch` owns the halves with hx & 1 == ch, i.e. always the query columns ch·64 … ch·64+63 of a
+    // tile (buffer ch), and converts all 64 of them; it fills and reads only its own 64 entries of the per-query
+    // statistics, so the two groups never wait for each other.
+    const int tid128 = qtr * 32 + lane;               // 0..127 inside the group
+    for (int hx = ch; hx < n_half; hx += 2) {
       const int it = hx >> 1, hf = hx & 1, st = it & 1, buf = hx & 1;
       const int hq = g * group + it / tiles_per_head;
       const int q0 = (i_begin + it % tiles_per_head) * BT;
       float* a_lse = aux + st * 3 * BT;
       float* a_dlt = a_lse + BT;
       int* a_lo = reinterpret_cast<int*>(a_dlt + BT);
-      if (hf == 0) {
-        // per-query statistics of this tile → shared memory (the first 128 softmax threads fill one entry each)
-        if (ok && tid256 < BT) {
-          const int rq = q0 + tid256;
-          const bool v = rq < p.T;
-          const size_t si = (static_cast<size_t>(b) * p.H + hq) * p.T + (v ? rq : 0);
-          a_lse[tid256] = v ? p.lse[si] * kLog2e_b : 0.f;
-          a_dlt[tid256] = v ? p.delta[si] : 0.f;
-          a_lo[tid256] = v ? lo_of_row(p, b, rq) : 0x7fffffff;    // invalid query rows see nothing
-        }
-        named_bar_sync_256();
+      if (ok && tid128 < HB) {
+        const int col = hf * HB + tid128;
+        const int rq = q0 + col;
+        const bool v = rq < p.T;
+        const size_t si = (static_cast<size_t>(b) * p.H + hq) * p.T + (v ? rq : 0);
+        a_lse[col] = v ? p.lse[si] * kLog2e_b : 0.f;
+        a_dlt[col] = v ? p.delta[si] : 0.f;
+        a_lo[col] = v ? lo_of_row(p, b, rq) : 0x7fffffff;    // invalid query rows see nothing
       }
+      if (ch == 0) asm volatile("bar.sync 1, 128;" ::: "memory"); else asm volatile("bar.sync 2, 128;" ::: "memory");
       if (!ok) continue;
       if (!mbar_wait(&sdp_full[buf], (hx >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; continue; }
       tc_fence_after();
-      const uint32_t ts = tmem_base + buf * 128 + ch * 32 + lane_off, tdp = ts + 64;
-      const int cbase = hf * HB + ch * 32;            // first query column (within the 128-query tile) of this warp
-      uint32_t sr[32], dr[32];
-      tmem_ld_32x32(ts, sr);
-      tmem_ld_32x32(tdp, dr);
-      tmem_ld_wait();
-      uint32_t wp[16], wd[16];
       const float sl2 = p.scale_log2;
       // every (key, query) pair of the tile is visible: queries at or after the last key, no window / document bound
       const bool full_tile = plain_causal && q0 >= k0 + BT - 1 && q0 + BT <= p.T;
-      if (full_tile) {
-        const float4* l4 = reinterpret_cast<const float4*>(a_lse + cbase);
-        const float4* d4 = reinterpret_cast<const float4*>(a_dlt + cbase);
 #pragma unroll
-        for (int v4 = 0; v4 < 8; ++v4) {
-          const float4 ls = l4[v4], dl = d4[v4];
-          const float lsa[4] = {ls.x, ls.y, ls.z, ls.w}, dla[4] = {dl.x, dl.y, dl.z, dl.w};
+      for (int cc = 0; cc < 2; ++cc) {
+        const uint32_t ts = tmem_base + buf * 128 + cc * 32 + lane_off, tdp = ts + 64;
+        const int cbase = hf * HB + cc * 32;          // first query column (within the 128-query tile) of this chunk
+        uint32_t sr[32], dr[32];
+        tmem_ld_32x32(ts, sr);
+        tmem_ld_32x32(tdp, dr);
+        tmem_ld_wait();
+        uint32_t wp[16], wd[16];
+        if (full_tile) {
+          const float4* l4 = reinterpret_cast<const float4*>(a_lse + cbase);
+          const float4* d4 = reinterpret_cast<const float4*>(a_dlt + cbase);
 #pragma unroll
-          for (int h2 = 0; h2 < 2; ++h2) {
-            const int c = 4 * v4 + 2 * h2;
-            const float p0 = exp2f(fmaf(__uint_as_float(sr[c]), sl2, -lsa[2 * h2]));
-            const float p1 = exp2f(fmaf(__uint_as_float(sr[c + 1]), sl2, -lsa[2 * h2 + 1]));
-            wp[c >> 1] = pack_bf16x2(p0, p1);
-            wd[c >> 1] = pack_bf16x2(p0 * (__uint_as_float(dr[c]) - dla[2 * h2]), p1 * (__uint_as_float(dr[c + 1]) - dla[2 * h2 + 1]));
+          for (int v4 = 0; v4 < 8; ++v4) {
+            const float4 ls = l4[v4], dl = d4[v4];
+            const float lsa[4] = {ls.x, ls.y, ls.z, ls.w}, dla[4] = {dl.x, dl.y, dl.z, dl.w};
+#pragma unroll
+            for (int h2 = 0; h2 < 2; ++h2) {
+              const int c = 4 * v4 + 2 * h2;
+              const float p0 = exp2f(fmaf(__uint_as_float(sr[c]), sl2, -lsa[2 * h2]));
+              const float p1 = exp2f(fmaf(__uint_as_float(sr[c + 1]), sl2, -lsa[2 * h2 + 1]));
+              wp[c >> 1] = pack_bf16x2(p0, p1);
+              wd[c >> 1] = pack_bf16x2(p0 * (__uint_as_float(dr[c]) - dla[2 * h2]), p1 * (__uint_as_float(dr[c + 1]) - dla[2 * h2 + 1]));
+            }
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            float pv[2], dv2[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int col = cbase + 2 * e + u;
+              const int rq = q0 + col;
+              float pr = exp2f(fmaf(__uint_as_float(sr[2 * e + u]), sl2, -a_lse[col]));
+              if (!key_valid || kk > rq || kk < a_lo[col]) pr = 0.f;
+              pv[u] = pr;
+              dv2[u] = pr * (__uint_as_float(dr[2 * e + u]) - a_dlt[col]);
+            }
+            wp[e] = pack_bf16x2(pv[0], pv[1]);
+            wd[e] = pack_bf16x2(dv2[0], dv2[1]);
           }
         }
-      } else {
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          float pv[2], dv2[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = cbase + 2 * e + u;
-            const int rq = q0 + col;
-            float pr = exp2f(fmaf(__uint_as_float(sr[2 * e + u]), sl2, -a_lse[col]));
-            if (!key_valid || kk > rq || kk < a_lo[col]) pr = 0.f;
-            pv[u] = pr;
-            dv2[u] = pr * (__uint_as_float(dr[2 * e + u]) - a_dlt[col]);
-          }
-          wp[e] = pack_bf16x2(pv[0], pv[1]);
-          wd[e] = pack_bf16x2(dv2[0], dv2[1]);
-        }
+        tmem_st_32x16(ts, wp);
+        tmem_st_32x16(tdp, wd);
       }
-      tmem_st_32x16(ts, wp);
-      tmem_st_32x16(tdp, wd);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
