@@ -12,6 +12,13 @@ import torch.multiprocessing as mp
 from archscale_b200.utils.health import Heartbeat, PeerFailure, check_device
 
 
+
+def _free_port() -> int:
+    import socket
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        return sk.getsockname()[1]
+
 def test_stale_heartbeat_and_abort_flag_are_detected():
     store = dist.HashStore()
     a = Heartbeat(store, 0, 2, stale_after_s=0.2)
@@ -57,7 +64,7 @@ def _worker(rank, world, port, path, q):
 def test_rank_failure_between_steps_stops_the_other_rank_on_the_host():
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29800 + os.getpid() % 90
+    port = _free_port()
     with tempfile.TemporaryDirectory() as d:
         procs = [ctx.Process(target=_worker, args=(r, 2, port, os.path.join(d, "store"), q)) for r in range(2)]
         for p in procs:

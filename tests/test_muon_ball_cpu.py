@@ -15,6 +15,13 @@ from archscale_b200.parallel.fsdp import FSDPEngine
 from archscale_b200.parallel.mesh import build_mesh
 
 
+
+def _free_port() -> int:
+    import socket
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        return sk.getsockname()[1]
+
 def _cfg():
     return Config.from_name("transformer_gqa4_d8", n_layer=2, ar=None, n_embd=128, n_head=2, n_query_groups=1, head_dim=64,
                             intermediate_size=256, vocab_size=512, padding_multiple=64, block_size=64)
@@ -100,7 +107,7 @@ def test_two_ranks_match_single_process():
     ref = [_step(m, eng, opt, data[s]) for s in range(3)]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29900 + os.getpid() % 90
+    port = _free_port()
     procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()

@@ -15,6 +15,13 @@ from archscale_b200.parallel.fsdp import FSDPEngine
 from archscale_b200.parallel.mesh import Mesh, build_mesh
 
 
+
+def _free_port() -> int:
+    import socket
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        return sk.getsockname()[1]
+
 def _cfg():
     return Config.from_name("transformer_gqa4_d8", n_layer=2, ar=None, n_embd=128, n_head=4, n_query_groups=2, head_dim=32,
                             intermediate_size=256, vocab_size=512, padding_multiple=64, block_size=64, qk_norm=True)
@@ -77,7 +84,7 @@ def test_tp2_matches_single_process():
     ref_losses, ref_norms, _ = _run(_model(), Mesh(world=1, rank=0, dp=1, fsdp=1, tp=1), 4)
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29500 + os.getpid() % 400
+    port = _free_port()
     procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
