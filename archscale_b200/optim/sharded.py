@@ -75,6 +75,7 @@ class ShardedOptimizer:
         self.hyper_vecs: List[Tuple[FlatGroup, ParamSpec, int]] = []   # Adam-H parameters (group, spec, norm_idx)
         self._classify()
         self.last_lrs: Dict[str, float] = {}
+        self._norm_idx_cache: Dict[tuple, torch.Tensor] = {}
 
     # ------------------------------------------------------------------ setup
     def _classify(self) -> None:
@@ -383,12 +384,33 @@ class ShardedOptimizer:
             for mt in mine:
                 by_shape.setdefault((mt.rows, mt.cols), []).append(mt)
             for (r, c), lst in by_shape.items():
-                stack = torch.stack([u_full[mt.offset:mt.offset + r * c].view(r, c) for mt in lst])
+                # runs of matrices stored back to back (the experts of one 3-D parameter, sibling projections) are
+                # orthogonalised from one strided view and written back with one copy: no per-matrix launches
+                lst = sorted(lst, key=lambda mt: mt.offset)
+                runs: List[List[_Mat]] = [[lst[0]]]
+                for mt in lst[1:]:
+                    if mt.offset == runs[-1][-1].offset + r * c:
+                        runs[-1].append(mt)
+                    else:
+                        runs.append([mt])
+                if len(runs) == 1:
+                    off0, n = runs[0][0].offset, len(lst)
+                    stack = u_full[off0:off0 + n * r * c].view(n, r, c)
+                else:
+                    stack = torch.cat([u_full[run[0].offset:run[0].offset + len(run) * r * c].view(len(run), r, c)
+                                       for run in runs])
                 O = self._orthogonalise(stack)
                 sq = torch.linalg.vector_norm(O, dim=(-2, -1), dtype=torch.float32).square()
-                for i, mt in enumerate(lst):
-                    o_full[mt.offset:mt.offset + r * c].copy_(O[i].reshape(-1))
-                    u_sq[mt.norm_idx] += sq[i]
+                i = 0
+                for run in runs:
+                    n = len(run)
+                    o_full[run[0].offset:run[0].offset + n * r * c].view(n, r, c).copy_(O[i:i + n])
+                    i += n
+                key = (gid, r, c)
+                idx = self._norm_idx_cache.get(key)
+                if idx is None:
+                    idx = self._norm_idx_cache[key] = torch.tensor([mt.norm_idx for mt in lst], device=eng.device)
+                u_sq.index_add_(0, idx, sq)
             # 4. return the updates to the shards
             if g.world > 1:
                 if eng.symm is not None:
