@@ -162,6 +162,8 @@ int b200_diff_combine_fwd(const void* a1, const void* a2, const float* lam, cons
 int b200_diff_combine_bwd(const void* dy, const void* a1, const void* a2, const float* lam, const float* w, float c, const float* rstd,
                           void* da1, void* da2, float* dlam, float* dw, long long rows, int width, cudaStream_t st);
 
+void b200_gemm_set_splitk_workspace(uint32_t* sem, int n);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,5 +1,6 @@
 // Python bindings: torch tensors in, raw pointers to the C entry points of api.h out.
 // Output tensors are allocated here with torch's caching allocator on the current stream.
+#include <cstdlib>
 #include <torch/extension.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -24,6 +25,13 @@ at::Tensor g_status;  // int32 [1] per process: device-side error word of the tc
 int num_sms() {
   if (!g_num_sms) g_num_sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   return g_num_sms;
+}
+at::Tensor g_splitk_sem;  // counters of the serial split-K weight-gradient path (see gemm_bf16.cu)
+void ensure_splitk_workspace(const at::Device& dev) {
+  if (!g_splitk_sem.defined()) {
+    g_splitk_sem = at::zeros({1 << 16}, at::TensorOptions().dtype(at::kInt).device(dev));
+    b200_gemm_set_splitk_workspace(reinterpret_cast<uint32_t*>(g_splitk_sem.data_ptr<int>()), 1 << 16);
+  }
 }
 int* status_ptr(const at::Device& dev) {
   if (!g_status.defined()) g_status = at::zeros({1}, at::TensorOptions().dtype(at::kInt).device(dev));
@@ -51,6 +59,10 @@ at::Tensor gemm_bf16(const at::Tensor& a, const at::Tensor& b, int64_t mode, at:
     out = at::empty({M, N}, a.options().dtype(out_dtype));
   }
   const int out_f32 = out.scalar_type() == at::kFloat;
+  // accumulating (weight-gradient) GEMMs may split K; the counters are shared, so such GEMMs must not overlap on
+  // different streams (they are all issued on the autograd stream).  ARCHSCALE_B200_NO_SPLITK=1 turns it off.
+  static const bool no_splitk = std::getenv("ARCHSCALE_B200_NO_SPLITK") != nullptr;
+  if (accumulate && !no_splitk) ensure_splitk_workspace(a.device());
   check(b200_gemm_bf16((int)mode, a.data_ptr(), b.data_ptr(), out.data_ptr(), nullptr, (int)M, (int)N, (int)K,
                        (int)a.stride(0), (int)b.stride(0), (int)out.stride(0), 1.f, 0.f, out_f32, accumulate, num_sms(),
                        status_ptr(a.device()), cur_stream()), "gemm_bf16");

@@ -81,6 +81,12 @@ struct GemmParams {
   float alpha, beta;
   int accumulate;   // fp32 output: out += result
   int* status;
+  // Serial split-K (fp32 accumulating output only): the K loop of every output tile is cut into `split_k` pieces that
+  // different CTAs compute; they add their partial tile to `out` one after the other, in split order, handing over
+  // through one counter per (tile, epilogue warp) in `sem` (zero between launches).  Fills the last wave of long-K
+  // weight-gradient GEMMs whose tile count is a poor multiple of the SM count; the summation order stays fixed.
+  int split_k;
+  uint32_t* sem;
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
@@ -188,6 +194,8 @@ struct Tile {
   int b_row;     // row offset added to B's row coordinate (expert base)
   int kb0, kb1;  // K-block range
   size_t out_off;  // element offset added to the output pointer (expert base for GROUPED=2)
+  int split;       // split-K piece of this work item (0 without split-K)
+  int tile_id;     // output tile index (semaphore slot)
 };
 
 template <int A_MN, int B_MN, int OUT_F32, int FUSED_AG = 0, int GROUPED = 0>
@@ -219,7 +227,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
   const int num_n = (p.N + BN - 1) / BN;
   const int num_m = GROUPED == 1 ? s_off[GROUPED ? gp.E : 0] / BM : (p.M + BM - 1) / BM;
-  const int num_tiles = ((GROUPED == 2 || GROUPED == 3) ? gp.E : 1) * num_m * num_n;
+  const int SK = (GROUPED == 0 && FUSED_AG == 0 && OUT_F32 && p.split_k > 1) ? p.split_k : 1;
+  const int num_tiles = ((GROUPED == 2 || GROUPED == 3) ? gp.E : 1) * num_m * num_n * SK;
   const int num_kb = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -263,8 +272,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tl.kb0 = s_off[e] / BK; tl.kb1 = s_off[e + 1] / BK;
       tl.out_off = static_cast<size_t>(e) * p.M * p.ldc;
     } else {
-      int mi, ni; tile_coords(t, mi, ni);
+      // split-K: all pieces 0 come first in the global order, so a piece only ever waits for work with a smaller index
+      const int base_tiles = num_m * num_n;
+      const int split = SK > 1 ? t / base_tiles : 0;
+      const int tt = t - split * base_tiles;
+      int mi, ni; tile_coords(tt, mi, ni);
       tl.m0 = mi * BM; tl.n0 = ni * BN; tl.kb0 = 0; tl.kb1 = num_kb; tl.out_off = 0; tl.b_row = 0;
+      tl.split = split; tl.tile_id = tt;
+      if (SK > 1) {
+        const int per = (num_kb + SK - 1) / SK;
+        tl.kb0 = split * per < num_kb ? split * per : num_kb;
+        tl.kb1 = tl.kb0 + per < num_kb ? tl.kb0 + per : num_kb;
+      }
       if (GROUPED == 1) {
         int lo = 0, hi = gp.E;          // expert whose segment holds row m0
         while (lo + 1 < hi) { const int mid = (lo + hi) >> 1; if (s_off[mid] <= tl.m0) lo = mid; else hi = mid; }
@@ -373,6 +392,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int col0 = tl.n0;
       const int row_limit = GROUPED == 1 ? s_off[gp.E] : p.M;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      int acc_flag = p.accumulate;
+      if (OUT_F32 && SK > 1) {
+        // wait for the previous piece of this tile (this warp's 32 rows) to have been added
+        if (tl.split > 0) {
+          bool ok = true;
+          if (lane == 0) {
+            const uint32_t* sp = p.sem + tl.tile_id * 4 + q;
+            const long long t0 = clock64();
+            while (ld_acquire_gpu(sp) != static_cast<uint32_t>(tl.split)) {
+              if (*abort_flag || clock64() - t0 > kWaitLimitCycles * 4) {
+                *abort_flag = 1;
+                if (p.status) atomicCAS(p.status, 0, STATUS_TIMEOUT_TMEM_EMPTY);
+                ok = false;
+                break;
+              }
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          if (!ok) goto done;
+          acc_flag = 1;
+        }
+      }
       // FUSED_AG == 2: a tile of this rank's own slice is finished here — the peers computed their partial products of
       // these rows first, so the epilogue adds them (loads from peer memory) and writes the reduced rows directly.
       bool own_tile = false;
@@ -423,7 +464,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               if (col + j < p.N) {
                 float4 v = make_float4(__uint_as_float(r[j]) * p.alpha, __uint_as_float(r[j + 1]) * p.alpha,
                                        __uint_as_float(r[j + 2]) * p.alpha, __uint_as_float(r[j + 3]) * p.alpha);
-                if (p.accumulate) {
+                if (acc_flag) {
                   const float4 old = *reinterpret_cast<const float4*>(o + j);
                   v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
                 }
@@ -478,6 +519,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (OUT_F32 && SK > 1) {
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) st_release_gpu(p.sem + tl.tile_id * 4 + q, tl.split + 1 == SK ? 0u : static_cast<uint32_t>(tl.split + 1));
+      }
       if (FUSED_AG == 2 && !own_tile) {
         // this warp's 32 rows × 256 columns of the tile are stored: publish them to the peers
         __threadfence_system();
@@ -549,6 +595,21 @@ int make_tmap_3d_bf16(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+static uint32_t* g_splitk_sem = nullptr;
+static int g_splitk_sem_len = 0;
+
+// Pieces per output tile that best fill whole waves of `sms` CTAs (1 = no split); every piece keeps ≥ 64 K-blocks.
+static int choose_split_k(int tiles, int num_kb, int sms) {
+  auto eff = [&](int s) { const long long w = static_cast<long long>(tiles) * s; return static_cast<double>(w) / (((w + sms - 1) / sms) * sms); };
+  int best = 1;
+  double best_eff = eff(1);
+  for (int s = 2; s <= 4; ++s) {
+    if (num_kb / s < 64 || tiles * 4 > g_splitk_sem_len) break;
+    if (eff(s) > best_eff * 1.08) { best = s; best_eff = eff(s); }
+  }
+  return best;
+}
+
 template <int A_MN, int B_MN, int OUT_F32>
 static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int sms, cudaStream_t st) {
   auto kern = gemm_bf16_kernel<A_MN, B_MN, OUT_F32>;
@@ -558,14 +619,27 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const Ge
     configured = true;
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-  const int grid = tiles < sms ? tiles : sms;
+  GemmParams pp = p;
+  if (OUT_F32 && p.accumulate && g_splitk_sem != nullptr) {
+    pp.split_k = choose_split_k(tiles, (p.K + BK - 1) / BK, sms);
+    pp.sem = g_splitk_sem;
+  }
+  const int work = tiles * (pp.split_k > 1 ? pp.split_k : 1);
+  const int grid = work < sms ? work : sms;
   AgParams none{};
   GroupParams nog{};
-  kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb, p, none, nog, RsParams{});
+  kern<<<grid, NUM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb, pp, none, nog, RsParams{});
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
 }  // namespace b200
+
+// Workspace of the serial split-K path: `n` zero-initialised uint32 counters on the current device (4 per output tile).
+// Without it (the default) weight-gradient GEMMs never split.
+extern "C" void b200_gemm_set_splitk_workspace(uint32_t* sem, int n) {
+  b200::g_splitk_sem = sem;
+  b200::g_splitk_sem_len = n;
+}
 
 extern "C" int b200_gemm_bf16(int mode, const void* A, const void* B, void* out, const void* cin, int M, int N, int K,
                               int lda, int ldb, int ldc, float alpha, float beta, int out_f32, int accumulate,

@@ -255,3 +255,24 @@ def test_newton_schulz_batched_matches_per_matrix():
     assert _rel(O, R) < 2e-2
     Gt = torch.randn(4, 1024, 256, device="cuda")          # tall: transposed internally
     assert _rel(ops.newton_schulz(Gt), ops.newton_schulz_ref(Gt)) < 0.1
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(3072, 2048, 16384), (2048, 5632, 8192), (512, 512, 32768)])
+def test_wgrad_split_k_accumulates_exactly_like_unsplit(M, N, K):
+    """Accumulating TN GEMM whose tile count fills the last wave badly: the serial split-K path must add the same
+    products (fp32 accumulation, fixed order) as a reference matmul, on top of the existing contents, twice in a row."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from archscale_b200.ops import backend
+    ext = backend.require_extension()
+    torch.manual_seed(0)
+    a = (torch.randn(K, M, device="cuda") * 0.1).bfloat16()
+    b = (torch.randn(K, N, device="cuda") * 0.1).bfloat16()
+    acc = torch.ones(M, N, device="cuda")
+    ext.gemm_bf16(a, b, 2, torch.float32, acc)
+    ext.gemm_bf16(a, b, 2, torch.float32, acc)
+    torch.cuda.synchronize()
+    ref = 1.0 + 2.0 * (a.float().t() @ b.float())
+    assert ext.device_status() == 0
+    assert (acc - ref).abs().max().item() <= 2e-3 * ref.abs().max().item()
