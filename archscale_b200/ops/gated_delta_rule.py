@@ -9,9 +9,11 @@ call at `lit_gpt/gated_deltanet.py:315-326`.  Per head, with state ``S ∈ R^{Dk
 q, k are L2-normalised over the head dim first; ``g ≤ 0`` is a log-decay; ``β`` may reach 2
 (negative eigenvalues).  Packed sequences reset ``S`` at ``cu_seqlens`` boundaries.
 
-Two PyTorch implementations: :func:`gated_delta_rule_recurrent_ref` (step-by-step oracle) and
-:func:`gated_delta_rule_chunk` (chunk-of-64 WY form, differentiable, all matmuls — the shape
-the CUDA kernel ``csrc/gdn_chunk.cu`` follows).
+Implementations: :func:`gated_delta_rule_recurrent_ref` (step-by-step oracle) and
+:func:`gated_delta_rule_chunk` (chunk-of-64 WY form, differentiable).  In the chunk form everything is a batched
+matmul over independent chunks except one recurrence over the chunks of a sequence; on a GPU that recurrence runs
+in the tcgen05 kernel ``csrc/gdn_chunk.cu`` (forward and, over the chunks in reverse, backward) and the
+chunk-parallel products around it are batched library matmuls.
 """
 from __future__ import annotations
 
@@ -51,6 +53,94 @@ def gated_delta_rule_recurrent_ref(q, k, v, g, beta, scale: Optional[float] = No
     return torch.stack(out, dim=1).to(dtype)
 
 
+def _chunk_core_ref(w, u, kd, qg, qk, a):
+    """The recurrence over chunks in plain PyTorch.  w, kd, qg: (BH,nC,c,Dk); u: (BH,nC,c,Dv); qk: (BH,nC,c,c);
+    a: (BH,nC) → o: (BH,nC,c,Dv).  With S the (Dk×Dv) state at the chunk start:
+    ``v = u − w·S``, ``o = qg·S + qk·v``, ``S ← a·S + kdᵀ·v``."""
+    BH, nC, _, Dk = w.shape
+    S = w.new_zeros(BH, Dk, u.shape[-1])
+    outs = []
+    for n in range(nC):
+        v_new = u[:, n] - w[:, n] @ S
+        outs.append(qg[:, n] @ S + qk[:, n] @ v_new)
+        S = S * a[:, n, None, None] + kd[:, n].transpose(-1, -2) @ v_new
+    return torch.stack(outs, dim=1)
+
+
+def _gdn_state_ref(a_op, c_add, bm_op, e_op, f_op, decay, reverse: bool, sgn_p: float, sgn_v: float):
+    """What one launch of the ``gdn_state`` kernel computes, in PyTorch (operand dtype kept, fp32 state).  With the
+    transposed state X (Dv×Dk), per chunk n: ``P = X·Aᵀ``, ``V = C + sgn_p·Pᵀ``, ``X ← a_n·X + sgn_v·Vᵀ·Bm (+ Eᵀ·F)``;
+    returns V, the state each chunk saw, and the final state."""
+    BH, Tp, Dk = a_op.shape
+    Dv, nC = c_add.shape[-1], Tp // 64
+    ch = lambda t: t.reshape(BH, nC, 64, t.shape[-1]).float()
+    A, C, Bm = ch(a_op), ch(c_add), ch(bm_op)
+    X = A.new_zeros(BH, Dv, Dk)
+    v_out, x_all = torch.empty_like(C), A.new_empty(BH, nC, Dv, Dk)
+    for s in range(nC):
+        n = nC - 1 - s if reverse else s
+        Xr = X.to(a_op.dtype).float()
+        x_all[:, n] = Xr
+        V = (C[:, n] + sgn_p * (Xr @ A[:, n].transpose(-1, -2)).transpose(-1, -2)).to(a_op.dtype).float()
+        v_out[:, n] = V
+        X = X * decay[:, n, None, None].float() + sgn_v * (V.transpose(-1, -2) @ Bm[:, n])
+        if e_op is not None:
+            X = X + ch(e_op)[:, n].transpose(-1, -2) @ ch(f_op)[:, n]
+    return v_out.reshape(BH, Tp, Dv).to(a_op.dtype), x_all.to(a_op.dtype), X
+
+
+def _gdn_state(a_op, c_add, bm_op, e_op, f_op, decay, reverse, sgn_p, sgn_v):
+    if a_op.is_cuda:
+        out = backend.require_extension().gdn_state(a_op, c_add, bm_op, e_op, f_op, decay, reverse, sgn_p, sgn_v)
+        backend.count_launch()
+        return out
+    return _gdn_state_ref(a_op, c_add, bm_op, e_op, f_op, decay, reverse, sgn_p, sgn_v)
+
+
+class _ChunkCoreFn(torch.autograd.Function):
+    """Same contract as :func:`_chunk_core_ref`; the recurrence runs in ``gdn_state`` (bf16 operands, fp32 state)."""
+
+    @staticmethod
+    def forward(ctx, w, u, kd, qg, qk, a):
+        BH, nC, c, Dk = w.shape
+        Dv = u.shape[-1]
+        bf = torch.bfloat16 if w.is_cuda else w.dtype          # the kernel takes bf16 operands
+        wb, ub, kdb, qgb = (t.to(bf).reshape(BH, nC * c, -1).contiguous() for t in (w, u, kd, qg))
+        qkb, af = qk.to(bf).contiguous(), a.float().contiguous()
+        v, s_all, _ = _gdn_state(wb, ub, kdb, None, None, af, False, -1.0, 1.0)
+        o = qgb.view(BH, nC, c, Dk) @ s_all.transpose(-1, -2) + qkb @ v.view(BH, nC, c, Dv)
+        ctx.save_for_backward(wb, ub, kdb, qgb, qkb, af)
+        ctx.dtypes = (w.dtype, u.dtype, kd.dtype, qg.dtype, qk.dtype, a.dtype)
+        return o.to(u.dtype)
+
+    @staticmethod
+    def backward(ctx, do):
+        wb, ub, kdb, qgb, qkb, af = ctx.saved_tensors
+        BH, nC, c, _ = qkb.shape
+        Dk, Dv = wb.shape[-1], ub.shape[-1]
+        # the states are not kept between the passes: the forward recurrence runs again
+        v, s_all, _ = _gdn_state(wb, ub, kdb, None, None, af, False, -1.0, 1.0)
+        dob = do.to(wb.dtype).contiguous()                                     # (BH,nC,c,Dv)
+        g = (qkb.transpose(-1, -2) @ dob).reshape(BH, nC * c, Dv)              # ∂L/∂v through o = qk·v
+        dv, ds_all, _ = _gdn_state(kdb, g, wb, dob.view(BH, nC * c, Dv), qgb, af, True, 1.0, -1.0)
+        v4, dv4 = v.view(BH, nC, c, Dv), dv.view(BH, nC, c, Dv)
+        dqg = dob @ s_all                                                      # s_all: (BH,nC,Dv,Dk)
+        dqk = dob @ v4.transpose(-1, -2)
+        dw = -(dv4 @ s_all)
+        dkd = v4 @ ds_all                                                      # ds_all[n] = ∂L/∂S after chunk n
+        da = torch.einsum("bnvk,bnvk->bn", s_all, ds_all)
+        dt = ctx.dtypes
+        return dw.to(dt[0]), dv4.to(dt[1]), dkd.to(dt[2]), dqg.to(dt[3]), dqk.to(dt[4]), da.to(dt[5])
+
+
+def _chunk_core(w, u, kd, qg, qk, a):
+    Dk, Dv = w.shape[-1], u.shape[-1]
+    if (w.is_cuda and w.shape[2] == 64 and Dk in (128, 256) and Dv % 128 == 0 and backend.has("gdn_state")
+            and backend.use_cuda_kernel("gated_delta_rule", w, u)):
+        return _ChunkCoreFn.apply(w, u, kd, qg, qk, a)
+    return _chunk_core_ref(w, u, kd, qg, qk, a)
+
+
 def gated_delta_rule_chunk(q, k, v, g, beta, scale: Optional[float] = None, l2norm: bool = True,
                            cu_seqlens: Optional[torch.Tensor] = None, chunk: int = 64):
     """Chunked WY formulation.  Equivalent to the recurrent oracle; differentiable."""
@@ -77,35 +167,29 @@ def gated_delta_rule_chunk(q, k, v, g, beta, scale: Optional[float] = None, l2no
         g, beta = (F.pad(t, (0, 0, 0, pad)) for t in (g, beta))
     Tp = T + pad
     nC = Tp // chunk
-    # (B,H,nC,c,·)
-    r = lambda t: t.permute(0, 2, 1, 3).reshape(B, H, nC, chunk, t.shape[-1])
+    # (B·H,nC,c,·)
+    r = lambda t: t.permute(0, 2, 1, 3).reshape(B * H, nC, chunk, t.shape[-1])
     q, k, v = r(q) * scale, r(k), r(v)
-    g = g.permute(0, 2, 1).reshape(B, H, nC, chunk)
-    beta = beta.permute(0, 2, 1).reshape(B, H, nC, chunk)
+    g = g.permute(0, 2, 1).reshape(B * H, nC, chunk)
+    beta = beta.permute(0, 2, 1).reshape(B * H, nC, chunk)
     gc = torch.cumsum(g, dim=-1)                                         # inclusive log-decay inside the chunk
     kb = k * beta.unsqueeze(-1)
     vb = v * beta.unsqueeze(-1)
     dec = torch.exp(gc.unsqueeze(-1) - gc.unsqueeze(-2))                 # [i,j] = exp(gc_i - gc_j)
     strict = torch.tril(torch.ones(chunk, chunk, device=q.device, dtype=torch.bool), -1)
     incl = torch.tril(torch.ones(chunk, chunk, device=q.device, dtype=torch.bool), 0)
-    A = torch.einsum("bhnik,bhnjk->bhnij", kb, k) * dec
-    A = A.masked_fill(~strict, 0.0)
+    A = ((kb @ k.transpose(-1, -2)) * dec).masked_fill(~strict, 0.0)
     eye = torch.eye(chunk, device=q.device, dtype=q.dtype)
     # (I + A) is unit lower-triangular → solve for W, U:  (I+A) U = β v ; (I+A) W = β k·exp(gc)
     Tm = torch.linalg.solve_triangular(eye + A, eye.expand_as(A), upper=False, unitriangular=True)
     u = Tm @ vb
     w = Tm @ (kb * torch.exp(gc).unsqueeze(-1))
-    S = q.new_zeros(B, H, Dk, Dv)
-    qk = (torch.einsum("bhnik,bhnjk->bhnij", q, k) * dec).masked_fill(~incl, 0.0)
-    outs = []
-    for n in range(nC):
-        v_new = u[:, :, n] - w[:, :, n] @ S                              # c × Dv
-        o_inter = (q[:, :, n] * torch.exp(gc[:, :, n]).unsqueeze(-1)) @ S
-        outs.append(o_inter + qk[:, :, n] @ v_new)
-        g_last = gc[:, :, n, -1]
-        kdec = k[:, :, n] * torch.exp(g_last.unsqueeze(-1) - gc[:, :, n]).unsqueeze(-1)
-        S = S * torch.exp(g_last).unsqueeze(-1).unsqueeze(-1) + kdec.transpose(-1, -2) @ v_new
-    o = torch.stack(outs, dim=2).reshape(B, H, Tp, Dv).permute(0, 2, 1, 3)[:, :T]
+    qk = ((q @ k.transpose(-1, -2)) * dec).masked_fill(~incl, 0.0)
+    g_last = gc[..., -1]
+    kd = k * torch.exp(g_last.unsqueeze(-1) - gc).unsqueeze(-1)          # keys decayed to the end of their chunk
+    qg = q * torch.exp(gc).unsqueeze(-1)                                 # queries decayed from the chunk start
+    o = _chunk_core(w, u, kd, qg, qk, torch.exp(g_last))                 # (B·H,nC,c,Dv)
+    o = o.reshape(B, H, Tp, Dv).permute(0, 2, 1, 3)[:, :T]
     return o.to(dtype)
 
 
