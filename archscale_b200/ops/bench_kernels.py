@@ -214,6 +214,47 @@ def bench_mamba(res: list) -> None:
         print(res[-1], flush=True)
 
 
+def bench_gdn(res: list) -> None:
+    """Gated delta rule at the Gated-DeltaNet layer shape (6 heads, Dk 256, Dv 512): the recurrence kernel alone, and
+    the whole op forward / forward+backward against the same chunk form with the recurrence as a PyTorch loop."""
+    import importlib
+    G = importlib.import_module("archscale_b200.ops.gated_delta_rule")
+    ext = backend.require_extension()
+    for (B, T, H, Dk, Dv) in [(1, 4096, 6, 256, 512), (8, 4096, 6, 256, 512)]:
+        BH, nC = B * H, T // 64
+        mk = lambda d, sc: (torch.randn(BH, T, d, device="cuda") * sc).bfloat16()
+        a_op, bm_op, c_add, e_op, f_op = mk(Dk, 0.06), mk(Dk, 0.06), mk(Dv, 1.0), mk(Dv, 0.3), mk(Dk, 0.3)
+        decay = torch.rand(BH, nC, device="cuda") * 0.5 + 0.5
+        t_f = time_ms(lambda: ext.gdn_state(a_op, c_add, bm_op, None, None, decay, False, -1.0, 1.0))
+        t_b = time_ms(lambda: ext.gdn_state(a_op, c_add, bm_op, e_op, f_op, decay, True, 1.0, -1.0))
+        fl_f = 2.0 * BH * T * Dk * Dv * 2
+        res.append({"kernel": "gdn_state", "shape": [B, T, H, Dk, Dv], "ctas": BH * Dv // 128, "fwd_pass_ms": t_f,
+                    "fwd_tflops": fl_f / t_f / 1e9, "bwd_pass_ms": t_b, "bwd_tflops": 1.5 * fl_f / t_b / 1e9,
+                    "us_per_chunk_fwd": t_f * 1e3 / nC / max(1, -(-BH * Dv // 128 // 148))})
+        print(res[-1], flush=True)
+        q, k = (torch.randn(B, T, H, Dk, device="cuda").bfloat16().requires_grad_() for _ in range(2))
+        v = torch.randn(B, T, H, Dv, device="cuda").bfloat16().requires_grad_()
+        g = (-torch.rand(B, T, H, device="cuda") * 0.3).requires_grad_()
+        beta = (torch.rand(B, T, H, device="cuda") * 2).requires_grad_()
+        row = {"kernel": "gated_delta_rule", "shape": [B, T, H, Dk, Dv]}
+        for name, core in (("kernel", G._chunk_core), ("torch_loop", G._chunk_core_ref)):
+            if name == "torch_loop" and B > 1:
+                continue
+            saved, G._chunk_core = G._chunk_core, core
+            try:
+                f = lambda: G.gated_delta_rule(q, k, v, g, beta)
+                row[name + "_fwd_ms"] = time_ms(f, iters=3)
+
+                def fb():
+                    o = f()
+                    torch.autograd.grad(o, (q, k, v, g, beta), torch.ones_like(o))
+                row[name + "_fwd_bwd_ms"] = time_ms(fb, iters=3)
+            finally:
+                G._chunk_core = saved
+        res.append(row)
+        print(row, flush=True)
+
+
 def bench_mxfp8(res: list) -> None:
     """Block-scaled MXFP8 GEMM and its quantisers against the bf16 tcgen05 kernel on the same shapes."""
     from archscale_b200.ops import mxfp8
@@ -238,7 +279,7 @@ def bench_mxfp8(res: list) -> None:
 
 
 ALL = {"gemm": bench_gemm, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "ce": bench_ce, "rope": bench_rope,
-       "attn": bench_attn, "mamba": bench_mamba, "mxfp8": bench_mxfp8}
+       "attn": bench_attn, "mamba": bench_mamba, "mxfp8": bench_mxfp8, "gdn": bench_gdn}
 
 
 def main() -> None:

@@ -128,7 +128,7 @@ class _ChunkCoreFn(torch.autograd.Function):
         dqk = dob @ v4.transpose(-1, -2)
         dw = -(dv4 @ s_all)
         dkd = v4 @ ds_all                                                      # ds_all[n] = ∂L/∂S after chunk n
-        da = torch.einsum("bnvk,bnvk->bn", s_all, ds_all)
+        da = (s_all * ds_all).sum((-1, -2), dtype=torch.float32)
         dt = ctx.dtypes
         return dw.to(dt[0]), dv4.to(dt[1]), dkd.to(dt[2]), dqg.to(dt[3]), dqk.to(dt[4]), da.to(dt[5])
 
@@ -157,9 +157,6 @@ def gated_delta_rule_chunk(q, k, v, g, beta, scale: Optional[float] = None, l2no
                 outs.append(gated_delta_rule_chunk(q[:, s:e], k[:, s:e], v[:, s:e], g[:, s:e], beta[:, s:e],
                                                    scale, l2norm, None, chunk))
         return torch.cat(outs, dim=1)
-    q, k, v, g, beta = (t.float() for t in (q, k, v, g, beta))
-    if l2norm:
-        q, k = _l2norm(q), _l2norm(k)
     scale = Dk ** -0.5 if scale is None else scale
     pad = (-T) % chunk
     if pad:
@@ -167,9 +164,13 @@ def gated_delta_rule_chunk(q, k, v, g, beta, scale: Optional[float] = None, l2no
         g, beta = (F.pad(t, (0, 0, 0, pad)) for t in (g, beta))
     Tp = T + pad
     nC = Tp // chunk
-    # (B·H,nC,c,·)
-    r = lambda t: t.permute(0, 2, 1, 3).reshape(B * H, nC, chunk, t.shape[-1])
-    q, k, v = r(q) * scale, r(k), r(v)
+    # (B·H,nC,c,·): the strided copy moves the input dtype (bf16 in training), the fp32 math starts after it
+    r = lambda t: t.permute(0, 2, 1, 3).reshape(B * H, nC, chunk, t.shape[-1]).float()
+    q, k, v = r(q), r(k), r(v)
+    g, beta = g.float(), beta.float()
+    if l2norm:
+        q, k = _l2norm(q), _l2norm(k)
+    q = q * scale
     g = g.permute(0, 2, 1).reshape(B * H, nC, chunk)
     beta = beta.permute(0, 2, 1).reshape(B * H, nC, chunk)
     gc = torch.cumsum(g, dim=-1)                                         # inclusive log-decay inside the chunk
