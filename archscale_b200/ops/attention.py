@@ -116,10 +116,52 @@ class _AttnFn(torch.autograd.Function):
         return dq, dk, dv, None, None, None
 
 
+class _AttnSinkFn(torch.autograd.Function):
+    """Attention with a learnable per-head sink logit on the same kernels.  The sink adds ``exp(sink)`` to every softmax
+    denominator and nothing to the numerator, so with ``lse`` the plain log-sum-exp: ``lse' = logaddexp(lse, sink)`` and
+    ``out' = out · exp(lse − lse')``.  The backward kernels recompute the probabilities from the saved log-sum-exp and δ
+    from ``dO·O``, so given (out', lse') they return the sink-softmax gradients unchanged; the sink column itself gets
+    ``d sink_h = −Σ_{b,t} p_sink · δ`` with ``p_sink = exp(sink − lse')``."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, sink, scale, window_left, cu_seqlens):
+        ext = backend.require_extension()
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        row_start = doc_end = None
+        if cu_seqlens is not None:
+            T = q.shape[1]
+            row_start, doc_end = row_start_from_cu_seqlens(cu_seqlens, T), doc_end_from_cu_seqlens(cu_seqlens, T)
+        out, lse = ext.attn_fwd(q, k, v, scale, window_left, row_start)                 # lse: (B,H,T)
+        backend.count_launch()
+        sk = sink.float().view(1, -1, 1)
+        lse_s = torch.logaddexp(lse, sk)
+        keep = torch.exp(lse - lse_s)                                                   # share of the real keys
+        out_s = (out.float() * keep.permute(0, 2, 1).unsqueeze(-1)).to(out.dtype)
+        none = torch.empty(0)
+        ctx.save_for_backward(q, k, v, out_s, lse_s, sink, row_start if row_start is not None else none,
+                              doc_end if doc_end is not None else none)
+        ctx.scale, ctx.window_left, ctx.varlen = scale, window_left, cu_seqlens is not None
+        ctx.mark_non_differentiable(lse_s)
+        return out_s, lse_s
+
+    @staticmethod
+    def backward(ctx, dout, _dlse):
+        ext = backend.require_extension()
+        q, k, v, out_s, lse_s, sink, row_start, doc_end = ctx.saved_tensors
+        dout = dout.contiguous()
+        dq, dk, dv = ext.attn_bwd(dout, q, k, v, out_s, lse_s, ctx.scale, ctx.window_left,
+                                  row_start if ctx.varlen else None, doc_end if ctx.varlen else None)
+        backend.count_launch(3)
+        delta = (dout.float() * out_s.float()).sum(-1).permute(0, 2, 1)                 # (B,H,T)
+        p_sink = torch.exp(sink.float().view(1, -1, 1) - lse_s)
+        dsink = -(p_sink * delta).sum((0, 2))
+        return dq, dk, dv, dsink.to(sink.dtype).view(sink.shape), None, None, None
+
+
 def cuda_supported(q, k, v, sink) -> bool:
     D = q.shape[-1]
     return (backend.has("attn_fwd") and backend.has("attn_bwd") and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
-            and v.dtype == torch.bfloat16 and D in (64, 128) and v.shape[-1] == D and sink is None and q.shape[1] == k.shape[1]
+            and v.dtype == torch.bfloat16 and D in (64, 128) and v.shape[-1] == D and q.shape[1] == k.shape[1]
             and q.shape[2] % k.shape[2] == 0)
 
 
@@ -131,7 +173,10 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional
         if cu_seqlens is not None:
             assert q.shape[0] == 1, "packed varlen attention expects batch 1"
             cu_seqlens = cu_seqlens.to(torch.int32).contiguous()
-        out, lse = _AttnFn.apply(q, k, v, float(scale), int(window[0]), cu_seqlens)
+        if sink is not None:
+            out, lse = _AttnSinkFn.apply(q, k, v, sink, float(scale), int(window[0]), cu_seqlens)
+        else:
+            out, lse = _AttnFn.apply(q, k, v, float(scale), int(window[0]), cu_seqlens)
         return (out, lse) if return_lse else out
     if q.is_cuda and sink is None and not return_lse:
         return _sdpa_fallback(q, k, v, scale, window, cu_seqlens)

@@ -337,6 +337,7 @@ class ShardedOptimizer:
         groups = {id(mt.group): mt.group for mt in self.mats}
         cdt = torch.bfloat16 if eng.is_cuda else torch.float32
         out: Dict[int, torch.Tensor] = {}
+        staged: Dict[int, tuple] = {}
         for gid, g in groups.items():
             if g.grad is None:
                 continue
@@ -373,45 +374,48 @@ class ShardedOptimizer:
                     du.all_gather_into(u_full, u_shard, group=g.group)
             else:
                 u_full = u_shard
-            # 3. Newton–Schulz on owned matrices, same shapes batched
             if g.world > 1 and eng.symm is not None:
                 o_full = eng.symm.o_buffer(g)
                 o_full.zero_()
             else:
                 o_full = torch.zeros(g.padded, dtype=cdt, device=eng.device) if g.world > 1 else u_full
-            mine = [mt for mt in mask_mats if mt.owner == g.rank]
-            by_shape: Dict[Tuple[int, int], List[_Mat]] = {}
+            staged[gid] = (g, u_full, o_full, [mt for mt in mask_mats if mt.owner == g.rank])
+        # 3. Newton–Schulz on owned matrices: one batch per shape over ALL groups (the same projection of every layer),
+        #    so that the batched GEMMs fill whole waves of CTAs and the launch count does not grow with depth.  Runs of
+        #    matrices stored back to back (the experts of one 3-D parameter, sibling projections) enter as one view.
+        by_shape: Dict[Tuple[int, int], List[Tuple[int, List[_Mat]]]] = {}
+        for gid, (g, u_full, o_full, mine) in staged.items():
+            per: Dict[Tuple[int, int], List[_Mat]] = {}
             for mt in mine:
-                by_shape.setdefault((mt.rows, mt.cols), []).append(mt)
-            for (r, c), lst in by_shape.items():
-                # runs of matrices stored back to back (the experts of one 3-D parameter, sibling projections) are
-                # orthogonalised from one strided view and written back with one copy: no per-matrix launches
+                per.setdefault((mt.rows, mt.cols), []).append(mt)
+            for shape, lst in per.items():
                 lst = sorted(lst, key=lambda mt: mt.offset)
-                runs: List[List[_Mat]] = [[lst[0]]]
+                run = [lst[0]]
                 for mt in lst[1:]:
-                    if mt.offset == runs[-1][-1].offset + r * c:
-                        runs[-1].append(mt)
+                    if mt.offset == run[-1].offset + shape[0] * shape[1]:
+                        run.append(mt)
                     else:
-                        runs.append([mt])
-                if len(runs) == 1:
-                    off0, n = runs[0][0].offset, len(lst)
-                    stack = u_full[off0:off0 + n * r * c].view(n, r, c)
-                else:
-                    stack = torch.cat([u_full[run[0].offset:run[0].offset + len(run) * r * c].view(len(run), r, c)
-                                       for run in runs])
-                O = self._orthogonalise(stack)
-                sq = torch.linalg.vector_norm(O, dim=(-2, -1), dtype=torch.float32).square()
-                i = 0
-                for run in runs:
-                    n = len(run)
-                    o_full[run[0].offset:run[0].offset + n * r * c].view(n, r, c).copy_(O[i:i + n])
-                    i += n
-                key = (gid, r, c)
-                idx = self._norm_idx_cache.get(key)
-                if idx is None:
-                    idx = self._norm_idx_cache[key] = torch.tensor([mt.norm_idx for mt in lst], device=eng.device)
-                u_sq.index_add_(0, idx, sq)
-            # 4. return the updates to the shards
+                        by_shape.setdefault(shape, []).append((gid, run))
+                        run = [mt]
+                by_shape.setdefault(shape, []).append((gid, run))
+        for (r, c), runs in by_shape.items():
+            views = [staged[gid][1][run[0].offset:run[0].offset + len(run) * r * c].view(len(run), r, c) for gid, run in runs]
+            stack = views[0] if len(views) == 1 else torch.cat(views)
+            O = self._orthogonalise(stack)
+            sq = torch.linalg.vector_norm(O, dim=(-2, -1), dtype=torch.float32).square()
+            i = 0
+            for gid, run in runs:
+                n = len(run)
+                staged[gid][2][run[0].offset:run[0].offset + n * r * c].view(n, r, c).copy_(O[i:i + n])
+                i += n
+            idx = self._norm_idx_cache.get((r, c))
+            if idx is None:
+                idx = self._norm_idx_cache[(r, c)] = torch.tensor([mt.norm_idx for _, run in runs for mt in run],
+                                                                  device=eng.device)
+            u_sq.index_add_(0, idx, sq)
+            del O, stack
+        # 4. return the updates to the shards
+        for gid, (g, u_full, o_full, _mine) in staged.items():
             if g.world > 1:
                 if eng.symm is not None:
                     o_shard = eng.symm.scatter_flat(g, o_full)

@@ -82,3 +82,28 @@ def test_attention_backward_is_deterministic():
         grads.append(torch.autograd.grad(out, (q, k, v), g))
     for a, b in zip(*grads):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("B,T,H,G,D,win,cu", [(2, 384, 4, 2, 128, -1, None), (1, 640, 4, 4, 64, 127, None),
+                                               (1, 700, 4, 2, 128, -1, [0, 130, 400, 700])])
+def test_sink_attention_matches_dense_softmax_with_sink_column(B, T, H, G, D, win, cu):
+    """Learnable per-head sink logit on the kernel path: forward, dq/dk/dv and the sink gradient."""
+    from archscale_b200 import ops
+    torch.manual_seed(5)
+    q = torch.randn(B, T, H, D, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(B, T, G, D, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(B, T, G, D, device="cuda").bfloat16().requires_grad_()
+    sink = (torch.randn(H, device="cuda") * 2).requires_grad_()
+    g = torch.randn(B, T, H, D, device="cuda").bfloat16()
+    cu_t = torch.tensor(cu, device="cuda", dtype=torch.int32) if cu else None
+    n0 = backend.launches()
+    out = ops.attention(q, k, v, window=(win, 0 if win >= 0 else -1), cu_seqlens=cu_t, sink=sink)
+    assert backend.launches() > n0, "sink attention did not take the kernel path"
+    grads = torch.autograd.grad(out, (q, k, v, sink), g)
+    assert backend.require_extension().device_status() == 0
+    leaves = [t.detach().float().requires_grad_() for t in (q, k, v, sink)]
+    ref = attention_ref(leaves[0], leaves[1], leaves[2], None, (win, 0 if win >= 0 else -1), cu_t, leaves[3])
+    g_ref = torch.autograd.grad(ref, leaves, g.float())
+    assert _rel(out, ref) < 2e-2, _rel(out, ref)
+    for name, x, y in zip(("dq", "dk", "dv", "dsink"), grads, g_ref):
+        assert _rel(x, y) < 3e-2, (name, _rel(x, y))
