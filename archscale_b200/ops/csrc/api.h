@@ -162,6 +162,11 @@ int b200_diff_combine_fwd(const void* a1, const void* a2, const float* lam, cons
 int b200_diff_combine_bwd(const void* dy, const void* a1, const void* a2, const float* lam, const float* w, float c, const float* rstd,
                           void* da1, void* da2, float* dlam, float* dw, long long rows, int width, cudaStream_t st);
 
+// 2-CTA (cta_group::2) variant of b200_gemm_bf16: one 256×256 tile per pair of SMs (gemm2_bf16.cu)
+int b200_gemm2_bf16(int mode, const void* A, const void* B, void* out, const void* cin, int M, int N, int K,
+                    int lda, int ldb, int ldc, float alpha, float beta, int out_f32, int accumulate,
+                    int num_sms, int* status, cudaStream_t stream);
+
 // One pass of the chunked gated-delta-rule recurrence (gdn_chunk.cu)
 int b200_gdn_state(const void* a_op, const void* c_add, const void* bm_op, const void* e_op, const void* f_op,
                    const float* decay, void* v_out, void* x_all, float* x_final, int BH, int Tp, int DK, int DV,

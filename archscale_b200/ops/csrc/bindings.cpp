@@ -39,6 +39,14 @@ int* status_ptr(const at::Device& dev) {
 }
 
 // ---- GEMM ---------------------------------------------------------------------------------
+// ARCHSCALE_B200_GEMM=1cta forces the one-CTA 128×256 kernel; otherwise plain GEMMs pair two SMs on a 256×256 tile.
+static int g_gemm_pair = -1;
+static bool gemm_use_pair() {
+  if (g_gemm_pair < 0) { const char* v = std::getenv("ARCHSCALE_B200_GEMM"); g_gemm_pair = (v != nullptr && std::string(v) == "1cta") ? 0 : 1; }
+  return g_gemm_pair == 1;
+}
+// tests switch between the two kernels at run time; returns the previous setting
+static bool set_gemm_pair(bool on) { const bool was = gemm_use_pair(); g_gemm_pair = on ? 1 : 0; return was; }
 // mode 0: a[M,K] b[N,K] ; 1: a[M,K] b[K,N] ; 2: a[K,M] b[K,N].  `acc`: fp32 [M,N] accumulated in place.
 at::Tensor gemm_bf16(const at::Tensor& a, const at::Tensor& b, int64_t mode, at::ScalarType out_dtype,
                      const c10::optional<at::Tensor>& acc) {
@@ -63,6 +71,12 @@ at::Tensor gemm_bf16(const at::Tensor& a, const at::Tensor& b, int64_t mode, at:
   // different streams (they are all issued on the autograd stream).  ARCHSCALE_B200_NO_SPLITK=1 turns it off.
   static const bool no_splitk = std::getenv("ARCHSCALE_B200_NO_SPLITK") != nullptr;
   if (accumulate && !no_splitk) ensure_splitk_workspace(a.device());
+  if (gemm_use_pair()) {
+    check(b200_gemm2_bf16((int)mode, a.data_ptr(), b.data_ptr(), out.data_ptr(), nullptr, (int)M, (int)N, (int)K,
+                          (int)a.stride(0), (int)b.stride(0), (int)out.stride(0), 1.f, 0.f, out_f32, accumulate, num_sms(),
+                          status_ptr(a.device()), cur_stream()), "gemm2_bf16");
+    return out;
+  }
   check(b200_gemm_bf16((int)mode, a.data_ptr(), b.data_ptr(), out.data_ptr(), nullptr, (int)M, (int)N, (int)K,
                        (int)a.stride(0), (int)b.stride(0), (int)out.stride(0), 1.f, 0.f, out_f32, accumulate, num_sms(),
                        status_ptr(a.device()), cur_stream()), "gemm_bf16");
@@ -80,8 +94,8 @@ at::Tensor gemm_bf16_epi(const at::Tensor& a, const at::Tensor& b, int64_t mode,
   else { K = a.size(0); M = a.size(1); N = b.size(1); }
   at::Tensor out = at::empty({M, N}, a.options());
   if (c.has_value()) TORCH_CHECK(c->is_contiguous() && c->scalar_type() == at::kBFloat16 && c->size(0) == M && c->size(1) == N);
-  check(b200_gemm_bf16((int)mode, a.data_ptr(), b.data_ptr(), out.data_ptr(), ptr_opt(c), (int)M, (int)N, (int)K,
-                       (int)a.stride(0), (int)b.stride(0), (int)N, (float)alpha, (float)beta, 0, 0, num_sms(),
+  check((gemm_use_pair() ? b200_gemm2_bf16 : b200_gemm_bf16)((int)mode, a.data_ptr(), b.data_ptr(), out.data_ptr(), ptr_opt(c), (int)M, (int)N,
+                       (int)K, (int)a.stride(0), (int)b.stride(0), (int)N, (float)alpha, (float)beta, 0, 0, num_sms(),
                        status_ptr(a.device()), cur_stream()), "gemm_bf16_epi");
   return out;
 }
@@ -215,6 +229,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_bf16", &gemm_bf16, "bf16 tcgen05 GEMM", py::arg("a"), py::arg("b"), py::arg("mode"), py::arg("out_dtype"),
         py::arg("acc") = py::none());
   m.def("gemm_bf16_epi", &gemm_bf16_epi);
+  m.def("set_gemm_pair", &set_gemm_pair);
   m.def("device_status", &device_status);
   m.def("reset_device_status", &reset_device_status);
   m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("w"), py::arg("eps"), py::arg("out_dtype") = py::none());

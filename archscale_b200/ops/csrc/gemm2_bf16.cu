@@ -1,0 +1,304 @@
+// bf16 GEMM with one 256×256 output tile per PAIR of SMs (tcgen05.mma.cta_group::2).
+//
+// A cluster of two CTAs (two SMs of one TPC) works on one tile: each CTA stages 128 rows of A and 128 of the 256 rows
+// of B in its own shared memory (6-stage ring, 32 KB per stage and CTA) and one thread of the even ("leader") CTA
+// issues M256 × N256 × K16 MMAs that read both CTAs' shared memory and write 128 accumulator rows × 256 fp32 columns
+// into EACH CTA's tensor memory.  Against the one-CTA 128×256 tile this moves a third less operand data from L2
+// per FLOP and halves the B traffic per SM, which is what bounds that kernel.
+//
+// Per CTA, 192 threads: warp 0 TMA producer (both CTAs; every load signals the leader's `full` barrier), warp 1
+// allocates tensor memory (both CTAs) and issues the MMAs (leader only), warps 2..5 epilogue (each CTA stores its own
+// 128 rows; two 256-column accumulators let the epilogue of tile i overlap the main loop of tile i+1).  tcgen05.commit
+// arrives on the `empty` / `tmem_full` barriers of both CTAs; the epilogue warps of both CTAs arrive on the leader's
+// `tmem_empty`.  No TMA load uses cluster multicast.  Every wait is bounded; the two CTAs leave together through a
+// cluster barrier so that neither signals into shared memory of a CTA that has exited.
+//
+// Layouts as in gemm_bf16.cu: A K-major [M,K] or MN-major [K,M]; B K-major [N,K] or MN-major [K,N].
+#include "sm100.cuh"
+#include "api.h"
+
+namespace b200 {
+
+int make_tmap_2d_bf16(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_elems,
+                      uint32_t box_inner, uint32_t box_outer);
+
+constexpr int T2_BM = 256, T2_BN = 256, T2_BK = 64, T2_STAGES = 6;
+constexpr int T2_HALF = 128;                          // rows of A / rows of B held by one CTA
+constexpr int T2_OP_BYTES = T2_HALF * T2_BK * 2;      // 16 KB
+constexpr int T2_STAGE_BYTES = 2 * T2_OP_BYTES;       // A then B
+constexpr int T2_SMEM_BYTES = T2_STAGES * T2_STAGE_BYTES + 1024 + 256;
+constexpr int T2_GROUP_M = 8;
+constexpr int T2_THREADS = 192;
+constexpr uint32_t kLeaderMask = 0xFEFFFFFFu;         // clears the CTA-rank bit of a shared::cluster address → even CTA of the pair
+
+struct Gemm2Params {
+  void* out;
+  const void* cin;
+  int M, N, K;
+  int ldc;
+  float alpha, beta;
+  int accumulate;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc_2sm(uint32_t* smem_dst, uint32_t ncols) {   // one warp in each CTA of the pair
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_2sm() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_2sm(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// TMA load into this CTA's shared memory; the transaction bytes are counted on the LEADER CTA's barrier at the same offset.
+__device__ __forceinline__ void tma_load_2d_2sm(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar) & kLeaderMask), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_2sm(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives (once all MMAs issued so far by this thread have completed) on the barrier at this offset in every CTA of `mask`
+__device__ __forceinline__ void umma_commit_2sm(uint64_t* bar, uint16_t mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & kLeaderMask) : "memory");
+}
+
+template <int A_MN, int B_MN, int OUT_F32>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1)
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Gemm2Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + T2_STAGES * T2_STAGE_BYTES);
+  uint64_t* full_bar = bars;                          // [STAGES]  used in the leader CTA
+  uint64_t* empty_bar = bars + T2_STAGES;             // [STAGES]  each CTA's producer waits on its own
+  uint64_t* tmem_full = bars + 2 * T2_STAGES;         // [2]       each CTA's epilogue waits on its own
+  uint64_t* tmem_empty = bars + 2 * T2_STAGES + 2;    // [2]       used in the leader CTA, 8 arrivals (4 warps × 2 CTAs)
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 2 * T2_STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = static_cast<int>(cluster_ctarank());
+  const int pair = static_cast<int>(blockIdx.x) >> 1, n_pair = static_cast<int>(gridDim.x) >> 1;
+  const int num_m = (p.M + T2_BM - 1) / T2_BM, num_n = (p.N + T2_BN - 1) / T2_BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + T2_BK - 1) / T2_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < T2_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 8); }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) { tmem_alloc_2sm(tmem_ptr, 512); tmem_relinquish_2sm(); }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();          // the peer's barriers are initialised before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  auto tile_coords = [&](int t, int& m0, int& n0) {
+    const int per_group = T2_GROUP_M * num_n;
+    const int g = t / per_group;
+    const int first_m = g * T2_GROUP_M;
+    const int gsz = min(num_m - first_m, T2_GROUP_M);
+    const int r = t - g * per_group;
+    m0 = (first_m + (r % gsz)) * T2_BM;
+    n0 = (r / gsz) * T2_BN;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      for (int t = pair; t < num_tiles; t += n_pair) {
+        int m0, n0; tile_coords(t, m0, n0);
+        const int ma = m0 + rank * T2_HALF, nb = n0 + rank * T2_HALF;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) goto done;
+          uint8_t* sa = smem + stage * T2_STAGE_BYTES;
+          uint8_t* sb = sa + T2_OP_BYTES;
+          if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * T2_STAGE_BYTES);   // both CTAs' loads
+          if (A_MN) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) tma_load_2d_2sm(sa + c * (64 * T2_BK * 2), &tmap_a, &full_bar[stage], ma + c * 64, kb * T2_BK);
+          } else {
+            tma_load_2d_2sm(sa, &tmap_a, &full_bar[stage], kb * T2_BK, ma);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) tma_load_2d_2sm(sb + c * (64 * T2_BK * 2), &tmap_b, &full_bar[stage], nb + c * 64, kb * T2_BK);
+          } else {
+            tma_load_2d_2sm(sb, &tmap_b, &full_bar[stage], kb * T2_BK, nb);
+          }
+          if (++stage == T2_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(T2_BM, T2_BN, A_MN, B_MN);
+      constexpr uint32_t a_kstep = A_MN ? (16 * 128) >> 4 : 32 >> 4;
+      constexpr uint32_t b_kstep = B_MN ? (16 * 128) >> 4 : 32 >> 4;
+      int stage = 0; uint32_t phase = 0;
+      int it = 0;
+      for (int t = pair; t < num_tiles; t += n_pair, ++it) {
+        const int acc = it & 1; const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) goto done;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * T2_BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_FULL)) goto done;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * T2_STAGE_BYTES);
+          const uint32_t sb = sa + T2_OP_BYTES;
+          const uint64_t da = A_MN ? make_smem_desc(sa, 64 * T2_BK * 2, 1024) : make_smem_desc(sa, 16, 1024);
+          const uint64_t db = B_MN ? make_smem_desc(sb, 64 * T2_BK * 2, 1024) : make_smem_desc(sb, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < T2_BK / 16; ++k)
+            umma_bf16_2sm(d_tmem, da + static_cast<uint64_t>(k * a_kstep), db + static_cast<uint64_t>(k * b_kstep), idesc,
+                          (kb != 0 || k != 0) ? 1u : 0u);
+          umma_commit_2sm(&empty_bar[stage], 3);          // frees the stage in both CTAs
+          if (++stage == T2_STAGES) { stage = 0; phase ^= 1; }
+        }
+        umma_commit_2sm(&tmem_full[acc], 3);              // both CTAs' epilogues may read their half
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    int it = 0;
+    for (int t = pair; t < num_tiles; t += n_pair, ++it) {
+      int m0, n0; tile_coords(t, m0, n0);
+      const int acc = it & 1; const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
+      tc_fence_after();
+      const int row = m0 + rank * T2_HALF + q * 32 + lane;
+      const uint32_t taddr = tmem_base + acc * T2_BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < T2_BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int col = n0 + c * 32;
+        if (row < p.M && col < p.N) {
+          if (OUT_F32) {
+            float* o = reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ldc + col;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (col + j < p.N) {
+                float4 v = make_float4(__uint_as_float(r[j]) * p.alpha, __uint_as_float(r[j + 1]) * p.alpha,
+                                       __uint_as_float(r[j + 2]) * p.alpha, __uint_as_float(r[j + 3]) * p.alpha);
+                if (p.accumulate) {
+                  const float4 old = *reinterpret_cast<const float4*>(o + j);
+                  v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                }
+                *reinterpret_cast<float4*>(o + j) = v;
+              }
+            }
+          } else {
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ldc + col;
+            const __nv_bfloat16* ci = p.cin ? reinterpret_cast<const __nv_bfloat16*>(p.cin) + static_cast<size_t>(row) * p.ldc + col : nullptr;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col + j < p.N) {
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[j + e]) * p.alpha;
+                if (ci) {
+                  const uint4 cv = *reinterpret_cast<const uint4*>(ci + j);
+                  const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 c2 = unpack_bf16x2(cw[e]);
+                    f[2 * e] += p.beta * c2.x; f[2 * e + 1] += p.beta * c2.y;
+                  }
+                }
+                uint4 ov;
+                ov.x = pack_bf16x2(f[0], f[1]); ov.y = pack_bf16x2(f[2], f[3]);
+                ov.z = pack_bf16x2(f[4], f[5]); ov.w = pack_bf16x2(f[6], f[7]);
+                *reinterpret_cast<uint4*>(o + j) = ov;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_leader(&tmem_empty[acc]);
+    }
+  }
+
+done:
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc_2sm(tmem_base, 512);
+  }
+}
+
+template <int A_MN, int B_MN, int OUT_F32>
+static int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm2Params& p, int sms, cudaStream_t st) {
+  auto kern = gemm2_bf16_kernel<A_MN, B_MN, OUT_F32>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES) != cudaSuccess) return -2;
+    configured = true;
+  }
+  const int tiles = ((p.M + T2_BM - 1) / T2_BM) * ((p.N + T2_BN - 1) / T2_BN);
+  const int pairs = sms / 2;
+  const int grid = 2 * (tiles < pairs ? tiles : pairs);
+  kern<<<grid, T2_THREADS, T2_SMEM_BYTES, st>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+}  // namespace b200
+
+// Same contract as b200_gemm_bf16 (modes 0 NT, 1 NN, 2 TN; bf16 or fp32 output, optional α·AB + β·C or accumulate).
+extern "C" int b200_gemm2_bf16(int mode, const void* A, const void* B, void* out, const void* cin, int M, int N, int K,
+                               int lda, int ldb, int ldc, float alpha, float beta, int out_f32, int accumulate,
+                               int num_sms, int* status, cudaStream_t stream) {
+  using namespace b200;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return -5;
+    ctx_bound = true;
+  }
+  CUtensorMap ta, tb;
+  int rc;
+  if (mode == 2) rc = make_tmap_2d_bf16(&ta, A, M, K, lda, 64, T2_BK);        // stored [K, M]
+  else           rc = make_tmap_2d_bf16(&ta, A, K, M, lda, T2_BK, T2_HALF);   // stored [M, K]
+  if (rc) return rc;
+  if (mode == 0) rc = make_tmap_2d_bf16(&tb, B, K, N, ldb, T2_BK, T2_HALF);   // stored [N, K]
+  else           rc = make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, T2_BK);        // stored [K, N]
+  if (rc) return rc;
+  Gemm2Params p{out, cin, M, N, K, ldc, alpha, beta, accumulate, status};
+  if (mode == 0) return out_f32 ? launch2<0, 0, 1>(ta, tb, p, num_sms, stream) : launch2<0, 0, 0>(ta, tb, p, num_sms, stream);
+  if (mode == 1) return out_f32 ? launch2<0, 1, 1>(ta, tb, p, num_sms, stream) : launch2<0, 1, 0>(ta, tb, p, num_sms, stream);
+  if (mode == 2) return out_f32 ? launch2<1, 1, 1>(ta, tb, p, num_sms, stream) : launch2<1, 1, 0>(ta, tb, p, num_sms, stream);
+  return -4;
+}

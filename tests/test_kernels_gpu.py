@@ -270,9 +270,39 @@ def test_wgrad_split_k_accumulates_exactly_like_unsplit(M, N, K):
     a = (torch.randn(K, M, device="cuda") * 0.1).bfloat16()
     b = (torch.randn(K, N, device="cuda") * 0.1).bfloat16()
     acc = torch.ones(M, N, device="cuda")
-    ext.gemm_bf16(a, b, 2, torch.float32, acc)
-    ext.gemm_bf16(a, b, 2, torch.float32, acc)
-    torch.cuda.synchronize()
+    was = ext.set_gemm_pair(False)          # split-K lives in the one-CTA kernel
+    try:
+        ext.gemm_bf16(a, b, 2, torch.float32, acc)
+        ext.gemm_bf16(a, b, 2, torch.float32, acc)
+        torch.cuda.synchronize()
+    finally:
+        ext.set_gemm_pair(was)
     ref = 1.0 + 2.0 * (a.float().t() @ b.float())
     assert ext.device_status() == 0
     assert (acc - ref).abs().max().item() <= 2e-3 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("pair", [False, True])
+@pytest.mark.parametrize("M,N,K,mode", [(384, 520, 320, 2), (1000, 776, 264, 0), (640, 1288, 512, 1), (4096, 4096, 1024, 0)])
+def test_gemm_one_cta_and_two_cta_kernels_agree_with_fp32(pair, M, N, K, mode):
+    """Both GEMM kernels (128×256 tile per SM, 256×256 tile per SM pair) against an fp32 matmul, all three layouts,
+    ragged edges, bf16 output and accumulating fp32 output."""
+    from archscale_b200.ops import backend
+    ext = backend.require_extension()
+    torch.manual_seed(3)
+    A = (torch.randn(M, K, device="cuda") * 0.3).bfloat16()
+    B = (torch.randn(N, K, device="cuda") * 0.3).bfloat16()
+    a = A if mode != 2 else A.t().contiguous()
+    b = B if mode == 0 else B.t().contiguous()
+    ref = A.float() @ B.float().t()
+    was = ext.set_gemm_pair(pair)
+    try:
+        out = ext.gemm_bf16(a, b, mode, torch.bfloat16, None)
+        acc = torch.full((M, N), 0.5, device="cuda")
+        ext.gemm_bf16(a, b, mode, torch.float32, acc)
+        torch.cuda.synchronize()
+    finally:
+        ext.set_gemm_pair(was)
+    assert ext.device_status() == 0
+    assert _rel(out, ref) < 1e-2
+    assert _rel(acc, ref + 0.5) < 1e-3
