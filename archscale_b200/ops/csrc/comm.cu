@@ -240,7 +240,7 @@ extern "C" int b200_reduce_scatter_pull_bf16(const void* const* bases, size_t fu
 //   send rows   [rows_cap, C] bf16, expert-sorted (segment of expert e starts at offsets[e], counts[e] rows)
 //   counts[E], offsets[E+1]
 // The owner of local expert e_l (global e = rank·E_l + e_l) lays its receive buffer out expert-major,
-// sources in rank order inside an expert, expert segments starting at multiples of 128 rows, and records
+// sources in rank order inside an expert, expert segments starting at multiples of 256 rows, and records
 // in `table[src][e_l]` where each source's rows start (sources read it to pull their results back).
 namespace b200 {
 
@@ -264,7 +264,7 @@ __global__ void ep_plan_kernel(EpArgs a, int* __restrict__ recv_offsets, int* st
   __syncthreads();
   if (threadIdx.x == 0) {
     int acc = 0;
-    for (int e = 0; e < a.e_local; ++e) { recv_offsets[e] = acc; acc += (s_total[e] + 127) / 128 * 128; }
+    for (int e = 0; e < a.e_local; ++e) { recv_offsets[e] = acc; acc += (s_total[e] + 255) / 256 * 256; }
     recv_offsets[a.e_local] = acc;
     if (acc > a.recv_cap && status) atomicCAS(status, 0, STATUS_BAD_ARG);
   }
@@ -351,7 +351,7 @@ static b200::EpArgs make_ep(const void* const* bases, size_t off_counts, size_t 
   return a;
 }
 
-// Step 1: layout of the rows this rank will receive (recv_offsets[e_local+1], 128-aligned) and the table
+// Step 1: layout of the rows this rank will receive (recv_offsets[e_local+1], 256-aligned) and the table
 // its peers read to find their results.  The caller reads recv_offsets[e_local] to size its buffers.
 extern "C" int b200_ep_plan(const void* const* bases, size_t off_counts, size_t off_table, int rank, int world, int e_local,
                             int recv_cap, int* recv_offsets, int* status, cudaStream_t st) {

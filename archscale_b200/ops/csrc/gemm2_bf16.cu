@@ -21,6 +21,8 @@ namespace b200 {
 
 int make_tmap_2d_bf16(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_elems,
                       uint32_t box_inner, uint32_t box_outer);
+int make_tmap_3d_bf16(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t rows, uint64_t batch,
+                      uint64_t row_stride_elems, uint64_t batch_stride_elems, uint32_t box_inner, uint32_t box_rows);
 
 constexpr int T2_BM = 256, T2_BN = 256, T2_BK = 64, T2_STAGES = 6;
 constexpr int T2_HALF = 128;                          // rows of A / rows of B held by one CTA
@@ -30,6 +32,16 @@ constexpr int T2_SMEM_BYTES = T2_STAGES * T2_STAGE_BYTES + 1024 + 256;
 constexpr int T2_GROUP_M = 8;
 constexpr int T2_THREADS = 192;
 constexpr uint32_t kLeaderMask = 0xFEFFFFFFu;         // clears the CTA-rank bit of a shared::cluster address → even CTA of the pair
+
+// Grouped / batched problems (same conventions as the one-CTA kernel):
+//   GROUPED 1  rows of A are grouped by expert (offsets[E+1], multiples of 256); expert e multiplies its rows with B_e
+//   GROUPED 2  per-expert weight gradient: out[e] = A[seg_e]ᵀ · B[seg_e], the K range of expert e is its row segment
+//   GROUPED 3  `E` independent problems of identical shape (3-D tensor maps, batch index = third coordinate)
+struct Group2Params {
+  const int* offsets;
+  int E;
+  int b_rows;           // rows of one expert's matrix inside B (GROUPED 1)
+};
 
 struct Gemm2Params {
   void* out;
@@ -65,6 +77,16 @@ __device__ __forceinline__ void tma_load_2d_2sm(void* smem_dst, const CUtensorMa
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar) & kLeaderMask), "r"(x), "r"(y)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_3d_2sm(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar) & kLeaderMask), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+// plain arrive on the barrier at this offset in the other CTA of the pair (issued by the leader, rank 0)
+__device__ __forceinline__ void mbar_arrive_peer(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) | ~kLeaderMask) : "memory");
+}
 __device__ __forceinline__ void umma_bf16_2sm(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n"
@@ -83,9 +105,17 @@ __device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & kLeaderMask) : "memory");
 }
 
-template <int A_MN, int B_MN, int OUT_F32>
+struct Tile2 {
+  int m0, n0;      // first row / column of the 256×256 tile (inside the expert's / batch entry's matrix)
+  int b_row;       // GROUPED 1: first row of the expert's matrix in B; GROUPED 3: batch index
+  int kb0, kb1;    // K-block range
+  size_t out_off;  // element offset of the expert's / batch entry's output
+};
+
+template <int A_MN, int B_MN, int OUT_F32, int GROUPED = 0>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1)
-gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Gemm2Params p) {
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Gemm2Params p,
+                  const Group2Params gp) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + T2_STAGES * T2_STAGE_BYTES);
@@ -99,8 +129,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = static_cast<int>(cluster_ctarank());
   const int pair = static_cast<int>(blockIdx.x) >> 1, n_pair = static_cast<int>(gridDim.x) >> 1;
-  const int num_m = (p.M + T2_BM - 1) / T2_BM, num_n = (p.N + T2_BN - 1) / T2_BN;
-  const int num_tiles = num_m * num_n;
+  __shared__ int s_off[258];
+  if (GROUPED == 1 || GROUPED == 2) {
+    for (int i = threadIdx.x; i <= gp.E; i += blockDim.x) s_off[i] = gp.offsets[i];
+    __syncthreads();
+  }
+  const int num_n = (p.N + T2_BN - 1) / T2_BN;
+  const int num_m = GROUPED == 1 ? s_off[gp.E] / T2_BM : (p.M + T2_BM - 1) / T2_BM;
+  const int num_tiles = ((GROUPED == 2 || GROUPED == 3) ? gp.E : 1) * num_m * num_n;
   const int num_kb = (p.K + T2_BK - 1) / T2_BK;
 
   if (threadIdx.x == 0) {
@@ -118,27 +154,59 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr;
 
-  auto tile_coords = [&](int t, int& m0, int& n0) {
-    const int per_group = T2_GROUP_M * num_n;
-    const int g = t / per_group;
-    const int first_m = g * T2_GROUP_M;
-    const int gsz = min(num_m - first_m, T2_GROUP_M);
-    const int r = t - g * per_group;
-    m0 = (first_m + (r % gsz)) * T2_BM;
-    n0 = (r / gsz) * T2_BN;
+  auto get_tile = [&](int t, Tile2& tl) {
+    tl.kb0 = 0; tl.kb1 = num_kb; tl.out_off = 0; tl.b_row = 0;
+    if (GROUPED == 2 || GROUPED == 3) {
+      const int per = num_m * num_n;
+      const int e = t / per, r = t - e * per;
+      tl.m0 = (r % num_m) * T2_BM; tl.n0 = (r / num_m) * T2_BN;
+      tl.out_off = static_cast<size_t>(e) * p.M * p.ldc;
+      if (GROUPED == 2) { tl.kb0 = s_off[e] / T2_BK; tl.kb1 = s_off[e + 1] / T2_BK; }
+      else tl.b_row = e;
+    } else {
+      const int per_group = T2_GROUP_M * num_n;
+      const int g = t / per_group;
+      const int first_m = g * T2_GROUP_M;
+      const int gsz = min(num_m - first_m, T2_GROUP_M);
+      const int r = t - g * per_group;
+      tl.m0 = (first_m + (r % gsz)) * T2_BM;
+      tl.n0 = (r / gsz) * T2_BN;
+      if (GROUPED == 1) {
+        int lo = 0, hi = gp.E;          // expert whose segment holds row m0
+        while (lo + 1 < hi) { const int mid = (lo + hi) >> 1; if (s_off[mid] <= tl.m0) lo = mid; else hi = mid; }
+        tl.b_row = lo * gp.b_rows;
+      }
+    }
   };
 
   if (warp == 0) {
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       for (int t = pair; t < num_tiles; t += n_pair) {
-        int m0, n0; tile_coords(t, m0, n0);
-        const int ma = m0 + rank * T2_HALF, nb = n0 + rank * T2_HALF;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        Tile2 tl; get_tile(t, tl);
+        const int ma = tl.m0 + rank * T2_HALF, nb = tl.n0 + rank * T2_HALF;
+        for (int kb = tl.kb0; kb < tl.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) goto done;
           uint8_t* sa = smem + stage * T2_STAGE_BYTES;
           uint8_t* sb = sa + T2_OP_BYTES;
           if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * T2_STAGE_BYTES);   // both CTAs' loads
+          if (GROUPED == 3) {
+            if (A_MN) {
+#pragma unroll
+              for (int c = 0; c < 2; ++c) tma_load_3d_2sm(sa + c * (64 * T2_BK * 2), &tmap_a, &full_bar[stage], ma + c * 64, kb * T2_BK, tl.b_row);
+            } else {
+              tma_load_3d_2sm(sa, &tmap_a, &full_bar[stage], kb * T2_BK, ma, tl.b_row);
+            }
+            if (B_MN) {
+#pragma unroll
+              for (int c = 0; c < 2; ++c) tma_load_3d_2sm(sb + c * (64 * T2_BK * 2), &tmap_b, &full_bar[stage], nb + c * 64, kb * T2_BK, tl.b_row);
+            } else {
+              tma_load_3d_2sm(sb, &tmap_b, &full_bar[stage], kb * T2_BK, nb, tl.b_row);
+            }
+            if (++stage == T2_STAGES) { stage = 0; phase ^= 1; }
+            continue;
+          }
+          const int brow = GROUPED == 1 ? tl.b_row : 0;
           if (A_MN) {
 #pragma unroll
             for (int c = 0; c < 2; ++c) tma_load_2d_2sm(sa + c * (64 * T2_BK * 2), &tmap_a, &full_bar[stage], ma + c * 64, kb * T2_BK);
@@ -147,9 +215,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           }
           if (B_MN) {
 #pragma unroll
-            for (int c = 0; c < 2; ++c) tma_load_2d_2sm(sb + c * (64 * T2_BK * 2), &tmap_b, &full_bar[stage], nb + c * 64, kb * T2_BK);
+            for (int c = 0; c < 2; ++c) tma_load_2d_2sm(sb + c * (64 * T2_BK * 2), &tmap_b, &full_bar[stage], nb + c * 64, brow + kb * T2_BK);
           } else {
-            tma_load_2d_2sm(sb, &tmap_b, &full_bar[stage], kb * T2_BK, nb);
+            tma_load_2d_2sm(sb, &tmap_b, &full_bar[stage], kb * T2_BK, brow + nb);
           }
           if (++stage == T2_STAGES) { stage = 0; phase ^= 1; }
         }
@@ -167,7 +235,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) goto done;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * T2_BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        Tile2 tl; get_tile(t, tl);
+        for (int kb = tl.kb0; kb < tl.kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_FULL)) goto done;
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * T2_STAGE_BYTES);
@@ -177,18 +246,22 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 #pragma unroll
           for (int k = 0; k < T2_BK / 16; ++k)
             umma_bf16_2sm(d_tmem, da + static_cast<uint64_t>(k * a_kstep), db + static_cast<uint64_t>(k * b_kstep), idesc,
-                          (kb != 0 || k != 0) ? 1u : 0u);
+                          (kb != tl.kb0 || k != 0) ? 1u : 0u);
           umma_commit_2sm(&empty_bar[stage], 3);          // frees the stage in both CTAs
           if (++stage == T2_STAGES) { stage = 0; phase ^= 1; }
         }
-        umma_commit_2sm(&tmem_full[acc], 3);              // both CTAs' epilogues may read their half
+        if (tl.kb0 == tl.kb1) { mbar_arrive(&tmem_full[acc]); mbar_arrive_peer(&tmem_full[acc]); }   // empty expert: nothing was issued
+        else umma_commit_2sm(&tmem_full[acc], 3);         // both CTAs' epilogues may read their half
       }
     }
   } else {
     const int q = warp & 3;
     int it = 0;
     for (int t = pair; t < num_tiles; t += n_pair, ++it) {
-      int m0, n0; tile_coords(t, m0, n0);
+      Tile2 tl; get_tile(t, tl);
+      const int m0 = tl.m0, n0 = tl.n0;
+      const bool empty_tile = tl.kb0 == tl.kb1;
+      const int row_limit = GROUPED == 1 ? s_off[gp.E] : p.M;
       const int acc = it & 1; const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
       tc_fence_after();
@@ -199,10 +272,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
+        if (empty_tile) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r[e] = 0u;
+        }
         const int col = n0 + c * 32;
-        if (row < p.M && col < p.N) {
+        if (row < row_limit && col < p.N) {
           if (OUT_F32) {
-            float* o = reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ldc + col;
+            float* o = reinterpret_cast<float*>(p.out) + tl.out_off + static_cast<size_t>(row) * p.ldc + col;
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
               if (col + j < p.N) {
@@ -216,8 +293,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
               }
             }
           } else {
-            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ldc + col;
-            const __nv_bfloat16* ci = p.cin ? reinterpret_cast<const __nv_bfloat16*>(p.cin) + static_cast<size_t>(row) * p.ldc + col : nullptr;
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + tl.out_off + static_cast<size_t>(row) * p.ldc + col;
+            const __nv_bfloat16* ci = p.cin ? reinterpret_cast<const __nv_bfloat16*>(p.cin) + tl.out_off + static_cast<size_t>(row) * p.ldc + col : nullptr;
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               if (col + j < p.N) {
@@ -270,7 +347,22 @@ static int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm2Para
   const int tiles = ((p.M + T2_BM - 1) / T2_BM) * ((p.N + T2_BN - 1) / T2_BN);
   const int pairs = sms / 2;
   const int grid = 2 * (tiles < pairs ? tiles : pairs);
-  kern<<<grid, T2_THREADS, T2_SMEM_BYTES, st>>>(ta, tb, p);
+  kern<<<grid, T2_THREADS, T2_SMEM_BYTES, st>>>(ta, tb, p, Group2Params{});
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+template <int A_MN, int B_MN, int OUT_F32, int GROUPED>
+static int launch2_grouped(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm2Params& p, const Group2Params& gp, int tiles,
+                           int sms, cudaStream_t st) {
+  auto kern = gemm2_bf16_kernel<A_MN, B_MN, OUT_F32, GROUPED>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES) != cudaSuccess) return -2;
+    configured = true;
+  }
+  const int pairs = sms / 2;
+  const int grid = 2 * (tiles < pairs ? (tiles > 0 ? tiles : 1) : pairs);
+  kern<<<grid, T2_THREADS, T2_SMEM_BYTES, st>>>(ta, tb, p, gp);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -301,4 +393,70 @@ extern "C" int b200_gemm2_bf16(int mode, const void* A, const void* B, void* out
   if (mode == 1) return out_f32 ? launch2<0, 1, 1>(ta, tb, p, num_sms, stream) : launch2<0, 1, 0>(ta, tb, p, num_sms, stream);
   if (mode == 2) return out_f32 ? launch2<1, 1, 1>(ta, tb, p, num_sms, stream) : launch2<1, 1, 0>(ta, tb, p, num_sms, stream);
   return -4;
+}
+
+// Grouped GEMM over expert segments, same contract as b200_grouped_gemm_bf16 except that `offsets` (and `capacity`) must
+// be multiples of 256 rows and N a multiple of 256 for kinds 0 / 1.
+extern "C" int b200_grouped_gemm2_bf16(int kind, const void* A, const void* B, void* out, const int* offsets, int E,
+                                       int capacity, int M, int N, int K, int out_f32, int accumulate, int num_sms,
+                                       int* status, cudaStream_t stream) {
+  using namespace b200;
+  if (E <= 0 || E > 256 || capacity <= 0 || capacity % T2_BM) return -1;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return -5;
+    ctx_bound = true;
+  }
+  CUtensorMap ta, tb;
+  int rc;
+  Group2Params gp{offsets, E, 0};
+  if (kind == 0 || kind == 1) {
+    if (N % T2_BN) return -1;
+    rc = make_tmap_2d_bf16(&ta, A, K, capacity, K, T2_BK, T2_HALF);
+    if (rc) return rc;
+    if (kind == 0) { rc = make_tmap_2d_bf16(&tb, B, K, static_cast<uint64_t>(E) * N, K, T2_BK, T2_HALF); gp.b_rows = N; }
+    else           { rc = make_tmap_2d_bf16(&tb, B, N, static_cast<uint64_t>(E) * K, N, 64, T2_BK); gp.b_rows = K; }
+    if (rc) return rc;
+    Gemm2Params p{out, nullptr, capacity, N, K, N, 1.f, 0.f, 0, status};
+    const int max_tiles = (capacity / T2_BM) * (N / T2_BN);
+    return kind == 0 ? launch2_grouped<0, 0, 0, 1>(ta, tb, p, gp, max_tiles, num_sms, stream)
+                     : launch2_grouped<0, 1, 0, 1>(ta, tb, p, gp, max_tiles, num_sms, stream);
+  }
+  if (kind == 2) {
+    rc = make_tmap_2d_bf16(&ta, A, M, capacity, M, 64, T2_BK);
+    if (rc) return rc;
+    rc = make_tmap_2d_bf16(&tb, B, N, capacity, N, 64, T2_BK);
+    if (rc) return rc;
+    Gemm2Params p{out, nullptr, M, N, capacity, N, 1.f, 0.f, accumulate, status};
+    const int tiles = E * ((M + T2_BM - 1) / T2_BM) * ((N + T2_BN - 1) / T2_BN);
+    return out_f32 ? launch2_grouped<1, 1, 1, 2>(ta, tb, p, gp, tiles, num_sms, stream)
+                   : launch2_grouped<1, 1, 0, 2>(ta, tb, p, gp, tiles, num_sms, stream);
+  }
+  return -4;
+}
+
+// Batched GEMM, same contract as b200_gemm_bf16_batched.
+extern "C" int b200_gemm2_bf16_batched(int mode, const void* A, const void* B, void* out, const void* cin, int batch, int M,
+                                       int N, int K, float alpha, float beta, int num_sms, int* status, cudaStream_t stream) {
+  using namespace b200;
+  if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return 0;
+  if (mode != 0 && mode != 1) return -4;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return -5;
+    ctx_bound = true;
+  }
+  CUtensorMap ta, tb;
+  int rc = make_tmap_3d_bf16(&ta, A, K, M, batch, K, static_cast<uint64_t>(M) * K, T2_BK, T2_HALF);
+  if (rc) return rc;
+  if (mode == 0) rc = make_tmap_3d_bf16(&tb, B, K, N, batch, K, static_cast<uint64_t>(N) * K, T2_BK, T2_HALF);
+  else           rc = make_tmap_3d_bf16(&tb, B, N, K, batch, N, static_cast<uint64_t>(K) * N, 64, T2_BK);
+  if (rc) return rc;
+  Gemm2Params p{out, cin, M, N, K, N, alpha, beta, 0, status};
+  Group2Params gp{nullptr, batch, 0};
+  const int tiles = batch * ((M + T2_BM - 1) / T2_BM) * ((N + T2_BN - 1) / T2_BN);
+  return mode == 0 ? launch2_grouped<0, 0, 0, 3>(ta, tb, p, gp, tiles, num_sms, stream)
+                   : launch2_grouped<0, 1, 0, 3>(ta, tb, p, gp, tiles, num_sms, stream);
 }

@@ -3,7 +3,7 @@
 //   topk_indices      per token: indices of the K largest of E router logits, ties to the lower index
 //                     (the `stable_topk` rule of the reference, lit_gpt/moe.py:33-39); E ≤ 256, K ≤ 16
 //   routing_layout    stable counting sort of the N·K (token, slot) pairs by expert into a layout where
-//                     every expert's segment starts at a multiple of 128 rows (so GEMM tiles never
+//                     every expert's segment starts at a multiple of 256 rows (so GEMM tiles never
 //                     straddle experts and the wgrad K-loop never reads a neighbour's rows):
 //                       counts[E], offsets[E+1] (padded), slot_pair[capacity] (pair id or −1), pair_slot[N·K]
 //                     three small kernels: per-chunk histograms → per-chunk bases → stable placement
@@ -16,7 +16,7 @@
 namespace b200 {
 
 constexpr int RT_CHUNK = 2048;   // pairs per CTA in the layout kernels
-constexpr int RT_ALIGN = 128;    // expert segments start at multiples of this many rows
+constexpr int RT_ALIGN = 256;    // expert segments start at multiples of this many rows (one tile of the two-CTA grouped GEMM)
 
 template <int E_MAX>
 __global__ void __launch_bounds__(128) topk_indices_kernel(const float* __restrict__ logits, int* __restrict__ idx, int N, int E, int K) {

@@ -3,7 +3,7 @@
 See :mod:`archscale_b200.ops.moe` for the semantics.  Data flow (all on the device, no host sync —
 the reference copies token counts to the host every layer, `lit_gpt/moe.py:622-623`):
 
-    indices ─► routing_layout ─► offsets (128-aligned expert segments), slot↔pair maps
+    indices ─► routing_layout ─► offsets (256-aligned expert segments), slot↔pair maps
     x ─► gather_rows ─► xs ─► grouped GEMM (W_in) ─► SwiGLU ─► grouped GEMM (W_out) ─► combine_rows(scores)
 
 Backward runs the same pieces transposed: gate-weight gradients are row dot products, the

@@ -121,7 +121,7 @@ class PeerDispatcher:
         # detected before anything is copied and raises.
         import os
         factor = float(os.environ.get("ARCHSCALE_B200_EP_CAPACITY", self.world))
-        self.recv_cap = ((int(rows_cap * min(factor, self.world)) + 127) // 128) * 128
+        self.recv_cap = ((int(rows_cap * min(factor, self.world)) + self.e_local * 256 + 255) // 256) * 256   # + segment padding
         row_bytes = C * 2
         need = 2 * rows_cap * row_bytes + self.recv_cap * row_bytes + 16 * (n_experts + 1) * 4 + (1 << 20)
         self.heap = SymmetricHeap(group, need, device)
@@ -150,7 +150,7 @@ class PeerDispatcher:
         if used > self.recv_cap:
             raise RuntimeError(f"expert-parallel receive overflow: {used} rows > capacity {self.recv_cap}; "
                                "raise ARCHSCALE_B200_EP_CAPACITY")
-        rows = torch.empty(max(used, 128), self.C, dtype=torch.bfloat16, device=self.device)
+        rows = torch.empty(max(used, 256), self.C, dtype=torch.bfloat16, device=self.device)
         self.ext.ep_pull(self.heap.bases, self.off_counts, self.off_offsets, self.off_table, self.off_send[0], rows,
                          self.rank, e_local, recv_off)
         return rows, recv_off

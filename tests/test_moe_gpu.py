@@ -34,7 +34,7 @@ def test_routing_layout_is_a_stable_aligned_sort(N, E, K):
     c_ref, _, order = routing_metadata_ref(idx, E)
     assert torch.equal(counts, c_ref)
     off = offsets.tolist()
-    assert all(o % 128 == 0 for o in off) and off[0] == 0
+    assert all(o % 256 == 0 for o in off) and off[0] == 0
     pos = 0
     sp = slot_pair.tolist()
     order = order.tolist()
