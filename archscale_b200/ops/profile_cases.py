@@ -4,7 +4,7 @@ Inputs are larger than the 126 MB L2 (so DRAM counters mean something) and well 
 no warm-up loop and no timing, so a capture with ``-k regex:<kernel> -c 3`` ends by itself quickly.
 
     python -m archscale_b200.ops.profile_cases gemm
-    ncu --set full --clock-control none -k regex:gemm_bf16_kernel -c 3 -o prof python -m archscale_b200.ops.profile_cases gemm
+    ncu --set full --clock-control none -k regex:gemm2_bf16_kernel -c 3 -o prof python -m archscale_b200.ops.profile_cases gemm
 """
 from __future__ import annotations
 
@@ -120,6 +120,18 @@ def case_moe():
         y = moe_ffn_cuda(x, w1, w2, scores.to(torch.float32), idx)
         y.float().sum().backward()
     _run(once)
+
+
+def case_gdn():
+    """One forward pass and one reversed pass (with the extra term) of the gated-delta-rule recurrence kernel."""
+    ext = backend.require_extension()
+    BH, T, Dk, Dv = 12, 4096, 256, 512
+    mk = lambda d, sc: (torch.randn(BH, T, d, device="cuda") * sc).bfloat16()
+    a_op, bm_op, c_add, e_op, f_op = mk(Dk, 0.06), mk(Dk, 0.06), mk(Dv, 1.0), mk(Dv, 0.3), mk(Dk, 0.3)
+    decay = torch.rand(BH, T // 64, device="cuda") * 0.5 + 0.5
+    ext.gdn_state(a_op, c_add, bm_op, None, None, decay, False, -1.0, 1.0)
+    ext.gdn_state(a_op, c_add, bm_op, e_op, f_op, decay, True, 1.0, -1.0)
+    torch.cuda.synchronize()
 
 
 CASES = {k[5:]: v for k, v in list(globals().items()) if k.startswith("case_")}
