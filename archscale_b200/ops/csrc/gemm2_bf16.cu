@@ -41,6 +41,8 @@ struct Group2Params {
   const int* offsets;
   int E;
   int b_rows;           // rows of one expert's matrix inside B (GROUPED 1)
+  int sym;              // GROUPED 3, square outputs known to be symmetric (X·Xᵀ, polynomials of a symmetric matrix): only the
+                        // tiles on and above the diagonal are computed, an off-diagonal tile is also stored transposed
 };
 
 struct Gemm2Params {
@@ -51,7 +53,14 @@ struct Gemm2Params {
   float alpha, beta;
   int accumulate;
   int* status;
+  // serial split-K for accumulating fp32 output (see GemmParams in gemm_bf16.cu); 8 counters per tile (CTA rank × epilogue warp)
+  int split_k;
+  uint32_t* sem;
 };
+
+extern uint32_t* g_splitk_sem;
+extern int g_splitk_sem_len;
+int choose_split_k(int tiles, int num_kb, int sms, int slots_per_tile);
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -110,6 +119,7 @@ struct Tile2 {
   int b_row;       // GROUPED 1: first row of the expert's matrix in B; GROUPED 3: batch index
   int kb0, kb1;    // K-block range
   size_t out_off;  // element offset of the expert's / batch entry's output
+  int split, tile_id;
 };
 
 template <int A_MN, int B_MN, int OUT_F32, int GROUPED = 0>
@@ -136,7 +146,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   }
   const int num_n = (p.N + T2_BN - 1) / T2_BN;
   const int num_m = GROUPED == 1 ? s_off[gp.E] / T2_BM : (p.M + T2_BM - 1) / T2_BM;
-  const int num_tiles = ((GROUPED == 2 || GROUPED == 3) ? gp.E : 1) * num_m * num_n;
+  const int SK = (GROUPED == 0 && OUT_F32 && p.split_k > 1) ? p.split_k : 1;
+  const bool sym = GROUPED == 3 && gp.sym != 0;
+  const int per_problem = sym ? num_m * (num_m + 1) / 2 : num_m * num_n;
+  const int num_tiles = ((GROUPED == 2 || GROUPED == 3) ? gp.E : 1) * per_problem * SK;
   const int num_kb = (p.K + T2_BK - 1) / T2_BK;
 
   if (threadIdx.x == 0) {
@@ -155,11 +168,27 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   const uint32_t tmem_base = *tmem_ptr;
 
   auto get_tile = [&](int t, Tile2& tl) {
-    tl.kb0 = 0; tl.kb1 = num_kb; tl.out_off = 0; tl.b_row = 0;
+    tl.kb0 = 0; tl.kb1 = num_kb; tl.out_off = 0; tl.b_row = 0; tl.split = 0; tl.tile_id = t;
+    if (SK > 1) {        // all pieces 0 come first in the global order: a piece only ever waits for work with a smaller index
+      const int base_tiles = num_m * num_n;
+      tl.split = t / base_tiles;
+      t -= tl.split * base_tiles;
+      tl.tile_id = t;
+      const int per = (num_kb + SK - 1) / SK;
+      tl.kb0 = tl.split * per < num_kb ? tl.split * per : num_kb;
+      tl.kb1 = tl.kb0 + per < num_kb ? tl.kb0 + per : num_kb;
+    }
     if (GROUPED == 2 || GROUPED == 3) {
-      const int per = num_m * num_n;
-      const int e = t / per, r = t - e * per;
-      tl.m0 = (r % num_m) * T2_BM; tl.n0 = (r / num_m) * T2_BN;
+      const int per = per_problem;
+      const int e = t / per;
+      int r = t - e * per;
+      if (sym) {           // row mi of the upper triangle holds num_m − mi tiles
+        int mi = 0;
+        while (r >= num_m - mi) { r -= num_m - mi; ++mi; }
+        tl.m0 = mi * T2_BM; tl.n0 = (mi + r) * T2_BN;
+      } else {
+        tl.m0 = (r % num_m) * T2_BM; tl.n0 = (r / num_m) * T2_BN;
+      }
       tl.out_off = static_cast<size_t>(e) * p.M * p.ldc;
       if (GROUPED == 2) { tl.kb0 = s_off[e] / T2_BK; tl.kb1 = s_off[e + 1] / T2_BK; }
       else tl.b_row = e;
@@ -266,6 +295,29 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
       tc_fence_after();
       const int row = m0 + rank * T2_HALF + q * 32 + lane;
+      int acc_flag = p.accumulate;
+      uint32_t* sem = nullptr;
+      if (OUT_F32 && SK > 1) {
+        // wait until the previous piece of this tile has been added to this warp's 32 rows
+        sem = p.sem + (tl.tile_id * 2 + rank) * 4 + q;
+        if (tl.split > 0) {
+          bool ok = true;
+          if (lane == 0) {
+            const long long t0 = clock64();
+            while (ld_acquire_gpu(sem) != static_cast<uint32_t>(tl.split)) {
+              if (*abort_flag || clock64() - t0 > kWaitLimitCycles * 4) {
+                *abort_flag = 1;
+                if (p.status) atomicCAS(p.status, 0, STATUS_TIMEOUT_TMEM_EMPTY);
+                ok = false;
+                break;
+              }
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          if (!ok) goto done;
+          acc_flag = 1;
+        }
+      }
       const uint32_t taddr = tmem_base + acc * T2_BN + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < T2_BN / 32; ++c) {
@@ -285,7 +337,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
               if (col + j < p.N) {
                 float4 v = make_float4(__uint_as_float(r[j]) * p.alpha, __uint_as_float(r[j + 1]) * p.alpha,
                                        __uint_as_float(r[j + 2]) * p.alpha, __uint_as_float(r[j + 3]) * p.alpha);
-                if (p.accumulate) {
+                if (acc_flag) {
                   const float4 old = *reinterpret_cast<const float4*>(o + j);
                   v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
                 }
@@ -314,6 +366,12 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 ov.x = pack_bf16x2(f[0], f[1]); ov.y = pack_bf16x2(f[2], f[3]);
                 ov.z = pack_bf16x2(f[4], f[5]); ov.w = pack_bf16x2(f[6], f[7]);
                 *reinterpret_cast<uint4*>(o + j) = ov;
+                if (GROUPED == 3 && sym && n0 != m0) {      // transposed copy: lanes hold consecutive rows → 64-byte segments
+                  __nv_bfloat16* ot = reinterpret_cast<__nv_bfloat16*>(p.out) + tl.out_off + static_cast<size_t>(col + j) * p.ldc + row;
+#pragma unroll
+                  for (int e = 0; e < 8; ++e)
+                    if (col + j + e < p.N) ot[static_cast<size_t>(e) * p.ldc] = __float2bfloat16_rn(f[e]);
+                }
               }
             }
           }
@@ -322,6 +380,11 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_leader(&tmem_empty[acc]);
+      if (OUT_F32 && SK > 1) {
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) st_release_gpu(sem, tl.split + 1 == SK ? 0u : static_cast<uint32_t>(tl.split + 1));
+      }
     }
   }
 
@@ -346,8 +409,15 @@ static int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm2Para
   }
   const int tiles = ((p.M + T2_BM - 1) / T2_BM) * ((p.N + T2_BN - 1) / T2_BN);
   const int pairs = sms / 2;
-  const int grid = 2 * (tiles < pairs ? tiles : pairs);
-  kern<<<grid, T2_THREADS, T2_SMEM_BYTES, st>>>(ta, tb, p, Group2Params{});
+  Gemm2Params pp = p;
+  pp.split_k = 1; pp.sem = nullptr;
+  if (OUT_F32 && p.accumulate && g_splitk_sem != nullptr) {
+    pp.split_k = choose_split_k(tiles, (p.K + T2_BK - 1) / T2_BK, pairs, 8);
+    pp.sem = g_splitk_sem;
+  }
+  const int work = tiles * pp.split_k;
+  const int grid = 2 * (work < pairs ? work : pairs);
+  kern<<<grid, T2_THREADS, T2_SMEM_BYTES, st>>>(ta, tb, pp, Group2Params{});
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -388,7 +458,7 @@ extern "C" int b200_gemm2_bf16(int mode, const void* A, const void* B, void* out
   if (mode == 0) rc = make_tmap_2d_bf16(&tb, B, K, N, ldb, T2_BK, T2_HALF);   // stored [N, K]
   else           rc = make_tmap_2d_bf16(&tb, B, N, K, ldb, 64, T2_BK);        // stored [K, N]
   if (rc) return rc;
-  Gemm2Params p{out, cin, M, N, K, ldc, alpha, beta, accumulate, status};
+  Gemm2Params p{out, cin, M, N, K, ldc, alpha, beta, accumulate, status, 1, nullptr};
   if (mode == 0) return out_f32 ? launch2<0, 0, 1>(ta, tb, p, num_sms, stream) : launch2<0, 0, 0>(ta, tb, p, num_sms, stream);
   if (mode == 1) return out_f32 ? launch2<0, 1, 1>(ta, tb, p, num_sms, stream) : launch2<0, 1, 0>(ta, tb, p, num_sms, stream);
   if (mode == 2) return out_f32 ? launch2<1, 1, 1>(ta, tb, p, num_sms, stream) : launch2<1, 1, 0>(ta, tb, p, num_sms, stream);
@@ -410,7 +480,7 @@ extern "C" int b200_grouped_gemm2_bf16(int kind, const void* A, const void* B, v
   }
   CUtensorMap ta, tb;
   int rc;
-  Group2Params gp{offsets, E, 0};
+  Group2Params gp{offsets, E, 0, 0};
   if (kind == 0 || kind == 1) {
     if (N % T2_BN) return -1;
     rc = make_tmap_2d_bf16(&ta, A, K, capacity, K, T2_BK, T2_HALF);
@@ -418,7 +488,7 @@ extern "C" int b200_grouped_gemm2_bf16(int kind, const void* A, const void* B, v
     if (kind == 0) { rc = make_tmap_2d_bf16(&tb, B, K, static_cast<uint64_t>(E) * N, K, T2_BK, T2_HALF); gp.b_rows = N; }
     else           { rc = make_tmap_2d_bf16(&tb, B, N, static_cast<uint64_t>(E) * K, N, 64, T2_BK); gp.b_rows = K; }
     if (rc) return rc;
-    Gemm2Params p{out, nullptr, capacity, N, K, N, 1.f, 0.f, 0, status};
+    Gemm2Params p{out, nullptr, capacity, N, K, N, 1.f, 0.f, 0, status, 1, nullptr};
     const int max_tiles = (capacity / T2_BM) * (N / T2_BN);
     return kind == 0 ? launch2_grouped<0, 0, 0, 1>(ta, tb, p, gp, max_tiles, num_sms, stream)
                      : launch2_grouped<0, 1, 0, 1>(ta, tb, p, gp, max_tiles, num_sms, stream);
@@ -428,7 +498,7 @@ extern "C" int b200_grouped_gemm2_bf16(int kind, const void* A, const void* B, v
     if (rc) return rc;
     rc = make_tmap_2d_bf16(&tb, B, N, capacity, N, 64, T2_BK);
     if (rc) return rc;
-    Gemm2Params p{out, nullptr, M, N, capacity, N, 1.f, 0.f, accumulate, status};
+    Gemm2Params p{out, nullptr, M, N, capacity, N, 1.f, 0.f, accumulate, status, 1, nullptr};
     const int tiles = E * ((M + T2_BM - 1) / T2_BM) * ((N + T2_BN - 1) / T2_BN);
     return out_f32 ? launch2_grouped<1, 1, 1, 2>(ta, tb, p, gp, tiles, num_sms, stream)
                    : launch2_grouped<1, 1, 0, 2>(ta, tb, p, gp, tiles, num_sms, stream);
@@ -436,9 +506,11 @@ extern "C" int b200_grouped_gemm2_bf16(int kind, const void* A, const void* B, v
   return -4;
 }
 
-// Batched GEMM, same contract as b200_gemm_bf16_batched.
+// Batched GEMM, same contract as b200_gemm_bf16_batched; `symmetric`: the (square) results are symmetric matrices (and so is C),
+// compute the upper triangle of tiles only and mirror it.
 extern "C" int b200_gemm2_bf16_batched(int mode, const void* A, const void* B, void* out, const void* cin, int batch, int M,
-                                       int N, int K, float alpha, float beta, int num_sms, int* status, cudaStream_t stream) {
+                                       int N, int K, float alpha, float beta, int symmetric, int num_sms, int* status,
+                                       cudaStream_t stream) {
   using namespace b200;
   if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return 0;
   if (mode != 0 && mode != 1) return -4;
@@ -454,9 +526,11 @@ extern "C" int b200_gemm2_bf16_batched(int mode, const void* A, const void* B, v
   if (mode == 0) rc = make_tmap_3d_bf16(&tb, B, K, N, batch, K, static_cast<uint64_t>(N) * K, T2_BK, T2_HALF);
   else           rc = make_tmap_3d_bf16(&tb, B, N, K, batch, N, static_cast<uint64_t>(K) * N, 64, T2_BK);
   if (rc) return rc;
-  Gemm2Params p{out, cin, M, N, K, N, alpha, beta, 0, status};
-  Group2Params gp{nullptr, batch, 0};
-  const int tiles = batch * ((M + T2_BM - 1) / T2_BM) * ((N + T2_BN - 1) / T2_BN);
+  Gemm2Params p{out, cin, M, N, K, N, alpha, beta, 0, status, 1, nullptr};
+  if (symmetric && M != N) return -1;
+  Group2Params gp{nullptr, batch, 0, symmetric};
+  const int nm = (M + T2_BM - 1) / T2_BM;
+  const int tiles = batch * (symmetric ? nm * (nm + 1) / 2 : nm * ((N + T2_BN - 1) / T2_BN));
   return mode == 0 ? launch2_grouped<0, 0, 0, 3>(ta, tb, p, gp, tiles, num_sms, stream)
                    : launch2_grouped<0, 1, 0, 3>(ta, tb, p, gp, tiles, num_sms, stream);
 }

@@ -89,14 +89,6 @@ struct GemmParams {
   uint32_t* sem;
 };
 
-__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 
 // Copier CTA: one thread drives bulk-asynchronous copies (peer global → shared → local global) through a
 // 3-deep ring of 64 KiB buffers, so ~192 KiB are in flight per CTA; NVLink round trips are several µs and
@@ -595,16 +587,16 @@ int make_tmap_3d_bf16(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
-static uint32_t* g_splitk_sem = nullptr;
-static int g_splitk_sem_len = 0;
+uint32_t* g_splitk_sem = nullptr;      // shared with the two-CTA kernel (gemm2_bf16.cu)
+int g_splitk_sem_len = 0;
 
 // Pieces per output tile that best fill whole waves of `sms` CTAs (1 = no split); every piece keeps ≥ 64 K-blocks.
-static int choose_split_k(int tiles, int num_kb, int sms) {
+int choose_split_k(int tiles, int num_kb, int sms, int slots_per_tile) {
   auto eff = [&](int s) { const long long w = static_cast<long long>(tiles) * s; return static_cast<double>(w) / (((w + sms - 1) / sms) * sms); };
   int best = 1;
   double best_eff = eff(1);
   for (int s = 2; s <= 4; ++s) {
-    if (num_kb / s < 64 || tiles * 4 > g_splitk_sem_len) break;
+    if (num_kb / s < 64 || tiles * slots_per_tile > g_splitk_sem_len) break;
     if (eff(s) > best_eff * 1.08) { best = s; best_eff = eff(s); }
   }
   return best;
@@ -621,7 +613,7 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const Ge
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   GemmParams pp = p;
   if (OUT_F32 && p.accumulate && g_splitk_sem != nullptr) {
-    pp.split_k = choose_split_k(tiles, (p.K + BK - 1) / BK, sms);
+    pp.split_k = choose_split_k(tiles, (p.K + BK - 1) / BK, sms, 4);
     pp.sem = g_splitk_sem;
   }
   const int work = tiles * (pp.split_k > 1 ? pp.split_k : 1);

@@ -6,7 +6,8 @@ kernel split of `lit_gpt/optim/newton_schulz_triton.py:344-381`: per iteration
 bf16, transposed when tall, divided by ``‖X‖_F + ε``.
 
 CUDA path: the three products run on the tcgen05 GEMM (``csrc/gemm_bf16.cu``) with fused
-``α·AB + β·C`` epilogues; ``A`` and ``B`` are symmetric so the NT layout serves all three.
+``α·AB + β·C`` epilogues; ``A`` and ``B`` are symmetric so the NT layout serves all three, and the batched
+kernel computes only the tiles on and above the diagonal of those two products (stored twice, once transposed).
 """
 from __future__ import annotations
 
@@ -81,8 +82,9 @@ def _ns_cuda_batched(G: torch.Tensor, epsilon: float, coeffs=None) -> torch.Tens
         X = X.mT
     X = (X / (X.norm(dim=(-2, -1), keepdim=True) + epsilon)).contiguous()
     for a, b, c in NS_COEFFS:
-        A = ext.gemm_bf16_batched(X, X, 0, 1.0, 0.0, None)
-        Bm = ext.gemm_bf16_batched(A, A, 0, c, b, A)
+        # X·Xᵀ and the polynomial in A are symmetric: the kernel computes the upper triangle of tiles and mirrors it
+        A = ext.gemm_bf16_batched(X, X, 0, 1.0, 0.0, None, True)
+        Bm = ext.gemm_bf16_batched(A, A, 0, c, b, A, True)
         X = ext.gemm_bf16_batched(Bm, X, 1, 1.0, a, X)
         backend.count_launch(3)
     return X.mT if tall else X

@@ -259,7 +259,8 @@ def test_newton_schulz_batched_matches_per_matrix():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("M,N,K", [(3072, 2048, 16384), (2048, 5632, 8192), (512, 512, 32768)])
-def test_wgrad_split_k_accumulates_exactly_like_unsplit(M, N, K):
+@pytest.mark.parametrize("pair", [False, True])
+def test_wgrad_split_k_accumulates_exactly_like_unsplit(M, N, K, pair):
     """Accumulating TN GEMM whose tile count fills the last wave badly: the serial split-K path must add the same
     products (fp32 accumulation, fixed order) as a reference matmul, on top of the existing contents, twice in a row."""
     if not torch.cuda.is_available():
@@ -270,7 +271,7 @@ def test_wgrad_split_k_accumulates_exactly_like_unsplit(M, N, K):
     a = (torch.randn(K, M, device="cuda") * 0.1).bfloat16()
     b = (torch.randn(K, N, device="cuda") * 0.1).bfloat16()
     acc = torch.ones(M, N, device="cuda")
-    was = ext.set_gemm_pair(False)          # split-K lives in the one-CTA kernel
+    was = ext.set_gemm_pair(pair)           # both kernels split K (148 CTAs or 74 pairs to fill)
     try:
         ext.gemm_bf16(a, b, 2, torch.float32, acc)
         ext.gemm_bf16(a, b, 2, torch.float32, acc)
@@ -306,3 +307,22 @@ def test_gemm_one_cta_and_two_cta_kernels_agree_with_fp32(pair, M, N, K, mode):
     assert ext.device_status() == 0
     assert _rel(out, ref) < 1e-2
     assert _rel(acc, ref + 0.5) < 1e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("Bn,M,K", [(3, 640, 264), (2, 2048, 512), (5, 256, 1024)])
+def test_batched_symmetric_product_matches_full_product(Bn, M, K):
+    """X·Xᵀ and c·A·A + b·A computed from the upper triangle of tiles and mirrored (two-CTA kernel) equal the full products."""
+    torch.manual_seed(12)
+    x = (torch.randn(Bn, M, K, device="cuda") * 0.1).bfloat16()
+    full = _ext().gemm_bf16_batched(x, x, 0, 1.0, 0.0, None, False)
+    sym = _ext().gemm_bf16_batched(x, x, 0, 1.0, 0.0, None, True)
+    ref = x.float() @ x.float().transpose(1, 2)
+    assert _rel(sym, ref) < 1e-2 and _rel(full, ref) < 1e-2
+    assert torch.equal(sym, sym.transpose(1, 2))
+    a = sym.contiguous()
+    poly = _ext().gemm_bf16_batched(a, a, 0, 0.7, -1.3, a, True)
+    ref2 = 0.7 * (a.float() @ a.float()) - 1.3 * a.float()
+    assert _rel(poly, ref2) < 1e-2
+    torch.cuda.synchronize()
+    assert _ext().device_status() == 0
