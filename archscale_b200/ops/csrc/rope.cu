@@ -1,5 +1,5 @@
 // Fused per-head RMSNorm (QK-norm) + rotary embedding (NeoX halves) for q:[N,H,D] and k:[N,G,D], bf16.
-// One warp per (token, head) row; D ∈ {64, 128} so a lane owns D/32 contiguous elements and its
+// One warp per token (all its heads); D ∈ {64, 128} so a lane owns D/32 contiguous elements of a head row and its
 // rotation partner (i ± D/2) lives in lane ^ 16.  Statistics and rotation in fp32.
 // Backward undoes the rotation (conjugate), then applies the RMSNorm backward; the weight gradient
 // is accumulated per warp in registers, per CTA in shared memory and written as per-CTA partials
@@ -37,6 +37,10 @@ __device__ __forceinline__ float wsum(float v) {
   return v;
 }
 
+// One warp per TOKEN: cos / sin and the norm gains are loaded once and serve all H + G heads of the token, there is no
+// per-row index arithmetic, and the heads are walked four at a time so that four 256-byte rows are in flight per warp.
+constexpr int ROPE_U = 4;
+
 template <int EPL, typename TW>
 __global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const TW* __restrict__ qw,
@@ -47,42 +51,59 @@ __global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(
   const int lane = threadIdx.x & 31;
   const int64_t warp_global = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
   const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  const int64_t q_rows = n_tokens * H, rows = q_rows + n_tokens * G;
-  for (int64_t r = warp_global; r < rows; r += n_warps) {
-    const bool is_q = r < q_rows;
-    const int64_t rr = is_q ? r : r - q_rows;
-    const int heads = is_q ? H : G;
-    const int64_t tok = rr / heads;
-    // inputs may be column slices of a wider (fused projection) matrix: token stride q_ts / k_ts elements
-    const __nv_bfloat16* src = (is_q ? q + tok * q_ts : k + tok * k_ts) + (rr - tok * heads) * D + lane * EPL;
-    __nv_bfloat16* dst = (is_q ? qo : ko) + rr * D + lane * EPL;
-    const TW* w = is_q ? qw : kw;
-    float x[EPL];
-    ld_row<EPL>(src, x);
-    if (w) {
-      float ss = 0.f;
+  const int ci = (lane & 15) * EPL;
+  float wq[EPL], wk[EPL];
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) ss += x[e] * x[e];
-      ss = wsum(ss);
-      const float rs = rsqrtf(ss / D + eps);
-      if (lane == 0) (is_q ? q_rstd : k_rstd)[rr] = rs;
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) x[e] = x[e] * rs * ldw<TW>(w, lane * EPL + e);
-    }
+  for (int e = 0; e < EPL; ++e) {
+    wq[e] = qw ? ldw<TW>(qw, lane * EPL + e) : 1.f;
+    wk[e] = kw ? ldw<TW>(kw, lane * EPL + e) : 1.f;
+  }
+  for (int64_t tok = warp_global; tok < n_tokens; tok += n_warps) {
+    float cs[EPL], sn[EPL];
     if (cosb) {
-      const int t = static_cast<int>(tok % T);
-      const int ci = (lane & 15) * EPL;
-      float o[EPL];
+      const size_t co = static_cast<size_t>(tok % T) * (D / 2) + ci;
+      ld_row<EPL>(cosb + co, cs);
+      ld_row<EPL>(sinb + co, sn);
+    }
+#pragma unroll 1
+    for (int part = 0; part < 2; ++part) {      // the token's query heads, then its key heads
+      const int heads = part ? G : H;
+      // inputs may be column slices of a wider (fused projection) matrix: token stride q_ts / k_ts elements
+      const __nv_bfloat16* src = (part ? k + tok * k_ts : q + tok * q_ts) + lane * EPL;
+      __nv_bfloat16* dst = (part ? ko : qo) + tok * heads * D + lane * EPL;
+      float* rstd = (part ? k_rstd : q_rstd) + tok * heads;
+      const bool has_w = part ? kw != nullptr : qw != nullptr;
+      for (int h0 = 0; h0 < heads; h0 += ROPE_U) {
+        float x[ROPE_U][EPL];
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) {
-        const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);
-        const float c = __bfloat162float(cosb[static_cast<size_t>(t) * (D / 2) + ci + e]);
-        const float s = __bfloat162float(sinb[static_cast<size_t>(t) * (D / 2) + ci + e]);
-        o[e] = lane < 16 ? x[e] * c - other * s : other * s + x[e] * c;
+        for (int u = 0; u < ROPE_U; ++u)
+          if (h0 + u < heads) ld_row<EPL>(src + (h0 + u) * D, x[u]);
+#pragma unroll
+        for (int u = 0; u < ROPE_U; ++u) {
+          if (h0 + u >= heads) continue;          // warp-uniform
+          if (has_w) {
+            float ss = 0.f;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) ss += x[u][e] * x[u][e];
+            ss = wsum(ss);
+            const float rs = rsqrtf(ss / D + eps);
+            if (lane == 0) rstd[h0 + u] = rs;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) x[u][e] = x[u][e] * rs * (part ? wk[e] : wq[e]);
+          }
+          if (cosb) {
+            float o[EPL];
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) {
+              const float other = __shfl_xor_sync(0xffffffffu, x[u][e], 16);
+              o[e] = lane < 16 ? x[u][e] * cs[e] - other * sn[e] : other * sn[e] + x[u][e] * cs[e];
+            }
+            st_row<EPL>(dst + (h0 + u) * D, o);
+          } else {
+            st_row<EPL>(dst + (h0 + u) * D, x[u]);
+          }
+        }
       }
-      st_row<EPL>(dst, o);
-    } else {
-      st_row<EPL>(dst, x);
     }
   }
 }
@@ -101,51 +122,69 @@ __global__ void __launch_bounds__(256) qknorm_rope_bwd_kernel(
   __syncthreads();
   const int64_t warp_global = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
   const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  const int64_t q_rows = n_tokens * H, rows = q_rows + n_tokens * G;
-  float dwq[EPL], dwk[EPL];
+  const int ci = (lane & 15) * EPL;
+  float dwq[EPL], dwk[EPL], wq[EPL], wk[EPL];
 #pragma unroll
-  for (int e = 0; e < EPL; ++e) dwq[e] = dwk[e] = 0.f;
-  for (int64_t r = warp_global; r < rows; r += n_warps) {
-    const bool is_q = r < q_rows;
-    const int64_t rr = is_q ? r : r - q_rows;
-    const int heads = is_q ? H : G;
-    const int64_t tok = rr / heads;
-    const size_t off = rr * D + lane * EPL;
-    float g[EPL];
-    ld_row<EPL>((is_q ? dqo : dko) + off, g);
+  for (int e = 0; e < EPL; ++e) {
+    dwq[e] = dwk[e] = 0.f;
+    wq[e] = qw ? ldw<TW>(qw, lane * EPL + e) : 1.f;
+    wk[e] = kw ? ldw<TW>(kw, lane * EPL + e) : 1.f;
+  }
+  for (int64_t tok = warp_global; tok < n_tokens; tok += n_warps) {
+    float cs[EPL], sn[EPL];
     if (cosb) {
-      const int t = static_cast<int>(tok % T);
-      const int ci = (lane & 15) * EPL;
-      float o[EPL];
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) {
-        const float other = __shfl_xor_sync(0xffffffffu, g[e], 16);
-        const float c = __bfloat162float(cosb[static_cast<size_t>(t) * (D / 2) + ci + e]);
-        const float s = __bfloat162float(sinb[static_cast<size_t>(t) * (D / 2) + ci + e]);
-        o[e] = lane < 16 ? g[e] * c + other * s : -other * s + g[e] * c;
-      }
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) g[e] = o[e];
+      const size_t co = static_cast<size_t>(tok % T) * (D / 2) + ci;
+      ld_row<EPL>(cosb + co, cs);
+      ld_row<EPL>(sinb + co, sn);
     }
-    const TW* w = is_q ? qw : kw;
-    if (w) {
-      float x[EPL];
-      ld_row<EPL>((is_q ? q + tok * q_ts : k + tok * k_ts) + (rr - tok * heads) * D + lane * EPL, x);
-      const float rs = (is_q ? q_rstd : k_rstd)[rr];
-      float dot = 0.f;
-      float gw[EPL];
+#pragma unroll 1
+    for (int part = 0; part < 2; ++part) {
+      const int heads = part ? G : H;
+      const size_t obase = static_cast<size_t>(tok) * heads * D + lane * EPL;
+      const __nv_bfloat16* gsrc = (part ? dko : dqo) + obase;
+      __nv_bfloat16* gdst = (part ? dk : dq) + obase;
+      const __nv_bfloat16* xsrc = (part ? k + tok * k_ts : q + tok * q_ts) + lane * EPL;
+      const float* rstd = (part ? k_rstd : q_rstd) + tok * heads;
+      const bool has_w = part ? kw != nullptr : qw != nullptr;
+      for (int h0 = 0; h0 < heads; h0 += ROPE_U) {
+        float g[ROPE_U][EPL], x[ROPE_U][EPL], rs[ROPE_U];
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) {
-        gw[e] = g[e] * ldw<TW>(w, lane * EPL + e);
-        dot += gw[e] * x[e];
-        if (is_q) dwq[e] += g[e] * x[e] * rs; else dwk[e] += g[e] * x[e] * rs;
+        for (int u = 0; u < ROPE_U; ++u) {
+          if (h0 + u >= heads) continue;
+          ld_row<EPL>(gsrc + (h0 + u) * D, g[u]);
+          if (has_w) { ld_row<EPL>(xsrc + (h0 + u) * D, x[u]); rs[u] = rstd[h0 + u]; }
+        }
+#pragma unroll
+        for (int u = 0; u < ROPE_U; ++u) {
+          if (h0 + u >= heads) continue;
+          if (cosb) {
+            float o[EPL];
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) {
+              const float other = __shfl_xor_sync(0xffffffffu, g[u][e], 16);
+              o[e] = lane < 16 ? g[u][e] * cs[e] + other * sn[e] : -other * sn[e] + g[u][e] * cs[e];
+            }
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) g[u][e] = o[e];
+          }
+          if (has_w) {
+            float dot = 0.f;
+            float gw[EPL];
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) {
+              gw[e] = g[u][e] * (part ? wk[e] : wq[e]);
+              dot += gw[e] * x[u][e];
+              if (part) dwk[e] += g[u][e] * x[u][e] * rs[u]; else dwq[e] += g[u][e] * x[u][e] * rs[u];
+            }
+            dot = wsum(dot);
+            const float c1 = dot * rs[u] * rs[u] * rs[u] / D;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) g[u][e] = gw[e] * rs[u] - x[u][e] * c1;
+          }
+          st_row<EPL>(gdst + (h0 + u) * D, g[u]);
+        }
       }
-      dot = wsum(dot);
-      const float c1 = dot * rs * rs * rs / D;
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) g[e] = gw[e] * rs - x[e] * c1;
     }
-    st_row<EPL>((is_q ? dq : dk) + off, g);
   }
   if (qw) {
 #pragma unroll
