@@ -230,6 +230,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("acc") = py::none());
   m.def("gemm_bf16_epi", &gemm_bf16_epi);
   m.def("set_gemm_pair", &set_gemm_pair);
+  m.def("gemm_pair", &gemm_use_pair);
   m.def("device_status", &device_status);
   m.def("reset_device_status", &reset_device_status);
   m.def("rmsnorm_fwd", &rmsnorm_fwd, py::arg("x"), py::arg("w"), py::arg("eps"), py::arg("out_dtype") = py::none());

@@ -513,7 +513,7 @@ extern "C" int b200_gemm2_bf16_batched(int mode, const void* A, const void* B, v
                                        cudaStream_t stream) {
   using namespace b200;
   if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return 0;
-  if (mode != 0 && mode != 1) return -4;
+  if (mode < 0 || mode > 2) return -4;
   static thread_local bool ctx_bound = false;
   if (!ctx_bound) {
     int dev = 0;
@@ -521,7 +521,9 @@ extern "C" int b200_gemm2_bf16_batched(int mode, const void* A, const void* B, v
     ctx_bound = true;
   }
   CUtensorMap ta, tb;
-  int rc = make_tmap_3d_bf16(&ta, A, K, M, batch, K, static_cast<uint64_t>(M) * K, T2_BK, T2_HALF);
+  int rc;
+  if (mode == 2) rc = make_tmap_3d_bf16(&ta, A, M, K, batch, M, static_cast<uint64_t>(K) * M, 64, T2_BK);        // stored [K, M]
+  else           rc = make_tmap_3d_bf16(&ta, A, K, M, batch, K, static_cast<uint64_t>(M) * K, T2_BK, T2_HALF);   // stored [M, K]
   if (rc) return rc;
   if (mode == 0) rc = make_tmap_3d_bf16(&tb, B, K, N, batch, K, static_cast<uint64_t>(N) * K, T2_BK, T2_HALF);
   else           rc = make_tmap_3d_bf16(&tb, B, N, K, batch, N, static_cast<uint64_t>(K) * N, 64, T2_BK);
@@ -531,6 +533,7 @@ extern "C" int b200_gemm2_bf16_batched(int mode, const void* A, const void* B, v
   Group2Params gp{nullptr, batch, 0, symmetric};
   const int nm = (M + T2_BM - 1) / T2_BM;
   const int tiles = batch * (symmetric ? nm * (nm + 1) / 2 : nm * ((N + T2_BN - 1) / T2_BN));
-  return mode == 0 ? launch2_grouped<0, 0, 0, 3>(ta, tb, p, gp, tiles, num_sms, stream)
-                   : launch2_grouped<0, 1, 0, 3>(ta, tb, p, gp, tiles, num_sms, stream);
+  if (mode == 0) return launch2_grouped<0, 0, 0, 3>(ta, tb, p, gp, tiles, num_sms, stream);
+  if (mode == 1) return launch2_grouped<0, 1, 0, 3>(ta, tb, p, gp, tiles, num_sms, stream);
+  return launch2_grouped<1, 1, 0, 3>(ta, tb, p, gp, tiles, num_sms, stream);
 }

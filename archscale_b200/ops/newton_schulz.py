@@ -73,21 +73,29 @@ def _ns_cuda_2d(G: torch.Tensor, epsilon: float, coeffs=None) -> torch.Tensor:
 
 
 def _ns_cuda_batched(G: torch.Tensor, epsilon: float, coeffs=None) -> torch.Tensor:
-    """G:(B,m,n) — all B matrices advance together: 3 batched tcgen05 GEMM launches per iteration."""
+    """G:(B,m,n) — all B matrices advance together: 3 batched tcgen05 GEMM launches per iteration.  Wide matrices iterate
+    ``A = X·Xᵀ``, ``X ← a·X + B·X``; tall ones the mirrored form ``A = Xᵀ·X``, ``X ← a·X + X·B`` on the untransposed
+    data (TN and NN products), so that no transposed copy of the stack is made on the way in or out."""
     NS_COEFFS = coeffs if coeffs is not None else globals()["NS_COEFFS"]
     ext = backend.require_extension()
     X = G.to(torch.bfloat16)
     tall = G.size(-2) > G.size(-1)
-    if tall:
+    in_place_tall = tall and hasattr(ext, "gemm_pair") and ext.gemm_pair()
+    if tall and not in_place_tall:
         X = X.mT
     X = (X / (X.norm(dim=(-2, -1), keepdim=True) + epsilon)).contiguous()
     for a, b, c in NS_COEFFS:
-        # X·Xᵀ and the polynomial in A are symmetric: the kernel computes the upper triangle of tiles and mirrors it
-        A = ext.gemm_bf16_batched(X, X, 0, 1.0, 0.0, None, True)
-        Bm = ext.gemm_bf16_batched(A, A, 0, c, b, A, True)
-        X = ext.gemm_bf16_batched(Bm, X, 1, 1.0, a, X)
+        # the Gram matrix and the polynomial in it are symmetric: the kernel computes the upper triangle of tiles and mirrors it
+        if in_place_tall:
+            A = ext.gemm_bf16_batched(X, X, 2, 1.0, 0.0, None, True)
+            Bm = ext.gemm_bf16_batched(A, A, 0, c, b, A, True)
+            X = ext.gemm_bf16_batched(X, Bm, 1, 1.0, a, X)
+        else:
+            A = ext.gemm_bf16_batched(X, X, 0, 1.0, 0.0, None, True)
+            Bm = ext.gemm_bf16_batched(A, A, 0, c, b, A, True)
+            X = ext.gemm_bf16_batched(Bm, X, 1, 1.0, a, X)
         backend.count_launch(3)
-    return X.mT if tall else X
+    return X.mT if (tall and not in_place_tall) else X
 
 
 def newton_schulz(G: torch.Tensor, epsilon: float = 1e-7, coeffs=None) -> torch.Tensor:

@@ -253,8 +253,16 @@ def test_newton_schulz_batched_matches_per_matrix():
     O = ops.newton_schulz(G)
     R = torch.stack([ops.newton_schulz(g) for g in G])
     assert _rel(O, R) < 2e-2
-    Gt = torch.randn(4, 1024, 256, device="cuda")          # tall: transposed internally
-    assert _rel(ops.newton_schulz(Gt), ops.newton_schulz_ref(Gt)) < 0.1
+    Gt = torch.randn(4, 1024, 256, device="cuda")          # tall: Gram matrix XᵀX on the untransposed data (two-CTA kernel)
+    Ot = ops.newton_schulz(Gt)
+    assert _rel(Ot, ops.newton_schulz_ref(Gt)) < 0.1
+    was = _ext().set_gemm_pair(False)                       # one-CTA kernel: transposed copy in and out
+    try:
+        Ot1 = ops.newton_schulz(Gt)
+    finally:
+        _ext().set_gemm_pair(was)
+    assert _rel(Ot, Ot1) < 2e-2
+    assert _ext().device_status() == 0
 
 
 @pytest.mark.gpu
