@@ -183,3 +183,30 @@ def compute_tokens_per_expert_seq(indices: torch.Tensor, n_experts: int, seq_len
     out = torch.zeros(Bn, n_experts, dtype=torch.float32, device=indices.device)
     out.scatter_add_(1, flat, torch.ones_like(flat, dtype=torch.float32))
     return out
+
+
+def activation_budget_loss(router_out: torch.Tensor, tau: float = 0.25, mask: Optional[torch.Tensor] = None,
+                           lambda_budget: float = 1.0, eps: float = 1e-6, loss: str = "mse",
+                           mode: str = "per_layer") -> torch.Tensor:
+    """Budget loss of the token-skipping layer configurator (`lit_gpt/aux_loss.py:7-84`): pushes the expected active
+    fraction towards ``tau``.  router_out: (B, L, T) keep-probabilities; ``mask``: (B, T) valid tokens.
+    ``per_layer`` compares every layer's mean over tokens with ``tau``, ``per_sequence`` the mean over layers and tokens;
+    ``loss`` is ``"mse"`` or ``"bce"``."""
+    p = router_out.clamp(eps, 1 - eps)
+    if mask is None:
+        frac = p.mean(dim=2)                                              # (B, L)
+    else:
+        m = mask.to(p.dtype).clamp(0.0, 1.0).unsqueeze(1)                 # (B, 1, T)
+        frac = (p * m).sum(dim=2) / m.sum(dim=(1, 2)).clamp_min(eps).unsqueeze(1)
+    if mode == "per_sequence":
+        frac = frac.mean(dim=1)                                           # (B,)
+    elif mode != "per_layer":
+        raise ValueError(f"unknown mode {mode!r}")
+    target = torch.full_like(frac, tau)
+    if loss == "bce":
+        val = torch.nn.functional.binary_cross_entropy(frac.clamp(eps, 1 - eps), target)
+    elif loss == "mse":
+        val = torch.nn.functional.mse_loss(frac, target)
+    else:
+        raise ValueError(f"unknown loss {loss!r}")
+    return lambda_budget * val

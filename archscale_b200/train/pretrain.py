@@ -484,6 +484,16 @@ class Trainer:
         if self.config.moe:
             bal = self.model.aux_loss
             back = back + bal
+        gates = getattr(self.model, "lc_gate_hist", None)
+        if gates:
+            # layer-configurator models: push the kept-token fraction of every layer towards the budget
+            # (`pretrain.py:910-924` of the reference)
+            from archscale_b200.ops.moe import activation_budget_loss
+            probs = torch.stack([g.squeeze(-1) for g in gates], dim=1)             # (B, L, T)
+            self.last_budget_loss = activation_budget_loss(probs, tau=self.config.lc_budget_tau,
+                                                           lambda_budget=self.config.lc_budget_lambda)
+            back = back + self.last_budget_loss
+            self.last_budget_loss = self.last_budget_loss.detach()
         self.engine.backward(back / accum if accum != 1 else back)
         loss = loss.detach()
         if tp > 1:

@@ -1,0 +1,43 @@
+"""Padding helpers, chunked cross-entropy and the activation-budget loss (CPU)."""
+import torch
+import torch.nn.functional as F
+
+from archscale_b200.ops.moe import activation_budget_loss
+from archscale_b200.utils.misc import chunked_cross_entropy
+from archscale_b200.utils.padding import pad_input, unpad_input
+
+
+def test_unpad_pad_roundtrip_and_cu_seqlens():
+    torch.manual_seed(0)
+    x = torch.randn(3, 7, 4, requires_grad=True)
+    mask = torch.tensor([[1, 1, 1, 0, 0, 0, 0], [1, 1, 1, 1, 1, 1, 1], [1, 0, 0, 0, 0, 0, 0]], dtype=torch.bool)
+    rows, idx, cu, mx = unpad_input(x, mask)
+    assert rows.shape == (11, 4) and cu.tolist() == [0, 3, 10, 11] and mx == 7
+    back = pad_input(rows, idx, 3, 7)
+    assert torch.equal(back[mask], x[mask]) and float(back[~mask].abs().sum()) == 0.0
+    back.sum().backward()
+    assert torch.equal(x.grad[mask], torch.ones_like(x.grad[mask])) and float(x.grad[~mask].abs().sum()) == 0.0
+
+
+def test_chunked_cross_entropy_matches_plain():
+    torch.manual_seed(1)
+    logits, tgt = torch.randn(2, 50, 33), torch.randint(0, 33, (2, 50))
+    tgt[0, :5] = -1
+    ref = F.cross_entropy(logits.reshape(-1, 33), tgt.reshape(-1), ignore_index=-1)
+    assert torch.allclose(chunked_cross_entropy(logits, tgt, 16), ref, atol=1e-6)
+    assert torch.allclose(chunked_cross_entropy(list(logits.split(20, dim=1)), tgt, 16), ref, atol=1e-6)
+    assert torch.allclose(chunked_cross_entropy(logits, tgt, 0), ref, atol=1e-6)
+
+
+def test_activation_budget_loss():
+    p = torch.full((2, 3, 8), 0.25)
+    assert float(activation_budget_loss(p, tau=0.25)) < 1e-12
+    p2 = torch.rand(2, 3, 8)
+    mask = torch.ones(2, 8)
+    mask[1, 4:] = 0
+    per_layer = activation_budget_loss(p2, 0.3, mask, mode="per_layer")
+    frac = torch.stack([p2[0].mean(-1), p2[1, :, :4].mean(-1)])
+    assert torch.allclose(per_layer, ((frac - 0.3) ** 2).mean(), atol=1e-6)
+    bce = activation_budget_loss(p2, 0.3, None, loss="bce", mode="per_sequence", lambda_budget=2.0)
+    m = p2.clamp(1e-6, 1 - 1e-6).mean(dim=(1, 2))
+    assert torch.allclose(bce, 2.0 * F.binary_cross_entropy(m, torch.full_like(m, 0.3)), atol=1e-6)
