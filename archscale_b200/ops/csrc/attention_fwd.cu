@@ -56,13 +56,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint64_t* q_full = bars;            // 1
   uint64_t* k_full = bars + 1;        // [2]
   uint64_t* v_full = bars + 3;        // [2]
-  uint64_t* kv_empty = bars + 5;      // [2]
+  uint64_t* k_empty = bars + 5;       // [2]  K stage free: S of its tile has completed
   uint64_t* s_full = bars + 7;        // [2]
   uint64_t* s_empty = bars + 9;       // [2]
   uint64_t* p_full = bars + 11;       // [2]
   uint64_t* p_empty = bars + 13;      // [2]
   uint64_t* o_done = bars + 15;       // 1
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* v_empty = bars + 16;      // [2]  V stage free: P·V of its tile has completed
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -86,7 +87,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1);
+      mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4); mbar_init(&p_full[s], 4); mbar_init(&p_empty[s], 1);
     }
     mbar_init(o_done, 1);
@@ -108,13 +109,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       for (int c = 0; c < DC; ++c) tma_load_2d(sq + c * CHUNK_BYTES, &tmap_q, q_full, h * D + c * 64, b * p.T + q0);
       for (int t = 0; t < n_tiles; ++t) {
         const int st = t & 1; const uint32_t ph = (t >> 1) & 1;
-        if (!mbar_wait(&kv_empty[st], ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) goto done;
+        // K and V stages are released separately: the K of tile t+2 can land while tile t is still in its softmax, so the
+        // next S = Q·Kᵀ never waits for a load (with one barrier for both, K waited for P·V and the softmax warps for S)
+        if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) goto done;
         uint8_t* sk = skv + st * 2 * SM::KV_BYTES;
         uint8_t* sv = sk + SM::KV_BYTES;
         const int k0 = (j_begin + t) * ATT_BN;
         mbar_arrive_expect_tx(&k_full[st], SM::KV_BYTES);
 #pragma unroll
         for (int c = 0; c < DC; ++c) tma_load_2d(sk + c * CHUNK_BYTES, &tmap_k, &k_full[st], g * D + c * 64, b * p.T + k0);
+        if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) goto done;
         mbar_arrive_expect_tx(&v_full[st], SM::KV_BYTES);
 #pragma unroll
         for (int c = 0; c < DC; ++c) tma_load_2d(sv + c * CHUNK_BYTES, &tmap_v, &v_full[st], g * D + c * 64, b * p.T + k0);
@@ -139,6 +143,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                     k != 0 ? 1u : 0u);
         }
         umma_commit(&s_full[st]);
+        umma_commit(&k_empty[st]);
         return true;
       };
       if (n_tiles > 0 && !issue_s(0)) goto done;
@@ -155,7 +160,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           umma_bf16_ts(T_O, T_P0 + st * 64 + k * 8, make_smem_desc(sv + k * 2048, CHUNK_BYTES, 1024), idesc_o,
                        (t | k) != 0 ? 1u : 0u);
         }
-        umma_commit(&kv_empty[st]);
+        umma_commit(&v_empty[st]);
         umma_commit(&p_empty[st]);
         umma_commit(o_done);
       }
@@ -174,16 +179,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const int k0 = (j_begin + t) * ATT_BN;
       if (!mbar_wait(&s_full[st], ph, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
       tc_fence_after();
-      // this row's 128 scores
+      // this row's 128 raw scores: four loads in flight, one wait; the softmax scale is folded into the exponent below
       float s[128];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rr[32];
-        tmem_ld_32x32(T_S0 + st * 128 + c * 32 + lane_off, rr);
-        tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < 32; ++e) s[c * 32 + e] = __uint_as_float(rr[e]) * p.scale_log2;
-      }
+      for (int c = 0; c < 4; ++c)
+        tmem_ld_32x32(T_S0 + st * 128 + c * 32 + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
+      tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[st]);     // S buffer may be overwritten by S_{t+2}
@@ -195,9 +196,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           if (kk > r || kk < lo_r) s[e] = -INFINITY;
         }
       }
-      float mx = s[0];
+      float mx8[8];                                  // eight independent chains instead of one of length 128
 #pragma unroll
-      for (int e = 1; e < 128; ++e) mx = fmaxf(mx, s[e]);
+      for (int e = 0; e < 8; ++e) mx8[e] = s[e];
+#pragma unroll
+      for (int e = 8; e < 128; ++e) mx8[e & 7] = fmaxf(mx8[e & 7], s[e]);
+      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]))) *
+                       p.scale_log2;
       // lazy rescale: only when the running max grew by more than 8 (factor 256); decided per warp
       const bool need = (mx - m_used) > 8.f;
       if (__any_sync(0xffffffffu, need)) {
@@ -229,18 +234,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // P = 2^(s − m_used), packed to bf16 and written to TMEM; row sum in fp32
       if (!mbar_wait(&p_empty[st], ph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) goto done;
       tc_fence_after();
-      float rs = 0.f;
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+      const float sl2 = p.scale_log2;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t w[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          const float p0 = exp2f(s[c * 32 + 2 * e] - m_used), p1 = exp2f(s[c * 32 + 2 * e + 1] - m_used);
-          rs += p0 + p1;
+          const float p0 = exp2f(fmaf(s[c * 32 + 2 * e], sl2, -m_used)), p1 = exp2f(fmaf(s[c * 32 + 2 * e + 1], sl2, -m_used));
+          rs4[e & 3] += p0 + p1;
           w[e] = pack_bf16x2(p0, p1);
         }
         tmem_st_32x16(T_P0 + st * 64 + c * 16 + lane_off, w);
       }
+      const float rs = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
       tmem_st_wait();
       l_sum += rs;
       tc_fence_before();
