@@ -1,9 +1,9 @@
 // Causal / sliding-window / packed-varlen attention forward on tcgen05 (GQA, head_dim 64 or 128).
 //
-// One CTA per (query tile of 128 rows, head, batch); 192 threads:
+// One CTA per (query tile of 128 rows, head, batch); 224 threads:
 //   warp 0      TMA: Q once, then K/V tiles of 128 keys through a 2-stage ring
-//   warp 1      MMA: S_j = Q·K_jᵀ into one of two 128-column TMEM buffers, then O += P_j·V_j with
-//               P_j (bf16) read from TMEM as the A operand and V_j from shared memory (N-major)
+//   warp 1      MMA: S_j = Q·K_jᵀ into one of two 128-column TMEM buffers
+//   warp 6      MMA: O += P_j·V_j with P_j (bf16) read from TMEM as the A operand and V_j from shared memory (N-major)
 //   warps 2..5  softmax: thread t owns query row t — tcgen05.ld its 128 scores, online softmax in
 //               base 2 with lazy rescaling of O (only when the running max grew by more than 2^8),
 //               write P_j to TMEM (packed bf16), finally normalise O and store it with the LSE
@@ -20,7 +20,8 @@
 namespace b200 {
 
 constexpr int ATT_BM = 128, ATT_BN = 128;
-constexpr int ATT_THREADS = 192;
+constexpr int ATT_THREADS = 224;          // warp 0 TMA, warp 1 MMA (S), warps 2..5 softmax, warp 6 MMA (P·V)
+constexpr int ATT_PV_WARP = 6;
 constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
 
 struct AttnFwdParams {
@@ -127,7 +128,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(ATT_BM, ATT_BN, 0, 0);       // S = Q·Kᵀ  (both K-major)
-      constexpr uint32_t idesc_o = make_idesc_bf16(ATT_BM, D, 0, 1);            // O += P·V  (V is N-major)
       if (!mbar_wait(q_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL)) goto done;
       auto issue_s = [&](int t) -> bool {
         const int st = t & 1; const uint32_t ph = (t >> 1) & 1;
@@ -146,10 +146,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         umma_commit(&k_empty[st]);
         return true;
       };
-      if (n_tiles > 0 && !issue_s(0)) goto done;
+      // One thread can issue a tcgen05.mma only every ~100 cycles: S and P·V are issued by two threads (this one and warp
+      // ATT_PV_WARP) so that neither stream waits behind the other's issue slots.  s_empty / p_empty order the buffer reuse.
+      for (int t = 0; t < n_tiles; ++t)
+        if (!issue_s(t)) goto done;
+    }
+  } else if (warp == ATT_PV_WARP) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_o = make_idesc_bf16(ATT_BM, D, 0, 1);            // O += P·V  (V is N-major)
       for (int t = 0; t < n_tiles; ++t) {
         const int st = t & 1; const uint32_t ph = (t >> 1) & 1;
-        if (t + 1 < n_tiles && !issue_s(t + 1)) goto done;
         if (!mbar_wait(&v_full[st], ph, abort_flag, p.status, STATUS_TIMEOUT_FULL)) goto done;
         if (!mbar_wait(&p_full[st], ph, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
         tc_fence_after();
