@@ -18,8 +18,9 @@
 namespace b200 {
 
 constexpr int BT = 128;                 // tile edge (queries and keys)
-constexpr int BWD_THREADS = 352;            // warp 0 TMA, warp 1 MMA (S, dP), warps 2..9 softmax, warp 10 MMA (accumulations)
+constexpr int BWD_THREADS = 384;            // warp 0 TMA, warp 1 MMA (S), warps 2..9 softmax, warp 10 MMA (accumulations), warp 11 MMA (dP)
 constexpr int ACC_WARP = 10;
+constexpr int DP_WARP = 11;
 constexpr float kLog2e_b = 1.4426950408889634f;
 
 int make_tmap_2d_bf16(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t row_stride_elems,
@@ -131,7 +132,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     mbar_init(fixed_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1);
-      mbar_init(&sdp_full[s], 1); mbar_init(&ds_full[s], 4); mbar_init(&buf_free[s], 1);
+      mbar_init(&sdp_full[s], 2); mbar_init(&ds_full[s], 4); mbar_init(&buf_free[s], 1);
     }
     mbar_init(acc_done, 1);
     *abort_flag = 0;
@@ -166,37 +167,34 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == DP_WARP) {
     if (lane == 0) {
+      // S = Q·Kᵀ is issued by warp 1 and dP = dO·Vᵀ by warp DP_WARP: one thread issues a tcgen05.mma only every ~100 cycles, and
+      // the softmax of a half cannot start before both products are in tensor memory.  sdp_full counts both commits.
+      const bool is_dp = warp == DP_WARP;
       constexpr uint32_t idesc_s = make_idesc_bf16(BT, HB, 0, 0);
       if (!mbar_wait(fixed_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL)) goto done;
-      const uint32_t sqa = smem_u32(sq), sdoa = smem_u32(sdo);
-      // S, dP of half `hx` into buffer hx & 1 (keys hf·64.. of the tile: rows 8192 bytes into each 64-column chunk)
-      auto issue_sdp = [&](int hx) -> bool {
+      const uint32_t sa = smem_u32(is_dp ? sdo : sq);
+      // keys hf·64.. of the tile: rows 8192 bytes into each 64-column chunk
+      auto issue_one = [&](int hx) -> bool {
         const int t = hx >> 1, hf = hx & 1, st = t & 1, buf = hx & 1;
         if (hf == 0 && !mbar_wait(&kv_full[st], (t >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
         tc_fence_after();
-        const uint32_t sk = smem_u32(ring + st * 2 * SM::TILE) + hf * 8192, sv = sk + SM::TILE;
-        const uint32_t ts = tmem_base + buf * 128, tdp = ts + 64;
+        const uint32_t sb = smem_u32(ring + st * 2 * SM::TILE) + hf * 8192 + (is_dp ? SM::TILE : 0);
+        const uint32_t td = tmem_base + buf * 128 + (is_dp ? 64 : 0);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k / 4) * CHUNK_BYTES + (k % 4) * 32;
-          umma_bf16(ts, make_smem_desc(sqa + off, 16, 1024), make_smem_desc(sk + off, 16, 1024), idesc_s, k != 0);
-        }
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k / 4) * CHUNK_BYTES + (k % 4) * 32;
-          umma_bf16(tdp, make_smem_desc(sdoa + off, 16, 1024), make_smem_desc(sv + off, 16, 1024), idesc_s, k != 0);
+          umma_bf16(td, make_smem_desc(sa + off, 16, 1024), make_smem_desc(sb + off, 16, 1024), idesc_s, k != 0);
         }
         umma_commit(&sdp_full[buf]);
         return true;
       };
-      // One thread can only issue a tcgen05.mma every ~85 cycles, whatever its N: S/dP and the accumulations are issued by
-      // two different threads so that the tensor pipe sees both streams.  buf_free[b] orders the reuse of buffer b:
-      // S, dP of half hx+2 may overwrite it once the accumulation MMAs of half hx (which read dS from it) have completed.
+      // buf_free[b] orders the reuse of buffer b: S, dP of half hx+2 may overwrite it once the accumulation MMAs of half hx
+      // (which read dS from it) have completed.
       for (int hx = 0; hx < n_half; ++hx) {
         if (hx >= 2 && !mbar_wait(&buf_free[hx & 1], ((hx - 2) >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) goto done;
-        if (!issue_sdp(hx)) goto done;
+        if (!issue_one(hx)) goto done;
       }
     }
   } else if (warp == ACC_WARP) {
@@ -353,7 +351,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     mbar_init(fixed_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&qd_full[s], 1); mbar_init(&qd_empty[s], 1);
-      mbar_init(&sdp_full[s], 1); mbar_init(&ds_full[s], 4); mbar_init(&buf_free[s], 1);
+      mbar_init(&sdp_full[s], 2); mbar_init(&ds_full[s], 4); mbar_init(&buf_free[s], 1);
     }
     mbar_init(acc_done, 1);
     *abort_flag = 0;
@@ -389,33 +387,30 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == DP_WARP) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(BT, HB, 0, 0);       // Sᵀ = K·Qᵀ, dPᵀ = V·dOᵀ (64 queries)
+      // Sᵀ = K·Qᵀ by warp 1, dPᵀ = V·dOᵀ by warp DP_WARP (64 queries per half); see the dQ kernel
+      const bool is_dp = warp == DP_WARP;
+      constexpr uint32_t idesc_s = make_idesc_bf16(BT, HB, 0, 0);
       if (!mbar_wait(fixed_full, 0, abort_flag, p.status, STATUS_TIMEOUT_FULL)) goto done;
-      const uint32_t ska = smem_u32(sk), sva = smem_u32(sv);
-      auto issue_sdp = [&](int hx) -> bool {
+      const uint32_t sa = smem_u32(is_dp ? sv : sk);
+      auto issue_one = [&](int hx) -> bool {
         const int it = hx >> 1, hf = hx & 1, st = it & 1, buf = hx & 1;
         if (hf == 0 && !mbar_wait(&qd_full[st], (it >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
         tc_fence_after();
-        const uint32_t sqa = smem_u32(ring + st * 2 * SM::TILE) + hf * 8192, sdoa = sqa + SM::TILE;
-        const uint32_t ts = tmem_base + buf * 128, tdp = ts + 64;
+        const uint32_t sb = smem_u32(ring + st * 2 * SM::TILE) + hf * 8192 + (is_dp ? SM::TILE : 0);
+        const uint32_t td = tmem_base + buf * 128 + (is_dp ? 64 : 0);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k / 4) * CHUNK_BYTES + (k % 4) * 32;
-          umma_bf16(ts, make_smem_desc(ska + off, 16, 1024), make_smem_desc(sqa + off, 16, 1024), idesc_s, k != 0);
-        }
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k / 4) * CHUNK_BYTES + (k % 4) * 32;
-          umma_bf16(tdp, make_smem_desc(sva + off, 16, 1024), make_smem_desc(sdoa + off, 16, 1024), idesc_s, k != 0);
+          umma_bf16(td, make_smem_desc(sa + off, 16, 1024), make_smem_desc(sb + off, 16, 1024), idesc_s, k != 0);
         }
         umma_commit(&sdp_full[buf]);
         return true;
       };
-      for (int hx = 0; hx < n_half; ++hx) {       // see the dQ kernel: two issuing threads, buf_free orders buffer reuse
+      for (int hx = 0; hx < n_half; ++hx) {
         if (hx >= 2 && !mbar_wait(&buf_free[hx & 1], ((hx - 2) >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) goto done;
-        if (!issue_sdp(hx)) goto done;
+        if (!issue_one(hx)) goto done;
       }
     }
   } else if (warp == ACC_WARP) {
