@@ -245,7 +245,7 @@ def run_ours(args) -> None:
 
 def run_reference(args) -> None:
     ref = os.path.join(ROOT, "baseline", "_ref")
-    why = ("reference is not installable offline: /root/reference has neither setup.py nor pyproject.toml "
+    why = ("reference is not installable offline: its tree has neither setup.py nor pyproject.toml "
            "(pip: 'Directory is not installable'), and its imports lightning, transformer_engine, sonicmoe, "
            "mamba_ssm, causal_conv1d, jsonargparse, blobfile, flash_attn.cute are not in the image")
     if os.path.isdir(ref) and os.listdir(ref):
