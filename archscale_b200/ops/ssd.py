@@ -6,7 +6,7 @@ per head ``h`` with scalar decay ``A_h < 0``:
     S_t = exp(dt_t·A_h)·S_{t-1} + dt_t · x_t ⊗ B_t ;   y_t = S_t C_t + D_h·x_t
 
 x:(B,L,H,P) dt:(B,L,H) (after softplus+bias) A:(H,) B,C:(B,L,G,N) D:(H,).  ``seq_idx`` resets
-the state at document boundaries.  Chunked (256) matmul form below is differentiable.
+the state at document boundaries.  The chunked matmul form below is differentiable.
 """
 from __future__ import annotations
 
@@ -38,42 +38,67 @@ def ssd_scan_ref(x, dt, A, B, C, D=None, seq_idx: Optional[torch.Tensor] = None)
     return y.to(dtype)
 
 
-def ssd_scan(x, dt, A, B, C, D=None, seq_idx: Optional[torch.Tensor] = None, chunk: int = 128):
-    """Chunked quadratic-within-chunk / recurrent-across-chunk form (differentiable)."""
+def ssd_scan(x, dt, A, B, C, D=None, seq_idx: Optional[torch.Tensor] = None, chunk: int = 64):
+    """Chunked form, vectorised over the chunks: the quadratic work inside a chunk and the chunk summaries are batched
+    matmuls over all chunks at once; only the (B,H,P,N) state is carried from chunk to chunk in a short loop of
+    element-wise updates.  Differentiable; equals :func:`ssd_scan_ref`."""
     dtype = x.dtype
     x, dt, B, C = x.float(), dt.float(), B.float(), C.float()
     Bb, L, H, P = x.shape
     G, N = B.shape[2], B.shape[3]
-    Bh = B.repeat_interleave(H // G, dim=2)
-    Ch = C.repeat_interleave(H // G, dim=2)
-    la = dt * A.float().view(1, 1, H)                                   # log decay per step
+    pad = (-L) % chunk
     if seq_idx is not None:
         brk = torch.zeros(Bb, L, dtype=torch.bool, device=x.device)
         brk[:, 1:] = seq_idx[:, 1:] != seq_idx[:, :-1]
     else:
-        brk = torch.zeros(Bb, L, dtype=torch.bool, device=x.device)
+        brk = None
+    if pad:
+        # padded steps have dt = 0: they neither decay nor write the state, and their outputs are cut off
+        x, B, C = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (x, B, C))
+        dt = F.pad(dt, (0, 0, 0, pad))
+        if brk is not None:
+            brk = F.pad(brk, (0, pad))
+    Lp = L + pad
+    nC, c = Lp // chunk, chunk
+    xb = (x * dt.unsqueeze(-1)).view(Bb, nC, c, H, P)
+    la = (dt * A.float().view(1, 1, H)).view(Bb, nC, c, H).permute(0, 1, 3, 2)          # (B,nC,H,c) log decay per step
+    cs = torch.cumsum(la, dim=-1)                                                        # inclusive, inside the chunk
+    tril = torch.tril(torch.ones(c, c, dtype=torch.bool, device=x.device))
+    if brk is not None:
+        bc = torch.cumsum(brk.view(Bb, nC, c).to(torch.int32), dim=-1)                   # breaks so far inside the chunk
+        same = (bc.unsqueeze(-1) == bc.unsqueeze(-2)) & tril                              # (B,nC,c,c): j reaches i
+        first = (bc == 0)                                                                 # still the segment entering the chunk
+        last_same = same[:, :, -1]                                                        # (B,nC,c): steps of the last segment
+    else:
+        same = tril.view(1, 1, c, c)
+        first = last_same = None
+    # inside a chunk: y_i = Σ_{j≤i} (C_i·B_j) · exp(cs_i − cs_j) · dt_j x_j
+    dec = cs.unsqueeze(-1) - cs.unsqueeze(-2)                                            # (B,nC,H,c,c)
+    w = torch.exp(dec.masked_fill(~same.unsqueeze(2), float("-inf")))
+    Bh = B.view(Bb, nC, c, G, N)
+    Ch = C.view(Bb, nC, c, G, N)
+    cb = torch.einsum("bnigk,bnjgk->bngij", Ch, Bh)                                      # (B,nC,G,c,c)
+    rep = H // G
+    wg = w.view(Bb, nC, G, rep, c, c) * cb.unsqueeze(3)
+    y = torch.einsum("bngrij,bnjgrp->bnigrp", wg, xb.view(Bb, nC, c, G, rep, P)).reshape(Bb, nC, c, H, P)
+    # chunk summaries: what each chunk adds to the state by its end, and how much of the entering state survives it
+    wl = torch.exp(cs[..., -1:] - cs)                                                    # (B,nC,H,c)
+    carry = torch.exp(cs)                                                                # decay from the chunk start to step i
+    if brk is not None:
+        wl = wl * last_same.unsqueeze(2)
+        carry = carry * first.unsqueeze(2)
+    add = torch.einsum("bngrj,bnjgrp,bnjgk->bngrpk", wl.view(Bb, nC, G, rep, c), xb.view(Bb, nC, c, G, rep, P), Bh)
+    add = add.reshape(Bb, nC, H, P, N)
+    keep = carry[..., -1]                                                                # (B,nC,H)
     S = x.new_zeros(Bb, H, P, N)
-    outs = []
-    for s in range(0, L, chunk):
-        e = min(s + chunk, L)
-        t = e - s
-        l = la[:, s:e].permute(0, 2, 1)                                 # B H t
-        cs = torch.cumsum(l, dim=-1)
-        bc = torch.cumsum(brk[:, s:e].to(torch.int32), dim=-1)          # B t (breaks so far, inclusive)
-        same = (bc.unsqueeze(-1) == bc.unsqueeze(-2)) & torch.tril(
-            torch.ones(t, t, dtype=torch.bool, device=x.device)).unsqueeze(0)
-        w = torch.exp((cs.unsqueeze(-1) - cs.unsqueeze(-2)).masked_fill(~same.unsqueeze(1), float("-inf")))
-        xb = x[:, s:e] * dt[:, s:e].unsqueeze(-1)                       # B t H P
-        cb = torch.einsum("bihn,bjhn->bhij", Ch[:, s:e], Bh[:, s:e]) * w
-        y = torch.einsum("bhij,bjhp->bihp", cb, xb)
-        carry = torch.exp(cs) * (bc == 0).unsqueeze(1)                  # B H t
-        y = y + torch.einsum("bhpn,bihn,bhi->bihp", S, Ch[:, s:e], carry)
-        outs.append(y)
-        # state at the end of the chunk
-        last_same = same[:, -1]                                         # B t : steps in the last segment
-        wl = torch.exp((cs[:, :, -1:] - cs).masked_fill(~last_same.unsqueeze(1), float("-inf")))
-        S = S * carry[:, :, -1].view(Bb, H, 1, 1) + torch.einsum("bhj,bjhp,bjhn->bhpn", wl, xb, Bh[:, s:e])
-    y = torch.cat(outs, dim=1)
+    states = []
+    for n in range(nC):                                                                  # the only sequential part
+        states.append(S)
+        S = S * keep[:, n].view(Bb, H, 1, 1) + add[:, n]
+    S_in = torch.stack(states, dim=1)                                                    # state entering each chunk
+    y = y + torch.einsum("bngrpk,bnigk,bngri->bnigrp", S_in.view(Bb, nC, G, rep, P, N), Ch,
+                         carry.view(Bb, nC, G, rep, c)).reshape(Bb, nC, c, H, P)
+    y = y.reshape(Bb, Lp, H, P)[:, :L]
     if D is not None:
-        y = y + x * D.float().view(1, 1, H, 1)
+        y = y + x[:, :L] * D.float().view(1, 1, H, 1)
     return y.to(dtype)
