@@ -171,7 +171,8 @@ int b200_grouped_gemm2_bf16(int kind, const void* A, const void* B, void* out, c
                             int capacity, int M, int N, int K, int out_f32, int accumulate, int num_sms,
                             int* status, cudaStream_t stream);
 int b200_gemm2_bf16_batched(int mode, const void* A, const void* B, void* out, const void* cin, int batch, int M,
-                            int N, int K, float alpha, float beta, int symmetric, int num_sms, int* status, cudaStream_t stream);
+                            int N, int K, float alpha, float beta, const float* alpha_vec, const float* beta_vec, int symmetric,
+                            int num_sms, int* status, cudaStream_t stream);
 
 // One pass of the chunked gated-delta-rule recurrence (gdn_chunk.cu)
 int b200_gdn_state(const void* a_op, const void* c_add, const void* bm_op, const void* e_op, const void* f_op,

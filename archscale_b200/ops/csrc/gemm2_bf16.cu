@@ -41,6 +41,8 @@ struct Group2Params {
   const int* offsets;
   int E;
   int b_rows;           // rows of one expert's matrix inside B (GROUPED 1)
+  const float* alpha_vec;   // GROUPED 3: optional per-problem factors multiplied into alpha / beta (device arrays of E floats)
+  const float* beta_vec;
   int sym;              // GROUPED 3, square outputs known to be symmetric (X·Xᵀ, polynomials of a symmetric matrix): only the
                         // tiles on and above the diagonal are computed, an off-diagonal tile is also stored transposed
 };
@@ -295,6 +297,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
       tc_fence_after();
       const int row = m0 + rank * T2_HALF + q * 32 + lane;
+      const float alpha = (GROUPED == 3 && gp.alpha_vec) ? p.alpha * gp.alpha_vec[tl.b_row] : p.alpha;
+      const float beta = (GROUPED == 3 && gp.beta_vec) ? p.beta * gp.beta_vec[tl.b_row] : p.beta;
       int acc_flag = p.accumulate;
       uint32_t* sem = nullptr;
       if (OUT_F32 && SK > 1) {
@@ -335,8 +339,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
               if (col + j < p.N) {
-                float4 v = make_float4(__uint_as_float(r[j]) * p.alpha, __uint_as_float(r[j + 1]) * p.alpha,
-                                       __uint_as_float(r[j + 2]) * p.alpha, __uint_as_float(r[j + 3]) * p.alpha);
+                float4 v = make_float4(__uint_as_float(r[j]) * alpha, __uint_as_float(r[j + 1]) * alpha,
+                                       __uint_as_float(r[j + 2]) * alpha, __uint_as_float(r[j + 3]) * alpha);
                 if (acc_flag) {
                   const float4 old = *reinterpret_cast<const float4*>(o + j);
                   v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
@@ -352,14 +356,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
               if (col + j < p.N) {
                 float f[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[j + e]) * p.alpha;
+                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[j + e]) * alpha;
                 if (ci) {
                   const uint4 cv = *reinterpret_cast<const uint4*>(ci + j);
                   const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
 #pragma unroll
                   for (int e = 0; e < 4; ++e) {
                     const float2 c2 = unpack_bf16x2(cw[e]);
-                    f[2 * e] += p.beta * c2.x; f[2 * e + 1] += p.beta * c2.y;
+                    f[2 * e] += beta * c2.x; f[2 * e + 1] += beta * c2.y;
                   }
                 }
                 uint4 ov;
@@ -480,7 +484,7 @@ extern "C" int b200_grouped_gemm2_bf16(int kind, const void* A, const void* B, v
   }
   CUtensorMap ta, tb;
   int rc;
-  Group2Params gp{offsets, E, 0, 0};
+  Group2Params gp{offsets, E, 0, nullptr, nullptr, 0};
   if (kind == 0 || kind == 1) {
     if (N % T2_BN) return -1;
     rc = make_tmap_2d_bf16(&ta, A, K, capacity, K, T2_BK, T2_HALF);
@@ -507,10 +511,11 @@ extern "C" int b200_grouped_gemm2_bf16(int kind, const void* A, const void* B, v
 }
 
 // Batched GEMM, same contract as b200_gemm_bf16_batched; `symmetric`: the (square) results are symmetric matrices (and so is C),
-// compute the upper triangle of tiles only and mirror it.
+// compute the upper triangle of tiles only and mirror it.  alpha_vec / beta_vec (device, `batch` floats, or null): per-problem
+// factors multiplied into alpha / beta.
 extern "C" int b200_gemm2_bf16_batched(int mode, const void* A, const void* B, void* out, const void* cin, int batch, int M,
-                                       int N, int K, float alpha, float beta, int symmetric, int num_sms, int* status,
-                                       cudaStream_t stream) {
+                                       int N, int K, float alpha, float beta, const float* alpha_vec, const float* beta_vec,
+                                       int symmetric, int num_sms, int* status, cudaStream_t stream) {
   using namespace b200;
   if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return 0;
   if (mode < 0 || mode > 2) return -4;
@@ -530,7 +535,7 @@ extern "C" int b200_gemm2_bf16_batched(int mode, const void* A, const void* B, v
   if (rc) return rc;
   Gemm2Params p{out, cin, M, N, K, N, alpha, beta, 0, status, 1, nullptr};
   if (symmetric && M != N) return -1;
-  Group2Params gp{nullptr, batch, 0, symmetric};
+  Group2Params gp{nullptr, batch, 0, alpha_vec, beta_vec, symmetric};
   const int nm = (M + T2_BM - 1) / T2_BM;
   const int tiles = batch * (symmetric ? nm * (nm + 1) / 2 : nm * ((N + T2_BN - 1) / T2_BN));
   if (mode == 0) return launch2_grouped<0, 0, 0, 3>(ta, tb, p, gp, tiles, num_sms, stream);

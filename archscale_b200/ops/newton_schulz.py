@@ -80,20 +80,32 @@ def _ns_cuda_batched(G: torch.Tensor, epsilon: float, coeffs=None) -> torch.Tens
     ext = backend.require_extension()
     X = G.to(torch.bfloat16)
     tall = G.size(-2) > G.size(-1)
-    in_place_tall = tall and hasattr(ext, "gemm_pair") and ext.gemm_pair()
+    pair = hasattr(ext, "gemm_pair") and ext.gemm_pair()
+    in_place_tall = tall and pair
     if tall and not in_place_tall:
         X = X.mT
-    X = (X / (X.norm(dim=(-2, -1), keepdim=True) + epsilon)).contiguous()
-    for a, b, c in NS_COEFFS:
+    X = X.contiguous()
+    # X₀ = G·s with s = 1 / (‖G‖ + ε).  The two-CTA kernel takes per-matrix factors, so the scaled copy is never made: the
+    # first iteration multiplies s² into the Gram product and s (and a·s) into the update of the unscaled matrices.
+    s_vec = 1.0 / (torch.linalg.vector_norm(X, dim=(-2, -1), dtype=torch.float32) + epsilon)
+    s2_vec = None
+    if pair:
+        s2_vec = (s_vec * s_vec).contiguous()
+        s_vec = s_vec.contiguous()
+    else:
+        X = (X * s_vec.view(-1, 1, 1).to(X.dtype)).contiguous()
+    for it, (a, b, c) in enumerate(NS_COEFFS):
+        first = pair and it == 0
+        av, sv = (s2_vec, s_vec) if first else (None, None)
         # the Gram matrix and the polynomial in it are symmetric: the kernel computes the upper triangle of tiles and mirrors it
         if in_place_tall:
-            A = ext.gemm_bf16_batched(X, X, 2, 1.0, 0.0, None, True)
+            A = ext.gemm_bf16_batched(X, X, 2, 1.0, 0.0, None, True, av, None)
             Bm = ext.gemm_bf16_batched(A, A, 0, c, b, A, True)
-            X = ext.gemm_bf16_batched(X, Bm, 1, 1.0, a, X)
+            X = ext.gemm_bf16_batched(X, Bm, 1, 1.0, a, X, False, sv, sv)
         else:
-            A = ext.gemm_bf16_batched(X, X, 0, 1.0, 0.0, None, True)
+            A = ext.gemm_bf16_batched(X, X, 0, 1.0, 0.0, None, True, av, None)
             Bm = ext.gemm_bf16_batched(A, A, 0, c, b, A, True)
-            X = ext.gemm_bf16_batched(Bm, X, 1, 1.0, a, X)
+            X = ext.gemm_bf16_batched(Bm, X, 1, 1.0, a, X, False, sv, sv)
         backend.count_launch(3)
     return X.mT if (tall and not in_place_tall) else X
 

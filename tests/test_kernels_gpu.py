@@ -334,3 +334,23 @@ def test_batched_symmetric_product_matches_full_product(Bn, M, K):
     assert _rel(poly, ref2) < 1e-2
     torch.cuda.synchronize()
     assert _ext().device_status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_batched_gemm_per_matrix_factors(mode):
+    """alpha_vec / beta_vec multiply into alpha / beta per matrix of the batch (first Newton–Schulz iteration on unscaled data)."""
+    torch.manual_seed(13)
+    Bn, M, N, K = 4, 384, 512, 320
+    a = (torch.randn(Bn, M, K, device="cuda") * 0.2).bfloat16()
+    b = (torch.randn(Bn, N, K, device="cuda") * 0.2).bfloat16()
+    c = torch.randn(Bn, M, N, device="cuda").bfloat16()
+    av = torch.rand(Bn, device="cuda") + 0.5
+    bv = torch.rand(Bn, device="cuda") - 0.5
+    aa = a if mode != 2 else a.transpose(1, 2).contiguous()
+    bb = b if mode == 0 else b.transpose(1, 2).contiguous()
+    out = _ext().gemm_bf16_batched(aa, bb, mode, 0.5, 2.0, c, False, av, bv)
+    ref = 0.5 * av.view(-1, 1, 1) * (a.float() @ b.float().transpose(1, 2)) + 2.0 * bv.view(-1, 1, 1) * c.float()
+    torch.cuda.synchronize()
+    assert _ext().device_status() == 0
+    assert _rel(out, ref) < 1e-2
