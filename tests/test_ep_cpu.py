@@ -9,6 +9,17 @@ from archscale_b200.ops.moe import moe_ffn_ref, router_topk_softmax_ref
 from archscale_b200.parallel.ep import moe_ffn_expert_parallel
 
 
+
+def _leave_together():
+    """Ranks leave the process group together: a rank that closes its sockets while a peer is still inside its last
+    collective's teardown can abort that peer."""
+    import datetime
+    try:
+        dist.monitored_barrier(timeout=datetime.timedelta(seconds=30))
+    except Exception:
+        pass
+    dist.destroy_process_group()
+
 def _make(world, N=24, C=16, E=8, I=8, K=2):
     g = torch.Generator().manual_seed(0)
     x = torch.randn(world, N, C, generator=g)
@@ -35,7 +46,7 @@ def _worker(rank, world, port, q):
         out.backward(gout[rank])
         q.put((rank, out.detach(), xr.grad, wi.grad, wo.grad, lg.grad))
     finally:
-        dist.destroy_process_group()
+        _leave_together()
 
 
 def test_expert_parallel_matches_oracle():

@@ -23,6 +23,17 @@ from archscale_b200.parallel.mesh import build_mesh
 from archscale_b200.utils import checkpoint as ckpt
 
 
+
+def _leave_together():
+    """Ranks leave the process group together: a rank that closes its sockets while a peer is still inside its last
+    collective's teardown can abort that peer."""
+    import datetime
+    try:
+        dist.monitored_barrier(timeout=datetime.timedelta(seconds=30))
+    except Exception:
+        pass
+    dist.destroy_process_group()
+
 def _cfg(**kw):
     base = dict(n_layer=2, ar=None, n_embd=256, n_head=2, n_query_groups=1, head_dim=128, intermediate_size=1024,
                 vocab_size=32000, padding_multiple=64, block_size=512, rope_base=10000, norm_eps=1e-5)
@@ -84,7 +95,7 @@ def _worker(rank, world, port, tmp, q):
         else:
             assert ok_bitwise
     finally:
-        dist.destroy_process_group()
+        _leave_together()
 
 
 def test_config1_two_ranks_ten_steps_save_reload_bitwise():
@@ -113,7 +124,7 @@ def _worker_equiv(rank, world, port, q):
         if rank == 0:
             q.put(losses)
     finally:
-        dist.destroy_process_group()
+        _leave_together()
 
 
 def test_two_ranks_match_single_process_muonh():

@@ -16,6 +16,17 @@ from archscale_b200.parallel.mesh import Mesh, build_mesh
 
 
 
+
+def _leave_together():
+    """Ranks leave the process group together: a rank that closes its sockets while a peer is still inside its last
+    collective's teardown can abort that peer."""
+    import datetime
+    try:
+        dist.monitored_barrier(timeout=datetime.timedelta(seconds=30))
+    except Exception:
+        pass
+    dist.destroy_process_group()
+
 def _free_port() -> int:
     import socket
     with socket.socket() as sk:
@@ -77,7 +88,7 @@ def _worker(rank, world, port, q):
         if rank == 0:
             q.put((losses, norms))
     finally:
-        dist.destroy_process_group()
+        _leave_together()
 
 
 def test_tp2_matches_single_process():
