@@ -13,7 +13,7 @@ Role of `lit_gpt/optim/muon.py:27-650` + `scalar_opts.py:380-443` + `pretrain.py
   the shards → MuonH norms are partial sums over local slices + **two** tiny all-reduces for the
   whole model (the reference issues three per parameter batch);
 * expert tensors ``(E, out, in)`` are E independent matrices; each keeps its own norm under
-  MuonH (the reference normalises the local slab as a whole — see DESIGN notes);
+  MuonH (the reference normalises the local slab as a whole, which makes the result depend on the expert-parallel degree);
 * state (``momentum``, ``variance``) lives in fp32 buffers aligned with the master shards, so
   checkpoints consolidate it with the same gather as the weights.
 
@@ -443,9 +443,10 @@ class ShardedOptimizer:
                 if gid not in store:
                     continue
                 full = eng._gather_master(store[gid], g)
-                if keep:
-                    for s in g.specs:
-                        state.setdefault(s.name, {})[key] = full[s.offset:s.offset + s.numel].view(s.shape).cpu().clone()
+                for s in g.specs:
+                    t = eng.consolidate(s, g, full)       # whole tensors: tp slices reassembled, ep slabs concatenated
+                    if keep:
+                        state.setdefault(s.name, {})[key] = t.cpu().clone()
                 del full
         return {"state": state, "step": self.step_count, "algorithm": self.algorithm} if keep else {}
 
@@ -461,4 +462,4 @@ class ShardedOptimizer:
                     continue
                 for key, store in (("momentum", self.m), ("variance", self.v)):
                     if key in st and gid in store:
-                        store[gid][slo:slo + hi - lo].copy_(st[key].reshape(-1)[lo:hi].to(torch.float32))
+                        store[gid][slo:slo + hi - lo].copy_(self.engine.localize(s, g, st[key])[lo:hi].to(torch.float32))

@@ -628,21 +628,65 @@ class FSDPEngine:
         return total
 
     # -- checkpoint support ----------------------------------------------------------
+    # Checkpoints hold WHOLE tensors under the model's own key names, whatever the parallel layout that wrote them:
+    # flat shards are gathered over the shard group, tensor-parallel slices are reassembled over the tp group (undoing
+    # the gate | up block cut), expert-parallel slabs are concatenated over the ep group.  Loading cuts the whole tensor
+    # the same way for this rank.  The optimizer's per-parameter state goes through the same two functions.
+    def consolidate(self, spec: ParamSpec, g: FlatGroup, full_flat: torch.Tensor) -> torch.Tensor:
+        """Whole tensor of ``spec`` from the group's gathered flat buffer (collective over tp / ep groups)."""
+        t = full_flat[spec.offset:spec.offset + spec.numel].view(spec.shape)
+        split = getattr(spec.param, "_tp_split", None)
+        if split is not None and self.mesh.tp > 1:
+            from .tp import tp_assemble
+            parts = [torch.empty_like(t) for _ in range(self.mesh.tp)]
+            torch.distributed.all_gather(parts, t.contiguous(), group=self.mesh.tp_group)
+            t = tp_assemble(parts, split)
+        if getattr(g, "ep_local", False) and self.mesh.ep > 1:
+            # every rank owns different experts: concatenate the slabs along the expert dim
+            parts = [torch.empty_like(t) for _ in range(self.mesh.ep)]
+            torch.distributed.all_gather(parts, t.contiguous(), group=self.mesh.ep_group)
+            t = torch.cat(parts, dim=0)
+        return t
+
+    def localize(self, spec: ParamSpec, g: FlatGroup, t: torch.Tensor) -> torch.Tensor:
+        """This rank's (tp / ep-local) tensor of ``spec``, flattened, from a whole checkpoint tensor; raises when the
+        checkpoint tensor has neither the whole nor the local number of elements."""
+        split = getattr(spec.param, "_tp_split", None)
+        tp_on = split is not None and self.mesh.tp > 1
+        ep_on = getattr(g, "ep_local", False) and self.mesh.ep > 1
+        whole = list(spec.shape)
+        if tp_on:
+            whole[split[0]] *= self.mesh.tp
+        if ep_on:
+            whole[0] *= self.mesh.ep
+        n_whole = 1
+        for d in whole:
+            n_whole *= d
+        if t.numel() == n_whole and (tp_on or ep_on):
+            t = t.reshape(whole)
+            if ep_on:
+                n_local = whole[0] // self.mesh.ep
+                t = t[self.mesh.ep_rank * n_local:(self.mesh.ep_rank + 1) * n_local]
+            if tp_on:
+                from .tp import tp_slice
+                t = tp_slice(t, split, self.mesh.tp, self.mesh.tp_rank)
+        elif t.numel() != spec.numel:
+            raise ValueError(f"checkpoint tensor {spec.name} has {t.numel()} elements; expected {n_whole} (whole) "
+                             f"or {spec.numel} (this rank's slice)")
+        elif tp_on or ep_on:
+            raise ValueError(f"checkpoint tensor {spec.name} holds one rank's slice ({t.numel()} elements), not the whole "
+                             f"tensor ({n_whole}); it was written by a version that did not consolidate tp / ep slices")
+        return t.reshape(-1)
+
     @torch.no_grad()
     def full_state_dict(self, rank0_only: bool = True, dtype: Optional[torch.dtype] = None) -> Dict[str, torch.Tensor]:
-        """Consolidated fp32 (or ``dtype``) state dict with the model's own key names, on CPU."""
+        """Consolidated fp32 (or ``dtype``) state dict with the model's own key names and whole-model shapes, on CPU."""
         out: Dict[str, torch.Tensor] = {}
         keep = (not rank0_only) or self.mesh.rank == 0
         for g in self.groups():
             full = self._gather_master(g.master, g)
-            ep = getattr(g, "ep_local", False) and self.mesh.ep > 1
             for s in g.specs:
-                t = full[s.offset:s.offset + s.numel].view(s.shape)
-                if ep:
-                    # every rank owns different experts: concatenate the slabs along the expert dim
-                    parts = [torch.empty_like(t) for _ in range(self.mesh.ep)]
-                    torch.distributed.all_gather(parts, t.contiguous(), group=self.mesh.ep_group)
-                    t = torch.cat(parts, dim=0)
+                t = self.consolidate(s, g, full)
                 if keep:
                     out[s.name] = (t.to(dtype) if dtype else t).cpu().clone()
             del full
@@ -667,16 +711,11 @@ class FSDPEngine:
     def load_full_state_dict(self, sd: Dict[str, torch.Tensor], strict: bool = True) -> None:
         missing = []
         for g in self.groups():
-            a, b = g.shard_range()
             for s, lo, hi, slo in g.local_slices():
                 if s.name not in sd:
                     missing.append(s.name)
                     continue
-                t = sd[s.name]
-                if getattr(g, "ep_local", False) and self.mesh.ep > 1:
-                    n_local = s.shape[0]
-                    t = t[self.mesh.ep_rank * n_local:(self.mesh.ep_rank + 1) * n_local]
-                src = t.reshape(-1)[lo:hi]
+                src = self.localize(s, g, sd[s.name])[lo:hi]
                 g.master[slo:slo + hi - lo].copy_(src.to(torch.float32))
             g.lp_stale = True
         if strict and missing:

@@ -113,11 +113,42 @@ class RowParallelLinear(Linear):
         return y
 
 
-def _new_param(t: torch.Tensor, like: nn.Parameter, sharded: bool) -> nn.Parameter:
+def _new_param(t: torch.Tensor, like: nn.Parameter, sharded: bool, split=None) -> nn.Parameter:
+    """``split = (dim, blocks)`` records how the slice was cut from the whole tensor (checkpoints undo it):
+    along ``dim``; for dim 0, ``blocks`` equal row blocks (gate | up) were each cut into ``tp`` pieces."""
     p = nn.Parameter(t.detach().clone().contiguous(), requires_grad=like.requires_grad)
     if sharded:
         p._tp_sharded = True
+        p._tp_split = split if split is not None else (0, 1)
     return p
+
+
+def tp_whole_shape(local_shape, split, tp: int):
+    shape = list(local_shape)
+    shape[split[0]] *= tp
+    return torch.Size(shape)
+
+
+def tp_assemble(parts, split) -> torch.Tensor:
+    """Inverse of the physical slicing: ``parts`` are the ``tp`` ranks' slices in rank order."""
+    dim, blocks = split
+    if dim != 0 or blocks == 1:
+        return torch.cat(parts, dim=dim)
+    sl = parts[0].shape[0] // blocks
+    rest = parts[0].shape[1:]
+    return torch.cat([t.reshape(blocks, sl, *rest) for t in parts], dim=1).reshape(blocks * sl * len(parts), *rest)
+
+
+def tp_slice(whole: torch.Tensor, split, tp: int, r: int) -> torch.Tensor:
+    """This rank's slice of a whole (unsplit) tensor, cut the way :func:`apply_tensor_parallel` cuts it."""
+    dim, blocks = split
+    if dim != 0 or blocks == 1:
+        n = whole.shape[dim] // tp
+        return whole.narrow(dim, r * n, n)
+    per = whole.shape[0] // blocks
+    sl = per // tp
+    rest = whole.shape[1:]
+    return whole.reshape(blocks, per, *rest)[:, r * sl:(r + 1) * sl].reshape(blocks * sl, *rest)
 
 
 def _split_rows(lin: Linear, tp: int, r: int, blocks: int = 1) -> None:
@@ -127,10 +158,10 @@ def _split_rows(lin: Linear, tp: int, r: int, blocks: int = 1) -> None:
     assert per % tp == 0, f"{out_f} output features in {blocks} block(s) do not divide over tp={tp}"
     sl = per // tp
     w = lin.weight.view(blocks, per, in_f)[:, r * sl:(r + 1) * sl].reshape(blocks * sl, in_f)
-    lin.weight = _new_param(w, lin.weight, True)
+    lin.weight = _new_param(w, lin.weight, True, (0, blocks))
     if lin.bias is not None:
         b = lin.bias.view(blocks, per)[:, r * sl:(r + 1) * sl].reshape(-1)
-        lin.bias = _new_param(b, lin.bias, True)
+        lin.bias = _new_param(b, lin.bias, True, (0, blocks))
     lin.out_features = blocks * sl
 
 
@@ -141,7 +172,7 @@ def _to_row_parallel(lin: Linear, tp: int, r: int, group) -> RowParallelLinear:
     new = RowParallelLinear.__new__(RowParallelLinear)
     nn.Module.__init__(new)
     new.in_features, new.out_features = sl, out_f
-    new.weight = _new_param(lin.weight[:, r * sl:(r + 1) * sl], lin.weight, True)
+    new.weight = _new_param(lin.weight[:, r * sl:(r + 1) * sl], lin.weight, True, (1, 1))
     new.bias = None if lin.bias is None else _new_param(lin.bias, lin.bias, False)
     new.mxfp8 = False
     new.tp_group = group
@@ -212,7 +243,7 @@ def apply_tensor_parallel(model: nn.Module, mesh: Mesh) -> None:
         attn.n_query_groups //= tp
         if hasattr(attn, "softmax_offset"):
             H = attn.softmax_offset.shape[0] // tp
-            attn.softmax_offset = _new_param(attn.softmax_offset[r * H:(r + 1) * H], attn.softmax_offset, True)
+            attn.softmax_offset = _new_param(attn.softmax_offset[r * H:(r + 1) * H], attn.softmax_offset, True, (0, 1))
         attn.proj = _to_row_parallel(attn.proj, tp, r, group)
         _wrap_gather_input(attn, group, model, attn.q_proj)
         _split_rows(mlp.w1, tp, r, blocks=1 if mlp.relu2 else 2)

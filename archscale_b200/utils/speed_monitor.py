@@ -50,6 +50,55 @@ def estimate_flops(config, n_params: float) -> float:
     return flops_per_param(config, n_params)
 
 
+def matmul_parameter_count(model, config, include_head: bool = False, tp: int = 1, ep: int = 1) -> float:
+    """Parameters that every token multiplies with, counted from the model that actually runs.
+
+    The reference feeds ``estimate_flops`` the analytic non-embedding law (`pretrain.py:744-751`,
+    `lit_gpt/config.py:232-265`), which hard-codes the 4·C MLP width; once a width is overridden
+    (e.g. SwiGLU hidden 5632 instead of 8192) the law over-counts, so the MFU printed here uses this
+    count instead.  Token embedding is a lookup (excluded); ``lm_head`` only with ``include_head``;
+    routed experts count by the fraction ``routed_top_k / routed_experts`` a token visits.  ``tp`` /
+    ``ep`` undo the physical slicing of tensor- / expert-parallel models (local shapes → whole model).
+    """
+    frac = 1.0
+    if getattr(config, "moe", False) and config.routed_experts > 0:
+        frac = config.routed_top_k / config.routed_experts
+    n = 0.0
+    for name, p in model.named_parameters():
+        if ".wte." in name or name.startswith("wte."):
+            continue
+        if "lm_head" in name:
+            if include_head:
+                n += p.numel()
+            continue
+        k = float(p.numel())
+        if getattr(p, "_tp_sharded", False):
+            k *= tp
+        if ".mods_in." in name or ".mods_out." in name:
+            k *= frac * (ep if getattr(p, "_ep_local", False) else 1)
+        n += k
+    return n
+
+
+def measured_peaks(root: Optional[str] = None) -> Dict[str, float]:
+    """Roofline denominators measured on this machine (``MEASURED_PEAKS.json`` beside the package's parent
+    directory) or the stated fallback (6.65 TB/s, 1.59 PFLOP/s burst, 1.4 PFLOP/s sustained)."""
+    import json
+    import os
+    root = root or os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "kind": "fallback"}
+    try:
+        with open(os.path.join(root, "MEASURED_PEAKS.json")) as fh:
+            d = json.load(fh)
+        for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+            if d.get(k):
+                out[k] = float(d[k])
+        out["kind"] = "measured"
+    except (OSError, ValueError):
+        pass
+    return out
+
+
 class SpeedMonitor:
     """Rolling-window throughput; call :meth:`on_train_batch_end` once per micro-batch."""
 

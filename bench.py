@@ -120,8 +120,7 @@ def run_ours(args) -> None:
     from archscale_b200.ops import backend
     from archscale_b200.parallel import dist_utils as du
     from archscale_b200.train.pretrain import setup
-    from archscale_b200.utils.speed_monitor import estimate_flops
-    from archscale_b200.config import get_parameters_count
+    from archscale_b200.utils.speed_monitor import estimate_flops, matmul_parameter_count, measured_peaks
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run"
@@ -212,8 +211,14 @@ def run_ours(args) -> None:
         phases = {"forward_backward_ms": fb / args.steps, "optimizer_step_ms": op / args.steps}
     status = backend.load_extension().device_status() if backend.load_extension() is not None else 0
 
-    n_law = get_parameters_count(trainer.plan.model_name, trainer.plan.depth, cfg, trainer.plan.train_config)
-    flops_step = estimate_flops(cfg, n_law) * mb
+    # MFU in the reference's convention (3·(2·N·T + attention over the full T×T square) per sequence, peak 2.25e15), but with N
+    # counted from the model that ran (non-embedding, routed experts by the fraction a token visits) instead of the analytic
+    # law, which assumes a 4·d_model MLP and over-counts the 5632-wide benchmark shape.
+    n_flops = matmul_parameter_count(trainer.model, cfg, include_head=False, tp=max(args.tp, 1), ep=ep)
+    n_flops_head = matmul_parameter_count(trainer.model, cfg, include_head=True, tp=max(args.tp, 1), ep=ep)
+    flops_step = estimate_flops(cfg, n_flops) * mb
+    flops_step_head = estimate_flops(cfg, n_flops_head) * mb
+    pk = measured_peaks(ROOT)
     if trainer.mesh.rank == 0:
         value = tokens_per_step / (ms_per_step / 1e3)
         out = {
@@ -223,13 +228,17 @@ def run_ours(args) -> None:
             "dtype": "mxfp8 linears (bf16 elsewhere)" if args.fp8 else "bf16", "data": "synthetic uniform-random token ids (seed 0), random-init weights",
             "tokens_per_sec_per_gpu": value / world,
             "mfu": flops_step / max(args.tp, 1) / (ms_per_step / 1e3) / 2.25e15,   # per GPU: tp peers share a micro-batch
+            "mfu_with_lm_head": flops_step_head / max(args.tp, 1) / (ms_per_step / 1e3) / 2.25e15,
+            "frac_of_sustained_bf16": flops_step_head / max(args.tp, 1) / (ms_per_step / 1e3) / (pk["bf16_tflops_sustained"] * 1e12),
+            "mfu_note": f"N = {n_flops:,.0f} non-embedding parameters of the shape that ran ({n_flops_head:,.0f} with lm_head); "
+                        f"sustained bf16 peak {pk['bf16_tflops_sustained']:.0f} TFLOP/s ({pk['kind']})",
             "config": {"model": c["name"], "global_batch": world * mb, "seq_len": T,
                        "parallelism": (f"fsdp{world // max(args.tp, 1)}" if world > 1 else "single") + (f"+ep{ep}" if ep > 1 else "")
                                       + (f"+tp{args.tp}" if args.tp > 1 else ""),
                        "optimizer": "MuonH (Newton-Schulz 5) + AdamW/Adam-H, grad clip 1.0",
                        "l2": "per-step working set (weights + activations, > 10 GB) far exceeds the 126 MB L2; "
                              "no explicit flush",
-                       "params": trainer.n_params_actual, "final_loss": losses[-1] if losses else None,
+                       "params": trainer.n_params_actual, "params_in_mfu": n_flops, "final_loss": losses[-1] if losses else None,
                        "device_status": int(status), "fused_comm": bool(args.fused_comm)},
             "clocks": clocks,
             **({"phases": phases} if phases else {}),

@@ -23,6 +23,9 @@ CASES = [
     (1, 1024, 2, 2, 64, 511, None),         # window 512, head_dim 64 (phi4-mini-flash shape)
     (1, 700, 4, 2, 128, -1, [0, 130, 131, 400, 700]),   # packed documents
     (1, 900, 2, 1, 64, 63, [0, 500, 900]),  # packed + window
+    (2, 2048, 4, 2, 128, -1, None),         # many key tiles per query-tile pair
+    (1, 1100, 2, 1, 128, 300, [0, 70, 610, 1100]),   # packed + window across tile pairs, odd number of query tiles
+    (1, 128, 2, 2, 128, -1, None),          # a single query tile: the second CTA of the pair has no rows
 ]
 
 
