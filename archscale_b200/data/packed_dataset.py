@@ -267,6 +267,7 @@ class PinnedBatchLoader:
         self._pin = torch.cuda.is_available() if pin is None else pin
         self._q: "queue.Queue" = queue.Queue(maxsize=prefetch)
         self._stop = threading.Event()
+        self._done = False      # the stream ended (or failed): every later __next__ raises again instead of blocking
         self._thread = threading.Thread(target=self._work, daemon=True)
         self._thread.start()
 
@@ -295,15 +296,20 @@ class PinnedBatchLoader:
         return self
 
     def __next__(self):
+        if self._done:
+            raise StopIteration
         item = self._q.get()
         if item is None:
+            self._done = True
             raise StopIteration
         if isinstance(item, BaseException):
+            self._done = True
             raise item
         return item
 
     def close(self) -> None:
         self._stop.set()
+        self._done = True
         try:
             while True:
                 self._q.get_nowait()

@@ -3,7 +3,7 @@ from . import backend  # noqa: F401
 from .activations import glu, swiglu, swiglu_packed, oss_swiglu_ref  # noqa: F401
 from .attention import attention, attention_ref  # noqa: F401
 from .conv1d import causal_conv1d, causal_conv1d_ref  # noqa: F401
-from .cross_entropy import (FusedCrossEntropyLoss, FusedLinearCrossEntropyLoss, cross_entropy_ref,  # noqa: F401
+from .cross_entropy import (FusedCrossEntropyLoss, FusedLinearCrossEntropyLoss, cross_entropy, cross_entropy_ref,  # noqa: F401
                             fused_linear_cross_entropy, fused_linear_cross_entropy_ref)
 from .gated_delta_rule import gated_delta_rule, gated_delta_rule_recurrent_ref  # noqa: F401
 from .gemm import linear, matmul_nn, matmul_nt, matmul_tn  # noqa: F401

@@ -156,6 +156,42 @@ class FusedLinearCrossEntropyLoss(torch.nn.Module):
                                           self.lse_square_scale)
 
 
+class _CEFn(torch.autograd.Function):
+    """Cross-entropy over materialised logits on the one-pass kernel (loss + dlogits in one read of the logits).  The
+    gradient is computed in the forward pass into a copy of the logits — the caller's logits tensor is left intact,
+    unlike the reference's in-place variant (`lit_gpt/fused_cross_entropy.py:29-150`, ``inplace_backward``)."""
+
+    @staticmethod
+    def forward(ctx, logits, target, ignore_index, label_smoothing, lse_square_scale, reduction):
+        need = logits.requires_grad
+        work = logits.detach().clone()       # the kernel overwrites its input with the gradient
+        loss_rows, dlogits = _ce_chunk_fwd_bwd(work, target, ignore_index, label_smoothing, lse_square_scale)
+        n_valid = (target != ignore_index).sum().clamp_min(1).to(torch.float32)
+        ctx.reduction = reduction
+        ctx.save_for_backward(dlogits if need else None, n_valid)
+        if reduction == "none":
+            return loss_rows
+        return loss_rows.sum() / n_valid if reduction == "mean" else loss_rows.sum()
+
+    @staticmethod
+    def backward(ctx, gout):
+        dlogits, n_valid = ctx.saved_tensors
+        if dlogits is None:
+            return (None,) * 6
+        if ctx.reduction == "none":
+            g = dlogits * gout.unsqueeze(1).to(dlogits.dtype)
+        else:
+            s = gout / n_valid if ctx.reduction == "mean" else gout
+            g = dlogits * s.to(dlogits.dtype)
+        return g, None, None, None, None, None
+
+
+def cross_entropy(logits: torch.Tensor, target: torch.Tensor, ignore_index: int = -100, label_smoothing: float = 0.0,
+                  lse_square_scale: float = 0.0, reduction: str = "mean") -> torch.Tensor:
+    """CE of ``logits`` (N, V) against ``target`` (N,) on ``csrc/cross_entropy.cu`` (PyTorch formulas on CPU)."""
+    return _CEFn.apply(logits.contiguous(), target, ignore_index, label_smoothing, lse_square_scale, reduction)
+
+
 class FusedCrossEntropyLoss(torch.nn.Module):
     """Plain CE over materialised logits (`lit_gpt/fused_cross_entropy.py:336-415`)."""
 
@@ -166,5 +202,5 @@ class FusedCrossEntropyLoss(torch.nn.Module):
         self.label_smoothing, self.lse_square_scale = label_smoothing, lse_square_scale
 
     def forward(self, logits: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
-        return cross_entropy_ref(logits.reshape(-1, logits.shape[-1]), target.reshape(-1), self.ignore_index,
-                                 self.label_smoothing, self.lse_square_scale, self.reduction)
+        return cross_entropy(logits.reshape(-1, logits.shape[-1]), target.reshape(-1), self.ignore_index,
+                             self.label_smoothing, self.lse_square_scale, self.reduction)

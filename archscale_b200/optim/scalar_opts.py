@@ -55,3 +55,33 @@ def lion_update_foreach(x: List[torch.Tensor], g: Sequence[torch.Tensor], m: Lis
     if weight_decay != 0.0:
         torch._foreach_mul_(x, 1 - lr * weight_decay)
     torch._foreach_add_(x, u, alpha=-lr)
+
+
+def nadam_mu(beta1: float, step: int, momentum_decay: float = 4e-3) -> float:
+    """Momentum coefficient of NAdam at ``step`` (1-based): ``beta1·(1 − 0.5·0.96^(step·momentum_decay))``."""
+    return beta1 * (1.0 - 0.5 * (0.96 ** (step * momentum_decay)))
+
+
+@torch.no_grad()
+def nadam_update_foreach(x: List[torch.Tensor], g: Sequence[torch.Tensor], m: List[torch.Tensor], v: List[torch.Tensor],
+                         lr: float, beta1: float, beta2: float, weight_decay: float, step: int, eps: float,
+                         mu_product: float, momentum_decay: float = 4e-3) -> float:
+    """NAdam with decoupled weight decay — the rule ``torch.optim.NAdam(decoupled_weight_decay=True)`` applies to the
+    weight matrices of the reference's ``hadam`` runs (`pretrain.py:646-654`).  ``mu_product`` is the running product
+    of the momentum coefficients of all earlier steps (1.0 before the first); the updated product is returned."""
+    mu = nadam_mu(beta1, step, momentum_decay)
+    mu_next = nadam_mu(beta1, step + 1, momentum_decay)
+    mu_product = mu_product * mu
+    if not x:
+        return mu_product
+    if weight_decay != 0.0:
+        torch._foreach_mul_(x, 1 - lr * weight_decay)
+    torch._foreach_lerp_(m, list(g), 1 - beta1)
+    torch._foreach_mul_(v, beta2)
+    torch._foreach_addcmul_(v, list(g), list(g), 1 - beta2)
+    denom = torch._foreach_sqrt(v)
+    torch._foreach_div_(denom, math.sqrt(1 - beta2 ** step))
+    torch._foreach_add_(denom, eps)
+    torch._foreach_addcdiv_(x, list(g), denom, value=-lr * (1.0 - mu) / (1.0 - mu_product))
+    torch._foreach_addcdiv_(x, m, denom, value=-lr * mu_next / (1.0 - mu_product * mu_next))
+    return mu_product

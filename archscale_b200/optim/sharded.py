@@ -55,11 +55,16 @@ class ShardedOptimizer:
                  eps: float = 1e-8, weight_decay: float = 0.0, vector_weight_decay: float = 0.0,
                  weight_lr_mult: float = 1.0, algorithm: str = "adamw", mu: float = 0.95, nesterov: bool = True,
                  adjust_lr: Optional[str] = "spectral_norm", ns_epsilon: float = 1e-8,
-                 hyperball_exclude: Sequence[str] = ("transformer.wte.weight",), split_groups: bool = True) -> None:
-        """algorithm: "adamw" | "muon" | "muonh" | "lion".  ``split_groups=False`` applies AdamW with
-        ``weight_decay`` to every parameter (the non-μP branch of the reference)."""
-        assert algorithm in ("adamw", "muon", "muonh", "lion")
+                 hyperball_exclude: Sequence[str] = ("transformer.wte.weight",), split_groups: bool = True,
+                 vector_betas: Optional[Tuple[float, float]] = None, vector_eps: Optional[float] = None) -> None:
+        """algorithm: "adamw" | "muon" | "muonh" | "lion" | "hadam".  ``split_groups=False`` applies AdamW with
+        ``weight_decay`` to every parameter (the non-μP branch of the reference).  "hadam" is the reference's
+        AdamW-for-vectors + NAdam-for-weights pair (`pretrain.py:646-654`): vectors use ``vector_betas`` /
+        ``vector_eps`` (default ``betas`` / ``eps``), weight matrices the NAdam rule with ``betas`` / ``eps``."""
+        assert algorithm in ("adamw", "muon", "muonh", "lion", "hadam")
         self.engine, self.lr, self.betas, self.eps = engine, lr, betas, eps
+        self.vector_betas, self.vector_eps = vector_betas, vector_eps
+        self.nadam_mu_product = 1.0
         self.weight_decay, self.vector_weight_decay = weight_decay, vector_weight_decay
         self.weight_lr_mult, self.algorithm = weight_lr_mult, algorithm
         self.mu, self.nesterov, self.adjust_lr, self.ns_epsilon = mu, nesterov, adjust_lr, ns_epsilon
@@ -142,13 +147,29 @@ class ShardedOptimizer:
 
     # ------------------------------------------------------------------ step
     @torch.no_grad()
-    def step(self, lr: Optional[float] = None, weight_decay: Optional[float] = None) -> None:
+    def step(self, lr: Optional[float] = None, weight_decay: Optional[float] = None,
+             vector_weight_decay: Optional[float] = None, betas: Optional[Tuple[float, float]] = None,
+             eps: Optional[float] = None, vector_betas: Optional[Tuple[float, float]] = None,
+             vector_eps: Optional[float] = None) -> None:
+        """One update.  Every hyper-parameter passed here replaces the stored one from this step on (the trainer
+        recomputes them per iteration: LR schedule, batch ramp-up, independent weight decay, beta schedules)."""
         if lr is not None:
             self.lr = lr
         if weight_decay is not None:
             self.weight_decay = weight_decay
+        if vector_weight_decay is not None:
+            self.vector_weight_decay = vector_weight_decay
+        if betas is not None:
+            self.betas = betas
+        if eps is not None:
+            self.eps = eps
+        if vector_betas is not None:
+            self.vector_betas = vector_betas
+        if vector_eps is not None:
+            self.vector_eps = vector_eps
         self.step_count += 1
         eng = self.engine
+        eng.reload_states()          # no-op unless master / state shards were offloaded to the host
         dev = eng.device
         x_sq = torch.zeros(max(self.n_norm, 1), dtype=torch.float32, device=dev)
         u_sq = torch.zeros_like(x_sq)
@@ -156,7 +177,9 @@ class ShardedOptimizer:
 
         # ---- vectors: AdamW / Lion / Adam-H on the local slices
         hyper_idx = {id(s): k for (_, s, k) in self.hyper_vecs}
-        buckets: Dict[Tuple[float, float], List[Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]]] = {}
+        buckets: Dict[tuple, List[Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]]] = {}
+        v_betas = self.vector_betas if self.vector_betas is not None else self.betas
+        v_eps = self.vector_eps if self.vector_eps is not None else self.eps
         for g in eng.groups():
             if g.grad is None:
                 continue
@@ -170,9 +193,9 @@ class ShardedOptimizer:
                 is_vec_cls = self.cls[id(s)] == "vector" and self.split_groups
                 lr_p = self.lr if is_vec_cls or not self.split_groups else self.lr * self.weight_lr_mult
                 wd = self.vector_weight_decay if is_vec_cls else self.weight_decay
+                bt, ep_ = (v_betas, v_eps) if is_vec_cls else (self.betas, self.eps)
                 if id(s) in hyper_idx:
-                    u = scalar_opts.adamw_direction_([m], [v], [gr], self.betas[0], self.betas[1], self.eps,
-                                                     self.step_count)[0]
+                    u = scalar_opts.adamw_direction_([m], [v], [gr], bt[0], bt[1], ep_, self.step_count)[0]
                     if wd:
                         x.mul_(1 - lr_p * wd)
                     k = hyper_idx[id(s)]
@@ -180,14 +203,20 @@ class ShardedOptimizer:
                     u_sq[k] += u.float().pow(2).sum()
                     pending_hyper.append((x, u, k, lr_p))
                 else:
-                    buckets.setdefault((lr_p, wd), []).append((x, gr, m, v))
-        for (lr_p, wd), items in buckets.items():
+                    rule = "nadam" if (self.algorithm == "hadam" and not is_vec_cls) else self.algorithm
+                    buckets.setdefault((lr_p, wd, bt, ep_, rule), []).append((x, gr, m, v))
+        for (lr_p, wd, bt, ep_, rule), items in buckets.items():
             xs, gs, ms, vs = (list(t) for t in zip(*items))
-            if self.algorithm == "lion":
-                scalar_opts.lion_update_foreach(xs, gs, ms, lr_p, self.betas[0], self.betas[1], wd)
+            if rule == "lion":
+                scalar_opts.lion_update_foreach(xs, gs, ms, lr_p, bt[0], bt[1], wd)
+            elif rule == "nadam":
+                scalar_opts.nadam_update_foreach(xs, gs, ms, vs, lr_p, bt[0], bt[1], wd, self.step_count, ep_,
+                                                 self.nadam_mu_product)
             else:
-                scalar_opts.adamw_update_foreach(xs, gs, ms, vs, lr_p, self.betas[0], self.betas[1], wd,
-                                                 self.step_count, self.eps)
+                scalar_opts.adamw_update_foreach(xs, gs, ms, vs, lr_p, bt[0], bt[1], wd, self.step_count, ep_)
+        if self.algorithm == "hadam":
+            # advance the product once per step on every rank (also on ranks whose shard holds no weight slice)
+            self.nadam_mu_product *= scalar_opts.nadam_mu(self.betas[0], self.step_count)
 
         # ---- matrices: momentum on local slices, orthogonalise on owners, scatter back
         hb_x: List[torch.Tensor] = [t[0] for t in pending_hyper]
@@ -435,6 +464,7 @@ class ShardedOptimizer:
     def state_dict(self, rank0_only: bool = True) -> Dict:
         """Consolidated, world-size independent: per-parameter ``momentum`` / ``variance`` tensors."""
         eng = self.engine
+        eng.reload_states()
         keep = (not rank0_only) or eng.mesh.rank == 0
         state: Dict[str, Dict[str, torch.Tensor]] = {}
         for g in eng.groups():
@@ -448,11 +478,14 @@ class ShardedOptimizer:
                     if keep:
                         state.setdefault(s.name, {})[key] = t.cpu().clone()
                 del full
-        return {"state": state, "step": self.step_count, "algorithm": self.algorithm} if keep else {}
+        return {"state": state, "step": self.step_count, "algorithm": self.algorithm,
+                "nadam_mu_product": self.nadam_mu_product} if keep else {}
 
     @torch.no_grad()
     def load_state_dict(self, sd: Dict) -> None:
         self.step_count = int(sd.get("step", 0))
+        self.nadam_mu_product = float(sd.get("nadam_mu_product", 1.0))
+        self.engine.reload_states()
         state = sd.get("state", {})
         for g in self.engine.groups():
             gid = id(g)

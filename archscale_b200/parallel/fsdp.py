@@ -529,6 +529,63 @@ class FSDPEngine:
             else:
                 self.pool.put(full_grad)
 
+    # ------------------------------------------------------------------ CPU offload of master / optimizer shards
+    # The role of ``CPUOffloadPolicy`` in the reference (`pretrain.py:544`, ``--offloading`` / ``--fsdp_save_mem``), done
+    # the other way round: the optimizer keeps running on the GPU, but between optimizer steps the fp32 master shards
+    # and the optimizer's fp32 state shards (12 bytes per parameter and shard with Adam) live in pinned host memory, so
+    # forward and backward — where activations peak — have that memory back.  Only the low-precision shard copy that the
+    # all-gather reads stays on the device.  Groups that travel in fp32 (a few small vectors) are not offloaded.
+    def enable_cpu_offload(self, state_dicts: Sequence[Dict[int, torch.Tensor]] = ()) -> None:
+        """``state_dicts``: dicts ``id(group) → shard-shaped tensor`` owned by the optimizer (momentum, variance)."""
+        self.cpu_offload = True
+        self._off_dicts = list(state_dicts)
+        self._off_host: Dict[Tuple[int, int], torch.Tensor] = {}
+        self._offloaded = False
+
+    def _to_host(self, key, t: torch.Tensor) -> torch.Tensor:
+        h = self._off_host.get(key)
+        if h is None or h.shape != t.shape or h.dtype != t.dtype:
+            h = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=self.is_cuda)
+            self._off_host[key] = h
+        h.copy_(t, non_blocking=True)
+        return h
+
+    @torch.no_grad()
+    def offload_states(self) -> None:
+        if not getattr(self, "cpu_offload", False) or self._offloaded:
+            return
+        for g in self.groups():
+            if g.dtype == torch.float32 or g.master is None:
+                continue
+            if self.symm is not None and g.world > 1:
+                self.symm.lp_shard(g)
+            else:
+                g.refresh_lp()                       # the forward pass gathers from this copy
+            self._to_host((id(g), -1), g.master)
+            g.master = None
+            for k, d in enumerate(self._off_dicts):
+                if id(g) in d and d[id(g)] is not None:
+                    self._to_host((id(g), k), d[id(g)])
+                    d[id(g)] = None
+        if self.is_cuda:
+            torch.cuda.current_stream().synchronize()   # host copies complete before the device tensors are released
+        self._offloaded = True
+
+    @torch.no_grad()
+    def reload_states(self) -> None:
+        if not getattr(self, "cpu_offload", False) or not self._offloaded:
+            return
+        for g in self.groups():
+            h = self._off_host.get((id(g), -1))
+            if h is None or g.master is not None:
+                continue
+            g.master = h.to(self.device, non_blocking=True)
+            for k, d in enumerate(self._off_dicts):
+                hk = self._off_host.get((id(g), k))
+                if hk is not None and id(g) in d and d[id(g)] is None:
+                    d[id(g)] = hk.to(self.device, non_blocking=True)
+        self._offloaded = False
+
     # ------------------------------------------------------------------ public API
     def backward(self, loss: torch.Tensor) -> None:
         """``loss.backward()`` with unit-wise gather / reduce-scatter; returns after every
@@ -683,6 +740,7 @@ class FSDPEngine:
         """Consolidated fp32 (or ``dtype``) state dict with the model's own key names and whole-model shapes, on CPU."""
         out: Dict[str, torch.Tensor] = {}
         keep = (not rank0_only) or self.mesh.rank == 0
+        self.reload_states()
         for g in self.groups():
             full = self._gather_master(g.master, g)
             for s in g.specs:
@@ -710,6 +768,7 @@ class FSDPEngine:
     @torch.no_grad()
     def load_full_state_dict(self, sd: Dict[str, torch.Tensor], strict: bool = True) -> None:
         missing = []
+        self.reload_states()
         for g in self.groups():
             for s, lo, hi, slo in g.local_slices():
                 if s.name not in sd:

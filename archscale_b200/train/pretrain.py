@@ -18,6 +18,7 @@ resume seeks the data stream in O(1) instead of replaying batches.
 """
 from __future__ import annotations
 
+import contextlib
 import dataclasses
 import glob
 import json
@@ -107,6 +108,40 @@ def get_lr(it: int, warmup_iters: int, max_iters: int, lr: float, min_lr_mult: f
     return lr + ratio * (min_lr_mult * lr - lr)
 
 
+def step_hparams(train_config: str, *, lr: float, learning_rate: float, weight_decay: float, vector_decay: float,
+                 matrix_lr_mult: float, super_mup: bool, ramp: Optional[Dict[str, float]] = None) -> Dict[str, Dict[str, Any]]:
+    """Optimizer hyper-parameters of one iteration for the two parameter classes, as the reference's ``update_param``
+    sets them on its param groups every iteration (`pretrain.py:829-878`).
+
+    ``lr`` is the scheduled value, ``learning_rate`` the peak it decays from, ``matrix_lr_mult`` the weight group's
+    LR multiplier (``d0/depth`` for AdamW-family runs, × ``weight_lr_scale`` for the hybrid ones).  ``ramp`` holds the
+    batch-size-scaled values on the iterations where the batch ramp-up changes the accumulation count.  A value of
+    ``None`` means "leave what the optimizer has".  Rules, per class with its own ``wd`` and ``lr_mult``:
+
+    * ramp iteration: ``eps``, ``betas`` ← scaled values; if ``wd > 0``: ``wd`` ← scaled weight decay, and for
+      ``v2scale`` runs divided by ``learning_rate·lr_mult`` (independent weight decay: the decay per step is
+      ``wd·lr/learning_rate`` whatever the LR multipliers);
+    * otherwise, if ``wd > 0``: ``v2scale`` → ``wd = weight_decay/(learning_rate·lr_mult)``; ``super_mup`` → betas follow
+      the LR schedule, ``(0.95 − 0.10·lr/learning_rate, 0.975 − 0.05·lr/learning_rate)``.
+    """
+    out: Dict[str, Dict[str, Any]] = {}
+    v2 = "v2scale" in train_config
+    frac = lr / learning_rate if learning_rate else 0.0
+    for cls, wd, mult in (("vector", vector_decay, 1.0), ("matrix", weight_decay, matrix_lr_mult)):
+        h: Dict[str, Any] = {"lr_mult": mult, "weight_decay": None, "betas": None, "eps": None}
+        if ramp is not None:
+            h["eps"], h["betas"] = ramp["eps"], (ramp["beta1"], ramp["beta2"])
+            if wd > 0:
+                h["weight_decay"] = ramp["weight_decay"] / learning_rate / mult if v2 else ramp["weight_decay"]
+        elif wd > 0:
+            if v2:
+                h["weight_decay"] = weight_decay / learning_rate / mult
+            if super_mup:
+                h["betas"] = (0.95 - (0.95 - 0.85) * frac, 0.975 - (0.975 - 0.925) * frac)
+        out[cls] = h
+    return out
+
+
 @dataclass
 class TrainPlan:
     """Everything ``setup()`` derives from the flags before any tensor is created."""
@@ -148,6 +183,7 @@ class TrainPlan:
     bsz_scaling: str = "default"
     cpu_offload: bool = False
     activation_checkpointing: bool = False
+    code_dropout: float = 0.0
     nodes: int = 1
     devices: int = 1
     overrides: Dict[str, Any] = field(default_factory=dict)
@@ -338,6 +374,10 @@ class Trainer:
                                  device=device, fused_comm=fused_comm)
         self.print(f"model {p.model_name}: {self.n_params_actual:,} parameters, built in {time.perf_counter() - t0:.1f}s")
         self.optimizer = self._build_optimizer()
+        if p.cpu_offload:
+            # --offloading / --fsdp_save_mem: fp32 master and optimizer-state shards wait in pinned host memory between steps
+            self.engine.enable_cpu_offload([self.optimizer.m, self.optimizer.v])
+            self.engine.offload_states()
         self.state = {"iter_num": 0, "step_count": 0}
         self.loss_func = (FusedLinearCrossEntropyLoss(label_smoothing=p.label_smoothing) if p.use_flce_loss
                           else FusedCrossEntropyLoss(label_smoothing=p.label_smoothing))
@@ -393,10 +433,26 @@ class Trainer:
                                     weight_decay=p.weight_decay, vector_weight_decay=vector_decay, weight_lr_mult=1.0,
                                     algorithm="muonh" if "muonh" in tc else "muon", mu=p.muon_beta, nesterov=True,
                                     adjust_lr="spectral_norm", ns_epsilon=p.eps)
-        betas, eps = ((0.8, 0.95), 1e-10) if "hadam" in tc else ((p.beta1, p.beta2), p.eps)
-        return ShardedOptimizer(self.engine, lr=p.learning_rate, betas=betas, eps=eps, weight_decay=p.weight_decay,
-                                vector_weight_decay=vector_decay, weight_lr_mult=self.base_hps.d0 / p.depth,
-                                algorithm="adamw")
+        if "hadam" in tc:
+            # AdamW(0.8, 0.95, eps 1e-10) for vectors + NAdam(beta1, beta2, eps) at lr·weight_lr_scale for the weights
+            return ShardedOptimizer(self.engine, lr=p.learning_rate, betas=(p.beta1, p.beta2), eps=p.eps,
+                                    weight_decay=p.weight_decay, vector_weight_decay=vector_decay,
+                                    weight_lr_mult=self.matrix_lr_mult(), algorithm="hadam",
+                                    vector_betas=(0.8, 0.95), vector_eps=1e-10)
+        return ShardedOptimizer(self.engine, lr=p.learning_rate, betas=(p.beta1, p.beta2), eps=p.eps,
+                                weight_decay=p.weight_decay, vector_weight_decay=vector_decay,
+                                weight_lr_mult=self.matrix_lr_mult(), algorithm="adamw")
+
+    def matrix_lr_mult(self) -> float:
+        """LR multiplier of the weight-matrix class (`pretrain.py:565-592,880-892`): 1 under Muon (the optimizer keeps the
+        update RMS itself), ``d0/depth`` otherwise, times ``weight_lr_scale`` for the two-optimizer runs."""
+        p, tc = self.plan, self.plan.train_config
+        if not p.mup:
+            return 1.0
+        mult = 1.0 if "muon" in tc else self.base_hps.d0 / p.depth
+        if "hadam" in tc or "muonball" in tc:
+            mult *= p.weight_lr_scale
+        return mult
 
     # ------------------------------------------------------------------ data
     def _sample_stream(self, data_dir: str, block: int, split: str, seed: int = 12345):
@@ -474,11 +530,12 @@ class Trainer:
             # the model returns this rank's chunk of the tokens; the global loss is the mean of the tp ranks' means
             from archscale_b200.parallel.tp import token_slice
             targets = token_slice(targets, tp, self.mesh.tp_rank).contiguous()
+        drop = p.code_dropout if is_code else 0.0        # residual dropout on batches that hold code samples
         if p.use_flce_loss:
-            out = self.model(input_ids, use_flce_loss=True)
+            out = self.model(input_ids, use_flce_loss=True, residual_dropout=drop)
             loss = self.loss_func(out.logits, out.weight, targets)
         else:
-            loss = self.loss_func(self.model(input_ids).logits, targets)
+            loss = self.loss_func(self.model(input_ids, residual_dropout=drop).logits, targets)
         back = loss / tp if tp > 1 else loss
         bal = None
         if self.config.moe:
@@ -501,22 +558,30 @@ class Trainer:
             du.all_reduce_sum(loss, group=self.mesh.tp_group)
         return loss, (bal.detach() if isinstance(bal, torch.Tensor) else None)
 
-    def optimizer_step(self, lr: float):
+    def optimizer_step(self, lr: float, hparams: Optional[Dict[str, Dict[str, Any]]] = None):
         if self.mesh.tp > 1:
             from archscale_b200.parallel.tp import sync_replicated_grads
             sync_replicated_grads(self.engine, self.mesh)
         gn = self.engine.clip_grad_norm_(self.plan.grad_clip)
-        self.optimizer.step(lr=lr)
+        kw: Dict[str, Any] = {}
+        if hparams is not None:
+            hv, hm = hparams["vector"], hparams["matrix"]
+            kw = dict(weight_decay=hm["weight_decay"], vector_weight_decay=hv["weight_decay"], betas=hm["betas"],
+                      eps=hm["eps"], vector_betas=hv["betas"], vector_eps=hv["eps"])
+        self.optimizer.step(lr=lr, **kw)
         self.optimizer.zero_grad()
+        self.engine.offload_states()
         return gn
 
     # ------------------------------------------------------------------ loops
     def fit(self) -> None:
         p, state = self.plan, self.state
         tc = p.train_config
-        val_loader = self.val_loader()
-        if val_loader is not None:
-            self.validate(val_loader, sanity_check="validation" not in tc)
+        # every evaluation reads the same leading batches of the validation stream (a fresh loader per call, as the
+        # reference re-iterates its DataLoader, `pretrain.py:1040`), so val_loss values are comparable between evals
+        has_val = bool(self.val_data_dir)
+        if has_val:
+            self.validate(sanity_check="validation" not in tc)
         if "validation" in tc:
             return
         n_params = get_parameters_count(p.model_name, p.depth, self.config, tc) if self.config.ar else self.n_params_actual
@@ -543,80 +608,107 @@ class Trainer:
         self.model.train()
         batch_info = None
         health = self._health()
-        for train_data, is_code in loader:
-            lu.drain_logging_queue(self.logger.log_dict, self.print)
-            if state["iter_num"] >= max_iters:
-                break
-            if health is not None:
-                # learn about a failed peer on the host, before launching collectives that would wait for it
-                health.check()
-                health.beat(state["iter_num"])
-            is_accumulating = (state["iter_num"] + 1) % accum != 0
-            if ramp and not is_accumulating:
-                mult = batch_size_rampup_func(state["iter_num"], max_iters, p.bsz_rampup_ratio)
-                accum = int(p.gradient_accumulation_steps * mult)
-                cur_b = p.micro_batch_size * accum * world * p.seq_len
-                sc = apply_batch_size_scaling(cur_b / self.base_hps.b0, self.base_hps, p.bsz_scaling)
-                # √-batch rule relative to the planned batch; depth / token multipliers of the plan are kept
-                learning_rate = p.learning_rate * math.sqrt(cur_b / (p.batch_size * world * p.seq_len))
-                self.optimizer.eps, self.optimizer.betas = sc["eps"], (sc["beta1"], sc["beta2"])
-                batch_info = {"grad_accum_steps": accum, "effective_batch_size": cur_b, "batch_multiplier": mult,
-                              "batch_ratio": cur_b / self.base_hps.b0}
-            lr = get_lr(state["iter_num"], warmup_iters, max_iters, learning_rate, p.min_lr, tc)
-            log_now = (state["iter_num"] + 1) % log_iter_interval == 0
-            self.model.set_collect_stats(log_now)
-            batch_dev = train_data.to(self.device, non_blocking=True)
-            loss, bal = self.forward_backward(batch_dev, is_code, accum)
-            gn = None
-            if not is_accumulating:
-                gn = self.optimizer_step(lr)
-                state["step_count"] += 1
-            state["iter_num"] += 1
-            total_lengths += train_data.shape[0] * self.config.block_size
-            if log_now:
-                timer.stop()
-                device_time_s += timer.elapsed_ms() / 1e3        # the only host sync of the loop
-                timer.start()
-                loss_v = float(loss)
-                self.monitor.on_train_batch_end(state["iter_num"] * p.micro_batch_size, device_time_s,
-                                                flops_per_batch=flops_per_batch, lengths=total_lengths,
-                                                train_loss=loss_v)
-                elapsed = time.perf_counter() - total_t0
-                remaining = elapsed / max(state["iter_num"], 1) * (max_iters - state["iter_num"]) / 3600
-                self.print(f"iter {state['iter_num']} step {state['step_count']}: loss {loss_v:.4f}, lr {lr:.3e}, "
-                           f"device time {device_time_s:.1f}s, remaining {remaining:.2f} h")
-                if gn is not None:
-                    payload = lu.build_logging_payload(
-                        state["iter_num"], state["step_count"], gn, p.grad_clip, model=self.model,
-                        optimizer_stats={"betas": self.optimizer.betas, "eps": self.optimizer.eps, "weight_lr": lr,
-                                         "vector_lr": lr, "weight_decay": self.optimizer.weight_decay},
-                        bal_loss=bal, batch_info=batch_info, vector_names=VECTOR_NAMES)
-                    if self.rank0:
-                        lu.submit_logging_task(payload)
-            if not is_accumulating and val_loader is not None and state["step_count"] % p.eval_step_interval == 0:
-                self.validate(val_loader)
-            if not is_accumulating and state["step_count"] % p.save_step_interval == 0:
-                self.print(f"saving checkpoint to {self.save_checkpoint()!r}")
+        fused = getattr(self.engine, "symm", None) is not None
+        check_every = int(os.environ.get("ARCHSCALE_B200_DEVICE_CHECK_EVERY", "1" if fused else "0"))
+        guard = health.guard() if health is not None else contextlib.nullcontext()
+        with guard:
+            for train_data, is_code in loader:
+                lu.drain_logging_queue(self.logger.log_dict, self.print)
+                if state["iter_num"] >= max_iters:
+                    break
+                if health is not None:
+                    # learn about a failed peer on the host, before launching collectives that would wait for it
+                    health.check()
+                    health.beat(state["iter_num"])
+                is_accumulating = (state["iter_num"] + 1) % accum != 0
+                ramp_now = None
+                if ramp and not is_accumulating:
+                    mult = batch_size_rampup_func(state["iter_num"], max_iters, p.bsz_rampup_ratio)
+                    accum = int(p.gradient_accumulation_steps * mult)
+                    cur_b = p.micro_batch_size * accum * world * p.seq_len
+                    ramp_now = apply_batch_size_scaling(cur_b / self.base_hps.b0, self.base_hps, p.bsz_scaling)
+                    # as in the reference (`pretrain.py:825-826`) the peak LR becomes the batch-scaled base value
+                    learning_rate = ramp_now["learning_rate"]
+                    batch_info = {"grad_accum_steps": accum, "effective_batch_size": cur_b, "batch_multiplier": mult,
+                                  "batch_ratio": cur_b / self.base_hps.b0}
+                lr = get_lr(state["iter_num"], warmup_iters, max_iters, learning_rate, p.min_lr, tc)
+                hp = step_hparams(tc, lr=lr, learning_rate=learning_rate, weight_decay=p.weight_decay,
+                                  vector_decay=p.weight_decay if p.original_mup else 0.0,
+                                  matrix_lr_mult=self.matrix_lr_mult(), super_mup=p.super_mup, ramp=ramp_now)
+                log_now = (state["iter_num"] + 1) % log_iter_interval == 0
+                self.model.set_collect_stats(log_now)
+                batch_dev = train_data.to(self.device, non_blocking=True)
+                loss, bal = self.forward_backward(batch_dev, is_code, accum)
+                gn = None
+                if not is_accumulating:
+                    if check_every and self.device.type == "cuda" and state["step_count"] % check_every == 0:
+                        # peer-memory kernels give up a wait after a time limit and return; the status word says so.  Read
+                        # it before the optimizer consumes gradients that a timed-out pull left incomplete.
+                        from archscale_b200.utils.health import check_device
+                        check_device()
+                    gn = self.optimizer_step(lr, hp)
+                    state["step_count"] += 1
+                    if fused and state["step_count"] == 3:
+                        # start-up skew (allocation, first launches) is over: a peer that stays silent for this long is gone
+                        from archscale_b200.ops import backend
+                        secs = float(os.environ.get("ARCHSCALE_B200_PEER_WAIT_S", "5"))
+                        backend.require_extension().set_peer_wait_limit_cycles(int(secs * 2e9))
+                state["iter_num"] += 1
+                total_lengths += train_data.shape[0] * self.config.block_size
+                if log_now:
+                    timer.stop()
+                    device_time_s += timer.elapsed_ms() / 1e3        # the only host sync of the loop
+                    timer.start()
+                    loss_v = float(loss)
+                    if self.device.type == "cuda" and not check_every:
+                        from archscale_b200.utils.health import check_device
+                        check_device()                                 # the stream is already synchronised here
+                    self.monitor.on_train_batch_end(state["iter_num"] * p.micro_batch_size, device_time_s,
+                                                    flops_per_batch=flops_per_batch, lengths=total_lengths,
+                                                    train_loss=loss_v)
+                    elapsed = time.perf_counter() - total_t0
+                    remaining = elapsed / max(state["iter_num"], 1) * (max_iters - state["iter_num"]) / 3600
+                    self.print(f"iter {state['iter_num']} step {state['step_count']}: loss {loss_v:.4f}, lr {lr:.3e}, "
+                               f"device time {device_time_s:.1f}s, remaining {remaining:.2f} h")
+                    if gn is not None:
+                        payload = lu.build_logging_payload(
+                            state["iter_num"], state["step_count"], gn, p.grad_clip, model=self.model,
+                            optimizer_stats={"betas": self.optimizer.betas, "eps": self.optimizer.eps, "weight_lr": lr,
+                                             "vector_lr": lr, "weight_decay": self.optimizer.weight_decay},
+                            bal_loss=bal, batch_info=batch_info, vector_names=VECTOR_NAMES)
+                        if self.rank0:
+                            lu.submit_logging_task(payload)
+                if not is_accumulating and has_val and state["step_count"] % p.eval_step_interval == 0:
+                    self.validate()
+                if not is_accumulating and state["step_count"] % p.save_step_interval == 0:
+                    self.print(f"saving checkpoint to {self.save_checkpoint()!r}")
         loader.close()
         if state["iter_num"] >= max_iters and self.max_steps is None:
-            if val_loader is not None:
-                self.validate(val_loader)
+            if has_val:
+                self.validate()
             self.print(f"saving final checkpoint to {self.save_checkpoint()!r}")
         lu.wait_for_logging_tasks(self.logger.log_dict, self.print)
         if self.device.type == "cuda":
             self.print(f"peak memory: {torch.cuda.max_memory_allocated(self.device) / 1e9:.2f} GB")
 
     @torch.no_grad()
-    def validate(self, val_loader, sanity_check: bool = False) -> torch.Tensor:
+    def validate(self, val_loader=None, sanity_check: bool = False) -> torch.Tensor:
         p = self.plan
         t0 = time.perf_counter()
         self.model.eval()
         iters = 2 if sanity_check else p.eval_iters
+        own_loader = val_loader is None
+        if own_loader:
+            val_loader = self.val_loader()
         losses = torch.zeros(iters, p.num_extrapol, device=self.device)
         accs = None if p.use_flce_loss else torch.zeros(iters, p.num_extrapol, device=self.device)
-        for k, (val_data, _) in enumerate(val_loader):
-            if k >= iters:
+        seen = 0
+        for k in range(iters):
+            try:
+                val_data, _ = next(val_loader)
+            except StopIteration:
                 break
+            seen += 1
             val_data = val_data.to(self.device, non_blocking=True)
             for i in range(p.num_extrapol):
                 length = (i + 1) * p.seq_len
@@ -628,6 +720,12 @@ class Trainer:
                     logits = self.model(ids).logits
                     losses[k, i] = self.loss_func(logits, tgt)
                     accs[k, i] = (logits.argmax(dim=-1) == tgt).float().mean()
+        if own_loader:
+            val_loader.close()
+        # average over the batches actually read (a short validation set must not average in zeros)
+        losses = losses[:max(seen, 1)]
+        if accs is not None:
+            accs = accs[:max(seen, 1)]
         out = losses.mean(0)
         if "v2scale" in p.train_config and self.mesh.world > 1:
             du.all_reduce_sum(out)
