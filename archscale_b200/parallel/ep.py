@@ -45,13 +45,16 @@ def attach(model: torch.nn.Module, mesh, seed: int = 3407) -> None:
             if holder.bias is not None:
                 holder.bias._ep_local = True
             with torch.no_grad():
-                scale = float(holder.weight.detach().float().std()) or 1.0
+                # each GLOBAL expert draws from its own seed with the package's default weight init (kaiming-uniform unless
+                # --ortho_init / --diag_init / --maxfan_init changed it), as the reference initialises every expert matrix
+                # (`lit_gpt/moe.py:533-581`); the values do not depend on the expert-parallel degree
                 for e_l in range(mod.n_local):
                     e = mesh.ep_rank * mod.n_local + e_l
-                    g = torch.Generator(device="cpu").manual_seed(seed + 1000003 * layer_idx + 7919 * e + (0 if holder is mod.mods_in else 1))
                     w = torch.empty(holder.weight.shape[1:], dtype=torch.float32)
-                    w.normal_(generator=g)
-                    holder.weight[e_l].copy_((w * scale).to(holder.weight.dtype))
+                    with torch.random.fork_rng(devices=[]):
+                        torch.manual_seed(seed + 1000003 * layer_idx + 7919 * e + (0 if holder is mod.mods_in else 1))
+                        torch_default_init(w)
+                    holder.weight[e_l].copy_(w.to(holder.weight.dtype))
 
 
 # ------------------------------------------------------------------ baseline transport (all_to_all)

@@ -214,6 +214,9 @@ def make_plan(*, train_model: Optional[str], train_name: str, depth: int, max_to
     p.data_chunks = 128 if "v2scale" in tc else 8
     if fsdp_save_mem:
         offloading = act_ckpt = True
+    if fp4 and os.environ.get("ARCHSCALE_B200_FP4_AS_MXFP8", "0") != "1":
+        raise NotImplementedError("--fp4 (NVFP4 linears) is not built; --fp8 runs block-scaled MXFP8 linears. "
+                                  "ARCHSCALE_B200_FP4_AS_MXFP8=1 maps --fp4 onto them explicitly.")
     fp8 = fp8 or fp4
     if data_mixture is not None:
         with open(data_mixture) as f:
@@ -338,8 +341,10 @@ class Trainer:
     def __init__(self, plan: TrainPlan, mesh: Mesh, device: torch.device, train_data_dir: str,
                  val_data_dir: Optional[str], resume, load_dir: Optional[str], base_hps: BaseHyperparameters,
                  use_mlflow: bool = False, wandb_project: Optional[str] = None, precision: str = "bf16",
-                 fused_comm: bool = False, max_steps: Optional[int] = None, quiet: bool = False) -> None:
+                 fused_comm: bool = False, max_steps: Optional[int] = None, quiet: bool = False,
+                 logging_multiprocessing: bool = False) -> None:
         self.plan, self.mesh, self.device, self.base_hps = plan, mesh, device, base_hps
+        self.logging_multiprocessing = logging_multiprocessing
         self.rank0 = mesh.rank == 0
         self.quiet = quiet
         self.max_steps = max_steps
@@ -598,7 +603,9 @@ class Trainer:
         ramp = p.bsz_rampup_ratio != 1
         learning_rate = p.learning_rate
         loader = self.train_loader(skip_batches=state["iter_num"] if self.resumed else 0)
-        lu.configure_logging_executor(use_multiprocessing=False)
+        # statistics of a logging step are reduced to scalars on this process; formatting them (and the per-layer hooks) runs
+        # on a worker — a spawned process when --logging_multiprocessing is on (`logging_utils.py:92-119` of the reference)
+        lu.configure_logging_executor(use_multiprocessing=self.logging_multiprocessing and self.rank0)
         total_t0 = time.perf_counter()
         total_lengths = 0
         timer = DeviceStepTimer()
@@ -796,7 +803,8 @@ def setup(train_data_dir: str = "data/redpajama_sample", val_data_dir: Optional[
         ckpt.make_dirs(plan.out_dir)
     trainer = Trainer(plan, mesh, device, train_data_dir, val_data_dir, resume, load_dir, base_hps,
                       use_mlflow=use_mlflow, wandb_project=wandb_project, precision=precision,
-                      fused_comm=fused_comm, max_steps=max_steps, quiet=quiet)
+                      fused_comm=fused_comm, max_steps=max_steps, quiet=quiet,
+                      logging_multiprocessing=logging_multiprocessing)
     if return_trainer:
         return trainer
     trainer.logger.log_hyperparams({**dataclasses.asdict(base_hps),

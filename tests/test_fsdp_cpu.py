@@ -180,3 +180,56 @@ def test_latest_checkpoint_skips_truncated_file(tmp_path):
     assert ckpt.latest_ckpt_in_dir(str(tmp_path)) == str(good)
     assert ckpt.find_resume_path("auto", str(tmp_path)) == str(good)
     assert ckpt.find_resume_path(False, str(tmp_path)) is None
+
+
+def _worker_hsdp(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        mesh = build_mesh(dp=2)
+        assert (mesh.dp, mesh.fsdp) == (2, 2) and mesh.data_world == 4
+        data = _data(1, 3, per_rank=4, T=64)     # one global batch of 4 rows, one row per rank
+        torch.manual_seed(0)
+        m = GPT(_cfg(block_size=64, vocab_size=512))
+        m.reset_parameters()
+        m.compute_dtype = torch.float32
+        eng = FSDPEngine(m, mesh, unit_classes=(Block,), param_dtype=torch.float32)
+        opt = ShardedOptimizer(eng, lr=1e-3, betas=(0.9, 0.95), algorithm="muonh", mu=0.95, nesterov=True, weight_decay=0.0)
+        # shards are 1/2 of each unit (sharded inside a replica), not 1/4
+        g0 = next(iter(eng.groups()))
+        assert g0.world == 2 and g0.shard_numel * 2 == g0.padded
+        losses = []
+        for s in range(3):
+            l = _step(m, eng, opt, data[s, rank:rank + 1] % 512)
+            dist.all_reduce(l)
+            losses.append(float(l) / world)
+        # the two replicas hold identical shards after training
+        mine = torch.cat([g.master for g in eng.groups()])
+        other = [torch.empty_like(mine) for _ in range(2)]
+        dist.all_gather(other, mine, group=mesh.dp_group)
+        same = bool(torch.equal(other[0], other[1]))
+        if rank == 0:
+            q.put((losses, same))
+        else:
+            assert same
+    finally:
+        _leave_together()
+
+
+def test_hybrid_sharding_dp2_fsdp2_matches_single_process():
+    """dp_replicate = 2: gradients are reduce-scattered inside a replica and all-reduced across replicas."""
+    data = _data(1, 3, per_rank=4, T=64) % 512
+    torch.manual_seed(0)
+    m = GPT(_cfg(block_size=64, vocab_size=512))
+    m.reset_parameters()
+    m.compute_dtype = torch.float32
+    eng = FSDPEngine(m, build_mesh(), unit_classes=(Block,), param_dtype=torch.float32)
+    opt = ShardedOptimizer(eng, lr=1e-3, betas=(0.9, 0.95), algorithm="muonh", mu=0.95, nesterov=True, weight_decay=0.0)
+    single = [float(_step(m, eng, opt, data[s])) for s in range(3)]
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    mp.spawn(_worker_hsdp, args=(4, 29613, q), nprocs=4, join=True)
+    multi, same = q.get()
+    assert same
+    for a, b in zip(single, multi):
+        assert abs(a - b) < 2e-3, (single, multi)

@@ -177,3 +177,31 @@ def test_fused_cross_entropy_module_matches_oracle(reduction):
     (a * w).sum().backward()
     (b * w).sum().backward()
     assert torch.allclose(logits.grad, ref_in.grad, atol=1e-5)
+
+
+def test_fp4_flag_raises_instead_of_silently_running_fp8():
+    from archscale_b200.train.pretrain import make_plan
+    kw = dict(train_model="transformer_gqa4", train_name="scaling_mup_muonh", depth=8, max_tokens=1e6, ctx_len=64, swa_len=None,
+              data_mixture=None, fsdp_save_mem=False, save_step=None, base_hps=BaseHyperparameters(), micro_bsz=1,
+              total_bsz=64, yarn_scale=1.0, sparsity=1, top_k=2, use_flce=True, norm_class=None, fp8=False, post_norm=None,
+              bramp_ratio=None, aux_style=None, aux_gamma=None, num_extrp=None, offloading=False, act_ckpt=False,
+              share_expert=None, global_aux=None, sqrt_gate=None, head_init_std=0.02, ar=None, load_dir=None, world_size=1,
+              local_world_size=1)
+    with pytest.raises(NotImplementedError):
+        make_plan(fp4=True, **kw)
+    plan = make_plan(fp4=False, **{**kw, "fsdp_save_mem": True})
+    assert plan.cpu_offload and plan.activation_checkpointing      # --fsdp_save_mem switches both on
+
+
+def test_logging_worker_process():
+    from archscale_b200.utils import logging_utils as lu
+    lu.configure_logging_executor(use_multiprocessing=True)
+    try:
+        payload = lu.build_logging_payload(10, 5, 1.5, 1.0, optimizer_stats={"betas": (0.9, 0.95), "eps": 1e-8, "weight_lr": 1e-3,
+                                                                            "vector_lr": 1e-3, "weight_decay": 0.0})
+        lu.submit_logging_task(payload)
+        got = {}
+        lu.wait_for_logging_tasks(lambda d, step: got.update(d, step=step), lambda s: None)
+        assert got["step"] == 5 and any(k.startswith("metric/") or k.startswith("optim") or "grad" in k for k in got)
+    finally:
+        lu.shutdown()
