@@ -6,12 +6,18 @@
 // does the work of two one-CTA instructions — the one-CTA kernel (attention_fwd.cu) is bound by the rate at which
 // tcgen05.mma instructions can be issued (≈85 cycles each, whatever their N) — and each CTA stages half the K/V bytes.
 //
-// Per CTA, 224 threads:
-//   warp 0      TMA: Q once, then its K / V halves through a 4-stage ring; every load signals the leader's `full` barrier
-//   warp 1      (leader) S_j = Q·K_jᵀ into one of two 128-column TMEM buffers of each CTA
-//   warp 6      (leader) O += P_j·V_j, P_j (bf16) read from each CTA's TMEM as the A operand
-//   warps 2..5  softmax of the CTA's own 128 rows: thread t owns row t; online softmax in base 2 with lazy rescaling of O;
-//               a quarter of the exponentials is evaluated on the FMA pipe (Cody–Waite split + cubic) instead of MUFU
+// Per CTA, 352 threads:
+//   warp 0       TMA: Q once, then its K / V halves through a 4-stage ring; every load signals the leader's `full` barrier
+//   warp 1       (leader) S_j = Q·K_jᵀ into one of two 128-column TMEM buffers of each CTA
+//   warp 10      (leader) O += P_j·V_j, P_j (bf16) read from each CTA's TMEM as the A operand
+//   warps 2..9   softmax of the CTA's own 128 rows by TWO warp groups: group w owns key columns 64w..64w+63 of every
+//                tile, so two threads share a row.  One warp per scheduler cannot hide the latency of its own
+//                load → max → exp2 → pack → store chain (measured: the tile time did not move when the MMA work per
+//                instruction doubled); two warps per scheduler, each with half the chain, can.  The two halves of a row
+//                exchange their maxima through shared memory (one named barrier per tile), use the same running max,
+//                keep separate row sums (added at the end) and each rescale / store their own 64 columns of O.
+//                Online softmax in base 2 with lazy rescaling of O; a quarter of the exponentials is evaluated on the
+//                FMA pipe (Cody–Waite split + cubic) instead of MUFU.
 // tcgen05.commit arrives on the barriers of both CTAs; the softmax warps of both CTAs arrive on the leader's barriers.
 // No TMA load uses cluster multicast.  Every wait is bounded; both CTAs leave through a cluster barrier.
 //
@@ -25,14 +31,15 @@
 namespace b200 {
 
 constexpr int A2_BM = 128, A2_BN = 128, A2_D = 128;
-constexpr int A2_THREADS = 224;
-constexpr int A2_PV_WARP = 6;
+constexpr int A2_THREADS = 352;
+constexpr int A2_PV_WARP = 10;
+constexpr int A2_SOFTMAX_THREADS = 256;
 constexpr int A2_STAGES = 4;
 constexpr int A2_Q_BYTES = A2_BM * A2_D * 2;            // 32 KB: this CTA's query tile
 constexpr int A2_KH_BYTES = (A2_BN / 2) * A2_D * 2;     // 16 KB: 64 keys × 128
 constexpr int A2_VH_BYTES = A2_BN * (A2_D / 2) * 2;     // 16 KB: 128 keys × 64 head-dim columns
 constexpr int A2_STAGE_BYTES = A2_KH_BYTES + A2_VH_BYTES;
-constexpr int A2_SMEM = A2_Q_BYTES + A2_STAGES * A2_STAGE_BYTES + 1024 + 512;
+constexpr int A2_SMEM = A2_Q_BYTES + A2_STAGES * A2_STAGE_BYTES + 1024 + 512 + 6 * A2_BM * 4;
 constexpr float kLog2e2 = 1.4426950408889634f, kLn2_2 = 0.6931471805599453f;
 
 struct AttnFwd2Params {
@@ -70,12 +77,14 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   uint64_t* k_empty = v_full + A2_STAGES;           // [STAGES] each CTA
   uint64_t* v_empty = k_empty + A2_STAGES;          // [STAGES] each CTA
   uint64_t* s_full = v_empty + A2_STAGES;           // [2] each CTA
-  uint64_t* s_empty = s_full + 2;                   // [2] leader, 8 arrivals (4 warps × 2 CTAs)
-  uint64_t* p_full = s_empty + 2;                   // [2] leader, 8 arrivals
+  uint64_t* s_empty = s_full + 2;                   // [2] leader, 16 arrivals (8 warps × 2 CTAs)
+  uint64_t* p_full = s_empty + 2;                   // [2] leader, 16 arrivals
   uint64_t* p_empty = p_full + 2;                   // [2] each CTA
   uint64_t* o_done = p_empty + 2;                   // each CTA
   uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(o_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
+  float* xmax = reinterpret_cast<float*>(tmem_ptr + 4);          // [2 tile parities][2 groups][128 rows]
+  float* xsum = xmax + 2 * 2 * A2_BM;                            // [2 groups][128 rows]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = static_cast<int>(cluster_ctarank());
@@ -102,7 +111,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 8); mbar_init(&p_full[s], 8); mbar_init(&p_empty[s], 1);
+      mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 16); mbar_init(&p_full[s], 16); mbar_init(&p_empty[s], 1);
     }
     mbar_init(o_done, 1);
     *abort_flag = 0;
@@ -180,54 +189,65 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       }
     }
   } else {
-    const int qtr = warp & 3;
-    const int r = q0 + qtr * 32 + lane;
+    const int qtr = warp & 3, wg = (warp - 2) >> 2;              // TMEM lane quarter of this warp; column half of its group
+    const int row_in_tile = qtr * 32 + lane;
+    const int r = q0 + row_in_tile;
     const bool row_valid = r < p.T;
     const int lo_r = row_valid ? lo_of(r) : 0;
     const int lo_last = lo_of(r_last);
     const uint32_t lane_off = static_cast<uint32_t>(qtr * 32) << 16;
     const float sl2 = p.scale_log2;
     float m_used = -1e30f, l_sum = 0.f;
+    bool ok = true;      // after a timed-out wait the thread keeps meeting its partner group at the named barrier, idle
     for (int t = 0; t < n_tiles; ++t) {
       const int buf = t & 1; const uint32_t bph = (t >> 1) & 1;
-      const int k0 = (j_begin + t) * A2_BN;
-      if (!mbar_wait(&s_full[buf], bph, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
-      tc_fence_after();
-      float s[128];
+      const int k0 = (j_begin + t) * A2_BN + wg * 64;            // first key column of this thread's half
+      float s[64];
+      float mloc = -INFINITY;
+      if (ok && !mbar_wait(&s_full[buf], bph, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) ok = false;
+      if (ok) {
+        tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
-        tmem_ld_32x32(T_S0 + buf * 128 + c * 32 + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_leader(&s_empty[buf]);     // S buffer may be overwritten by S_{t+2}
-      const bool full_tile = (k0 + A2_BN - 1 <= q0) && (k0 >= lo_last);
-      if (!full_tile) {
+        for (int c = 0; c < 2; ++c)
+          tmem_ld_32x32(T_S0 + buf * 128 + wg * 64 + c * 32 + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_leader(&s_empty[buf]);        // S buffer may be overwritten by S_{t+2}
+        const int kt0 = (j_begin + t) * A2_BN;
+        const bool full_tile = (kt0 + A2_BN - 1 <= q0) && (kt0 >= lo_last);
+        if (!full_tile) {
 #pragma unroll
-        for (int e = 0; e < 128; ++e) {
-          const int kk = k0 + e;
-          if (kk > r || kk < lo_r) s[e] = -INFINITY;
+          for (int e = 0; e < 64; ++e) {
+            const int kk = k0 + e;
+            if (kk > r || kk < lo_r) s[e] = -INFINITY;
+          }
         }
+        float mx8[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) mx8[e] = s[e];
+#pragma unroll
+        for (int e = 8; e < 64; ++e) mx8[e & 7] = fmaxf(mx8[e & 7], s[e]);
+        mloc = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+        xmax[(buf * 2 + wg) * A2_BM + row_in_tile] = mloc;
       }
-      float mx8[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) mx8[e] = s[e];
-#pragma unroll
-      for (int e = 8; e < 128; ++e) mx8[e & 7] = fmaxf(mx8[e & 7], s[e]);
-      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]))) * sl2;
-      // lazy rescale: only when the running max grew by more than 8 (factor 256); decided per warp
+      asm volatile("bar.sync 1, 256;" ::: "memory");              // both halves of every row have published their maximum
+      if (!ok) continue;
+      const float mx = fmaxf(mloc, xmax[(buf * 2 + (wg ^ 1)) * A2_BM + row_in_tile]) * sl2;
+      // lazy rescale: only when the running max grew by more than 8 (factor 256); decided per warp, and the same way in
+      // both groups (their warps with the same lane quarter see the same 32 rows)
       const bool need = (mx - m_used) > 8.f;
       if (__any_sync(0xffffffffu, need)) {
         const float m_new = fmaxf(m_used, mx);
         const float alpha = exp2f(m_used - m_new);
         if (t > 0) {
           // O of all previous tiles must be complete before it is rescaled: wait for P·V of tile t−1
-          if (!mbar_wait(o_done, (t - 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
+          if (!mbar_wait(o_done, (t - 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; continue; }
           tc_fence_after();
 #pragma unroll
-          for (int c = 0; c < A2_D / 32; ++c) {
+          for (int c = 0; c < 2; ++c) {                          // this group's 64 columns of O
             uint32_t rr[32];
-            tmem_ld_32x32(T_O + c * 32 + lane_off, rr);
+            tmem_ld_32x32(T_O + wg * 64 + c * 32 + lane_off, rr);
             tmem_ld_wait();
             uint32_t w0[16], w1[16];
 #pragma unroll
@@ -235,19 +255,19 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
               w0[e] = __float_as_uint(__uint_as_float(rr[e]) * alpha);
               w1[e] = __float_as_uint(__uint_as_float(rr[16 + e]) * alpha);
             }
-            tmem_st_32x16(T_O + c * 32 + lane_off, w0);
-            tmem_st_32x16(T_O + c * 32 + 16 + lane_off, w1);
+            tmem_st_32x16(T_O + wg * 64 + c * 32 + lane_off, w0);
+            tmem_st_32x16(T_O + wg * 64 + c * 32 + 16 + lane_off, w1);
           }
           tmem_st_wait();
         }
         l_sum *= alpha;
         m_used = m_new;
       }
-      if (!mbar_wait(&p_empty[buf], bph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) goto done;
+      if (!mbar_wait(&p_empty[buf], bph ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) { ok = false; continue; }
       tc_fence_after();
       float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t w[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
@@ -258,7 +278,7 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           rs4[e & 3] += p0 + p1;
           w[e] = pack_bf16x2(p0, p1);
         }
-        tmem_st_32x16(T_P0 + buf * 64 + c * 16 + lane_off, w);
+        tmem_st_32x16(T_P0 + buf * 64 + wg * 32 + c * 16 + lane_off, w);
       }
       tmem_st_wait();
       l_sum += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
@@ -266,15 +286,19 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       __syncwarp();
       if (lane == 0) mbar_arrive_leader(&p_full[buf]);
     }
-    // epilogue: O / l, LSE
+    // epilogue: the row sum is the sum of the two halves; each group normalises and stores its 64 columns of O
+    xsum[wg * A2_BM + row_in_tile] = l_sum;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (!ok) goto done;
+    l_sum += xsum[(wg ^ 1) * A2_BM + row_in_tile];
     if (!mbar_wait(o_done, (n_tiles - 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
     tc_fence_after();
     const float inv_l = l_sum > 0.f ? 1.f / l_sum : 0.f;
-    __nv_bfloat16* orow = p.out + ((static_cast<size_t>(b) * p.T + r) * p.H + h) * A2_D;
+    __nv_bfloat16* orow = p.out + ((static_cast<size_t>(b) * p.T + r) * p.H + h) * A2_D + wg * 64;
 #pragma unroll
-    for (int c = 0; c < A2_D / 32; ++c) {
+    for (int c = 0; c < 2; ++c) {
       uint32_t rr[32];
-      tmem_ld_32x32(T_O + c * 32 + lane_off, rr);
+      tmem_ld_32x32(T_O + wg * 64 + c * 32 + lane_off, rr);
       tmem_ld_wait();
       if (row_valid) {
 #pragma unroll
@@ -288,7 +312,8 @@ attn_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
       }
     }
-    if (row_valid) p.lse[(static_cast<size_t>(b) * p.H + h) * p.T + r] = l_sum > 0.f ? (m_used + log2f(l_sum)) * kLn2_2 : -INFINITY;
+    if (row_valid && wg == 0)
+      p.lse[(static_cast<size_t>(b) * p.H + h) * p.T + r] = l_sum > 0.f ? (m_used + log2f(l_sum)) * kLn2_2 : -INFINITY;
   }
 
 done:

@@ -433,6 +433,7 @@ class FSDPEngine:
         if self.symm is not None and g.world > 1:
             g.full_grad = g.symm_full_grad
             if not g.symm_fg_dirty:
+                self.symm.wait_readers(g)        # peers may still pull the previous micro-step's slice (accumulation)
                 g.full_grad.zero_()
                 g.symm_fg_dirty = True
         else:

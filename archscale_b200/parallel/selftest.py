@@ -5,7 +5,8 @@
 
 Checks (rank 0 prints ``SELFTEST PASS`` / raises): pull all-gather == ``all_gather_into_tensor``
 bitwise; pull reduce-scatter matches ``reduce_scatter_tensor`` in fp32; three training steps with
-``fused_comm=True`` follow the NCCL run; prints bandwidths of both collectives.
+``fused_comm=True`` follow the NCCL run, also with two micro-steps per optimizer step (the heap gradient buffers
+are then reused inside a step); prints bandwidths of both collectives.
 """
 from __future__ import annotations
 
@@ -130,7 +131,7 @@ def main() -> None:
 
     mesh = build_mesh()
 
-    def run(fused: bool):
+    def run(fused: bool, accum: int = 1):
         torch.manual_seed(0)
         cfg = Config.from_name("transformer_gqa4_d16", n_layer=4, ar=None, n_embd=1024, n_head=8, n_query_groups=4,
                                head_dim=128, intermediate_size=2816, block_size=1024, qk_norm=True, mup=True,
@@ -143,10 +144,11 @@ def main() -> None:
         g = torch.Generator().manual_seed(100 + rank)
         losses = []
         for _ in range(4):
-            data = torch.randint(0, cfg.vocab_size, (2, 1025), generator=g).to(dev)
-            o = model(data[:, :-1], use_flce_loss=True)
-            loss = fused_linear_cross_entropy(o.logits, o.weight, data[:, 1:])
-            eng.backward(loss)
+            for _micro in range(accum):      # accum > 1: the heap gradient buffers are reused inside one optimizer step
+                data = torch.randint(0, cfg.vocab_size, (2, 1025), generator=g).to(dev)
+                o = model(data[:, :-1], use_flce_loss=True)
+                loss = fused_linear_cross_entropy(o.logits, o.weight, data[:, 1:])
+                eng.backward(loss / accum)
             eng.clip_grad_norm_(1.0)
             opt.step()
             opt.zero_grad()
@@ -165,6 +167,14 @@ def main() -> None:
     assert status == 0, f"device status {status}"
     for x, y in zip(a, b):
         assert abs(x - y) < 5e-2, (a, b)
+    a2, b2 = run(False, accum=2), run(True, accum=2)
+    torch.cuda.synchronize()
+    status = ext.device_status()
+    if rank == 0:
+        print("gradient accumulation 2: NCCL", a2, "fused", b2, "device status", status, flush=True)
+    assert status == 0, f"device status {status}"
+    for x, y in zip(a2, b2):
+        assert abs(x - y) < 5e-2, (a2, b2)
     dist.barrier()
     if rank == 0:
         print("SELFTEST PASS", flush=True)

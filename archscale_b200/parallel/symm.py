@@ -90,8 +90,11 @@ class SymmetricContext:
         self.heap = SymmetricHeap(engine.group, need, engine.device)
         self.ext = self.heap.ext
         self.meta: Dict[int, dict] = {}
+        assert 1 + 4 * len(groups) <= _SIGNAL_BYTES // (8 * 4), \
+            f"{len(groups)} flat groups need {1 + 4 * len(groups)} signal channels; the heap has {_SIGNAL_BYTES // 32}"
         for i, g in enumerate(groups):
-            m = {"chan": 1 + 4 * i}
+            # channels of a group: +0 gradients posted, +1 Muon U posted, +2 Muon O posted, +3 gradient slice read
+            m = {"chan": 1 + 4 * i, "rd_epoch": None}
             m["lp_off"] = self.heap.alloc(g.shard_numel * esize(g.dtype))
             lp = self.heap.tensor(m["lp_off"], (g.shard_numel,), g.dtype)
             lp.copy_(g.master)
@@ -122,6 +125,17 @@ class SymmetricContext:
     def step_barrier(self) -> None:
         """All ranks have finished writing their shards / reading their peers' buffers for this step."""
         self.heap.barrier(0)
+        for m in self.meta.values():
+            m["rd_epoch"] = None         # nobody still reads a gradient buffer of the finished step
+
+    def wait_readers(self, g) -> None:
+        """Before the heap gradient buffer of ``g`` is zeroed or accumulated into again inside one optimizer step
+        (gradient accumulation): wait until every peer has pulled its slice of the previous micro-step from it."""
+        m = self.meta[id(g)]
+        if m["rd_epoch"] is not None:
+            self.heap.wait(m["chan"] + 3, m["rd_epoch"])
+            m["rd_epoch"] = None
+            backend.count_launch()
 
     def all_gather(self, g, lp: torch.Tensor) -> None:
         m = self.meta[id(g)]
@@ -149,7 +163,8 @@ class SymmetricContext:
         e = self.heap.post(m["chan"])
         self.heap.wait(m["chan"], e)
         self.ext.reduce_scatter_pull(self.heap.bases, m["fg_off"], out, self.heap.rank, scale, False, self.reduce_ctas)
-        backend.count_launch(3)
+        m["rd_epoch"] = self.heap.post(m["chan"] + 3)       # "I have read my slice of everybody's buffer"
+        backend.count_launch(4)
 
     # ------------------------------------------------------------------ Muon transport
     def u_buffer(self, g) -> torch.Tensor:

@@ -45,7 +45,8 @@ from archscale_b200.utils import checkpoint as ckpt
 from archscale_b200.utils import init as init_utils
 from archscale_b200.utils import logging_utils as lu
 from archscale_b200.utils.misc import num_parameters
-from archscale_b200.utils.speed_monitor import DeviceStepTimer, SpeedMonitor, estimate_flops, get_flops_available
+from archscale_b200.utils.speed_monitor import (DeviceStepTimer, SpeedMonitor, estimate_flops, get_flops_available,
+                                                 matmul_parameter_count)
 
 RNG_SEED = 3407
 
@@ -589,10 +590,14 @@ class Trainer:
             self.validate(sanity_check="validation" not in tc)
         if "validation" in tc:
             return
-        n_params = get_parameters_count(p.model_name, p.depth, self.config, tc) if self.config.ar else self.n_params_actual
-        flops_per_batch = estimate_flops(self.config, n_params) * p.micro_batch_size
-        self.print(f"estimated parameters (law): {n_params:,.0f}; actual: {self.n_params_actual:,}; "
-                   f"TFLOPs / micro-batch (all ranks): {flops_per_batch * self.mesh.data_world / 1e12:.2f}")
+        # MFU counts the parameters of the model that runs (non-embedding; routed experts by the fraction a token visits).
+        # The analytic law of the reference (`lit_gpt/config.py:232-265`) assumes the registry shape and is printed beside it.
+        n_law = get_parameters_count(p.model_name, p.depth, self.config, tc) if self.config.ar else float("nan")
+        n_params = matmul_parameter_count(self.model, self.config, tp=self.mesh.tp, ep=self.mesh.ep)
+        flops_per_batch = estimate_flops(self.config, n_params) * p.micro_batch_size / max(self.mesh.tp, 1)
+        self.print(f"parameters in the FLOPs estimate: {n_params:,.0f} (non-embedding, counted); analytic law: {n_law:,.0f}; "
+                   f"all parameters: {self.n_params_actual:,}; "
+                   f"TFLOPs / micro-batch (all ranks): {flops_per_batch * self.mesh.world / 1e12:.2f}")
         world = self.mesh.data_world
         tokens_per_iter = p.micro_batch_size * self.config.block_size
         max_iters = p.train_tokens // world // tokens_per_iter
