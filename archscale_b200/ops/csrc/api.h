@@ -73,10 +73,6 @@ int b200_grouped_gemm_bf16(int kind, const void* A, const void* B, void* out, co
 int b200_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* row_start, int B, int T,
                   int H, int G, int D, int window_left, float scale, int* status, cudaStream_t stream);
 
-// The same on SM pairs (attention_fwd2.cu, head_dim 128 only); b200_attn_fwd dispatches to it.
-int b200_attn_fwd_pair(const void* q, const void* k, const void* v, void* out, float* lse, const int* row_start, int B,
-                       int T, int H, int G, int D, int window_left, float scale, int* status, cudaStream_t stream);
-
 // Attention backward (attention_bwd.cu): δ preprocess + dK/dV kernel + dQ kernel, deterministic.
 // delta: fp32 scratch [B,H,T]; doc_end: optional int32 [B*T] (exclusive end of each position's document).
 int b200_attn_bwd(const void* d_out, const void* q, const void* k, const void* v, const void* out, const float* lse,

@@ -14,8 +14,6 @@
 // KV tiles entirely outside [lo(first row), last row] are skipped.
 //
 // TMEM columns: S0 0..127 | S1 128..255 | P0 256..319 | P1 320..383 | O 384..511.
-#include <stdlib.h>
-#include <string.h>
 #include "sm100.cuh"
 #include "api.h"
 
@@ -327,10 +325,6 @@ extern "C" int b200_attn_fwd(const void* q, const void* k, const void* v, void* 
   using namespace b200;
   if (B <= 0 || T <= 0) return 0;
   if ((D != 64 && D != 128) || H % G) return -1;
-  // head_dim 128 runs on SM pairs (attention_fwd2.cu); ARCHSCALE_B200_ATTN=1cta keeps the one-CTA kernel below
-  static const bool one_cta = [] { const char* e = getenv("ARCHSCALE_B200_ATTN"); return e && !strcmp(e, "1cta"); }();
-  if (D == 128 && !one_cta)
-    return b200_attn_fwd_pair(q, k, v, out, lse, row_start, B, T, H, G, D, window_left, scale, status, stream);
   static thread_local bool ctx_bound = false;
   if (!ctx_bound) {
     int dev = 0;

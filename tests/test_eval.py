@@ -60,3 +60,24 @@ def test_phonebook_prompts_are_reproducible_and_answerable():
     for prompt, label in zip(b1["input"], b1["label"]):
         q = prompt.rsplit("\n", 1)[-1]
         assert q.endswith(":") and f"{q} {label}" in prompt and len(label) == 10
+
+
+def test_reasoning_tasks_extraction_and_pass_at_1():
+    import random
+    from archscale_b200.eval import reasoning as R
+    assert set(R.TASKS) == {"aime24", "aime25", "math_500", "gpqa", "gpqa_diamond"}
+    assert R.TASKS["aime24"].n_samples == 64 and R.TASKS["math_500"].n_samples == 8 and R.TASKS["aime24"].generation_size == 32768
+    d = R.aime_prompt({"problem": "What is 1+1?", "answer": 2})
+    assert d.query.startswith("Please reason step by step, and put your final answer within \\boxed{}.") and d.gold == "2"
+    g = R.gpqa_prompt({"Question": "Q?", "Correct Answer": "yes", "Incorrect Answer 1": "a", "Incorrect Answer 2": "b",
+                       "Incorrect Answer 3": "c"}, rng=random.Random(1))
+    assert g.choices == ["A", "B", "C", "D"] and f"{g.gold}) yes" in g.query
+    assert R.last_boxed("so \\boxed{1} then \\boxed{\\frac{3}{4}}.") == "\\frac{3}{4}"
+    assert R.last_boxed("no box") is None
+    assert R.math_equal("\\dfrac{3}{4}", "the answer is \\boxed{0.75}")
+    assert R.math_equal("1,000", "1000") and R.math_equal("x=5", "5") and not R.math_equal("6", "5")
+    assert R.extract_choice("... \\boxed{(C)}") == "C" and R.extract_choice("Answer: b") == "B"
+    assert R.pass_at_k(8, 2, 1) == 0.25 and R.pass_at_k(4, 4, 1) == 1.0 and R.pass_at_k(4, 0, 1) == 0.0
+    lines = [{"problem": "1+1", "answer": 2}, {"problem": "2+2", "answer": 4}]
+    res = R.evaluate("aime24", lines, lambda prompt, n: ["\\boxed{2}"] * n, n_samples=4)
+    assert res["n_problems"] == 2 and res["pass@1:4_samples"] == 0.5

@@ -41,3 +41,19 @@ def test_activation_budget_loss():
     bce = activation_budget_loss(p2, 0.3, None, loss="bce", mode="per_sequence", lambda_budget=2.0)
     m = p2.clamp(1e-6, 1 - 1e-6).mean(dim=(1, 2))
     assert torch.allclose(bce, 2.0 * F.binary_cross_entropy(m, torch.full_like(m, 0.3)), atol=1e-6)
+
+
+def test_incremental_save_and_lazy_load(tmp_path):
+    import torch
+    from archscale_b200.utils.lazy_ckpt import incremental_save, lazy_load
+    p = tmp_path / "ckpt.pth"
+    a, b, c = torch.randn(5, 7), torch.arange(10, dtype=torch.bfloat16), torch.randn(4, 4)[:, 1:3]
+    with incremental_save(p) as s:
+        tree = {"model": {"a": s.store_early(a), "b": s.store_early(b)}, "late": c, "iter_num": 3,
+                "param": torch.nn.Parameter(torch.ones(2))}
+        s.save(tree)
+    x = torch.load(p, weights_only=True)                 # an ordinary torch checkpoint
+    assert torch.equal(x["model"]["a"], a) and torch.equal(x["model"]["b"], b) and torch.equal(x["late"], c)
+    assert x["iter_num"] == 3 and torch.equal(x["param"], torch.ones(2))
+    with lazy_load(p) as sd:                              # tensors mapped from the file, read on access
+        assert torch.equal(sd["model"]["a"], a) and sd["model"]["b"].dtype == torch.bfloat16
