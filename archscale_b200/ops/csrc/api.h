@@ -73,6 +73,12 @@ int b200_grouped_gemm_bf16(int kind, const void* A, const void* B, void* out, co
 int b200_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* row_start, int B, int T,
                   int H, int G, int D, int window_left, float scale, int* status, cudaStream_t stream);
 
+// Two-stream variant of the forward kernel (attention_fwd2s.cu); same contract.  ARCHSCALE_B200_ATTN_FWD=2stream routes
+// b200_attn_fwd to it.  set_trace: development aid, 16×64 int64 clock stamps of the first CTA, null = off.
+int b200_attn_fwd_2s(const void* q, const void* k, const void* v, void* out, float* lse, const int* row_start, int B, int T,
+                     int H, int G, int D, int window_left, float scale, int* status, cudaStream_t stream);
+void b200_attn_fwd_2s_set_trace(long long* buf);
+
 // Attention backward (attention_bwd.cu): δ preprocess + dK/dV kernel + dQ kernel, deterministic.
 // delta: fp32 scratch [B,H,T]; doc_end: optional int32 [B*T] (exclusive end of each position's document).
 int b200_attn_bwd(const void* d_out, const void* q, const void* k, const void* v, const void* out, const float* lse,
@@ -149,6 +155,8 @@ int b200_gemm_rs_bf16(const void* A, const void* B, int M, int N, int K, int lda
 int b200_muon_momentum(const float* g, float* m, void* u, long long n, float mu, int nesterov, const float* gscale, cudaStream_t st);
 int b200_seg_update(int mode, float* x, const void* u, long long n, const long long* bounds, const int* kidx, int nseg,
                     const float* coef, float* acc, cudaStream_t st);
+int b200_adamw_fused(int mode, float* x, const float* g, float* m, float* v, float* u_out, long long n, float lr, float beta1,
+                     float beta2, float eps, float wd, float bc1, float bc2, const float* gscale, float* acc, cudaStream_t st);
 
 // Gated RMSNorm with groups (gated_norm.cu)
 int b200_gated_rmsnorm_fwd(const void* x, const void* z, const float* w, void* y, float* rstd, int dtype, long long rows, int cols,

@@ -14,6 +14,8 @@
 // KV tiles entirely outside [lo(first row), last row] are skipped.
 //
 // TMEM columns: S0 0..127 | S1 128..255 | P0 256..319 | P1 320..383 | O 384..511.
+#include <stdlib.h>
+#include <string.h>
 #include "sm100.cuh"
 #include "api.h"
 
@@ -325,6 +327,8 @@ extern "C" int b200_attn_fwd(const void* q, const void* k, const void* v, void* 
   using namespace b200;
   if (B <= 0 || T <= 0) return 0;
   if ((D != 64 && D != 128) || H % G) return -1;
+  static const bool two_stream = [] { const char* e = getenv("ARCHSCALE_B200_ATTN_FWD"); return e && !strcmp(e, "2stream"); }();
+  if (two_stream) return b200_attn_fwd_2s(q, k, v, out, lse, row_start, B, T, H, G, D, window_left, scale, status, stream);
   static thread_local bool ctx_bound = false;
   if (!ctx_bound) {
     int dev = 0;

@@ -2,6 +2,8 @@
 //
 //   muon_momentum      m ← mu·m + g·s;  u ← (nesterov ? g·s + mu·m : m) as bf16        (s: optional device scalar, e.g. the
 //                                                                                      gradient-clip coefficient)
+//   adamw_fused        one pass of AdamW over a slice (moments, bias correction, decoupled decay, update), or — for the
+//                      hyperball rule — moments + direction u = m̂/(√v̂ + eps) written out with Σx² and Σu² accumulated
 //   seg_sq_norm        acc[k(i)] += x[i]²                                               segment = one matrix of the flat shard
 //   seg_axpy_sq        x[i] ← x[i] − coef[k(i)]·u[i];  acc[k(i)] += x[i]²               (hyperball step + norm of the result)
 //   seg_scale          x[i] ← x[i]·scale[k(i)]                                          (renormalisation)
@@ -43,6 +45,50 @@ __global__ void __launch_bounds__(OPT_THREADS) muon_momentum_kernel(const float*
     uint2 p;
     p.x = pack_bf16x2(o.x, o.y); p.y = pack_bf16x2(o.z, o.w);
     reinterpret_cast<uint2*>(u)[i] = p;
+  }
+}
+
+// MODE 0: x ← x·(1 − lr·wd) − lr·m̂/(√v̂ + eps).  MODE 1: only the moments change; u_out ← m̂/(√v̂ + eps), acc[0] += Σx², acc[1] += Σu².
+template <int MODE>
+__global__ void __launch_bounds__(OPT_THREADS) adamw_fused_kernel(float* __restrict__ x, const float* __restrict__ g, float* __restrict__ m,
+                                                                 float* __restrict__ v, float* __restrict__ u_out, long long n4, float lr,
+                                                                 float b1, float b2, float eps, float wd, float inv_bc1, float inv_sqrt_bc2,
+                                                                 const float* __restrict__ gscale, float* __restrict__ acc) {
+  const float s = gscale ? *gscale : 1.f;
+  const float decay = 1.f - lr * wd;
+  float sx = 0.f, su = 0.f;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4 gv = reinterpret_cast<const float4*>(g)[i];
+    float4 mv = reinterpret_cast<float4*>(m)[i];
+    float4 vv = reinterpret_cast<float4*>(v)[i];
+    float4 xv = reinterpret_cast<float4*>(x)[i];
+    float ga[4] = {gv.x * s, gv.y * s, gv.z * s, gv.w * s};
+    float ma[4] = {mv.x, mv.y, mv.z, mv.w}, va[4] = {vv.x, vv.y, vv.z, vv.w}, xa[4] = {xv.x, xv.y, xv.z, xv.w}, ua[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      ma[e] += (1.f - b1) * (ga[e] - ma[e]);                       // lerp, as torch._foreach_lerp_
+      va[e] = b2 * va[e] + (1.f - b2) * ga[e] * ga[e];
+      ua[e] = (ma[e] * inv_bc1) / (sqrtf(va[e]) * inv_sqrt_bc2 + eps);
+      if (MODE == 0) xa[e] = xa[e] * decay - lr * ua[e];
+      else { sx += xa[e] * xa[e]; su += ua[e] * ua[e]; }
+    }
+    reinterpret_cast<float4*>(m)[i] = make_float4(ma[0], ma[1], ma[2], ma[3]);
+    reinterpret_cast<float4*>(v)[i] = make_float4(va[0], va[1], va[2], va[3]);
+    if (MODE == 0) reinterpret_cast<float4*>(x)[i] = make_float4(xa[0], xa[1], xa[2], xa[3]);
+    else reinterpret_cast<float4*>(u_out)[i] = make_float4(ua[0], ua[1], ua[2], ua[3]);
+  }
+  if (MODE == 1) {
+    __shared__ float s_acc[2][OPT_THREADS / 32];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { sx += __shfl_xor_sync(0xffffffffu, sx, o); su += __shfl_xor_sync(0xffffffffu, su, o); }
+    if ((threadIdx.x & 31) == 0) { s_acc[0][threadIdx.x >> 5] = sx; s_acc[1][threadIdx.x >> 5] = su; }
+    __syncthreads();
+    if (threadIdx.x < 2) {
+      float t = 0.f;
+      for (int k = 0; k < OPT_THREADS / 32; ++k) t += s_acc[threadIdx.x][k];
+      atomicAdd(&acc[threadIdx.x], t);
+    }
   }
 }
 
@@ -134,5 +180,22 @@ extern "C" int b200_seg_update(int mode, float* x, const void* u, long long n, c
   else if (mode == 1) seg_kernel<1><<<grid, OPT_THREADS, 0, st>>>(x, up, n4, bounds, kidx, nseg, coef, acc);
   else if (mode == 2) seg_kernel<2><<<grid, OPT_THREADS, 0, st>>>(x, up, n4, bounds, kidx, nseg, coef, acc);
   else return -1;
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// One AdamW step over a contiguous fp32 slice (n % 4 == 0, 16-byte aligned pointers).  mode 0: update x in place;
+// mode 1: leave x, write the direction to u_out (fp32) and add Σx², Σu² to acc[0], acc[1].  gscale: device scalar
+// multiplied into the gradient (gradient-clip coefficient) or null.  bc1 = 1 − β1^t, bc2 = 1 − β2^t.
+extern "C" int b200_adamw_fused(int mode, float* x, const float* g, float* m, float* v, float* u_out, long long n, float lr,
+                                float beta1, float beta2, float eps, float wd, float bc1, float bc2, const float* gscale,
+                                float* acc, cudaStream_t st) {
+  if (n % 4 || (mode != 0 && mode != 1) || (mode == 1 && (!u_out || !acc))) return -1;
+  if (n == 0) return 0;
+  const float inv_bc1 = 1.f / bc1, inv_sqrt_bc2 = 1.f / sqrtf(bc2);
+  const unsigned grid = opt_grid_stride(n / 4);
+  if (mode == 0)
+    adamw_fused_kernel<0><<<grid, OPT_THREADS, 0, st>>>(x, g, m, v, nullptr, n / 4, lr, beta1, beta2, eps, wd, inv_bc1, inv_sqrt_bc2, gscale, nullptr);
+  else
+    adamw_fused_kernel<1><<<grid, OPT_THREADS, 0, st>>>(x, g, m, v, u_out, n / 4, lr, beta1, beta2, eps, wd, inv_bc1, inv_sqrt_bc2, gscale, acc);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

@@ -98,6 +98,6 @@ class ShardedMuonBall(ShardedOptimizer):
             torch._foreach_mul_(xs, list(scale[torch.tensor(ks, device=dev)].unbind(0)))
 
     @torch.no_grad()
-    def step(self, lr=None, weight_decay=None) -> None:
+    def step(self, lr=None, weight_decay=None, **kw) -> None:
         self._retract()
-        super().step(lr=lr, weight_decay=0.0)
+        super().step(lr=lr, weight_decay=0.0, **kw)

@@ -150,9 +150,11 @@ class ShardedOptimizer:
     def step(self, lr: Optional[float] = None, weight_decay: Optional[float] = None,
              vector_weight_decay: Optional[float] = None, betas: Optional[Tuple[float, float]] = None,
              eps: Optional[float] = None, vector_betas: Optional[Tuple[float, float]] = None,
-             vector_eps: Optional[float] = None) -> None:
+             vector_eps: Optional[float] = None, grad_scale: Optional[torch.Tensor] = None) -> None:
         """One update.  Every hyper-parameter passed here replaces the stored one from this step on (the trainer
-        recomputes them per iteration: LR schedule, batch ramp-up, independent weight decay, beta schedules)."""
+        recomputes them per iteration: LR schedule, batch ramp-up, independent weight decay, beta schedules).
+        ``grad_scale``: device scalar multiplied into every gradient on the fly (the gradient-clip coefficient of
+        ``FSDPEngine.clip_grad_norm_(..., defer=True)``), so that clipping costs no pass over the gradients."""
         if lr is not None:
             self.lr = lr
         if weight_decay is not None:
@@ -171,6 +173,12 @@ class ShardedOptimizer:
         eng = self.engine
         eng.reload_states()          # no-op unless master / state shards were offloaded to the host
         dev = eng.device
+        fused_ok = eng.is_cuda and ops.backend.has("adamw_fused_")
+        if grad_scale is not None and not (fused_ok and ops.backend.has("muon_momentum_")):
+            # no kernel takes the scale on the fly here (CPU ranks): apply it to the gradient shards once
+            torch._foreach_mul_([g.grad for g in eng.groups() if g.grad is not None], grad_scale)
+            grad_scale = None
+        self._grad_scale = grad_scale
         x_sq = torch.zeros(max(self.n_norm, 1), dtype=torch.float32, device=dev)
         u_sq = torch.zeros_like(x_sq)
         pending_hyper: List[Tuple[torch.Tensor, torch.Tensor, int, float]] = []   # (x_slice, u_slice, norm_idx, lr)
@@ -194,16 +202,36 @@ class ShardedOptimizer:
                 lr_p = self.lr if is_vec_cls or not self.split_groups else self.lr * self.weight_lr_mult
                 wd = self.vector_weight_decay if is_vec_cls else self.weight_decay
                 bt, ep_ = (v_betas, v_eps) if is_vec_cls else (self.betas, self.eps)
+                rule = "nadam" if (self.algorithm == "hadam" and not is_vec_cls) else self.algorithm
+                # one-pass kernel for slices big enough to matter (embedding, head, …); small ones stay on foreach
+                big = (fused_ok and v is not None and n >= (1 << 16) and n % 4 == 0 and slo % 4 == 0 and rule not in ("lion", "nadam")
+                       and x.dtype == torch.float32 and gr.dtype == torch.float32)
                 if id(s) in hyper_idx:
-                    u = scalar_opts.adamw_direction_([m], [v], [gr], bt[0], bt[1], ep_, self.step_count)[0]
-                    if wd:
-                        x.mul_(1 - lr_p * wd)
                     k = hyper_idx[id(s)]
-                    x_sq[k] += x.float().pow(2).sum()
-                    u_sq[k] += u.float().pow(2).sum()
+                    if big and not wd:
+                        u = torch.empty_like(x)
+                        acc2 = torch.zeros(2, dtype=torch.float32, device=dev)
+                        ops.backend.require_extension().adamw_fused_(1, x, gr, m, v, u, lr_p, bt[0], bt[1], ep_, 0.0, self.step_count,
+                                                                     grad_scale, acc2)
+                        ops.backend.count_launch()
+                        x_sq[k] += acc2[0]
+                        u_sq[k] += acc2[1]
+                    else:
+                        if grad_scale is not None:
+                            gr = gr * grad_scale
+                        u = scalar_opts.adamw_direction_([m], [v], [gr], bt[0], bt[1], ep_, self.step_count)[0]
+                        if wd:
+                            x.mul_(1 - lr_p * wd)
+                        x_sq[k] += x.float().pow(2).sum()
+                        u_sq[k] += u.float().pow(2).sum()
                     pending_hyper.append((x, u, k, lr_p))
+                elif big:
+                    ops.backend.require_extension().adamw_fused_(0, x, gr, m, v, None, lr_p, bt[0], bt[1], ep_, wd, self.step_count,
+                                                                 grad_scale, None)
+                    ops.backend.count_launch()
                 else:
-                    rule = "nadam" if (self.algorithm == "hadam" and not is_vec_cls) else self.algorithm
+                    if grad_scale is not None:
+                        gr = gr * grad_scale
                     buckets.setdefault((lr_p, wd, bt, ep_, rule), []).append((x, gr, m, v))
         for (lr_p, wd, bt, ep_, rule), items in buckets.items():
             xs, gs, ms, vs = (list(t) for t in zip(*items))
@@ -386,9 +414,12 @@ class ShardedOptimizer:
                 if (eng.is_cuda and u_shard.dtype == torch.bfloat16 and ms.dtype == torch.float32 and gs.dtype == torch.float32
                         and n_loc % 4 == 0 and ops.backend.has("muon_momentum_")):
                     # one pass: momentum update, Nesterov combination and the bf16 cast of U
-                    ops.backend.require_extension().muon_momentum_(gs, ms, u_shard[:n_loc], self.mu, self.nesterov, None)
+                    ops.backend.require_extension().muon_momentum_(gs, ms, u_shard[:n_loc], self.mu, self.nesterov,
+                                                                   getattr(self, "_grad_scale", None))
                     ops.backend.count_launch()
                 else:
+                    if getattr(self, "_grad_scale", None) is not None:
+                        gs = gs * self._grad_scale
                     ms.mul_(self.mu).add_(gs)
                     if self.nesterov:
                         u_shard[:n_loc].copy_(torch.add(gs, ms, alpha=self.mu))

@@ -646,9 +646,11 @@ class FSDPEngine:
             self.symm.step_barrier()
 
     @torch.no_grad()
-    def clip_grad_norm_(self, max_norm: float, eps: float = 1e-6) -> torch.Tensor:
+    def clip_grad_norm_(self, max_norm: float, eps: float = 1e-6, defer: bool = False):
         """Global L2 norm over all gradient shards (+ scale when above ``max_norm``);
-        the role of ``fabric.clip_gradients`` (`pretrain.py:965-971`)."""
+        the role of ``fabric.clip_gradients`` (`pretrain.py:965-971`).  With ``defer=True`` the gradients are left
+        untouched and ``(norm, coefficient)`` is returned: the optimizer multiplies the coefficient (a device scalar)
+        into the gradients while it reads them (``ShardedOptimizer.step(grad_scale=...)``)."""
         # accumulators indexed [needs a sum over the fsdp group][parameter is split over the tp group]
         sq = [[torch.zeros((), dtype=torch.float32, device=self.device) for _ in range(2)] for _ in range(2)]
         grads = []
@@ -679,11 +681,12 @@ class FSDPEngine:
             split = split.clone()
             du.all_reduce_sum(split, group=self.mesh.tp_group)
         total = torch.sqrt(rep + split)
+        coef = None
         if max_norm is not None and max_norm > 0:
             coef = torch.clamp(max_norm / (total + eps), max=1.0)
-            if grads:
+            if grads and not defer:
                 torch._foreach_mul_(grads, coef)
-        return total
+        return (total, coef) if defer else total
 
     # -- checkpoint support ----------------------------------------------------------
     # Checkpoints hold WHOLE tensors under the model's own key names, whatever the parallel layout that wrote them:

@@ -568,11 +568,11 @@ class Trainer:
         if self.mesh.tp > 1:
             from archscale_b200.parallel.tp import sync_replicated_grads
             sync_replicated_grads(self.engine, self.mesh)
-        gn = self.engine.clip_grad_norm_(self.plan.grad_clip)
-        kw: Dict[str, Any] = {}
+        gn, coef = self.engine.clip_grad_norm_(self.plan.grad_clip, defer=True)      # the optimizer applies the coefficient
+        kw: Dict[str, Any] = {"grad_scale": coef}
         if hparams is not None:
             hv, hm = hparams["vector"], hparams["matrix"]
-            kw = dict(weight_decay=hm["weight_decay"], vector_weight_decay=hv["weight_decay"], betas=hm["betas"],
+            kw.update(weight_decay=hm["weight_decay"], vector_weight_decay=hv["weight_decay"], betas=hm["betas"],
                       eps=hm["eps"], vector_betas=hv["betas"], vector_eps=hv["eps"])
         self.optimizer.step(lr=lr, **kw)
         self.optimizer.zero_grad()

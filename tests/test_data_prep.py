@@ -30,3 +30,44 @@ def test_tokenize_files_round_trip(tmp_path):
     want = np.concatenate([encode(d) for d in docs])
     assert np.array_equal(stream[:len(want)], want[:len(stream)][:len(want)])
     assert (stream[len(want):] == 1).all()
+
+
+def test_mixture_weights_from_inventory(tmp_path):
+    from archscale_b200.data import tools
+    inv = tmp_path / "data_stats.txt"
+    rows = ["L1\tL2\tL3\tL4\tL5\tL6\ttokens\tfiles",
+            "web\t\t\t\t\t\t3B\t10", "web\tcc\t\t\t\t\t2B\t6", "web\twiki\t\t\t\t\t1B\t4", "code\t\t\t\t\t\t500M\t2"]
+    inv.write_text("\n".join(rows) + "\n")
+    leaves = tools.leaf_folders(tools.parse_inventory(str(inv)))
+    assert leaves == {"web/cc": 2e9, "web/wiki": 1e9, "code": 5e8}        # "web" is an inner node
+    w = tools.mixture_weights(leaves, "proportional", suffix="/packed")
+    assert abs(sum(w.values()) - 1) < 1e-12 and abs(w["web/cc/packed"] - 2 / 3.5) < 1e-12
+    ws = tools.mixture_weights(leaves, "sqrt")
+    assert ws["code"] > w["code/packed"]                                   # sqrt flattens the mixture
+    assert set(tools.mixture_weights(leaves, "uniform").values()) == {1 / 3}
+
+
+def test_streaming_shuffle_and_chat_template(tmp_path):
+    import json
+    from archscale_b200.data import tools
+    src = tmp_path / "raw"
+    src.mkdir()
+    for f in range(3):
+        with open(src / f"part{f}.jsonl", "w") as fh:
+            for i in range(40):
+                fh.write(json.dumps({"text": f"doc {f}-{i}"}) + "\n")
+    with open(src / "chat.jsonl", "w") as fh:
+        fh.write(json.dumps({"messages": [{"role": "user", "content": "hi"}, {"role": "assistant", "content": "yo"}]}) + "\n")
+    n = tools.shuffle_corpus(str(src), str(tmp_path / "out"), batch_size=4, buffer_rows=50, seed=0)
+    docs = []
+    for p in sorted((tmp_path / "out").glob("*.jsonl")):
+        docs += [json.loads(l)["text"] for l in open(p)]
+    assert n == len(list((tmp_path / "out").glob("*.jsonl"))) >= 2
+    assert sorted(docs) == sorted([f"doc {f}-{i}" for f in range(3) for i in range(40)] + ["<|user|>\nhi<|end|>\n<|assistant|>\nyo<|end|>\n"])
+    first = docs[:40]
+    assert len({d.split()[1].split("-")[0] for d in first if d.startswith("doc")}) > 1     # files interleave
+    prob, alias = tools.build_alias([3, 0, 1])
+    import random
+    rng = random.Random(0)
+    draws = [tools.sample_alias(prob, alias, rng) for _ in range(4000)]
+    assert draws.count(1) == 0 and 0.70 < draws.count(0) / 4000 < 0.80

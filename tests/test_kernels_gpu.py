@@ -354,3 +354,30 @@ def test_batched_gemm_per_matrix_factors(mode):
     torch.cuda.synchronize()
     assert _ext().device_status() == 0
     assert _rel(out, ref) < 1e-2
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+def test_adamw_fused_matches_foreach(mode):
+    """One-pass AdamW over a flat fp32 slice (with the gradient-clip coefficient folded in) against the foreach formulas."""
+    from archscale_b200.optim import scalar_opts
+    ext = backend.require_extension()
+    torch.manual_seed(0)
+    n = 1 << 18
+    x = torch.randn(n, device="cuda")
+    m, v = torch.randn(n, device="cuda") * 0.1, torch.rand(n, device="cuda") * 0.01
+    g = torch.randn(n, device="cuda")
+    scale = torch.tensor(0.37, device="cuda")
+    xr, mr, vr = x.clone(), m.clone(), v.clone()
+    lr, b1, b2, eps, wd, step = 3e-3, 0.9, 0.95, 1e-8, 0.1, 7
+    if mode == 0:
+        ext.adamw_fused_(0, x, g, m, v, None, lr, b1, b2, eps, wd, step, scale, None)
+        scalar_opts.adamw_update_foreach([xr], [g * scale], [mr], [vr], lr, b1, b2, wd, step, eps)
+        assert torch.allclose(x, xr, atol=1e-6, rtol=1e-5)
+    else:
+        u, acc = torch.empty_like(x), torch.zeros(2, device="cuda")
+        ext.adamw_fused_(1, x, g, m, v, u, lr, b1, b2, eps, 0.0, step, scale, acc)
+        ur = scalar_opts.adamw_direction_([mr], [vr], [g * scale], b1, b2, eps, step)[0]
+        assert torch.equal(x, xr)                                   # mode 1 leaves the parameter alone
+        assert torch.allclose(u, ur, atol=1e-5, rtol=1e-4)
+        assert torch.allclose(acc, torch.stack([xr.pow(2).sum(), ur.pow(2).sum()]), rtol=1e-4)
+    assert torch.allclose(m, mr, atol=1e-6) and torch.allclose(v, vr, atol=1e-7)

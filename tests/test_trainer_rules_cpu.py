@@ -205,3 +205,27 @@ def test_logging_worker_process():
         assert got["step"] == 5 and any(k.startswith("metric/") or k.startswith("optim") or "grad" in k for k in got)
     finally:
         lu.shutdown()
+
+
+def test_deferred_clip_equals_clip_in_place():
+    data = torch.randint(0, 256, (2, 2, 33), generator=torch.Generator().manual_seed(0))
+
+    def run(defer):
+        m, eng, opt = _build("muonh")
+        for s in range(2):
+            out = m(data[s][:, :-1], use_flce_loss=True)
+            eng.backward(fused_linear_cross_entropy(out.logits, out.weight, data[s][:, 1:]) * 50.0)   # large gradients: clip bites
+            if defer:
+                gn, coef = eng.clip_grad_norm_(1.0, defer=True)
+                assert float(coef) < 1.0
+                opt.step(grad_scale=coef)
+            else:
+                gn = eng.clip_grad_norm_(1.0)
+                opt.step()
+            opt.zero_grad()
+        return eng.full_state_dict(), float(gn)
+
+    a, ga = run(False)
+    b, gb = run(True)
+    assert ga == gb
+    assert all(torch.allclose(a[k], b[k], atol=1e-6) for k in a)
