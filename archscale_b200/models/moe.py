@@ -103,7 +103,7 @@ class SonicMoE(nn.Module):
             w_in, w_out = w_in.to(h.dtype), w_out.to(h.dtype)
         if self.ep_size > 1:
             from archscale_b200.parallel import ep
-            routed = ep.moe_ffn_expert_parallel(h, w_in, w_out, scores, indices, self.n_mods, self.ep_group)
+            routed = ep.moe_ffn_expert_parallel(h, w_in, w_out, scores, indices, self.n_mods, self.ep_group, site=id(self))
         else:
             routed = ops.moe_ffn(h, w_in, w_out, scores.to(h.dtype), indices, b_in, b_out)
         with torch.no_grad():

@@ -78,6 +78,7 @@ int b200_attn_fwd(const void* q, const void* k, const void* v, void* out, float*
 int b200_attn_fwd_2s(const void* q, const void* k, const void* v, void* out, float* lse, const int* row_start, int B, int T,
                      int H, int G, int D, int window_left, float scale, int* status, cudaStream_t stream);
 void b200_attn_fwd_2s_set_trace(long long* buf);
+void b200_attn_bwd_set_trace(long long* buf);       // same aid for the dK/dV kernel: 8×64 stamps
 
 // Attention backward (attention_bwd.cu): δ preprocess + dK/dV kernel + dQ kernel, deterministic.
 // delta: fp32 scratch [B,H,T]; doc_end: optional int32 [B*T] (exclusive end of each position's document).

@@ -38,7 +38,9 @@ struct AttnBwdParams {
   int window_left;
   float scale, scale_log2;
   int* status;
+  long long* trace;        // optional [8][64] clock64 stamps of the first dK/dV CTA (development aid, null in normal use)
 };
+#define BWD_TRACE(ev, hx) do { if (p.trace && traced && (hx) < 64) p.trace[(ev) * 64 + (hx)] = clock64(); } while (0)
 
 __device__ __forceinline__ int lo_of_row(const AttnBwdParams& p, int b, int r) {
   int lo = p.row_start ? p.row_start[static_cast<size_t>(b) * p.T + r] : 0;
@@ -346,6 +348,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const int tiles_per_head = i_end - i_begin;
   const int n_iter = tiles_per_head * group;
   const int n_half = 2 * n_iter;
+  const bool traced = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0;
 
   if (threadIdx.x == 0) {
     mbar_init(fixed_full, 1);
@@ -409,8 +412,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         return true;
       };
       for (int hx = 0; hx < n_half; ++hx) {
+        if (!is_dp) BWD_TRACE(3, hx);
         if (hx >= 2 && !mbar_wait(&buf_free[hx & 1], ((hx - 2) >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) goto done;
         if (!issue_one(hx)) goto done;
+        if (!is_dp) BWD_TRACE(4, hx);
       }
     }
   } else if (warp == ACC_WARP) {
@@ -418,8 +423,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       constexpr uint32_t idesc_acc = make_idesc_bf16(BT, D, 0, 1);      // dV += Pᵀ·dO, dK += dSᵀ·Q (N-major B)
       for (int hx = 0; hx < n_half; ++hx) {
         const int it = hx >> 1, hf = hx & 1, st = it & 1, buf = hx & 1;
+        BWD_TRACE(5, hx);
         if (!mbar_wait(&ds_full[buf], (hx >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
         tc_fence_after();
+        BWD_TRACE(6, hx);
         const uint32_t sqa = smem_u32(ring + st * 2 * SM::TILE), sdoa = sqa + SM::TILE;
         const uint32_t ts = tmem_base + buf * 128, tdp = ts + 64;
 #pragma unroll
@@ -431,6 +438,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
         umma_commit(&buf_free[buf]);
         if (hf == 1) umma_commit(&qd_empty[st]);
+        BWD_TRACE(7, hx);
       }
       umma_commit(acc_done);
     }
@@ -452,6 +460,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       float* a_lse = aux + st * 3 * BT;
       float* a_dlt = a_lse + BT;
       int* a_lo = reinterpret_cast<int*>(a_dlt + BT);
+      if (qtr == 0) BWD_TRACE(0, hx);
       if (ok && tid128 < HB) {
         const int col = hf * HB + tid128;
         const int rq = q0 + col;
@@ -465,6 +474,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       if (!ok) continue;
       if (!mbar_wait(&sdp_full[buf], (hx >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) { ok = false; continue; }
       tc_fence_after();
+      if (qtr == 0) BWD_TRACE(1, hx);
       const float sl2 = p.scale_log2;
       // every (key, query) pair of the tile is visible: queries at or after the last key, no window / document bound
       const bool full_tile = plain_causal && q0 >= k0 + BT - 1 && q0 + BT <= p.T;
@@ -517,6 +527,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ds_full[buf]);
+      if (qtr == 0) BWD_TRACE(2, hx);
     }
     if (!ok) goto done;
     if (!mbar_wait(acc_done, 0, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
@@ -580,6 +591,9 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const CUten
 
 }  // namespace b200
 
+static long long* g_attn_bwd_trace = nullptr;
+extern "C" void b200_attn_bwd_set_trace(long long* buf) { g_attn_bwd_trace = buf; }
+
 extern "C" int b200_attn_bwd(const void* d_out, const void* q, const void* k, const void* v, const void* out,
                              const float* lse, float* delta, const int* row_start, const int* doc_end, void* dq, void* dk,
                              void* dv, int B, int T, int H, int G, int D, int window_left, float scale, int* status,
@@ -608,6 +622,6 @@ extern "C" int b200_attn_bwd(const void* d_out, const void* q, const void* k, co
   rc = make_tmap_2d_bf16(&tv, v, gd, bt, gd, 64, 128);
   if (rc) return rc;
   AttnBwdParams p{lse, delta, row_start, doc_end, (__nv_bfloat16*)dq, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv,
-                  B, T, H, G, window_left, scale, scale * kLog2e_b, status};
+                  B, T, H, G, window_left, scale, scale * kLog2e_b, status, g_attn_bwd_trace};
   return D == 128 ? launch_bwd<128>(tq, tdo, tk, tv, p, stream) : launch_bwd<64>(tq, tdo, tk, tv, p, stream);
 }

@@ -239,7 +239,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       Tile2 tl; get_tile(t, tl);
       const int m0 = tl.m0, n0 = tl.n0;
       const bool empty_tile = tl.kb0 == tl.kb1;
-      const int row_limit = GROUPED == 1 ? s_off[gp.E] : p.M;
+      const int row_limit = GROUPED == 1 ? min(s_off[gp.E], p.M) : p.M;     // never past the rows the caller allocated
       const int acc = it & 1; const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
       tc_fence_after();

@@ -382,7 +382,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tc_fence_after();
       const int row = tl.m0 + q * 32 + lane;
       const int col0 = tl.n0;
-      const int row_limit = GROUPED == 1 ? s_off[gp.E] : p.M;
+      const int row_limit = GROUPED == 1 ? min(s_off[gp.E], p.M) : p.M;     // never past the rows the caller allocated
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
       int acc_flag = p.accumulate;
       if (OUT_F32 && SK > 1) {

@@ -141,29 +141,63 @@ class PeerDispatcher:
         self.offsets = self.heap.tensor(self.off_offsets, (n_experts + 1,), torch.int32)
         self.table = self.heap.tensor(self.off_table, (self.world, self.e_local), torch.int32)
         self.chan = 0
+        self.stats = {}                                  # call site → rows received there on earlier steps
+        self.margin = float(os.environ.get("ARCHSCALE_B200_EP_MARGIN", "1.25"))
 
     def exchange(self) -> None:
         self.heap.barrier(self.chan)
 
-    def receive(self, e_local: int) -> tuple:
-        """Plan + pull: returns (rows received [used, C] in local memory, recv_offsets).  One 4-byte
-        device→host read sizes the buffers exactly (the reference reads all counts per layer)."""
-        recv_off = self.ext.ep_plan(self.heap.bases, self.off_counts, self.off_table, self.rank, e_local, self.recv_cap)
-        used = int(recv_off[-1].item())
-        if used > self.recv_cap:
-            raise RuntimeError(f"expert-parallel receive overflow: {used} rows > capacity {self.recv_cap}; "
-                               "raise ARCHSCALE_B200_EP_CAPACITY")
-        rows = torch.empty(max(used, 256), self.C, dtype=torch.bfloat16, device=self.device)
+    def _rows_to_allocate(self, key) -> Optional[int]:
+        """Rows to allocate for what this rank is about to receive at call site ``key``, from the counts seen there on
+        earlier steps (read back asynchronously, never waited for); None while there is no estimate yet."""
+        st = self.stats[key]
+        if st["event"] is not None and st["event"].query():
+            st["seen"] = max(int(st["pinned"].item()), int(st["seen"] * 0.98))      # slow decay after a spike
+            st["event"] = None
+        if st["seen"] <= 0:
+            return None
+        want = int(st["seen"] * self.margin) + 2 * 256
+        return min(((want + 255) // 256) * 256, self.recv_cap)
+
+    def receive(self, e_local: int, key=None) -> tuple:
+        """Plan + pull: returns (rows received, in local memory; recv_offsets).
+
+        The buffer is sized from the row counts this call site (``key``: one MoE layer, forward or backward) received on
+        earlier steps plus a margin — a device-side bound, no device→host wait in the step.  The plan kernel compares
+        the real total with that size: on overflow it raises the device status word, the pull copies nothing and the
+        grouped GEMMs never store past the buffer, so the step computes garbage but touches no foreign memory; the
+        trainer reads the status word before the optimizer step and stops.  The first two calls of a site read the
+        count on the host once (there is nothing to estimate from yet)."""
+        st = self.stats.setdefault(key, {"seen": 0, "event": None, "calls": 0,
+                                         "pinned": torch.zeros(1, dtype=torch.int32).pin_memory()})
+        st["calls"] += 1
+        cap = self._rows_to_allocate(key) if st["calls"] > 2 else None
+        recv_off = self.ext.ep_plan(self.heap.bases, self.off_counts, self.off_table, self.rank, e_local,
+                                    self.recv_cap if cap is None else cap)
+        if cap is None:
+            # start-up: routing moves fastest right after initialisation, and there is no history yet
+            used = int(recv_off[-1].item())
+            if used > self.recv_cap:
+                raise RuntimeError(f"expert-parallel receive overflow: {used} rows > capacity {self.recv_cap}; "
+                                   "raise ARCHSCALE_B200_EP_CAPACITY")
+            st["seen"] = max(st["seen"], used, 1)
+            cap = max(((used + 255) // 256) * 256, 256)
+        elif st["event"] is None:
+            st["pinned"].copy_(recv_off[-1:], non_blocking=True)       # read by a later call, never waited for
+            st["event"] = torch.cuda.Event()
+            st["event"].record()
+        rows = torch.empty(cap, self.C, dtype=torch.bfloat16, device=self.device)
         self.ext.ep_pull(self.heap.bases, self.off_counts, self.off_offsets, self.off_table, self.off_send[0], rows,
                          self.rank, e_local, recv_off)
         return rows, recv_off
 
 
 class _EPPeerFn(torch.autograd.Function):
-    """Expert-parallel routed FFN with peer-memory dispatch / combine (no NCCL, no host sync)."""
+    """Expert-parallel routed FFN with peer-memory dispatch / combine (no NCCL; no host wait after a layer's first two
+    calls — see :meth:`PeerDispatcher.receive`)."""
 
     @staticmethod
-    def forward(ctx, h, w_in, w_out, scores, indices, n_experts, group):
+    def forward(ctx, h, w_in, w_out, scores, indices, n_experts, group, site=None):
         ext = backend.require_extension()
         N, C = h.shape
         K = indices.shape[1]
@@ -177,7 +211,8 @@ class _EPPeerFn(torch.autograd.Function):
         d.offsets.copy_(offsets)
         ext.gather_rows(h, slot_pair, None, K, offsets, d.send[0])
         d.exchange()                                                       # every rank's rows and counts are published
-        xr, recv_off = d.receive(E_l)
+        xr, recv_off = d.receive(E_l, key=(site, "fwd"))
+        ctx.site = site
         h1 = ext.grouped_gemm_bf16(0, xr, w_in.reshape(E_l * I2, C), recv_off, 0, I2, C)
         a = ext.swiglu_packed_fwd(h1)
         ext.grouped_gemm_bf16(0, a, w_out.reshape(E_l * C, I), recv_off, 0, C, I, None, d.result)
@@ -203,7 +238,7 @@ class _EPPeerFn(torch.autograd.Function):
         d.offsets.copy_(offsets)
         ext.gather_rows(dout, slot_pair, sc.reshape(-1), K, offsets, d.send[0])      # dy[slot] = score · dout[token]
         d.exchange()
-        dyr, recv_off = d.receive(E_l)
+        dyr, recv_off = d.receive(E_l, key=(ctx.site, "bwd"))
         a = ext.swiglu_packed_fwd(h1)
         da = ext.grouped_gemm_bf16(1, dyr, w_out.reshape(E_l * C, I), recv_off, 0, I, C)
         mg_out = getattr(ctx.w_refs[1], "main_grad", None)
@@ -217,7 +252,7 @@ class _EPPeerFn(torch.autograd.Function):
         ext.ep_return(d.heap.bases, d.off_counts, d.off_offsets, d.off_table, d.off_result, dxs, d.rank, E_l, C)
         dx = ext.combine_rows(dxs, pair_slot, None, N, K)
         backend.count_launch(14)
-        return dx, (None if mg_in is not None else dw_in), (None if mg_out is not None else dw_out), dscores, None, None, None
+        return dx, (None if mg_in is not None else dw_in), (None if mg_out is not None else dw_out), dscores, None, None, None, None
 
 
 def peer_path_supported(h, w_in, w_out) -> bool:
@@ -228,10 +263,11 @@ def peer_path_supported(h, w_in, w_out) -> bool:
 USE_PEER_TRANSPORT = True
 
 
-def moe_ffn_expert_parallel(h, w_in, w_out, scores, indices, n_experts: int, group) -> torch.Tensor:
-    """Routed expert FFN with experts sharded over ``group``.  h:(N,C); w_in:(E_l,2I,C); w_out:(E_l,C,I)."""
+def moe_ffn_expert_parallel(h, w_in, w_out, scores, indices, n_experts: int, group, site=None) -> torch.Tensor:
+    """Routed expert FFN with experts sharded over ``group``.  h:(N,C); w_in:(E_l,2I,C); w_out:(E_l,C,I).
+    ``site``: any hashable that names the calling layer (receive buffers are sized from that layer's own history)."""
     if group is None or dist.get_world_size(group) == 1:
         return ops.moe_ffn(h, w_in, w_out, scores.to(h.dtype), indices)
     if USE_PEER_TRANSPORT and dist.get_world_size(group) <= 8 and peer_path_supported(h, w_in, w_out):
-        return _EPPeerFn.apply(h, w_in, w_out, scores, indices, n_experts, group)
+        return _EPPeerFn.apply(h, w_in, w_out, scores, indices, n_experts, group, site)
     return _moe_ffn_all_to_all(h, w_in, w_out, scores, indices, n_experts, group)
