@@ -112,11 +112,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   uint64_t* fixed_full = bars;      // 1
   uint64_t* kv_full = bars + 1;     // [2]
   uint64_t* kv_empty = bars + 3;    // [2]
-  uint64_t* sdp_full = bars + 5;    // [2]  S and dP of a half are in TMEM buffer b
-  uint64_t* ds_full = bars + 7;     // [2]  (count 4) dS of buffer b written by its warp group
-  uint64_t* acc_done = bars + 9;    // 1    all dQ MMAs finished
-  uint64_t* buf_free = bars + 10;   // [2]  accumulation MMAs that read buffer b have completed
-  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 12);
+  // The dQ accumulator takes 128 of the 512 tensor-memory columns, which leaves room for THREE (S, dP) half-tile buffers:
+  // a buffer's cycle (products → softmax → accumulation → free) is latency-bound, so three in flight instead of two
+  // raise the rate at which halves complete.  Half hx lives in buffer hx % 3; warp group hx % 2 converts it.
+  uint64_t* sdp_full = bars + 5;    // [3]  S and dP of a half are in TMEM buffer b
+  uint64_t* ds_full = bars + 8;     // [3]  (count 4) dS of buffer b written by a warp group
+  uint64_t* acc_done = bars + 11;   // 1    all dQ MMAs finished
+  uint64_t* buf_free = bars + 12;   // [3]  accumulation MMAs that read buffer b have completed
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -132,10 +135,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(fixed_full, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1);
-      mbar_init(&sdp_full[s], 2); mbar_init(&ds_full[s], 4); mbar_init(&buf_free[s], 1);
-    }
+    for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    for (int s = 0; s < 3; ++s) { mbar_init(&sdp_full[s], 2); mbar_init(&ds_full[s], 4); mbar_init(&buf_free[s], 1); }
     mbar_init(acc_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -145,7 +146,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr;
-  const uint32_t T_DQ = tmem_base + 256;            // buffers: S[b] = base + 128 b, dP[b] = base + 128 b + 64
+  const uint32_t T_DQ = tmem_base + 384;            // buffers b = 0..2: S[b] = base + 128 b, dP[b] = base + 128 b + 64
 
   if (warp == 0) {
     if (lane == 0) {
@@ -179,7 +180,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       const uint32_t sa = smem_u32(is_dp ? sdo : sq);
       // keys hf·64.. of the tile: rows 8192 bytes into each 64-column chunk
       auto issue_one = [&](int hx) -> bool {
-        const int t = hx >> 1, hf = hx & 1, st = t & 1, buf = hx & 1;
+        const int t = hx >> 1, hf = hx & 1, st = t & 1, buf = hx % 3;
         if (hf == 0 && !mbar_wait(&kv_full[st], (t >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_FULL)) return false;
         tc_fence_after();
         const uint32_t sb = smem_u32(ring + st * 2 * SM::TILE) + hf * 8192 + (is_dp ? SM::TILE : 0);
@@ -195,7 +196,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       // buf_free[b] orders the reuse of buffer b: S, dP of half hx+2 may overwrite it once the accumulation MMAs of half hx
       // (which read dS from it) have completed.
       for (int hx = 0; hx < n_half; ++hx) {
-        if (hx >= 2 && !mbar_wait(&buf_free[hx & 1], ((hx - 2) >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) goto done;
+        if (hx >= 3 && !mbar_wait(&buf_free[hx % 3], ((hx - 3) / 3) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) goto done;
         if (!issue_one(hx)) goto done;
       }
     }
@@ -203,8 +204,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     if (lane == 0) {
       constexpr uint32_t idesc_dq = make_idesc_bf16(BT, D, 0, 1);        // dQ += dS·K, K is N-major
       for (int hx = 0; hx < n_half; ++hx) {
-        const int t = hx >> 1, hf = hx & 1, st = t & 1, buf = hx & 1;
-        if (!mbar_wait(&ds_full[buf], (hx >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
+        const int t = hx >> 1, hf = hx & 1, st = t & 1, buf = hx % 3;
+        if (!mbar_wait(&ds_full[buf], (hx / 3) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
         tc_fence_after();
         const uint32_t sk = smem_u32(ring + st * 2 * SM::TILE);
         const uint32_t tdp = tmem_base + buf * 128 + 64;
@@ -227,12 +228,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const float lse2 = row_valid ? p.lse[stat_idx] * kLog2e_b : 0.f;
     const float dlt = row_valid ? p.delta[stat_idx] : 0.f;
     const uint32_t lane_off = static_cast<uint32_t>(qtr * 32) << 16;
-    // Ping-pong: warp group `ch` owns the halves with hx & 1 == ch (buffer ch) and converts all 64 columns of such a half,
+    // Ping-pong: warp group `ch` owns the halves with hx & 1 == ch (in buffer hx % 3) and converts all 64 columns of such a half,
     // so the load → exp2 → store chains of two consecutive halves overlap instead of running back to back.
     for (int hx = ch; hx < n_half; hx += 2) {
-      const int t = hx >> 1, hf = hx & 1, buf = hx & 1;
+      const int t = hx >> 1, hf = hx & 1, buf = hx % 3;
       const int kt0 = (j_begin + t) * BT;
-      if (!mbar_wait(&sdp_full[buf], (hx >> 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
+      if (!mbar_wait(&sdp_full[buf], (hx / 3) & 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
       tc_fence_after();
       const bool full_tile = (kt0 + BT - 1 <= q0) && (kt0 >= lo_last);
       const float sl2 = p.scale_log2;

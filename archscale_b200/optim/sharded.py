@@ -81,6 +81,11 @@ class ShardedOptimizer:
         self._classify()
         self.last_lrs: Dict[str, float] = {}
         self._norm_idx_cache: Dict[tuple, torch.Tensor] = {}
+        # MuonH keeps every matrix on its sphere: after the renormalisation ‖X‖ is what it was before the step, so the
+        # squared norms measured once stay valid until weights are loaded or weight decay shrinks them (one pass over
+        # all master weights saved per step)
+        self._xsq_cache: Optional[torch.Tensor] = None
+        self._xsq_version = -1
 
     # ------------------------------------------------------------------ setup
     def _classify(self) -> None:
@@ -253,6 +258,8 @@ class ShardedOptimizer:
         hb_lr: List[float] = [t[3] for t in pending_hyper]
         seg_groups: List[Tuple[torch.Tensor, torch.Tensor, dict]] = []   # (master prefix, O prefix, tables): fused path
         lr_m = self._lr_for("matrix")
+        xsq_cached = (self.use_muonh and not self.weight_decay and self._xsq_cache is not None
+                      and self._xsq_version == getattr(eng, "master_version", 0))
         if self.mats:
             o_shards = self._orthogonalised_updates(u_sq)
             wd = self.weight_decay
@@ -283,8 +290,9 @@ class ShardedOptimizer:
                 if wd:
                     torch._foreach_mul_(xs, 1 - lr_m * wd)
                 if self.use_muonh:
-                    sq = torch.stack(torch._foreach_norm(xs)).square()
-                    x_sq.index_add_(0, torch.tensor(ks, device=dev), sq)
+                    if not xsq_cached:
+                        sq = torch.stack(torch._foreach_norm(xs)).square()
+                        x_sq.index_add_(0, torch.tensor(ks, device=dev), sq)
                     hb_x += xs
                     hb_u += os_
                     hb_k += ks
@@ -295,8 +303,9 @@ class ShardedOptimizer:
             if seg_groups:
                 ext = ops.backend.require_extension()
                 if self.use_muonh:
-                    for x, _, tb in seg_groups:
-                        ext.seg_update_(0, x, None, tb["bounds"], tb["kidx"], None, x_sq)
+                    if not xsq_cached:
+                        for x, _, tb in seg_groups:
+                            ext.seg_update_(0, x, None, tb["bounds"], tb["kidx"], None, x_sq)
                 else:
                     for x, o, tb in seg_groups:          # plain Muon: x ← x − lr·sqrt(rows/cols)·O
                         ext.seg_update_(1, x, o, tb["bounds"], tb["kidx"], self._adjusted_lr_vector(lr_m), self._scratch_acc())
@@ -312,6 +321,12 @@ class ShardedOptimizer:
                 if keep is not None:
                     packed[:, self.local_norm_idx] = keep
                 x_sq, u_sq = packed[0], packed[1]
+            if self.use_muonh and not self.weight_decay and self.mats:
+                mat_idx = self._mat_norm_idx(dev)
+                if xsq_cached:
+                    x_sq[mat_idx] = self._xsq_cache[mat_idx]
+                else:
+                    self._xsq_cache, self._xsq_version = x_sq.clone(), getattr(eng, "master_version", 0)
             x_norm, u_norm = x_sq.sqrt(), u_sq.sqrt().clamp_min(self.ns_epsilon)
             ratio = x_norm / u_norm
             new_sq = torch.zeros_like(x_sq)
@@ -371,6 +386,11 @@ class ShardedOptimizer:
         cache[id(g)] = tb
         return tb
 
+    def _mat_norm_idx(self, dev) -> torch.Tensor:
+        if getattr(self, "_mat_idx_t", None) is None:
+            self._mat_idx_t = torch.tensor(sorted({mt.norm_idx for mt in self.mats}), dtype=torch.long, device=dev)
+        return self._mat_idx_t
+
     def _adjusted_lr_vector(self, lr_m: float) -> torch.Tensor:
         """Per-matrix step sizes (slot = norm index) for the plain-Muon fused update."""
         v = torch.zeros(max(self.n_norm, 1), dtype=torch.float32)
@@ -403,11 +423,11 @@ class ShardedOptimizer:
             m = self.m[gid]
             mask_mats = [mt for mt in self.mats if mt.group is g]
             a, b = g.shard_range()
+            # only the matrix ranges of U are ever read (by the owners' Newton–Schulz batches): the tail needs no fill
             if eng.symm is not None and g.world > 1:
                 u_shard = eng.symm.u_buffer(g)
-                u_shard.zero_()
             else:
-                u_shard = torch.zeros(g.shard_numel, dtype=cdt, device=eng.device)
+                u_shard = torch.empty(g.shard_numel, dtype=cdt, device=eng.device)
             n_loc = min(b, g.matrix_numel) - a
             if n_loc > 0:
                 ms, gs = m[:n_loc], g.grad[:n_loc]
@@ -509,13 +529,21 @@ class ShardedOptimizer:
                     if keep:
                         state.setdefault(s.name, {})[key] = t.cpu().clone()
                 del full
+        extra = {}
+        if self._xsq_cache is not None and self._xsq_version == getattr(eng, "master_version", 0):
+            extra["muonh_sq_norms"] = self._xsq_cache.cpu()      # so that a resumed run keeps projecting onto the same spheres
         return {"state": state, "step": self.step_count, "algorithm": self.algorithm,
-                "nadam_mu_product": self.nadam_mu_product} if keep else {}
+                "nadam_mu_product": self.nadam_mu_product, **extra} if keep else {}
 
     @torch.no_grad()
     def load_state_dict(self, sd: Dict) -> None:
         self.step_count = int(sd.get("step", 0))
         self.nadam_mu_product = float(sd.get("nadam_mu_product", 1.0))
+        self._xsq_cache = None
+        sq = sd.get("muonh_sq_norms")
+        if sq is not None and sq.numel() == max(self.n_norm, 1):
+            self._xsq_cache = sq.to(self.engine.device, torch.float32)
+            self._xsq_version = getattr(self.engine, "master_version", 0)
         self.engine.reload_states()
         state = sd.get("state", {})
         for g in self.engine.groups():

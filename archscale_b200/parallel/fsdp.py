@@ -773,6 +773,7 @@ class FSDPEngine:
     def load_full_state_dict(self, sd: Dict[str, torch.Tensor], strict: bool = True) -> None:
         missing = []
         self.reload_states()
+        self.master_version = getattr(self, "master_version", 0) + 1      # cached norms of the old weights are void
         for g in self.groups():
             for s, lo, hi, slo in g.local_slices():
                 if s.name not in sd:
