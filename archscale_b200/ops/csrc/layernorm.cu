@@ -145,13 +145,11 @@ __global__ void __launch_bounds__(256) layernorm_bwd_kernel(const T* __restrict_
   for (int c = threadIdx.x; c < 2 * cols; c += blockDim.x) part[static_cast<size_t>(blockIdx.x) * 2 * cols + c] = ln_s[c];
 }
 
-__global__ void layernorm_reduce_kernel(const float* __restrict__ part, float* __restrict__ dw, float* __restrict__ db, int n,
-                                        int cols) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= 2 * cols) return;
-  float s = 0.f;
-  for (int i = 0; i < n; ++i) s += part[static_cast<size_t>(i) * 2 * cols + c];
-  if (c < cols) dw[c] = s; else db[c - cols] = s;
+__global__ void __launch_bounds__(1024) layernorm_reduce_kernel(const float* __restrict__ part, float* __restrict__ dw, float* __restrict__ db,
+                                                                int n, int cols) {
+  const float t = column_sum_block(part, n, 2 * cols);
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  if (threadIdx.x < 32 && c < 2 * cols) { if (c < cols) dw[c] = t; else db[c - cols] = t; }
 }
 
 }  // namespace b200
@@ -187,6 +185,6 @@ extern "C" int b200_layernorm_bwd(const void* dy, const void* x, int dtype, cons
   if (nch <= 4) LN_D(4) else if (nch <= 8) LN_D(8) else LN_D(10)
 #undef LN_D
 #undef LN_L
-  layernorm_reduce_kernel<<<(2 * cols + 255) / 256, 256, 0, st>>>(part, dw, db, grid, cols);
+  layernorm_reduce_kernel<<<(2 * cols + 31) / 32, 1024, 0, st>>>(part, dw, db, grid, cols);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

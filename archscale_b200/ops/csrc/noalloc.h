@@ -22,6 +22,9 @@
 //    to start at zero (every CTA overwrites its own row before the reduction reads it), but two
 //    calls that overlap on the GPU (different streams) race on it: serialise them.
 //  * It calls no cudaMalloc / cudaFree and no allocating library routine.
+//  * The cached device addresses and the last-error string are plain process globals without locks:
+//    concurrent first calls from several host threads, or reading the error string while another
+//    thread's call fails, are the caller's to serialise.
 #pragma once
 #include <cuda_runtime.h>
 

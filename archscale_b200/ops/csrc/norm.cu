@@ -119,12 +119,10 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const TDY* __restrict_
   }
 }
 
-__global__ void reduce_partials_kernel(const float* __restrict__ part, float* __restrict__ out, int n, int cols) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
-  float s = 0.f;
-  for (int i = 0; i < n; ++i) s += part[static_cast<size_t>(i) * cols + c];
-  out[c] = s;
+__global__ void __launch_bounds__(1024) reduce_partials_kernel(const float* __restrict__ part, float* __restrict__ out, int n, int cols) {
+  const float t = column_sum_block(part, n, cols);
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  if (threadIdx.x < 32 && c < cols) out[c] = t;
 }
 
 
@@ -214,7 +212,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_bwd_kernel(const float* __res
 #pragma unroll
         for (int e = 0; e < 8; ++e) o[e] += gr[e];
       }
-      Vec8<float>::store(d_res + base + c, o);
+      if (d_res) Vec8<float>::store(d_res + base + c, o);
       if (d_h) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) o[e] *= h_scale;
@@ -265,11 +263,21 @@ extern "C" int b200_rmsnorm_bwd_partials(int rows, int cols) {
   return need < kBwdCtas ? need : kBwdCtas;
 }
 
+extern "C" int b200_add_rmsnorm_bwd(const float* g_res, const void* g_n, const void* x, int x_dtype, const void* w, int w_dtype,
+                                    const float* rstd, float* d_res, void* d_h, float h_scale, float* dw_partial, float* dw,
+                                    int rows, int cols, cudaStream_t stream);
+
 extern "C" int b200_rmsnorm_bwd(const void* dy, int dy_dtype, const void* x, int x_dtype, const void* w, int w_dtype,
                                 const float* rstd, void* dx, float* dw_partial, float* dw, int rows, int cols,
                                 cudaStream_t stream) {
   if (rows == 0) return 0;
   if (cols % 8) return -1;
+  // bf16 upstream gradient, a weight and one of the model widths: the kernel of the fused residual-add variant (weight
+  // gradient accumulated in registers, one shared-memory add per column and CTA instead of one per element) does this job
+  // with no residual gradient: dx is its bf16 output for bf16 x, its fp32 output for fp32 x
+  if (dy_dtype == 1 && w && (cols == 1024 || cols == 2048 || cols == 2560 || cols == 3072 || cols == 4096))
+    return b200_add_rmsnorm_bwd(nullptr, dy, x, x_dtype, w, w_dtype, rstd, x_dtype == 0 ? static_cast<float*>(dx) : nullptr,
+                                x_dtype == 1 ? dx : nullptr, 1.f, dw_partial, dw, rows, cols, stream);
   const int grid = b200_rmsnorm_bwd_partials(rows, cols);
   const size_t smem = w ? sizeof(float) * cols : 0;
 #define CALL(TDY, TW, TX)                                                                                     \
@@ -281,7 +289,7 @@ extern "C" int b200_rmsnorm_bwd(const void* dy, int dy_dtype, const void* x, int
   }
   DISPATCH_3(dy_dtype, w_dtype, x_dtype, CALL)
 #undef CALL
-  if (w) reduce_partials_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(dw_partial, dw, grid, cols);
+  if (w) reduce_partials_kernel<<<(cols + 31) / 32, 1024, 0, stream>>>(dw_partial, dw, grid, cols);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -338,6 +346,6 @@ extern "C" int b200_add_rmsnorm_bwd(const float* g_res, const void* g_n, const v
   }
 #undef LN
 #undef L
-  reduce_partials_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(dw_partial, dw, grid, cols);
+  reduce_partials_kernel<<<(cols + 31) / 32, 1024, 0, stream>>>(dw_partial, dw, grid, cols);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

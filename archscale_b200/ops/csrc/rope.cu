@@ -198,12 +198,11 @@ __global__ void __launch_bounds__(256) qknorm_rope_bwd_kernel(
   }
 }
 
-__global__ void qk_dw_reduce_kernel(const float* __restrict__ part, float* __restrict__ dqw, float* __restrict__ dkw, int n, int D) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= 2 * D) return;
-  float s = 0.f;
-  for (int b = 0; b < n; ++b) s += part[static_cast<size_t>(b) * 2 * D + i];
-  if (i < D) dqw[i] = s; else dkw[i - D] = s;
+// partials are [n, 2·D]: columns 0..D−1 belong to dqw, D..2D−1 to dkw
+__global__ void __launch_bounds__(1024) qk_dw_reduce_kernel(const float* __restrict__ part, float* __restrict__ dqw, float* __restrict__ dkw, int n, int D) {
+  const float t = column_sum_block(part, n, 2 * D);
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  if (threadIdx.x < 32 && c < 2 * D) { if (c < D) dqw[c] = t; else dkw[c - D] = t; }
 }
 
 constexpr int kRopeGrid = 148 * 8;
@@ -243,6 +242,6 @@ extern "C" int b200_qknorm_rope_bwd(const void* dqo, const void* dko, const void
   else if (D == 64) { if (w_dtype == 1) LAUNCH(2, bf16); else LAUNCH(2, float); }
   else return -1;
 #undef LAUNCH
-  if (qw) qk_dw_reduce_kernel<<<(2 * D + 127) / 128, 128, 0, st>>>(dw_partial, dqw, dkw, kRopeGrid, D);
+  if (qw) qk_dw_reduce_kernel<<<(2 * D + 31) / 32, 1024, 0, st>>>(dw_partial, dqw, dkw, kRopeGrid, D);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

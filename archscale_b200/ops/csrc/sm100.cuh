@@ -283,6 +283,37 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, int a_mn_ma
          (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
 }
 
+// ------------------------------------------------------------------ column sums of per-CTA partials
+// Σ_i part[i, c] for a [n, cols] fp32 matrix.  Grid: one block of 1024 threads per 32 columns; warp w sums rows
+// w, w+32, … (lanes = columns: 128-byte coalesced loads, four rows in flight), the 32 warps meet in shared memory and are
+// added in warp order, so the result does not depend on scheduling.  A single thread looping over n rows (n in the
+// hundreds to thousands) is a chain of n dependent loads: tens of microseconds for a few hundred kilobytes.
+// Returns, in the lanes of warp 0, the sum of column blockIdx.x·32 + lane (0 for columns ≥ cols and in other warps).
+__device__ __forceinline__ float column_sum_block(const float* __restrict__ part, int n, int cols) {
+  __shared__ float s_cs[32][33];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  if (c < cols) {
+    int i = warp;
+    for (; i + 96 < n; i += 128) {
+      a0 += part[static_cast<size_t>(i) * cols + c];
+      a1 += part[static_cast<size_t>(i + 32) * cols + c];
+      a2 += part[static_cast<size_t>(i + 64) * cols + c];
+      a3 += part[static_cast<size_t>(i + 96) * cols + c];
+    }
+    for (; i < n; i += 32) a0 += part[static_cast<size_t>(i) * cols + c];
+  }
+  s_cs[warp][lane] = (a0 + a1) + (a2 + a3);
+  __syncthreads();
+  float t = 0.f;
+  if (warp == 0) {
+#pragma unroll
+    for (int w = 0; w < 32; ++w) t += s_cs[w][lane];
+  }
+  return t;
+}
+
 // ------------------------------------------------------------------ misc
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
   uint32_t v;

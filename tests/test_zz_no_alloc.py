@@ -13,6 +13,7 @@ import pytest
 import torch
 
 from archscale_b200.ops import backend
+from archscale_b200.ops.norm import rms_norm_ref
 
 pytestmark = pytest.mark.gpu
 
@@ -50,14 +51,23 @@ def test_noalloc_matches_regular_entry_point_twice():
         dx_ref, dw_ref = ext.rmsnorm_bwd(dy, x, w, rstd)
         dx = torch.empty_like(x)
         dw = torch.empty(cols, device="cuda", dtype=torch.float32)
+        torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before, _ = torch.cuda.mem_get_info()       # the driver's view: sees a raw cudaMalloc that torch's counter cannot
         rc = _call(lib, dy, x, w, rstd, dx, dw)
         torch.cuda.synchronize()
         assert rc == 0, lib.b200_noalloc_last_error()
         assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.mem_get_info()[0] == free_before
         tol = 2e-2 if xdt == torch.bfloat16 else 1e-5
         assert (dx.float() - dx_ref.float()).norm() <= tol * dx_ref.float().norm()
         assert (dw - dw_ref).norm() <= 1e-5 * dw_ref.norm()
+        # and against the plain PyTorch fp32 formula of the same op
+        xo = x.float().detach().requires_grad_()
+        wo = w.clone().requires_grad_()
+        rms_norm_ref(xo, wo, 1e-5).backward(dy.float())
+        assert (dx.float() - xo.grad).norm() <= (2e-2 if xdt == torch.bfloat16 else 2e-3) * xo.grad.norm()
+        assert (dw - wo.grad).norm() <= 2e-3 * wo.grad.norm()
 
 
 def test_noalloc_rejects_oversized_rows():
