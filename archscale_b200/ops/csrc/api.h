@@ -78,6 +78,12 @@ int b200_attn_fwd(const void* q, const void* k, const void* v, void* out, float*
 int b200_attn_fwd_2s(const void* q, const void* k, const void* v, void* out, float* lse, const int* row_start, int B, int T,
                      int H, int G, int D, int window_left, float scale, int* status, cudaStream_t stream);
 void b200_attn_fwd_2s_set_trace(long long* buf);
+// Single-kernel backward (attention_bwd1.cu): five products per tile pair, dQ summed in fp32 through `dq_acc` [B,T,H,D]
+// with reductions in memory (fast, not bitwise reproducible).  ARCHSCALE_B200_ATTN_BWD=split selects the two-kernel form.
+int b200_attn_bwd1(const void* d_out, const void* q, const void* k, const void* v, const void* out, const float* lse, float* delta,
+                   float* dq_acc, const int* row_start, const int* doc_end, void* dq, void* dk, void* dv, int B, int T, int H,
+                   int G, int D, int window_left, float scale, int* status, cudaStream_t stream);
+int b200_attn_bwd_delta(const void* out, const void* d_out, float* delta, int B, int T, int H, int D, cudaStream_t stream);
 void b200_attn_bwd_set_trace(long long* buf);       // same aid for the dK/dV kernel: 8×64 stamps
 
 // Attention backward (attention_bwd.cu): δ preprocess + dK/dV kernel + dQ kernel, deterministic.

@@ -592,7 +592,18 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const CUten
 
 }  // namespace b200
 
-static long long* g_attn_bwd_trace = nullptr;
+// δ[b,h,r] = Σ_d dO·O alone (also used by the single-kernel backward in attention_bwd1.cu)
+extern "C" int b200_attn_bwd_delta(const void* out, const void* d_out, float* delta, int B, int T, int H, int D, cudaStream_t stream) {
+  using namespace b200;
+  if (D != 64 && D != 128) return -1;
+  const size_t rows = static_cast<size_t>(B) * T * H;
+  const int grid = static_cast<int>((rows * 32 + 255) / 256);
+  if (D == 128) attn_bwd_delta_kernel<128><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out, delta, B, T, H);
+  else attn_bwd_delta_kernel<64><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)out, (const __nv_bfloat16*)d_out, delta, B, T, H);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+long long* g_attn_bwd_trace = nullptr;   // also read by the single-kernel backward (attention_bwd1.cu)
 extern "C" void b200_attn_bwd_set_trace(long long* buf) { g_attn_bwd_trace = buf; }
 
 extern "C" int b200_attn_bwd(const void* d_out, const void* q, const void* k, const void* v, const void* out,

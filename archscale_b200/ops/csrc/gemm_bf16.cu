@@ -587,6 +587,22 @@ int make_tmap_3d_bf16(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+// 3-D fp32 tensor map [inner (contiguous), rows, batch] with a box of 16 floats × box_rows × 1 and the 64-byte swizzle: the
+// target of the attention backward's bulk reductions (cp.reduce.async.bulk.tensor, add) into its fp32 dQ accumulator.
+int make_tmap_3d_f32_sw64(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t rows, uint64_t batch,
+                          uint64_t row_stride_elems, uint64_t batch_stride_elems, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t gdim[3] = {inner, rows, batch};
+  cuuint64_t gstride[2] = {row_stride_elems * 4, batch_stride_elems * 4};
+  cuuint32_t box[3] = {16, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
 uint32_t* g_splitk_sem = nullptr;      // shared with the two-CTA kernel (gemm2_bf16.cu)
 int g_splitk_sem_len = 0;
 

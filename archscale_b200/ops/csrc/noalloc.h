@@ -17,7 +17,9 @@
 //  * The array (B200_NOALLOC_SCRATCH_FLOATS floats ≈ 4.6 MiB) is part of the loaded module: every
 //    GPU that loads the library holds it until the process exits.
 //  * The first call on a device resolves the array's device address (cudaGetSymbolAddress, with
-//    that device current) and caches it; make that first call outside any stream capture.
+//    that device current) and caches it; make that first call outside any stream capture.  With
+//    lazy module loading (the CUDA default) the driver also materialises the array at that moment,
+//    so the device's free memory drops by the array's size during the first call and never again.
 //  * All calls share the one array and it keeps the previous call's contents.  Nothing in it has
 //    to start at zero (every CTA overwrites its own row before the reduction reads it), but two
 //    calls that overlap on the GPU (different streams) race on it: serialise them.

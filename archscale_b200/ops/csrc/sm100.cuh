@@ -81,6 +81,27 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// The same bounded wait for roles that are not on the critical path (loaders, read-out warps): it sleeps between polls,
+// so the polling warp leaves the issue slots of its scheduler to the warps that compute.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                                  int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  long long t0 = clock64();
+  int spins = 0;
+  while (true) {
+    __nanosleep(40);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 0xff) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------ TMA (no multicast)
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
@@ -100,6 +121,13 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+// Bulk tensor reduction shared → global: global[box] += smem[box] in the tensor map's data type (out-of-range parts of the
+// box are dropped).  Completion is tracked like a store (commit_group / wait_group).
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* map, const void* smem_src, int x, int y, int z) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
                : "memory");
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }

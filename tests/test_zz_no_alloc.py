@@ -8,6 +8,7 @@ symbol directly (ctypes, no torch binding in between) and checks it against the 
 on two consecutive calls, because the shared scratch array keeps the first call's contents.
 """
 import ctypes
+import gc
 
 import pytest
 import torch
@@ -43,6 +44,11 @@ def test_noalloc_matches_regular_entry_point_twice():
     lib = _lib()
     ext = backend.require_extension()
     torch.manual_seed(0)
+    # The first call on a device resolves the address of the built-in array; with lazy module loading that is also when the
+    # driver materialises the array (its 4.6 MiB come out of free memory once, there).  Make that call before measuring.
+    x0 = torch.randn(8, 1024, device="cuda")
+    assert _call(lib, x0.bfloat16(), x0, torch.ones(1024, device="cuda"), torch.ones(8, device="cuda"), torch.empty_like(x0),
+                 torch.empty(1024, device="cuda")) == 0
     for rows, cols, xdt in [(1000, 2048, torch.float32), (333, 1024, torch.bfloat16)]:   # two calls in a row
         x = torch.randn(rows, cols, device="cuda").to(xdt)
         w = 1 + 0.1 * torch.randn(cols, device="cuda")
@@ -51,13 +57,16 @@ def test_noalloc_matches_regular_entry_point_twice():
         dx_ref, dw_ref = ext.rmsnorm_bwd(dy, x, w, rstd)
         dx = torch.empty_like(x)
         dw = torch.empty(cols, device="cuda", dtype=torch.float32)
+        gc.collect()                                     # unrelated garbage freed during the call would move the counters
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        n_allocs = torch.cuda.memory_stats()["allocation.all.allocated"]
         free_before, _ = torch.cuda.mem_get_info()       # the driver's view: sees a raw cudaMalloc that torch's counter cannot
         rc = _call(lib, dy, x, w, rstd, dx, dw)
         torch.cuda.synchronize()
         assert rc == 0, lib.b200_noalloc_last_error()
-        assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.memory_stats()["allocation.all.allocated"] == n_allocs     # no allocation event at all
+        assert torch.cuda.memory_allocated() <= before
         assert torch.cuda.mem_get_info()[0] == free_before
         tol = 2e-2 if xdt == torch.bfloat16 else 1e-5
         assert (dx.float() - dx_ref.float()).norm() <= tol * dx_ref.float().norm()
