@@ -1,8 +1,8 @@
 """Per-kernel microbenchmarks against the measured roofline (``MEASURED_PEAKS.json``) and the
 library kernel doing the same op.  CUDA-event timing, warm-up, L2 flushed between iterations.
 
-    python -m archscale_b200.ops.bench_kernels gemm rmsnorm swiglu ce rope attn mamba    # any subset
-    python -m archscale_b200.ops.bench_kernels gemm --json out.json
+    python -m archscale_b200.benchmarks.kernels gemm rmsnorm swiglu ce rope attn mamba    # any subset
+    python -m archscale_b200.benchmarks.kernels gemm --json out.json
 """
 from __future__ import annotations
 

@@ -3,8 +3,8 @@
 Inputs are larger than the 126 MB L2 (so DRAM counters mean something) and well under a few GB; there is
 no warm-up loop and no timing, so a capture with ``-k regex:<kernel> -c 3`` ends by itself quickly.
 
-    python -m archscale_b200.ops.profile_cases gemm
-    ncu --set full --clock-control none -k regex:gemm2_bf16_kernel -c 3 -o prof python -m archscale_b200.ops.profile_cases gemm
+    python -m archscale_b200.benchmarks.profile_cases gemm
+    ncu --set full --clock-control none -k regex:gemm2_bf16_kernel -c 3 -o prof python -m archscale_b200.benchmarks.profile_cases gemm
 """
 from __future__ import annotations
 

@@ -7,7 +7,7 @@ Ampere attention path, `lit_gpt/attention.py:119-120`) and QuACK's sm_100 GEMM (
 importable (``fla``'s gated-delta-rule kernel faulted on this GPU and is left out, see :func:`bench_gdn`).  Every row: op, shape, our time, their time, ratio.  A bar that cannot
 be loaded prints ``unavailable`` with the reason; nothing here is used by training or by ``bench.py``.
 
-    ARCHSCALE_REFERENCE_DIR=/path/to/ArchScale python -m archscale_b200.ops.bench_reference [rmsnorm rope flce ns gated attn gdn gemm]
+    ARCHSCALE_REFERENCE_DIR=/path/to/ArchScale python -m archscale_b200.benchmarks.reference_bars [rmsnorm rope flce ns gated attn gdn gemm]
 """
 from __future__ import annotations
 
@@ -21,7 +21,7 @@ import types
 import torch
 
 from archscale_b200 import ops
-from archscale_b200.ops.bench_kernels import time_ms
+from archscale_b200.benchmarks.kernels import time_ms
 
 
 def ref_module(name: str):
@@ -171,7 +171,7 @@ def bench_gdn(res):
     """``fla``'s ``chunk_gated_delta_rule`` (what `lit_gpt/gated_deltanet.py:315-326` calls) is not run: on B200 with
     driver 580 its Triton kernel raised "misaligned address" at the Gated-DeltaNet layer shape (B8 T4096 H6 Dk256 Dv512,
     fla 0.5.1, triton 3.6) and left the CUDA context unusable for the bars after it.  Our own numbers for the op are in
-    ``bench_kernels gdn``."""
+    ``benchmarks.kernels gdn``."""
     r = {"op": "gated_delta_rule", "unavailable": "fla chunk_gated_delta_rule raised a misaligned-address fault on this GPU; not run"}
     res.append(r)
     print(json.dumps(r), flush=True)

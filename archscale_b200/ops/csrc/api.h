@@ -104,6 +104,8 @@ int b200_symm_post(const void* const* bases, size_t signal_off, int channel, int
                    cudaStream_t stream);
 int b200_symm_wait(const void* const* bases, size_t signal_off, int channel, int rank, int world, uint32_t epoch,
                    int* status, cudaStream_t stream);
+int b200_pull_pieces(const void* const* bases, size_t obj_off, void* dst, const void* table, int n_pieces, int world,
+                     int max_ctas, cudaStream_t st);
 int b200_allgather_pull(const void* const* bases, size_t src_off, void* dst, size_t shard_bytes, int rank, int world,
                         int max_ctas, cudaStream_t stream);
 int b200_reduce_scatter_pull(const void* const* bases, size_t full_off, float* out, size_t shard_elems, int rank,
@@ -189,6 +191,12 @@ int b200_gemm2_bf16_batched(int mode, const void* A, const void* B, void* out, c
                             int N, int K, float alpha, float beta, const float* alpha_vec, const float* beta_vec, int symmetric,
                             int num_sms, int* status, cudaStream_t stream);
 
+// Chunk-to-chunk state recurrence of the SSD scan and its backward (ssd_scan.cu); PN = head_dim · state, a multiple of 1024
+int b200_ssd_state_fwd(const float* add, const float* keep, float* s_in, int B, int nC, int H, int PN, cudaStream_t st);
+int b200_ssd_state_bwd(const float* d_s_in, const float* s_in, const float* keep, float* d_add, float* d_keep_part,
+                       int B, int nC, int H, int PN, cudaStream_t st);
+// (I + A)^-1 for [n_mat, 64, 64] strictly lower-triangular fp32 matrices (tri_inverse.cu)
+int b200_tri_inverse64(const float* A, float* T, int n_mat, cudaStream_t st);
 // One pass of the chunked gated-delta-rule recurrence (gdn_chunk.cu)
 int b200_gdn_state(const void* a_op, const void* c_add, const void* bm_op, const void* e_op, const void* f_op,
                    const float* decay, void* v_out, void* x_all, float* x_final, int BH, int Tp, int DK, int DV,

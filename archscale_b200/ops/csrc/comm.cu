@@ -6,7 +6,7 @@
 //   symm_barrier            all ranks signal all peers and wait (bounded) — a device-side barrier
 //   allgather_pull          local_full[p·S .. (p+1)·S) ← peer p's shard, for all p (16-byte loads)
 //   reduce_scatter_pull     out[i] (+)= scale · Σ_p peer_p.full[r·S + i]   fp32, fixed rank order
-//   gather_ranges / …       used by the distributed Muon step (flat U → owner, O → shards)
+//   pull_pieces             a host-built list of ranges copied from named peers (Muon: U → owners, O → shards)
 //
 // Signals are 32-bit epoch counters in the heaps' signal areas: a rank writes `epoch` into slot
 // [its rank] of every peer with a system-scope release store; waiting is an acquire load in a spin
@@ -89,6 +89,30 @@ __global__ void __launch_bounds__(512) allgather_pull_kernel(Peers peers, size_t
     for (int u = 0; u < U; ++u) { const size_t j = j0 + static_cast<size_t>(u) * blockDim.x; if (j < shard_vec) v[u] = src[j]; }
 #pragma unroll
     for (int u = 0; u < U; ++u) { const size_t j = j0 + static_cast<size_t>(u) * blockDim.x; if (j < shard_vec) d[j] = v[u]; }
+  }
+}
+
+// A list of copies from peers: piece i moves `len` 16-byte vectors from vector `src` of the object at heap offset `obj_off`
+// in rank `rank`'s heap to vector `dst` of the local buffer.  The table is built once on the host (the owned matrices of
+// the Muon step never change) with every piece cut to at most kPiece vectors, so one CTA takes one piece per round.
+struct PullPiece {
+  long long src, dst;
+  int len, rank;
+};
+constexpr int kPullPieceVecs = 512 * 8;
+
+__global__ void __launch_bounds__(512) pull_pieces_kernel(Peers peers, size_t obj_off, uint4* __restrict__ dst,
+                                                         const PullPiece* __restrict__ table, int n_pieces) {
+  constexpr int U = 8;
+  for (int i = blockIdx.x; i < n_pieces; i += gridDim.x) {
+    const PullPiece pc = table[i];
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const char*>(peers.base[pc.rank]) + obj_off) + pc.src;
+    uint4* d = dst + pc.dst;
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) { const int j = threadIdx.x + u * 512; if (j < pc.len) v[u] = src[j]; }
+#pragma unroll
+    for (int u = 0; u < U; ++u) { const int j = threadIdx.x + u * 512; if (j < pc.len) d[j] = v[u]; }
   }
 }
 
@@ -215,6 +239,16 @@ extern "C" int b200_allgather_pull(const void* const* bases, size_t src_off, voi
   const size_t sv = shard_bytes / 16;
   allgather_pull_kernel<<<comm_grid(sv * world, max_ctas), 512, 0, st>>>(make_peers(bases, world), src_off,
                                                                          static_cast<uint4*>(dst), sv, rank, world);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+// table: device array of n_pieces PullPiece records (see above); len ≤ 4096 vectors each.
+extern "C" int b200_pull_pieces(const void* const* bases, size_t obj_off, void* dst, const void* table, int n_pieces,
+                                int world, int max_ctas, cudaStream_t st) {
+  if (world > 8 || obj_off % 16) return -1;
+  if (n_pieces <= 0) return 0;
+  const int grid = n_pieces < max_ctas ? n_pieces : max_ctas;
+  pull_pieces_kernel<<<grid, 512, 0, st>>>(make_peers(bases, world), obj_off, static_cast<uint4*>(dst),
+                                           static_cast<const PullPiece*>(table), n_pieces);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 extern "C" int b200_reduce_scatter_pull(const void* const* bases, size_t full_off, float* out, size_t shard_elems, int rank,

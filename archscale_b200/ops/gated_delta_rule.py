@@ -133,6 +133,34 @@ class _ChunkCoreFn(torch.autograd.Function):
         return dw.to(dt[0]), dv4.to(dt[1]), dkd.to(dt[2]), dqg.to(dt[3]), dqk.to(dt[4]), da.to(dt[5])
 
 
+class _TriInverseFn(torch.autograd.Function):
+    """``(I + A)⁻¹`` for strictly lower-triangular 64×64 blocks on the substitution kernel (``csrc/tri_inverse.cu``);
+    backward from ``dA = −Tᵀ · dT · Tᵀ`` (strictly lower part)."""
+
+    @staticmethod
+    def forward(ctx, A):
+        T = backend.require_extension().tri_inverse64(A.contiguous())
+        backend.count_launch()
+        ctx.save_for_backward(T)
+        return T
+
+    @staticmethod
+    def backward(ctx, dT):
+        (T,) = ctx.saved_tensors
+        Tt = T.transpose(-1, -2)
+        return (-(Tt @ dT @ Tt)).tril(-1)
+
+
+def unit_lower_inverse(A: torch.Tensor) -> torch.Tensor:
+    """``(I + A)⁻¹`` for strictly lower-triangular ``A (…, c, c)``."""
+    c = A.shape[-1]
+    if (A.is_cuda and c == 64 and A.dtype == torch.float32 and backend.has("tri_inverse64")
+            and backend.use_cuda_kernel("gated_delta_rule", A)):
+        return _TriInverseFn.apply(A)
+    eye = torch.eye(c, device=A.device, dtype=A.dtype)
+    return torch.linalg.solve_triangular(eye + A, eye.expand_as(A), upper=False, unitriangular=True)
+
+
 def _chunk_core(w, u, kd, qg, qk, a):
     Dk, Dv = w.shape[-1], u.shape[-1]
     if (w.is_cuda and w.shape[2] == 64 and Dk in (128, 256) and Dv % 128 == 0 and backend.has("gdn_state")
@@ -180,9 +208,8 @@ def gated_delta_rule_chunk(q, k, v, g, beta, scale: Optional[float] = None, l2no
     strict = torch.tril(torch.ones(chunk, chunk, device=q.device, dtype=torch.bool), -1)
     incl = torch.tril(torch.ones(chunk, chunk, device=q.device, dtype=torch.bool), 0)
     A = ((kb @ k.transpose(-1, -2)) * dec).masked_fill(~strict, 0.0)
-    eye = torch.eye(chunk, device=q.device, dtype=q.dtype)
-    # (I + A) is unit lower-triangular → solve for W, U:  (I+A) U = β v ; (I+A) W = β k·exp(gc)
-    Tm = torch.linalg.solve_triangular(eye + A, eye.expand_as(A), upper=False, unitriangular=True)
+    # (I + A) is unit lower-triangular → W, U from its inverse:  (I+A) U = β v ; (I+A) W = β k·exp(gc)
+    Tm = unit_lower_inverse(A)
     u = Tm @ vb
     w = Tm @ (kb * torch.exp(gc).unsqueeze(-1))
     qk = ((q @ k.transpose(-1, -2)) * dec).masked_fill(~incl, 0.0)

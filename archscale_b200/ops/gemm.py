@@ -8,11 +8,13 @@ Three operand layouts cover forward, dgrad and wgrad of ``y = x @ Wᵀ``
 * ``matmul_nn(a[M,K], b[K,N])  = a @ b``   (dgrad; B is N-major)
 * ``matmul_tn(a[K,M], b[K,N])  = aᵀ @ b``  (wgrad; both operands MN-major)
 
-CUDA path: ``csrc/gemm_bf16.cu`` — persistent, warp-specialised tcgen05 kernel: a TMA
-producer warp fills a multi-stage shared-memory ring, one elected thread issues
-``tcgen05.mma`` into double-buffered TMEM accumulators, four epilogue warps drain TMEM with
-``tcgen05.ld`` and store bf16 or accumulate fp32.  All three layouts run the same kernel
-with different TMA boxes and UMMA descriptor major-ness.
+CUDA path: ``csrc/gemm2_bf16.cu`` by default — SM pairs (``cta_group::2``) share one 256×256
+output tile: each CTA loads its half of both operands with TMA, the leader's elected thread
+issues ``tcgen05.mma`` for the pair into double-buffered TMEM accumulators, epilogue warps of
+both CTAs drain their 128 rows with ``tcgen05.ld``.  ``csrc/gemm_bf16.cu`` is the one-CTA
+kernel of the same structure (128×256 tiles), kept for shapes the pair kernel does not take and
+selectable with ``ARCHSCALE_B200_GEMM=1cta``.  All three layouts run the same kernels with
+different TMA boxes and UMMA descriptor major-ness.
 """
 from __future__ import annotations
 

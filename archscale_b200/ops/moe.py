@@ -11,9 +11,10 @@ GLU layout: **chunk halves** everywhere (``w_in[e]`` rows ``[0, I)`` are the gat
 the up projection), the same as the dense MLP and the shared expert of the reference
 (`lit_gpt/moe.py:96-99`); upstream SonicMoE's interleaved layout is not used.
 
-CUDA path: ``csrc/moe_routing.cu`` (router + metadata without a host sync) and
-``csrc/grouped_gemm.cu`` (tcgen05 grouped GEMM over device-side expert offsets, gather-A for
-the up projection, SwiGLU epilogue; down projection with score-weighted scatter epilogue).
+CUDA path: ``csrc/moe_routing.cu`` (top-k indices, slot layout, row gather / score-weighted
+combine, all without a host sync) and the grouped mode of the two-CTA GEMM in
+``csrc/gemm2_bf16.cu`` (per-expert row ranges read from device-side offsets); ``grouped_gemm.py``
+strings them together as one autograd function.
 """
 from __future__ import annotations
 

@@ -98,6 +98,30 @@ def supported(x2: torch.Tensor, weight: torch.Tensor) -> bool:
             and T % 128 == 0 and backend.has("gemm_mxfp8"))
 
 
+# Quantised weights are reused until the weights change: a forward under activation checkpointing runs twice and every
+# micro-step of a gradient-accumulation window sees the same values.  The optimizer step (and a checkpoint load) call
+# ``invalidate_weight_cache()``; an entry is also dropped when the tensor's storage or in-place version moved.
+_W_EPOCH = 0
+_W_CACHE: dict = {}
+
+
+def invalidate_weight_cache() -> None:
+    global _W_EPOCH
+    _W_EPOCH += 1
+    _W_CACHE.clear()
+
+
+def quantize_weight(weight: torch.Tensor, colwise: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+    key = (id(weight), colwise)
+    tag = (_W_EPOCH, weight.data_ptr(), weight._version, tuple(weight.shape))
+    hit = _W_CACHE.get(key)
+    if hit is not None and hit[0] == tag:
+        return hit[1]
+    out = quantize(weight, colwise)
+    _W_CACHE[key] = (tag, out)
+    return out
+
+
 class _LinearMXFP8Fn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias):
@@ -105,7 +129,7 @@ class _LinearMXFP8Fn(torch.autograd.Function):
         if not x2.is_contiguous():
             x2 = x2.contiguous()
         xq, xs = quantize(x2)
-        wq, ws = quantize(weight)
+        wq, ws = quantize_weight(weight, False)
         y = gemm(xq, xs, wq, ws)
         if bias is not None:
             y = y + bias.to(y.dtype)
@@ -124,7 +148,7 @@ class _LinearMXFP8Fn(torch.autograd.Function):
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
             gq, gs = quantize(dy2)                          # (T, N) blocks along N
-            wtq, wts = quantize(weight, colwise=True)       # Wᵀ: (K, N) blocks along N
+            wtq, wts = quantize_weight(weight, True)        # Wᵀ: (K, N) blocks along N
             dx = gemm(gq, gs, wtq, wts).view(ctx.x_shape)
         if ctx.needs_input_grad[1]:
             gtq, gts = quantize(dy2, colwise=True)          # dyᵀ: (N, T) blocks along T

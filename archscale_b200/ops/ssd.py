@@ -15,6 +15,8 @@ from typing import Optional
 import torch
 import torch.nn.functional as F
 
+from . import backend
+
 
 def ssd_scan_ref(x, dt, A, B, C, D=None, seq_idx: Optional[torch.Tensor] = None):
     dtype = x.dtype
@@ -36,6 +38,43 @@ def ssd_scan_ref(x, dt, A, B, C, D=None, seq_idx: Optional[torch.Tensor] = None)
     if D is not None:
         y = y + x * D.float().view(1, 1, H, 1)
     return y.to(dtype)
+
+
+def chunk_state_scan_ref(add: torch.Tensor, keep: torch.Tensor) -> torch.Tensor:
+    """``S_in[:, 0] = 0, S_in[:, n+1] = keep[:, n]·S_in[:, n] + add[:, n]`` — add (B,nC,H,P,N), keep (B,nC,H)."""
+    Bb, nC, H, P, N = add.shape
+    S = add.new_zeros(Bb, H, P, N)
+    states = []
+    for n in range(nC):                                                                  # the only sequential part
+        states.append(S)
+        S = S * keep[:, n].view(Bb, H, 1, 1) + add[:, n]
+    return torch.stack(states, dim=1)
+
+
+class _StateScanFn(torch.autograd.Function):
+    """The recurrence over chunks as one kernel each way (``csrc/ssd_scan.cu``)."""
+
+    @staticmethod
+    def forward(ctx, add, keep):
+        add, keep = add.contiguous(), keep.contiguous()
+        s_in = backend.require_extension().ssd_state_fwd(add, keep)
+        backend.count_launch()
+        ctx.save_for_backward(s_in, keep)
+        return s_in
+
+    @staticmethod
+    def backward(ctx, d_s_in):
+        s_in, keep = ctx.saved_tensors
+        d_add, d_keep = backend.require_extension().ssd_state_bwd(d_s_in.contiguous(), s_in, keep)
+        backend.count_launch(2)
+        return d_add, d_keep
+
+
+def chunk_state_scan(add: torch.Tensor, keep: torch.Tensor) -> torch.Tensor:
+    if (add.is_cuda and add.dtype == torch.float32 and keep.dtype == torch.float32 and (add.shape[3] * add.shape[4]) % 1024 == 0
+            and backend.has("ssd_state_fwd") and backend.use_cuda_kernel("ssd", add)):
+        return _StateScanFn.apply(add, keep)
+    return chunk_state_scan_ref(add, keep)
 
 
 def ssd_scan(x, dt, A, B, C, D=None, seq_idx: Optional[torch.Tensor] = None, chunk: int = 64):
@@ -90,12 +129,7 @@ def ssd_scan(x, dt, A, B, C, D=None, seq_idx: Optional[torch.Tensor] = None, chu
     add = torch.einsum("bngrj,bnjgrp,bnjgk->bngrpk", wl.view(Bb, nC, G, rep, c), xb.view(Bb, nC, c, G, rep, P), Bh)
     add = add.reshape(Bb, nC, H, P, N)
     keep = carry[..., -1]                                                                # (B,nC,H)
-    S = x.new_zeros(Bb, H, P, N)
-    states = []
-    for n in range(nC):                                                                  # the only sequential part
-        states.append(S)
-        S = S * keep[:, n].view(Bb, H, 1, 1) + add[:, n]
-    S_in = torch.stack(states, dim=1)                                                    # state entering each chunk
+    S_in = chunk_state_scan(add, keep)                                                   # state entering each chunk
     y = y + torch.einsum("bngrpk,bnigk,bngri->bnigrp", S_in.view(Bb, nC, G, rep, P, N), Ch,
                          carry.view(Bb, nC, G, rep, c)).reshape(Bb, nC, c, H, P)
     y = y.reshape(Bb, Lp, H, P)[:, :L]

@@ -402,6 +402,32 @@ class ShardedOptimizer:
         return torch.zeros(max(self.n_norm, 1), dtype=torch.float32, device=self.engine.device)
 
     # ------------------------------------------------------------------ Muon transport + NS
+    def _transport_tables(self, g):
+        """(gather table, return table) of the peer-memory Muon transport for flat group ``g``, built once: which 16-byte
+        ranges this rank pulls from which shard to assemble the matrices it owns, and from which owner it pulls each
+        range of its own shard afterwards.  None if a range is not 16-byte aligned (the full gather is used then)."""
+        cache = self.__dict__.setdefault("_transport_cache", {})
+        if id(g) in cache:
+            return cache[id(g)]
+        S, r, W = g.shard_numel, g.rank, g.world
+        mats = [mt for mt in self.mats if mt.group is g]
+        gather, ret = [], []
+        a0, b0 = r * S, min((r + 1) * S, g.matrix_numel)
+        for mt in mats:
+            lo, hi = mt.offset, mt.offset + mt.rows * mt.cols
+            if mt.owner == r:
+                for sh in range(lo // S, (hi - 1) // S + 1):
+                    a, b = max(lo, sh * S), min(hi, (sh + 1) * S)
+                    gather.append((sh, a - sh * S, a, b - a))
+            a, b = max(lo, a0), min(hi, b0)
+            if b > a:
+                ret.append((mt.owner, a, a - a0, b - a))
+        sym = self.engine.symm
+        tg = sym._piece_table(gather, r, W, self.engine.device)
+        tr = sym._piece_table(ret, r, W, self.engine.device)
+        cache[id(g)] = None if (tg is None or tr is None) else (tg, tr)
+        return cache[id(g)]
+
     def _orthogonalise(self, stack: torch.Tensor) -> torch.Tensor:
         """(B, rows, cols) pre-orthogonalisation updates → orthogonalised updates (overridden by MuonBall)."""
         return ops.newton_schulz(stack, epsilon=self.ns_epsilon)
@@ -445,9 +471,13 @@ class ShardedOptimizer:
                         u_shard[:n_loc].copy_(torch.add(gs, ms, alpha=self.mu))
                     else:
                         u_shard[:n_loc].copy_(ms)
-            # 2. assemble whole matrices (every rank gets the full flat U; owners use their matrices)
+            # 2. assemble whole matrices.  Peer-memory path: a rank pulls only the matrices it owns; collective path:
+            #    every rank gets the full flat U and owners use their matrices.
+            tabs = self._transport_tables(g) if (g.world > 1 and eng.symm is not None) else None
             if g.world > 1:
-                if eng.symm is not None:
+                if tabs is not None:
+                    u_full = eng.symm.gather_owned(g, u_shard, tabs[0])
+                elif eng.symm is not None:
                     u_full = eng.symm.gather_flat(g, u_shard)
                 else:
                     u_full = torch.empty(g.padded, dtype=cdt, device=eng.device)
@@ -456,7 +486,8 @@ class ShardedOptimizer:
                 u_full = u_shard
             if g.world > 1 and eng.symm is not None:
                 o_full = eng.symm.o_buffer(g)
-                o_full.zero_()
+                if tabs is None:
+                    o_full.zero_()              # the summing return path reads every rank's whole buffer
             else:
                 o_full = torch.zeros(g.padded, dtype=cdt, device=eng.device) if g.world > 1 else u_full
             staged[gid] = (g, u_full, o_full, [mt for mt in mask_mats if mt.owner == g.rank])
@@ -497,7 +528,10 @@ class ShardedOptimizer:
         # 4. return the updates to the shards
         for gid, (g, u_full, o_full, _mine) in staged.items():
             if g.world > 1:
-                if eng.symm is not None:
+                tabs = self._transport_tables(g) if eng.symm is not None else None
+                if tabs is not None:
+                    o_shard = eng.symm.scatter_owned(g, o_full, tabs[1])
+                elif eng.symm is not None:
                     o_shard = eng.symm.scatter_flat(g, o_full)
                 else:
                     o_shard = torch.empty(g.shard_numel, dtype=cdt, device=eng.device)

@@ -21,7 +21,7 @@ Replaces the NCCL all-gather / reduce-scatter that torch FSDP2 issues for the re
 """
 from __future__ import annotations
 
-from typing import Dict, List, Tuple
+from typing import Dict, Optional, List, Tuple
 
 import torch
 import torch.distributed as dist
@@ -182,6 +182,51 @@ class SymmetricContext:
         self.ext.allgather_pull(self.heap.bases, m["u_off"], full, g.shard_numel * 2, self.heap.rank, self.comm_ctas)
         backend.count_launch(3)
         return full
+
+    @staticmethod
+    def _piece_table(pieces, rank: int, world: int, device) -> Optional[torch.Tensor]:
+        """``pieces``: (src_rank, src_elem, dst_elem, n_elem) of bf16 ranges → int64 [n, 3] device table of 16-byte-vector
+        pieces of at most 4096 vectors, interleaved over the source ranks starting after ``rank`` (no two ranks start on
+        the same peer).  None if a range is not 16-byte aligned."""
+        per_rank = [[] for _ in range(world)]
+        for src_rank, src, dst, n in pieces:
+            if src % 8 or dst % 8 or n % 8:
+                return None
+            sv, dv, nv = src // 8, dst // 8, n // 8
+            while nv > 0:
+                step = min(nv, 4096)
+                per_rank[(src_rank - rank - 1) % world].append((sv, dv, step | (src_rank << 32)))
+                sv, dv, nv = sv + step, dv + step, nv - step
+        rows = []
+        depth = max((len(l) for l in per_rank), default=0)
+        for i in range(depth):
+            rows.extend(l[i] for l in per_rank if i < len(l))
+        return torch.tensor(rows, dtype=torch.int64, device=device).reshape(-1, 3)
+
+    def gather_owned(self, g, u_shard: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+        """Flat-sized buffer in which only the ranges named by ``table`` (this rank's own matrices) are filled, each
+        from the shards that hold it: a rank moves 1/world of what :meth:`gather_flat` moves
+        (reference: the all-to-all of `lit_gpt/optim/muon.py:531-535`)."""
+        m = self.meta[id(g)]
+        assert u_shard.data_ptr() == m["u"].data_ptr()
+        e = self.heap.post(m["chan"] + 1)
+        self.heap.wait(m["chan"] + 1, e)
+        full = torch.empty(g.padded, dtype=torch.bfloat16, device=self.engine.device)
+        self.ext.pull_pieces(self.heap.bases, m["u_off"], full, table, self.comm_ctas)
+        backend.count_launch(3)
+        return full
+
+    def scatter_owned(self, g, o_full: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+        """This rank's shard of the orthogonalised updates, every range copied from the one rank that computed it
+        (no sum, so the owners' buffers need no zero fill; reference: `lit_gpt/optim/muon.py:554-558`)."""
+        m = self.meta[id(g)]
+        assert o_full.data_ptr() == m["o"].data_ptr()
+        e = self.heap.post(m["chan"] + 2)
+        self.heap.wait(m["chan"] + 2, e)
+        out = torch.empty(g.shard_numel, dtype=torch.bfloat16, device=self.engine.device)
+        self.ext.pull_pieces(self.heap.bases, m["o_off"], out, table, self.comm_ctas)
+        backend.count_launch(3)
+        return out
 
     def scatter_flat(self, g, o_full: torch.Tensor) -> torch.Tensor:
         m = self.meta[id(g)]

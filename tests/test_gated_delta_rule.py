@@ -112,3 +112,22 @@ def test_gated_deltanet_block_runs_on_the_kernel():
     for n, p in m.named_parameters():
         assert p.grad is not None and torch.isfinite(p.grad.float()).all(), n
     assert backend.require_extension().device_status() == 0
+
+
+@pytest.mark.gpu
+def test_unit_lower_inverse_kernel_matches_solve_and_autograd():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from archscale_b200.ops.gated_delta_rule import unit_lower_inverse
+    torch.manual_seed(4)
+    A = (0.3 * torch.randn(37, 3, 64, 64, device="cuda")).tril(-1).requires_grad_()
+    T = unit_lower_inverse(A)
+    eye = torch.eye(64, device="cuda")
+    Ar = A.detach().clone().requires_grad_()
+    Tr = torch.linalg.solve_triangular(eye + Ar, eye.expand_as(Ar), upper=False, unitriangular=True)
+    assert (T - Tr).abs().max() <= 1e-4 * Tr.abs().max()
+    assert ((eye + A.detach()) @ T.detach() - eye).abs().max() < 1e-3
+    g = torch.randn_like(T)
+    T.backward(g)
+    Tr.backward(g)
+    assert (A.grad - Ar.grad.tril(-1)).norm() <= 1e-4 * Ar.grad.norm()

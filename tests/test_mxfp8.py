@@ -78,3 +78,42 @@ def test_linear_mxfp8_forward_backward_close_to_bf16():
     rel = lambda a, b: ((a.float() - b).norm() / b.norm()).item()
     assert torch.allclose(y.float(), mxfp8.linear_mxfp8_ref(x.detach(), w.detach()).float(), atol=2e-2, rtol=2e-2)
     assert rel(y, yr) < 0.06 and rel(x.grad, xr.grad) < 0.06 and rel(w.grad, wr.grad) < 0.06
+
+
+def test_weight_cache_keys(monkeypatch):
+    """The quantised-weight cache returns the stored pair while the weight is untouched and requantises after an
+    in-place change, after ``invalidate_weight_cache()`` and for the other orientation (host logic, any device)."""
+    calls = []
+
+    def fake_quantize(x, colwise=False):
+        calls.append((x.data_ptr(), colwise))
+        return x.clone(), torch.zeros(1)
+
+    monkeypatch.setattr(mxfp8, "quantize", fake_quantize)
+    mxfp8.invalidate_weight_cache()
+    w = torch.randn(8, 8)
+    a = mxfp8.quantize_weight(w, False)
+    assert mxfp8.quantize_weight(w, False) is a and len(calls) == 1            # reused (checkpoint recompute, micro-steps)
+    mxfp8.quantize_weight(w, True)
+    assert len(calls) == 2                                                      # the other orientation is its own entry
+    w.mul_(2)                                                                    # torch-visible in-place change
+    assert mxfp8.quantize_weight(w, False) is not a and len(calls) == 3
+    mxfp8.invalidate_weight_cache()                                              # what the optimizer step calls
+    mxfp8.quantize_weight(w, False)
+    assert len(calls) == 4
+
+
+@pytest.mark.gpu
+def test_linear_mxfp8_sees_new_weights_after_invalidation():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    torch.manual_seed(5)
+    x = torch.randn(256, 256, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(128, 256, device="cuda") * 0.05).bfloat16()
+    mxfp8.invalidate_weight_cache()
+    y0 = mxfp8.linear_mxfp8(x, w)
+    assert torch.equal(mxfp8.linear_mxfp8(x, w), y0)
+    w.copy_(w * 2)
+    mxfp8.invalidate_weight_cache()
+    y1 = mxfp8.linear_mxfp8(x, w)
+    assert ((y1.float() - 2 * y0.float()).norm() / (2 * y0.float()).norm()).item() < 0.03
