@@ -101,6 +101,13 @@ class LLaMAMLP(nn.Module):
             self.norm.reset_parameters()
 
     def forward(self, x: torch.Tensor, layer_idx: int, gmu_mems=None):
+        if (not self.relu2 and not self.oss_swiglu and type(self.w1) is Linear and self.w1.bias is None and not self.w1.mxfp8
+                and not (self.config.gmu_mlp and layer_idx == self.config.n_layer // 2 + 1)):
+            h = ops.linear_swiglu(x, self.w1.weight)    # SwiGLU in the GEMM epilogue when the kernel takes this case
+            if h is not None:
+                if self.config.ffn_norm:
+                    h = self.norm(h)
+                return self.w3(h), gmu_mems
         h = self.w1(x)
         if self.relu2:
             h = F.relu(h).square()

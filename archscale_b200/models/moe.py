@@ -94,7 +94,12 @@ class SonicMoE(nn.Module):
         B, T, C = x.shape
         h = x.reshape(-1, C)
         if self.share_expert:
-            shared = self.shared_mod_out(ops.swiglu_packed(self.shared_mod_in(h)))
+            act = None
+            if type(self.shared_mod_in) is Linear and self.shared_mod_in.bias is None and not self.shared_mod_in.mxfp8:
+                act = ops.linear_swiglu(h, self.shared_mod_in.weight)
+            if act is None:
+                act = ops.swiglu_packed(self.shared_mod_in(h))
+            shared = self.shared_mod_out(act)
         # router in fp32 accumulate; logits kept for z-loss statistic and aux loss
         logits = self._router_logits(h).float() * self.logit_scale
         scores, indices = ops.router_topk_softmax(logits, self.top_k, self.config.sqrt_gate)

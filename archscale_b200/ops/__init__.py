@@ -6,7 +6,7 @@ from .conv1d import causal_conv1d, causal_conv1d_ref  # noqa: F401
 from .cross_entropy import (FusedCrossEntropyLoss, FusedLinearCrossEntropyLoss, cross_entropy, cross_entropy_ref,  # noqa: F401
                             fused_linear_cross_entropy, fused_linear_cross_entropy_ref)
 from .gated_delta_rule import gated_delta_rule, gated_delta_rule_recurrent_ref  # noqa: F401
-from .gemm import linear, matmul_nn, matmul_nt, matmul_tn  # noqa: F401
+from .gemm import linear, linear_swiglu, matmul_nn, matmul_nt, matmul_tn  # noqa: F401
 from .moe import (load_balance_loss, moe_ffn, moe_ffn_ref, router_topk_softmax, routing_metadata,  # noqa: F401
                   stable_topk)
 from .newton_schulz import newton_schulz, newton_schulz_ref  # noqa: F401

@@ -195,6 +195,11 @@ int b200_gemm2_bf16_batched(int mode, const void* A, const void* B, void* out, c
 int b200_ssd_state_fwd(const float* add, const float* keep, float* s_in, int B, int nC, int H, int PN, cudaStream_t st);
 int b200_ssd_state_bwd(const float* d_s_in, const float* s_in, const float* keep, float* d_add, float* d_keep_part,
                        int B, int nC, int H, int PN, cudaStream_t st);
+// NT product with SwiGLU in the epilogue on the SM-pair kernel (gemm2_bf16.cu): act = silu(A·B_gateᵀ)∘(A·B_upᵀ), h optional
+int b200_gemm2_swiglu_bf16(const void* A, const void* B, void* h, void* act, int M, int I, int K, int lda, int ldb, int num_sms,
+                           int* status, cudaStream_t stream);
+int b200_grouped_gemm2_swiglu_bf16(const void* A, const void* B, void* h, void* act, const int* offsets, int E, int capacity,
+                                   int I, int K, int num_sms, int* status, cudaStream_t stream);
 // (I + A)^-1 for [n_mat, 64, 64] strictly lower-triangular fp32 matrices (tri_inverse.cu)
 int b200_tri_inverse64(const float* A, float* T, int n_mat, cudaStream_t st);
 // One pass of the chunked gated-delta-rule recurrence (gdn_chunk.cu)

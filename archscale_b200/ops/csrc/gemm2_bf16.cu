@@ -57,6 +57,15 @@ struct Gemm2Params {
   // serial split-K for accumulating fp32 output (see GemmParams in gemm_bf16.cu); 8 counters per tile (CTA rank × epilogue warp)
   int split_k;
   uint32_t* sem;
+  // SwiGLU in the epilogue (NT products with bf16 output, plain or GROUPED 1).  B holds [gate rows | up rows] per (expert)
+  // matrix, glu_half rows each.  A tile pairs 128 gate columns with the 128 up columns of the same index: the leader CTA
+  // loads the gate rows as its half of the B operand and its peer the up rows, so that every epilogue thread finds
+  // gate j in accumulator column j and up j in column 128 + j of its row.  out (may be null) receives the pre-activation
+  // [M, 2·glu_half] as without the fusion, out2 [M, glu_half] (leading dimension ldc2) receives silu(gate)·up computed from
+  // the bf16-rounded values, i.e. bit for bit what the separate SwiGLU kernel makes of `out`.
+  int glu_half;
+  void* out2;
+  int ldc2;
 };
 
 extern uint32_t* g_splitk_sem;
@@ -93,7 +102,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     for (int i = threadIdx.x; i <= gp.E; i += blockDim.x) s_off[i] = gp.offsets[i];
     __syncthreads();
   }
-  const int num_n = (p.N + T2_BN - 1) / T2_BN;
+  const int glu = (!OUT_F32 && !A_MN && !B_MN && (GROUPED == 0 || GROUPED == 1)) ? p.glu_half : 0;
+  const int num_n = glu ? (glu + T2_HALF - 1) / T2_HALF : (p.N + T2_BN - 1) / T2_BN;
   const int num_m = GROUPED == 1 ? s_off[gp.E] / T2_BM : (p.M + T2_BM - 1) / T2_BM;
   const int SK = (GROUPED == 0 && OUT_F32 && p.split_k > 1) ? p.split_k : 1;
   const bool sym = GROUPED == 3 && gp.sym != 0;
@@ -162,7 +172,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       int stage = 0; uint32_t phase = 0;
       for (int t = pair; t < num_tiles; t += n_pair) {
         Tile2 tl; get_tile(t, tl);
-        const int ma = tl.m0 + rank * T2_HALF, nb = tl.n0 + rank * T2_HALF;
+        const int ma = tl.m0 + rank * T2_HALF, nb = glu ? tl.n0 / 2 + rank * glu : tl.n0 + rank * T2_HALF;
         for (int kb = tl.kb0; kb < tl.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) goto done;
           uint8_t* sa = smem + stage * T2_STAGE_BYTES;
@@ -270,6 +280,41 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         }
       }
       const uint32_t taddr = tmem_base + acc * T2_BN + (static_cast<uint32_t>(q * 32) << 16);
+      if (glu) {
+#pragma unroll 1
+        for (int c = 0; c < T2_HALF / 32; ++c) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32(taddr + c * 32, rg);
+          tmem_ld_32x32(taddr + T2_HALF + c * 32, ru);
+          tmem_ld_wait();
+          const int col = n0 / 2 + c * 32;              // gate column; its up column is glu + col
+          if (row < row_limit && col < glu && !empty_tile) {
+            __nv_bfloat16* hg = p.out ? reinterpret_cast<__nv_bfloat16*>(p.out) + tl.out_off + static_cast<size_t>(row) * p.ldc + col : nullptr;
+            __nv_bfloat16* oa = reinterpret_cast<__nv_bfloat16*>(p.out2) + static_cast<size_t>(row) * p.ldc2 + col;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col + j < glu) {
+                uint32_t gw[4], uw[4], aw[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  gw[e] = pack_bf16x2(__uint_as_float(rg[j + 2 * e]) * alpha, __uint_as_float(rg[j + 2 * e + 1]) * alpha);
+                  uw[e] = pack_bf16x2(__uint_as_float(ru[j + 2 * e]) * alpha, __uint_as_float(ru[j + 2 * e + 1]) * alpha);
+                  const float2 g2 = unpack_bf16x2(gw[e]), u2 = unpack_bf16x2(uw[e]);
+                  aw[e] = pack_bf16x2(g2.x * (1.f / (1.f + __expf(-g2.x))) * u2.x, g2.y * (1.f / (1.f + __expf(-g2.y))) * u2.y);
+                }
+                if (hg) {
+                  *reinterpret_cast<uint4*>(hg + j) = make_uint4(gw[0], gw[1], gw[2], gw[3]);
+                  *reinterpret_cast<uint4*>(hg + glu + j) = make_uint4(uw[0], uw[1], uw[2], uw[3]);
+                }
+                *reinterpret_cast<uint4*>(oa + j) = make_uint4(aw[0], aw[1], aw[2], aw[3]);
+              }
+            }
+          } else if (row < row_limit && col < glu) {    // expert without rows: nothing was accumulated
+            __nv_bfloat16* oa = reinterpret_cast<__nv_bfloat16*>(p.out2) + static_cast<size_t>(row) * p.ldc2 + col;
+            for (int j = 0; j < 32 && col + j < glu; j += 8) *reinterpret_cast<uint4*>(oa + j) = make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < T2_BN / 32; ++c) {
         uint32_t r[32];
@@ -414,6 +459,60 @@ extern "C" int b200_gemm2_bf16(int mode, const void* A, const void* B, void* out
   if (mode == 1) return out_f32 ? launch2<0, 1, 1>(ta, tb, p, num_sms, stream) : launch2<0, 1, 0>(ta, tb, p, num_sms, stream);
   if (mode == 2) return out_f32 ? launch2<1, 1, 1>(ta, tb, p, num_sms, stream) : launch2<1, 1, 0>(ta, tb, p, num_sms, stream);
   return -4;
+}
+
+// act [M, I] = silu(A·B_gateᵀ) ∘ (A·B_upᵀ) with B [2I, K] = [gate rows | up rows]; h (may be null) also receives the
+// pre-activation [M, 2I].  A [M, K] with leading dimension lda; I a multiple of 8.
+extern "C" int b200_gemm2_swiglu_bf16(const void* A, const void* B, void* h, void* act, int M, int I, int K, int lda, int ldb,
+                                      int num_sms, int* status, cudaStream_t stream) {
+  using namespace b200;
+  if (M <= 0 || I <= 0 || K <= 0) return 0;
+  if (I % 8) return -1;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return -5;
+    ctx_bound = true;
+  }
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d_bf16(&ta, A, K, M, lda, T2_BK, T2_HALF);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tb, B, K, 2 * static_cast<uint64_t>(I), ldb, T2_BK, T2_HALF);
+  if (rc) return rc;
+  Gemm2Params p{h, nullptr, M, 2 * I, K, 2 * I, 1.f, 0.f, 0, status, 1, nullptr, I, act, I};
+  auto kern = gemm2_bf16_kernel<0, 0, 0>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES) != cudaSuccess) return -2;
+    configured = true;
+  }
+  const int tiles = ((M + T2_BM - 1) / T2_BM) * ((I + T2_HALF - 1) / T2_HALF);
+  const int pairs = num_sms / 2;
+  const int grid = 2 * (tiles < pairs ? tiles : pairs);
+  kern<<<grid, T2_THREADS, T2_SMEM_BYTES, stream>>>(ta, tb, p, Group2Params{});
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// The same over expert segments (GROUPED 1): A rows grouped by expert (offsets[E+1], multiples of 256), B [E · 2I, K].
+extern "C" int b200_grouped_gemm2_swiglu_bf16(const void* A, const void* B, void* h, void* act, const int* offsets, int E,
+                                              int capacity, int I, int K, int num_sms, int* status, cudaStream_t stream) {
+  using namespace b200;
+  if (E <= 0 || E > 256 || capacity <= 0 || capacity % T2_BM || I % 8) return -1;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return -5;
+    ctx_bound = true;
+  }
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d_bf16(&ta, A, K, capacity, K, T2_BK, T2_HALF);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tb, B, K, static_cast<uint64_t>(E) * 2 * I, K, T2_BK, T2_HALF);
+  if (rc) return rc;
+  Group2Params gp{offsets, E, 2 * I, nullptr, nullptr, 0};
+  Gemm2Params p{h, nullptr, capacity, 2 * I, K, 2 * I, 1.f, 0.f, 0, status, 1, nullptr, I, act, I};
+  const int max_tiles = (capacity / T2_BM) * ((I + T2_HALF - 1) / T2_HALF);
+  return launch2_grouped<0, 0, 0, 1>(ta, tb, p, gp, max_tiles, num_sms, stream);
 }
 
 // Grouped GEMM over expert segments, same contract as b200_grouped_gemm_bf16 except that `offsets` (and `capacity`) must

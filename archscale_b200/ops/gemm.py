@@ -125,6 +125,63 @@ class _LinearFn(torch.autograd.Function):
         return dx, dw, db
 
 
+class _LinearSwiGLUFn(torch.autograd.Function):
+    """``silu(x·W_gateᵀ) ∘ (x·W_upᵀ)`` with the activation computed in the GEMM epilogue (``W = [gate rows | up rows]``).
+    The pre-activation is still written (the backward needs it) but not read back in the forward pass."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        x2 = x.reshape(-1, x.shape[-1])
+        h, act = backend.require_extension().gemm_swiglu(x2, weight, True)
+        backend.count_launch()
+        ctx.save_for_backward(x, weight, h)
+        ctx.weight_ref = weight
+        return act.view(*x.shape[:-1], weight.shape[0] // 2)
+
+    @staticmethod
+    def backward(ctx, dact):
+        x, weight, h = ctx.saved_tensors
+        da2 = dact.reshape(-1, dact.shape[-1])
+        if not da2.is_contiguous():
+            da2 = da2.contiguous()
+        dh = backend.require_extension().swiglu_packed_bwd(h, da2)
+        backend.count_launch()
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = matmul_nn(dh, weight).view(x.shape)
+        if ctx.needs_input_grad[1]:
+            main_grad = getattr(ctx.weight_ref, "main_grad", None)
+            if main_grad is not None:
+                matmul_tn_acc_(main_grad, dh, x2)
+            else:
+                dw = matmul_tn(dh, x2)
+        return dx, dw
+
+
+def fused_swiglu_enabled() -> bool:
+    """SwiGLU in the epilogue of the SM-pair GEMM (off with ``ARCHSCALE_B200_FUSED_SWIGLU=0`` or the one-CTA GEMM)."""
+    import os
+    return (os.environ.get("ARCHSCALE_B200_FUSED_SWIGLU", "1") != "0" and os.environ.get("ARCHSCALE_B200_GEMM", "") != "1cta"
+            and backend.has("gemm_swiglu"))
+
+
+def linear_swiglu(x: torch.Tensor, weight: torch.Tensor) -> Optional[torch.Tensor]:
+    """SwiGLU of ``x @ weightᵀ`` (gate = first half of the output features) in one GEMM launch, or ``None`` when the
+    fused kernel does not take this case (the caller then runs ``linear`` + ``swiglu_packed``)."""
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.dim() == 2
+            and weight.shape[0] % 16 == 0 and x.shape[-1] % 8 == 0 and x.shape[-1] >= 64
+            and (x.numel() // x.shape[-1]) % 8 == 0 and weight.stride(-1) == 1 and weight.stride(0) % 8 == 0
+            and weight.data_ptr() % 16 == 0 and fused_swiglu_enabled() and backend.use_cuda_kernel("gemm", x, weight)):
+        return None
+    g = getattr(weight, "_fsdp_group", None)
+    if g is not None and getattr(g, "ag_pending", False):
+        return None                                     # this GEMM carries the unit's fused all-gather: keep that path
+    if not x.is_contiguous():
+        x = x.contiguous()
+    return _LinearSwiGLUFn.apply(x, weight)
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x @ weightᵀ + bias``; bf16 CUDA inputs run the tcgen05 kernel for fwd, dgrad and wgrad."""
     if (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16

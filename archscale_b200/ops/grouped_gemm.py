@@ -15,6 +15,7 @@ from __future__ import annotations
 import torch
 
 from . import backend
+from .gemm import fused_swiglu_enabled
 
 
 def supported(x, w_in, w_out, b_in, b_out) -> bool:
@@ -39,12 +40,16 @@ class _MoEFFNFn(torch.autograd.Function):
         sc = scores.float().contiguous()
         counts, offsets, slot_pair, pair_slot = ext.routing_layout(indices.reshape(-1).contiguous(), E)
         xs = ext.gather_rows(x, slot_pair, None, K, offsets)
-        h = ext.grouped_gemm_bf16(0, xs, w_in.reshape(E * I2, C), offsets, 0, I2, C, None)
-        a = ext.swiglu_packed_fwd(h)
+        if xs.shape[0] % 256 == 0 and fused_swiglu_enabled():
+            h, a = ext.grouped_gemm_swiglu(xs, w_in.reshape(E * I2, C), offsets, I, True)      # SwiGLU in the epilogue
+        else:
+            h = ext.grouped_gemm_bf16(0, xs, w_in.reshape(E * I2, C), offsets, 0, I2, C, None)
+            a = ext.swiglu_packed_fwd(h)
         y = ext.grouped_gemm_bf16(0, a, w_out.reshape(E * C, I), offsets, 0, C, I, None)
         out = ext.combine_rows(y, pair_slot, sc, N, K)
         backend.count_launch(9)
-        ctx.save_for_backward(xs, h, y, w_in, w_out, sc, offsets, slot_pair, pair_slot)
+        # `a` is kept as well (a quarter of the size of xs or y): recomputing it in backward is one more pass over h
+        ctx.save_for_backward(xs, h, a, y, w_in, w_out, sc, offsets, slot_pair, pair_slot)
         ctx.dims = (N, C, E, I2, I, K)
         ctx.w_refs = (w_in, w_out)
         ctx.score_dtype = scores.dtype
@@ -53,12 +58,11 @@ class _MoEFFNFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout):
         ext = backend.require_extension()
-        xs, h, y, w_in, w_out, sc, offsets, slot_pair, pair_slot = ctx.saved_tensors
+        xs, h, a, y, w_in, w_out, sc, offsets, slot_pair, pair_slot = ctx.saved_tensors
         N, C, E, I2, I, K = ctx.dims
         dout = dout.contiguous()
         dscores = ext.pair_dots(y, dout, pair_slot, K).view(N, K).to(ctx.score_dtype)
         dy = ext.gather_rows(dout, slot_pair, sc.reshape(-1), K, offsets)             # dy[slot] = score · dout[token]
-        a = ext.swiglu_packed_fwd(h)
         da = ext.grouped_gemm_bf16(1, dy, w_out.reshape(E * C, I), offsets, 0, I, C, None)
         mg_out = getattr(ctx.w_refs[1], "main_grad", None)
         dw_out = ext.grouped_gemm_bf16(2, dy, a, offsets, C, I, 0, mg_out)
@@ -67,7 +71,7 @@ class _MoEFFNFn(torch.autograd.Function):
         mg_in = getattr(ctx.w_refs[0], "main_grad", None)
         dw_in = ext.grouped_gemm_bf16(2, dh, xs, offsets, I2, C, 0, mg_in)
         dx = ext.combine_rows(dxs, pair_slot, None, N, K)
-        backend.count_launch(9)
+        backend.count_launch(8)
         return dx, (None if mg_in is not None else dw_in), (None if mg_out is not None else dw_out), dscores, None
 
 

@@ -28,6 +28,7 @@ import torch.distributed as dist
 
 from archscale_b200 import ops
 from archscale_b200.ops import backend
+from archscale_b200.ops.gemm import fused_swiglu_enabled
 
 
 # ------------------------------------------------------------------ setup
@@ -213,15 +214,18 @@ class _EPPeerFn(torch.autograd.Function):
         d.exchange()                                                       # every rank's rows and counts are published
         xr, recv_off = d.receive(E_l, key=(site, "fwd"))
         ctx.site = site
-        h1 = ext.grouped_gemm_bf16(0, xr, w_in.reshape(E_l * I2, C), recv_off, 0, I2, C)
-        a = ext.swiglu_packed_fwd(h1)
+        if xr.shape[0] % 256 == 0 and fused_swiglu_enabled():
+            h1, a = ext.grouped_gemm_swiglu(xr, w_in.reshape(E_l * I2, C), recv_off, I, True)   # SwiGLU in the epilogue
+        else:
+            h1 = ext.grouped_gemm_bf16(0, xr, w_in.reshape(E_l * I2, C), recv_off, 0, I2, C)
+            a = ext.swiglu_packed_fwd(h1)
         ext.grouped_gemm_bf16(0, a, w_out.reshape(E_l * C, I), recv_off, 0, C, I, None, d.result)
         d.exchange()                                                       # expert outputs are ready everywhere
         yb = torch.empty(slot_pair.numel(), C, dtype=h.dtype, device=h.device)
         ext.ep_return(d.heap.bases, d.off_counts, d.off_offsets, d.off_table, d.off_result, yb, d.rank, E_l, C)
         out = ext.combine_rows(yb, pair_slot, sc, N, K)
         backend.count_launch(14)
-        ctx.save_for_backward(xr, h1, yb, w_in, w_out, sc, counts, offsets, slot_pair, pair_slot)
+        ctx.save_for_backward(xr, h1, a, yb, w_in, w_out, sc, counts, offsets, slot_pair, pair_slot)
         ctx.meta = (N, C, K, E_l, I2, I, n_experts, group, scores.dtype)
         ctx.w_refs = (w_in, w_out)
         return out
@@ -229,7 +233,7 @@ class _EPPeerFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout):
         ext = backend.require_extension()
-        xr, h1, yb, w_in, w_out, sc, counts, offsets, slot_pair, pair_slot = ctx.saved_tensors
+        xr, h1, a, yb, w_in, w_out, sc, counts, offsets, slot_pair, pair_slot = ctx.saved_tensors
         N, C, K, E_l, I2, I, n_experts, group, score_dtype = ctx.meta
         dout = dout.contiguous()
         d = PeerDispatcher.get(group, dout.device, slot_pair.numel(), C, n_experts)
@@ -239,7 +243,6 @@ class _EPPeerFn(torch.autograd.Function):
         ext.gather_rows(dout, slot_pair, sc.reshape(-1), K, offsets, d.send[0])      # dy[slot] = score · dout[token]
         d.exchange()
         dyr, recv_off = d.receive(E_l, key=(ctx.site, "bwd"))
-        a = ext.swiglu_packed_fwd(h1)
         da = ext.grouped_gemm_bf16(1, dyr, w_out.reshape(E_l * C, I), recv_off, 0, I, C)
         mg_out = getattr(ctx.w_refs[1], "main_grad", None)
         dw_out = ext.grouped_gemm_bf16(2, dyr, a, recv_off, C, I, 0, mg_out)

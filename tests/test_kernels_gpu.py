@@ -381,3 +381,36 @@ def test_adamw_fused_matches_foreach(mode):
         assert torch.allclose(u, ur, atol=1e-5, rtol=1e-4)
         assert torch.allclose(acc, torch.stack([xr.pow(2).sum(), ur.pow(2).sum()]), rtol=1e-4)
     assert torch.allclose(m, mr, atol=1e-6) and torch.allclose(v, vr, atol=1e-7)
+
+
+@pytest.mark.parametrize("M,I,K", [(512, 256, 256), (1000, 1408, 512), (4096, 5632, 2048), (264, 72, 136)])
+def test_gemm_with_swiglu_epilogue_equals_gemm_then_swiglu(M, I, K):
+    """The pre-activation is the plain GEMM's result bit for bit, and the activation is what the separate SwiGLU kernel
+    makes of it (both computed from the bf16-rounded values); against fp32 PyTorch the usual bf16 tolerance holds."""
+    torch.manual_seed(8)
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(2 * I, K, device="cuda") * 0.05).bfloat16()
+    h, act = _ext().gemm_swiglu(x, w, True)
+    h_ref = ops.matmul_nt(x, w)
+    assert torch.equal(h, h_ref)
+    assert torch.equal(act, _ext().swiglu_packed_fwd(h_ref))
+    _, act_only = _ext().gemm_swiglu(x, w, False)
+    assert torch.equal(act_only, act)
+    hf = x.float() @ w.float().t()
+    assert _rel(act, torch.nn.functional.silu(hf[:, :I]) * hf[:, I:]) < 2e-2
+    assert _ext().device_status() == 0
+
+
+def test_linear_swiglu_autograd_matches_reference():
+    torch.manual_seed(9)
+    x = torch.randn(4, 256, 512, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(2 * 1024, 512, device="cuda") * 0.05).bfloat16().requires_grad_()
+    y = ops.linear_swiglu(x, w)
+    assert y is not None and y.shape == (4, 256, 1024)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    hr = xr @ wr.t()
+    yr = torch.nn.functional.silu(hr[..., :1024]) * hr[..., 1024:]
+    yr.backward(g.float())
+    assert _rel(y, yr) < 2e-2 and _rel(x.grad, xr.grad) < 3e-2 and _rel(w.grad, wr.grad) < 3e-2

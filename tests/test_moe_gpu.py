@@ -68,3 +68,23 @@ def test_moe_ffn_forward_backward(N, C, E, I, K):
     assert _rel(w_in.grad, wir.grad) < 3e-2
     assert _rel(w_out.grad, wor.grad) < 3e-2
     assert _rel(logits.grad, lr.grad) < 3e-2
+
+
+def test_grouped_gemm_with_swiglu_epilogue_equals_unfused():
+    """Expert up-projection with SwiGLU in the epilogue against the grouped GEMM followed by the SwiGLU kernel."""
+    ext = backend.require_extension()
+    torch.manual_seed(5)
+    N, C, E, I, K = 1536, 512, 8, 384, 2
+    x = (torch.randn(N, C, device="cuda") * 0.5).bfloat16()
+    w_in = (torch.randn(E, 2 * I, C, device="cuda") * 0.05).bfloat16()
+    idx = torch.stack([torch.randperm(E, device="cuda")[:K] for _ in range(N)]).to(torch.int32)
+    counts, offsets, slot_pair, pair_slot = ext.routing_layout(idx.reshape(-1).contiguous(), E)
+    xs = ext.gather_rows(x, slot_pair, None, K, offsets)
+    assert xs.shape[0] % 256 == 0
+    h_ref = ext.grouped_gemm_bf16(0, xs, w_in.reshape(E * 2 * I, C), offsets, 0, 2 * I, C, None)
+    a_ref = ext.swiglu_packed_fwd(h_ref)
+    h, a = ext.grouped_gemm_swiglu(xs, w_in.reshape(E * 2 * I, C), offsets, I, True)
+    rows = int(offsets[-1].item())
+    assert torch.equal(h[:rows], h_ref[:rows])
+    assert torch.equal(a[:rows], a_ref[:rows])
+    assert ext.device_status() == 0
