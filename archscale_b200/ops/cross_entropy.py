@@ -112,12 +112,21 @@ class _FLCEFn(torch.autograd.Function):
         return gx, gw, None, None, None, None, None
 
 
-def default_chunk_rows(N: int, H: int, V: int) -> int:
-    """Rows per chunk so that the logits chunk is about as large as the hidden states."""
+def default_chunk_rows(N: int, H: int, V: int, on_gpu: bool = False) -> int:
+    """Rows per chunk.  The reference's rule makes the logits chunk about as large as the hidden states
+    (``ceil(V / H)`` chunks, `lit_gpt/fused_linear_cross_entropy.py`): right when memory is the constraint, but every chunk
+    is one more read-modify-write pass over the fp32 weight gradient ``[V, H]`` (2 GB for a 200 K vocabulary: 32 chunks of
+    256 rows cost 130 GB of traffic for 8192 tokens).  On a GPU the chunk therefore grows until its logits reach a byte
+    budget (``ARCHSCALE_B200_FLCE_CHUNK_MB``, default 2048 MiB of bf16 logits), never below the reference's size."""
     chunks = max(1, -(-V // max(H, 1)))
     chunks = min(chunks, 64)
     rows = -(-N // chunks)
     rows = max(256, ((rows + 255) // 256) * 256)
+    if on_gpu:
+        import os
+        budget = int(float(os.environ.get("ARCHSCALE_B200_FLCE_CHUNK_MB", "2048")) * (1 << 20))
+        by_budget = (budget // max(2 * V, 1)) // 256 * 256
+        rows = max(rows, by_budget)
     return min(rows, N)
 
 
@@ -131,7 +140,7 @@ def fused_linear_cross_entropy(x: torch.Tensor, weight: torch.Tensor, target: to
     x2 = x.reshape(-1, x.shape[-1])
     t = target.reshape(-1)
     if chunk_rows is None:
-        chunk_rows = default_chunk_rows(x2.shape[0], x2.shape[1], weight.shape[0])
+        chunk_rows = default_chunk_rows(x2.shape[0], x2.shape[1], weight.shape[0], on_gpu=x2.is_cuda)
     return _FLCEFn.apply(x2, weight, t, ignore_index, label_smoothing, lse_square_scale, chunk_rows)
 
 

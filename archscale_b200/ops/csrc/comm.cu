@@ -300,7 +300,7 @@ __global__ void ep_plan_kernel(EpArgs a, int* __restrict__ recv_offsets, int* st
     int acc = 0;
     for (int e = 0; e < a.e_local; ++e) { recv_offsets[e] = acc; acc += (s_total[e] + 255) / 256 * 256; }
     recv_offsets[a.e_local] = acc;
-    if (acc > a.recv_cap && status) atomicCAS(status, 0, STATUS_BAD_ARG);
+    if (acc > a.recv_cap && status) atomicCAS(status, 0, STATUS_EP_OVERFLOW);
   }
   __syncthreads();
   if (el < a.e_local) {

@@ -144,6 +144,8 @@ class PeerDispatcher:
         self.chan = 0
         self.stats = {}                                  # call site → rows received there on earlier steps
         self.margin = float(os.environ.get("ARCHSCALE_B200_EP_MARGIN", "1.25"))
+        self.sizing = os.environ.get("ARCHSCALE_B200_EP_SIZING", "exact")       # "exact" | "history" (see receive())
+        self.sync_calls = int(os.environ.get("ARCHSCALE_B200_EP_SYNC_CALLS", "8"))
 
     def exchange(self) -> None:
         self.heap.barrier(self.chan)
@@ -161,32 +163,45 @@ class PeerDispatcher:
         return min(((want + 255) // 256) * 256, self.recv_cap)
 
     def receive(self, e_local: int, key=None) -> tuple:
-        """Plan + pull: returns (rows received, in local memory; recv_offsets).
+        """Plan + pull: returns (rows received, in local memory; recv_offsets).  ``key = (site, "fwd" | "bwd")`` names the
+        MoE layer and the pass.
 
-        The buffer is sized from the row counts this call site (``key``: one MoE layer, forward or backward) received on
-        earlier steps plus a margin — a device-side bound, no device→host wait in the step.  The plan kernel compares
-        the real total with that size: on overflow it raises the device status word, the pull copies nothing and the
-        grouped GEMMs never store past the buffer, so the step computes garbage but touches no foreign memory; the
-        trainer reads the status word before the optimizer step and stops.  The first two calls of a site read the
-        count on the host once (there is nothing to estimate from yet)."""
-        st = self.stats.setdefault(key, {"seen": 0, "event": None, "calls": 0,
+        How many rows arrive is known on the device only (the plan kernel sums the peers' counts), and the buffer that
+        holds them is kept for the backward pass, so it should not be worst-case sized.  Sizing rules:
+
+        * forward, default: the host reads the total once (4 bytes, one wait per MoE layer and step) and allocates exactly;
+        * backward: the gradient rows of a layer are as many as its forward rows were, so the forward's size is reused —
+          no read, no wait;
+        * forward with ``ARCHSCALE_B200_EP_SIZING=history``: after a site's first calls the size comes from the counts it
+          saw on earlier steps times ``ARCHSCALE_B200_EP_MARGIN`` (read back asynchronously, never waited for).  Routing
+          that shifts by more than the margin between two steps overflows the buffer: the plan kernel then raises the
+          device status word (``STATUS_EP_OVERFLOW``), the pull copies nothing past the buffer and the grouped GEMMs never
+          store past it, so the step computes garbage but touches no foreign memory, and the trainer stops at its next
+          status check.  Early in training (routing collapses and recovers within a few steps) this mode is not safe."""
+        st = self.stats.setdefault(key, {"seen": 0, "event": None, "calls": 0, "last_cap": 0,
                                          "pinned": torch.zeros(1, dtype=torch.int32).pin_memory()})
         st["calls"] += 1
-        cap = self._rows_to_allocate(key) if st["calls"] > 2 else None
+        cap = None
+        site, direction = key if isinstance(key, tuple) and len(key) == 2 else (key, "fwd")
+        fwd = self.stats.get((site, "fwd")) if direction == "bwd" else None
+        if fwd is not None and fwd["last_cap"] > 0:
+            cap = fwd["last_cap"]
+        elif self.sizing == "history" and st["calls"] > self.sync_calls:
+            cap = self._rows_to_allocate(key)
         recv_off = self.ext.ep_plan(self.heap.bases, self.off_counts, self.off_table, self.rank, e_local,
                                     self.recv_cap if cap is None else cap)
         if cap is None:
-            # start-up: routing moves fastest right after initialisation, and there is no history yet
             used = int(recv_off[-1].item())
             if used > self.recv_cap:
                 raise RuntimeError(f"expert-parallel receive overflow: {used} rows > capacity {self.recv_cap}; "
                                    "raise ARCHSCALE_B200_EP_CAPACITY")
             st["seen"] = max(st["seen"], used, 1)
             cap = max(((used + 255) // 256) * 256, 256)
-        elif st["event"] is None:
+        elif self.sizing == "history" and st["event"] is None:
             st["pinned"].copy_(recv_off[-1:], non_blocking=True)       # read by a later call, never waited for
             st["event"] = torch.cuda.Event()
             st["event"].record()
+        st["last_cap"] = cap
         rows = torch.empty(cap, self.C, dtype=torch.bfloat16, device=self.device)
         self.ext.ep_pull(self.heap.bases, self.off_counts, self.off_offsets, self.off_table, self.off_send[0], rows,
                          self.rank, e_local, recv_off)
@@ -194,8 +209,8 @@ class PeerDispatcher:
 
 
 class _EPPeerFn(torch.autograd.Function):
-    """Expert-parallel routed FFN with peer-memory dispatch / combine (no NCCL; no host wait after a layer's first two
-    calls — see :meth:`PeerDispatcher.receive`)."""
+    """Expert-parallel routed FFN with peer-memory dispatch / combine (no NCCL; one 4-byte host read per layer in the
+    forward pass to size the receive buffer, none in the backward pass — see :meth:`PeerDispatcher.receive`)."""
 
     @staticmethod
     def forward(ctx, h, w_in, w_out, scores, indices, n_experts, group, site=None):

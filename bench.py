@@ -209,6 +209,22 @@ def run_ours(args) -> None:
             fb += ev[0].elapsed_time(ev[1])
             op += ev[1].elapsed_time(ev[2])
         phases = {"forward_backward_ms": fb / args.steps, "optimizer_step_ms": op / args.steps}
+    if args.kernel_table > 0:
+        from torch.profiler import ProfilerActivity, profile
+        sync_all()
+        if trainer.mesh.rank == 0:
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                step_dev(0)
+                torch.cuda.synchronize()
+            rows = sorted(prof.key_averages(), key=lambda e: -e.device_time_total)
+            tot = sum(e.device_time_total for e in rows)
+            print(f"kernel table: {tot / 1e3:.2f} ms of device time over {sum(e.count for e in rows)} launches in one step "
+                  f"(step {ms_per_step:.2f} ms)", file=sys.stderr)
+            for e in rows[:args.kernel_table]:
+                print(f"{e.device_time_total / 1e3:9.3f} ms {100 * e.device_time_total / tot:5.1f}% x{e.count:5d}  {e.key[:120]}", file=sys.stderr)
+        else:
+            step_dev(0)
+        sync_all()
     status = backend.load_extension().device_status() if backend.load_extension() is not None else 0
 
     # MFU in the reference's convention (3·(2·N·T + attention over the full T×T square) per sequence, peak 2.25e15), but with N
@@ -272,6 +288,9 @@ def main() -> None:
     ap.add_argument("--config", default="dense", choices=sorted(CONFIGS))
     ap.add_argument("--act-ckpt", dest="act_ckpt", action="store_true", help="activation checkpointing per block")
     ap.add_argument("--phases", action="store_true", help="also report forward+backward and optimizer-step times")
+    ap.add_argument("--kernel-table", dest="kernel_table", type=int, default=0, metavar="N",
+                    help="after the measurement, run one more step under torch.profiler on rank 0 and print the N kernels with "
+                         "the largest device time to stderr (shares of the step; not part of any reported number)")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (ranks of a tp group share a micro-batch)")
     ap.add_argument("--fp8", action="store_true", help="MXFP8 block-scaled linear layers (dtype is then reported as mxfp8)")
     ap.add_argument("--fused-comm", dest="fused_comm", action="store_true", default=True,
