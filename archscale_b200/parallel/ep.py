@@ -196,7 +196,9 @@ class PeerDispatcher:
                 raise RuntimeError(f"expert-parallel receive overflow: {used} rows > capacity {self.recv_cap}; "
                                    "raise ARCHSCALE_B200_EP_CAPACITY")
             st["seen"] = max(st["seen"], used, 1)
-            cap = max(((used + 255) // 256) * 256, 256)
+            # rounded up to 8192 rows: sizes that differ a little from step to step then map to the same cached block of
+            # the allocator instead of forcing a new cudaMalloc (a device synchronisation) now and then
+            cap = min(max(((used + 8191) // 8192) * 8192, 256), max(self.recv_cap, ((used + 255) // 256) * 256))
         elif self.sizing == "history" and st["event"] is None:
             st["pinned"].copy_(recv_off[-1:], non_blocking=True)       # read by a later call, never waited for
             st["event"] = torch.cuda.Event()
