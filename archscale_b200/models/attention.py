@@ -98,7 +98,11 @@ class CausalSelfAttention(nn.Module):
         if self.qk_norm:
             self.q_norm = FusedRMSNorm(hs, eps=config.norm_eps)
             self.k_norm = FusedRMSNorm(hs, eps=config.norm_eps)
-        if self.use_da:
+        self.use_sigmoid = config.use_sigmoid
+        if self.use_sigmoid:
+            # sigmoid attention with a per-head norm on its output (`lit_gpt/attention.py:77-81,353-356`)
+            self.sub_norm = config.norm_class(hs, eps=config.norm_eps)
+        elif self.use_da:
             depth = 10000 if config.da_const_lamb else layer_idx
             self.da = DiffAttention(hs, depth, softmax_scale=self.scale, window_size=self.win_tuple)
         if config.sink_attn:
@@ -124,7 +128,7 @@ class CausalSelfAttention(nn.Module):
                 torch_default_init(m.weight)
                 if m.bias is not None:
                     nn.init.zeros_(m.bias)
-        for name in ("q_norm", "k_norm", "attn_norm"):
+        for name in ("q_norm", "k_norm", "attn_norm", "sub_norm"):
             m = getattr(self, name, None)
             if m is not None and hasattr(m, "reset_parameters"):
                 m.reset_parameters()
@@ -153,6 +157,14 @@ class CausalSelfAttention(nn.Module):
         return cos[:T], sin[:T]
 
     def _attend(self, q, k, v, cu_seqlens):
+        if not self.config.fa2:
+            # the reference's non-flash path: sqrt of the softmax weights over silu(v), no window / packing (`:426-441`)
+            self.z_mean = None
+            return ops.pointwise_attention(q, k, v, "sqrt_softmax", scale=self.scale)
+        if self.use_sigmoid:
+            self.z_mean = None
+            out = ops.pointwise_attention(q, k, v, "sigmoid", scale=self.scale, window=self.win_tuple, cu_seqlens=cu_seqlens)
+            return self.sub_norm(out)
         if self.use_da:
             self.z_mean = None
             return self.da(q, k, v, cu_seqlens=cu_seqlens)

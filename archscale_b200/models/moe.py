@@ -187,5 +187,131 @@ class MoE(SonicMoE):
         return self.mods_in.stacked(), self.mods_out.stacked(), None, None
 
 
+class AttentionExperts(nn.Module):
+    """Mixture of attention experts (`lit_gpt/moe.py:101-345` with ``is_attn=True``): every routed expert owns the q/k/v
+    and output projections of ``n_head / top_k`` heads; a token's top-k experts each attend, causally and inside the
+    token's own sequence, over the tokens that were routed to the same expert, and the outputs are summed with the router
+    gates.  The tokens of one (expert, sequence) pair form one packed document of a variable-length attention call, RoPE
+    uses the tokens' original positions with the window-derived base of the reference (`:405-417`).
+
+    Parameters are named like the per-expert MLP variant (``router.lc_proj``, ``mods_in.weight{e}``, ``mods_out.weight{e}``).
+    The expert projections run one GEMM per expert and the segment table is read on the host: this variant is never
+    instantiated by the reference's own model code (`lit_gpt/model.py:443` passes ``is_attn=False``) and is kept simple."""
+
+    def __init__(self, config: Config) -> None:
+        super().__init__()
+        assert not config.share_expert, "a shared expert is not supported for attention experts (`lit_gpt/moe.py:138`)"
+        self.config = config
+        self.aux_gamma, self.aux_style = config.aux_gamma, config.aux_style
+        self.global_aux = config.global_aux and config.aux_style != "switch_seq"
+        self.top_k = config.top_k
+        self.n_mods = config.sparsity * config.top_k
+        self.n_head = config.n_head // config.top_k
+        self.n_query_groups = config.n_query_groups // config.top_k
+        assert self.n_head >= 1 and self.n_query_groups >= 1 and self.n_head % self.n_query_groups == 0
+        hs, C = config.head_size, config.n_embd
+        self.head_size = hs
+        mod_in = (self.n_head + 2 * self.n_query_groups) * hs + (self.n_head * hs if config.gated_attn else 0)
+        self.mod_out_size = self.n_head * hs
+        self.router = _Router(config, self.n_mods)
+        self.mods_in = _PerExpertLinear(self.n_mods, C, mod_in)
+        self.mods_out = _PerExpertLinear(self.n_mods, self.mod_out_size, C)
+        self.scale = config.attn_scale if config.attn_scale is not None else 1.0 / math.sqrt(hs)
+        if config.mup:
+            self.scale = self.scale * math.sqrt(config.mup_hd0) / math.sqrt(hs)
+        self.win_tuple = (config.local_window - 1, 0) if config.local_window > -1 else (-1, -1)
+        self.logit_scale = config.mup_d0 / config.n_layer if (config.mup and not config.use_muon) else 1.0
+        self.aux_loss = 0.0
+        self.router_z_mean = None
+        self.tokens_per_expert = None
+        self.token_indices = None
+        self.collect_stats = False
+        self._rope = None
+
+    @torch.no_grad()
+    def reset_parameters(self) -> None:
+        if self.config.use_muon:
+            torch_default_init(self.router.lc_proj.weight)
+        else:
+            nn.init.normal_(self.router.lc_proj.weight, std=0.02)
+        for mod in (self.mods_in, self.mods_out):
+            for e in range(mod.n):
+                torch_default_init(getattr(mod, f"weight{e}"))
+
+    def _rope_cache(self, T: int, device):
+        cfg = self.config
+        if self._rope is None or self._rope[0].shape[0] < T or self._rope[0].device != device:
+            initial_window = cfg.local_window if cfg.local_window > 0 else cfg.block_size
+            self._rope = ops.build_rope_cache(max(T, cfg.block_size), int(cfg.rotary_percentage * self.head_size),
+                                              torch.bfloat16, device, base=0.09 * initial_window ** 1.628,
+                                              scaling_factor=cfg.scaling_factor)
+        return self._rope
+
+    @staticmethod
+    def _grouped_linear(x: torch.Tensor, mod: "_PerExpertLinear", bounds) -> torch.Tensor:
+        outs = []
+        for e in range(mod.n):
+            s, t = bounds[e], bounds[e + 1]
+            w = getattr(mod, f"weight{e}")
+            outs.append(ops.linear(x[s:t], w.to(x.dtype)) if t > s else x.new_zeros(0, w.shape[0]))
+        return torch.cat(outs)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        B, T, C = x.shape
+        h = x.reshape(-1, C)
+        E, K, hs = self.n_mods, self.top_k, self.head_size
+        logits = self.router.lc_proj(h).float() * self.logit_scale
+        scores, indices = ops.router_topk_softmax(logits, K, self.config.sqrt_gate)
+        flat = indices.reshape(-1).long()
+        order = torch.argsort(flat, stable=True)                 # pairs sorted by expert, token order kept inside an expert
+        tok = order // K
+        counts = torch.bincount(flat, minlength=E)
+        bounds = [0] + torch.cumsum(counts, 0).tolist()
+        # one packed document per (expert, sequence): consecutive pairs with the same key
+        key = flat[order] * B + tok // T
+        _, seg_len = torch.unique_consecutive(key, return_counts=True)
+        cu = F.pad(torch.cumsum(seg_len, 0), (1, 0)).to(torch.int32)
+        qkv = self._grouped_linear(h[tok], self.mods_in, bounds)
+        gate_dim = self.n_head * hs if self.config.gated_attn else 0
+        if gate_dim:
+            qkv, attn_gate = qkv.split((qkv.shape[-1] - gate_dim, gate_dim), dim=-1)
+        G, qpk = self.n_query_groups, self.n_head // self.n_query_groups
+        qkv = qkv.reshape(-1, G, qpk + 2, hs)
+        q, k, v = qkv.split((qpk, 1, 1), dim=-2)
+        q = q.reshape(1, -1, G * qpk, hs)
+        k = k.reshape(1, -1, G, hs)
+        v = v.reshape(1, -1, G, hs)
+        if not self.config.nope:
+            cos, sin = self._rope_cache(T, x.device)
+            pos = (tok % T).unsqueeze(0)
+            q = ops.apply_rotary_emb(q, cos, sin, False, positions=pos)
+            k = ops.apply_rotary_emb(k, cos, sin, False, positions=pos)
+        y = ops.attention(q.contiguous(), k.contiguous(), v.contiguous(), scale=self.scale, window=self.win_tuple, cu_seqlens=cu)
+        y = y.reshape(-1, self.mod_out_size)
+        if gate_dim:
+            y = ops.glu(attn_gate.contiguous(), y)
+        out_rows = self._grouped_linear(y, self.mods_out, bounds)
+        gate = scores.reshape(-1)[order].unsqueeze(-1)
+        out = torch.zeros(B * T, C, dtype=torch.float32, device=x.device)
+        out.index_add_(0, tok, out_rows.float() * gate.float())
+        with torch.no_grad():
+            tpe = counts.to(torch.float32)
+            if self.collect_stats:
+                self.router_z_mean = (torch.logsumexp(logits, dim=-1) ** 2).mean()
+            if self.global_aux and torch.distributed.is_available() and torch.distributed.is_initialized():
+                torch.distributed.all_reduce(tpe)
+            self.tokens_per_expert = tpe
+            self.token_indices = indices
+        if self.aux_gamma > 0:
+            t_aux = tpe if self.aux_style != "switch_seq" else ops.moe.compute_tokens_per_expert_seq(indices, E, T)
+            self.aux_loss = ops.load_balance_loss(F.softmax(logits, dim=-1, dtype=torch.float32), t_aux, gamma=self.aux_gamma,
+                                                  global_stats=self.global_aux, style=self.aux_style, seq_len=T)
+        else:
+            self.aux_loss = 0.0
+        return out.to(x.dtype).view(B, T, C)
+
+
 def get_moe(config: Config, is_attn: bool = False, is_mlp: bool = True):
+    if is_attn:
+        return AttentionExperts(config)
     return SonicMoE(config, is_attn, is_mlp) if config.use_sonicmoe else MoE(config, is_attn, is_mlp)

@@ -1,7 +1,7 @@
 """Hot-path operators.  Each op has a PyTorch oracle (``*_ref``) and an sm_100a kernel."""
 from . import backend  # noqa: F401
 from .activations import glu, swiglu, swiglu_packed, oss_swiglu_ref  # noqa: F401
-from .attention import attention, attention_ref  # noqa: F401
+from .attention import attention, attention_ref, pointwise_attention  # noqa: F401
 from .conv1d import causal_conv1d, causal_conv1d_ref  # noqa: F401
 from .cross_entropy import (FusedCrossEntropyLoss, FusedLinearCrossEntropyLoss, cross_entropy, cross_entropy_ref,  # noqa: F401
                             fused_linear_cross_entropy, fused_linear_cross_entropy_ref)

@@ -58,6 +58,41 @@ def attention_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Opti
     return (o, lse) if return_lse else o
 
 
+def pointwise_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kind: str, scale: Optional[float] = None,
+                        window: Tuple[int, int] = (-1, -1), cu_seqlens: Optional[torch.Tensor] = None,
+                        sigmoid_bias: float = 0.0, q_chunk: int = 1024) -> torch.Tensor:
+    """The two attention variants of the reference that are not softmax-weighted sums, as query-chunked PyTorch math
+    (memory O(q_chunk · Tk) per head; both are small-scale options of the reference, not hot paths):
+
+    * ``kind="sigmoid"`` — ``Σ_j sigmoid(scale·q_i·k_j + bias)·v_j`` over the causal (windowed, per-document) keys: what
+      ``flash_sigmoid.flash_attn_func(..., sigmoid_bias=0)`` computes at `lit_gpt/attention.py:353-356`;
+    * ``kind="sqrt_softmax"`` — ``sqrt(softmax(scale·q kᵀ + causal mask) + 1e-5) @ silu(v)``, the non-``fa2`` path at
+      `lit_gpt/attention.py:426-441`.
+    q:(B,Tq,H,D) k,v:(B,Tk,G,D) → (B,Tq,H,D)."""
+    B, Tq, H, D = q.shape
+    Tk, G = k.shape[1], k.shape[2]
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(H // G, dim=1)     # B H Tk D
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(H // G, dim=1)
+    if kind == "sqrt_softmax":
+        vf = torch.nn.functional.silu(vf)
+    mask = _build_mask(Tq, Tk, q.device, window, cu_seqlens)                 # Tq × Tk, True = visible
+    outs = []
+    for s0 in range(0, Tq, q_chunk):
+        qf = q[:, s0:s0 + q_chunk].float().permute(0, 2, 1, 3)              # B H c D
+        logits = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+        m = mask[s0:s0 + q_chunk]
+        if kind == "sigmoid":
+            w = torch.sigmoid(logits + sigmoid_bias).masked_fill(~m, 0.0)
+        elif kind == "sqrt_softmax":
+            # as in the reference, the 1e-5 sits inside the root for every key, masked ones included (weight 0.0032 each)
+            w = torch.sqrt(torch.softmax(logits.masked_fill(~m, float("-inf")), dim=-1) + 1e-5)
+        else:
+            raise ValueError(kind)
+        outs.append(torch.matmul(w, vf))
+    return torch.cat(outs, dim=2).permute(0, 2, 1, 3).to(q.dtype)
+
+
 def row_start_from_cu_seqlens(cu_seqlens: torch.Tensor, total: int) -> torch.Tensor:
     """int32 (total,) first token of the document each position belongs to (device op, no host sync)."""
     pos = torch.arange(total, device=cu_seqlens.device)
