@@ -287,6 +287,7 @@ def main() -> None:
     ap.add_argument("which", nargs="*", default=list(ALL))
     ap.add_argument("--json", default=None)
     a = ap.parse_args()
+    torch.set_float32_matmul_precision("high")          # as the trainer sets it: fp32 matmuls of the chunked scans on TF32
     res: list = []
     for w in a.which:
         ALL[w](res)

@@ -200,6 +200,12 @@ int b200_gemm2_swiglu_bf16(const void* A, const void* B, void* h, void* act, int
                            int* status, cudaStream_t stream);
 int b200_grouped_gemm2_swiglu_bf16(const void* A, const void* B, void* h, void* act, const int* offsets, int E, int capacity,
                                    int I, int K, int num_sms, int* status, cudaStream_t stream);
+// Row-wise "prepare" stage of the chunked gated delta rule and its backward (gdn_prepare.cu)
+int b200_gdn_prepare_fwd(const void* q, const void* k, const void* v, const float* gc, void* qn, void* kn, void* vc, void* kd,
+                         void* qg, int B, int T, int Tp, int H, int Dk, int Dv, float scale, float eps, cudaStream_t st);
+int b200_gdn_prepare_bwd(const void* q, const void* k, const float* gc, const void* dqn, const void* dkn, const void* dvc,
+                         const void* dkd, const void* dqg, void* dq, void* dk, void* dv, float* a_row, float* s_row, int B, int T,
+                         int Tp, int H, int Dk, int Dv, float scale, float eps, cudaStream_t st);
 // (I + A)^-1 for [n_mat, 64, 64] strictly lower-triangular fp32 matrices (tri_inverse.cu)
 int b200_tri_inverse64(const float* A, float* T, int n_mat, cudaStream_t st);
 // One pass of the chunked gated-delta-rule recurrence (gdn_chunk.cu)

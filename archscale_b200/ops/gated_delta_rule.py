@@ -169,6 +169,89 @@ def _chunk_core(w, u, kd, qg, qk, a):
     return _chunk_core_ref(w, u, kd, qg, qk, a)
 
 
+class _PrepareFn(torch.autograd.Function):
+    """(q, k, v token-major bf16; gc chunk-major fp32) → (qn, kn, vc, kd, qg) chunk-major bf16 on ``csrc/gdn_prepare.cu``:
+    l2-normalisation, the softmax scale, the two decay factors and the layout change in one pass each way."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, gc, scale, eps):
+        q, k, v, gc = q.contiguous(), k.contiguous(), v.contiguous(), gc.contiguous()
+        outs = backend.require_extension().gdn_prepare_fwd(q, k, v, gc, scale, eps)
+        backend.count_launch()
+        ctx.save_for_backward(q, k, v, gc)
+        ctx.consts = (scale, eps)
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, dqn, dkn, dvc, dkd, dqg):
+        q, k, v, gc = ctx.saved_tensors
+        scale, eps = ctx.consts
+        z = lambda t, ref_d: (t if t is not None else torch.zeros(gc.shape[0], gc.shape[1], ref_d, dtype=q.dtype, device=q.device)).contiguous()
+        Dk, Dv = q.shape[-1], v.shape[-1]
+        dq, dk, dv, a_row, s_row = backend.require_extension().gdn_prepare_bwd(
+            q, k, v, gc, z(dqn, Dk), z(dkn, Dk), z(dvc, Dv), z(dkd, Dk), z(dqg, Dk), scale, eps)
+        backend.count_launch()
+        # gc enters through qg = qn·exp(gc) and kd = kn·exp(gl − gc), gl = gc at the chunk's last token
+        s_c = s_row.view(gc.shape[0], -1, 64)
+        dgc = (a_row.view_as(s_c) - s_c).clone()
+        dgc[..., -1] += s_c.sum(-1)
+        return dq, dk, dv, dgc.view_as(gc), None, None
+
+
+class _BmmNTf32(torch.autograd.Function):
+    """``a @ bᵀ`` for bf16 operands with an fp32 result (the 64×64 Gram blocks feed a triangular inverse); gradients in bf16."""
+
+    @staticmethod
+    def forward(ctx, a, b):
+        ctx.save_for_backward(a, b)
+        try:
+            return torch.bmm(a.flatten(0, -3), b.flatten(0, -3).transpose(-1, -2), out_dtype=torch.float32).view(*a.shape[:-1], b.shape[-2])
+        except (TypeError, RuntimeError):
+            return a.float() @ b.float().transpose(-1, -2)
+
+    @staticmethod
+    def backward(ctx, g):
+        a, b = ctx.saved_tensors
+        gb = g.to(a.dtype)
+        return gb @ b, gb.transpose(-1, -2) @ a
+
+
+def _prepare_kernel_ok(q, k, v, chunk: int, l2norm: bool) -> bool:
+    Dk, Dv = q.shape[-1], v.shape[-1]
+    return (q.is_cuda and l2norm and chunk == 64 and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16
+            and (Dk, Dv) in ((128, 128), (128, 256), (256, 256), (256, 512)) and backend.has("gdn_prepare_fwd")
+            and backend.has("gdn_state") and backend.use_cuda_kernel("gated_delta_rule", q, k, v))
+
+
+def _chunk_fused_prepare(q, k, v, g, beta, scale: float, eps: float = 1e-6):
+    """The chunked form with the row-wise work on the prepare kernels and bf16 operands for every product; the 64×64
+    pieces (decay matrix, masks, triangular inverse, its column scalings) stay small fp32 PyTorch ops."""
+    B, T, H, Dk = q.shape
+    Dv = v.shape[-1]
+    c = 64
+    Tp = -(-T // c) * c
+    nC = Tp // c
+    g = g.float().permute(0, 2, 1).reshape(B * H, T)
+    beta = beta.float().permute(0, 2, 1).reshape(B * H, T)
+    if Tp != T:
+        g, beta = F.pad(g, (0, Tp - T)), F.pad(beta, (0, Tp - T))
+    gc = torch.cumsum(g.view(B * H, nC, c), dim=-1)                      # inclusive log-decay inside the chunk
+    beta = beta.view(B * H, nC, c)
+    qn, kn, vc, kd, qg = _PrepareFn.apply(q, k, v, gc.view(B * H, Tp), float(scale), eps)
+    r4 = lambda t: t.view(B * H, nC, c, t.shape[-1])
+    qn, kn, vc, kd, qg = r4(qn), r4(kn), r4(vc), r4(kd), r4(qg)
+    dec = torch.exp(gc.unsqueeze(-1) - gc.unsqueeze(-2))                 # [i, j] = exp(gc_i − gc_j)
+    strict = torch.tril(torch.ones(c, c, device=q.device, dtype=torch.bool), -1)
+    incl = torch.tril(torch.ones(c, c, device=q.device, dtype=torch.bool), 0)
+    A = (_BmmNTf32.apply(kn, kn) * dec * beta.unsqueeze(-1)).masked_fill(~strict, 0.0)
+    Tm = unit_lower_inverse(A)
+    u = (Tm * beta.unsqueeze(-2)).to(q.dtype) @ vc                       # (I + A)⁻¹ · diag(β) · v
+    w = (Tm * (beta * torch.exp(gc)).unsqueeze(-2)).to(q.dtype) @ kn     # (I + A)⁻¹ · diag(β·exp(gc)) · k̂
+    qk = (_BmmNTf32.apply(qn, kn) * dec).masked_fill(~incl, 0.0)
+    o = _chunk_core(w, u, kd, qg, qk, torch.exp(gc[..., -1]))            # (B·H, nC, c, Dv)
+    return o.reshape(B, H, Tp, Dv).permute(0, 2, 1, 3)[:, :T].to(v.dtype)
+
+
 def gated_delta_rule_chunk(q, k, v, g, beta, scale: Optional[float] = None, l2norm: bool = True,
                            cu_seqlens: Optional[torch.Tensor] = None, chunk: int = 64):
     """Chunked WY formulation.  Equivalent to the recurrent oracle; differentiable."""
@@ -186,6 +269,8 @@ def gated_delta_rule_chunk(q, k, v, g, beta, scale: Optional[float] = None, l2no
                                                    scale, l2norm, None, chunk))
         return torch.cat(outs, dim=1)
     scale = Dk ** -0.5 if scale is None else scale
+    if _prepare_kernel_ok(q, k, v, chunk, l2norm):
+        return _chunk_fused_prepare(q, k, v, g, beta, scale)
     pad = (-T) % chunk
     if pad:
         q, k, v = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (q, k, v))

@@ -782,6 +782,9 @@ def setup(train_data_dir: str = "data/redpajama_sample", val_data_dir: Optional[
 
     ``fsdp2`` is accepted for compatibility: this engine is always the sharded one.
     ``dp_replicate`` > 1 gives hybrid sharding (replicate across nodes, shard inside)."""
+    # fp32 matmuls (the chunk-parallel products of the SSD scan and the gated delta rule, their backward) on the TF32 tensor
+    # cores, as the reference sets at its entry point (`pretrain.py:1329`); here for every caller of setup()
+    torch.set_float32_matmul_precision("high")
     base_hps = base_hps or BaseHyperparameters()
     for flag, kind in ((ortho_init, "ortho"), (diag_init, "diag"), (maxfan_init, "maxfan")):
         if flag:
