@@ -206,6 +206,11 @@ int b200_gdn_prepare_fwd(const void* q, const void* k, const void* v, const floa
 int b200_gdn_prepare_bwd(const void* q, const void* k, const float* gc, const void* dqn, const void* dkn, const void* dvc,
                          const void* dkd, const void* dqg, void* dq, void* dk, void* dv, float* a_row, float* s_row, int B, int T,
                          int Tp, int H, int Dk, int Dv, float scale, float eps, cudaStream_t st);
+// Intra-chunk part of the SSD scan and its backward (ssd_intra.cu); x_dtype 0 fp32 / 1 bf16
+int b200_ssd_intra_fwd(const void* x, int x_dtype, const float* dt, const float* cs, const float* CB, const int* bc, float* y,
+                       int B, int nC, int H, int G, int P, cudaStream_t st);
+int b200_ssd_intra_bwd(const void* x, int x_dtype, const float* dt, const float* cs, const float* CB, const int* bc, const float* dy,
+                       float* dx, float* ddt, float* dcs, float* dCB, int B, int nC, int H, int G, int P, int hsplit, cudaStream_t st);
 // (I + A)^-1 for [n_mat, 64, 64] strictly lower-triangular fp32 matrices (tri_inverse.cu)
 int b200_tri_inverse64(const float* A, float* T, int n_mat, cudaStream_t st);
 // One pass of the chunked gated-delta-rule recurrence (gdn_chunk.cu)

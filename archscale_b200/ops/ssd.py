@@ -70,6 +70,33 @@ class _StateScanFn(torch.autograd.Function):
         return d_add, d_keep
 
 
+class _IntraChunkFn(torch.autograd.Function):
+    """``y[i] = Σ_{j ≤ i, same document} (C_i·B_j) · exp(cs_i − cs_j) · dt_j · x_j`` inside every chunk, on
+    ``csrc/ssd_intra.cu``: the per-head 64×64 weights never reach memory.  x (B,Lp,H,P), dt (B,Lp,H), cs (B,nC,H,64),
+    cb (B,nC,G,64,64), bc (B,nC,64) int32 or None → y (B,Lp,H,P) fp32."""
+
+    @staticmethod
+    def forward(ctx, x, dt, cs, cb, bc):
+        x, dt, cs, cb = x.contiguous(), dt.contiguous(), cs.contiguous(), cb.contiguous()
+        y = backend.require_extension().ssd_intra_fwd(x, dt, cs, cb, bc)
+        backend.count_launch()
+        ctx.save_for_backward(x, dt, cs, cb, bc)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, dt, cs, cb, bc = ctx.saved_tensors
+        dx, ddt, dcs, dcb = backend.require_extension().ssd_intra_bwd(x, dt, cs, cb, bc, dy.float().contiguous())
+        backend.count_launch()
+        Bb, Lp, H, _ = x.shape
+        return dx.to(x.dtype), ddt.permute(0, 1, 3, 2).reshape(Bb, Lp, H), dcs, dcb, None
+
+
+def _intra_kernel_ok(x: torch.Tensor, c: int) -> bool:
+    return (x.is_cuda and c == 64 and x.shape[-1] % 64 == 0 and x.dtype in (torch.float32, torch.bfloat16)
+            and backend.has("ssd_intra_fwd") and backend.use_cuda_kernel("ssd", x))
+
+
 def chunk_state_scan(add: torch.Tensor, keep: torch.Tensor) -> torch.Tensor:
     if (add.is_cuda and add.dtype == torch.float32 and keep.dtype == torch.float32 and (add.shape[3] * add.shape[4]) % 1024 == 0
             and backend.has("ssd_state_fwd") and backend.use_cuda_kernel("ssd", add)):
@@ -99,7 +126,13 @@ def ssd_scan(x, dt, A, B, C, D=None, seq_idx: Optional[torch.Tensor] = None, chu
             brk = F.pad(brk, (0, pad))
     Lp = L + pad
     nC, c = Lp // chunk, chunk
-    xb = (x * dt.unsqueeze(-1)).view(Bb, nC, c, H, P)
+    xb_cache = []
+
+    def xb():                                          # dt·x in chunk layout, formed only by the paths that read it
+        if not xb_cache:
+            xb_cache.append((x * dt.unsqueeze(-1)).view(Bb, nC, c, H, P))
+        return xb_cache[0]
+
     la = (dt * A.float().view(1, 1, H)).view(Bb, nC, c, H).permute(0, 1, 3, 2)          # (B,nC,H,c) log decay per step
     cs = torch.cumsum(la, dim=-1)                                                        # inclusive, inside the chunk
     tril = torch.tril(torch.ones(c, c, dtype=torch.bool, device=x.device))
@@ -112,26 +145,40 @@ def ssd_scan(x, dt, A, B, C, D=None, seq_idx: Optional[torch.Tensor] = None, chu
         same = tril.view(1, 1, c, c)
         first = last_same = None
     # inside a chunk: y_i = Σ_{j≤i} (C_i·B_j) · exp(cs_i − cs_j) · dt_j x_j
-    dec = cs.unsqueeze(-1) - cs.unsqueeze(-2)                                            # (B,nC,H,c,c)
-    w = torch.exp(dec.masked_fill(~same.unsqueeze(2), float("-inf")))
     Bh = B.view(Bb, nC, c, G, N)
     Ch = C.view(Bb, nC, c, G, N)
     cb = torch.einsum("bnigk,bnjgk->bngij", Ch, Bh)                                      # (B,nC,G,c,c)
     rep = H // G
-    wg = w.view(Bb, nC, G, rep, c, c) * cb.unsqueeze(3)
-    y = torch.einsum("bngrij,bnjgrp->bnigrp", wg, xb.view(Bb, nC, c, G, rep, P)).reshape(Bb, nC, c, H, P)
+    if _intra_kernel_ok(x, c):
+        y = _IntraChunkFn.apply(x, dt, cs, cb, bc.to(torch.int32).contiguous() if brk is not None else None)
+        y = y.view(Bb, nC, c, H, P)
+    else:
+        dec = cs.unsqueeze(-1) - cs.unsqueeze(-2)                                        # (B,nC,H,c,c)
+        w = torch.exp(dec.masked_fill(~same.unsqueeze(2), float("-inf")))
+        wg = w.view(Bb, nC, G, rep, c, c) * cb.unsqueeze(3)
+        y = torch.einsum("bngrij,bnjgrp->bnigrp", wg, xb().view(Bb, nC, c, G, rep, P)).reshape(Bb, nC, c, H, P)
     # chunk summaries: what each chunk adds to the state by its end, and how much of the entering state survives it
     wl = torch.exp(cs[..., -1:] - cs)                                                    # (B,nC,H,c)
     carry = torch.exp(cs)                                                                # decay from the chunk start to step i
     if brk is not None:
         wl = wl * last_same.unsqueeze(2)
         carry = carry * first.unsqueeze(2)
-    add = torch.einsum("bngrj,bnjgrp,bnjgk->bngrpk", wl.view(Bb, nC, G, rep, c), xb.view(Bb, nC, c, G, rep, P), Bh)
-    add = add.reshape(Bb, nC, H, P, N)
     keep = carry[..., -1]                                                                # (B,nC,H)
-    S_in = chunk_state_scan(add, keep)                                                   # state entering each chunk
-    y = y + torch.einsum("bngrpk,bnigk,bngri->bnigrp", S_in.view(Bb, nC, G, rep, P, N), Ch,
-                         carry.view(Bb, nC, G, rep, c)).reshape(Bb, nC, c, H, P)
+    if G == 1:
+        # one group: inside a chunk the token-major layout (c, H·P) is already what a batched matmul over the chunks wants,
+        # so both products run without operand permutes or per-head copies of B / C
+        BN = Bb * nC
+        xw = (x.view(Bb, nC, c, H, P) * (dt.view(Bb, nC, c, H) * wl.permute(0, 1, 3, 2)).unsqueeze(-1)).view(BN, c, H * P)
+        add = torch.bmm(xw.transpose(1, 2), Bh.reshape(BN, c, N)).view(Bb, nC, H, P, N)
+        S_in = chunk_state_scan(add, keep)                                               # state entering each chunk
+        y2 = torch.bmm(Ch.reshape(BN, c, N), S_in.view(BN, H * P, N).transpose(1, 2)).view(Bb, nC, c, H, P)
+        y = torch.addcmul(y, y2, carry.permute(0, 1, 3, 2).unsqueeze(-1))
+    else:
+        add = torch.einsum("bngrj,bnjgrp,bnjgk->bngrpk", wl.view(Bb, nC, G, rep, c), xb().view(Bb, nC, c, G, rep, P), Bh)
+        add = add.reshape(Bb, nC, H, P, N)
+        S_in = chunk_state_scan(add, keep)                                               # state entering each chunk
+        y = y + torch.einsum("bngrpk,bnigk,bngri->bnigrp", S_in.view(Bb, nC, G, rep, P, N), Ch,
+                             carry.view(Bb, nC, G, rep, c)).reshape(Bb, nC, c, H, P)
     y = y.reshape(Bb, Lp, H, P)[:, :L]
     if D is not None:
         y = y + x[:, :L] * D.float().view(1, 1, H, 1)

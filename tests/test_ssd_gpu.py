@@ -42,3 +42,28 @@ def test_ssd_scan_gpu_matches_recurrence():
     g = torch.randn_like(y)
     for a, b in zip(torch.autograd.grad(y_ref, ins, g), torch.autograd.grad(y, ins, g)):
         assert float((a - b).abs().max()) <= 3e-3 * float(a.abs().max()) + 1e-4
+
+
+@pytest.mark.parametrize("Bb,L,H,P,G,N,packed", [(2, 200, 4, 128, 2, 16, True), (1, 130, 6, 64, 3, 32, False)])
+def test_ssd_scan_gpu_groups_wide_heads_and_documents(Bb, L, H, P, G, N, packed):
+    """The intra-chunk kernel with several groups, 128-wide heads, a ragged last chunk and document breaks inside chunks."""
+    torch.manual_seed(3)
+    x = torch.randn(Bb, L, H, P, device="cuda", requires_grad=True)
+    dt = (torch.rand(Bb, L, H, device="cuda") * 0.5).requires_grad_()
+    A = (-torch.rand(H, device="cuda") - 0.1).requires_grad_()
+    B = torch.randn(Bb, L, G, N, device="cuda", requires_grad=True)
+    C = torch.randn(Bb, L, G, N, device="cuda", requires_grad=True)
+    seq_idx = None
+    if packed:
+        seq_idx = torch.zeros(Bb, L, dtype=torch.int32, device="cuda")
+        for i, cut in enumerate((40, 41, 150)):
+            seq_idx[:, cut:] = i + 1
+    ins = (x, dt, A, B, C)
+    n0 = ssd.backend.launches()
+    y = ssd.ssd_scan(x, dt, A, B, C, None, seq_idx)
+    assert ssd.backend.launches() >= n0 + 2                  # intra-chunk kernel + state scan kernel
+    y_ref = ssd.ssd_scan_ref(x, dt, A, B, C, None, seq_idx)
+    assert torch.allclose(y, y_ref, atol=3e-3, rtol=3e-3)
+    g = torch.randn_like(y)
+    for name, a, b in zip("x dt A B C".split(), torch.autograd.grad(y_ref, ins, g), torch.autograd.grad(y, ins, g)):
+        assert float((a - b).abs().max()) <= 4e-3 * float(a.abs().max()) + 1e-4, name
