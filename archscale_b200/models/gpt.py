@@ -501,7 +501,7 @@ class GPT(nn.Module):
         blocks = list(self.transformer.h)
         from archscale_b200.models.norms import FusedRMSNorm
         use_deferred = (self.compute_dtype == torch.bfloat16 and self.layer_configurator is None
-                        and type(self.transformer.ln_f) is FusedRMSNorm and cfg.n_embd in ops.norm._FUSED_COLS
+                        and type(self.transformer.ln_f) is FusedRMSNorm and ops.norm.fused_cols_ok(cfg.n_embd)
                         and all(b._deferred_ok(x, None, residual_dropout) for b in blocks))
 
         def run(block):

@@ -167,7 +167,10 @@ __global__ void __launch_bounds__(256) add_rmsnorm_fwd_kernel(const TRES* __rest
   }
 }
 
-template <typename TX, typename TW, int NCH>
+// cols ≤ NCH·256, a multiple of 8: a lane owns the 8-element vectors at columns lane·8 + i·256 (i < NCH) that lie inside the
+// row; widths that are not a multiple of 256 (1984, 1536, …) leave the last chunk partly or wholly empty.
+// FULL: cols == NCH·256, no bounds checks (they cost the common widths ≈ 40 % when left in).
+template <typename TX, typename TW, int NCH, bool FULL>
 __global__ void __launch_bounds__(256) add_rmsnorm_bwd_kernel(const float* __restrict__ g_res, const __nv_bfloat16* __restrict__ g_n,
                                                               const TX* __restrict__ x, const TW* __restrict__ w,
                                                               const float* __restrict__ rstd, float* __restrict__ d_res,
@@ -184,7 +187,13 @@ __global__ void __launch_bounds__(256) add_rmsnorm_bwd_kernel(const float* __res
     for (int e = 0; e < 8; ++e) dwacc[i][e] = 0.f;
   float wreg[NCH][8];
 #pragma unroll
-  for (int i = 0; i < NCH; ++i) Vec8<TW>::load(w + lane * 8 + i * 256, wreg[i]);
+  for (int i = 0; i < NCH; ++i) {
+    if (FULL || lane * 8 + i * 256 < cols) Vec8<TW>::load(w + lane * 8 + i * 256, wreg[i]);
+    else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) wreg[i][e] = 0.f;
+    }
+  }
   for (int row = blockIdx.x * 8 + warp; row < rows; row += gridDim.x * 8) {
     const size_t base = static_cast<size_t>(row) * cols;
     const float rs = rstd[row];
@@ -192,15 +201,18 @@ __global__ void __launch_bounds__(256) add_rmsnorm_bwd_kernel(const float* __res
 #pragma unroll
     for (int i = 0; i < NCH; ++i) {
       const int c = lane * 8 + i * 256;
-      float xv[8], dv[8]; Vec8<TX>::load(x + base + c, xv); Vec8<__nv_bfloat16>::load(g_n + base + c, dv);
+      if (FULL || c < cols) {
+        float xv[8], dv[8]; Vec8<TX>::load(x + base + c, xv); Vec8<__nv_bfloat16>::load(g_n + base + c, dv);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) dot += dv[e] * wreg[i][e] * xv[e];
+        for (int e = 0; e < 8; ++e) dot += dv[e] * wreg[i][e] * xv[e];
+      }
     }
     dot = warp_sum(dot);
     const float c1 = dot * rs * rs * rs / cols;
 #pragma unroll
     for (int i = 0; i < NCH; ++i) {
       const int c = lane * 8 + i * 256;
+      if (!FULL && c >= cols) continue;
       float xv[8], dv[8], o[8]; Vec8<TX>::load(x + base + c, xv); Vec8<__nv_bfloat16>::load(g_n + base + c, dv);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
@@ -222,8 +234,10 @@ __global__ void __launch_bounds__(256) add_rmsnorm_bwd_kernel(const float* __res
   }
 #pragma unroll
   for (int i = 0; i < NCH; ++i)
+    if (FULL || lane * 8 + i * 256 < cols) {
 #pragma unroll
-    for (int e = 0; e < 8; ++e) atomicAdd(&dw_s[lane * 8 + i * 256 + e], dwacc[i][e]);
+      for (int e = 0; e < 8; ++e) atomicAdd(&dw_s[lane * 8 + i * 256 + e], dwacc[i][e]);
+    }
   __syncthreads();
   for (int c = threadIdx.x; c < cols; c += blockDim.x) dw_partial[static_cast<size_t>(blockIdx.x) * cols + c] = dw_s[c];
 }
@@ -275,7 +289,7 @@ extern "C" int b200_rmsnorm_bwd(const void* dy, int dy_dtype, const void* x, int
   // bf16 upstream gradient, a weight and one of the model widths: the kernel of the fused residual-add variant (weight
   // gradient accumulated in registers, one shared-memory add per column and CTA instead of one per element) does this job
   // with no residual gradient: dx is its bf16 output for bf16 x, its fp32 output for fp32 x
-  if (dy_dtype == 1 && w && (cols == 1024 || cols == 2048 || cols == 2560 || cols == 3072 || cols == 4096))
+  if (dy_dtype == 1 && w && cols >= 512 && cols <= 4096)
     return b200_add_rmsnorm_bwd(nullptr, dy, x, x_dtype, w, w_dtype, rstd, x_dtype == 0 ? static_cast<float*>(dx) : nullptr,
                                 x_dtype == 1 ? dx : nullptr, 1.f, dw_partial, dw, rows, cols, stream);
   const int grid = b200_rmsnorm_bwd_partials(rows, cols);
@@ -328,22 +342,28 @@ extern "C" int b200_add_rmsnorm_bwd(const float* g_res, const void* g_n, const v
   const size_t smem = sizeof(float) * cols;
   typedef __nv_bfloat16 bf;
 #define L(TX, TW, NCH)                                                                                                 \
-  add_rmsnorm_bwd_kernel<TX, TW, NCH><<<grid, 256, smem, stream>>>(g_res, static_cast<const bf*>(g_n), static_cast<const TX*>(x), \
-                                                                   static_cast<const TW*>(w), rstd, d_res, static_cast<bf*>(d_h), \
-                                                                   h_scale, dw_partial, rows, cols)
+  do {                                                                                                                 \
+    if (cols == NCH * 256)                                                                                             \
+      add_rmsnorm_bwd_kernel<TX, TW, NCH, true><<<grid, 256, smem, stream>>>(g_res, static_cast<const bf*>(g_n), static_cast<const TX*>(x), \
+                                                                         static_cast<const TW*>(w), rstd, d_res, static_cast<bf*>(d_h), \
+                                                                         h_scale, dw_partial, rows, cols);             \
+    else                                                                                                               \
+      add_rmsnorm_bwd_kernel<TX, TW, NCH, false><<<grid, 256, smem, stream>>>(g_res, static_cast<const bf*>(g_n), static_cast<const TX*>(x), \
+                                                                          static_cast<const TW*>(w), rstd, d_res, static_cast<bf*>(d_h), \
+                                                                          h_scale, dw_partial, rows, cols);            \
+  } while (0)
 #define LN(NCH)                                                  \
   if (x_dtype == 0 && w_dtype == 0) L(float, float, NCH);        \
   else if (x_dtype == 0 && w_dtype == 1) L(float, bf, NCH);      \
   else if (x_dtype == 1 && w_dtype == 0) L(bf, float, NCH);      \
   else L(bf, bf, NCH);
-  switch (cols) {
-    case 1024: LN(4) break;
-    case 2048: LN(8) break;
-    case 2560: LN(10) break;
-    case 3072: LN(12) break;
-    case 4096: LN(16) break;
-    default: return -2;
-  }
+  // the instantiation with the fewest 256-column chunks that covers the row (the kernel skips what lies beyond `cols`)
+  if (cols % 8 || cols > 4096) return -2;
+  if (cols <= 1024) { LN(4) }
+  else if (cols <= 2048) { LN(8) }
+  else if (cols <= 2560) { LN(10) }
+  else if (cols <= 3072) { LN(12) }
+  else { LN(16) }
 #undef LN
 #undef L
   reduce_partials_kernel<<<(cols + 31) / 32, 1024, 0, stream>>>(dw_partial, dw, grid, cols);

@@ -214,7 +214,10 @@ class _AddRMSNormFn(torch.autograd.Function):
         return d_res.view(ctx.shape), (d_h.view(ctx.shape) if ctx.has_h else None), dw.to(weight.dtype), None, None
 
 
-_FUSED_COLS = (1024, 2048, 2560, 3072, 4096)
+def fused_cols_ok(cols: int) -> bool:
+    """Row widths the fused residual-add + RMSNorm kernels take (register-resident weight-gradient accumulators)."""
+    return cols % 8 == 0 and 512 <= cols <= 4096
+
 
 
 def add_rms_norm(res: torch.Tensor, h: Optional[torch.Tensor], weight: torch.Tensor, eps: float = 1e-5,
@@ -223,7 +226,7 @@ def add_rms_norm(res: torch.Tensor, h: Optional[torch.Tensor], weight: torch.Ten
 
     One kernel forward; backward fuses the residual-gradient add, the RMSNorm backward and the bf16
     cast of the branch gradient."""
-    if (res.shape[-1] in _FUSED_COLS and out_dtype == torch.bfloat16 and res.dtype in (torch.float32, torch.bfloat16)
+    if (fused_cols_ok(res.shape[-1]) and out_dtype == torch.bfloat16 and res.dtype in (torch.float32, torch.bfloat16)
             and (h is None or h.dtype == torch.bfloat16) and backend.has("add_rmsnorm_fwd")
             and backend.use_cuda_kernel("add_rmsnorm", res, h, weight)):
         return _AddRMSNormFn.apply(res.contiguous(), None if h is None else h.contiguous(), weight, eps, h_scale)
