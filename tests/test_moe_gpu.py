@@ -88,3 +88,28 @@ def test_grouped_gemm_with_swiglu_epilogue_equals_unfused():
     assert torch.equal(h[:rows], h_ref[:rows])
     assert torch.equal(a[:rows], a_ref[:rows])
     assert ext.device_status() == 0
+
+
+def test_attention_experts_gpu_matches_cpu(monkeypatch):
+    """The mixture of attention experts on the GPU (bf16, variable-length attention kernel, GEMM kernels) against the
+    same module in fp32 on the CPU, with the routing decision fixed (a token that flips experts under bf16 logits changes
+    the attention context of every token behind it in both experts, which is not what this test is about)."""
+    from archscale_b200.config import Config
+    from archscale_b200.models import moe as moe_mod
+    torch.manual_seed(4)
+    cfg = Config(n_layer=2, n_embd=512, n_head=8, n_query_groups=4, head_dim=128, block_size=256, vocab_size=128,
+                 padded_vocab_size=128, intermediate_size=1024, sparsity=2, top_k=2, sqrt_gate=True, aux_gamma=0.0)
+    m = moe_mod.get_moe(cfg, is_attn=True)
+    m.reset_parameters()
+    x = torch.randn(2, 256, 512) * 0.5
+    with torch.no_grad():
+        scores, idx = router_topk_softmax_ref(m.router.lc_proj(x.reshape(-1, 512)).float(), 2, sqrt_gate=True)
+    monkeypatch.setattr(moe_mod.ops, "router_topk_softmax", lambda logits, k, sq: (scores.to(logits.device), idx.to(logits.device)))
+    ref = m(x)
+    mg = moe_mod.get_moe(cfg, is_attn=True).cuda().bfloat16()
+    mg.load_state_dict(m.state_dict())
+    xg = x.cuda().bfloat16().requires_grad_()
+    out = mg(xg)
+    assert _rel(out.float().cpu(), ref) < 3e-2
+    out.float().pow(2).mean().backward()
+    assert xg.grad is not None and torch.isfinite(xg.grad).all()
