@@ -104,3 +104,25 @@ def test_attention_experts_match_per_segment_oracle():
     assert torch.allclose(out.reshape(-1, C), ref, atol=2e-4, rtol=1e-3)
     out.sum().backward()
     assert all(p.grad is not None for p in m.parameters())
+
+
+def test_differential_attention_one_call_equals_four_calls():
+    """The four softmax products of differential attention run as one call over stacked heads; the result must be the
+    four-call statement of the reference (`lit_gpt/diff_attn.py:161-175`)."""
+    from archscale_b200.models.attention import DiffAttention
+    from archscale_b200.ops.diff_attn import diff_combine_ref
+    torch.manual_seed(5)
+    B, T, H, G, D = 2, 24, 8, 4, 16
+    da = DiffAttention(D, depth=3, softmax_scale=0.25, window_size=(7, 0))
+    da.reset_parameters()
+    q, k, v = torch.randn(B, T, H, D), torch.randn(B, T, G, D), torch.randn(B, T, G, D)
+    out = da(q, k, v)
+    q1, q2 = q.view(B, T, H // 2, 2, D).unbind(3)
+    k1, k2 = k.view(B, T, G // 2, 2, D).unbind(3)
+    v1, v2 = v.view(B, T, G // 2, 2, D).unbind(3)
+    kw = dict(scale=0.25, window=(7, 0))
+    a1 = torch.cat((attention_ref(q1, k1, v1, **kw), attention_ref(q1, k1, v2, **kw)), dim=-1)
+    a2 = torch.cat((attention_ref(q2, k2, v1, **kw), attention_ref(q2, k2, v2, **kw)), dim=-1)
+    lam = (torch.exp((da.lambda_q1 * da.lambda_k1).sum()) - torch.exp((da.lambda_q2 * da.lambda_k2).sum()) + da.lambda_init)
+    ref = diff_combine_ref(a1, a2, lam, da.subln.weight, 1 - da.lambda_init, 1e-5).reshape(B, T, H, D)
+    assert torch.allclose(out, ref, atol=1e-5, rtol=1e-5)
