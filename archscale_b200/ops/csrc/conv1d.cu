@@ -103,6 +103,13 @@ __global__ void __launch_bounds__(128) conv1d_fwd_kernel(const T* __restrict__ x
 }
 
 // g[t] = dy[t]·act'(pre[t]);  dx[t'] = Σ_j w[j]·g[t'+(W-1)-j] (same-document taps only)
+// A thread owns 8 channels and CV_TSTEP_BWD consecutive positions and walks the output steps once with two rolling
+// windows (the last W inputs, the last W values of g): one load of x and dy, one activation derivative per step.  dx of a
+// position is complete W−1 steps later, so the walk runs W−1 steps past the block's end (reading, not owning, those
+// steps).  Weight / bias gradients belong to the block that owns the output step; they leave through atomics once per
+// thread (W·8 + 8 of them per 128 positions).
+constexpr int CV_TSTEP_BWD = 128;
+
 template <typename T, int W>
 __global__ void __launch_bounds__(128) conv1d_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ w,
                                                          const float* __restrict__ bias, const int* __restrict__ seq_idx,
@@ -111,7 +118,7 @@ __global__ void __launch_bounds__(128) conv1d_bwd_kernel(const T* __restrict__ d
   const int cv = blockIdx.x * blockDim.x + threadIdx.x;
   const int c0 = cv * 8;
   if (c0 >= C) return;
-  const int t0 = blockIdx.y * CV_TSTEP, b = blockIdx.z;
+  const int t0 = blockIdx.y * CV_TSTEP_BWD, b = blockIdx.z;
   float wk[W][8], bs[8], dwa[W][8], dba[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
@@ -121,85 +128,80 @@ __global__ void __launch_bounds__(128) conv1d_bwd_kernel(const T* __restrict__ d
   }
   const size_t base = static_cast<size_t>(b) * L * C + c0;
   const int* sb = seq_idx ? seq_idx + static_cast<size_t>(b) * L : nullptr;
-  auto ldx = [&](int tt, float (&v)[8]) {
-    if (tt >= 0 && tt < L) V8<T>::ld(x + (static_cast<size_t>(b) * L + tt) * xs + c0, v);
+  const int t_end = min(t0 + CV_TSTEP_BWD, L);
+  // windows: slot k holds step t − (W−1) + k, slot W−1 the current step
+  float xw[W][8], gw[W][8];
+  int sw[W];                                            // document ids of the window's steps (−1: before the sequence)
+#pragma unroll
+  for (int k = 0; k < W; ++k) {
+    const int tt = t0 - W + k;                          // the window "before" step t0 (shifted in at the loop top)
+    sw[k] = (tt >= 0) ? (sb ? sb[tt] : 0) : -1;
+    if (tt >= 0) V8<T>::ld(x + (static_cast<size_t>(b) * L + tt) * xs + c0, xw[k]);
     else {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) v[e] = 0.f;
+      for (int e = 0; e < 8; ++e) xw[k][e] = 0.f;
     }
-  };
-  // g for output steps t0 .. t0+TSTEP+W-2 (the dx of this block needs W-1 steps beyond it)
-  const int t_end = min(t0 + CV_TSTEP, L);
-  for (int tp = t0; tp < t_end; ++tp) {           // tp: input position whose dx we produce
-    float dxa[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) dxa[e] = 0.f;
-    const int sid_tp = sb ? sb[tp] : 0;
+    for (int e = 0; e < 8; ++e) gw[k][e] = 0.f;
+  }
+  for (int t = t0; t < t_end + W - 1; ++t) {
+    // shift the windows by one step
 #pragma unroll
-    for (int j = 0; j < W; ++j) {
-      const int t = tp + (W - 1) - j;             // output step that used x[tp] with tap j
-      if (t >= L) continue;
-      if (sb && sb[t] != sid_tp) continue;
-      // recompute pre[t]
-      float pre[8];
+    for (int k = 0; k < W - 1; ++k) {
+      sw[k] = sw[k + 1];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { xw[k][e] = xw[k + 1][e]; gw[k][e] = gw[k + 1][e]; }
+    }
+    if (t < L) {
+      sw[W - 1] = sb ? sb[t] : 0;
+      V8<T>::ld(x + (static_cast<size_t>(b) * L + t) * xs + c0, xw[W - 1]);
+      float pre[8], g[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) pre[e] = bs[e];
-      const int sid_t = sb ? sb[t] : 0;
 #pragma unroll
-      for (int jj = 0; jj < W; ++jj) {
-        const int tt = t - (W - 1) + jj;
-        if (tt < 0 || (sb && sb[tt] != sid_t)) continue;
-        float xv[8]; ldx(tt, xv);
+      for (int k = 0; k < W; ++k) {
+        if (sw[k] == sw[W - 1]) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) pre[e] += wk[jj][e] * xv[e];
-      }
-      float g[8]; V8<T>::ld(dy + (static_cast<size_t>(b) * L + t) * dys + c0, g);
-      if (silu) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) g[e] *= dsilu_f(pre[e]);
-      }
-#pragma unroll
-      for (int e = 0; e < 8; ++e) dxa[e] += wk[j][e] * g[e];
-      // weight / bias gradients are owned by the block that owns output step t
-      if (t >= t0 && t < t_end) {
-        float xv[8]; ldx(tp, xv);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) dwa[j][e] += g[e] * xv[e];
-        if (j == W - 1) {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) dba[e] += g[e];
+          for (int e = 0; e < 8; ++e) pre[e] += wk[k][e] * xw[k][e];
         }
       }
-    }
-    V8<T>::st(dx + base + static_cast<size_t>(tp) * C, dxa);
-  }
-  // taps whose input position lies before this block (tp < t0) but whose output step is inside it
-#pragma unroll
-  for (int j = 0; j < W - 1; ++j) {
-    for (int t = t0; t < min(t0 + (W - 1) - j, t_end); ++t) {
-      const int tp = t - (W - 1) + j;
-      if (tp < 0 || tp >= t0) continue;
-      if (sb && sb[t] != sb[tp]) continue;
-      float pre[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) pre[e] = bs[e];
-      const int sid_t = sb ? sb[t] : 0;
-#pragma unroll
-      for (int jj = 0; jj < W; ++jj) {
-        const int tt = t - (W - 1) + jj;
-        if (tt < 0 || (sb && sb[tt] != sid_t)) continue;
-        float xv[8]; ldx(tt, xv);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) pre[e] += wk[jj][e] * xv[e];
-      }
-      float g[8]; V8<T>::ld(dy + (static_cast<size_t>(b) * L + t) * dys + c0, g);
+      V8<T>::ld(dy + (static_cast<size_t>(b) * L + t) * dys + c0, g);
       if (silu) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) g[e] *= dsilu_f(pre[e]);
       }
-      float xv[8]; ldx(tp, xv);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) dwa[j][e] += g[e] * xv[e];
+      for (int e = 0; e < 8; ++e) gw[W - 1][e] = g[e];
+      if (t < t_end) {                                  // this block owns output step t: its weight / bias gradients
+#pragma unroll
+        for (int k = 0; k < W; ++k) {
+          if (sw[k] == sw[W - 1]) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) dwa[k][e] += g[e] * xw[k][e];
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dba[e] += g[e];
+      }
+    } else {
+      sw[W - 1] = -2;                                   // past the end: matches no document
+#pragma unroll
+      for (int e = 0; e < 8; ++e) gw[W - 1][e] = 0.f;
+    }
+    // position tp = t − (W−1) has now seen every output step that read it: slot k of the windows is step tp + k, tap W−1−k
+    const int tp = t - (W - 1);
+    if (tp >= t0 && tp < t_end) {
+      float dxa[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dxa[e] = 0.f;
+#pragma unroll
+      for (int k = 0; k < W; ++k) {
+        if (sw[k] == sw[0]) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) dxa[e] += wk[W - 1 - k][e] * gw[k][e];
+        }
+      }
+      V8<T>::st(dx + base + static_cast<size_t>(tp) * C, dxa);
     }
   }
 #pragma unroll
@@ -229,7 +231,7 @@ static int conv_fwd_t(const void* x, const float* w, const float* bias, const in
 template <typename T>
 static int conv_bwd_t(const void* dy, const void* x, const float* w, const float* bias, const int* seq_idx, void* dx, float* dw,
                       float* db, int B, int L, int C, int W, int silu, int xs, int dys, cudaStream_t st) {
-  dim3 grid((C / 8 + 127) / 128, (L + CV_TSTEP - 1) / CV_TSTEP, B);
+  dim3 grid((C / 8 + 127) / 128, (L + CV_TSTEP_BWD - 1) / CV_TSTEP_BWD, B);
   switch (W) {
     case 2: conv1d_bwd_kernel<T, 2><<<grid, 128, 0, st>>>((const T*)dy, (const T*)x, w, bias, seq_idx, (T*)dx, dw, db, B, L, C, silu, xs, dys); break;
     case 3: conv1d_bwd_kernel<T, 3><<<grid, 128, 0, st>>>((const T*)dy, (const T*)x, w, bias, seq_idx, (T*)dx, dw, db, B, L, C, silu, xs, dys); break;
