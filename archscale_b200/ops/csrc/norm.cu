@@ -194,6 +194,8 @@ __global__ void __launch_bounds__(256) add_rmsnorm_bwd_kernel(const float* __res
       for (int e = 0; e < 8; ++e) wreg[i][e] = 0.f;
     }
   }
+  // Partial rows: a chunk that lies beyond the row loads from the row's last vector instead (always in bounds, no branch
+  // around the loads, so the compiler still issues all of a row's loads together) and its gradient vector is zeroed.
   for (int row = blockIdx.x * 8 + warp; row < rows; row += gridDim.x * 8) {
     const size_t base = static_cast<size_t>(row) * cols;
     const float rs = rstd[row];
@@ -201,34 +203,37 @@ __global__ void __launch_bounds__(256) add_rmsnorm_bwd_kernel(const float* __res
 #pragma unroll
     for (int i = 0; i < NCH; ++i) {
       const int c = lane * 8 + i * 256;
-      if (FULL || c < cols) {
-        float xv[8], dv[8]; Vec8<TX>::load(x + base + c, xv); Vec8<__nv_bfloat16>::load(g_n + base + c, dv);
+      const bool valid = FULL || c < cols;
+      const int cl = FULL ? c : min(c, cols - 8);
+      float xv[8], dv[8]; Vec8<TX>::load(x + base + cl, xv); Vec8<__nv_bfloat16>::load(g_n + base + cl, dv);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) dot += dv[e] * wreg[i][e] * xv[e];
-      }
+      for (int e = 0; e < 8; ++e) dot += valid ? dv[e] * wreg[i][e] * xv[e] : 0.f;
     }
     dot = warp_sum(dot);
     const float c1 = dot * rs * rs * rs / cols;
 #pragma unroll
     for (int i = 0; i < NCH; ++i) {
       const int c = lane * 8 + i * 256;
-      if (!FULL && c >= cols) continue;
-      float xv[8], dv[8], o[8]; Vec8<TX>::load(x + base + c, xv); Vec8<__nv_bfloat16>::load(g_n + base + c, dv);
+      const bool valid = FULL || c < cols;
+      const int cl = FULL ? c : min(c, cols - 8);
+      float xv[8], dv[8], o[8]; Vec8<TX>::load(x + base + cl, xv); Vec8<__nv_bfloat16>::load(g_n + base + cl, dv);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         o[e] = dv[e] * wreg[i][e] * rs - xv[e] * c1;
-        dwacc[i][e] += dv[e] * xv[e] * rs;
+        dwacc[i][e] += valid ? dv[e] * xv[e] * rs : 0.f;
       }
       if (g_res) {
-        float gr[8]; Vec8<float>::load(g_res + base + c, gr);
+        float gr[8]; Vec8<float>::load(g_res + base + cl, gr);
 #pragma unroll
         for (int e = 0; e < 8; ++e) o[e] += gr[e];
       }
-      if (d_res) Vec8<float>::store(d_res + base + c, o);
-      if (d_h) {
+      if (valid) {
+        if (d_res) Vec8<float>::store(d_res + base + c, o);
+        if (d_h) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] *= h_scale;
-        Vec8<__nv_bfloat16>::store(d_h + base + c, o);
+          for (int e = 0; e < 8; ++e) o[e] *= h_scale;
+          Vec8<__nv_bfloat16>::store(d_h + base + c, o);
+        }
       }
     }
   }

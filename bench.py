@@ -52,6 +52,14 @@ CONFIGS = {
              "differential attention, LayerNorm, vocab 200064, tied embeddings), packed 8192-token rows",
         train_model="phi4miniflash", depth=32, train_name="scaling_mup_muonh_tie", micro_bsz=1, ctx_len=8192,
         overrides={}, sparsity=1, top_k=2),
+    "gdny": dict(
+        name="GDN-Y d16 (Gated DeltaNet + YOCO decoder-hybrid-decoder), muP++ MuonH",
+        train_model="gdny", depth=16, train_name="scaling_mup_muonh", micro_bsz=8, ctx_len=4096,
+        overrides={}, sparsity=1, top_k=2),
+    "mambay2": dict(
+        name="Mamba-2-Y d16 (Mamba-2 SSD + YOCO decoder-hybrid-decoder), muP++ MuonH",
+        train_model="mambay2", depth=16, train_name="scaling_mup_muonh", micro_bsz=8, ctx_len=4096,
+        overrides={}, sparsity=1, top_k=2),
     "sambay": dict(
         name="SambaY d16 (Mamba-1 + SWA + YOCO + GMU), muP++ MuonH",
         train_model="sambay", depth=16, train_name="scaling_mup_muonh", micro_bsz=8, ctx_len=4096,
