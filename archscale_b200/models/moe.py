@@ -106,11 +106,16 @@ class SonicMoE(nn.Module):
         w_in, w_out, b_in, b_out = self._expert_weights()
         if w_in.dtype != h.dtype:
             w_in, w_out = w_in.to(h.dtype), w_out.to(h.dtype)
+        mix = math.sqrt(0.5) if (self.share_expert and self.config.sqrt_gate) else 1.0
+        mixed = False
         if self.ep_size > 1:
             from archscale_b200.parallel import ep
             routed = ep.moe_ffn_expert_parallel(h, w_in, w_out, scores, indices, self.n_mods, self.ep_group, site=id(self))
         else:
-            routed = ops.moe_ffn(h, w_in, w_out, scores.to(h.dtype), indices, b_in, b_out)
+            # the shared expert's output and the 1/sqrt(2) mix are added inside the routed FFN's combine pass
+            routed = ops.moe_ffn(h, w_in, w_out, scores.to(h.dtype), indices, b_in, b_out,
+                                 shared=shared if self.share_expert else None, alpha=mix)
+            mixed = self.share_expert
         with torch.no_grad():
             counts = torch.bincount(indices.reshape(-1).long(), minlength=self.n_mods).to(torch.float32)
             if self.collect_stats:
@@ -128,7 +133,7 @@ class SonicMoE(nn.Module):
                                                   style=self.aux_style, seq_len=T)
         else:
             self.aux_loss = 0.0
-        if self.share_expert:
+        if self.share_expert and not mixed:
             if self.config.sqrt_gate:
                 routed = math.sqrt(0.5) * routed + math.sqrt(0.5) * shared
             else:

@@ -30,7 +30,7 @@ def supported(x, w_in, w_out, b_in, b_out) -> bool:
 
 class _MoEFFNFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w_in, w_out, scores, indices):
+    def forward(ctx, x, w_in, w_out, scores, indices, shared=None, alpha=1.0):
         ext = backend.require_extension()
         N, C = x.shape
         E, I2, _ = w_in.shape
@@ -46,13 +46,16 @@ class _MoEFFNFn(torch.autograd.Function):
             h = ext.grouped_gemm_bf16(0, xs, w_in.reshape(E * I2, C), offsets, 0, I2, C, None)
             a = ext.swiglu_packed_fwd(h)
         y = ext.grouped_gemm_bf16(0, a, w_out.reshape(E * C, I), offsets, 0, C, I, None)
-        out = ext.combine_rows(y, pair_slot, sc, N, K)
+        # out = alpha · (Σ_k score_k · y_k + shared): the shared expert's output and the mixing factor ride on the combine pass
+        out = ext.combine_rows(y, pair_slot, sc, N, K, None if shared is None else shared.contiguous(), float(alpha))
         backend.count_launch(9)
         # `a` is kept as well (a quarter of the size of xs or y): recomputing it in backward is one more pass over h
         ctx.save_for_backward(xs, h, a, y, w_in, w_out, sc, offsets, slot_pair, pair_slot)
         ctx.dims = (N, C, E, I2, I, K)
         ctx.w_refs = (w_in, w_out)
         ctx.score_dtype = scores.dtype
+        ctx.alpha = float(alpha)
+        ctx.has_shared = shared is not None
         return out
 
     @staticmethod
@@ -61,8 +64,12 @@ class _MoEFFNFn(torch.autograd.Function):
         xs, h, a, y, w_in, w_out, sc, offsets, slot_pair, pair_slot = ctx.saved_tensors
         N, C, E, I2, I, K = ctx.dims
         dout = dout.contiguous()
-        dscores = ext.pair_dots(y, dout, pair_slot, K).view(N, K).to(ctx.score_dtype)
-        dy = ext.gather_rows(dout, slot_pair, sc.reshape(-1), K, offsets)             # dy[slot] = score · dout[token]
+        alpha = ctx.alpha
+        dots = ext.pair_dots(y, dout, pair_slot, K).view(N, K)
+        if alpha != 1.0:
+            dots, sc = dots * alpha, sc * alpha                                        # [N, K] tensors: the factor costs no pass over rows
+        dscores = dots.to(ctx.score_dtype)
+        dy = ext.gather_rows(dout, slot_pair, sc.reshape(-1), K, offsets)             # dy[slot] = alpha · score · dout[token]
         da = ext.grouped_gemm_bf16(1, dy, w_out.reshape(E * C, I), offsets, 0, I, C, None)
         mg_out = getattr(ctx.w_refs[1], "main_grad", None)
         dw_out = ext.grouped_gemm_bf16(2, dy, a, offsets, C, I, 0, mg_out)
@@ -72,8 +79,13 @@ class _MoEFFNFn(torch.autograd.Function):
         dw_in = ext.grouped_gemm_bf16(2, dh, xs, offsets, I2, C, 0, mg_in)
         dx = ext.combine_rows(dxs, pair_slot, None, N, K)
         backend.count_launch(8)
-        return dx, (None if mg_in is not None else dw_in), (None if mg_out is not None else dw_out), dscores, None
+        dshared = None
+        if ctx.has_shared:
+            dshared = dout if alpha == 1.0 else dout * alpha
+        return (dx, (None if mg_in is not None else dw_in), (None if mg_out is not None else dw_out), dscores, None,
+                dshared, None)
 
 
-def moe_ffn_cuda(x, w_in, w_out, scores, indices):
-    return _MoEFFNFn.apply(x, w_in, w_out, scores, indices.to(torch.int32))
+def moe_ffn_cuda(x, w_in, w_out, scores, indices, shared=None, alpha=1.0):
+    """alpha · (routed FFN + shared); ``shared`` (N, C) is the shared expert's output, if any."""
+    return _MoEFFNFn.apply(x, w_in, w_out, scores, indices.to(torch.int32), shared, alpha)

@@ -122,11 +122,17 @@ def moe_ffn_sorted_torch(x, w_in, w_out, scores, indices, b_in=None, b_out=None)
     return out.to(x.dtype)
 
 
-def moe_ffn(x, w_in, w_out, scores, indices, b_in=None, b_out=None):
+def moe_ffn(x, w_in, w_out, scores, indices, b_in=None, b_out=None, shared=None, alpha: float = 1.0):
+    """Routed expert FFN; with ``shared`` (the shared expert's output, (N, C)) and ``alpha`` the result is
+    ``alpha * (routed + shared)`` — the mix of `lit_gpt/moe.py:636-641` folded into the combine pass."""
     from . import grouped_gemm
-    if grouped_gemm.supported(x, w_in, w_out, b_in, b_out) and backend.use_cuda_kernel("grouped_gemm", x, w_in, w_out):
-        return grouped_gemm.moe_ffn_cuda(x, w_in, w_out, scores, indices)
-    return moe_ffn_sorted_torch(x, w_in, w_out, scores, indices, b_in, b_out)
+    if grouped_gemm.supported(x, w_in, w_out, b_in, b_out) and backend.use_cuda_kernel("grouped_gemm", x, w_in, w_out) \
+            and (shared is None or shared.dtype == x.dtype):
+        return grouped_gemm.moe_ffn_cuda(x, w_in, w_out, scores, indices, shared, alpha)
+    out = moe_ffn_sorted_torch(x, w_in, w_out, scores, indices, b_in, b_out)
+    if shared is not None:
+        out = out + shared
+    return out if alpha == 1.0 else out * alpha
 
 
 # ------------------------------------------------------------------ aux loss

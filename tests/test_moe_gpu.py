@@ -70,6 +70,31 @@ def test_moe_ffn_forward_backward(N, C, E, I, K):
     assert _rel(logits.grad, lr.grad) < 3e-2
 
 
+def test_moe_ffn_with_shared_output_and_mix_in_the_combine_pass():
+    """alpha * (routed + shared) from the combine kernel, and its gradients, against the same sum in fp32."""
+    torch.manual_seed(5)
+    N, C, E, I, K, alpha = 700, 512, 16, 128, 4, 0.5 ** 0.5
+    x = (torch.randn(N, C, device="cuda") * 0.5).bfloat16().requires_grad_()
+    w_in = (torch.randn(E, 2 * I, C, device="cuda") * 0.05).bfloat16().requires_grad_()
+    w_out = (torch.randn(E, C, I, device="cuda") * 0.05).bfloat16().requires_grad_()
+    shared = (torch.randn(N, C, device="cuda") * 0.3).bfloat16().requires_grad_()
+    logits = torch.randn(N, E, device="cuda", requires_grad=True)
+    scores, idx = ops.router_topk_softmax(logits, K, sqrt_gate=True)
+    out = ops.moe_ffn(x, w_in, w_out, scores, idx, shared=shared, alpha=alpha)
+    g = torch.randn_like(out)
+    out.backward(g)
+    torch.cuda.synchronize()
+    assert backend.require_extension().device_status() == 0
+    xr, wir, wor, lr, shr = (t.detach().float().requires_grad_() for t in (x, w_in, w_out, logits, shared))
+    sr, ir = router_topk_softmax_ref(lr, K, sqrt_gate=True)
+    ref = alpha * (moe_ffn_ref(xr, wir, wor, sr, ir) + shr)
+    ref.backward(g.float())
+    assert _rel(out, ref) < 2e-2
+    for got, want in ((x.grad, xr.grad), (w_in.grad, wir.grad), (w_out.grad, wor.grad), (logits.grad, lr.grad),
+                      (shared.grad, shr.grad)):
+        assert _rel(got, want) < 3e-2
+
+
 def test_grouped_gemm_with_swiglu_epilogue_equals_unfused():
     """Expert up-projection with SwiGLU in the epilogue against the grouped GEMM followed by the SwiGLU kernel."""
     ext = backend.require_extension()
