@@ -133,6 +133,7 @@ class Config:
     ep_size: int = 1   # expert-parallel degree (experts sharded over this many ranks)
     tp_size: int = 1   # tensor-parallel degree
     mxfp8: bool = False  # E4M3 values + E8M0 scale per 32 elements on every Linear except lm_head
+    nvfp4: bool = False  # e2m1 values + E4M3 scale per 16 elements + one fp32 scale per tensor, same layers
 
     def __post_init__(self) -> None:
         if self.padded_vocab_size is None:

@@ -101,7 +101,8 @@ class LLaMAMLP(nn.Module):
             self.norm.reset_parameters()
 
     def forward(self, x: torch.Tensor, layer_idx: int, gmu_mems=None):
-        if (not self.relu2 and not self.oss_swiglu and type(self.w1) is Linear and self.w1.bias is None and not self.w1.mxfp8
+        if (not self.relu2 and not self.oss_swiglu and type(self.w1) is Linear and self.w1.bias is None
+                and not self.w1.mxfp8 and not self.w1.nvfp4
                 and not (self.config.gmu_mlp and layer_idx == self.config.n_layer // 2 + 1)):
             h = ops.linear_swiglu(x, self.w1.weight)    # SwiGLU in the GEMM epilogue when the kernel takes this case
             if h is not None:

@@ -95,7 +95,8 @@ class SonicMoE(nn.Module):
         h = x.reshape(-1, C)
         if self.share_expert:
             act = None
-            if type(self.shared_mod_in) is Linear and self.shared_mod_in.bias is None and not self.shared_mod_in.mxfp8:
+            if type(self.shared_mod_in) is Linear and self.shared_mod_in.bias is None and not self.shared_mod_in.mxfp8 \
+                    and not self.shared_mod_in.nvfp4:
                 act = ops.linear_swiglu(h, self.shared_mod_in.weight)
             if act is None:
                 act = ops.swiglu_packed(self.shared_mod_in(h))

@@ -142,9 +142,19 @@ int b200_selective_scan_channel_blocks(int Di);
 
 // Block-scaled MXFP8 (gemm_mxfp8.cu): quantisers and the tcgen05 block-scaled GEMM.
 size_t b200_mxfp8_sf_bytes(int rows, int K);
-int b200_mxfp8_quantize(const void* x, int ld, void* q, void* sf, int R, int C, int colwise, cudaStream_t st);
+int b200_mxfp8_quantize(const void* x, int ld, void* q, void* sf, int R, int C, int colwise, cudaStream_t st,
+                        void* qT = nullptr, void* sfT = nullptr);   // colwise 2: both orientations from one read
 int b200_gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, void* out, int M, int N, int K, int lda,
                     int ldb, int ldc, float alpha, int out_f32, int accumulate, int num_sms, int* status, cudaStream_t stream);
+// NVFP4 (gemm_mxfp8.cu): packed e2m1 elements, E4M3 scales per 16 elements, one fp32 scale per tensor derived on the device
+// from the tensor's largest magnitude (amax: fp32 [1] in device memory, zeroed before b200_nvfp4_amax).
+size_t b200_nvfp4_sf_bytes(int rows, int K);
+int b200_nvfp4_amax(const void* x, int ld, float* amax, int R, int C, cudaStream_t st);
+int b200_nvfp4_quantize(const void* x, int ld, void* q, void* sf, void* qT, void* sfT, const float* amax, int R, int C, int mode,
+                        cudaStream_t st);
+int b200_gemm_nvfp4(const void* A, const void* sfa, const void* B, const void* sfb, const float* amax_a, const float* amax_b,
+                    void* out, int M, int N, int K, int lda, int ldb, int ldc, float alpha, int out_f32, int accumulate,
+                    int num_sms, int* status, cudaStream_t stream);
 
 // LayerNorm (layernorm.cu)
 int b200_layernorm_bwd_partials(int rows);

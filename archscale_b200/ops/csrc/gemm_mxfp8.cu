@@ -288,10 +288,14 @@ __global__ void __launch_bounds__(256) mxfp8_quant_rowwise_kernel(const __nv_bfl
   sf[sf_offset(r, kb, nblk >> 2)] = static_cast<uint8_t>(ex);
 }
 
-// Column-wise: writes the transposed operand qT [C, R] with scale blocks along R.  R % 128 == 0, C % 64 == 0.
+// Column-wise: writes the transposed operand qT [C, R] with scale blocks along R; with ROWS it also writes the row-wise
+// operand q [R, C] from the same shared-memory tile (one read of a tensor that is needed in both orientations).
+// R % 128 == 0, C % 64 == 0 (ROWS: C % 128 == 0).
+template <int ROWS>
 __global__ void __launch_bounds__(256) mxfp8_quant_colwise_kernel(const __nv_bfloat16* __restrict__ x, int ld,
-                                                                 uint8_t* __restrict__ qT, uint8_t* __restrict__ sfT, int R, int C) {
-  __shared__ __nv_bfloat16 s[128][72];
+                                                                 uint8_t* __restrict__ qT, uint8_t* __restrict__ sfT,
+                                                                 uint8_t* __restrict__ q, uint8_t* __restrict__ sf, int R, int C) {
+  __shared__ __align__(16) __nv_bfloat16 s[128][72];
   const int r0 = blockIdx.y * 128, c0 = blockIdx.x * 64, tid = threadIdx.x;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -300,24 +304,55 @@ __global__ void __launch_bounds__(256) mxfp8_quant_colwise_kernel(const __nv_bfl
     *reinterpret_cast<uint4*>(&s[row][cv * 8]) = u;
   }
   __syncthreads();
-  const int c = tid & 63, rb = tid >> 6;
-  float v[32];
-  float amax = 0.f;
+  {
+    const int c = tid & 63, rb = tid >> 6;
+    float v[32];
+    float amax = 0.f;
 #pragma unroll
-  for (int j = 0; j < 32; ++j) { v[j] = __bfloat162float(s[rb * 32 + j][c]); amax = fmaxf(amax, fabsf(v[j])); }
-  const uint32_t ex = e8m0_for_amax(amax);
-  const float inv = __uint_as_float((254u - ex) << 23);
-  uint4* dst = reinterpret_cast<uint4*>(qT + static_cast<size_t>(c0 + c) * R + r0 + rb * 32);
+    for (int j = 0; j < 32; ++j) { v[j] = __bfloat162float(s[rb * 32 + j][c]); amax = fmaxf(amax, fabsf(v[j])); }
+    const uint32_t ex = e8m0_for_amax(amax);
+    const float inv = __uint_as_float((254u - ex) << 23);
+    uint4* dst = reinterpret_cast<uint4*>(qT + static_cast<size_t>(c0 + c) * R + r0 + rb * 32);
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    uint4 o;
-    o.x = cvt4_e4m3(v[i * 16 + 0] * inv, v[i * 16 + 1] * inv, v[i * 16 + 2] * inv, v[i * 16 + 3] * inv);
-    o.y = cvt4_e4m3(v[i * 16 + 4] * inv, v[i * 16 + 5] * inv, v[i * 16 + 6] * inv, v[i * 16 + 7] * inv);
-    o.z = cvt4_e4m3(v[i * 16 + 8] * inv, v[i * 16 + 9] * inv, v[i * 16 + 10] * inv, v[i * 16 + 11] * inv);
-    o.w = cvt4_e4m3(v[i * 16 + 12] * inv, v[i * 16 + 13] * inv, v[i * 16 + 14] * inv, v[i * 16 + 15] * inv);
-    dst[i] = o;
+    for (int i = 0; i < 2; ++i) {
+      uint4 o;
+      o.x = cvt4_e4m3(v[i * 16 + 0] * inv, v[i * 16 + 1] * inv, v[i * 16 + 2] * inv, v[i * 16 + 3] * inv);
+      o.y = cvt4_e4m3(v[i * 16 + 4] * inv, v[i * 16 + 5] * inv, v[i * 16 + 6] * inv, v[i * 16 + 7] * inv);
+      o.z = cvt4_e4m3(v[i * 16 + 8] * inv, v[i * 16 + 9] * inv, v[i * 16 + 10] * inv, v[i * 16 + 11] * inv);
+      o.w = cvt4_e4m3(v[i * 16 + 12] * inv, v[i * 16 + 13] * inv, v[i * 16 + 14] * inv, v[i * 16 + 15] * inv);
+      dst[i] = o;
+    }
+    sfT[sf_offset(c0 + c, (r0 >> 5) + rb, R >> 7)] = static_cast<uint8_t>(ex);
   }
-  sfT[sf_offset(c0 + c, (r0 >> 5) + rb, R >> 7)] = static_cast<uint8_t>(ex);
+  if (ROWS) {
+    const int row = tid >> 1, blk = tid & 1;                              // 128 rows × 2 blocks of 32 columns
+    float v[32];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 u = *reinterpret_cast<const uint4*>(&s[row][blk * 32 + i * 8]);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = unpack_bf16x2(w[e]);
+        v[i * 8 + 2 * e] = f.x; v[i * 8 + 2 * e + 1] = f.y;
+        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+      }
+    }
+    const uint32_t ex = e8m0_for_amax(amax);
+    const float inv = __uint_as_float((254u - ex) << 23);
+    uint4* dst = reinterpret_cast<uint4*>(q + static_cast<size_t>(r0 + row) * C + c0 + blk * 32);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      uint4 o;
+      o.x = cvt4_e4m3(v[i * 16 + 0] * inv, v[i * 16 + 1] * inv, v[i * 16 + 2] * inv, v[i * 16 + 3] * inv);
+      o.y = cvt4_e4m3(v[i * 16 + 4] * inv, v[i * 16 + 5] * inv, v[i * 16 + 6] * inv, v[i * 16 + 7] * inv);
+      o.z = cvt4_e4m3(v[i * 16 + 8] * inv, v[i * 16 + 9] * inv, v[i * 16 + 10] * inv, v[i * 16 + 11] * inv);
+      o.w = cvt4_e4m3(v[i * 16 + 12] * inv, v[i * 16 + 13] * inv, v[i * 16 + 14] * inv, v[i * 16 + 15] * inv);
+      dst[i] = o;
+    }
+    sf[sf_offset(r0 + row, (c0 >> 5) + blk, C >> 7)] = static_cast<uint8_t>(ex);
+  }
 }
 
 typedef CUresult (*EncodeTiledFnQ)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -344,6 +379,339 @@ static int make_tmap_2d_u8(CUtensorMap* map, const void* ptr, uint64_t inner, ui
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+
+// =====================================================================================================================
+// NVFP4: e2m1 elements (two per byte, element 2i in the low nibble), one unsigned E4M3 scale per 16 elements along K and
+// one fp32 scale per tensor:  x ≈ tensor_scale · block_scale · e2m1.   tcgen05.mma.kind::mxf4nvf4.block_scale.scale_vec::4X
+// consumes 64 elements (32 bytes) of K per instruction and the four block scales of that span from one 32-bit column of
+// tensor memory per 32 rows, so the 512-byte scale chunk above (128 rows × 4 scales) is exactly one instruction's worth and
+// the quantisers reuse sf_offset() with 16-element blocks and K/64 chunks per row chunk.
+//   tile 128 × 192 × 256 elements (128 bytes of K per row and stage), 4-stage ring of 46 KB, two accumulators.
+// The epilogue reads the two tensors' largest magnitudes from device memory and forms the product of the tensor scales
+// itself (no host round trip, no launch in between).
+constexpr int FBK = 256, FSTAGES = 4;                                   // elements of K per stage
+constexpr int FA_BYTES = QBM * 128, FB_BYTES = QBN * 128;
+constexpr int FSFA_OFF = FA_BYTES + FB_BYTES, FSFB_OFF = FSFA_OFF + 2048;
+constexpr int FSTAGE_BYTES = FSFB_OFF + 4096;                           // 47104 = 46 KiB, a multiple of 1024
+constexpr int FSMEM_BYTES = FSTAGES * FSTAGE_BYTES + 1024 + 256;
+constexpr int F_TMEM_SFA = 384, F_TMEM_SFB = 400;                       // 16 + 32 columns after the two accumulators
+static_assert(FSTAGE_BYTES % 1024 == 0, "stages must stay 1024-byte aligned");
+
+// tensor scale from the tensor's largest magnitude: amax / (6 · 448), or 1 for an all-zero tensor
+__device__ __forceinline__ float nvfp4_tensor_scale(float amax) {
+  return amax > 0.f ? __fmul_rn(amax, static_cast<float>(1.0 / 2688.0)) : 1.f;
+}
+__device__ __forceinline__ void umma_nvf4(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t tsfa,
+                                          uint32_t tsfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n" ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb)
+      : "memory");
+}
+// e2m1 × e2m1 (format code 1 in both operand fields), unsigned E4M3 scales (scale-format bit clear), fp32 accumulate
+__host__ __device__ constexpr uint32_t make_idesc_nvf4(int M, int N) {
+  return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+template <int OUT_F32>
+__global__ void __launch_bounds__(192, 1)
+gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const QGemmParams p,
+                  const float* __restrict__ amax_a, const float* __restrict__ amax_b) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FSTAGES * FSTAGE_BYTES);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + FSTAGES;
+  uint64_t* tmem_full = bars + 2 * FSTAGES;
+  uint64_t* tmem_empty = bars + 2 * FSTAGES + 2;
+  uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(bars + 2 * FSTAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cta = blockIdx.x, n_cta = gridDim.x;
+  const int num_m = (p.M + QBM - 1) / QBM, num_n = (p.N + QBN - 1) / QBN;
+  const int num_tiles = num_m * num_n;
+  const int KC = p.K / FBK;                      // stages along K: 256 elements = 4 instructions = 4 scale chunks
+  const int n_chunks_n = (p.N + 127) / 128;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < FSTAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 4); }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) { tmem_alloc(tmem_ptr, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  auto tile_coords = [&](int t, int& m0, int& n0) {
+    const int per_group = Q_GROUP_M * num_n;
+    const int g = t / per_group, first_m = g * Q_GROUP_M;
+    const int gsz = min(num_m - first_m, Q_GROUP_M);
+    const int r = t - g * per_group;
+    m0 = (first_m + (r % gsz)) * QBM;
+    n0 = (r / gsz) * QBN;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      for (int t = cta; t < num_tiles; t += n_cta) {
+        int m0, n0; tile_coords(t, m0, n0);
+        const int c0 = n0 >> 7;                                  // first 128-row scale chunk of the B tile
+        const int nb = (c0 + 1 < n_chunks_n) ? 2 : 1;
+        for (int kb = 0; kb < KC; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY)) goto done;
+          uint8_t* sa = smem + stage * FSTAGE_BYTES;
+          mbar_arrive_expect_tx(&full_bar[stage], FA_BYTES + FB_BYTES + 2048 + 2048 * nb);
+          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * 128, m0);                      // coordinates in bytes
+          tma_load_2d(sa + FA_BYTES, &tmap_b, &full_bar[stage], kb * 128, n0);
+          // the four chunks of one row chunk and one stage are adjacent in memory
+          q_bulk_g2s(sa + FSFA_OFF, p.sfa + (static_cast<size_t>(m0 >> 7) * KC + kb) * 2048, 2048, &full_bar[stage]);
+          q_bulk_g2s(sa + FSFB_OFF, p.sfb + (static_cast<size_t>(c0) * KC + kb) * 2048, 2048, &full_bar[stage]);
+          if (nb == 2)
+            q_bulk_g2s(sa + FSFB_OFF + 2048, p.sfb + (static_cast<size_t>(c0 + 1) * KC + kb) * 2048, 2048, &full_bar[stage]);
+          if (++stage == FSTAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_nvf4(QBM, QBN);
+      int stage = 0; uint32_t phase = 0;
+      int it = 0;
+      for (int t = cta; t < num_tiles; t += n_cta, ++it) {
+        const int acc = it & 1; const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, STATUS_TIMEOUT_TMEM_EMPTY)) goto done;
+        tc_fence_after();
+        int m0, n0; tile_coords(t, m0, n0);
+        const uint32_t d_tmem = tmem_base + acc * QBN;
+        const uint32_t sfb_shift = (n0 >> 5) & 3;                         // 0 or 2: rows 64.. of the first row chunk
+        for (int kb = 0; kb < KC; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_FULL)) goto done;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * FSTAGE_BYTES);
+#pragma unroll
+          for (uint32_t k = 0; k < 4; ++k) {
+            tmem_cp_sf(tmem_base + F_TMEM_SFA + 4 * k, make_sf_desc(sa + FSFA_OFF + 512 * k));
+            tmem_cp_sf(tmem_base + F_TMEM_SFB + 8 * k, make_sf_desc(sa + FSFB_OFF + 512 * k));
+            tmem_cp_sf(tmem_base + F_TMEM_SFB + 8 * k + 4, make_sf_desc(sa + FSFB_OFF + 2048 + 512 * k));
+          }
+          const uint64_t da = make_smem_desc(sa, 16, 1024);
+          const uint64_t db = make_smem_desc(sa + FA_BYTES, 16, 1024);
+#pragma unroll
+          for (uint32_t k = 0; k < 4; ++k)                               // 64 elements = 32 bytes of K per instruction
+            umma_nvf4(d_tmem, da + static_cast<uint64_t>(k * 2), db + static_cast<uint64_t>(k * 2), idesc,
+                      tmem_base + F_TMEM_SFA + 4 * k, tmem_base + F_TMEM_SFB + 8 * k + sfb_shift,
+                      (kb != 0 || k != 0) ? 1u : 0u);
+          umma_commit(&empty_bar[stage]);
+          if (++stage == FSTAGES) { stage = 0; phase ^= 1; }
+        }
+        if (KC == 0) mbar_arrive(&tmem_full[acc]);
+        else umma_commit(&tmem_full[acc]);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const float alpha = p.alpha * __fmul_rn(nvfp4_tensor_scale(*amax_a), nvfp4_tensor_scale(*amax_b));
+    int it = 0;
+    for (int t = cta; t < num_tiles; t += n_cta, ++it) {
+      int m0, n0; tile_coords(t, m0, n0);
+      const int acc = it & 1; const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, STATUS_TIMEOUT_TMEM_FULL)) goto done;
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t taddr = tmem_base + acc * QBN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < QBN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (KC == 0) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r[e] = 0u;
+        }
+        const int col = n0 + c * 32;
+        if (row < p.M && col < p.N) {
+          if (OUT_F32) {
+            float* o = reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ldc + col;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (col + j < p.N) {
+                float4 v = make_float4(__uint_as_float(r[j]) * alpha, __uint_as_float(r[j + 1]) * alpha,
+                                       __uint_as_float(r[j + 2]) * alpha, __uint_as_float(r[j + 3]) * alpha);
+                if (p.accumulate) {
+                  const float4 old = *reinterpret_cast<const float4*>(o + j);
+                  v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+                }
+                *reinterpret_cast<float4*>(o + j) = v;
+              }
+            }
+          } else {
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ldc + col;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col + j < p.N) {
+                uint4 ov;
+                ov.x = pack_bf16x2(__uint_as_float(r[j]) * alpha, __uint_as_float(r[j + 1]) * alpha);
+                ov.y = pack_bf16x2(__uint_as_float(r[j + 2]) * alpha, __uint_as_float(r[j + 3]) * alpha);
+                ov.z = pack_bf16x2(__uint_as_float(r[j + 4]) * alpha, __uint_as_float(r[j + 5]) * alpha);
+                ov.w = pack_bf16x2(__uint_as_float(r[j + 6]) * alpha, __uint_as_float(r[j + 7]) * alpha);
+                *reinterpret_cast<uint4*>(o + j) = ov;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+    }
+  }
+
+done:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---- NVFP4 quantisers.  amax[0] = max |x| over the tensor (nvfp4_amax_kernel); tensor scale = amax / (6 · 448), 1 if zero.
+// block scale = E4M3(amax_block · (1 / (6 · tensor_scale))), round to nearest; element = e2m1(x / (block · tensor)), round to
+// nearest even, saturating at 6.
+__device__ __forceinline__ uint32_t e2m1_code(float v) {
+  const float a = fabsf(v);
+  uint32_t c = (a > 0.25f) + (a >= 0.75f) + (a > 1.25f) + (a >= 1.75f) + (a > 2.5f) + (a >= 3.5f) + (a > 5.f);
+  return c | (v < 0.f ? 8u : 0u);
+}
+__device__ __forceinline__ float nvfp4_block_scale(float amax, float tensor_scale, uint8_t* code) {
+  // amax · (1 / (6 · tensor_scale)) with every step rounded to nearest: the same three operations as the PyTorch
+  // restatement, so that both give the same scale even where the exact quotient is a tie between two E4M3 values
+  const float want = fminf(__fmul_rn(amax, __frcp_rn(__fmul_rn(tensor_scale, 6.f))), 448.f);
+  const __nv_fp8_storage_t b = __nv_cvt_float_to_fp8(want, __NV_SATFINITE, __NV_E4M3);
+  *code = static_cast<uint8_t>(b);
+  const __half_raw h = __nv_cvt_fp8_to_halfraw(b, __NV_E4M3);
+  const float sb = __half2float(*reinterpret_cast<const __half*>(&h));
+  return sb > 0.f ? __frcp_rn(sb * tensor_scale) : 0.f;                 // multiply by this, then round to e2m1
+}
+
+// Quantise 16 values held in registers: returns the two packed words and the scale code.
+__device__ __forceinline__ uint2 nvfp4_pack16(const float (&v)[16], float ts, uint8_t* code) {
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+  const float inv = nvfp4_block_scale(amax, ts, code);
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { lo |= e2m1_code(v[e] * inv) << (4 * e); hi |= e2m1_code(v[8 + e] * inv) << (4 * e); }
+  return make_uint2(lo, hi);
+}
+__device__ __forceinline__ void unpack16(const uint4& u0, const uint4& u1, float (&v)[16]) {
+  const uint32_t w[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { const float2 f = unpack_bf16x2(w[e]); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
+}
+
+// One thread per 16-element block of a row.  x: [R, C] bf16, q: [R, C/2] bytes, C % 256 == 0.  (A thread per 64 elements,
+// with whole 32-byte sectors and aligned scale words out, was measured slower: 0.072 against 0.076 ms net became 0.083 for
+// 32768 × 2048 — consecutive threads then read 128 bytes apart.)
+__global__ void __launch_bounds__(256) nvfp4_quant_rowwise_kernel(const __nv_bfloat16* __restrict__ x, int ld,
+                                                                 uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
+                                                                 const float* __restrict__ amax_t, int R, int C) {
+  const int nblk = C >> 4;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long long>(R) * nblk) return;
+  const int r = static_cast<int>(idx / nblk), kb = static_cast<int>(idx % nblk);
+  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * ld + kb * 16);
+  const uint4 u0 = src[0], u1 = src[1];
+  float v[16];
+  unpack16(u0, u1, v);
+  uint8_t code;
+  const uint2 w = nvfp4_pack16(v, nvfp4_tensor_scale(*amax_t), &code);
+  *reinterpret_cast<uint2*>(q + static_cast<size_t>(r) * (C >> 1) + kb * 8) = w;
+  sf[sf_offset(r, kb, nblk >> 2)] = code;
+}
+
+// Column-wise: writes the transposed operand qT [C, R/2] with 16-element scale blocks along R; with ROWS it also writes
+// the row-wise operand q [R, C/2] (blocks along C) from the same shared-memory tile, so that a tensor needed in both
+// orientations (an activation for forward and weight gradient, an output gradient for both backward products) is read
+// once.  Tile 128 rows × 64 columns.  R % 256 == 0, C % 64 == 0 (ROWS: C % 256 == 0).
+template <int ROWS>
+__global__ void __launch_bounds__(256) nvfp4_quant_colwise_kernel(const __nv_bfloat16* __restrict__ x, int ld,
+                                                                 uint8_t* __restrict__ qT, uint8_t* __restrict__ sfT,
+                                                                 uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
+                                                                 const float* __restrict__ amax_t, int R, int C) {
+  __shared__ __align__(16) __nv_bfloat16 s[128][72];
+  const int r0 = blockIdx.y * 128, c0 = blockIdx.x * 64, tid = threadIdx.x;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int idx = tid + 256 * i, row = idx >> 3, cv = idx & 7;
+    const uint4 u = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(r0 + row) * ld + c0 + cv * 8);
+    *reinterpret_cast<uint4*>(&s[row][cv * 8]) = u;
+  }
+  __syncthreads();
+  const float ts = nvfp4_tensor_scale(*amax_t);
+  {
+    const int c = tid & 63, rb = tid >> 6;                               // 32 rows = two blocks per thread
+    uint32_t words[4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = __bfloat162float(s[rb * 32 + h * 16 + j][c]);
+      uint8_t code;
+      const uint2 w = nvfp4_pack16(v, ts, &code);
+      words[2 * h] = w.x; words[2 * h + 1] = w.y;
+      sfT[sf_offset(c0 + c, (r0 >> 4) + rb * 2 + h, R >> 6)] = code;
+    }
+    *reinterpret_cast<uint4*>(qT + static_cast<size_t>(c0 + c) * (R >> 1) + ((r0 + rb * 32) >> 1)) =
+        make_uint4(words[0], words[1], words[2], words[3]);
+  }
+  if (ROWS) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {                                        // 128 rows × 4 blocks of 16 columns
+      const int item = tid + 256 * i, row = item >> 2, blk = item & 3;
+      const uint4 u0 = *reinterpret_cast<const uint4*>(&s[row][blk * 16]);
+      const uint4 u1 = *reinterpret_cast<const uint4*>(&s[row][blk * 16 + 8]);
+      float v[16];
+      unpack16(u0, u1, v);
+      uint8_t code;
+      const uint2 w = nvfp4_pack16(v, ts, &code);
+      *reinterpret_cast<uint2*>(q + static_cast<size_t>(r0 + row) * (C >> 1) + ((c0 + blk * 16) >> 1)) = w;
+      sf[sf_offset(r0 + row, (c0 >> 4) + blk, C >> 6)] = code;
+    }
+  }
+}
+
+// amax[0] = max(amax[0], max |x|) over a [R, C] bf16 tensor with row stride ld (amax zeroed by the caller); C % 8 == 0.
+// (Four loads in flight per thread, strided over the grid or consecutive within the block, were both measured slower
+// than this plain grid-stride loop: 0.054 against 0.043 ms for 134 MB.)
+__global__ void __launch_bounds__(256) nvfp4_amax_kernel(const __nv_bfloat16* __restrict__ x, int ld, float* __restrict__ amax,
+                                                        int R, int C) {
+  const int vec_per_row = C >> 3;
+  const size_t total = static_cast<size_t>(R) * vec_per_row;
+  float m = 0.f;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const uint4 u = *reinterpret_cast<const uint4*>(x + (i / vec_per_row) * ld + (i % vec_per_row) * 8);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { const float2 f = unpack_bf16x2(w[e]); m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y))); }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(reinterpret_cast<unsigned int*>(amax), __float_as_uint(m));   // m ≥ 0: bit order = value order
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -352,7 +720,10 @@ using namespace b200;
 // beyond the operand inside the last 128-row chunk are never written by the quantisers).
 extern "C" size_t b200_mxfp8_sf_bytes(int rows, int K) { return static_cast<size_t>((rows + 127) / 128) * (K / 128) * 512; }
 
-extern "C" int b200_mxfp8_quantize(const void* x, int ld, void* q, void* sf, int R, int C, int colwise, cudaStream_t st) {
+// colwise 0: row-wise (q, sf); 1: column-wise, the transposed operand (into q, sf); 2: both from one read of x
+// (row-wise into q, sf and the transposed operand into qT, sfT).
+extern "C" int b200_mxfp8_quantize(const void* x, int ld, void* q, void* sf, int R, int C, int colwise, cudaStream_t st,
+                                   void* qT, void* sfT) {
   if (R <= 0 || C <= 0) return 0;
   if (ld % 8) return -1;
   if (!colwise) {
@@ -360,9 +731,14 @@ extern "C" int b200_mxfp8_quantize(const void* x, int ld, void* q, void* sf, int
     const long long total = static_cast<long long>(R) * (C / 32);
     mxfp8_quant_rowwise_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(
         (const __nv_bfloat16*)x, ld, (uint8_t*)q, (uint8_t*)sf, R, C);
-  } else {
+  } else if (colwise == 1) {
     if (R % 128 || C % 64) return -1;
-    mxfp8_quant_colwise_kernel<<<dim3(C / 64, R / 128), 256, 0, st>>>((const __nv_bfloat16*)x, ld, (uint8_t*)q, (uint8_t*)sf, R, C);
+    mxfp8_quant_colwise_kernel<0><<<dim3(C / 64, R / 128), 256, 0, st>>>((const __nv_bfloat16*)x, ld, (uint8_t*)q, (uint8_t*)sf,
+                                                                         nullptr, nullptr, R, C);
+  } else {
+    if (R % 128 || C % 128 || !qT || !sfT) return -1;
+    mxfp8_quant_colwise_kernel<1><<<dim3(C / 64, R / 128), 256, 0, st>>>((const __nv_bfloat16*)x, ld, (uint8_t*)qT, (uint8_t*)sfT,
+                                                                         (uint8_t*)q, (uint8_t*)sf, R, C);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
@@ -400,6 +776,80 @@ extern "C" int b200_gemm_mxfp8(const void* A, const void* sfa, const void* B, co
       configured[0] = true;
     }
     gemm_mxfp8_kernel<0><<<grid, 192, QSMEM_BYTES, stream>>>(ta, tb, p);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// ---- NVFP4 entry points ---------------------------------------------------------------------------------------------
+// Bytes of the scale buffer of an operand with `rows` rows and K elements per row (one byte per 16 elements, 128-row chunks).
+extern "C" size_t b200_nvfp4_sf_bytes(int rows, int K) { return static_cast<size_t>((rows + 127) / 128) * (K / 64) * 512; }
+
+extern "C" int b200_nvfp4_amax(const void* x, int ld, float* amax, int R, int C, cudaStream_t st) {
+  if (R <= 0 || C <= 0) return 0;
+  if (ld % 8 || C % 8) return -1;
+  const size_t vecs = static_cast<size_t>(R) * (C / 8);
+  const int grid = static_cast<int>(vecs / 256 + 1 < 148 * 8 ? vecs / 256 + 1 : 148 * 8);
+  nvfp4_amax_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, ld, amax, R, C);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// mode 0: row-wise (q, sf); 1: column-wise (qT, sfT); 2: both from one read of x.  amax: device pointer to max |x|.
+extern "C" int b200_nvfp4_quantize(const void* x, int ld, void* q, void* sf, void* qT, void* sfT, const float* amax, int R, int C,
+                                   int mode, cudaStream_t st) {
+  if (R <= 0 || C <= 0) return 0;
+  if (ld % 8) return -1;
+  if (mode == 0) {
+    if (C % 256) return -1;
+    const long long total = static_cast<long long>(R) * (C / 16);
+    nvfp4_quant_rowwise_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(
+        (const __nv_bfloat16*)x, ld, (uint8_t*)q, (uint8_t*)sf, amax, R, C);
+  } else {
+    if (R % 256 || C % 64 || (mode == 2 && C % 256)) return -1;
+    const dim3 grid(C / 64, R / 128);
+    if (mode == 2)
+      nvfp4_quant_colwise_kernel<1><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, ld, (uint8_t*)qT, (uint8_t*)sfT, (uint8_t*)q,
+                                                          (uint8_t*)sf, amax, R, C);
+    else
+      nvfp4_quant_colwise_kernel<0><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, ld, (uint8_t*)qT, (uint8_t*)sfT, nullptr, nullptr,
+                                                          amax, R, C);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// out[M,N] = alpha · scale(amax_a) · scale(amax_b) · A[M,K] · B[N,K]ᵀ with packed e2m1 operands (K elements = K/2 bytes per
+// row; row strides lda, ldb in bytes), chunked E4M3 block scales and the two tensors' largest magnitudes in device memory.
+extern "C" int b200_gemm_nvfp4(const void* A, const void* sfa, const void* B, const void* sfb, const float* amax_a,
+                               const float* amax_b, void* out, int M, int N, int K, int lda, int ldb, int ldc, float alpha,
+                               int out_f32, int accumulate, int num_sms, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % FBK || lda % 16 || ldb % 16 || N % 8) return -1;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return -5;
+    ctx_bound = true;
+  }
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d_u8(&ta, A, K / 2, M, lda, 128, QBM);
+  if (rc) return rc;
+  rc = make_tmap_2d_u8(&tb, B, K / 2, N, ldb, 128, QBN);
+  if (rc) return rc;
+  QGemmParams p{out, (const uint8_t*)sfa, (const uint8_t*)sfb, M, N, K, ldc, alpha, accumulate, status};
+  const int tiles = ((M + QBM - 1) / QBM) * ((N + QBN - 1) / QBN);
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  static bool configured[2] = {false, false};
+  if (out_f32) {
+    if (!configured[1]) {
+      if (cudaFuncSetAttribute(gemm_nvfp4_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, FSMEM_BYTES) != cudaSuccess) return -2;
+      configured[1] = true;
+    }
+    gemm_nvfp4_kernel<1><<<grid, 192, FSMEM_BYTES, stream>>>(ta, tb, p, amax_a, amax_b);
+  } else {
+    if (!configured[0]) {
+      if (cudaFuncSetAttribute(gemm_nvfp4_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, FSMEM_BYTES) != cudaSuccess) return -2;
+      configured[0] = true;
+    }
+    gemm_nvfp4_kernel<0><<<grid, 192, FSMEM_BYTES, stream>>>(ta, tb, p, amax_a, amax_b);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

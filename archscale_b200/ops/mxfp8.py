@@ -83,6 +83,14 @@ def quantize(x: torch.Tensor, colwise: bool = False) -> Tuple[torch.Tensor, torc
     return ext.mxfp8_quantize(x, colwise)
 
 
+def quantize_both(x: torch.Tensor):
+    """x:(R,C) bf16 → ((q, scales) row-wise, (qT, scales) of the transposed operand) from one read of x."""
+    ext = backend.require_extension()
+    backend.count_launch()
+    q, sf, qt, sft = ext.mxfp8_quantize_both(x)
+    return (q, sf), (qt, sft)
+
+
 def gemm(a_q, a_sf, b_q, b_sf, out_f32: bool = False, acc: Optional[torch.Tensor] = None, alpha: float = 1.0):
     """``a_q:(M,K) · b_q:(N,K)ᵀ`` with block scales → (M,N) bf16 / fp32, or ``acc += …`` (fp32)."""
     ext = backend.require_extension()
@@ -123,17 +131,24 @@ def quantize_weight(weight: torch.Tensor, colwise: bool) -> Tuple[torch.Tensor, 
 
 
 class _LinearMXFP8Fn(torch.autograd.Function):
+    """A tensor needed in both orientations is read once: x is quantised row-wise (forward product) and transposed (weight
+    gradient; saved in place of x itself) by one kernel, and so is dy in the backward pass (dgrad and wgrad)."""
+
     @staticmethod
     def forward(ctx, x, weight, bias):
         x2 = x.reshape(-1, x.shape[-1])
         if not x2.is_contiguous():
             x2 = x2.contiguous()
-        xq, xs = quantize(x2)
+        if ctx.needs_input_grad[1]:
+            (xq, xs), xt = quantize_both(x2)
+            ctx.save_for_backward(weight, *xt)
+        else:
+            xq, xs = quantize(x2)
+            ctx.save_for_backward(weight)
         wq, ws = quantize_weight(weight, False)
         y = gemm(xq, xs, wq, ws)
         if bias is not None:
             y = y + bias.to(y.dtype)
-        ctx.save_for_backward(x2, weight)
         ctx.has_bias = bias is not None
         ctx.weight_ref = weight
         ctx.x_shape = x.shape
@@ -141,23 +156,28 @@ class _LinearMXFP8Fn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        x2, weight = ctx.saved_tensors
+        weight, *xt = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         dx = dw = db = None
-        if ctx.needs_input_grad[0]:
-            gq, gs = quantize(dy2)                          # (T, N) blocks along N
+        need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        if need_dx and need_dw:
+            g, gt = quantize_both(dy2)                      # (T, N) blocks along N; dyᵀ: (N, T) blocks along T
+        elif need_dx:
+            g, gt = quantize(dy2), None
+        else:
+            g, gt = None, quantize(dy2, colwise=True)
+        if need_dx:
             wtq, wts = quantize_weight(weight, True)        # Wᵀ: (K, N) blocks along N
-            dx = gemm(gq, gs, wtq, wts).view(ctx.x_shape)
-        if ctx.needs_input_grad[1]:
-            gtq, gts = quantize(dy2, colwise=True)          # dyᵀ: (N, T) blocks along T
-            xtq, xts = quantize(x2, colwise=True)           # xᵀ : (K, T) blocks along T
+            dx = gemm(g[0], g[1], wtq, wts).view(ctx.x_shape)
+        if need_dw:
+            xtq, xts = xt                                   # xᵀ : (K, T) blocks along T
             main_grad = getattr(ctx.weight_ref, "main_grad", None)
             if main_grad is not None:
-                gemm(gtq, gts, xtq, xts, acc=main_grad)
+                gemm(gt[0], gt[1], xtq, xts, acc=main_grad)
             else:
-                dw = gemm(gtq, gts, xtq, xts).to(weight.dtype)
+                dw = gemm(gt[0], gt[1], xtq, xts).to(weight.dtype)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.float().sum(0).to(dy.dtype)
         return dx, dw, db

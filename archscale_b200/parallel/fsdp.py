@@ -631,8 +631,9 @@ class FSDPEngine:
 
     def mark_params_updated(self) -> None:
         """Call after the optimizer changed the master shards."""
-        from archscale_b200.ops import mxfp8
+        from archscale_b200.ops import mxfp8, nvfp4
         mxfp8.invalidate_weight_cache()          # quantised copies of the old weights are void
+        nvfp4.invalidate_weight_cache()
         for g in self.groups():
             g.lp_stale = True
         for u in self.units:
@@ -776,8 +777,9 @@ class FSDPEngine:
         missing = []
         self.reload_states()
         self.master_version = getattr(self, "master_version", 0) + 1      # cached norms of the old weights are void
-        from archscale_b200.ops import mxfp8
+        from archscale_b200.ops import mxfp8, nvfp4
         mxfp8.invalidate_weight_cache()
+        nvfp4.invalidate_weight_cache()
         for g in self.groups():
             for s, lo, hi, slo in g.local_slices():
                 if s.name not in sd:

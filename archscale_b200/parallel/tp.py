@@ -174,7 +174,7 @@ def _to_row_parallel(lin: Linear, tp: int, r: int, group) -> RowParallelLinear:
     new.in_features, new.out_features = sl, out_f
     new.weight = _new_param(lin.weight[:, r * sl:(r + 1) * sl], lin.weight, True, (1, 1))
     new.bias = None if lin.bias is None else _new_param(lin.bias, lin.bias, False)
-    new.mxfp8 = False
+    new.mxfp8 = new.nvfp4 = False
     new.tp_group = group
     return new
 

@@ -215,10 +215,8 @@ def make_plan(*, train_model: Optional[str], train_name: str, depth: int, max_to
     p.data_chunks = 128 if "v2scale" in tc else 8
     if fsdp_save_mem:
         offloading = act_ckpt = True
-    if fp4 and os.environ.get("ARCHSCALE_B200_FP4_AS_MXFP8", "0") != "1":
-        raise NotImplementedError("--fp4 (NVFP4 linears) is not built; --fp8 runs block-scaled MXFP8 linears. "
-                                  "ARCHSCALE_B200_FP4_AS_MXFP8=1 maps --fp4 onto them explicitly.")
-    fp8 = fp8 or fp4
+    # --fp4 selects NVFP4 linears; like the reference (`pretrain.py:250`) it implies the settings --fp8 implies
+    low_precision = fp8 or fp4
     if data_mixture is not None:
         with open(data_mixture) as f:
             p.train_data_config = list(json.load(f).items())
@@ -240,7 +238,7 @@ def make_plan(*, train_model: Optional[str], train_name: str, depth: int, max_to
         base_config = Config.from_name(p.base_model_name)
     except KeyError:
         base_config = None
-    p.use_flce_loss = use_flce if use_flce is not None else (model_config.vocab_size > 100_000 or "validation" in tc or fp8)
+    p.use_flce_loss = use_flce if use_flce is not None else (model_config.vocab_size > 100_000 or "validation" in tc or low_precision)
     name = f"{tc}_{model_name}"
     if ar is not None:
         name += f"_ar{ar}"
@@ -325,7 +323,9 @@ def make_plan(*, train_model: Optional[str], train_name: str, depth: int, max_to
     for key, upd in switches:
         if key in tc:
             ov.update(upd)
-    if fp8:
+    if fp4:
+        ov["nvfp4"] = True
+    elif fp8:
         ov["mxfp8"] = True
     if tp > 1:
         ov["tp_size"] = tp
@@ -364,6 +364,10 @@ class Trainer:
             from archscale_b200.models.layers import apply_mxfp8
             n_fp8 = apply_mxfp8(self.model)
             self.print(f"MXFP8: {n_fp8} linear layers run the block-scaled e4m3 GEMM")
+        if self.config.nvfp4:
+            from archscale_b200.models.layers import apply_nvfp4
+            n_fp4 = apply_nvfp4(self.model)
+            self.print(f"NVFP4: {n_fp4} linear layers run the block-scaled e2m1 GEMM")
         if self.config.tp_size > 1:
             from archscale_b200.parallel import tp as tp_mod
             tp_mod.apply_tensor_parallel(self.model, mesh)

@@ -138,7 +138,7 @@ def run_ours(args) -> None:
     kwargs = dict(train_data_dir="synthetic", train_model=c["train_model"], depth=c["depth"], train_name=c["train_name"],
                   micro_bsz=c["micro_bsz"], ctx_len=c["ctx_len"], total_bsz=(world // max(args.tp, 1)) * c["micro_bsz"] * c["ctx_len"],
                   max_tokens=1e12, use_flce=True, sparsity=c["sparsity"], top_k=c["top_k"],
-                  config_overrides=dict(c["overrides"]), ep=ep, tp=args.tp, fused_comm=args.fused_comm, fp8=args.fp8,
+                  config_overrides=dict(c["overrides"]), ep=ep, tp=args.tp, fused_comm=args.fused_comm, fp8=args.fp8, fp4=args.fp4,
                   act_ckpt=args.act_ckpt, return_trainer=True, quiet=True)
     for k in ("share_expert", "sqrt_gate", "global_aux", "aux_gamma"):
         if k in c:
@@ -249,7 +249,7 @@ def run_ours(args) -> None:
             "metric": "train tokens/sec (whole job; per GPU = value / n_gpus), device-timed, max over ranks",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "mxfp8 linears (bf16 elsewhere)" if args.fp8 else "bf16", "data": "synthetic uniform-random token ids (seed 0), random-init weights",
+            "dtype": "nvfp4 linears (bf16 elsewhere)" if args.fp4 else "mxfp8 linears (bf16 elsewhere)" if args.fp8 else "bf16", "data": "synthetic uniform-random token ids (seed 0), random-init weights",
             "tokens_per_sec_per_gpu": value / world,
             "mfu": flops_step / max(args.tp, 1) / (ms_per_step / 1e3) / 2.25e15,   # per GPU: tp peers share a micro-batch
             "mfu_with_lm_head": flops_step_head / max(args.tp, 1) / (ms_per_step / 1e3) / 2.25e15,
@@ -301,6 +301,7 @@ def main() -> None:
                          "the largest device time to stderr (shares of the step; not part of any reported number)")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (ranks of a tp group share a micro-batch)")
     ap.add_argument("--fp8", action="store_true", help="MXFP8 block-scaled linear layers (dtype is then reported as mxfp8)")
+    ap.add_argument("--fp4", action="store_true", help="NVFP4 block-scaled linear layers (dtype is then reported as nvfp4)")
     ap.add_argument("--fused-comm", dest="fused_comm", action="store_true", default=True,
                     help="peer-memory collectives fused with compute (default on more than one GPU)")
     ap.add_argument("--no-fused-comm", dest="fused_comm", action="store_false", help="NCCL collectives (the baseline path)")

@@ -36,6 +36,8 @@ def test_quantise_kernels_match_reference(R, C):
     assert qt.shape == (C, R)
     assert torch.equal(mxfp8.unchunk_scales_ref(sft, C, R), etr)
     assert torch.equal(qt.view(torch.float8_e4m3fn).float(), qtr.float())
+    (q2, sf2), (qt2, sft2) = mxfp8.quantize_both(x)                 # one read, both orientations
+    assert torch.equal(q2, q) and torch.equal(sf2, sf) and torch.equal(qt2, qt) and torch.equal(sft2, sft)
 
 
 @pytest.mark.gpu

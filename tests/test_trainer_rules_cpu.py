@@ -179,7 +179,7 @@ def test_fused_cross_entropy_module_matches_oracle(reduction):
     assert torch.allclose(logits.grad, ref_in.grad, atol=1e-5)
 
 
-def test_fp4_flag_raises_instead_of_silently_running_fp8():
+def test_fp4_flag_selects_nvfp4_linears_and_not_mxfp8():
     from archscale_b200.train.pretrain import make_plan
     kw = dict(train_model="transformer_gqa4", train_name="scaling_mup_muonh", depth=8, max_tokens=1e6, ctx_len=64, swa_len=None,
               data_mixture=None, fsdp_save_mem=False, save_step=None, base_hps=BaseHyperparameters(), micro_bsz=1,
@@ -187,8 +187,10 @@ def test_fp4_flag_raises_instead_of_silently_running_fp8():
               bramp_ratio=None, aux_style=None, aux_gamma=None, num_extrp=None, offloading=False, act_ckpt=False,
               share_expert=None, global_aux=None, sqrt_gate=None, head_init_std=0.02, ar=None, load_dir=None, world_size=1,
               local_world_size=1)
-    with pytest.raises(NotImplementedError):
-        make_plan(fp4=True, **kw)
+    plan4 = make_plan(fp4=True, **kw)
+    assert plan4.overrides.get("nvfp4") and not plan4.overrides.get("mxfp8")
+    plan8 = make_plan(fp4=False, **{**kw, "fp8": True})
+    assert plan8.overrides.get("mxfp8") and not plan8.overrides.get("nvfp4")
     plan = make_plan(fp4=False, **{**kw, "fsdp_save_mem": True})
     assert plan.cpu_offload and plan.activation_checkpointing      # --fsdp_save_mem switches both on
 
