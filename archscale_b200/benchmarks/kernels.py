@@ -278,8 +278,33 @@ def bench_mxfp8(res: list) -> None:
         print(res[-1], flush=True)
 
 
+def bench_nvfp4(res: list) -> None:
+    """NVFP4 block-scaled GEMM and its quantisers against the MXFP8 and bf16 tcgen05 kernels on the same shapes."""
+    from archscale_b200.ops import mxfp8, nvfp4
+    ext = backend.require_extension()
+    pk = peaks()
+    for (M, N, K, what) in [(32768, 3072, 2048, "fwd qkv d16"), (32768, 11264, 2048, "fwd w1 d16"),
+                            (32768, 2048, 5632, "fwd w3 d16"), (8192, 8192, 8192, "square 8192")]:
+        a, b = torch.randn(M, K, device="cuda").bfloat16(), torch.randn(N, K, device="cuda").bfloat16()
+        qa, qb = nvfp4.quantize(a), nvfp4.quantize(b)
+        ma, mb = mxfp8.quantize(a), mxfp8.quantize(b)
+        t_q = time_ms(lambda: nvfp4.gemm(qa, qb))
+        t_8 = time_ms(lambda: mxfp8.gemm(ma[0], ma[1], mb[0], mb[1]))
+        t_b = time_ms(lambda: ext.gemm_bf16(a, b, 0, torch.bfloat16, None))
+        am = nvfp4.amax(a)
+        t_amax = time_ms(lambda: nvfp4.amax(a))
+        t_row = time_ms(lambda: nvfp4.quantize(a, amax_t=am))
+        t_both = time_ms(lambda: nvfp4.quantize_both(a, amax_t=am))
+        fl = 2.0 * M * N * K
+        res.append({"kernel": "gemm_nvfp4", "case": what, "M": M, "N": N, "K": K, "ms": t_q, "tflops": fl / t_q / 1e9,
+                    "mxfp8_kernel_ms": t_8, "bf16_kernel_ms": t_b, "speedup_vs_bf16_kernel": t_b / t_q,
+                    "frac_of_" + pk["kind"] + "_bf16_peak": fl / t_q / 1e9 / pk["bf16_tflops"],
+                    "amax_ms": t_amax, "quant_rowwise_ms": t_row, "quant_both_orientations_ms": t_both})
+        print(res[-1], flush=True)
+
+
 ALL = {"gemm": bench_gemm, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu, "ce": bench_ce, "rope": bench_rope,
-       "attn": bench_attn, "mamba": bench_mamba, "mxfp8": bench_mxfp8, "gdn": bench_gdn}
+       "attn": bench_attn, "mamba": bench_mamba, "mxfp8": bench_mxfp8, "nvfp4": bench_nvfp4, "gdn": bench_gdn}
 
 
 def main() -> None:

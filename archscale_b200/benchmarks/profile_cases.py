@@ -44,6 +44,13 @@ def case_mxfp8():
     _run(lambda: mxfp8.gemm(aq, asf, bq, bsf))
 
 
+def case_nvfp4():
+    from archscale_b200.ops import nvfp4
+    a, b = torch.randn(8192, 4096, device="cuda").bfloat16(), torch.randn(8192, 4096, device="cuda").bfloat16()
+    qa, qb = nvfp4.quantize(a), nvfp4.quantize(b)
+    _run(lambda: nvfp4.gemm(qa, qb))
+
+
 def _qkv(B=4, T=4096, H=16, G=4, D=128):
     mk = lambda h: torch.randn(B, T, h, D, device="cuda").bfloat16().requires_grad_()
     return mk(H), mk(G), mk(G)
