@@ -215,6 +215,11 @@ class Block(nn.Module):
                 getattr(self, n).reset_parameters()
 
     # -- helpers -------------------------------------------------------------------
+    def _stream_dtype(self, compute_dtype: torch.dtype) -> torch.dtype:
+        """Type of the residual stream: fp32 (``residual_in_fp32``), else the compute dtype — what the reference's bf16 mixed
+        precision amounts to, where ``x = ox + h`` (`lit_gpt/model.py:603`) adds two bf16 tensors."""
+        return torch.float32 if self.config.residual_in_fp32 else compute_dtype
+
     def _norm_in(self, norm, x, compute_dtype):
         """Returns (residual stream ox, mixer input n)."""
         if self.config.post_norm:
@@ -224,7 +229,7 @@ class Block(nn.Module):
             if self.config.skip_gain:
                 ox = ox * norm.weight1
             return ox, n
-        ox = x.to(torch.float32)
+        ox = x.to(self._stream_dtype(compute_dtype))
         return ox, norm(x).to(compute_dtype)
 
     def post_process_residual(self, h, ox, lc, input_embed, residual_dropout: float = 0.0):
@@ -261,7 +266,8 @@ class Block(nn.Module):
         cu_seqlens = seq_meta.get("cu_seqlens") if seq_meta else None
         seq_idx = seq_meta.get("seq_idx") if seq_meta else None
         pad_mask = seq_meta.get("pad_mask") if seq_meta else None
-        x, n_1 = ops.add_rms_norm(x, h_pending, self.norm_1.weight, self.norm_1.eps, scale, compute_dtype)
+        stream = self._stream_dtype(compute_dtype)
+        x, n_1 = ops.add_rms_norm(x, h_pending, self.norm_1.weight, self.norm_1.eps, scale, compute_dtype, stream)
         new_kv_cache = kv_cache
         if self.use_rnn:
             if self.rnn_type in ("mamba", "mamba2"):
@@ -279,7 +285,7 @@ class Block(nn.Module):
                 self.attn_output_rmsnorm = compute_rmsnorm(h) * scale
                 self.attn_outlier_pct = compute_outlier_percentage(h)
                 self.attn_z_mean = getattr(self.attn, "z_mean", None)
-        x, n_2 = ops.add_rms_norm(x, h.to(compute_dtype), self.norm_2.weight, self.norm_2.eps, scale, compute_dtype)
+        x, n_2 = ops.add_rms_norm(x, h.to(compute_dtype), self.norm_2.weight, self.norm_2.eps, scale, compute_dtype, stream)
         if cfg.moe:
             h = self.mlp(n_2)
         else:
@@ -312,7 +318,7 @@ class Block(nn.Module):
             if self.use_skip_proj:
                 ox = self.skip_proj(ox)
         else:
-            ox = ox_src.to(torch.float32)
+            ox = ox_src.to(self._stream_dtype(compute_dtype))
             n_1 = _norm_to(self.norm_1, x, compute_dtype)
         new_kv_cache = kv_cache
         if self.use_rnn:
@@ -342,7 +348,7 @@ class Block(nn.Module):
             if cfg.post_norm:
                 ox, n_2 = self._norm_in(self.norm_2, ox_src, compute_dtype)
             else:
-                ox = ox_src.to(torch.float32)
+                ox = ox_src.to(self._stream_dtype(compute_dtype))
                 n_2 = _norm_to(self.norm_2, x, compute_dtype)
             if cfg.moe:
                 h = self.mlp(n_2)
@@ -542,8 +548,9 @@ class GPT(nn.Module):
             x = input_embed
         if use_deferred:
             scale = 1.0 / math.sqrt(2 * cfg.n_layer) if cfg.depth_scale else 1.0
+            stream = torch.float32 if cfg.residual_in_fp32 else self.compute_dtype
             _, x = ops.add_rms_norm(x, h_pending, self.transformer.ln_f.weight, self.transformer.ln_f.eps, scale,
-                                    self.compute_dtype)
+                                    self.compute_dtype, stream)
         else:
             x = _norm_to(self.transformer.ln_f, x, self.compute_dtype)
         if self.logit_scale != 1.0:

@@ -25,13 +25,16 @@ int b200_rmsnorm_bwd_partials(int rows, int cols);
 int b200_rmsnorm_bwd(const void* dy, int dy_dtype, const void* x, int x_dtype, const void* w, int w_dtype,
                      const float* rstd, void* dx, float* dw_partial, float* dw, int rows, int cols, cudaStream_t stream);
 
-// Fused residual add + RMSNorm: x = res + h_scale·h (fp32, stored to res_out when h != null), n = rmsnorm(x)·w (bf16).
+// Fused residual add + RMSNorm: x = res + h_scale·h (stored to res_out when h != null; out_dtype 0: fp32 stream, 1: bf16 stream,
+// which needs bf16 res), n = rmsnorm(x)·w (bf16).
 int b200_add_rmsnorm_fwd(const void* res, int res_dtype, const void* h, float h_scale, const void* w, int w_dtype,
-                         float* res_out, void* n_out, float* rstd, int rows, int cols, float eps, cudaStream_t stream);
-// d_res = g_res + rmsnorm_bwd(g_n) (fp32), d_h = bf16(h_scale·d_res) (optional); cols ∈ {1024,2048,2560,3072,4096}.
-int b200_add_rmsnorm_bwd(const float* g_res, const void* g_n, const void* x, int x_dtype, const void* w, int w_dtype,
-                         const float* rstd, float* d_res, void* d_h, float h_scale, float* dw_partial, float* dw,
-                         int rows, int cols, cudaStream_t stream);
+                         void* res_out, void* n_out, float* rstd, int rows, int cols, float eps, cudaStream_t stream,
+                         int out_dtype = 0);
+// d_res = g_res + rmsnorm_bwd(g_n), d_h = bf16(h_scale·d_res) (optional); g_dtype: type of g_res and d_res (0 fp32, 1 bf16 with bf16 x);
+// cols: a multiple of 8 up to 4096.
+int b200_add_rmsnorm_bwd(const void* g_res, const void* g_n, const void* x, int x_dtype, const void* w, int w_dtype,
+                         const float* rstd, void* d_res, void* d_h, float h_scale, float* dw_partial, float* dw,
+                         int rows, int cols, cudaStream_t stream, int g_dtype = 0);
 
 // SwiGLU: y = silu(g)·u.  Packed variant reads g = x[:, :I], u = x[:, I:] from a [rows, 2I] bf16 tensor.
 int b200_swiglu_fwd(const void* g, const void* u, void* y, int64_t n, cudaStream_t stream);

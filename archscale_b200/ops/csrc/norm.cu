@@ -128,13 +128,14 @@ __global__ void __launch_bounds__(1024) reduce_partials_kernel(const float* __re
 
 // ---------------------------------------------------------------------------------------------
 // Fused residual-add + RMSNorm (pre-norm transformer block):
-//   x = res + h_scale·h  (fp32, written back as the new residual stream)   n = rmsnorm(x)·w  (bf16)
+//   x = res + h_scale·h  (written back as the new residual stream, fp32 or bf16)   n = rmsnorm(x)·w  (bf16)
+// With a bf16 stream the sum is rounded to bf16 before it is normalised, so that forward and backward see the same x.
 // Backward in one pass: d_res = g_res + rmsnorm_bwd(g_n),  d_h = bf16(h_scale·d_res); the weight
 // gradient is accumulated in registers (a lane owns columns lane·8 + 256·i), then per CTA in shared
 // memory, then written as per-CTA partials.
-template <typename TRES, typename TW, bool HAS_H>
+template <typename TRES, typename TW, bool HAS_H, typename TOUT = float>
 __global__ void __launch_bounds__(256) add_rmsnorm_fwd_kernel(const TRES* __restrict__ res, const __nv_bfloat16* __restrict__ h,
-                                                              float h_scale, const TW* __restrict__ w, float* __restrict__ res_out,
+                                                              float h_scale, const TW* __restrict__ w, TOUT* __restrict__ res_out,
                                                               __nv_bfloat16* __restrict__ n_out, float* __restrict__ rstd_out,
                                                               int rows, int cols, float eps) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -148,7 +149,8 @@ __global__ void __launch_bounds__(256) add_rmsnorm_fwd_kernel(const TRES* __rest
       float hv[8]; Vec8<__nv_bfloat16>::load(h + base + c, hv);
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[i] += h_scale * hv[i];
-      Vec8<float>::store(res_out + base + c, v);
+      Vec8<TOUT>::store(res_out + base + c, v);
+      if (sizeof(TOUT) == 2) Vec8<TOUT>::load(res_out + base + c, v);      // the rounded values (L1 hit)
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
@@ -158,7 +160,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_fwd_kernel(const TRES* __rest
   if (lane == 0) rstd_out[row] = rstd;
   for (int c = lane * 8; c < cols; c += 256) {
     float v[8];
-    if (HAS_H) Vec8<float>::load(res_out + base + c, v);   // just written by this lane (L1 hit)
+    if (HAS_H) Vec8<TOUT>::load(res_out + base + c, v);   // just written by this lane (L1 hit)
     else Vec8<TRES>::load(res + base + c, v);
     float g[8]; Vec8<TW>::load(w + c, g);
 #pragma unroll
@@ -170,10 +172,11 @@ __global__ void __launch_bounds__(256) add_rmsnorm_fwd_kernel(const TRES* __rest
 // cols ≤ NCH·256, a multiple of 8: a lane owns the 8-element vectors at columns lane·8 + i·256 (i < NCH) that lie inside the
 // row; widths that are not a multiple of 256 (1984, 1536, …) leave the last chunk partly or wholly empty.
 // FULL: cols == NCH·256, no bounds checks (they cost the common widths ≈ 40 % when left in).
-template <typename TX, typename TW, int NCH, bool FULL>
-__global__ void __launch_bounds__(256) add_rmsnorm_bwd_kernel(const float* __restrict__ g_res, const __nv_bfloat16* __restrict__ g_n,
+// TG: type of the residual-stream gradient in and out (fp32, or bf16 for a bf16 stream).
+template <typename TX, typename TW, int NCH, bool FULL, typename TG = float>
+__global__ void __launch_bounds__(256) add_rmsnorm_bwd_kernel(const TG* __restrict__ g_res, const __nv_bfloat16* __restrict__ g_n,
                                                               const TX* __restrict__ x, const TW* __restrict__ w,
-                                                              const float* __restrict__ rstd, float* __restrict__ d_res,
+                                                              const float* __restrict__ rstd, TG* __restrict__ d_res,
                                                               __nv_bfloat16* __restrict__ d_h, float h_scale,
                                                               float* __restrict__ dw_partial, int rows, int cols) {
   extern __shared__ float dw_s[];
@@ -223,12 +226,12 @@ __global__ void __launch_bounds__(256) add_rmsnorm_bwd_kernel(const float* __res
         dwacc[i][e] += valid ? dv[e] * xv[e] * rs : 0.f;
       }
       if (g_res) {
-        float gr[8]; Vec8<float>::load(g_res + base + cl, gr);
+        float gr[8]; Vec8<TG>::load(g_res + base + cl, gr);
 #pragma unroll
         for (int e = 0; e < 8; ++e) o[e] += gr[e];
       }
       if (valid) {
-        if (d_res) Vec8<float>::store(d_res + base + c, o);
+        if (d_res) Vec8<TG>::store(d_res + base + c, o);
         if (d_h) {
 #pragma unroll
           for (int e = 0; e < 8; ++e) o[e] *= h_scale;
@@ -282,9 +285,9 @@ extern "C" int b200_rmsnorm_bwd_partials(int rows, int cols) {
   return need < kBwdCtas ? need : kBwdCtas;
 }
 
-extern "C" int b200_add_rmsnorm_bwd(const float* g_res, const void* g_n, const void* x, int x_dtype, const void* w, int w_dtype,
-                                    const float* rstd, float* d_res, void* d_h, float h_scale, float* dw_partial, float* dw,
-                                    int rows, int cols, cudaStream_t stream);
+extern "C" int b200_add_rmsnorm_bwd(const void* g_res, const void* g_n, const void* x, int x_dtype, const void* w, int w_dtype,
+                                    const float* rstd, void* d_res, void* d_h, float h_scale, float* dw_partial, float* dw,
+                                    int rows, int cols, cudaStream_t stream, int g_dtype);
 
 extern "C" int b200_rmsnorm_bwd(const void* dy, int dy_dtype, const void* x, int x_dtype, const void* w, int w_dtype,
                                 const float* rstd, void* dx, float* dw_partial, float* dw, int rows, int cols,
@@ -295,8 +298,8 @@ extern "C" int b200_rmsnorm_bwd(const void* dy, int dy_dtype, const void* x, int
   // gradient accumulated in registers, one shared-memory add per column and CTA instead of one per element) does this job
   // with no residual gradient: dx is its bf16 output for bf16 x, its fp32 output for fp32 x
   if (dy_dtype == 1 && w && cols >= 512 && cols <= 4096)
-    return b200_add_rmsnorm_bwd(nullptr, dy, x, x_dtype, w, w_dtype, rstd, x_dtype == 0 ? static_cast<float*>(dx) : nullptr,
-                                x_dtype == 1 ? dx : nullptr, 1.f, dw_partial, dw, rows, cols, stream);
+    return b200_add_rmsnorm_bwd(nullptr, dy, x, x_dtype, w, w_dtype, rstd, x_dtype == 0 ? dx : nullptr,
+                                x_dtype == 1 ? dx : nullptr, 1.f, dw_partial, dw, rows, cols, stream, 0);
   const int grid = b200_rmsnorm_bwd_partials(rows, cols);
   const size_t smem = w ? sizeof(float) * cols : 0;
 #define CALL(TDY, TW, TX)                                                                                     \
@@ -312,16 +315,28 @@ extern "C" int b200_rmsnorm_bwd(const void* dy, int dy_dtype, const void* x, int
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
+// out_dtype: type of the new residual stream res_out (0 fp32, 1 bf16; a bf16 stream needs bf16 res).
 extern "C" int b200_add_rmsnorm_fwd(const void* res, int res_dtype, const void* h, float h_scale, const void* w, int w_dtype,
-                                    float* res_out, void* n_out, float* rstd, int rows, int cols, float eps,
-                                    cudaStream_t stream) {
+                                    void* res_out, void* n_out, float* rstd, int rows, int cols, float eps,
+                                    cudaStream_t stream, int out_dtype) {
   if (rows == 0) return 0;
   if (cols % 8) return -1;
   const int grid = (rows + 7) / 8;
   typedef __nv_bfloat16 bf;
+  if (out_dtype == 1) {
+    if (res_dtype != 1) return -1;
+#define LB(TW, HH)                                                                                                    \
+  add_rmsnorm_fwd_kernel<bf, TW, HH, bf><<<grid, 256, 0, stream>>>(static_cast<const bf*>(res), static_cast<const bf*>(h), \
+                                                                   h_scale, static_cast<const TW*>(w), static_cast<bf*>(res_out), \
+                                                                   static_cast<bf*>(n_out), rstd, rows, cols, eps)
+    if (h) { if (w_dtype == 0) LB(float, true); else LB(bf, true); }
+    else { if (w_dtype == 0) LB(float, false); else LB(bf, false); }
+#undef LB
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  }
 #define L(TRES, TW, HH)                                                                                              \
   add_rmsnorm_fwd_kernel<TRES, TW, HH><<<grid, 256, 0, stream>>>(static_cast<const TRES*>(res), static_cast<const bf*>(h), \
-                                                                 h_scale, static_cast<const TW*>(w), res_out,         \
+                                                                 h_scale, static_cast<const TW*>(w), static_cast<float*>(res_out), \
                                                                  static_cast<bf*>(n_out), rstd, rows, cols, eps)
   if (h) {
     if (res_dtype == 0 && w_dtype == 0) L(float, float, true);
@@ -338,30 +353,34 @@ extern "C" int b200_add_rmsnorm_fwd(const void* res, int res_dtype, const void* 
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-// cols must be one of 1024, 2048, 2560, 3072, 4096 (register-resident dw accumulators); returns -2 otherwise.
-extern "C" int b200_add_rmsnorm_bwd(const float* g_res, const void* g_n, const void* x, int x_dtype, const void* w, int w_dtype,
-                                    const float* rstd, float* d_res, void* d_h, float h_scale, float* dw_partial, float* dw,
-                                    int rows, int cols, cudaStream_t stream) {
+// cols: a multiple of 8 up to 4096 (register-resident dw accumulators); returns -2 otherwise.
+// g_dtype: type of g_res and d_res (0 fp32, 1 bf16; bf16 gradients need bf16 x).
+extern "C" int b200_add_rmsnorm_bwd(const void* g_res, const void* g_n, const void* x, int x_dtype, const void* w, int w_dtype,
+                                    const float* rstd, void* d_res, void* d_h, float h_scale, float* dw_partial, float* dw,
+                                    int rows, int cols, cudaStream_t stream, int g_dtype) {
   if (rows == 0) return 0;
+  if (g_dtype == 1 && x_dtype != 1) return -1;
   const int grid = b200_rmsnorm_bwd_partials(rows, cols);
   const size_t smem = sizeof(float) * cols;
   typedef __nv_bfloat16 bf;
-#define L(TX, TW, NCH)                                                                                                 \
+#define L(TX, TW, NCH, TG)                                                                                             \
   do {                                                                                                                 \
     if (cols == NCH * 256)                                                                                             \
-      add_rmsnorm_bwd_kernel<TX, TW, NCH, true><<<grid, 256, smem, stream>>>(g_res, static_cast<const bf*>(g_n), static_cast<const TX*>(x), \
-                                                                         static_cast<const TW*>(w), rstd, d_res, static_cast<bf*>(d_h), \
-                                                                         h_scale, dw_partial, rows, cols);             \
+      add_rmsnorm_bwd_kernel<TX, TW, NCH, true, TG><<<grid, 256, smem, stream>>>(                                      \
+          static_cast<const TG*>(g_res), static_cast<const bf*>(g_n), static_cast<const TX*>(x), static_cast<const TW*>(w), rstd, \
+          static_cast<TG*>(d_res), static_cast<bf*>(d_h), h_scale, dw_partial, rows, cols);                            \
     else                                                                                                               \
-      add_rmsnorm_bwd_kernel<TX, TW, NCH, false><<<grid, 256, smem, stream>>>(g_res, static_cast<const bf*>(g_n), static_cast<const TX*>(x), \
-                                                                          static_cast<const TW*>(w), rstd, d_res, static_cast<bf*>(d_h), \
-                                                                          h_scale, dw_partial, rows, cols);            \
+      add_rmsnorm_bwd_kernel<TX, TW, NCH, false, TG><<<grid, 256, smem, stream>>>(                                     \
+          static_cast<const TG*>(g_res), static_cast<const bf*>(g_n), static_cast<const TX*>(x), static_cast<const TW*>(w), rstd, \
+          static_cast<TG*>(d_res), static_cast<bf*>(d_h), h_scale, dw_partial, rows, cols);                            \
   } while (0)
-#define LN(NCH)                                                  \
-  if (x_dtype == 0 && w_dtype == 0) L(float, float, NCH);        \
-  else if (x_dtype == 0 && w_dtype == 1) L(float, bf, NCH);      \
-  else if (x_dtype == 1 && w_dtype == 0) L(bf, float, NCH);      \
-  else L(bf, bf, NCH);
+#define LN(NCH)                                                         \
+  if (g_dtype == 1 && w_dtype == 0) L(bf, float, NCH, bf);              \
+  else if (g_dtype == 1) L(bf, bf, NCH, bf);                            \
+  else if (x_dtype == 0 && w_dtype == 0) L(float, float, NCH, float);   \
+  else if (x_dtype == 0 && w_dtype == 1) L(float, bf, NCH, float);      \
+  else if (x_dtype == 1 && w_dtype == 0) L(bf, float, NCH, float);      \
+  else L(bf, bf, NCH, float);
   // the instantiation with the fewest 256-column chunks that covers the row (the kernel skips what lies beyond `cols`)
   if (cols % 8 || cols > 4096) return -2;
   if (cols <= 1024) { LN(4) }

@@ -171,25 +171,27 @@ def gated_rms_norm(x, weight, z=None, eps: float = 1e-5, group_size: Optional[in
 
 # ------------------------------------------------------------------ fused residual add + RMSNorm
 def add_rms_norm_ref(res: torch.Tensor, h: Optional[torch.Tensor], weight: torch.Tensor, eps: float = 1e-5,
-                     h_scale: float = 1.0, out_dtype: torch.dtype = torch.bfloat16):
-    """x = res + h_scale·h in fp32; returns (x fp32, rmsnorm(x)·w in ``out_dtype``)."""
+                     h_scale: float = 1.0, out_dtype: torch.dtype = torch.bfloat16,
+                     stream_dtype: torch.dtype = torch.float32):
+    """x = res + h_scale·h computed in fp32 and kept in ``stream_dtype``; returns (x, rmsnorm(x)·w in ``out_dtype``)."""
     x = res.float()
     if h is not None:
         x = x + h_scale * h.float()
+    x = x.to(stream_dtype)
     return x, rms_norm_ref(x, weight, eps).to(out_dtype)
 
 
 class _AddRMSNormFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, res, h, weight, eps, h_scale):
+    def forward(ctx, res, h, weight, eps, h_scale, bf16_stream):
         ext = backend.require_extension()
         shape = res.shape
         res2 = res.reshape(-1, shape[-1])
         h2 = h.reshape(-1, shape[-1]) if h is not None else None
-        x, n, rstd = ext.add_rmsnorm_fwd(res2, h2, h_scale, weight, eps)
+        x, n, rstd = ext.add_rmsnorm_fwd(res2, h2, h_scale, weight, eps, bf16_stream)
         backend.count_launch()
         ctx.save_for_backward(x, weight, rstd)
-        ctx.shape, ctx.h_scale, ctx.has_h, ctx.res_dtype = shape, h_scale, h is not None, res.dtype
+        ctx.shape, ctx.h_scale, ctx.has_h, ctx.res_dtype, ctx.bf16_stream = shape, h_scale, h is not None, res.dtype, bf16_stream
         return x.view(shape), n.view(shape)
 
     @staticmethod
@@ -202,16 +204,17 @@ class _AddRMSNormFn(torch.autograd.Function):
         g_n2 = g_n.reshape(-1, C)
         if not g_n2.is_contiguous():
             g_n2 = g_n2.contiguous()
+        g_dtype = torch.bfloat16 if ctx.bf16_stream else torch.float32
         g_x2 = None
         if g_x is not None:
             g_x2 = g_x.reshape(-1, C)
-            if g_x2.dtype != torch.float32 or not g_x2.is_contiguous():
-                g_x2 = g_x2.float().contiguous()
-        d_res, d_h, dw = ext.add_rmsnorm_bwd(g_x2, g_n2, x, weight, rstd, ctx.has_h, ctx.h_scale)
+            if g_x2.dtype != g_dtype or not g_x2.is_contiguous():
+                g_x2 = g_x2.to(g_dtype).contiguous()
+        d_res, d_h, dw = ext.add_rmsnorm_bwd(g_x2, g_n2, x, weight, rstd, ctx.has_h, ctx.h_scale, ctx.bf16_stream)
         backend.count_launch(2)
-        if ctx.res_dtype != torch.float32:
+        if ctx.res_dtype != d_res.dtype:
             d_res = d_res.to(ctx.res_dtype)
-        return d_res.view(ctx.shape), (d_h.view(ctx.shape) if ctx.has_h else None), dw.to(weight.dtype), None, None
+        return d_res.view(ctx.shape), (d_h.view(ctx.shape) if ctx.has_h else None), dw.to(weight.dtype), None, None, None
 
 
 def fused_cols_ok(cols: int) -> bool:
@@ -221,13 +224,15 @@ def fused_cols_ok(cols: int) -> bool:
 
 
 def add_rms_norm(res: torch.Tensor, h: Optional[torch.Tensor], weight: torch.Tensor, eps: float = 1e-5,
-                 h_scale: float = 1.0, out_dtype: torch.dtype = torch.bfloat16):
-    """Pre-norm block entry: ``x = res + h_scale·h`` (new fp32 residual stream) and ``rmsnorm(x)·w``.
+                 h_scale: float = 1.0, out_dtype: torch.dtype = torch.bfloat16, stream_dtype: torch.dtype = torch.float32):
+    """Pre-norm block entry: ``x = res + h_scale·h`` (the new residual stream, in ``stream_dtype``: fp32, or bf16 as the
+    reference's bf16 mixed precision keeps it) and ``rmsnorm(x)·w``.
 
     One kernel forward; backward fuses the residual-gradient add, the RMSNorm backward and the bf16
     cast of the branch gradient."""
+    bf16_stream = stream_dtype == torch.bfloat16 and res.dtype == torch.bfloat16
     if (fused_cols_ok(res.shape[-1]) and out_dtype == torch.bfloat16 and res.dtype in (torch.float32, torch.bfloat16)
             and (h is None or h.dtype == torch.bfloat16) and backend.has("add_rmsnorm_fwd")
             and backend.use_cuda_kernel("add_rmsnorm", res, h, weight)):
-        return _AddRMSNormFn.apply(res.contiguous(), None if h is None else h.contiguous(), weight, eps, h_scale)
-    return add_rms_norm_ref(res, h, weight, eps, h_scale, out_dtype)
+        return _AddRMSNormFn.apply(res.contiguous(), None if h is None else h.contiguous(), weight, eps, h_scale, bf16_stream)
+    return add_rms_norm_ref(res, h, weight, eps, h_scale, out_dtype, stream_dtype)

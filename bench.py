@@ -135,10 +135,22 @@ def run_ours(args) -> None:
     c = CONFIGS[args.config]
     os.environ.setdefault("LIGHTNING_ARTIFACTS_DIR", os.path.join(tempfile.gettempdir(), "archscale_b200_bench"))
     ep = world if (args.config == "moe" and world > 1 and not args.no_ep) else 1
+    overrides = dict(c["overrides"])
+    for item in args.cfg:
+        key, _, val = item.partition("=")
+        overrides[key] = {"true": True, "false": False}.get(val.lower(), None)
+        if overrides[key] is None:
+            try:
+                overrides[key] = int(val)
+            except ValueError:
+                try:
+                    overrides[key] = float(val)
+                except ValueError:
+                    overrides[key] = val
     kwargs = dict(train_data_dir="synthetic", train_model=c["train_model"], depth=c["depth"], train_name=c["train_name"],
                   micro_bsz=c["micro_bsz"], ctx_len=c["ctx_len"], total_bsz=(world // max(args.tp, 1)) * c["micro_bsz"] * c["ctx_len"],
                   max_tokens=1e12, use_flce=True, sparsity=c["sparsity"], top_k=c["top_k"],
-                  config_overrides=dict(c["overrides"]), ep=ep, tp=args.tp, fused_comm=args.fused_comm, fp8=args.fp8, fp4=args.fp4,
+                  config_overrides=overrides, ep=ep, tp=args.tp, fused_comm=args.fused_comm, fp8=args.fp8, fp4=args.fp4,
                   act_ckpt=args.act_ckpt, return_trainer=True, quiet=True)
     for k in ("share_expert", "sqrt_gate", "global_aux", "aux_gamma"):
         if k in c:
@@ -257,6 +269,7 @@ def run_ours(args) -> None:
             "mfu_note": f"N = {n_flops:,.0f} non-embedding parameters of the shape that ran ({n_flops_head:,.0f} with lm_head); "
                         f"sustained bf16 peak {pk['bf16_tflops_sustained']:.0f} TFLOP/s ({pk['kind']})",
             "config": {"model": c["name"], "global_batch": world * mb, "seq_len": T,
+                       "residual_stream": "fp32" if cfg.residual_in_fp32 else "bf16",
                        "parallelism": (f"fsdp{world // max(args.tp, 1)}" if world > 1 else "single") + (f"+ep{ep}" if ep > 1 else "")
                                       + (f"+tp{args.tp}" if args.tp > 1 else ""),
                        "optimizer": "MuonH (Newton-Schulz 5) + AdamW/Adam-H, grad clip 1.0",
@@ -306,6 +319,8 @@ def main() -> None:
                     help="peer-memory collectives fused with compute (default on more than one GPU)")
     ap.add_argument("--no-fused-comm", dest="fused_comm", action="store_false", help="NCCL collectives (the baseline path)")
     ap.add_argument("--no-ep", dest="no_ep", action="store_true")
+    ap.add_argument("--cfg", action="append", default=[], metavar="FIELD=VALUE",
+                    help="override a Config field of the benchmarked model (repeatable), e.g. --cfg residual_in_fp32=false")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

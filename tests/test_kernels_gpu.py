@@ -204,6 +204,29 @@ def test_add_rms_norm_fused(cols, res_dtype):
     assert _rel(n2, ops.rms_norm_ref(res.detach().float(), w.detach(), 1e-5)) < 1e-2
 
 
+@pytest.mark.parametrize("cols", [1024, 2048, 1984])
+def test_add_rms_norm_fused_bf16_stream(cols):
+    """Residual stream kept in bf16: x is the bf16-rounded sum, the norm and every gradient follow from that x."""
+    torch.manual_seed(11)
+    rows = 517
+    res = torch.randn(rows, cols, device="cuda").bfloat16().requires_grad_()
+    h = torch.randn(rows, cols, device="cuda").bfloat16().requires_grad_()
+    w = (1 + 0.1 * torch.randn(cols, device="cuda")).requires_grad_()
+    x, n = ops.add_rms_norm(res, h, w, 1e-5, 0.25, stream_dtype=torch.bfloat16)
+    assert x.dtype == torch.bfloat16 and n.dtype == torch.bfloat16
+    gx, gn = torch.randn_like(x), torch.randn_like(n)
+    torch.autograd.backward((x, n), (gx, gn))
+    assert res.grad.dtype == torch.bfloat16
+    rr, hr, wr = (t.detach().float().requires_grad_() for t in (res, h, w))
+    xr, nr = ops.add_rms_norm_ref(rr, hr, wr, 1e-5, 0.25, torch.float32, torch.float32)
+    torch.autograd.backward((xr, nr), (gx.float(), gn.float()))
+    assert torch.equal(x, xr.bfloat16())                          # the stream is the rounded fp32 sum
+    assert _rel(n, nr) < 1e-2
+    assert _rel(res.grad, rr.grad) < 1e-2 and _rel(h.grad, hr.grad) < 1e-2 and _rel(w.grad, wr.grad) < 1e-2
+    x2, n2 = ops.add_rms_norm(res.detach(), None, w.detach(), 1e-5, 1.0, stream_dtype=torch.bfloat16)
+    assert x2.dtype == torch.bfloat16 and _rel(n2, ops.rms_norm_ref(res.detach().float(), w.detach(), 1e-5)) < 1e-2
+
+
 def test_model_deferred_residual_matches_generic_path():
     """The fused (deferred residual) block path and the generic module path give the same loss/grads."""
     from archscale_b200 import Config
