@@ -273,10 +273,8 @@ class AttentionExperts(nn.Module):
         tok = order // K
         counts = torch.bincount(flat, minlength=E)
         bounds = [0] + torch.cumsum(counts, 0).tolist()
-        # one packed document per (expert, sequence): consecutive pairs with the same key
-        key = flat[order] * B + tok // T
-        _, seg_len = torch.unique_consecutive(key, return_counts=True)
-        cu = F.pad(torch.cumsum(seg_len, 0), (1, 0)).to(torch.int32)
+        # one packed document per (expert, sequence)
+        cu, _ = ops.moe.segment_cu_seqlens(tok // T, counts)
         qkv = self._grouped_linear(h[tok], self.mods_in, bounds)
         gate_dim = self.n_head * hs if self.config.gated_attn else 0
         if gate_dim:

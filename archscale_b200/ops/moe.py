@@ -135,6 +135,25 @@ def moe_ffn(x, w_in, w_out, scores, indices, b_in=None, b_out=None, shared=None,
     return out if alpha == 1.0 else out * alpha
 
 
+def segment_cu_seqlens(sorted_sequence_ids: torch.Tensor, tokens_per_expert: torch.Tensor):
+    """Packed-attention segments of expert-sorted tokens: a new segment starts where the expert or the sequence id changes, so
+    that an attention expert never attends across sequences (or into another expert's rows).  Returns (cu_seqlens int32
+    [n_seg + 1], segment lengths int32 [n_seg]).  Same contract as the helper the reference pins in
+    `tests/test_build_segment_cu_seqlen.py:4-48`; here one run-length pass over the combined (expert, sequence) key."""
+    n = sorted_sequence_ids.numel()
+    dev = sorted_sequence_ids.device
+    if n == 0:
+        return torch.zeros(1, dtype=torch.int32, device=dev), torch.empty(0, dtype=torch.int32, device=dev)
+    seq = sorted_sequence_ids.reshape(-1).long()
+    counts = tokens_per_expert.reshape(-1).long()
+    expert = torch.repeat_interleave(torch.arange(counts.numel(), device=dev), counts, output_size=n) if counts.numel() \
+        else torch.zeros(n, dtype=torch.long, device=dev)
+    key = expert * (int(seq.max()) + 1) + seq
+    _, lengths = torch.unique_consecutive(key, return_counts=True)
+    cu = F.pad(torch.cumsum(lengths, 0), (1, 0)).to(torch.int32)
+    return cu, lengths.to(torch.int32)
+
+
 # ------------------------------------------------------------------ aux loss
 class _DiffAllReduceSum(torch.autograd.Function):
     """all-reduce(SUM) whose backward is another all-reduce(SUM) (torch.distributed.nn semantics)."""

@@ -126,3 +126,19 @@ def test_differential_attention_one_call_equals_four_calls():
     lam = (torch.exp((da.lambda_q1 * da.lambda_k1).sum()) - torch.exp((da.lambda_q2 * da.lambda_k2).sum()) + da.lambda_init)
     ref = diff_combine_ref(a1, a2, lam, da.subln.weight, 1 - da.lambda_init, 1e-5).reshape(B, T, H, D)
     assert torch.allclose(out, ref, atol=1e-5, rtol=1e-5)
+
+
+def test_segment_cu_seqlens_respects_sequence_and_expert_boundaries():
+    """Inputs of the reference's `tests/test_build_segment_cu_seqlen.py:50-71`.  A boundary at every change of expert or of
+    sequence id (the contract its helper states and implements, `:4-48`) gives four segments for the first input; the vector
+    pinned there ([0, 2, 3, 5]) would let the token of sequence 2 attend to sequence 1 inside the second expert."""
+    import torch
+    from archscale_b200.ops.moe import segment_cu_seqlens
+    cu, lens = segment_cu_seqlens(torch.tensor([0, 0, 1, 1, 2], dtype=torch.int32), torch.tensor([3, 2], dtype=torch.int32))
+    assert cu.dtype == torch.int32 and lens.dtype == torch.int32
+    assert cu.tolist() == [0, 2, 3, 4, 5] and lens.tolist() == [2, 1, 1, 1]
+    cu, lens = segment_cu_seqlens(torch.empty(0, dtype=torch.int32), torch.empty(0, dtype=torch.int32))
+    assert cu.tolist() == [0] and lens.numel() == 0 and cu.dtype == torch.int32 and lens.dtype == torch.int32
+    # the same sequence id on both sides of an expert boundary still splits
+    cu, lens = segment_cu_seqlens(torch.tensor([4, 4, 4, 4]), torch.tensor([1, 0, 3]))
+    assert cu.tolist() == [0, 1, 4]
