@@ -220,6 +220,7 @@ class CausalSelfAttention(nn.Module):
                 y = ops.glu(g, y)
             return self.proj(y.reshape(B, T, -1)), kv_cache, gmu_mems
 
+        fused_qkv = False
         if cfg.separate_qkv:
             q, k, v = ops.gemm.linear_multi(x, (self.q_proj, self.k_proj, self.v_proj))
             if cfg.gated_attn:
@@ -231,7 +232,15 @@ class CausalSelfAttention(nn.Module):
                 g = g.reshape(B, T, H, 1)
             q_per_kv = H // G
             qkv = qkv.view(B, T, G, q_per_kv + 2, hs)
-            q, k, v = qkv.split((q_per_kv, 1, 1), dim=-2)
+            use_rope = not cfg.nope and not (cfg.yoco_nope and self.win_tuple == (-1, -1))
+            cos, sin = rope if use_rope else (None, None)
+            if not self.sc and ops.qkv_norm_rope_supported(qkv, cos, self.q_norm.weight if self.qk_norm else None):
+                # norm + rotation read the heads in place from the per-group layout and deliver dense q, k, v in one launch
+                q, k, v = ops.qkv_norm_rope(qkv, self.q_norm.weight if self.qk_norm else None,
+                                            self.k_norm.weight if self.qk_norm else None, cos, sin, cfg.norm_eps)
+                fused_qkv = True
+            else:
+                q, k, v = qkv.split((q_per_kv, 1, 1), dim=-2)
         if self.sc:
             conv = lambda t, m: ops.causal_conv1d(t.reshape(B, T, -1), m.weight.squeeze(1), m.bias,
                                                   activation="silu", channel_last=True)
@@ -241,7 +250,7 @@ class CausalSelfAttention(nn.Module):
         v = v.reshape(B, T, -1, hs)
         use_rope = not cfg.nope and not (cfg.yoco_nope and self.win_tuple == (-1, -1))
         cos, sin = rope if use_rope else (None, None)
-        if self.qk_norm or use_rope:
+        if not fused_qkv and (self.qk_norm or use_rope):
             q, k = ops.qk_norm_rope(q, k, self.q_norm.weight if self.qk_norm else None,
                                     self.k_norm.weight if self.qk_norm else None, cos, sin, cfg.norm_eps)
         kv_cache = (k, v)

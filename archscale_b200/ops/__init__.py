@@ -11,7 +11,7 @@ from .moe import (load_balance_loss, moe_ffn, moe_ffn_ref, router_topk_softmax, 
                   stable_topk)
 from .newton_schulz import newton_schulz, newton_schulz_ref  # noqa: F401
 from .norm import add_rms_norm, add_rms_norm_ref, gated_rms_norm, layer_norm, rms_norm, rms_norm_ref, layer_norm_ref, gated_rms_norm_ref  # noqa: F401
-from .rope import apply_rotary_emb, build_rope_cache, qk_norm_rope  # noqa: F401
+from .rope import apply_rotary_emb, build_rope_cache, qk_norm_rope, qkv_norm_rope, qkv_norm_rope_supported  # noqa: F401
 from .selective_scan import selective_scan, selective_scan_ref  # noqa: F401
 from .ssd import ssd_scan, ssd_scan_ref  # noqa: F401
 from .diff_attn import diff_combine, diff_combine_ref  # noqa: F401,E402

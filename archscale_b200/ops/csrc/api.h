@@ -56,6 +56,20 @@ int b200_qknorm_rope_bwd(const void* dqo, const void* dko, const void* q, const 
                          void* dq, void* dk, float* dqw, float* dkw, float* dw_partial /* [grid, 2, D] */,
                          int64_t n_tokens, int T, int H, int G, int D, int64_t q_token_stride, int64_t k_token_stride,
                          cudaStream_t stream);
+// The same on heads addressed through a group layout: query head h of a token sits at (h / q_hpg)·q_gs + (h % q_hpg)·D from the
+// token's query base, key (value) head g at g·k_gs from its base.  Dense rows: q_hpg = H, k_gs = D.  The per-group interleaved
+// output of a fused QKV projection: q_hpg = q_per_kv, q_gs = k_gs = (q_per_kv + 2)·D.  Forward can also copy the value heads to
+// dense rows (v, vo); backward writes dq / dk in a layout of its own (o_*) and can copy a dense dv into that layout (dvo, dv_dst),
+// so the gradient of the fused projection is assembled without a concatenation.
+int b200_qknorm_rope_fwd_ex(const void* q, const void* k, const void* v, const void* qw, const void* kw, int w_dtype, const void* cos,
+                            const void* sin, void* qo, void* ko, void* vo, float* q_rstd, float* k_rstd, int64_t n_tokens, int T,
+                            int H, int G, int D, float eps, int64_t q_ts, int64_t k_ts, int q_hpg, int64_t q_gs, int64_t k_gs,
+                            cudaStream_t stream);
+int b200_qknorm_rope_bwd_ex(const void* dqo, const void* dko, const void* dvo, const void* q, const void* k, const void* qw,
+                            const void* kw, int w_dtype, const void* cos, const void* sin, const float* q_rstd, const float* k_rstd,
+                            void* dq, void* dk, void* dv_dst, float* dqw, float* dkw, float* dw_partial, int64_t n_tokens, int T,
+                            int H, int G, int D, int64_t q_ts, int64_t k_ts, int q_hpg, int64_t q_gs, int64_t k_gs, int64_t o_q_ts,
+                            int64_t o_k_ts, int o_q_hpg, int64_t o_q_gs, int64_t o_k_gs, cudaStream_t stream);
 int b200_qknorm_rope_grid();
 
 // ---- mixture of experts (moe_routing.cu, gemm_bf16.cu)

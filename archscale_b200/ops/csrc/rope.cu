@@ -41,12 +41,25 @@ __device__ __forceinline__ float wsum(float v) {
 // per-row index arithmetic, and the heads are walked four at a time so that four 256-byte rows are in flight per warp.
 constexpr int ROPE_U = 4;
 
+// Where the heads of a token sit.  Dense rows [tokens, heads, D] are q_hpg = H, k_gs = D; the output of a fused QKV projection
+// laid out per key/value group as [group][q_per_kv query heads, key head, value head][D] is q_hpg = q_per_kv and
+// q_gs = k_gs = (q_per_kv + 2)·D with the key / value base pointers advanced to their slot of group 0.
+struct QKLayout {
+  long long q_ts, k_ts;      // token strides (elements)
+  long long q_gs, k_gs;      // stride between groups of query heads / between key (value) heads
+  int q_hpg;                 // query heads per group
+};
+__device__ __forceinline__ long long q_head_off(const QKLayout& L, int h, int D) {
+  return static_cast<long long>(h / L.q_hpg) * L.q_gs + static_cast<long long>(h % L.q_hpg) * D;
+}
+
 template <int EPL, typename TW>
 __global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const TW* __restrict__ qw,
     const TW* __restrict__ kw, const __nv_bfloat16* __restrict__ cosb, const __nv_bfloat16* __restrict__ sinb,
     __nv_bfloat16* __restrict__ qo, __nv_bfloat16* __restrict__ ko, float* __restrict__ q_rstd,
-    float* __restrict__ k_rstd, int64_t n_tokens, int T, int H, int G, float eps, int64_t q_ts, int64_t k_ts) {
+    float* __restrict__ k_rstd, int64_t n_tokens, int T, int H, int G, float eps, const QKLayout L,
+    const __nv_bfloat16* __restrict__ v, __nv_bfloat16* __restrict__ vo) {
   constexpr int D = EPL * 32;
   const int lane = threadIdx.x & 31;
   const int64_t warp_global = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
@@ -68,8 +81,8 @@ __global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(
 #pragma unroll 1
     for (int part = 0; part < 2; ++part) {      // the token's query heads, then its key heads
       const int heads = part ? G : H;
-      // inputs may be column slices of a wider (fused projection) matrix: token stride q_ts / k_ts elements
-      const __nv_bfloat16* src = (part ? k + tok * k_ts : q + tok * q_ts) + lane * EPL;
+      // inputs may be column slices of a wider (fused projection) matrix, dense or interleaved per group: see QKLayout
+      const __nv_bfloat16* src = (part ? k + tok * L.k_ts : q + tok * L.q_ts) + lane * EPL;
       __nv_bfloat16* dst = (part ? ko : qo) + tok * heads * D + lane * EPL;
       float* rstd = (part ? k_rstd : q_rstd) + tok * heads;
       const bool has_w = part ? kw != nullptr : qw != nullptr;
@@ -77,7 +90,7 @@ __global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(
         float x[ROPE_U][EPL];
 #pragma unroll
         for (int u = 0; u < ROPE_U; ++u)
-          if (h0 + u < heads) ld_row<EPL>(src + (h0 + u) * D, x[u]);
+          if (h0 + u < heads) ld_row<EPL>(src + (part ? (h0 + u) * L.k_gs : q_head_off(L, h0 + u, D)), x[u]);
 #pragma unroll
         for (int u = 0; u < ROPE_U; ++u) {
           if (h0 + u >= heads) continue;          // warp-uniform
@@ -105,6 +118,19 @@ __global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(
         }
       }
     }
+    if (v) {                                        // the value heads, copied out of the fused projection into dense rows
+      const __nv_bfloat16* src = v + tok * L.k_ts + lane * EPL;
+      __nv_bfloat16* dst = vo + tok * G * D + lane * EPL;
+      for (int g0 = 0; g0 < G; g0 += ROPE_U) {
+        float x[ROPE_U][EPL];
+#pragma unroll
+        for (int u = 0; u < ROPE_U; ++u)
+          if (g0 + u < G) ld_row<EPL>(src + (g0 + u) * L.k_gs, x[u]);
+#pragma unroll
+        for (int u = 0; u < ROPE_U; ++u)
+          if (g0 + u < G) st_row<EPL>(dst + (g0 + u) * D, x[u]);
+      }
+    }
   }
 }
 
@@ -114,7 +140,8 @@ __global__ void __launch_bounds__(256) qknorm_rope_bwd_kernel(
     const __nv_bfloat16* __restrict__ k, const TW* __restrict__ qw, const TW* __restrict__ kw,
     const __nv_bfloat16* __restrict__ cosb, const __nv_bfloat16* __restrict__ sinb, const float* __restrict__ q_rstd,
     const float* __restrict__ k_rstd, __nv_bfloat16* __restrict__ dq, __nv_bfloat16* __restrict__ dk,
-    float* __restrict__ dw_partial /* [grid, 2, D] */, int64_t n_tokens, int T, int H, int G, int64_t q_ts, int64_t k_ts) {
+    float* __restrict__ dw_partial /* [grid, 2, D] */, int64_t n_tokens, int T, int H, int G, const QKLayout L,
+    const QKLayout LO /* layout of dq, dk (and dv_dst) */, const __nv_bfloat16* __restrict__ dvo, __nv_bfloat16* __restrict__ dv_dst) {
   constexpr int D = EPL * 32;
   __shared__ float dw_s[2][D];
   const int lane = threadIdx.x & 31;
@@ -140,10 +167,9 @@ __global__ void __launch_bounds__(256) qknorm_rope_bwd_kernel(
 #pragma unroll 1
     for (int part = 0; part < 2; ++part) {
       const int heads = part ? G : H;
-      const size_t obase = static_cast<size_t>(tok) * heads * D + lane * EPL;
-      const __nv_bfloat16* gsrc = (part ? dko : dqo) + obase;
-      __nv_bfloat16* gdst = (part ? dk : dq) + obase;
-      const __nv_bfloat16* xsrc = (part ? k + tok * k_ts : q + tok * q_ts) + lane * EPL;
+      const __nv_bfloat16* gsrc = (part ? dko : dqo) + static_cast<size_t>(tok) * heads * D + lane * EPL;
+      __nv_bfloat16* gdst = (part ? dk + tok * LO.k_ts : dq + tok * LO.q_ts) + lane * EPL;
+      const __nv_bfloat16* xsrc = (part ? k + tok * L.k_ts : q + tok * L.q_ts) + lane * EPL;
       const float* rstd = (part ? k_rstd : q_rstd) + tok * heads;
       const bool has_w = part ? kw != nullptr : qw != nullptr;
       for (int h0 = 0; h0 < heads; h0 += ROPE_U) {
@@ -152,7 +178,7 @@ __global__ void __launch_bounds__(256) qknorm_rope_bwd_kernel(
         for (int u = 0; u < ROPE_U; ++u) {
           if (h0 + u >= heads) continue;
           ld_row<EPL>(gsrc + (h0 + u) * D, g[u]);
-          if (has_w) { ld_row<EPL>(xsrc + (h0 + u) * D, x[u]); rs[u] = rstd[h0 + u]; }
+          if (has_w) { ld_row<EPL>(xsrc + (part ? (h0 + u) * L.k_gs : q_head_off(L, h0 + u, D)), x[u]); rs[u] = rstd[h0 + u]; }
         }
 #pragma unroll
         for (int u = 0; u < ROPE_U; ++u) {
@@ -181,8 +207,21 @@ __global__ void __launch_bounds__(256) qknorm_rope_bwd_kernel(
 #pragma unroll
             for (int e = 0; e < EPL; ++e) g[u][e] = gw[e] * rs[u] - x[u][e] * c1;
           }
-          st_row<EPL>(gdst + (h0 + u) * D, g[u]);
+          st_row<EPL>(gdst + (part ? (h0 + u) * LO.k_gs : q_head_off(LO, h0 + u, D)), g[u]);
         }
+      }
+    }
+    if (dvo) {                                      // the value gradient takes its slot of the fused-projection gradient
+      const __nv_bfloat16* src = dvo + static_cast<size_t>(tok) * G * D + lane * EPL;
+      __nv_bfloat16* dst = dv_dst + tok * LO.k_ts + lane * EPL;
+      for (int g0 = 0; g0 < G; g0 += ROPE_U) {
+        float x[ROPE_U][EPL];
+#pragma unroll
+        for (int u = 0; u < ROPE_U; ++u)
+          if (g0 + u < G) ld_row<EPL>(src + (g0 + u) * D, x[u]);
+#pragma unroll
+        for (int u = 0; u < ROPE_U; ++u)
+          if (g0 + u < G) st_row<EPL>(dst + (g0 + u) * LO.k_gs, x[u]);
       }
     }
   }
@@ -214,14 +253,18 @@ typedef __nv_bfloat16 bf16;
 
 extern "C" int b200_qknorm_rope_grid() { return kRopeGrid; }
 
-extern "C" int b200_qknorm_rope_fwd(const void* q, const void* k, const void* qw, const void* kw, int w_dtype,
-                                    const void* cos, const void* sin, void* qo, void* ko, float* q_rstd, float* k_rstd,
-                                    int64_t n_tokens, int T, int H, int G, int D, float eps, int64_t q_ts, int64_t k_ts, cudaStream_t st) {
+// q_hpg / gs: see QKLayout (q_hpg = H, gs = D for dense rows).  v / vo: optional value heads (k's layout) copied to dense rows.
+extern "C" int b200_qknorm_rope_fwd_ex(const void* q, const void* k, const void* v, const void* qw, const void* kw, int w_dtype,
+                                       const void* cos, const void* sin, void* qo, void* ko, void* vo, float* q_rstd, float* k_rstd,
+                                       int64_t n_tokens, int T, int H, int G, int D, float eps, int64_t q_ts, int64_t k_ts,
+                                       int q_hpg, int64_t q_gs, int64_t k_gs, cudaStream_t st) {
   if (n_tokens == 0) return 0;
+  if (q_hpg <= 0) return -1;
+  const QKLayout L{q_ts, k_ts, q_gs, k_gs, q_hpg};
 #define LAUNCH(EPL, TW)                                                                                               \
   qknorm_rope_fwd_kernel<EPL, TW><<<kRopeGrid, 256, 0, st>>>((const bf16*)q, (const bf16*)k, (const TW*)qw, (const TW*)kw, \
                                                              (const bf16*)cos, (const bf16*)sin, (bf16*)qo, (bf16*)ko,  \
-                                                             q_rstd, k_rstd, n_tokens, T, H, G, eps, q_ts, k_ts)
+                                                             q_rstd, k_rstd, n_tokens, T, H, G, eps, L, (const bf16*)v, (bf16*)vo)
   if (D == 128) { if (w_dtype == 1) LAUNCH(4, bf16); else LAUNCH(4, float); }
   else if (D == 64) { if (w_dtype == 1) LAUNCH(2, bf16); else LAUNCH(2, float); }
   else return -1;
@@ -229,19 +272,41 @@ extern "C" int b200_qknorm_rope_fwd(const void* q, const void* k, const void* qw
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-extern "C" int b200_qknorm_rope_bwd(const void* dqo, const void* dko, const void* q, const void* k, const void* qw,
-                                     const void* kw, int w_dtype, const void* cos, const void* sin, const float* q_rstd,
-                                     const float* k_rstd, void* dq, void* dk, float* dqw, float* dkw, float* dw_partial,
-                                     int64_t n_tokens, int T, int H, int G, int D, int64_t q_ts, int64_t k_ts, cudaStream_t st) {
+extern "C" int b200_qknorm_rope_fwd(const void* q, const void* k, const void* qw, const void* kw, int w_dtype,
+                                    const void* cos, const void* sin, void* qo, void* ko, float* q_rstd, float* k_rstd,
+                                    int64_t n_tokens, int T, int H, int G, int D, float eps, int64_t q_ts, int64_t k_ts, cudaStream_t st) {
+  return b200_qknorm_rope_fwd_ex(q, k, nullptr, qw, kw, w_dtype, cos, sin, qo, ko, nullptr, q_rstd, k_rstd, n_tokens, T, H, G, D, eps,
+                                 q_ts, k_ts, H, 0, D, st);
+}
+
+// dq / dk are written with the layout (o_q_ts, o_k_ts, o_q_hpg, o_q_gs, o_k_gs); dvo (dense) is copied to dv_dst in k's output layout.
+extern "C" int b200_qknorm_rope_bwd_ex(const void* dqo, const void* dko, const void* dvo, const void* q, const void* k, const void* qw,
+                                       const void* kw, int w_dtype, const void* cos, const void* sin, const float* q_rstd,
+                                       const float* k_rstd, void* dq, void* dk, void* dv_dst, float* dqw, float* dkw,
+                                       float* dw_partial, int64_t n_tokens, int T, int H, int G, int D, int64_t q_ts, int64_t k_ts,
+                                       int q_hpg, int64_t q_gs, int64_t k_gs, int64_t o_q_ts, int64_t o_k_ts, int o_q_hpg,
+                                       int64_t o_q_gs, int64_t o_k_gs, cudaStream_t st) {
   if (n_tokens == 0) return 0;
+  if (q_hpg <= 0 || o_q_hpg <= 0) return -1;
+  const QKLayout L{q_ts, k_ts, q_gs, k_gs, q_hpg}, LO{o_q_ts, o_k_ts, o_q_gs, o_k_gs, o_q_hpg};
 #define LAUNCH(EPL, TW)                                                                                                \
   qknorm_rope_bwd_kernel<EPL, TW><<<kRopeGrid, 256, 0, st>>>((const bf16*)dqo, (const bf16*)dko, (const bf16*)q, (const bf16*)k, \
                                                              (const TW*)qw, (const TW*)kw, (const bf16*)cos, (const bf16*)sin,  \
-                                                             q_rstd, k_rstd, (bf16*)dq, (bf16*)dk, dw_partial, n_tokens, T, H, G, q_ts, k_ts)
+                                                             q_rstd, k_rstd, (bf16*)dq, (bf16*)dk, dw_partial, n_tokens, T, H, G, L, LO, \
+                                                             (const bf16*)dvo, (bf16*)dv_dst)
   if (D == 128) { if (w_dtype == 1) LAUNCH(4, bf16); else LAUNCH(4, float); }
   else if (D == 64) { if (w_dtype == 1) LAUNCH(2, bf16); else LAUNCH(2, float); }
   else return -1;
 #undef LAUNCH
   if (qw) qk_dw_reduce_kernel<<<(2 * D + 31) / 32, 1024, 0, st>>>(dw_partial, dqw, dkw, kRopeGrid, D);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int b200_qknorm_rope_bwd(const void* dqo, const void* dko, const void* q, const void* k, const void* qw,
+                                     const void* kw, int w_dtype, const void* cos, const void* sin, const float* q_rstd,
+                                     const float* k_rstd, void* dq, void* dk, float* dqw, float* dkw, float* dw_partial,
+                                     int64_t n_tokens, int T, int H, int G, int D, int64_t q_ts, int64_t k_ts, cudaStream_t st) {
+  return b200_qknorm_rope_bwd_ex(dqo, dko, nullptr, q, k, qw, kw, w_dtype, cos, sin, q_rstd, k_rstd, dq, dk, nullptr, dqw, dkw,
+                                 dw_partial, n_tokens, T, H, G, D, q_ts, k_ts, H, 0, D, static_cast<int64_t>(H) * D,
+                                 static_cast<int64_t>(G) * D, H, 0, D, st);
 }

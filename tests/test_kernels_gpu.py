@@ -437,3 +437,34 @@ def test_linear_swiglu_autograd_matches_reference():
     yr = torch.nn.functional.silu(hr[..., :1024]) * hr[..., 1024:]
     yr.backward(g.float())
     assert _rel(y, yr) < 2e-2 and _rel(x.grad, xr.grad) < 3e-2 and _rel(w.grad, wr.grad) < 3e-2
+
+
+@pytest.mark.parametrize("G,qpk,D,norm,rope", [(4, 4, 128, True, True), (2, 5, 64, False, True), (3, 1, 128, True, False)])
+def test_qkv_norm_rope_from_the_fused_projection_layout(G, qpk, D, norm, rope):
+    """Norm + rotation read in place from the per-group [q…, k, v] layout equal split → qk_norm_rope, values and gradients."""
+    torch.manual_seed(12)
+    B, T = 2, 96
+    pad = 40                                                 # a column slice of a wider matrix (e.g. a gate projection beside it)
+    wide = torch.randn(B, T, G * (qpk + 2) * D + pad, device="cuda").bfloat16().requires_grad_()
+    qw = (1 + 0.1 * torch.randn(D, device="cuda")).requires_grad_() if norm else None
+    kw = (1 + 0.1 * torch.randn(D, device="cuda")).requires_grad_() if norm else None
+    cos, sin = (None, None)
+    if rope:
+        cos, sin = ops.build_rope_cache(T, D, torch.bfloat16, "cuda")
+    qkv = wide[..., :G * (qpk + 2) * D].view(B, T, G, qpk + 2, D)
+    assert ops.qkv_norm_rope_supported(qkv, cos, qw)
+    q, k, v = ops.qkv_norm_rope(qkv, qw, kw, cos, sin, 1e-5)
+    gq, gk, gv = torch.randn_like(q), torch.randn_like(k), torch.randn_like(v)
+    torch.autograd.backward((q, k, v), (gq, gk, gv))
+    got = [wide.grad.clone()] + ([qw.grad.clone(), kw.grad.clone()] if norm else [])
+    wide.grad = None
+    if norm:
+        qw.grad = kw.grad = None
+    qs, ks, vs = wide[..., :G * (qpk + 2) * D].view(B, T, G, qpk + 2, D).split((qpk, 1, 1), dim=-2)
+    qs, ks, vs = qs.reshape(B, T, -1, D), ks.reshape(B, T, -1, D), vs.reshape(B, T, -1, D)
+    q2, k2 = ops.qk_norm_rope(qs, ks, qw, kw, cos, sin, 1e-5)
+    torch.autograd.backward((q2, k2, vs), (gq, gk, gv))
+    assert torch.equal(q, q2) and torch.equal(k, k2) and torch.equal(v, vs)
+    assert torch.equal(got[0], wide.grad)
+    if norm:
+        assert _rel(got[1], qw.grad) < 1e-5 and _rel(got[2], kw.grad) < 1e-5
