@@ -221,8 +221,26 @@ class CausalSelfAttention(nn.Module):
             return self.proj(y.reshape(B, T, -1)), kv_cache, gmu_mems
 
         fused_qkv = False
+        use_rope = not cfg.nope and not (cfg.yoco_nope and self.win_tuple == (-1, -1))
+        cos, sin = rope if use_rope else (None, None)
+        qw = self.q_norm.weight if self.qk_norm else None
+        kw = self.k_norm.weight if self.qk_norm else None
+
+        def from_fused(y, grouped):
+            """Norm + rotation read the heads in place from the projection's output and deliver dense q, k, v in one launch."""
+            nonlocal fused_qkv
+            if self.sc or not ops.qkv_norm_rope_supported(y, H, G, cos, qw):
+                return None
+            fused_qkv = True
+            return ops.qkv_norm_rope(y, H, G, grouped, qw, kw, cos, sin, cfg.norm_eps)
+
         if cfg.separate_qkv:
-            q, k, v = ops.gemm.linear_multi(x, (self.q_proj, self.k_proj, self.v_proj))
+            y = ops.gemm.linear_multi(x, (self.q_proj, self.k_proj, self.v_proj), keep_fused=True)
+            if isinstance(y, torch.Tensor):                     # the three projections ran as one GEMM: [queries | keys | values]
+                out = from_fused(y, False)
+                q, k, v = out if out is not None else y.split((H * hs, G * hs, G * hs), dim=-1)
+            else:
+                q, k, v = y
             if cfg.gated_attn:
                 g = self.g_proj(x).reshape(B, T, H, 1)
         else:
@@ -231,16 +249,11 @@ class CausalSelfAttention(nn.Module):
                 qkv, g = qkv.split((self.attn_shape - H, H), dim=-1)
                 g = g.reshape(B, T, H, 1)
             q_per_kv = H // G
-            qkv = qkv.view(B, T, G, q_per_kv + 2, hs)
-            use_rope = not cfg.nope and not (cfg.yoco_nope and self.win_tuple == (-1, -1))
-            cos, sin = rope if use_rope else (None, None)
-            if not self.sc and ops.qkv_norm_rope_supported(qkv, cos, self.q_norm.weight if self.qk_norm else None):
-                # norm + rotation read the heads in place from the per-group layout and deliver dense q, k, v in one launch
-                q, k, v = ops.qkv_norm_rope(qkv, self.q_norm.weight if self.qk_norm else None,
-                                            self.k_norm.weight if self.qk_norm else None, cos, sin, cfg.norm_eps)
-                fused_qkv = True
+            out = from_fused(qkv, True)                          # per group: [q_per_kv queries, key, value]
+            if out is not None:
+                q, k, v = out
             else:
-                q, k, v = qkv.split((q_per_kv, 1, 1), dim=-2)
+                q, k, v = qkv.view(B, T, G, q_per_kv + 2, hs).split((q_per_kv, 1, 1), dim=-2)
         if self.sc:
             conv = lambda t, m: ops.causal_conv1d(t.reshape(B, T, -1), m.weight.squeeze(1), m.bias,
                                                   activation="silu", channel_last=True)
@@ -248,8 +261,6 @@ class CausalSelfAttention(nn.Module):
         q = q.reshape(B, T, -1, hs)
         k = k.reshape(B, T, -1, hs)
         v = v.reshape(B, T, -1, hs)
-        use_rope = not cfg.nope and not (cfg.yoco_nope and self.win_tuple == (-1, -1))
-        cos, sin = rope if use_rope else (None, None)
         if not fused_qkv and (self.qk_norm or use_rope):
             q, k = ops.qk_norm_rope(q, k, self.q_norm.weight if self.qk_norm else None,
                                     self.k_norm.weight if self.qk_norm else None, cos, sin, cfg.norm_eps)

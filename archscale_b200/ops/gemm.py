@@ -262,17 +262,20 @@ class _MultiLinearFn(torch.autograd.Function):
         return (dx,) + tuple(outs)
 
 
-def linear_multi(x: torch.Tensor, layers) -> list:
+def linear_multi(x: torch.Tensor, layers, keep_fused: bool = False):
     """Outputs of several bias-free ``Linear`` layers that share the input ``x``.  When their weights sit back to back in
     memory (consecutive views of the flat parameter buffer) the layers run as one GEMM and the outputs are column
-    slices of its result; otherwise each layer is called on its own."""
+    slices of its result; otherwise each layer is called on its own.  ``keep_fused``: return the one GEMM's result unsplit
+    (a tensor instead of a list) when the layers did run as one GEMM."""
     ws = [l.weight for l in layers]
     fusable = (x.is_cuda and x.dtype == torch.bfloat16 and all(type(l).__name__ == "Linear" and l.bias is None and not l.mxfp8
-                                                              for l in layers)
+                                                              and not getattr(l, "nvfp4", False) for l in layers)
                and all(w.dtype == torch.bfloat16 for w in ws) and _adjacent(ws)
                and (x.numel() // x.shape[-1]) % 8 == 0 and x.shape[-1] % 8 == 0 and x.shape[-1] >= 64
                and backend.use_cuda_kernel("gemm", x, ws[0]))
     if not fusable:
         return [l(x) for l in layers]
     y = _MultiLinearFn.apply(x if x.is_contiguous() else x.contiguous(), *ws)
+    if keep_fused:
+        return y
     return list(y.split([w.shape[0] for w in ws], dim=-1))

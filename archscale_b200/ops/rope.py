@@ -138,43 +138,49 @@ def qk_norm_rope(q, k, q_weight, k_weight, cos, sin, eps: float = 1e-5, position
 
 
 class _QKVNormRopeFn(torch.autograd.Function):
-    """The fused QKV projection output [B,T,G,q_per_kv+2,D] → (q', k', v): per-head RMSNorm + RoPE on the query and key heads read
-    in place from the per-group layout, the value heads copied to dense rows, one launch; backward writes dq, dk and dv into one
-    tensor of the projection's layout (no split copies forward, no concatenation backward)."""
+    """The fused QKV projection output [B,T,(H+2G)·D] → (q', k', v): per-head RMSNorm + RoPE on the query and key heads read in
+    place, the value heads copied to dense rows, one launch; backward writes dq, dk and dv into one tensor of the projection's
+    layout (no split copies forward, no concatenation backward).  ``grouped``: per key/value group [queries, key, value] (one
+    fused ``attn`` projection, the checkpoint layout of the reference); else blocked [queries | keys | values] (the q / k / v
+    projections run as one GEMM)."""
 
     @staticmethod
-    def forward(ctx, qkv, qw, kw, cos, sin, eps):
+    def forward(ctx, qkv, H, G, grouped, qw, kw, cos, sin, eps):
         ext = backend.require_extension()
-        qo, ko, vo, q_rstd, k_rstd = ext.qkvnorm_rope_fwd(qkv, qw, kw, cos, sin, eps)
+        qo, ko, vo, q_rstd, k_rstd = ext.qkvnorm_rope_fwd(qkv, H, G, grouped, qw, kw, cos, sin, eps)
         backend.count_launch()
         ctx.save_for_backward(qkv, qw, kw, cos, sin, q_rstd, k_rstd)
+        ctx.meta = (H, G, grouped)
         return qo, ko, vo
 
     @staticmethod
     def backward(ctx, dqo, dko, dvo):
         ext = backend.require_extension()
         qkv, qw, kw, cos, sin, q_rstd, k_rstd = ctx.saved_tensors
-        zeros = lambda ref_shape: torch.zeros(ref_shape, dtype=qkv.dtype, device=qkv.device)
-        B, T, G, P, D = qkv.shape
-        dqo = zeros((B, T, G * (P - 2), D)) if dqo is None else dqo.contiguous()
-        dko = zeros((B, T, G, D)) if dko is None else dko.contiguous()
-        dvo = zeros((B, T, G, D)) if dvo is None else dvo.contiguous()
-        dqkv, dqw, dkw = ext.qkvnorm_rope_bwd(dqo, dko, dvo, qkv, qw, kw, cos, sin, q_rstd, k_rstd)
+        H, G, grouped = ctx.meta
+        B, T, W = qkv.shape
+        D = W // (H + 2 * G)
+        zeros = lambda heads: torch.zeros(B, T, heads, D, dtype=qkv.dtype, device=qkv.device)
+        dqo = zeros(H) if dqo is None else dqo.contiguous()
+        dko = zeros(G) if dko is None else dko.contiguous()
+        dvo = zeros(G) if dvo is None else dvo.contiguous()
+        dqkv, dqw, dkw = ext.qkvnorm_rope_bwd(dqo, dko, dvo, qkv, H, G, grouped, qw, kw, cos, sin, q_rstd, k_rstd)
         backend.count_launch()
         if qw is not None:
             dqw, dkw = dqw.to(qw.dtype), dkw.to(kw.dtype)
         else:
             dqw = dkw = None
-        return dqkv, dqw, dkw, None, None, None
+        return dqkv, None, None, None, dqw, dkw, None, None, None
 
 
-def qkv_norm_rope_supported(qkv: torch.Tensor, cos, q_weight) -> bool:
-    """The fused path takes a bf16 CUDA tensor [B,T,G,q_per_kv+2,D] whose last three dimensions are dense, D 64 or 128, a full
-    rotation (or none) and at least one of norm / rotation to apply."""
-    if not (qkv.dim() == 5 and qkv.is_cuda and qkv.dtype == torch.bfloat16 and qkv.shape[-1] in (64, 128)):
+def qkv_norm_rope_supported(qkv: torch.Tensor, H: int, G: int, cos, q_weight) -> bool:
+    """The fused path takes a bf16 CUDA tensor [B,T,(H+2G)·D] with a dense last dimension and a uniform token stride, D 64 or
+    128, a full rotation (or none) and at least one of norm / rotation to apply."""
+    if not (qkv.dim() == 3 and qkv.is_cuda and qkv.dtype == torch.bfloat16 and H % G == 0 and qkv.shape[-1] % (H + 2 * G) == 0):
         return False
-    B, T, G, P, D = qkv.shape
-    if not (qkv.stride(4) == 1 and qkv.stride(3) == D and qkv.stride(2) == P * D and (B == 1 or qkv.stride(0) == T * qkv.stride(1))):
+    B, T, W = qkv.shape
+    D = W // (H + 2 * G)
+    if D not in (64, 128) or qkv.stride(2) != 1 or not (B == 1 or qkv.stride(0) == T * qkv.stride(1)):
         return False
     if cos is None and q_weight is None:
         return False
@@ -183,12 +189,12 @@ def qkv_norm_rope_supported(qkv: torch.Tensor, cos, q_weight) -> bool:
     return backend.has("qkvnorm_rope_fwd") and backend.use_cuda_kernel("qkv_fused", qkv)
 
 
-def qkv_norm_rope(qkv, q_weight, k_weight, cos, sin, eps: float = 1e-5):
-    """(q', k', v) from the per-group fused projection output; see :class:`_QKVNormRopeFn`.  Callers check
+def qkv_norm_rope(qkv, H: int, G: int, grouped: bool, q_weight, k_weight, cos, sin, eps: float = 1e-5):
+    """(q' [B,T,H,D], k' [B,T,G,D], v [B,T,G,D]) from the fused projection output; see :class:`_QKVNormRopeFn`.  Callers check
     :func:`qkv_norm_rope_supported` first."""
     if cos is not None:
         cos, sin = cos[: qkv.shape[1]].contiguous(), sin[: qkv.shape[1]].contiguous()
-    return _QKVNormRopeFn.apply(qkv, q_weight, k_weight, cos, sin, eps)
+    return _QKVNormRopeFn.apply(qkv, H, G, grouped, q_weight, k_weight, cos, sin, eps)
 
 
 def apply_rotary_emb(x, cos, sin, interleaved: bool = False, positions=None):

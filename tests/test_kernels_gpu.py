@@ -439,29 +439,40 @@ def test_linear_swiglu_autograd_matches_reference():
     assert _rel(y, yr) < 2e-2 and _rel(x.grad, xr.grad) < 3e-2 and _rel(w.grad, wr.grad) < 3e-2
 
 
+@pytest.mark.parametrize("grouped", [True, False])
 @pytest.mark.parametrize("G,qpk,D,norm,rope", [(4, 4, 128, True, True), (2, 5, 64, False, True), (3, 1, 128, True, False)])
-def test_qkv_norm_rope_from_the_fused_projection_layout(G, qpk, D, norm, rope):
-    """Norm + rotation read in place from the per-group [q…, k, v] layout equal split → qk_norm_rope, values and gradients."""
+def test_qkv_norm_rope_from_the_fused_projection_layout(G, qpk, D, norm, rope, grouped):
+    """Norm + rotation read in place from the projection's layout (per group [q…, k, v], or blocked [q | k | v]) equal
+    split → qk_norm_rope, values and gradients."""
     torch.manual_seed(12)
-    B, T = 2, 96
+    B, T, H = 2, 96, G * qpk
+    W = (H + 2 * G) * D
     pad = 40                                                 # a column slice of a wider matrix (e.g. a gate projection beside it)
-    wide = torch.randn(B, T, G * (qpk + 2) * D + pad, device="cuda").bfloat16().requires_grad_()
+    wide = torch.randn(B, T, W + pad, device="cuda").bfloat16().requires_grad_()
     qw = (1 + 0.1 * torch.randn(D, device="cuda")).requires_grad_() if norm else None
     kw = (1 + 0.1 * torch.randn(D, device="cuda")).requires_grad_() if norm else None
     cos, sin = (None, None)
     if rope:
         cos, sin = ops.build_rope_cache(T, D, torch.bfloat16, "cuda")
-    qkv = wide[..., :G * (qpk + 2) * D].view(B, T, G, qpk + 2, D)
-    assert ops.qkv_norm_rope_supported(qkv, cos, qw)
-    q, k, v = ops.qkv_norm_rope(qkv, qw, kw, cos, sin, 1e-5)
+
+    def split(t):
+        y = t[..., :W]
+        if grouped:
+            a, b, c = y.view(B, T, G, qpk + 2, D).split((qpk, 1, 1), dim=-2)
+        else:
+            a, b, c = y.split((H * D, G * D, G * D), dim=-1)
+        return a.reshape(B, T, H, D), b.reshape(B, T, G, D), c.reshape(B, T, G, D)
+
+    qkv = wide[..., :W]
+    assert ops.qkv_norm_rope_supported(qkv, H, G, cos, qw)
+    q, k, v = ops.qkv_norm_rope(qkv, H, G, grouped, qw, kw, cos, sin, 1e-5)
     gq, gk, gv = torch.randn_like(q), torch.randn_like(k), torch.randn_like(v)
     torch.autograd.backward((q, k, v), (gq, gk, gv))
     got = [wide.grad.clone()] + ([qw.grad.clone(), kw.grad.clone()] if norm else [])
     wide.grad = None
     if norm:
         qw.grad = kw.grad = None
-    qs, ks, vs = wide[..., :G * (qpk + 2) * D].view(B, T, G, qpk + 2, D).split((qpk, 1, 1), dim=-2)
-    qs, ks, vs = qs.reshape(B, T, -1, D), ks.reshape(B, T, -1, D), vs.reshape(B, T, -1, D)
+    qs, ks, vs = split(wide)
     q2, k2 = ops.qk_norm_rope(qs, ks, qw, kw, cos, sin, 1e-5)
     torch.autograd.backward((q2, k2, vs), (gq, gk, gv))
     assert torch.equal(q, q2) and torch.equal(k, k2) and torch.equal(v, vs)
