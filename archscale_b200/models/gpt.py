@@ -3,7 +3,7 @@
 Reference: `lit_gpt/model.py:101-351` (``GPT``: constructor, ``reset_parameters`` with the
 μP++ head rule / GPT-2 out-projection scaling / ``w_init_scale``, ``forward`` returning
 ``CausalLMOutput(logits, weight)``), `:354-605` (``Block``: YOCO / SambaY layer map, pre/post
-norm, fp32 residual stream, depth scaling) and `:620-677` (``LLaMAMLP`` with fused
+norm, residual stream, depth scaling) and `:620-677` (``LLaMAMLP`` with fused
 ``w1 = [gate; up]`` and ``w3`` down projection).  Module and parameter names are unchanged
 because they are the checkpoint format.
 
