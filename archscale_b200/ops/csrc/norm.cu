@@ -250,11 +250,97 @@ __global__ void __launch_bounds__(256) add_rmsnorm_bwd_kernel(const TG* __restri
   for (int c = threadIdx.x; c < cols; c += blockDim.x) dw_partial[static_cast<size_t>(blockIdx.x) * cols + c] = dw_s[c];
 }
 
+// The same backward with every row split over a PAIR of warps (cols == NCH·256, NCH even): a lane keeps NCH/2 chunks of the
+// weight-gradient accumulator instead of NCH and reads the weight from shared memory, which brings the kernel under 128
+// registers and two CTAs onto an SM (the one-warp-per-row form needs 255 registers at 2048 columns).  The two partial dot products of a row meet
+// in shared memory behind a 64-thread named barrier; two buffers alternate so that one barrier per row suffices.
+template <typename TX, typename TW, int NCH, typename TG>
+__global__ void __launch_bounds__(256, 2) add_rmsnorm_bwd2_kernel(const TG* __restrict__ g_res, const __nv_bfloat16* __restrict__ g_n,
+                                                                 const TX* __restrict__ x, const TW* __restrict__ w,
+                                                                 const float* __restrict__ rstd, TG* __restrict__ d_res,
+                                                                 __nv_bfloat16* __restrict__ d_h, float h_scale,
+                                                                 float* __restrict__ dw_partial, int rows, int cols) {
+  extern __shared__ float dw_s[];                                       // [cols] weight-gradient sums, then [cols] the weight in fp32
+  __shared__ float dot_s[2][8];
+  constexpr int NCL = NCH / 2;
+  float* w_s = dw_s + cols;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pair = warp >> 1, half = warp & 1;
+  const int c0 = lane * 8 + half * NCL * 256;                           // first column of this lane
+  for (int c = threadIdx.x * 8; c < cols; c += blockDim.x * 8) {
+    float t[8]; Vec8<TW>::load(w + c, t);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { w_s[c + e] = t[e]; dw_s[c + e] = 0.f; }
+  }
+  __syncthreads();
+  float dwacc[NCL][8];
+#pragma unroll
+  for (int i = 0; i < NCL; ++i)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dwacc[i][e] = 0.f;
+  int it = 0;
+  for (int row = blockIdx.x * 4 + pair; row < rows; row += gridDim.x * 4, ++it) {
+    const size_t base = static_cast<size_t>(row) * cols + c0;
+    const float rs = rstd[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NCL; ++i) {
+      float xv[8], dv[8], wv[8];
+      Vec8<TX>::load(x + base + i * 256, xv);
+      Vec8<__nv_bfloat16>::load(g_n + base + i * 256, dv);
+      Vec8<float>::load(w_s + c0 + i * 256, wv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dot += dv[e] * wv[e] * xv[e];
+    }
+    dot = warp_sum(dot);
+    if (lane == 0) dot_s[it & 1][warp] = dot;
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory");
+    dot = dot_s[it & 1][pair * 2] + dot_s[it & 1][pair * 2 + 1];
+    const float c1 = dot * rs * rs * rs / cols;
+#pragma unroll
+    for (int i = 0; i < NCL; ++i) {
+      float xv[8], dv[8], wv[8], o[8];             // second read of the row: L1 / L2 hits
+      Vec8<TX>::load(x + base + i * 256, xv);
+      Vec8<__nv_bfloat16>::load(g_n + base + i * 256, dv);
+      Vec8<float>::load(w_s + c0 + i * 256, wv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        o[e] = dv[e] * wv[e] * rs - xv[e] * c1;
+        dwacc[i][e] += dv[e] * xv[e] * rs;
+      }
+      if (g_res) {
+        float gr[8]; Vec8<TG>::load(g_res + base + i * 256, gr);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] += gr[e];
+      }
+      if (d_res) Vec8<TG>::store(d_res + base + i * 256, o);
+      if (d_h) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] *= h_scale;
+        Vec8<__nv_bfloat16>::store(d_h + base + i * 256, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NCL; ++i)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) atomicAdd(&dw_s[c0 + i * 256 + e], dwacc[i][e]);
+  __syncthreads();
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) dw_partial[static_cast<size_t>(blockIdx.x) * cols + c] = dw_s[c];
+}
+
 constexpr int kBwdCtas = 148 * 2;
 
 }  // namespace b200
 
 using namespace b200;
+
+#include <cstdlib>
+// ARCHSCALE_B200_NORM_BWD=warp keeps the one-warp-per-row backward for the widths the warp-pair kernel takes.
+static bool use_pair_rows() {
+  static const bool v = [] { const char* e = std::getenv("ARCHSCALE_B200_NORM_BWD"); return !(e && e[0] == 'w'); }();
+  return v;
+}
 
 #define DISPATCH_3(xd, wd, od, CALL)                                                           \
   if (xd == 0 && wd == 0 && od == 0) { CALL(float, float, float) }                              \
@@ -383,6 +469,24 @@ extern "C" int b200_add_rmsnorm_bwd(const void* g_res, const void* g_n, const vo
   else L(bf, bf, NCH, float);
   // the instantiation with the fewest 256-column chunks that covers the row (the kernel skips what lies beyond `cols`)
   if (cols % 8 || cols > 4096) return -2;
+  if (use_pair_rows() && cols == 2048) {      // wider rows spill at 128 registers
+#define L2(TX, TW, NCH, TG)                                                                                            \
+  add_rmsnorm_bwd2_kernel<TX, TW, NCH, TG><<<grid, 256, 2 * smem, stream>>>(                                               \
+      static_cast<const TG*>(g_res), static_cast<const bf*>(g_n), static_cast<const TX*>(x), static_cast<const TW*>(w), rstd, \
+      static_cast<TG*>(d_res), static_cast<bf*>(d_h), h_scale, dw_partial, rows, cols)
+#define LN2(NCH)                                                         \
+  if (g_dtype == 1 && w_dtype == 0) L2(bf, float, NCH, bf);              \
+  else if (g_dtype == 1) L2(bf, bf, NCH, bf);                            \
+  else if (x_dtype == 0 && w_dtype == 0) L2(float, float, NCH, float);   \
+  else if (x_dtype == 0 && w_dtype == 1) L2(float, bf, NCH, float);      \
+  else if (x_dtype == 1 && w_dtype == 0) L2(bf, float, NCH, float);      \
+  else L2(bf, bf, NCH, float);
+    LN2(8)
+#undef LN2
+#undef L2
+    reduce_partials_kernel<<<(cols + 31) / 32, 1024, 0, stream>>>(dw_partial, dw, grid, cols);
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  }
   if (cols <= 1024) { LN(4) }
   else if (cols <= 2048) { LN(8) }
   else if (cols <= 2560) { LN(10) }

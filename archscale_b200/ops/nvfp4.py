@@ -30,7 +30,6 @@ from typing import Optional, Tuple
 import torch
 
 from . import backend
-from .mxfp8 import chunk_scales_ref, unchunk_scales_ref  # the 512-byte scale chunks are shared with MXFP8
 
 E2M1_MAX = 6.0
 E4M3_MAX = 448.0
