@@ -469,7 +469,7 @@ extern "C" int b200_add_rmsnorm_bwd(const void* g_res, const void* g_n, const vo
   else L(bf, bf, NCH, float);
   // the instantiation with the fewest 256-column chunks that covers the row (the kernel skips what lies beyond `cols`)
   if (cols % 8 || cols > 4096) return -2;
-  if (use_pair_rows() && cols == 2048) {      // wider rows spill at 128 registers
+  if (use_pair_rows() && cols == 2048) {      // wider rows spill at 128 registers; 1024-wide rows measured no faster this way
 #define L2(TX, TW, NCH, TG)                                                                                            \
   add_rmsnorm_bwd2_kernel<TX, TW, NCH, TG><<<grid, 256, 2 * smem, stream>>>(                                               \
       static_cast<const TG*>(g_res), static_cast<const bf*>(g_n), static_cast<const TX*>(x), static_cast<const TW*>(w), rstd, \
