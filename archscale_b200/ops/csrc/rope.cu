@@ -49,12 +49,26 @@ struct QKLayout {
   long long q_gs, k_gs;      // stride between groups of query heads / between key (value) heads
   int q_hpg;                 // query heads per group
 };
-__device__ __forceinline__ long long q_head_off(const QKLayout& L, int h, int D) {
-  return static_cast<long long>(h / L.q_hpg) * L.q_gs + static_cast<long long>(h % L.q_hpg) * D;
+
+// Copies G head rows of one token between two head strides; kept out of line so that the row copy does not change how the
+// compiler schedules the norm / rotation loops around it (inlined, both kernels ran about twice as long).
+template <int EPL>
+__device__ __noinline__ void copy_head_rows(const __nv_bfloat16* src, long long sstride, __nv_bfloat16* dst, long long dstride, int G) {
+  for (int g0 = 0; g0 < G; g0 += ROPE_U) {
+    float x[ROPE_U][EPL];
+#pragma unroll
+    for (int u = 0; u < ROPE_U; ++u)
+      if (g0 + u < G) ld_row<EPL>(src + (g0 + u) * sstride, x[u]);
+#pragma unroll
+    for (int u = 0; u < ROPE_U; ++u)
+      if (g0 + u < G) st_row<EPL>(dst + (g0 + u) * dstride, x[u]);
+  }
 }
 
-template <int EPL, typename TW>
-__global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(
+// GROUPED: the per-group layout (else every head of a part is D elements after the previous one: dense rows or the blocked
+// fused projection, for which the loops below reduce to the plain walk over heads).  WITH_V: also copy the value heads.
+template <int EPL, typename TW, bool GROUPED, bool WITH_V>
+__global__ void __launch_bounds__(256, 4) qknorm_rope_fwd_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k, const TW* __restrict__ qw,
     const TW* __restrict__ kw, const __nv_bfloat16* __restrict__ cosb, const __nv_bfloat16* __restrict__ sinb,
     __nv_bfloat16* __restrict__ qo, __nv_bfloat16* __restrict__ ko, float* __restrict__ q_rstd,
@@ -80,62 +94,55 @@ __global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(
     }
 #pragma unroll 1
     for (int part = 0; part < 2; ++part) {      // the token's query heads, then its key heads
-      const int heads = part ? G : H;
-      // inputs may be column slices of a wider (fused projection) matrix, dense or interleaved per group: see QKLayout
-      const __nv_bfloat16* src = (part ? k + tok * L.k_ts : q + tok * L.q_ts) + lane * EPL;
-      __nv_bfloat16* dst = (part ? ko : qo) + tok * heads * D + lane * EPL;
-      float* rstd = (part ? k_rstd : q_rstd) + tok * heads;
+      // inputs may be column slices of a wider (fused projection) matrix, dense or interleaved per group: see QKLayout.
+      // Heads are walked group by group (one group of H heads for dense rows), so no head index is ever divided.
+      const int per = part ? G : (GROUPED ? L.q_hpg : H), n_groups = (part || !GROUPED) ? 1 : H / L.q_hpg;
+      const long long gstride = (part || !GROUPED) ? 0 : L.q_gs, hstride = (GROUPED && part) ? L.k_gs : D;
       const bool has_w = part ? kw != nullptr : qw != nullptr;
-      for (int h0 = 0; h0 < heads; h0 += ROPE_U) {
-        float x[ROPE_U][EPL];
+      for (int grp = 0; grp < n_groups; ++grp) {
+        const __nv_bfloat16* src = (part ? k + tok * L.k_ts : q + tok * L.q_ts) + grp * gstride + lane * EPL;
+        __nv_bfloat16* dst = (part ? ko + tok * G * D : qo + tok * H * D) + static_cast<long long>(grp) * per * D + lane * EPL;
+        float* rstd = (part ? k_rstd + tok * G : q_rstd + tok * H) + grp * per;
+        for (int h0 = 0; h0 < per; h0 += ROPE_U) {
+          float x[ROPE_U][EPL];
 #pragma unroll
-        for (int u = 0; u < ROPE_U; ++u)
-          if (h0 + u < heads) ld_row<EPL>(src + (part ? (h0 + u) * L.k_gs : q_head_off(L, h0 + u, D)), x[u]);
+          for (int u = 0; u < ROPE_U; ++u)
+            if (h0 + u < per) ld_row<EPL>(src + (h0 + u) * hstride, x[u]);
 #pragma unroll
-        for (int u = 0; u < ROPE_U; ++u) {
-          if (h0 + u >= heads) continue;          // warp-uniform
-          if (has_w) {
-            float ss = 0.f;
+          for (int u = 0; u < ROPE_U; ++u) {
+            if (h0 + u >= per) continue;          // warp-uniform
+            if (has_w) {
+              float ss = 0.f;
 #pragma unroll
-            for (int e = 0; e < EPL; ++e) ss += x[u][e] * x[u][e];
-            ss = wsum(ss);
-            const float rs = rsqrtf(ss / D + eps);
-            if (lane == 0) rstd[h0 + u] = rs;
+              for (int e = 0; e < EPL; ++e) ss += x[u][e] * x[u][e];
+              ss = wsum(ss);
+              const float rs = rsqrtf(ss / D + eps);
+              if (lane == 0) rstd[h0 + u] = rs;
 #pragma unroll
-            for (int e = 0; e < EPL; ++e) x[u][e] = x[u][e] * rs * (part ? wk[e] : wq[e]);
-          }
-          if (cosb) {
-            float o[EPL];
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) {
-              const float other = __shfl_xor_sync(0xffffffffu, x[u][e], 16);
-              o[e] = lane < 16 ? x[u][e] * cs[e] - other * sn[e] : other * sn[e] + x[u][e] * cs[e];
+              for (int e = 0; e < EPL; ++e) x[u][e] = x[u][e] * rs * (part ? wk[e] : wq[e]);
             }
-            st_row<EPL>(dst + (h0 + u) * D, o);
-          } else {
-            st_row<EPL>(dst + (h0 + u) * D, x[u]);
+            if (cosb) {
+              float o[EPL];
+#pragma unroll
+              for (int e = 0; e < EPL; ++e) {
+                const float other = __shfl_xor_sync(0xffffffffu, x[u][e], 16);
+                o[e] = lane < 16 ? x[u][e] * cs[e] - other * sn[e] : other * sn[e] + x[u][e] * cs[e];
+              }
+              st_row<EPL>(dst + (h0 + u) * D, o);
+            } else {
+              st_row<EPL>(dst + (h0 + u) * D, x[u]);
+            }
           }
         }
       }
     }
-    if (v) {                                        // the value heads, copied out of the fused projection into dense rows
-      const __nv_bfloat16* src = v + tok * L.k_ts + lane * EPL;
-      __nv_bfloat16* dst = vo + tok * G * D + lane * EPL;
-      for (int g0 = 0; g0 < G; g0 += ROPE_U) {
-        float x[ROPE_U][EPL];
-#pragma unroll
-        for (int u = 0; u < ROPE_U; ++u)
-          if (g0 + u < G) ld_row<EPL>(src + (g0 + u) * L.k_gs, x[u]);
-#pragma unroll
-        for (int u = 0; u < ROPE_U; ++u)
-          if (g0 + u < G) st_row<EPL>(dst + (g0 + u) * D, x[u]);
-      }
-    }
+    if (WITH_V)                                     // the value heads, copied out of the fused projection into dense rows
+      copy_head_rows<EPL>(v + tok * L.k_ts + lane * EPL, GROUPED ? L.k_gs : D, vo + tok * G * D + lane * EPL, D, G);
   }
 }
 
-template <int EPL, typename TW>
-__global__ void __launch_bounds__(256) qknorm_rope_bwd_kernel(
+template <int EPL, typename TW, bool GROUPED, bool WITH_V>
+__global__ void __launch_bounds__(256, 2) qknorm_rope_bwd_kernel(
     const __nv_bfloat16* __restrict__ dqo, const __nv_bfloat16* __restrict__ dko, const __nv_bfloat16* __restrict__ q,
     const __nv_bfloat16* __restrict__ k, const TW* __restrict__ qw, const TW* __restrict__ kw,
     const __nv_bfloat16* __restrict__ cosb, const __nv_bfloat16* __restrict__ sinb, const float* __restrict__ q_rstd,
@@ -166,64 +173,59 @@ __global__ void __launch_bounds__(256) qknorm_rope_bwd_kernel(
     }
 #pragma unroll 1
     for (int part = 0; part < 2; ++part) {
-      const int heads = part ? G : H;
-      const __nv_bfloat16* gsrc = (part ? dko : dqo) + static_cast<size_t>(tok) * heads * D + lane * EPL;
-      __nv_bfloat16* gdst = (part ? dk + tok * LO.k_ts : dq + tok * LO.q_ts) + lane * EPL;
-      const __nv_bfloat16* xsrc = (part ? k + tok * L.k_ts : q + tok * L.q_ts) + lane * EPL;
-      const float* rstd = (part ? k_rstd : q_rstd) + tok * heads;
+      const int per = part ? G : (GROUPED ? L.q_hpg : H), n_groups = (part || !GROUPED) ? 1 : H / L.q_hpg;      // LO: same grouping
+      const long long gstride = (part || !GROUPED) ? 0 : L.q_gs, hstride = (GROUPED && part) ? L.k_gs : D;
+      const long long o_gstride = (part || !GROUPED) ? 0 : LO.q_gs, o_hstride = (GROUPED && part) ? LO.k_gs : D;
       const bool has_w = part ? kw != nullptr : qw != nullptr;
-      for (int h0 = 0; h0 < heads; h0 += ROPE_U) {
-        float g[ROPE_U][EPL], x[ROPE_U][EPL], rs[ROPE_U];
+      for (int grp = 0; grp < n_groups; ++grp) {
+        const long long dense = static_cast<long long>(grp) * per * D + lane * EPL;
+        const __nv_bfloat16* gsrc = (part ? dko + tok * G * D : dqo + tok * H * D) + dense;
+        __nv_bfloat16* gdst = (part ? dk + tok * LO.k_ts : dq + tok * LO.q_ts) + grp * o_gstride + lane * EPL;
+        const __nv_bfloat16* xsrc = (part ? k + tok * L.k_ts : q + tok * L.q_ts) + grp * gstride + lane * EPL;
+        const float* rstd = (part ? k_rstd + tok * G : q_rstd + tok * H) + grp * per;
+        for (int h0 = 0; h0 < per; h0 += ROPE_U) {
+          float g[ROPE_U][EPL], x[ROPE_U][EPL], rs[ROPE_U];
 #pragma unroll
-        for (int u = 0; u < ROPE_U; ++u) {
-          if (h0 + u >= heads) continue;
-          ld_row<EPL>(gsrc + (h0 + u) * D, g[u]);
-          if (has_w) { ld_row<EPL>(xsrc + (part ? (h0 + u) * L.k_gs : q_head_off(L, h0 + u, D)), x[u]); rs[u] = rstd[h0 + u]; }
-        }
-#pragma unroll
-        for (int u = 0; u < ROPE_U; ++u) {
-          if (h0 + u >= heads) continue;
-          if (cosb) {
-            float o[EPL];
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) {
-              const float other = __shfl_xor_sync(0xffffffffu, g[u][e], 16);
-              o[e] = lane < 16 ? g[u][e] * cs[e] + other * sn[e] : -other * sn[e] + g[u][e] * cs[e];
-            }
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) g[u][e] = o[e];
+          for (int u = 0; u < ROPE_U; ++u) {
+            if (h0 + u >= per) continue;
+            ld_row<EPL>(gsrc + (h0 + u) * D, g[u]);
+            if (has_w) { ld_row<EPL>(xsrc + (h0 + u) * hstride, x[u]); rs[u] = rstd[h0 + u]; }
           }
-          if (has_w) {
-            float dot = 0.f;
-            float gw[EPL];
 #pragma unroll
-            for (int e = 0; e < EPL; ++e) {
-              gw[e] = g[u][e] * (part ? wk[e] : wq[e]);
-              dot += gw[e] * x[u][e];
-              if (part) dwk[e] += g[u][e] * x[u][e] * rs[u]; else dwq[e] += g[u][e] * x[u][e] * rs[u];
+          for (int u = 0; u < ROPE_U; ++u) {
+            if (h0 + u >= per) continue;
+            if (cosb) {
+              float o[EPL];
+#pragma unroll
+              for (int e = 0; e < EPL; ++e) {
+                const float other = __shfl_xor_sync(0xffffffffu, g[u][e], 16);
+                o[e] = lane < 16 ? g[u][e] * cs[e] + other * sn[e] : -other * sn[e] + g[u][e] * cs[e];
+              }
+#pragma unroll
+              for (int e = 0; e < EPL; ++e) g[u][e] = o[e];
             }
-            dot = wsum(dot);
-            const float c1 = dot * rs[u] * rs[u] * rs[u] / D;
+            if (has_w) {
+              float dot = 0.f;
+              float gw[EPL];
 #pragma unroll
-            for (int e = 0; e < EPL; ++e) g[u][e] = gw[e] * rs[u] - x[u][e] * c1;
+              for (int e = 0; e < EPL; ++e) {
+                gw[e] = g[u][e] * (part ? wk[e] : wq[e]);
+                dot += gw[e] * x[u][e];
+                if (part) dwk[e] += g[u][e] * x[u][e] * rs[u]; else dwq[e] += g[u][e] * x[u][e] * rs[u];
+              }
+              dot = wsum(dot);
+              const float c1 = dot * rs[u] * rs[u] * rs[u] / D;
+#pragma unroll
+              for (int e = 0; e < EPL; ++e) g[u][e] = gw[e] * rs[u] - x[u][e] * c1;
+            }
+            st_row<EPL>(gdst + (h0 + u) * o_hstride, g[u]);
           }
-          st_row<EPL>(gdst + (part ? (h0 + u) * LO.k_gs : q_head_off(LO, h0 + u, D)), g[u]);
         }
       }
     }
-    if (dvo) {                                      // the value gradient takes its slot of the fused-projection gradient
-      const __nv_bfloat16* src = dvo + static_cast<size_t>(tok) * G * D + lane * EPL;
-      __nv_bfloat16* dst = dv_dst + tok * LO.k_ts + lane * EPL;
-      for (int g0 = 0; g0 < G; g0 += ROPE_U) {
-        float x[ROPE_U][EPL];
-#pragma unroll
-        for (int u = 0; u < ROPE_U; ++u)
-          if (g0 + u < G) ld_row<EPL>(src + (g0 + u) * D, x[u]);
-#pragma unroll
-        for (int u = 0; u < ROPE_U; ++u)
-          if (g0 + u < G) st_row<EPL>(dst + (g0 + u) * LO.k_gs, x[u]);
-      }
-    }
+    if (WITH_V)                                     // the value gradient takes its slot of the fused-projection gradient
+      copy_head_rows<EPL>(dvo + static_cast<size_t>(tok) * G * D + lane * EPL, D, dv_dst + tok * LO.k_ts + lane * EPL,
+                          GROUPED ? LO.k_gs : D, G);
   }
   if (qw) {
 #pragma unroll
@@ -259,16 +261,24 @@ extern "C" int b200_qknorm_rope_fwd_ex(const void* q, const void* k, const void*
                                        int64_t n_tokens, int T, int H, int G, int D, float eps, int64_t q_ts, int64_t k_ts,
                                        int q_hpg, int64_t q_gs, int64_t k_gs, cudaStream_t st) {
   if (n_tokens == 0) return 0;
-  if (q_hpg <= 0) return -1;
+  if (q_hpg <= 0 || H % q_hpg) return -1;
   const QKLayout L{q_ts, k_ts, q_gs, k_gs, q_hpg};
-#define LAUNCH(EPL, TW)                                                                                               \
-  qknorm_rope_fwd_kernel<EPL, TW><<<kRopeGrid, 256, 0, st>>>((const bf16*)q, (const bf16*)k, (const TW*)qw, (const TW*)kw, \
+  const bool grouped = q_hpg != H, with_v = v != nullptr;
+  if (!grouped && k_gs != D) return -1;
+#define LAUNCH2(EPL, TW, GR, WV)                                                                                      \
+  qknorm_rope_fwd_kernel<EPL, TW, GR, WV><<<kRopeGrid, 256, 0, st>>>((const bf16*)q, (const bf16*)k, (const TW*)qw, (const TW*)kw, \
                                                              (const bf16*)cos, (const bf16*)sin, (bf16*)qo, (bf16*)ko,  \
                                                              q_rstd, k_rstd, n_tokens, T, H, G, eps, L, (const bf16*)v, (bf16*)vo)
+#define LAUNCH(EPL, TW)                                                        \
+  do {                                                                         \
+    if (grouped) { if (with_v) LAUNCH2(EPL, TW, true, true); else LAUNCH2(EPL, TW, true, false); } \
+    else { if (with_v) LAUNCH2(EPL, TW, false, true); else LAUNCH2(EPL, TW, false, false); }       \
+  } while (0)
   if (D == 128) { if (w_dtype == 1) LAUNCH(4, bf16); else LAUNCH(4, float); }
   else if (D == 64) { if (w_dtype == 1) LAUNCH(2, bf16); else LAUNCH(2, float); }
   else return -1;
 #undef LAUNCH
+#undef LAUNCH2
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -287,17 +297,25 @@ extern "C" int b200_qknorm_rope_bwd_ex(const void* dqo, const void* dko, const v
                                        int q_hpg, int64_t q_gs, int64_t k_gs, int64_t o_q_ts, int64_t o_k_ts, int o_q_hpg,
                                        int64_t o_q_gs, int64_t o_k_gs, cudaStream_t st) {
   if (n_tokens == 0) return 0;
-  if (q_hpg <= 0 || o_q_hpg <= 0) return -1;
+  if (q_hpg <= 0 || o_q_hpg != q_hpg || H % q_hpg) return -1;       // input and output share one grouping
   const QKLayout L{q_ts, k_ts, q_gs, k_gs, q_hpg}, LO{o_q_ts, o_k_ts, o_q_gs, o_k_gs, o_q_hpg};
-#define LAUNCH(EPL, TW)                                                                                                \
-  qknorm_rope_bwd_kernel<EPL, TW><<<kRopeGrid, 256, 0, st>>>((const bf16*)dqo, (const bf16*)dko, (const bf16*)q, (const bf16*)k, \
+  const bool grouped = q_hpg != H, with_v = dvo != nullptr;
+  if (!grouped && (k_gs != D || o_k_gs != D)) return -1;
+#define LAUNCH2(EPL, TW, GR, WV)                                                                                       \
+  qknorm_rope_bwd_kernel<EPL, TW, GR, WV><<<kRopeGrid, 256, 0, st>>>((const bf16*)dqo, (const bf16*)dko, (const bf16*)q, (const bf16*)k, \
                                                              (const TW*)qw, (const TW*)kw, (const bf16*)cos, (const bf16*)sin,  \
                                                              q_rstd, k_rstd, (bf16*)dq, (bf16*)dk, dw_partial, n_tokens, T, H, G, L, LO, \
                                                              (const bf16*)dvo, (bf16*)dv_dst)
+#define LAUNCH(EPL, TW)                                                        \
+  do {                                                                         \
+    if (grouped) { if (with_v) LAUNCH2(EPL, TW, true, true); else LAUNCH2(EPL, TW, true, false); } \
+    else { if (with_v) LAUNCH2(EPL, TW, false, true); else LAUNCH2(EPL, TW, false, false); }       \
+  } while (0)
   if (D == 128) { if (w_dtype == 1) LAUNCH(4, bf16); else LAUNCH(4, float); }
   else if (D == 64) { if (w_dtype == 1) LAUNCH(2, bf16); else LAUNCH(2, float); }
   else return -1;
 #undef LAUNCH
+#undef LAUNCH2
   if (qw) qk_dw_reduce_kernel<<<(2 * D + 31) / 32, 1024, 0, st>>>(dw_partial, dqw, dkw, kRopeGrid, D);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
