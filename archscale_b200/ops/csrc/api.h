@@ -168,7 +168,7 @@ int b200_gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* s
 size_t b200_nvfp4_sf_bytes(int rows, int K);
 int b200_nvfp4_amax(const void* x, int ld, float* amax, int R, int C, cudaStream_t st);
 int b200_nvfp4_quantize(const void* x, int ld, void* q, void* sf, void* qT, void* sfT, const float* amax, int R, int C, int mode,
-                        cudaStream_t st);
+                        cudaStream_t st, int stochastic = 0, unsigned seed = 0, int rht = 0, unsigned sign_mask = 0);
 int b200_gemm_nvfp4(const void* A, const void* sfa, const void* B, const void* sfb, const float* amax_a, const float* amax_b,
                     void* out, int M, int N, int K, int lda, int ldb, int ldc, float alpha, int out_f32, int accumulate,
                     int num_sms, int* status, cudaStream_t stream);

@@ -14,6 +14,7 @@
 // tcgen05.cp.32x128b.warpx4: lane m % 32 of every lane quarter, column (m / 32) % 4, byte kb % 4.
 // A 192-wide B tile starts at a multiple of 64 rows; when that is the middle of a chunk the MMA is given
 // the scale address two columns further (rows 64.. of the first chunk), and two chunks are always loaded.
+#include <cuda_fp4.h>
 #include <cuda_fp8.h>
 
 #include "api.h"
@@ -588,11 +589,6 @@ done:
 // ---- NVFP4 quantisers.  amax[0] = max |x| over the tensor (nvfp4_amax_kernel); tensor scale = amax / (6 · 448), 1 if zero.
 // block scale = E4M3(amax_block · (1 / (6 · tensor_scale))), round to nearest; element = e2m1(x / (block · tensor)), round to
 // nearest even, saturating at 6.
-__device__ __forceinline__ uint32_t e2m1_code(float v) {
-  const float a = fabsf(v);
-  uint32_t c = (a > 0.25f) + (a >= 0.75f) + (a > 1.25f) + (a >= 1.75f) + (a > 2.5f) + (a >= 3.5f) + (a > 5.f);
-  return c | (v < 0.f ? 8u : 0u);
-}
 __device__ __forceinline__ float nvfp4_block_scale(float amax, float tensor_scale, uint8_t* code) {
   // amax · (1 / (6 · tensor_scale)) with every step rounded to nearest: the same three operations as the PyTorch
   // restatement, so that both give the same scale even where the exact quotient is a tie between two E4M3 values
@@ -604,15 +600,61 @@ __device__ __forceinline__ float nvfp4_block_scale(float amax, float tensor_scal
   return sb > 0.f ? __frcp_rn(sb * tensor_scale) : 0.f;                 // multiply by this, then round to e2m1
 }
 
-// Quantise 16 values held in registers: returns the two packed words and the scale code.
-__device__ __forceinline__ uint2 nvfp4_pack16(const float (&v)[16], float ts, uint8_t* code) {
+// Stochastic rounding of four values to e2m1 in one instruction (the converter rounds a magnitude up to the next grid value
+// with probability (a − lower) / (upper − lower), drawing on the 32 random bits it is given).  The first operand of the vector
+// lands in the most significant nibble, so the values are passed last-first to get element 0 into nibble 0.
+__device__ __forceinline__ uint32_t e2m1x4_sr(float x0, float x1, float x2, float x3, uint32_t rbits) {
+  uint16_t d;
+  asm("cvt.rs.satfinite.e2m1x4.f32 %0, {%1, %2, %3, %4}, %5;" : "=h"(d) : "f"(x3), "f"(x2), "f"(x1), "f"(x0), "r"(rbits));
+  return d;
+}
+// 32 random bits from a counter (the 32-bit finaliser of MurmurHash3 over index ^ seed): no state, any element order.
+__device__ __forceinline__ uint32_t hashed_bits(uint32_t seed, unsigned long long index) {
+  uint32_t x = static_cast<uint32_t>(index) * 0x9E3779B1u ^ static_cast<uint32_t>(index >> 32) ^ seed;
+  x ^= x >> 16; x *= 0x85EBCA6Bu; x ^= x >> 13; x *= 0xC2B2AE35u; x ^= x >> 16;
+  return x;
+}
+// v ← (sign ⊙ v) · H16 / 4 with H16 the 16 × 16 Sylvester Hadamard matrix (four butterfly stages); orthogonal.
+__device__ __forceinline__ void hadamard16(float (&v)[16], uint32_t sign_mask) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) v[j] = (sign_mask >> j) & 1u ? -v[j] : v[j];
+#pragma unroll
+  for (int h = 1; h < 16; h <<= 1)
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      if (!(j & h)) { const float a = v[j], b = v[j | h]; v[j] = a + b; v[j | h] = a - b; }
+#pragma unroll
+  for (int j = 0; j < 16; ++j) v[j] *= 0.25f;
+}
+
+// Quantise 16 values held in registers: returns the two packed words and the scale code.  SR: stochastic rounding of the
+// elements with random bits hashed from (seed, index of every fourth element).
+template <bool SR>
+__device__ __forceinline__ uint2 nvfp4_pack16(const float (&v)[16], float ts, uint8_t* code, uint32_t seed = 0,
+                                              unsigned long long index = 0) {
   float amax = 0.f;
 #pragma unroll
   for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
   const float inv = nvfp4_block_scale(amax, ts, code);
   uint32_t lo = 0, hi = 0;
+  if (SR) {
 #pragma unroll
-  for (int e = 0; e < 8; ++e) { lo |= e2m1_code(v[e] * inv) << (4 * e); hi |= e2m1_code(v[8 + e] * inv) << (4 * e); }
+    for (int g = 0; g < 2; ++g) {                    // one hash and one conversion per four elements
+      lo |= e2m1x4_sr(v[4 * g] * inv, v[4 * g + 1] * inv, v[4 * g + 2] * inv, v[4 * g + 3] * inv, hashed_bits(seed, index + 4 * g)) << (16 * g);
+      hi |= e2m1x4_sr(v[8 + 4 * g] * inv, v[9 + 4 * g] * inv, v[10 + 4 * g] * inv, v[11 + 4 * g] * inv,
+                      hashed_bits(seed, index + 8 + 4 * g)) << (16 * g);
+    }
+  } else {
+    // the converter instruction, two values at a time (round to nearest even, saturating); + 0 turns the −0 of a negative
+    // value times a zero scale into +0, as the PyTorch restatement has it
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      lo |= static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(make_float2(__fadd_rn(v[2 * e] * inv, 0.f), __fadd_rn(v[2 * e + 1] * inv, 0.f)),
+                                                            __NV_E2M1, cudaRoundNearest)) << (8 * e);
+      hi |= static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(make_float2(__fadd_rn(v[8 + 2 * e] * inv, 0.f), __fadd_rn(v[9 + 2 * e] * inv, 0.f)),
+                                                            __NV_E2M1, cudaRoundNearest)) << (8 * e);
+    }
+  }
   return make_uint2(lo, hi);
 }
 __device__ __forceinline__ void unpack16(const uint4& u0, const uint4& u1, float (&v)[16]) {
@@ -624,9 +666,10 @@ __device__ __forceinline__ void unpack16(const uint4& u0, const uint4& u1, float
 // One thread per 16-element block of a row.  x: [R, C] bf16, q: [R, C/2] bytes, C % 256 == 0.  (A thread per 64 elements,
 // with whole 32-byte sectors and aligned scale words out, was measured slower: 0.072 against 0.076 ms net became 0.083 for
 // 32768 × 2048 — consecutive threads then read 128 bytes apart.)
+template <bool SR>
 __global__ void __launch_bounds__(256) nvfp4_quant_rowwise_kernel(const __nv_bfloat16* __restrict__ x, int ld,
                                                                  uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
-                                                                 const float* __restrict__ amax_t, int R, int C) {
+                                                                 const float* __restrict__ amax_t, int R, int C, uint32_t seed) {
   const int nblk = C >> 4;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<long long>(R) * nblk) return;
@@ -636,7 +679,7 @@ __global__ void __launch_bounds__(256) nvfp4_quant_rowwise_kernel(const __nv_bfl
   float v[16];
   unpack16(u0, u1, v);
   uint8_t code;
-  const uint2 w = nvfp4_pack16(v, nvfp4_tensor_scale(*amax_t), &code);
+  const uint2 w = nvfp4_pack16<SR>(v, nvfp4_tensor_scale(*amax_t), &code, seed, static_cast<unsigned long long>(r) * C + kb * 16);
   *reinterpret_cast<uint2*>(q + static_cast<size_t>(r) * (C >> 1) + kb * 8) = w;
   sf[sf_offset(r, kb, nblk >> 2)] = code;
 }
@@ -645,11 +688,16 @@ __global__ void __launch_bounds__(256) nvfp4_quant_rowwise_kernel(const __nv_bfl
 // the row-wise operand q [R, C/2] (blocks along C) from the same shared-memory tile, so that a tensor needed in both
 // orientations (an activation for forward and weight gradient, an output gradient for both backward products) is read
 // once.  Tile 128 rows × 64 columns.  R % 256 == 0, C % 64 == 0 (ROWS: C % 256 == 0).
-template <int ROWS>
+// SR: stochastic rounding of both outputs.  RHT: every 16-element block of the TRANSPOSED operand is multiplied by
+// diag(sign) · H16 / 4 before it is quantised (both operands of a weight-gradient product get the same transform, which
+// cancels in the product and spreads outliers over the block); its tensor scale is then taken from 4 · amax, the bound of
+// a transformed element.
+template <int ROWS, bool SR, bool RHT>
 __global__ void __launch_bounds__(256) nvfp4_quant_colwise_kernel(const __nv_bfloat16* __restrict__ x, int ld,
                                                                  uint8_t* __restrict__ qT, uint8_t* __restrict__ sfT,
                                                                  uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
-                                                                 const float* __restrict__ amax_t, int R, int C) {
+                                                                 const float* __restrict__ amax_t, int R, int C, uint32_t seed,
+                                                                 uint32_t sign_mask) {
   __shared__ __align__(16) __nv_bfloat16 s[128][72];
   const int r0 = blockIdx.y * 128, c0 = blockIdx.x * 64, tid = threadIdx.x;
 #pragma unroll
@@ -668,8 +716,10 @@ __global__ void __launch_bounds__(256) nvfp4_quant_colwise_kernel(const __nv_bfl
       float v[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) v[j] = __bfloat162float(s[rb * 32 + h * 16 + j][c]);
+      if (RHT) hadamard16(v, sign_mask);
       uint8_t code;
-      const uint2 w = nvfp4_pack16(v, ts, &code);
+      const uint2 w = nvfp4_pack16<SR>(v, RHT ? nvfp4_tensor_scale(4.f * *amax_t) : ts, &code, seed ^ 0x5bd1e995u,
+                                       static_cast<unsigned long long>(c0 + c) * R + r0 + rb * 32 + h * 16);
       words[2 * h] = w.x; words[2 * h + 1] = w.y;
       sfT[sf_offset(c0 + c, (r0 >> 4) + rb * 2 + h, R >> 6)] = code;
     }
@@ -685,7 +735,7 @@ __global__ void __launch_bounds__(256) nvfp4_quant_colwise_kernel(const __nv_bfl
       float v[16];
       unpack16(u0, u1, v);
       uint8_t code;
-      const uint2 w = nvfp4_pack16(v, ts, &code);
+      const uint2 w = nvfp4_pack16<SR>(v, ts, &code, seed, static_cast<unsigned long long>(r0 + row) * C + c0 + blk * 16);
       *reinterpret_cast<uint2*>(q + static_cast<size_t>(r0 + row) * (C >> 1) + ((c0 + blk * 16) >> 1)) = w;
       sf[sf_offset(r0 + row, (c0 >> 4) + blk, C >> 6)] = code;
     }
@@ -794,24 +844,38 @@ extern "C" int b200_nvfp4_amax(const void* x, int ld, float* amax, int R, int C,
 }
 
 // mode 0: row-wise (q, sf); 1: column-wise (qT, sfT); 2: both from one read of x.  amax: device pointer to max |x|.
+// stochastic: stochastic rounding of the elements (seed selects the random numbers); rht: random Hadamard transform of the
+// transposed operand with the signs of sign_mask (its tensor scale then belongs to 4 · amax).
 extern "C" int b200_nvfp4_quantize(const void* x, int ld, void* q, void* sf, void* qT, void* sfT, const float* amax, int R, int C,
-                                   int mode, cudaStream_t st) {
+                                   int mode, cudaStream_t st, int stochastic, unsigned seed, int rht, unsigned sign_mask) {
   if (R <= 0 || C <= 0) return 0;
   if (ld % 8) return -1;
   if (mode == 0) {
     if (C % 256) return -1;
     const long long total = static_cast<long long>(R) * (C / 16);
-    nvfp4_quant_rowwise_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(
-        (const __nv_bfloat16*)x, ld, (uint8_t*)q, (uint8_t*)sf, amax, R, C);
+    const unsigned grid = static_cast<unsigned>((total + 255) / 256);
+    if (stochastic)
+      nvfp4_quant_rowwise_kernel<true><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, ld, (uint8_t*)q, (uint8_t*)sf, amax, R, C, seed);
+    else
+      nvfp4_quant_rowwise_kernel<false><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, ld, (uint8_t*)q, (uint8_t*)sf, amax, R, C, seed);
   } else {
     if (R % 256 || C % 64 || (mode == 2 && C % 256)) return -1;
     const dim3 grid(C / 64, R / 128);
-    if (mode == 2)
-      nvfp4_quant_colwise_kernel<1><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, ld, (uint8_t*)qT, (uint8_t*)sfT, (uint8_t*)q,
-                                                          (uint8_t*)sf, amax, R, C);
-    else
-      nvfp4_quant_colwise_kernel<0><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, ld, (uint8_t*)qT, (uint8_t*)sfT, nullptr, nullptr,
-                                                          amax, R, C);
+#define QC(RW, SRV, RH)                                                                                                  \
+  nvfp4_quant_colwise_kernel<RW, SRV, RH><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, ld, (uint8_t*)qT, (uint8_t*)sfT, \
+                                                                (uint8_t*)q, (uint8_t*)sf, amax, R, C, seed, sign_mask)
+    const int key = (mode == 2 ? 4 : 0) | (stochastic ? 2 : 0) | (rht ? 1 : 0);
+    switch (key) {
+      case 0: QC(0, false, false); break;
+      case 1: QC(0, false, true); break;
+      case 2: QC(0, true, false); break;
+      case 3: QC(0, true, true); break;
+      case 4: QC(1, false, false); break;
+      case 5: QC(1, false, true); break;
+      case 6: QC(1, true, false); break;
+      default: QC(1, true, true); break;
+    }
+#undef QC
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

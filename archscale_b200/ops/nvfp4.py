@@ -11,12 +11,16 @@ operands on the fly, with the same three K-major "NT" products as :mod:`archscal
 
 Two implementations of the same arithmetic:
 
-* the kernel path (``csrc/gemm_mxfp8.cu``: ``tcgen05.mma.kind::mxf4nvf4.block_scale.scale_vec::4X`` and the quantisers):
-  round-to-nearest-even everywhere, scales along one dimension for weights as for activations;
-* the emulated path (plain PyTorch, any device): quantise → dequantise → matmul.  It is the CPU path and the test oracle,
-  and it alone offers the two gradient-side options of the recipe: stochastic rounding of the gradient operands and a random
-  16 × 16 Hadamard transform of both weight-gradient operands along the token dimension
-  (``ARCHSCALE_B200_NVFP4=emulate`` selects it on a GPU, ``ARCHSCALE_B200_NVFP4_SR=0`` / ``_RHT=0`` switch the options off).
+* the kernel path (``csrc/gemm_mxfp8.cu``: ``tcgen05.mma.kind::mxf4nvf4.block_scale.scale_vec::4X`` and the quantisers),
+  scales along one dimension for weights as for activations;
+* the emulated path (plain PyTorch, any device): quantise → dequantise → matmul.  It is the CPU path and the test oracle
+  (``ARCHSCALE_B200_NVFP4=emulate`` selects it on a GPU).
+
+Both apply the two gradient-side options of the recipe by default: stochastic rounding of the gradient operands (round to
+nearest everywhere else) and a random 16 × 16 Hadamard transform of both weight-gradient operands along the token dimension
+(``ARCHSCALE_B200_NVFP4_SR=0`` / ``ARCHSCALE_B200_NVFP4_RHT=0`` switch them off).  The kernels draw their random numbers from a
+counter hash and scale a transformed operand from 4 · amax (the bound of a transformed element), so the two paths agree in
+distribution, not bit for bit, once an option is on.
 
 Quantisation rule (both paths, bit for bit): ``tensor_scale = amax(x) / (6·448)`` (1 for an all-zero tensor);
 ``block_scale = E4M3(amax_block · (1 / (6 · tensor_scale)))`` rounded to nearest (each step in fp32);
@@ -195,24 +199,44 @@ def amax(x: torch.Tensor) -> torch.Tensor:
     return ext.nvfp4_amax(x)
 
 
-def quantize(x: torch.Tensor, colwise: bool = False, amax_t: Optional[torch.Tensor] = None):
-    """x:(R,C) bf16 → operand triple.  ``colwise`` returns the transposed operand (C,R/2)."""
+_SEED = [0x1234567]
+
+
+def _next_seed() -> int:
+    """A new 31-bit seed per stochastic quantisation (a counter through an odd multiplier: no two calls of a run share numbers)."""
+    _SEED[0] = (_SEED[0] * 1103515245 + 12345) & 0x7FFFFFFF
+    return _SEED[0]
+
+
+def _sign_mask() -> int:
+    """The fixed ±1 vector of the Hadamard transform as a bit mask (bit j set: element j is negated)."""
+    sign = _rht_sign("cpu")
+    return int(sum(1 << j for j in range(16) if sign[j] < 0))
+
+
+def quantize(x: torch.Tensor, colwise: bool = False, amax_t: Optional[torch.Tensor] = None, stochastic: bool = False,
+             rht: bool = False):
+    """x:(R,C) bf16 → operand triple.  ``colwise`` returns the transposed operand (C,R/2); ``rht`` (transposed operand only)
+    applies the random Hadamard transform to its 16-element blocks, ``stochastic`` rounds the elements stochastically."""
+    ext = backend.require_extension()
+    if amax_t is None:
+        amax_t = amax(x)
+    rht = rht and colwise
+    backend.count_launch()
+    q, sf = ext.nvfp4_quantize(x, amax_t, 1 if colwise else 0, stochastic, _next_seed() if stochastic else 0, rht,
+                               _sign_mask() if rht else 0)
+    return q, sf, (amax_t * 4.0 if rht else amax_t)
+
+
+def quantize_both(x: torch.Tensor, amax_t: Optional[torch.Tensor] = None, stochastic: bool = False, rht: bool = False):
+    """x:(R,C) bf16 → (row-wise operand, transposed operand) from one read of x; ``rht`` transforms the transposed one."""
     ext = backend.require_extension()
     if amax_t is None:
         amax_t = amax(x)
     backend.count_launch()
-    q, sf = ext.nvfp4_quantize(x, amax_t, 1 if colwise else 0)
-    return q, sf, amax_t
-
-
-def quantize_both(x: torch.Tensor, amax_t: Optional[torch.Tensor] = None):
-    """x:(R,C) bf16 → (row-wise operand, transposed operand) from one read of x."""
-    ext = backend.require_extension()
-    if amax_t is None:
-        amax_t = amax(x)
-    backend.count_launch()
-    q, sf, qt, sft = ext.nvfp4_quantize(x, amax_t, 2)
-    return (q, sf, amax_t), (qt, sft, amax_t)
+    q, sf, qt, sft = ext.nvfp4_quantize(x, amax_t, 2, stochastic, _next_seed() if stochastic else 0, rht,
+                                        _sign_mask() if rht else 0)
+    return (q, sf, amax_t), (qt, sft, amax_t * 4.0 if rht else amax_t)
 
 
 def gemm(a, b, out_f32: bool = False, acc: Optional[torch.Tensor] = None, alpha: float = 1.0):
@@ -255,15 +279,16 @@ def quantize_weight(weight: torch.Tensor, colwise: bool):
 class _LinearNVFP4Fn(torch.autograd.Function):
     """Each tensor is read twice per use at most: once for its largest magnitude, once by a quantiser that writes every
     orientation the step needs (x: row-wise for the forward product and transposed for the weight gradient, saved in place
-    of x itself; dy: row-wise for dgrad and transposed for wgrad)."""
+    of x itself; dy: row-wise for dgrad and transposed for wgrad).  ``stochastic``: the gradient operands are rounded
+    stochastically; ``rht``: both operands of the weight-gradient product get the random Hadamard transform."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias):
+    def forward(ctx, x, weight, bias, stochastic, rht):
         x2 = x.reshape(-1, x.shape[-1])
         if not x2.is_contiguous():
             x2 = x2.contiguous()
         if ctx.needs_input_grad[1]:
-            xq, xt = quantize_both(x2)
+            xq, xt = quantize_both(x2, rht=rht)
             ctx.save_for_backward(weight, *xt)
         else:
             xq = quantize(x2)
@@ -274,22 +299,24 @@ class _LinearNVFP4Fn(torch.autograd.Function):
         ctx.has_bias = bias is not None
         ctx.weight_ref = weight
         ctx.x_shape = x.shape
+        ctx.opts = (bool(stochastic), bool(rht))
         return y.view(*x.shape[:-1], weight.shape[0])
 
     @staticmethod
     def backward(ctx, dy):
         weight, *xt = ctx.saved_tensors
+        stochastic, rht = ctx.opts
         dy2 = dy.reshape(-1, dy.shape[-1])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         dx = dw = db = None
         need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         if need_dx and need_dw:
-            g, gt = quantize_both(dy2)
+            g, gt = quantize_both(dy2, stochastic=stochastic, rht=rht)
         elif need_dx:
-            g, gt = quantize(dy2), None
+            g, gt = quantize(dy2, stochastic=stochastic), None
         else:
-            g, gt = None, quantize(dy2, colwise=True)
+            g, gt = None, quantize(dy2, colwise=True, stochastic=stochastic, rht=rht)
         if need_dx:
             dx = gemm(g, quantize_weight(weight, True)).view(ctx.x_shape)       # Wᵀ: (K, N) blocks along N
         if need_dw:
@@ -300,7 +327,7 @@ class _LinearNVFP4Fn(torch.autograd.Function):
                 dw = gemm(gt, tuple(xt)).to(weight.dtype)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.float().sum(0).to(dy.dtype)
-        return dx, dw, db
+        return dx, dw, db, None, None
 
 
 def linear_nvfp4(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -309,7 +336,7 @@ def linear_nvfp4(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
     x2 = x.reshape(-1, x.shape[-1])
     mode = os.environ.get("ARCHSCALE_B200_NVFP4", "kernel")
     if mode != "emulate" and supported(x2, weight) and backend.use_cuda_kernel("nvfp4", x2, weight):
-        return _LinearNVFP4Fn.apply(x, weight, bias)
+        return _LinearNVFP4Fn.apply(x, weight, bias, _opt("ARCHSCALE_B200_NVFP4_SR"), _opt("ARCHSCALE_B200_NVFP4_RHT"))
     if emulated_supported(x2, weight):
         return linear_nvfp4_emulated(x, weight, bias)
     from .gemm import linear

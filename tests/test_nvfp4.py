@@ -123,7 +123,48 @@ def test_block_scaled_fp4_gemm_matches_dequantised_matmul(M, N, K):
 
 
 @pytest.mark.gpu
-def test_nvfp4_linear_kernel_path_matches_emulation():
+def test_kernel_stochastic_rounding_is_unbiased_and_stays_on_neighbouring_grid_values():
+    x = torch.full((256, 256), 1.2, device="cuda").bfloat16()
+    x[:, ::16] = 6.0                                   # pins every block scale so that 1.2 sits between 1.0 and 1.5
+    acc = torch.zeros(256, 256, device="cuda")
+    first = None
+    for _ in range(64):
+        q, sf, am = nvfp4.quantize(x, stochastic=True)
+        d = nvfp4.dequantize_ref(q, unchunk_scales_ref(sf, 256, 512), nvfp4.scale_from_amax(am))
+        first = d if first is None else first
+        acc += d
+    body = torch.ones(256, 256, dtype=torch.bool, device="cuda")
+    body[:, ::16] = False
+    vals = torch.unique(first[body])
+    assert set(round(float(v), 4) for v in vals) <= {1.0, 1.5}            # only the two neighbours of 1.2 (bf16: 1.203)
+    mean = float((acc / 64)[body].mean())
+    assert abs(mean - float(x[0, 1])) < 0.01
+    assert torch.equal(first[~body], torch.full_like(first[~body], 6.0))
+
+
+@pytest.mark.gpu
+def test_kernel_hadamard_transform_cancels_in_the_product():
+    """(dyᵀ·D·H)(xᵀ·D·H)ᵀ = dyᵀ·x: the transformed transposed operands give the same weight gradient up to quantisation."""
+    torch.manual_seed(8)
+    T, N, K = 512, 256, 256
+    dy = torch.randn(T, N, device="cuda").bfloat16()
+    x = torch.randn(T, K, device="cuda").bfloat16()
+    x[5, 7] = 40.0                                     # an outlier that the transform spreads over its block
+    ref = dy.float().t() @ x.float()
+    plain = nvfp4.gemm(nvfp4.quantize(dy, colwise=True), nvfp4.quantize(x, colwise=True), out_f32=True)
+    rht = nvfp4.gemm(nvfp4.quantize(dy, colwise=True, rht=True), nvfp4.quantize(x, colwise=True, rht=True), out_f32=True)
+    assert _rel(plain, ref) < 0.2 and _rel(rht, ref) < 0.2
+    # the kernel's transform equals the restatement's: dequantised transposed operand against fake-quantised H-transformed xᵀ
+    qt, sft, am4 = nvfp4.quantize(x, colwise=True, rht=True)
+    got = nvfp4.dequantize_ref(qt, unchunk_scales_ref(sft, K, 2 * T), nvfp4.scale_from_amax(am4))
+    want = nvfp4.random_hadamard(x.float().t().contiguous(), nvfp4._rht_sign("cuda"))
+    assert _rel(got, want) < 0.15
+
+
+@pytest.mark.gpu
+def test_nvfp4_linear_kernel_path_matches_emulation(monkeypatch):
+    monkeypatch.setenv("ARCHSCALE_B200_NVFP4_SR", "0")
+    monkeypatch.setenv("ARCHSCALE_B200_NVFP4_RHT", "0")
     torch.manual_seed(7)
     x = torch.randn(2, 256, 512, device="cuda").bfloat16().requires_grad_()
     w = (torch.randn(768, 512, device="cuda") * 0.05).bfloat16().requires_grad_()
@@ -138,3 +179,17 @@ def test_nvfp4_linear_kernel_path_matches_emulation():
     yr = torch.nn.functional.linear(xr, wr)
     yr.backward(g.float())
     assert _rel(y, yr) < 0.2 and _rel(x.grad, xr.grad) < 0.25 and _rel(w.grad, wr.grad) < 0.25
+
+
+@pytest.mark.gpu
+def test_nvfp4_linear_with_stochastic_rounding_and_hadamard_close_to_fp32():
+    torch.manual_seed(9)
+    x = torch.randn(2, 256, 512, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(768, 512, device="cuda") * 0.05).bfloat16().requires_grad_()
+    y = nvfp4.linear_nvfp4(x, w)                       # both options on by default
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = (t.detach().float().requires_grad_() for t in (x, w))
+    yr = torch.nn.functional.linear(xr, wr)
+    yr.backward(g.float())
+    assert _rel(y, yr) < 0.2 and _rel(x.grad, xr.grad) < 0.3 and _rel(w.grad, wr.grad) < 0.3
