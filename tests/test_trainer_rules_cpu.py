@@ -231,3 +231,30 @@ def test_deferred_clip_equals_clip_in_place():
     b, gb = run(True)
     assert ga == gb
     assert all(torch.allclose(a[k], b[k], atol=1e-6) for k in a)
+
+
+def test_residual_stream_dtype_follows_the_flag():
+    """``residual_in_fp32`` decides the type of the residual stream between the blocks (fp32, or the compute dtype)."""
+    from archscale_b200 import Config
+    from archscale_b200.models.gpt import GPT
+    seen = {}
+
+    def run(flag):
+        torch.manual_seed(0)
+        cfg = Config.from_name("transformer_gqa4_d8", n_layer=2, ar=None, n_embd=64, n_head=2, n_query_groups=1, head_dim=32,
+                               intermediate_size=128, vocab_size=128, padding_multiple=64, block_size=32, residual_in_fp32=flag)
+        model = GPT(cfg).bfloat16()
+        model.reset_parameters()
+        model.compute_dtype = torch.bfloat16
+        dtypes = []
+        h = model.transformer.h[1].norm_1.register_forward_pre_hook(lambda m, args: dtypes.append(args[0].dtype))
+        out = model(torch.randint(0, 128, (2, 16)))
+        h.remove()
+        seen[flag] = (dtypes[0], out.logits.float())
+
+    run(True)
+    run(False)
+    assert seen[True][0] == torch.float32 and seen[False][0] == torch.bfloat16
+    a, b = seen[True][1], seen[False][1]
+    assert torch.isfinite(a).all() and torch.isfinite(b).all()
+    assert float((a - b).norm() / a.norm()) < 0.1          # same model, the stream's rounding is the only difference
