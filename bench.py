@@ -121,6 +121,28 @@ class ClockSampler:
         return out
 
 
+
+def parse_cfg_overrides(items) -> dict:
+    """``FIELD=VALUE`` strings → Config overrides: true / false, integers and floats are converted, anything else stays a string."""
+    out = {}
+    for item in items:
+        key, sep, val = item.partition("=")
+        if not sep or not key:
+            raise ValueError(f"--cfg expects FIELD=VALUE, got {item!r}")
+        low = val.lower()
+        if low in ("true", "false"):
+            out[key] = low == "true"
+            continue
+        for conv in (int, float):
+            try:
+                out[key] = conv(val)
+                break
+            except ValueError:
+                pass
+        else:
+            out[key] = val
+    return out
+
 def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
@@ -136,17 +158,7 @@ def run_ours(args) -> None:
     os.environ.setdefault("LIGHTNING_ARTIFACTS_DIR", os.path.join(tempfile.gettempdir(), "archscale_b200_bench"))
     ep = world if (args.config == "moe" and world > 1 and not args.no_ep) else 1
     overrides = dict(c["overrides"])
-    for item in args.cfg:
-        key, _, val = item.partition("=")
-        overrides[key] = {"true": True, "false": False}.get(val.lower(), None)
-        if overrides[key] is None:
-            try:
-                overrides[key] = int(val)
-            except ValueError:
-                try:
-                    overrides[key] = float(val)
-                except ValueError:
-                    overrides[key] = val
+    overrides.update(parse_cfg_overrides(args.cfg))
     kwargs = dict(train_data_dir="synthetic", train_model=c["train_model"], depth=c["depth"], train_name=c["train_name"],
                   micro_bsz=c["micro_bsz"], ctx_len=c["ctx_len"], total_bsz=(world // max(args.tp, 1)) * c["micro_bsz"] * c["ctx_len"],
                   max_tokens=1e12, use_flce=True, sparsity=c["sparsity"], top_k=c["top_k"],

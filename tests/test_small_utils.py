@@ -57,3 +57,16 @@ def test_incremental_save_and_lazy_load(tmp_path):
     assert x["iter_num"] == 3 and torch.equal(x["param"], torch.ones(2))
     with lazy_load(p) as sd:                              # tensors mapped from the file, read on access
         assert torch.equal(sd["model"]["a"], a) and sd["model"]["b"].dtype == torch.bfloat16
+
+
+def test_bench_cfg_overrides_are_typed():
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location("bench_mod", os.path.join(os.path.dirname(os.path.dirname(__file__)), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    got = bench.parse_cfg_overrides(["residual_in_fp32=true", "n_layer=4", "norm_eps=1e-6", "aux_style=switch_seq", "qk_norm=False"])
+    assert got == {"residual_in_fp32": True, "n_layer": 4, "norm_eps": 1e-6, "aux_style": "switch_seq", "qk_norm": False}
+    import pytest
+    with pytest.raises(ValueError):
+        bench.parse_cfg_overrides(["no_equals_sign"])
