@@ -70,3 +70,26 @@ def test_bench_cfg_overrides_are_typed():
     import pytest
     with pytest.raises(ValueError):
         bench.parse_cfg_overrides(["no_equals_sign"])
+
+
+def test_moe_ffn_adds_the_shared_output_and_the_mix_on_cpu():
+    """``moe_ffn(..., shared, alpha)`` = alpha · (routed + shared), values and gradients, on the PyTorch path."""
+    import torch
+    from archscale_b200 import ops
+    from archscale_b200.ops.moe import moe_ffn_ref, router_topk_softmax_ref
+    torch.manual_seed(0)
+    N, C, E, I, K, alpha = 40, 16, 4, 8, 2, 0.5 ** 0.5
+    x = torch.randn(N, C, requires_grad=True)
+    w_in = (torch.randn(E, 2 * I, C) * 0.2).requires_grad_()
+    w_out = (torch.randn(E, C, I) * 0.2).requires_grad_()
+    shared = torch.randn(N, C, requires_grad=True)
+    scores, idx = router_topk_softmax_ref(torch.randn(N, E), K, sqrt_gate=True)
+    out = ops.moe_ffn(x, w_in, w_out, scores, idx, shared=shared, alpha=alpha)
+    g = torch.randn_like(out)
+    out.backward(g)
+    xr, wir, wor, shr = (t.detach().clone().requires_grad_() for t in (x, w_in, w_out, shared))
+    ref = alpha * (moe_ffn_ref(xr, wir, wor, scores, idx) + shr)
+    ref.backward(g)
+    assert torch.allclose(out, ref, atol=1e-5)
+    for a, b in ((x.grad, xr.grad), (w_in.grad, wir.grad), (w_out.grad, wor.grad), (shared.grad, shr.grad)):
+        assert torch.allclose(a, b, atol=1e-5)
