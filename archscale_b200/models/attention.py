@@ -12,7 +12,7 @@ the device and the kernel needs no ``max_seqlen``.
 from __future__ import annotations
 
 import math
-from typing import Optional, Tuple
+from typing import Optional
 
 import torch
 import torch.nn as nn

@@ -17,7 +17,7 @@ from __future__ import annotations
 
 import copy
 import math
-from typing import Any, List, NamedTuple, Optional, Tuple
+from typing import Any, List, NamedTuple, Optional
 
 import torch
 import torch.nn as nn

@@ -13,7 +13,6 @@ and tokens travel by the dispatch/combine path in :mod:`archscale_b200.parallel.
 from __future__ import annotations
 
 import math
-from typing import Optional
 
 import torch
 import torch.nn as nn

@@ -9,7 +9,7 @@ CUDA path: ``csrc/norm.cu`` — one warp-group per row block, fp32 statistics, t
 """
 from __future__ import annotations
 
-from typing import Optional, Tuple
+from typing import Optional
 
 import torch
 

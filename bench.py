@@ -24,7 +24,6 @@ import statistics
 import subprocess
 import sys
 import tempfile
-import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
@@ -148,7 +147,6 @@ def run_ours(args) -> None:
     import torch.distributed as dist
 
     from archscale_b200.ops import backend
-    from archscale_b200.parallel import dist_utils as du
     from archscale_b200.train.pretrain import setup
     from archscale_b200.utils.speed_monitor import estimate_flops, matmul_parameter_count, measured_peaks
 
