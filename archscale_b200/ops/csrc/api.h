@@ -78,11 +78,14 @@ int b200_routing_chunks(int n_pairs);
 int b200_routing_capacity(int n_pairs, int E);
 int b200_routing_layout(const int* expert_of_pair, int n_pairs, int E, int* counts, int* offsets, int* slot_pair,
                         int* pair_slot, int capacity, int* scratch, cudaStream_t stream);
+// The three row kernels check every index they read against its table (pair < n_pairs, 0 <= slot < capacity): an index
+// outside is reported as STATUS_INDEX_RANGE in the status word and its access is skipped.
 int b200_gather_rows(const void* x, const int* slot_pair, const float* pair_scale, void* xs, int capacity, int C, int K,
-                     const int* offsets, int E, cudaStream_t stream);
+                     const int* offsets, int E, cudaStream_t stream, int n_pairs, int* status);
 int b200_combine_rows(const void* y, const int* pair_slot, const float* w, void* out, int N, int C, int K, const void* add,
-                      float alpha, cudaStream_t stream);
-int b200_pair_dots(const void* y, const void* g, const int* pair_slot, float* dots, int n_pairs, int C, int K, cudaStream_t stream);
+                      float alpha, cudaStream_t stream, int capacity, int* status);
+int b200_pair_dots(const void* y, const void* g, const int* pair_slot, float* dots, int n_pairs, int C, int K, cudaStream_t stream,
+                   int capacity, int* status);
 int b200_grouped_gemm_bf16(int kind, const void* A, const void* B, void* out, const int* offsets, int E, int capacity, int M,
                            int N, int K, int out_f32, int accumulate, int num_sms, int* status, cudaStream_t stream);
 

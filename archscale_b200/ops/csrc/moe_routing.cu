@@ -115,9 +115,11 @@ __global__ void __launch_bounds__(256) route_place_kernel(const int* __restrict_
 }
 
 // xs[slot, :] = scale · x[pair / K, :]   (bf16 rows of C elements, 16-byte vectors; zero for padding slots)
+// A pair index outside [0, n_pairs) (a corrupted table) is reported in the status word and its row is written as zeros.
 __global__ void __launch_bounds__(256) gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ slot_pair,
                                                           const float* __restrict__ pair_scale, __nv_bfloat16* __restrict__ xs,
-                                                          int capacity, int C, int K, const int* __restrict__ offsets, int E) {
+                                                          int capacity, int C, int K, const int* __restrict__ offsets, int E,
+                                                          int n_pairs, int* __restrict__ status) {
   const int vec_per_row = C / 8;
   const int used = offsets[E];
   // one (index -> row -> store) chain per thread and pass; four independent chains per thread were measured slower
@@ -126,7 +128,11 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const __nv_bfloat16* _
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
     const int slot = static_cast<int>(i / vec_per_row);
     const int c = static_cast<int>(i % vec_per_row) * 8;
-    const int pr = slot_pair[slot];
+    int pr = slot_pair[slot];
+    if (pr >= n_pairs) {
+      if (status) atomicCAS(status, 0, STATUS_INDEX_RANGE);
+      pr = -1;
+    }
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (pr >= 0) {
       v = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(pr / K) * C + c);
@@ -145,7 +151,8 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const __nv_bfloat16* _
 // out[t, :] = alpha · (Σ_k w[t,k] · y[pair_slot[t·K + k], :] + add[t, :])      (add may be null)
 __global__ void __launch_bounds__(256) combine_rows_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ pair_slot,
                                                            const float* __restrict__ w, __nv_bfloat16* __restrict__ out, int N, int C,
-                                                           int K, const __nv_bfloat16* __restrict__ add, float alpha) {
+                                                           int K, const __nv_bfloat16* __restrict__ add, float alpha, int capacity,
+                                                           int* __restrict__ status) {
   const int vec_per_row = C / 8;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < static_cast<size_t>(N) * vec_per_row;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
@@ -160,6 +167,10 @@ __global__ void __launch_bounds__(256) combine_rows_kernel(const __nv_bfloat16* 
     }
     for (int k = 0; k < K; ++k) {
       const int slot = pair_slot[static_cast<size_t>(t) * K + k];
+      if (slot < 0 || slot >= capacity) {            // a slot outside the row buffer: reported, contributes nothing
+        if (status) atomicCAS(status, 0, STATUS_INDEX_RANGE);
+        continue;
+      }
       const float wk = w ? w[static_cast<size_t>(t) * K + k] : 1.f;
       const uint4 v = *reinterpret_cast<const uint4*>(y + static_cast<size_t>(slot) * C + c);
       const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
@@ -176,11 +187,16 @@ __global__ void __launch_bounds__(256) combine_rows_kernel(const __nv_bfloat16* 
 // dots[pair] = <y[pair_slot[pair], :], g[pair / K, :]>     one warp per pair
 __global__ void __launch_bounds__(256) pair_dots_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ g,
                                                         const int* __restrict__ pair_slot, float* __restrict__ dots, int n_pairs,
-                                                        int C, int K) {
+                                                        int C, int K, int capacity, int* __restrict__ status) {
   const int lane = threadIdx.x & 31;
   const size_t pr = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
   if (pr >= static_cast<size_t>(n_pairs)) return;
-  const __nv_bfloat16* a = y + static_cast<size_t>(pair_slot[pr]) * C;
+  const int slot = pair_slot[pr];
+  if (slot < 0 || slot >= capacity) {                // warp-uniform: every lane reads the same slot
+    if (lane == 0) { if (status) atomicCAS(status, 0, STATUS_INDEX_RANGE); dots[pr] = 0.f; }
+    return;
+  }
+  const __nv_bfloat16* a = y + static_cast<size_t>(slot) * C;
   const __nv_bfloat16* b = g + (pr / K) * C;
   float s = 0.f;
   for (int c = lane * 8; c < C; c += 256) {
@@ -226,26 +242,26 @@ extern "C" int b200_routing_layout(const int* expert_of_pair, int n_pairs, int E
 }
 
 extern "C" int b200_gather_rows(const void* x, const int* slot_pair, const float* pair_scale, void* xs, int capacity, int C,
-                                int K, const int* offsets, int E, cudaStream_t st) {
+                                int K, const int* offsets, int E, cudaStream_t st, int n_pairs, int* status) {
   if (C % 8) return -1;
   gather_rows_kernel<<<148 * 8, 256, 0, st>>>((const __nv_bfloat16*)x, slot_pair, pair_scale, (__nv_bfloat16*)xs, capacity, C, K,
-                                              offsets, E);
+                                              offsets, E, n_pairs, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 extern "C" int b200_combine_rows(const void* y, const int* pair_slot, const float* w, void* out, int N, int C, int K,
-                                 const void* add, float alpha, cudaStream_t st) {
+                                 const void* add, float alpha, cudaStream_t st, int capacity, int* status) {
   if (C % 8) return -1;
   if (N == 0) return 0;
   combine_rows_kernel<<<148 * 8, 256, 0, st>>>((const __nv_bfloat16*)y, pair_slot, w, (__nv_bfloat16*)out, N, C, K,
-                                             (const __nv_bfloat16*)add, alpha);
+                                             (const __nv_bfloat16*)add, alpha, capacity, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 extern "C" int b200_pair_dots(const void* y, const void* g, const int* pair_slot, float* dots, int n_pairs, int C, int K,
-                              cudaStream_t st) {
+                              cudaStream_t st, int capacity, int* status) {
   if (C % 8) return -1;
   if (n_pairs == 0) return 0;
   const size_t threads = static_cast<size_t>(n_pairs) * 32;
   pair_dots_kernel<<<static_cast<int>((threads + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)y, (const __nv_bfloat16*)g,
-                                                                           pair_slot, dots, n_pairs, C, K);
+                                                                           pair_slot, dots, n_pairs, C, K, capacity, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

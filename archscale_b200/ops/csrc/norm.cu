@@ -240,13 +240,19 @@ __global__ void __launch_bounds__(256) add_rmsnorm_bwd_kernel(const TG* __restri
       }
     }
   }
+  // the eight warps add their sums in turn (a lane owns its columns within a warp): a fixed order, so that the weight
+  // gradient repeats bit for bit from run to run, which shared-memory atomics would not give
+  for (int turn = 0; turn < 8; ++turn) {
+    if (warp == turn) {
 #pragma unroll
-  for (int i = 0; i < NCH; ++i)
-    if (FULL || lane * 8 + i * 256 < cols) {
+      for (int i = 0; i < NCH; ++i)
+        if (FULL || lane * 8 + i * 256 < cols) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) atomicAdd(&dw_s[lane * 8 + i * 256 + e], dwacc[i][e]);
+          for (int e = 0; e < 8; ++e) dw_s[lane * 8 + i * 256 + e] += dwacc[i][e];
+        }
     }
-  __syncthreads();
+    __syncthreads();
+  }
   for (int c = threadIdx.x; c < cols; c += blockDim.x) dw_partial[static_cast<size_t>(blockIdx.x) * cols + c] = dw_s[c];
 }
 
@@ -321,11 +327,15 @@ __global__ void __launch_bounds__(256, 2) add_rmsnorm_bwd2_kernel(const TG* __re
       }
     }
   }
+  for (int turn = 0; turn < 8; ++turn) {            // fixed order of the eight warps: repeatable sums (see above)
+    if (warp == turn) {
 #pragma unroll
-  for (int i = 0; i < NCL; ++i)
+      for (int i = 0; i < NCL; ++i)
 #pragma unroll
-    for (int e = 0; e < 8; ++e) atomicAdd(&dw_s[c0 + i * 256 + e], dwacc[i][e]);
-  __syncthreads();
+        for (int e = 0; e < 8; ++e) dw_s[c0 + i * 256 + e] += dwacc[i][e];
+    }
+    __syncthreads();
+  }
   for (int c = threadIdx.x; c < cols; c += blockDim.x) dw_partial[static_cast<size_t>(blockIdx.x) * cols + c] = dw_s[c];
 }
 

@@ -14,7 +14,8 @@ namespace b200 {
 
 // status codes written to the global status word (0 = ok)
 enum : int { STATUS_OK = 0, STATUS_TIMEOUT_FULL = 1, STATUS_TIMEOUT_EMPTY = 2, STATUS_TIMEOUT_TMEM_FULL = 3,
-             STATUS_TIMEOUT_TMEM_EMPTY = 4, STATUS_TIMEOUT_PEER = 5, STATUS_BAD_ARG = 6, STATUS_EP_OVERFLOW = 7 };
+             STATUS_TIMEOUT_TMEM_EMPTY = 4, STATUS_TIMEOUT_PEER = 5, STATUS_BAD_ARG = 6, STATUS_EP_OVERFLOW = 7,
+             STATUS_INDEX_RANGE = 8 /* an index tensor pointed outside its table: the access was skipped */ };
 
 constexpr long long kWaitLimitCycles = 4000000000LL;  // ≈ 2 s at 2 GHz
 

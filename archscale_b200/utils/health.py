@@ -78,6 +78,7 @@ def check_device(ext=None) -> None:
     if code != 0:
         names = {1: "shared-memory stage never filled", 2: "shared-memory stage never released", 3: "accumulator never filled",
                  4: "accumulator never released", 5: "a peer never signalled", 6: "bad kernel argument",
-                 7: "expert-parallel receive buffer too small for the rows routed to this rank"}
+                 7: "expert-parallel receive buffer too small for the rows routed to this rank",
+                 8: "an index tensor pointed outside its table (the access was skipped)"}
         ext.reset_device_status()
         raise PeerFailure(f"a device-side wait timed out: code {code} ({names.get(code, 'unknown')})")
