@@ -9,13 +9,6 @@ from archscale_b200.utils import canary
 pytestmark = pytest.mark.gpu
 
 
-def test_guard_bands_detect_a_stray_write_on_the_host_side():
-    v, raw = canary.guarded((3, 5), torch.float32, "cpu")
-    assert canary.guards_intact(v, raw)
-    raw[canary._GUARD_BYTES + v.numel() * 4 + 2] = 0          # one byte past the end
-    assert not canary.guards_intact(v, raw)
-
-
 def test_kernels_with_caller_provided_outputs_stay_inside_them():
     ext = backend.require_extension()
     torch.manual_seed(0)

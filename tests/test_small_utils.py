@@ -93,3 +93,25 @@ def test_moe_ffn_adds_the_shared_output_and_the_mix_on_cpu():
     assert torch.allclose(out, ref, atol=1e-5)
     for a, b in ((x.grad, xr.grad), (w_in.grad, wir.grad), (w_out.grad, wor.grad), (shared.grad, shr.grad)):
         assert torch.allclose(a, b, atol=1e-5)
+
+
+def test_guard_bands_and_run_twice_comparison():
+    import torch
+    from archscale_b200.utils import canary
+    v, raw = canary.guarded((3, 5), torch.float32, "cpu")
+    assert v.shape == (3, 5) and float(v.abs().sum()) == 0.0 and canary.guards_intact(v, raw)
+    v.fill_(7.0)                                               # writes inside the tensor leave the bands alone
+    assert canary.guards_intact(v, raw)
+    raw[canary._GUARD_BYTES + v.numel() * 4 + 2] = 0           # one byte past the end
+    assert not canary.guards_intact(v, raw)
+    v2, raw2 = canary.guarded((4,), torch.bfloat16, "cpu")
+    raw2[canary._GUARD_BYTES - 1] = 0                          # one byte before the start
+    assert not canary.guards_intact(v2, raw2)
+    x = torch.randn(8, 8)
+    assert canary.bitwise_repeatable(lambda: (x @ x, None, [x + 1]))
+    state = {"n": 0}
+
+    def drifting():
+        state["n"] += 1
+        return x + state["n"] * 1e-7
+    assert not canary.bitwise_repeatable(drifting)
